@@ -1,0 +1,76 @@
+// Shared helpers of the sm_100a kernels: error reporting through the C ABI,
+// bfloat16 widening and rounding, fixed-order block reductions.
+//
+// Every exported function returns 0 on success. On a refused argument or a CUDA
+// error it returns non-zero and leaves a message that `sb_last_error()` of the
+// same library returns; nothing is launched after a refused argument.
+#pragma once
+
+#include <cuda_bf16.h>
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+#include <cstdarg>
+#include <cstdio>
+
+#define SB_EXPORT extern "C" __attribute__((visibility("default")))
+
+namespace sb {
+
+inline char* error_buffer() {
+  static thread_local char buf[512] = {0};
+  return buf;
+}
+
+inline int fail(const char* fmt, ...) {
+  va_list ap;
+  va_start(ap, fmt);
+  vsnprintf(error_buffer(), 512, fmt, ap);
+  va_end(ap);
+  return 1;
+}
+
+inline int check_launch(const char* what) {
+  cudaError_t e = cudaGetLastError();
+  if (e != cudaSuccess) return fail("%s: %s", what, cudaGetErrorString(e));
+  return 0;
+}
+
+__device__ __forceinline__ float widen(float v) { return v; }
+__device__ __forceinline__ float widen(__nv_bfloat16 v) { return __bfloat162float(v); }
+
+template <class T>
+__device__ __forceinline__ T narrow(float v);
+template <>
+__device__ __forceinline__ float narrow<float>(float v) { return v; }
+template <>
+__device__ __forceinline__ __nv_bfloat16 narrow<__nv_bfloat16>(float v) { return __float2bfloat16_rn(v); }
+
+// Sum over the block in an order that depends only on blockDim: lanes by xor
+// shuffles, then the warps' sums left to right. Every thread gets the result.
+__device__ __forceinline__ float block_sum(float v, float* smem32) {
+  for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, nwarps = (blockDim.x + 31) >> 5;
+  __syncthreads();
+  if (lane == 0) smem32[warp] = v;
+  __syncthreads();
+  float total = smem32[0];
+  for (int i = 1; i < nwarps; ++i) total += smem32[i];
+  return total;
+}
+
+__device__ __forceinline__ float block_max(float v, float* smem32) {
+  for (int o = 16; o > 0; o >>= 1) v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, o));
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, nwarps = (blockDim.x + 31) >> 5;
+  __syncthreads();
+  if (lane == 0) smem32[warp] = v;
+  __syncthreads();
+  float total = smem32[0];
+  for (int i = 1; i < nwarps; ++i) total = fmaxf(total, smem32[i]);
+  return total;
+}
+
+}  // namespace sb
+
+#define SB_DEFINE_LAST_ERROR() \
+  SB_EXPORT const char* sb_last_error() { return sb::error_buffer(); }

@@ -1,0 +1,226 @@
+// Memory-bound kernels of the decoder that are no contraction: embedding lookup,
+// RMSNorm (fused with the reduction of split-K partial sums into the residual),
+// rotary position encoding fused with the append to the paged cache, the SwiGLU
+// product, and the row gather before the head. All arithmetic is 32-bit; only
+// loads and stores may be bfloat16.
+//
+// Counterparts in arhaamatiq/stride: Embed (src/kernels.cu:98-116), RmsNorm
+// (src/kernels.cu:119-200), the rotation and append at the end of Qkv
+// (src/kernels.cu:247-281), the activation of Mlp13 (src/kernels.cu:359-360),
+// Compact (src/kernels.cu:365-380).
+#include "common.cuh"
+
+SB_DEFINE_LAST_ERROR()
+
+namespace {
+
+using bf16 = __nv_bfloat16;
+
+// ------------------------------------------------------------------ embedding
+template <class TW>
+__global__ void embed_kernel(const int32_t* __restrict__ tokens, const TW* __restrict__ table,
+                             float* __restrict__ out, int H, int vocab) {
+  const int row = blockIdx.x;
+  const int tok = tokens[row];
+  const bool ok = tok >= 0 && tok < vocab;
+  const TW* src = table + static_cast<int64_t>(ok ? tok : 0) * H;
+  float* dst = out + static_cast<int64_t>(row) * H;
+  for (int i = threadIdx.x; i < H; i += blockDim.x) dst[i] = ok ? sb::widen(src[i]) : 0.0f;
+}
+
+// ------------------------------------------------------------------ rmsnorm
+// One block per row. The row is (h + partial_0 + partial_1 + ...), summed left to
+// right; when partials are given the sum is written back to h. Then
+// r = 1/sqrt(sum(x^2)/H + eps) and out = w * (x * r).
+template <class TW, class TO>
+__global__ void rmsnorm_kernel(float* __restrict__ h, const float* __restrict__ partials, int n_partials,
+                               int64_t partial_stride, const TW* __restrict__ weight, TO* __restrict__ out,
+                               int H, float eps) {
+  extern __shared__ float row[];
+  __shared__ float red[32];
+  const int r = blockIdx.x;
+  float* hr = h + static_cast<int64_t>(r) * H;
+  float ss = 0.0f;
+  for (int i = threadIdx.x; i < H; i += blockDim.x) {
+    float v = hr[i];
+    for (int s = 0; s < n_partials; ++s) v += partials[s * partial_stride + static_cast<int64_t>(r) * H + i];
+    if (n_partials > 0) hr[i] = v;
+    row[i] = v;
+    ss = fmaf(v, v, ss);
+  }
+  const float total = sb::block_sum(ss, red);
+  const float scale = 1.0f / sqrtf(total / static_cast<float>(H) + eps);
+  TO* o = out + static_cast<int64_t>(r) * H;
+  for (int i = threadIdx.x; i < H; i += blockDim.x) o[i] = sb::narrow<TO>(sb::widen(weight[i]) * (row[i] * scale));
+}
+
+// ------------------------------------------------------------------ rope + append
+struct RopeAppendParams {
+  const float* qkv;          // [n_partials][n][(Hq + 2 Hkv) D], partials summed left to right
+  int n_partials;
+  int64_t partial_stride;
+  const int32_t* positions;  // [n]
+  const int32_t* slots;      // [n]
+  const float* cos_sin;      // [max_pos][rotary_dim / 2][2]
+  int rotary_dim;
+  void* q_out;               // [n][Hq D]
+  void* k_base;              // this layer's key plane of page 0
+  const int32_t* block_table;  // [slots][max_pages]
+  int max_pages;
+  int page_size;
+  int64_t page_stride;  // elements between pages
+  int64_t v_offset;     // elements from a page's keys to its values
+  int64_t head_stride;  // elements between kv heads (= page_size * D)
+  int Hq, Hkv, D;
+  int write_kv;
+};
+
+template <class TQ, class TKV>
+__global__ void rope_append_kernel(RopeAppendParams p) {
+  const int row = blockIdx.x;
+  const int pos = p.positions[row];
+  const int slot = p.slots[row];
+  const int D = p.D, half = D / 2, rh = p.rotary_dim / 2;
+  const int heads = p.Hq + 2 * p.Hkv;
+  const int width = heads * D;
+  const float* cs = p.cos_sin + static_cast<int64_t>(pos) * rh * 2;
+  int64_t kv_at = 0;
+  if (p.write_kv) {
+    const int page = p.block_table[static_cast<int64_t>(slot) * p.max_pages + pos / p.page_size];
+    kv_at = static_cast<int64_t>(page) * p.page_stride + static_cast<int64_t>(pos % p.page_size) * D;
+  }
+  for (int item = threadIdx.x; item < heads * half; item += blockDim.x) {
+    const int head = item / half, j = item % half;
+    int d0, d1;
+    if (j < rh) {
+      d0 = j;
+      d1 = j + rh;
+    } else {
+      d0 = p.rotary_dim + 2 * (j - rh);
+      d1 = d0 + 1;
+    }
+    const int64_t at = static_cast<int64_t>(row) * width + static_cast<int64_t>(head) * D;
+    float a = p.qkv[at + d0], b = p.qkv[at + d1];
+    for (int s = 1; s < p.n_partials; ++s) {
+      a += p.qkv[s * p.partial_stride + at + d0];
+      b += p.qkv[s * p.partial_stride + at + d1];
+    }
+    const bool is_v = head >= p.Hq + p.Hkv;
+    if (j < rh && !is_v) {
+      const float c = cs[2 * j], s = cs[2 * j + 1];
+      const float ra = __fsub_rn(__fmul_rn(a, c), __fmul_rn(b, s));
+      const float rb = __fadd_rn(__fmul_rn(b, c), __fmul_rn(a, s));
+      a = ra;
+      b = rb;
+    }
+    if (head < p.Hq) {
+      TQ* q = static_cast<TQ*>(p.q_out) + static_cast<int64_t>(row) * p.Hq * D + static_cast<int64_t>(head) * D;
+      q[d0] = sb::narrow<TQ>(a);
+      q[d1] = sb::narrow<TQ>(b);
+    } else if (p.write_kv) {
+      const int kvh = is_v ? head - p.Hq - p.Hkv : head - p.Hq;
+      TKV* dst = static_cast<TKV*>(p.k_base) + kv_at + static_cast<int64_t>(kvh) * p.head_stride + (is_v ? p.v_offset : 0);
+      dst[d0] = sb::narrow<TKV>(a);
+      dst[d1] = sb::narrow<TKV>(b);
+    }
+  }
+}
+
+// ------------------------------------------------------------------ swiglu
+template <class TO>
+__global__ void swiglu_kernel(const float* __restrict__ gate_up, TO* __restrict__ out, int n, int I) {
+  const int64_t total = static_cast<int64_t>(n) * I;
+  for (int64_t i = blockIdx.x * static_cast<int64_t>(blockDim.x) + threadIdx.x; i < total;
+       i += static_cast<int64_t>(gridDim.x) * blockDim.x) {
+    const int64_t r = i / I, c = i % I;
+    const float a = gate_up[r * 2 * I + c], b = gate_up[r * 2 * I + I + c];
+    out[i] = sb::narrow<TO>((a / (1.0f + expf(-a))) * b);
+  }
+}
+
+// ------------------------------------------------------------------ gather
+__global__ void gather_rows_kernel(const float* __restrict__ in, const float* __restrict__ partials, int n_partials,
+                                   int64_t partial_stride, const int32_t* __restrict__ rows,
+                                   float* __restrict__ out, int H) {
+  const int src = rows[blockIdx.x];
+  for (int i = threadIdx.x; i < H; i += blockDim.x) {
+    float v = in[static_cast<int64_t>(src) * H + i];
+    for (int s = 0; s < n_partials; ++s) v += partials[s * partial_stride + static_cast<int64_t>(src) * H + i];
+    out[static_cast<int64_t>(blockIdx.x) * H + i] = v;
+  }
+}
+
+}  // namespace
+
+// dtype codes shared with the Python side: 0 = float32, 1 = bfloat16.
+
+SB_EXPORT int sb_embed(const int32_t* tokens, const void* table, int table_dtype, float* out, int n, int H, int vocab,
+                       cudaStream_t stream) {
+  if (n <= 0) return 0;
+  if (table_dtype == 0)
+    embed_kernel<float><<<n, 256, 0, stream>>>(tokens, static_cast<const float*>(table), out, H, vocab);
+  else if (table_dtype == 1)
+    embed_kernel<bf16><<<n, 256, 0, stream>>>(tokens, static_cast<const bf16*>(table), out, H, vocab);
+  else
+    return sb::fail("sb_embed: unsupported table dtype %d", table_dtype);
+  return sb::check_launch("sb_embed");
+}
+
+SB_EXPORT int sb_rmsnorm(float* h, const float* partials, int n_partials, int64_t partial_stride, const void* weight,
+                         int weight_dtype, void* out, int out_dtype, int n, int H, float eps, cudaStream_t stream) {
+  if (n <= 0) return 0;
+  const size_t smem = static_cast<size_t>(H) * sizeof(float);
+  if (smem > 200 * 1024) return sb::fail("sb_rmsnorm: width %d does not fit the row buffer (max 51200)", H);
+  const int threads = H >= 1024 ? 256 : 128;
+#define SB_NORM(TW, TO)                                                                                          \
+  do {                                                                                                           \
+    if (smem > 48 * 1024)                                                                                        \
+      cudaFuncSetAttribute(rmsnorm_kernel<TW, TO>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);      \
+    rmsnorm_kernel<TW, TO><<<n, threads, smem, stream>>>(h, partials, n_partials, partial_stride,               \
+                                                         static_cast<const TW*>(weight), static_cast<TO*>(out), H, eps); \
+  } while (0)
+  if (weight_dtype == 0 && out_dtype == 0) SB_NORM(float, float);
+  else if (weight_dtype == 0 && out_dtype == 1) SB_NORM(float, bf16);
+  else if (weight_dtype == 1 && out_dtype == 0) SB_NORM(bf16, float);
+  else if (weight_dtype == 1 && out_dtype == 1) SB_NORM(bf16, bf16);
+  else return sb::fail("sb_rmsnorm: unsupported dtypes weight=%d out=%d", weight_dtype, out_dtype);
+#undef SB_NORM
+  return sb::check_launch("sb_rmsnorm");
+}
+
+SB_EXPORT int sb_rope_append(const float* qkv, int n_partials, int64_t partial_stride, const int32_t* positions,
+                             const int32_t* slots, const float* cos_sin, int rotary_dim, void* q_out, int q_dtype,
+                             void* k_base, int kv_dtype, const int32_t* block_table, int max_pages, int page_size,
+                             int64_t page_stride, int64_t v_offset, int64_t head_stride, int n, int Hq, int Hkv, int D,
+                             int write_kv, cudaStream_t stream) {
+  if (n <= 0) return 0;
+  if (D % 2 != 0 || rotary_dim % 2 != 0 || rotary_dim > D || rotary_dim < 0)
+    return sb::fail("sb_rope_append: head_dim %d / rotary_dim %d must be even and rotary_dim <= head_dim", D, rotary_dim);
+  if (n_partials < 1) return sb::fail("sb_rope_append: n_partials must be >= 1");
+  RopeAppendParams p{qkv, n_partials, partial_stride, positions, slots, cos_sin, rotary_dim, q_out, k_base,
+                     block_table, max_pages, page_size, page_stride, v_offset, head_stride, Hq, Hkv, D, write_kv};
+  const int threads = 256;
+  if (q_dtype == 0 && kv_dtype == 0) rope_append_kernel<float, float><<<n, threads, 0, stream>>>(p);
+  else if (q_dtype == 1 && kv_dtype == 1) rope_append_kernel<bf16, bf16><<<n, threads, 0, stream>>>(p);
+  else if (q_dtype == 0 && kv_dtype == 1) rope_append_kernel<float, bf16><<<n, threads, 0, stream>>>(p);
+  else if (q_dtype == 1 && kv_dtype == 0) rope_append_kernel<bf16, float><<<n, threads, 0, stream>>>(p);
+  else return sb::fail("sb_rope_append: unsupported dtypes q=%d kv=%d", q_dtype, kv_dtype);
+  return sb::check_launch("sb_rope_append");
+}
+
+SB_EXPORT int sb_swiglu(const float* gate_up, void* out, int out_dtype, int n, int I, cudaStream_t stream) {
+  if (n <= 0) return 0;
+  const int64_t total = static_cast<int64_t>(n) * I;
+  const int blocks = static_cast<int>((total + 255) / 256 < 148 * 16 ? (total + 255) / 256 : 148 * 16);
+  if (out_dtype == 0) swiglu_kernel<float><<<blocks, 256, 0, stream>>>(gate_up, static_cast<float*>(out), n, I);
+  else if (out_dtype == 1) swiglu_kernel<bf16><<<blocks, 256, 0, stream>>>(gate_up, static_cast<bf16*>(out), n, I);
+  else return sb::fail("sb_swiglu: unsupported out dtype %d", out_dtype);
+  return sb::check_launch("sb_swiglu");
+}
+
+SB_EXPORT int sb_gather_rows(const float* in, const float* partials, int n_partials, int64_t partial_stride,
+                             const int32_t* rows, float* out, int count, int H, cudaStream_t stream) {
+  if (count <= 0) return 0;
+  gather_rows_kernel<<<count, 256, 0, stream>>>(in, partials, n_partials, partial_stride, rows, out, H);
+  return sb::check_launch("sb_gather_rows");
+}

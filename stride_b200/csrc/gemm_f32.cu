@@ -1,0 +1,103 @@
+// True 32-bit linear layer: out[n, M] (+)= x[n, K] . W[M, K]^T with FMA on the
+// CUDA cores, no tensor cores and no reduced-precision matrix mode. Weights may be
+// stored in bfloat16 (widened exactly) or in float32. Every output element is one
+// chain of fused multiply-adds over k = 0 .. K-1 in ascending order, whatever the
+// number of rows n, so a token's result does not depend on its batch.
+//
+// Counterparts in arhaamatiq/stride: gemm_partial and its users GemmResidual,
+// Mlp13, LmFull of the exact path (src/kernels.cu:63-94, 294-325, 329-363, 427-452).
+#include "common.cuh"
+
+SB_DEFINE_LAST_ERROR()
+
+namespace {
+
+using bf16 = __nv_bfloat16;
+
+constexpr int TM = 64;  // rows of x (tokens) per block
+constexpr int TN = 64;  // rows of W (output features) per block
+constexpr int TK = 16;
+
+template <class TX, class TW, bool ACC>
+__global__ void __launch_bounds__(256) gemm_f32_kernel(const TX* __restrict__ x, int64_t ldx,
+                                                        const TW* __restrict__ w, int64_t ldw,
+                                                        float* __restrict__ out, int64_t ldo, int n, int M, int K) {
+  __shared__ float xs[TK][TM + 4];
+  __shared__ float ws[TK][TN + 4];
+  const int t = threadIdx.x;
+  const int row0 = blockIdx.y * TM, col0 = blockIdx.x * TN;
+  const int ty = t / 16, tx = t % 16;  // 16 x 16 threads, each 4 x 4 outputs
+  float acc[4][4];
+#pragma unroll
+  for (int i = 0; i < 4; ++i)
+#pragma unroll
+    for (int j = 0; j < 4; ++j) acc[i][j] = 0.0f;
+
+  const int lr = t / 4;        // 0..63: tile row loaded by this thread
+  const int lk = (t % 4) * 4;  // 0,4,8,12: first k of its four
+  for (int k0 = 0; k0 < K; k0 += TK) {
+#pragma unroll
+    for (int e = 0; e < 4; ++e) {
+      const int k = k0 + lk + e;
+      const int xr = row0 + lr, wr = col0 + lr;
+      xs[lk + e][lr] = (xr < n && k < K) ? sb::widen(x[static_cast<int64_t>(xr) * ldx + k]) : 0.0f;
+      ws[lk + e][lr] = (wr < M && k < K) ? sb::widen(w[static_cast<int64_t>(wr) * ldw + k]) : 0.0f;
+    }
+    __syncthreads();
+#pragma unroll
+    for (int k = 0; k < TK; ++k) {
+      float a[4], b[4];
+#pragma unroll
+      for (int i = 0; i < 4; ++i) a[i] = xs[k][ty * 4 + i];
+#pragma unroll
+      for (int j = 0; j < 4; ++j) b[j] = ws[k][tx * 4 + j];
+#pragma unroll
+      for (int i = 0; i < 4; ++i)
+#pragma unroll
+        for (int j = 0; j < 4; ++j) acc[i][j] = fmaf(a[i], b[j], acc[i][j]);
+    }
+    __syncthreads();
+  }
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    const int r = row0 + ty * 4 + i;
+    if (r >= n) continue;
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      const int c = col0 + tx * 4 + j;
+      if (c >= M) continue;
+      float* o = out + static_cast<int64_t>(r) * ldo + c;
+      *o = ACC ? (*o + acc[i][j]) : acc[i][j];
+    }
+  }
+}
+
+}  // namespace
+
+// out[n, M] = x . W^T, or out += x . W^T when `accumulate` is set (the residual add).
+// x_dtype, weight_dtype: 0 = float32, 1 = bfloat16 (widened exactly; the products and
+// sums are float32 either way). Leading dimensions in elements.
+SB_EXPORT int sb_gemm_f32(const void* x, int x_dtype, int64_t ldx, const void* w, int weight_dtype, int64_t ldw, float* out,
+                          int64_t ldo, int n, int M, int K, int accumulate, cudaStream_t stream) {
+  if (n <= 0 || M <= 0) return 0;
+  if (K <= 0) return sb::fail("sb_gemm_f32: K must be positive");
+  dim3 grid((M + TN - 1) / TN, (n + TM - 1) / TM);
+  if (grid.y > 65535) return sb::fail("sb_gemm_f32: %d rows exceed the grid (max %d)", n, 65535 * TM);
+#define SB_GEMM(TX, TW, ACC)                                                                          \
+  gemm_f32_kernel<TX, TW, ACC><<<grid, 256, 0, stream>>>(static_cast<const TX*>(x), ldx, static_cast<const TW*>(w), \
+                                                          ldw, out, ldo, n, M, K)
+#define SB_GEMM_W(TX)                                                     \
+  do {                                                                    \
+    if (weight_dtype == 0 && accumulate) SB_GEMM(TX, float, true);        \
+    else if (weight_dtype == 0) SB_GEMM(TX, float, false);                \
+    else if (accumulate) SB_GEMM(TX, bf16, true);                         \
+    else SB_GEMM(TX, bf16, false);                                        \
+  } while (0)
+  if (weight_dtype != 0 && weight_dtype != 1) return sb::fail("sb_gemm_f32: unsupported weight dtype %d", weight_dtype);
+  if (x_dtype == 0) SB_GEMM_W(float);
+  else if (x_dtype == 1) SB_GEMM_W(bf16);
+  else return sb::fail("sb_gemm_f32: unsupported activation dtype %d", x_dtype);
+#undef SB_GEMM_W
+#undef SB_GEMM
+  return sb::check_launch("sb_gemm_f32");
+}

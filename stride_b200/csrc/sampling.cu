@@ -1,0 +1,195 @@
+// Token choice on the device: argmax (greedy) and temperature sampling.
+//
+// Greedy keeps the largest logit and, among equal logits, the smallest index,
+// whatever the order in which threads meet them.
+//
+// Temperature sampling restates arhaamatiq/stride's host sampler
+// (src/scheduler.cpp:193-243) without sorting: tokens are ranked by (logit
+// descending, index ascending), weight_i = exp((l_i - l_max) / T) in 64-bit,
+// u = uniform * sum of weights, and the token is the first in rank order whose
+// cumulative weight exceeds u. The rank order is walked by a radix search over
+// the logit's bit pattern (four passes of eight bits, weighted histograms).
+// The uniform is keyed on (seed, length of the sequence) alone:
+// r = splitmix64(seed ^ (length * 0x9E3779B97F4A7C15)), uniform = (r >> 11) * 2^-53,
+// so a draw does not depend on the batch or the schedule.
+#include "common.cuh"
+
+SB_DEFINE_LAST_ERROR()
+
+namespace {
+
+constexpr int kThreads = 1024;
+
+__device__ __forceinline__ uint32_t order_key(float v) {
+  const uint32_t b = __float_as_uint(v);
+  return (b & 0x80000000u) ? ~b : (b | 0x80000000u);
+}
+
+__device__ __forceinline__ unsigned long long splitmix64(unsigned long long x) {
+  x += 0x9E3779B97F4A7C15ULL;
+  x = (x ^ (x >> 30)) * 0xBF58476D1CE4E5B9ULL;
+  x = (x ^ (x >> 27)) * 0x94D049BB133111EBULL;
+  return x ^ (x >> 31);
+}
+
+// (value, index) -> one 64-bit word whose unsigned order is value ascending, then index descending.
+__device__ __forceinline__ unsigned long long pack_best(float v, int idx) {
+  return (static_cast<unsigned long long>(order_key(v)) << 32) | (0xFFFFFFFFu - static_cast<uint32_t>(idx));
+}
+
+__global__ void __launch_bounds__(kThreads) argmax_kernel(const float* __restrict__ logits, int64_t ld, int vocab,
+                                                           int32_t* __restrict__ tokens, float* __restrict__ values) {
+  __shared__ unsigned long long best_s[32];
+  const float* l = logits + static_cast<int64_t>(blockIdx.x) * ld;
+  unsigned long long best = 0;
+  for (int i = threadIdx.x; i < vocab; i += kThreads) {
+    const float v = l[i];
+    if (v == v) {
+      const unsigned long long c = pack_best(v, i);
+      best = c > best ? c : best;
+    }
+  }
+  for (int o = 16; o > 0; o >>= 1) {
+    const unsigned long long other = __shfl_xor_sync(0xffffffffu, best, o);
+    best = other > best ? other : best;
+  }
+  if ((threadIdx.x & 31) == 0) best_s[threadIdx.x >> 5] = best;
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    for (int i = 1; i < kThreads / 32; ++i) best = best_s[i] > best ? best_s[i] : best;
+    const int idx = best == 0 ? 0 : static_cast<int>(0xFFFFFFFFu - static_cast<uint32_t>(best & 0xFFFFFFFFu));
+    tokens[blockIdx.x] = idx;
+    values[blockIdx.x] = l[idx];
+  }
+}
+
+__global__ void __launch_bounds__(kThreads) sample_temperature_kernel(
+    const float* __restrict__ logits, int64_t ld, int vocab, const float* __restrict__ temperatures,
+    const unsigned long long* __restrict__ seeds, const int32_t* __restrict__ lengths, int32_t* __restrict__ tokens,
+    float* __restrict__ values) {
+  __shared__ double hist[256];
+  __shared__ int count[256];
+  __shared__ float red[32];
+  __shared__ double dred[32];
+  __shared__ uint32_t prefix_s;
+  __shared__ double u_s;
+  __shared__ int found_s;
+  const int row = blockIdx.x, t = threadIdx.x;
+  const float* l = logits + static_cast<int64_t>(row) * ld;
+  const double T = static_cast<double>(temperatures[row]);
+
+  float mx = -INFINITY;
+  for (int i = t; i < vocab; i += kThreads) {
+    const float v = l[i];
+    if (v == v) mx = fmaxf(mx, v);
+  }
+  mx = sb::block_max(mx, red);
+  const double top = static_cast<double>(mx);
+
+  // Sum of the weights, in a fixed order: per thread ascending, lanes by shuffle, warps left to right.
+  double sum = 0.0;
+  for (int i = t; i < vocab; i += kThreads) {
+    const float v = l[i];
+    if (v == v) sum += exp((static_cast<double>(v) - top) / T);
+  }
+  for (int o = 16; o > 0; o >>= 1) sum += __shfl_xor_sync(0xffffffffu, sum, o);
+  if ((t & 31) == 0) dred[t >> 5] = sum;
+  __syncthreads();
+  if (t == 0) {
+    double total = 0.0;
+    for (int i = 0; i < kThreads / 32; ++i) total += dred[i];
+    const unsigned long long r =
+        splitmix64(seeds[row] ^ (static_cast<unsigned long long>(static_cast<uint32_t>(lengths[row])) * 0x9E3779B97F4A7C15ULL));
+    u_s = static_cast<double>(r >> 11) * (1.0 / 9007199254740992.0) * total;
+    prefix_s = 0;
+  }
+  __syncthreads();
+
+  for (int shift = 24; shift >= 0; shift -= 8) {
+    for (int b = t; b < 256; b += kThreads) {
+      hist[b] = 0.0;
+      count[b] = 0;
+    }
+    __syncthreads();
+    const uint32_t prefix = prefix_s;
+    const uint32_t mask = shift == 24 ? 0u : (0xFFFFFFFFu << (shift + 8));
+    for (int i = t; i < vocab; i += kThreads) {
+      const float v = l[i];
+      if (v != v) continue;
+      const uint32_t key = order_key(v);
+      if ((key & mask) != prefix) continue;
+      const int b = (key >> shift) & 0xFF;
+      atomicAdd(&hist[b], exp((static_cast<double>(v) - top) / T));
+      atomicAdd(&count[b], 1);
+    }
+    __syncthreads();
+    if (t == 0) {
+      double u = u_s, cum = 0.0;
+      int chosen = -1, lowest = 0;
+      for (int b = 255; b >= 0; --b) {
+        if (count[b] == 0) continue;
+        lowest = b;
+        if (u < cum + hist[b]) {
+          chosen = b;
+          break;
+        }
+        cum += hist[b];
+      }
+      if (chosen < 0) {  // u is not below the total (rounding): the last token in rank order
+        chosen = lowest;
+        cum = 0.0;
+        u = hist[lowest];  // past every token of the bucket, so the last one is taken below
+      }
+      u_s = u - cum;
+      prefix_s = prefix | (static_cast<uint32_t>(chosen) << shift);
+      found_s = count[chosen];
+    }
+    __syncthreads();
+  }
+
+  // Every token whose key is prefix_s has the same logit and weight; they rank by index.
+  const uint32_t key = prefix_s;
+  if (found_s == 1) {
+    for (int i = t; i < vocab; i += kThreads) {
+      const float v = l[i];
+      if (v == v && order_key(v) == key) {
+        tokens[row] = i;
+        values[row] = v;
+      }
+    }
+  } else if (t == 0) {
+    int first = -1;
+    for (int i = 0; i < vocab && first < 0; ++i)
+      if (l[i] == l[i] && order_key(l[i]) == key) first = i;
+    const double w = exp((static_cast<double>(l[first]) - top) / T);
+    int skip = w > 0.0 ? static_cast<int>(fmin(u_s / w, static_cast<double>(found_s - 1))) : found_s - 1;
+    int pick = first;
+    for (int i = first; i < vocab; ++i) {
+      if (l[i] == l[i] && order_key(l[i]) == key) {
+        pick = i;
+        if (skip-- == 0) break;
+      }
+    }
+    tokens[row] = pick;
+    values[row] = l[pick];
+  }
+}
+
+}  // namespace
+
+SB_EXPORT int sb_argmax(const float* logits, int64_t ld, int rows, int vocab, int32_t* tokens, float* values,
+                        cudaStream_t stream) {
+  if (rows <= 0) return 0;
+  if (vocab <= 0) return sb::fail("sb_argmax: empty vocabulary");
+  argmax_kernel<<<rows, kThreads, 0, stream>>>(logits, ld, vocab, tokens, values);
+  return sb::check_launch("sb_argmax");
+}
+
+SB_EXPORT int sb_sample_temperature(const float* logits, int64_t ld, int rows, int vocab, const float* temperatures,
+                                    const unsigned long long* seeds, const int32_t* lengths, int32_t* tokens,
+                                    float* values, cudaStream_t stream) {
+  if (rows <= 0) return 0;
+  if (vocab <= 0) return sb::fail("sb_sample_temperature: empty vocabulary");
+  sample_temperature_kernel<<<rows, kThreads, 0, stream>>>(logits, ld, vocab, temperatures, seeds, lengths, tokens, values);
+  return sb::check_launch("sb_sample_temperature");
+}

@@ -1,0 +1,159 @@
+"""Python faces of the CUDA kernels: torch tensors in, raw pointers down.
+
+Every function here launches hand-written CUDA from `stride_b200/csrc` on the
+current torch stream. There is no torch or CPU implementation behind them: a
+tensor that is not on a CUDA device, or a library that cannot be built, raises.
+"""
+from __future__ import annotations
+
+import ctypes
+from ctypes import c_float, c_int, c_int64, c_void_p
+
+import torch
+
+from .build import library
+
+F32, BF16 = 0, 1
+_DTYPE_CODE = {torch.float32: F32, torch.bfloat16: BF16}
+
+_configured: set = set()
+
+
+def dtype_code(dtype: torch.dtype) -> int:
+    try:
+        return _DTYPE_CODE[dtype]
+    except KeyError:
+        raise TypeError(f"stride_b200 kernels take float32 or bfloat16 tensors, not {dtype}") from None
+
+
+def _fn(lib_name: str, fn_name: str, argtypes):
+    lib = library(lib_name)
+    fn = getattr(lib, fn_name)
+    if (lib_name, fn_name) not in _configured:
+        fn.argtypes = argtypes
+        fn.restype = c_int
+        _configured.add((lib_name, fn_name))
+    return lib, fn
+
+
+def _check(lib, rc: int) -> None:
+    if rc != 0:
+        raise RuntimeError(lib.sb_last_error().decode(errors="replace"))
+
+
+def _cuda(*tensors) -> None:
+    for t in tensors:
+        if t is not None and not t.is_cuda:
+            raise RuntimeError("stride_b200 kernels run on CUDA tensors only; got a tensor on " + str(t.device))
+
+
+def _ptr(t) -> int:
+    return 0 if t is None else t.data_ptr()
+
+
+def _stream() -> int:
+    return torch.cuda.current_stream().cuda_stream
+
+
+def embed(tokens: torch.Tensor, table: torch.Tensor, out: torch.Tensor) -> None:
+    """out[i, :] = float32(table[tokens[i], :])."""
+    _cuda(tokens, table, out)
+    lib, fn = _fn("elementwise", "sb_embed", [c_void_p, c_void_p, c_int, c_void_p, c_int, c_int, c_int, c_void_p])
+    n, H = out.shape
+    _check(lib, fn(_ptr(tokens), _ptr(table), dtype_code(table.dtype), _ptr(out), n, H, table.shape[0], _stream()))
+
+
+def rmsnorm(h: torch.Tensor, weight: torch.Tensor, eps: float, out: torch.Tensor, partials=None) -> None:
+    """out = weight * (x / sqrt(mean(x^2) + eps)) with x = h (+ partials[0] + partials[1] ...).
+
+    `partials` [S, n, H] float32 are summed into h left to right and h is updated in place.
+    """
+    _cuda(h, weight, out, partials)
+    lib, fn = _fn("elementwise", "sb_rmsnorm", [c_void_p, c_void_p, c_int, c_int64, c_void_p, c_int, c_void_p, c_int,
+                                               c_int, c_int, c_float, c_void_p])
+    n, H = h.shape
+    S = 0 if partials is None else partials.shape[0]
+    stride = 0 if partials is None else partials.stride(0)
+    _check(lib, fn(_ptr(h), _ptr(partials), S, stride, _ptr(weight), dtype_code(weight.dtype), _ptr(out),
+                   dtype_code(out.dtype), n, H, eps, _stream()))
+
+
+def rope_append(qkv: torch.Tensor, positions, slots, cos_sin, rotary_dim: int, q_out, cache_layer, block_table,
+                num_heads: int, num_kv_heads: int, head_dim: int, write_kv: bool = True) -> None:
+    """Rotate q and k of `qkv` [S, n, (Hq + 2 Hkv) D] (partials summed), store q, append k and v to the pages.
+
+    `cache_layer` is this layer's view [pages, 2, Hkv, page_size, D] of the arena.
+    """
+    _cuda(qkv, positions, slots, cos_sin, q_out, cache_layer, block_table)
+    lib, fn = _fn("elementwise", "sb_rope_append",
+                  [c_void_p, c_int, c_int64, c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_int, c_void_p, c_int,
+                   c_void_p, c_int, c_int, c_int64, c_int64, c_int64, c_int, c_int, c_int, c_int, c_int, c_void_p])
+    if qkv.dim() == 2:
+        qkv = qkv.unsqueeze(0)
+    S, n, _ = qkv.shape
+    _check(lib, fn(_ptr(qkv), S, qkv.stride(0), _ptr(positions), _ptr(slots), _ptr(cos_sin), rotary_dim, _ptr(q_out),
+                   dtype_code(q_out.dtype), _ptr(cache_layer), dtype_code(cache_layer.dtype), _ptr(block_table),
+                   block_table.shape[1], cache_layer.shape[3], cache_layer.stride(0), cache_layer.stride(1),
+                   cache_layer.stride(2), n, num_heads, num_kv_heads, head_dim, int(write_kv), _stream()))
+
+
+def swiglu(gate_up: torch.Tensor, out: torch.Tensor) -> None:
+    """out[n, I] = silu(gate_up[:, :I]) * gate_up[:, I:]."""
+    _cuda(gate_up, out)
+    lib, fn = _fn("elementwise", "sb_swiglu", [c_void_p, c_void_p, c_int, c_int, c_int, c_void_p])
+    n, I = out.shape
+    _check(lib, fn(_ptr(gate_up), _ptr(out), dtype_code(out.dtype), n, I, _stream()))
+
+
+def gather_rows(src: torch.Tensor, rows: torch.Tensor, out: torch.Tensor, partials=None) -> None:
+    """out[i, :] = src[rows[i], :] (+ partials[s, rows[i], :] for every s)."""
+    _cuda(src, rows, out, partials)
+    lib, fn = _fn("elementwise", "sb_gather_rows", [c_void_p, c_void_p, c_int, c_int64, c_void_p, c_void_p, c_int, c_int, c_void_p])
+    S = 0 if partials is None else partials.shape[0]
+    stride = 0 if partials is None else partials.stride(0)
+    _check(lib, fn(_ptr(src), _ptr(partials), S, stride, _ptr(rows), _ptr(out), out.shape[0], out.shape[1], _stream()))
+
+
+def gemm_f32(x: torch.Tensor, weight: torch.Tensor, out: torch.Tensor, accumulate: bool = False) -> None:
+    """out[n, M] (+)= x[n, K] . weight[M, K]^T in true 32-bit FMA; x and weight float32 or bfloat16."""
+    _cuda(x, weight, out)
+    if out.dtype != torch.float32:
+        raise TypeError("gemm_f32 writes float32")
+    lib, fn = _fn("gemm_f32", "sb_gemm_f32", [c_void_p, c_int, c_int64, c_void_p, c_int, c_int64, c_void_p, c_int64, c_int,
+                                              c_int, c_int, c_int, c_void_p])
+    n, K = x.shape
+    M = weight.shape[0]
+    if weight.shape[1] != K or out.shape[0] != n or out.shape[1] != M:
+        raise ValueError(f"gemm_f32 shapes: x {tuple(x.shape)}, weight {tuple(weight.shape)}, out {tuple(out.shape)}")
+    _check(lib, fn(_ptr(x), dtype_code(x.dtype), x.stride(0), _ptr(weight), dtype_code(weight.dtype), weight.stride(0), _ptr(out),
+                   out.stride(0), n, M, K, int(accumulate), _stream()))
+
+
+def attention_generic(q, out, cache_layer, block_table, positions, slots, num_heads: int, num_kv_heads: int,
+                      head_dim: int, window: int, scale: float) -> None:
+    """Causal paged attention of every token of the step over its request's cache (any head size)."""
+    _cuda(q, out, cache_layer, block_table, positions, slots)
+    if not (q.dtype == out.dtype == cache_layer.dtype):
+        raise TypeError("attention_generic takes q, out and cache of one dtype")
+    lib, fn = _fn("attention_generic", "sb_attention_generic",
+                  [c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_int, c_int, c_int64, c_int64, c_int64, c_void_p,
+                   c_void_p, c_int, c_int, c_int, c_int, c_int, c_float, c_void_p])
+    _check(lib, fn(_ptr(q), _ptr(out), dtype_code(q.dtype), _ptr(cache_layer), _ptr(block_table), block_table.shape[1],
+                   cache_layer.shape[3], cache_layer.stride(0), cache_layer.stride(1), cache_layer.stride(2),
+                   _ptr(positions), _ptr(slots), q.shape[0], num_heads, num_kv_heads, head_dim, window, scale, _stream()))
+
+
+def argmax(logits: torch.Tensor, tokens: torch.Tensor, values: torch.Tensor) -> None:
+    """tokens[i] = index of the largest logit of row i (smallest index among equals); values[i] = that logit."""
+    _cuda(logits, tokens, values)
+    lib, fn = _fn("sampling", "sb_argmax", [c_void_p, c_int64, c_int, c_int, c_void_p, c_void_p, c_void_p])
+    _check(lib, fn(_ptr(logits), logits.stride(0), logits.shape[0], logits.shape[1], _ptr(tokens), _ptr(values), _stream()))
+
+
+def sample_temperature(logits, temperatures, seeds, lengths, tokens, values) -> None:
+    """Temperature sampling keyed on (seed, sequence length) for every row; see csrc/sampling.cu."""
+    _cuda(logits, temperatures, seeds, lengths, tokens, values)
+    lib, fn = _fn("sampling", "sb_sample_temperature", [c_void_p, c_int64, c_int, c_int, c_void_p, c_void_p, c_void_p,
+                                                        c_void_p, c_void_p, c_void_p])
+    _check(lib, fn(_ptr(logits), logits.stride(0), logits.shape[0], logits.shape[1], _ptr(temperatures), _ptr(seeds),
+                   _ptr(lengths), _ptr(tokens), _ptr(values), _stream()))

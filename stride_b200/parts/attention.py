@@ -1,0 +1,88 @@
+"""Grouped-query attention over the paged cache.
+
+One step of it, for all tokens of the batch at once: q, k, v = W x; rotate q and k
+by the position encoding; append k and v to the request's pages; every token then
+attends to the keys of its own request at positions first..pos (its own included),
+first = 0 or pos - window + 1; the result goes through the output projection
+into the residual. Order and formulas as in arhaamatiq/stride (Qkv: src/kernels.cu:204-284;
+attention: src/kernel_common.h:90-309; scale = float(pow(double(D), -0.5)), src/engine.cpp:151;
+output projection added to the residual: src/kernels.cu:294-325). The token's own key is in the
+cache before attention runs, so a portion of a prompt needs no mask tensor.
+"""
+from __future__ import annotations
+
+import math
+
+import numpy as np
+import torch
+
+from ..kernels import ops
+from ..kernels.linear import Linear
+from .base import CacheNeed, Mixer, part_class, register_part
+from .spec import TensorPlan
+
+
+@register_part("mixer", "attention")
+class AttentionMixer(Mixer):
+    """params: hidden_size, num_heads, num_kv_heads, head_dim, window (0 = all keys),
+    position (a PartSpec of category "position", or None), scale (default head_dim ** -0.5).
+    tensors: q, k, v, o."""
+
+    def __init__(self, spec, env):
+        super().__init__(spec, env)
+        p = spec.params
+        self.hidden = int(p["hidden_size"])
+        self.num_heads = int(p["num_heads"])
+        self.num_kv_heads = int(p["num_kv_heads"])
+        self.head_dim = int(p["head_dim"])
+        self.window = int(p.get("window", 0) or 0)
+        if self.num_heads % self.num_kv_heads:
+            raise ValueError(f"attention: {self.num_heads} heads do not divide into {self.num_kv_heads} key/value heads")
+        scale = p.get("scale")
+        self.scale = float(np.float32(math.pow(float(self.head_dim), -0.5))) if scale is None else float(scale)
+        pos = p.get("position")
+        self.position = part_class("position", pos.kind)(pos, env) if pos is not None else None
+        self.qkv = self.o = None
+
+    @property
+    def qkv_width(self):
+        return (self.num_heads + 2 * self.num_kv_heads) * self.head_dim
+
+    def tensor_plan(self):
+        t, D = self.spec.tensors, self.head_dim
+        return {t["q"]: TensorPlan((self.num_heads * D, self.hidden)),
+                t["k"]: TensorPlan((self.num_kv_heads * D, self.hidden)),
+                t["v"]: TensorPlan((self.num_kv_heads * D, self.hidden)),
+                t["o"]: TensorPlan((self.hidden, self.num_heads * D))}
+
+    def bind(self, tensors):
+        t = self.spec.tensors
+        q, k, v = tensors[t["q"]], tensors[t["k"]], tensors[t["v"]]
+        if not (q.dtype == k.dtype == v.dtype):
+            q, k, v = (w.to(torch.float32) for w in (q, k, v))
+        self.qkv = Linear(torch.cat([q, k, v], dim=0), self.env.compute_dtype)
+        self.o = Linear(tensors[t["o"]], self.env.compute_dtype)
+        if self.position is None:
+            # No rotation: a table of cos = 1, sin = 0 is never read because rotary_dim is 0.
+            self._cos_sin, self._rotary = torch.zeros(1, device=self.env.device), 0
+        else:
+            self._cos_sin, self._rotary = self.position.cos_sin, self.position.rotary_dim
+
+    def weight_bytes(self):
+        return self.qkv.weight_bytes() + self.o.weight_bytes()
+
+    def cache_need(self):
+        return CacheNeed("pages", kv_heads=self.num_kv_heads, head_dim=self.head_dim, window=self.window,
+                         dtype=self.env.act_dtype)
+
+    def forward(self, ctx, x, stream, cache):
+        n, ws, D = ctx.n, ctx.workspace, self.head_dim
+        qkv = ws.get("attn.qkv", n, (self.qkv_width,), torch.float32)
+        self.qkv.forward(x, qkv)
+        q = ws.get("attn.q", n, (self.num_heads * D,), ctx.act_dtype)
+        ops.rope_append(qkv, ctx.positions, ctx.slots, self._cos_sin, self._rotary, q, cache.pages, cache.block_table,
+                        self.num_heads, self.num_kv_heads, D, write_kv=cache.writes)
+        mixed = ws.get("attn.out", n, (self.num_heads * D,), ctx.act_dtype)
+        ops.attention_generic(q, mixed, cache.pages, cache.block_table, ctx.positions, ctx.slots,
+                              self.num_heads, self.num_kv_heads, D, self.window, self.scale)
+        self.o.forward_add(mixed, stream)

@@ -1,0 +1,83 @@
+"""A decoder put together from a `ModelSpec`: embedding, layers run in the order the
+schedule gives, final norm and head on the rows whose logits are wanted."""
+from __future__ import annotations
+
+import torch
+
+from ..kernels import ops
+from .base import BuildEnv, part_class
+from .context import ResidualStream
+from .spec import ModelSpec
+
+
+class DecoderModel:
+    def __init__(self, spec: ModelSpec, env: BuildEnv):
+        self.spec, self.env = spec, env
+        self.embedding = part_class("embedding", spec.embedding.kind)(spec.embedding, env)
+        self.blocks = []
+        for layer in spec.layers:
+            mixer = part_class("mixer", layer.mixer.kind)(layer.mixer, env)
+            ff = part_class("feed_forward", layer.feed_forward.kind)(layer.feed_forward, env)
+            n1 = part_class("norm", layer.mixer_norm.kind)(layer.mixer_norm, env)
+            n2 = part_class("norm", layer.feed_forward_norm.kind)(layer.feed_forward_norm, env)
+            self.blocks.append(part_class("block", layer.block)(layer, env, mixer, ff, n1, n2))
+        self.final_norm = part_class("norm", spec.final_norm.kind)(spec.final_norm, env)
+        self.head = part_class("head", spec.head.kind)(spec.head, env)
+        for i, e in enumerate(spec.schedule):
+            if not 0 <= e.layer < len(self.blocks):
+                raise ValueError(f"schedule entry {i} names layer {e.layer}, but the model has {len(self.blocks)} layers")
+            if e.cache_of is not None and not 0 <= e.cache_of < i:
+                raise ValueError(f"schedule entry {i} reads the cache of entry {e.cache_of}, which does not run before it")
+
+    def _parts(self):
+        return [self.embedding, *self.blocks, self.final_norm, self.head]
+
+    def tensor_plan(self) -> dict:
+        plan = {}
+        for p in self._parts():
+            for name, want in p.tensor_plan().items():
+                if name in plan and plan[name].shape != want.shape:
+                    raise ValueError(f"tensor '{name}' is expected with shapes {plan[name].shape} and {want.shape}")
+                if name not in plan or plan[name].optional:
+                    plan[name] = want
+        return plan
+
+    def bind(self, tensors: dict) -> None:
+        for p in self._parts():
+            p.bind(tensors)
+
+    def cache_needs(self) -> list:
+        """Per schedule entry: a CacheNeed, None, or ("shared", j)."""
+        needs = []
+        for e in self.spec.schedule:
+            needs.append(("shared", e.cache_of) if e.cache_of is not None else self.blocks[e.layer].mixer.cache_need())
+        return needs
+
+    def weight_bytes(self) -> int:
+        """Bytes of weights that one decode step reads: every scheduled layer once, the final
+        norm and the head (arhaamatiq/stride counts the same, src/model.cpp:198,235)."""
+        total = self.final_norm.weight_bytes() + self.head.weight_bytes()
+        for e in self.spec.schedule:
+            total += self.blocks[e.layer].weight_bytes()
+        return total
+
+    def forward(self, ctx, caches: list, logit_rows: torch.Tensor, count: int):
+        """Run the step's tokens through the model; returns logits [count, vocab] float32 for the
+        rows listed in `logit_rows` (int32, device), or None when count is 0."""
+        ws, H = ctx.workspace, self.spec.hidden_size
+        stream = ResidualStream(ws.get("model.h", ctx.n, (H,), torch.float32))
+        self.embedding.forward(ctx, stream.h)
+        for i, e in enumerate(self.spec.schedule):
+            self.blocks[e.layer].forward(ctx, stream, caches[i])
+        if count == 0:
+            stream.fold()
+            return None
+        rows = ws.raw("model.head_rows", (ws.max_tokens, H), torch.float32)[:count]
+        ops.gather_rows(stream.h, logit_rows, rows, partials=stream.take_pending())
+        x = ws.raw("model.head_x", (ws.max_tokens, H), ctx.act_dtype)[:count]
+        self.final_norm.forward_rows(rows, x)
+        if count > self.env.max_logit_rows:
+            raise ValueError(f"logits are wanted at {count} places, more than the engine's max_logit_rows {self.env.max_logit_rows}")
+        logits = ws.raw("model.logits", (self.env.max_logit_rows, self.spec.vocab_size), torch.float32)[:count]
+        self.head.forward(x, logits)
+        return logits

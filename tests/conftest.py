@@ -1,0 +1,124 @@
+"""Shared fixtures: tiny configurations of the architecture, model folders with random
+weights in a temporary place, and the replay harness."""
+from __future__ import annotations
+
+import json
+import os
+import subprocess
+import sys
+from pathlib import Path
+
+import numpy as np
+import pytest
+import torch
+
+ROOT = Path(__file__).resolve().parents[1]
+sys.path.insert(0, str(ROOT))
+sys.path.insert(0, str(Path(__file__).resolve().parent))
+
+
+def pytest_configure(config):
+    config.addinivalue_line("markers", "gpu: needs a CUDA device (sm_100a)")
+
+
+def pytest_collection_modifyitems(config, items):
+    if torch.cuda.is_available():
+        return
+    skip = pytest.mark.skip(reason="no CUDA device")
+    for item in items:
+        if "gpu" in item.keywords:
+            item.add_marker(skip)
+
+
+# Three tiny configurations that differ in every size and option.
+TINY_A = {
+    "architectures": ["LlamaForCausalLM"], "hidden_size": 64, "intermediate_size": 128, "num_hidden_layers": 2,
+    "num_attention_heads": 4, "num_key_value_heads": 2, "head_dim": 16, "vocab_size": 256, "rope_theta": 10000.0,
+    "tie_word_embeddings": True, "rms_norm_eps": 1e-5, "max_position_embeddings": 128,
+}
+TINY_B = {
+    "architectures": ["LlamaForCausalLM"], "hidden_size": 192, "intermediate_size": 320, "num_hidden_layers": 3,
+    "num_attention_heads": 6, "num_key_value_heads": 2, "head_dim": 32, "vocab_size": 384, "rope_theta": 500000.0,
+    "rope_scaling": {"rope_type": "llama3", "factor": 32.0, "low_freq_factor": 1.0, "high_freq_factor": 4.0,
+                     "original_max_position_embeddings": 64},
+    "tie_word_embeddings": False, "rms_norm_eps": 1e-6, "max_position_embeddings": 256,
+}
+# Sizes that are no power of two, head_dim that is not hidden/heads, ratio 1, one more layer count.
+TINY_C = {
+    "model_type": "llama", "hidden_size": 88, "intermediate_size": 136, "num_hidden_layers": 1,
+    "num_attention_heads": 3, "num_key_value_heads": 3, "head_dim": 48, "vocab_size": 333, "rope_theta": 2500.0,
+    "rope_scaling": {"type": "llama3", "factor": 8.0, "low_freq_factor": 1.0, "high_freq_factor": 4.0,
+                     "original_max_position_embeddings": 32},
+    "rms_norm_eps": 3e-4, "max_position_embeddings": 192,
+}
+TINY = {"A": (TINY_A, 0, 64), "B": (TINY_B, 2, 8), "C": (TINY_C, 5, 16)}   # config, weight seed, page size
+
+# Weights N(0, 0.2) and gains 1 + 0.2 N(0, 1): large enough that attention is far from uniform and
+# every part changes the logits, as arhaamatiq/stride's own tiny model does (tests/make_tiny_model.py:19-54).
+TEST_STD, TEST_GAIN_STD = 0.2, 0.2
+
+
+@pytest.fixture(scope="session")
+def model_dirs(tmp_path_factory):
+    """name -> model folder written by the framework's random-weights mode."""
+    from stride_b200.weights.random_init import write_random_model
+    root = tmp_path_factory.mktemp("models")
+    out = {}
+    for name, (cfg, seed, _) in TINY.items():
+        out[name] = write_random_model(root / name, cfg, seed, std=TEST_STD, gain_std=TEST_GAIN_STD)
+    return out
+
+
+def random_tokens(vocab: int, n: int, seed: int) -> list:
+    g = torch.Generator().manual_seed(seed)
+    return torch.randint(0, vocab, (n,), generator=g).tolist()
+
+
+class TraceRun:
+    """Drives bin/trace_run as a user would: one JSON line per step on its standard input, the next
+    step only after `done <step>` came back."""
+
+    def __init__(self, model_dir, dtype: str, out_dir, max_tokens: int, page_size: int = 64, extra=()):
+        self.out_dir = Path(out_dir)
+        cmd = [sys.executable, str(ROOT / "bin" / "trace_run"), "--model", str(model_dir), "--dtype", dtype,
+               "--out", str(out_dir), "--max-tokens", str(max_tokens), "--page-size", str(page_size), *extra]
+        self.proc = subprocess.Popen(cmd, stdin=subprocess.PIPE, stdout=subprocess.PIPE, text=True, bufsize=1)
+        self.step = 0
+
+    def run(self, entries: list, end=()) -> int:
+        """entries: [(id, tokens, want)]. Returns the step number."""
+        s = self.step
+        rec = {"step": s, "entries": [{"id": i, "tokens": list(t), "want": list(w)} for i, t, w in entries], "end": list(end)}
+        self.proc.stdin.write(json.dumps(rec) + "\n")
+        self.proc.stdin.flush()
+        line = self.proc.stdout.readline()
+        if line.strip() != f"done {s}":
+            self.proc.wait(timeout=60)
+            raise AssertionError(f"trace_run answered {line!r} to step {s} (exit code {self.proc.returncode})")
+        self.step += 1
+        return s
+
+    def logits(self, step: int, vocab: int) -> torch.Tensor:
+        return torch.from_numpy(np.fromfile(self.out_dir / f"{step}.f32", dtype="<f4").reshape(-1, vocab).copy())
+
+    def close(self) -> int:
+        self.proc.stdin.close()
+        rc = self.proc.wait(timeout=120)
+        assert rc == 0, f"trace_run exited with {rc}"
+        return rc
+
+
+def logit_tolerance(dtype: str, reference: torch.Tensor) -> float:
+    """Largest allowed |engine - plain| over a set of logits.
+
+    float32: 2e-4 absolute at logits of rms ~1-2, the bound arhaamatiq/stride's own suite uses
+    for its exact path (tests/test_correctness.py:21), scaled with the rms for other magnitudes.
+    bfloat16: compared with the plain implementation rounding to bfloat16 at the same places; what is
+    left are sums taken in another order that flip a rounding now and then, each flip worth 2^-8
+    of one activation. 3% of the logits' rms bounds that for these depths and is far below what a
+    wrong key, page or position costs (tens of percent).
+    """
+    rms = float(reference.float().pow(2).mean().sqrt())
+    if dtype == "float32":
+        return 2e-4 * max(rms, 1.0)
+    return 3e-2 * rms
