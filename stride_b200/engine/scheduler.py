@@ -1,0 +1,270 @@
+"""Continuous batching above the step function.
+
+Each `step()`: drop cancelled requests; admit waiting requests while slots and pages
+allow; plan the batch under the token budget (every request with exactly one unprocessed
+token first, one row each; then portions of prompts, at most `prefill_chunk` tokens per
+request, in running order); if the plan needs more pages than are free, preempt the
+youngest running request (its slot and pages go back, it returns to the FRONT of the
+waiting queue and is later recomputed from its first token, prompt and generated tokens
+alike) and plan again; run the batch through `Engine.step`; choose a token for every
+request whose last known token was in the batch; finish on a stop token ("stop") or on
+max_new_tokens ("length") and give slot and pages back.
+
+This restates arhaamatiq/stride's Scheduler (src/scheduler.cpp:72-304) including its
+admission rule (free pages >= pages of the prompt + one page of growth per running request
++ one, unless nothing is running) and its failure when a single running request does not
+fit ("KV arena too small for one sequence"). Requests longer than the context capacity, or
+empty, finish at intake with "context_length" / "empty_prompt" (src/scheduler.cpp:82-89).
+"""
+from __future__ import annotations
+
+import threading
+from collections import deque
+from dataclasses import dataclass, field
+from typing import Callable, Optional
+
+import numpy as np
+
+from ..sampling.sampler import Sampler, SamplingParams, splitmix64
+from .engine import Engine, EngineError, StepEntry
+
+_FNV_OFFSET = 14695981039346656037
+_FNV_PRIME = 1099511628211
+_MASK = (1 << 64) - 1
+
+
+def _fnv_mix(h: int, v: int) -> int:
+    for i in range(4):
+        h ^= (v >> (i * 8)) & 0xFF
+        h = (h * _FNV_PRIME) & _MASK
+    return h
+
+
+def _float_bits(v: float) -> int:
+    return int(np.float32(v).view(np.uint32))
+
+
+@dataclass
+class TokenEvent:
+    token: int = -1
+    value: float = 0.0
+    index: int = 0                 # 0-based index among the generated tokens
+    finished: bool = False
+    finish_reason: Optional[str] = None
+    fingerprint: int = 0           # FNV-1a over (token, bits of its logit) of all tokens so far
+
+
+@dataclass
+class GenRequest:
+    prompt: list
+    max_new_tokens: int = 16
+    sampling: SamplingParams = field(default_factory=SamplingParams)
+    stop_tokens: tuple = ()
+    full_logits: bool = False      # pass the logits row to on_token at every generated token
+    on_token: Optional[Callable] = None    # on_token(event, logits or None)
+    cancelled: Optional[threading.Event] = None
+
+
+@dataclass
+class SchedulerOptions:
+    max_seqs: int = 256            # most requests running at once
+    max_rows: int = 256            # token budget of one step
+    prefill_chunk: int = 64        # most prompt tokens of one request in one step
+    row_shuffle_seed: int = 0      # tests: shuffle the order of the requests inside a batch
+
+
+@dataclass
+class SchedulerStats:
+    steps: int = 0
+    rows: int = 0
+    generated: int = 0
+    preemptions: int = 0
+    replayed_rows: int = 0
+    peak_seqs: int = 0
+    peak_blocks: int = 0
+
+
+class _Seq:
+    __slots__ = ("req", "tokens", "prompt_len", "next_pos", "generated", "slot", "arrival", "fingerprint", "done")
+
+    def __init__(self, req: GenRequest, arrival: int):
+        self.req = req
+        self.tokens = list(req.prompt)
+        self.prompt_len = len(self.tokens)
+        self.next_pos = 0
+        self.generated = 0
+        self.slot = -1
+        self.arrival = arrival
+        self.fingerprint = _FNV_OFFSET
+        self.done = False
+
+
+class Scheduler:
+    def __init__(self, engine: Engine, options: Optional[SchedulerOptions] = None, sampler=None):
+        self.engine = engine
+        self.opts = options or SchedulerOptions()
+        if self.opts.max_rows > engine.options.max_rows:
+            raise EngineError(f"scheduler max_rows {self.opts.max_rows} exceeds the engine's {engine.options.max_rows}")
+        self.stats = SchedulerStats()
+        self._mu = threading.Lock()
+        self._incoming: deque = deque()
+        self._waiting: deque = deque()
+        self._running: list = []
+        self._arrival = 0
+        self._rng_state = self.opts.row_shuffle_seed
+        self._sampler = sampler or Sampler(engine.device, engine.env.max_logit_rows)
+
+    # ------------------------------------------------------------------ intake
+    def submit(self, request: GenRequest) -> None:
+        """Thread-safe."""
+        with self._mu:
+            self._incoming.append(request)
+
+    def idle(self) -> bool:
+        with self._mu:
+            return not (self._incoming or self._waiting or self._running)
+
+    def _finish(self, seq: _Seq) -> None:
+        seq.done = True
+        if seq.slot >= 0:
+            self.engine.cache.release_slot(seq.slot)
+            seq.slot = -1
+
+    def _page_need(self, tokens: int) -> list:
+        ps = self.engine.cache.page_size
+        return [(tokens + ps - 1) // ps for _ in self.engine.cache.groups]
+
+    def _admit(self) -> None:
+        cache = self.engine.cache
+        capacity = self.engine.max_context
+        with self._mu:
+            while self._incoming:
+                seq = _Seq(self._incoming.popleft(), self._arrival)
+                self._arrival += 1
+                room = capacity - seq.prompt_len
+                if room <= 0 or seq.prompt_len == 0:
+                    if seq.req.on_token:
+                        seq.req.on_token(TokenEvent(finished=True, finish_reason="empty_prompt" if seq.prompt_len == 0
+                                                    else "context_length"), None)
+                    continue
+                seq.req.max_new_tokens = min(seq.req.max_new_tokens, room)
+                self._waiting.append(seq)
+        while self._waiting and len(self._running) < self.opts.max_seqs:
+            nxt = self._waiting[0]
+            if nxt.req.cancelled is not None and nxt.req.cancelled.is_set():
+                self._waiting.popleft()
+                continue
+            # Keep room for one page of growth per running request before admitting another.
+            reserve = len(self._running) + 1
+            need = self._page_need(len(nxt.tokens))
+            if self._running and any(f < n + reserve for f, n in zip(cache.free_pages(), need)):
+                break
+            slot = cache.acquire_slot()
+            if slot < 0:
+                break
+            nxt.slot = slot
+            nxt.next_pos = 0        # (re)computed from the first token: its pages were given back on preemption
+            self._running.append(self._waiting.popleft())
+        self.stats.peak_seqs = max(self.stats.peak_seqs, len(self._running))
+
+    def _preempt_youngest(self) -> None:
+        victim = max(self._running, key=lambda s: s.arrival)
+        self.engine.cache.release_slot(victim.slot)
+        victim.slot = -1
+        self.stats.preemptions += 1
+        self.stats.replayed_rows += victim.next_pos
+        self._running.remove(victim)
+        self._waiting.appendleft(victim)
+
+    # ------------------------------------------------------------------ planning
+    def plan(self):
+        """[(sequence, tokens to run)] for the next step, pages ensured; None if nothing is to run."""
+        cache = self.engine.cache
+        while True:
+            plan = []
+            budget = self.opts.max_rows
+            for s in self._running:
+                if len(s.tokens) - s.next_pos == 1 and budget > 0:
+                    plan.append((s, 1))
+                    budget -= 1
+            for s in self._running:
+                remaining = len(s.tokens) - s.next_pos
+                if remaining > 1 and budget > 0:
+                    chunk = min(remaining, self.opts.prefill_chunk, budget)
+                    plan.append((s, chunk))
+                    budget -= chunk
+            if not plan:
+                return None
+            need = [0] * len(cache.groups)
+            for s, count in plan:
+                for g, k in enumerate(cache.pages_needed(s.slot, s.next_pos + count)):
+                    need[g] += k
+            if any(n > f for n, f in zip(need, cache.free_pages())):
+                if len(self._running) <= 1:
+                    raise EngineError("the cache pool is too small for one sequence")
+                self._preempt_youngest()
+                continue
+            for s, count in plan:
+                if not cache.ensure(s.slot, s.next_pos + count):
+                    raise EngineError("page accounting failed: ensure() refused a planned allocation")
+            if self.opts.row_shuffle_seed:
+                for i in range(len(plan) - 1, 0, -1):
+                    self._rng_state = splitmix64(self._rng_state)
+                    j = self._rng_state % (i + 1)
+                    plan[i], plan[j] = plan[j], plan[i]
+            return plan
+
+    # ------------------------------------------------------------------ one step
+    def step(self) -> bool:
+        """Run one engine step. False when nothing is queued or running."""
+        cache = self.engine.cache
+        for s in list(self._running):
+            if s.req.cancelled is not None and s.req.cancelled.is_set():
+                cache.release_slot(s.slot)
+                self._running.remove(s)
+        self._admit()
+        plan = self.plan()
+        if plan is None:
+            return False
+        entries, wanted = [], []
+        for s, count in plan:
+            a = s.next_pos
+            last = a + count == len(s.tokens)
+            entries.append(StepEntry(slot=s.slot, first_pos=a, tokens=s.tokens[a:a + count], want=[count - 1] if last else []))
+            if last:
+                wanted.append(s)
+            s.next_pos += count
+        logits = self.engine.step(entries)
+        self.stats.steps += 1
+        self.stats.rows += sum(c for _, c in plan)
+        used = max((t - f for t, f in zip(cache.total_pages(), cache.free_pages())), default=0)
+        self.stats.peak_blocks = max(self.stats.peak_blocks, used)
+        if wanted:
+            tokens, values = self._sampler.choose(logits, [s.req.sampling for s in wanted], [len(s.tokens) for s in wanted])
+            full = None
+            if any(s.req.full_logits and s.req.on_token for s in wanted):
+                full = logits.to("cpu").numpy()
+            for i, s in enumerate(wanted):
+                tok, val = int(tokens[i]), float(values[i])
+                s.fingerprint = _fnv_mix(_fnv_mix(s.fingerprint, tok & 0xFFFFFFFF), _float_bits(val))
+                s.tokens.append(tok)
+                s.generated += 1
+                self.stats.generated += 1
+                ev = TokenEvent(token=tok, value=val, index=s.generated - 1, fingerprint=s.fingerprint)
+                if tok in s.req.stop_tokens:
+                    ev.finished, ev.finish_reason = True, "stop"
+                elif s.generated >= s.req.max_new_tokens:
+                    ev.finished, ev.finish_reason = True, "length"
+                if s.req.on_token:
+                    s.req.on_token(ev, full[i] if (full is not None and s.req.full_logits) else None)
+                if ev.finished:
+                    self._finish(s)
+        for s in self._running:
+            if not s.done:
+                cache.trim(s.slot)
+        self._running = [s for s in self._running if not s.done]
+        return True
+
+    def run(self) -> None:
+        while self.step():
+            pass

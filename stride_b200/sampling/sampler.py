@@ -1,0 +1,121 @@
+"""Choosing the next token from logits.
+
+`SamplingParams` and the rule are arhaamatiq/stride's (src/scheduler.h:20-25,
+src/scheduler.cpp:193-243): temperature <= 0 takes the largest logit (the smallest index
+among equals); otherwise tokens are ranked by (logit descending, index ascending), cut to
+top_k if > 0, weighted by exp((l - l_max) / T) in 64-bit, cut to the shortest prefix whose
+normalised cumulative weight reaches top_p if < 1, and the token is the first whose
+cumulative weight exceeds u = uniform * total. The uniform is keyed on (seed, number of
+tokens the sequence has) only, never on a stream, so a request's draws do not depend
+on what else was scheduled with it.
+
+Greedy rows and plain temperature rows are chosen by CUDA kernels (`csrc/sampling.cu`);
+rows with top_k or top_p are chosen on the host from the downloaded logits, as the
+reference does for all rows.
+"""
+from __future__ import annotations
+
+import math
+from dataclasses import dataclass
+
+import numpy as np
+import torch
+
+from ..kernels import ops
+
+_MASK = (1 << 64) - 1
+
+
+@dataclass
+class SamplingParams:
+    temperature: float = 0.0
+    top_p: float = 1.0
+    top_k: int = 0
+    seed: int = 0
+
+
+def splitmix64(x: int) -> int:
+    x = (x + 0x9E3779B97F4A7C15) & _MASK
+    x = ((x ^ (x >> 30)) * 0xBF58476D1CE4E5B9) & _MASK
+    x = ((x ^ (x >> 27)) * 0x94D049BB133111EB) & _MASK
+    return x ^ (x >> 31)
+
+
+def keyed_uniform(seed: int, length: int) -> float:
+    """In [0, 1): depends on the request's seed and its sequence length only."""
+    r = splitmix64((seed & _MASK) ^ ((length * 0x9E3779B97F4A7C15) & _MASK))
+    return float(r >> 11) * (1.0 / 9007199254740992.0)
+
+
+def choose_token_host(logits: np.ndarray, params: SamplingParams, length: int):
+    """The full rule on the host, in 64-bit. Returns (token, its logit)."""
+    l = np.asarray(logits, dtype=np.float32)
+    valid = ~np.isnan(l)
+    best = int(np.argmax(np.where(valid, l, -np.inf)))
+    if params.temperature <= 0.0:
+        return best, float(l[best])
+    order = np.lexsort((np.arange(l.shape[0]), -l.astype(np.float64)))
+    count = l.shape[0]
+    if params.top_k > 0:
+        count = min(count, params.top_k)
+    t = float(np.float32(params.temperature))
+    ranked = l[order[:count]].astype(np.float64)
+    probs = np.exp((ranked - ranked[0]) / t)
+    total = math.fsum([]) if count == 0 else float(np.cumsum(probs)[-1])
+    if params.top_p < 1.0:
+        cum = np.cumsum(probs / total)
+        kept = int(np.searchsorted(cum, float(np.float32(params.top_p)), side="left")) + 1
+        count = min(kept, count)
+        probs = probs[:count]
+        total = float(np.cumsum(probs)[-1])
+    u = keyed_uniform(params.seed, length) * total
+    cum = np.cumsum(probs)
+    i = int(np.searchsorted(cum, u, side="right"))
+    i = min(i, count - 1)
+    tok = int(order[i])
+    return tok, float(l[tok])
+
+
+class Sampler:
+    """Chooses tokens for the rows of one step's logits."""
+
+    def __init__(self, device, max_rows: int):
+        self.device = torch.device(device)
+        self.max_rows = max_rows
+        self._tokens = torch.zeros(2, max_rows, dtype=torch.int32, device=self.device)
+        self._values = torch.zeros(2, max_rows, dtype=torch.float32, device=self.device)
+        self._temps = torch.zeros(max_rows, dtype=torch.float32, device=self.device)
+        self._seeds = torch.zeros(max_rows, dtype=torch.int64, device=self.device)
+        self._lengths = torch.zeros(max_rows, dtype=torch.int32, device=self.device)
+        self._host_tokens = torch.zeros(2, max_rows, dtype=torch.int32, pin_memory=True)
+        self._host_values = torch.zeros(2, max_rows, dtype=torch.float32, pin_memory=True)
+
+    def choose(self, logits: torch.Tensor, params: list, lengths: list):
+        """logits [rows, vocab] on the device; params[i], lengths[i] belong to row i (length = tokens the
+        sequence has before the new one). Returns (tokens list, values list)."""
+        rows = logits.shape[0]
+        if rows > self.max_rows:
+            raise ValueError(f"{rows} rows exceed the sampler's {self.max_rows}")
+        ops.argmax(logits, self._tokens[0, :rows], self._values[0, :rows])
+        device_rows = [i for i, p in enumerate(params) if p.temperature > 0.0 and p.top_k <= 0 and p.top_p >= 1.0]
+        host_rows = [i for i, p in enumerate(params) if p.temperature > 0.0 and not (p.top_k <= 0 and p.top_p >= 1.0)]
+        if device_rows:
+            temps = torch.tensor([max(p.temperature, 1e-30) if p.temperature > 0 else 1.0 for p in params], dtype=torch.float32)
+            seeds = torch.tensor([np.uint64(p.seed & _MASK).astype(np.int64) for p in params], dtype=torch.int64)
+            self._temps[:rows].copy_(temps)
+            self._seeds[:rows].copy_(seeds)
+            self._lengths[:rows].copy_(torch.tensor(lengths, dtype=torch.int32))
+            ops.sample_temperature(logits, self._temps[:rows], self._seeds[:rows], self._lengths[:rows],
+                                   self._tokens[1, :rows], self._values[1, :rows])
+        self._host_tokens[:, :rows].copy_(self._tokens[:, :rows], non_blocking=True)
+        self._host_values[:, :rows].copy_(self._values[:, :rows], non_blocking=True)
+        host_logits = logits[host_rows].to("cpu") if host_rows else None
+        torch.cuda.current_stream().synchronize()
+        tokens = self._host_tokens[0, :rows].tolist()
+        values = self._host_values[0, :rows].tolist()
+        for i in device_rows:
+            tokens[i] = int(self._host_tokens[1, i])
+            values[i] = float(self._host_values[1, i])
+        for k, i in enumerate(host_rows):
+            tokens[i], values[i] = choose_token_host(host_logits[k].numpy(), params[i], lengths[i])
+        return tokens, values
