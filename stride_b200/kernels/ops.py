@@ -36,7 +36,12 @@ def _fn(lib_name: str, fn_name: str, argtypes):
     return lib, fn
 
 
+launches = 0    # kernels launched through this module since import (bench.py reports the difference)
+
+
 def _check(lib, rc: int) -> None:
+    global launches
+    launches += 1
     if rc != 0:
         raise RuntimeError(lib.sb_last_error().decode(errors="replace"))
 

@@ -12,6 +12,7 @@ from __future__ import annotations
 import json
 import mmap
 import struct
+import warnings
 from pathlib import Path
 
 import numpy as np
@@ -85,7 +86,9 @@ class SafetensorsFile:
         if end == begin:
             return torch.empty(shape, dtype=tdt)
         buf = memoryview(self._map)[self._data_start + begin:self._data_start + end]
-        flat = torch.frombuffer(buf, dtype=tdt)
+        with warnings.catch_warnings():
+            warnings.simplefilter("ignore", UserWarning)     # the map is read-only; callers copy, never write
+            flat = torch.frombuffer(buf, dtype=tdt)
         return flat.reshape(shape)
 
     def close(self):
