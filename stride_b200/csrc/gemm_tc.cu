@@ -1,0 +1,430 @@
+// Linear layers of the bfloat16 path on the 5th-generation tensor cores (sm_100a):
+// D[m, n] = sum_k W[m, k] * X[n, k], W [M, K] and X [N, K] bfloat16 with K contiguous,
+// float32 accumulation in tensor memory.
+//
+// One CTA computes a tile of 128 weight rows (the M operand of tcgen05.mma, one TMEM
+// lane per row) by BN tokens (the N operand, one TMEM column per token), BN in
+// {16, 32, 64, 128, 256}, over a range of K. Warp 0 streams 128 x 64 and BN x 64 element
+// tiles into 128-byte-swizzled shared memory with TMA (cp.async.bulk.tensor, no
+// multicast) through a ring of stages guarded by mbarriers; one thread of warp 1 issues
+// tcgen05.mma (four K = 16 steps per stage) and tcgen05.commit; warps 2-5 read the
+// accumulator with tcgen05.ld and apply the epilogue:
+//   kStore   out[n, m]  = d            (with split-K: one partial buffer per K range)
+//   kAdd     out[n, m] += d            (the residual add)
+//   kSwiglu  out[n, j]  = silu(g) * u  (bfloat16; the tile holds 64 gate rows and their
+//                                      64 up rows, exchanged through shared memory)
+// Split-K partials are summed by the consumer in ascending order, so the order of every
+// sum is fixed by the launch shape alone. Rows or columns of a tile that lie outside the
+// matrix are zero-filled by TMA and masked in the epilogue, so M, N and K need not be
+// multiples of the tile (K must be a multiple of 8: TMA strides are multiples of 16 bytes).
+//
+// Every wait on an mbarrier is bounded: after about a second it records an error code in
+// `status` (device memory owned by this library) and goes on, so the kernel always ends
+// and frees its tensor memory; the host reads the status after the launch it cares about.
+//
+// Counterparts in arhaamatiq/stride: TcQkv, TcGemmResidual, TcMlp13, TcLmFull on wmma
+// (src/kernels_tc.cu:347-655).
+#include <cuda.h>
+
+#include <map>
+#include <mutex>
+#include <tuple>
+
+#include "common.cuh"
+
+SB_DEFINE_LAST_ERROR()
+
+namespace {
+
+using bf16 = __nv_bfloat16;
+
+constexpr int kTileM = 128;
+constexpr int kTileK = 64;            // elements: 128 bytes of bfloat16, one swizzle row
+constexpr int kStageA = kTileM * 128;  // bytes
+constexpr int kMaxStages = 8;
+constexpr int kThreads = 192;
+constexpr int kSmemBudget = 200 * 1024;
+constexpr long long kWaitCycles = 2000000000LL;
+
+enum Epilogue { kStore = 0, kAdd = 1, kSwiglu = 2 };
+
+// ------------------------------------------------------------------ PTX wrappers
+__device__ __forceinline__ uint32_t smem_u32(const void* p) { return static_cast<uint32_t>(__cvta_generic_to_shared(p)); }
+
+__device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
+  asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count));
+}
+__device__ __forceinline__ void mbar_expect_tx(uint32_t bar, uint32_t bytes) {
+  asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
+  uint32_t ok;
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+      "selp.u32 %0, 1, 0, p;\n\t}"
+      : "=r"(ok)
+      : "r"(bar), "r"(parity)
+      : "memory");
+  return ok != 0;
+}
+// Bounded wait: gives up after kWaitCycles, records `code` and returns false.
+__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, int* status, int code) {
+  if (mbar_try_wait(bar, parity)) return true;
+  const long long t0 = clock64();
+  while (!mbar_try_wait(bar, parity)) {
+    if (clock64() - t0 > kWaitCycles) {
+      atomicCAS(status, 0, code);
+      return false;
+    }
+  }
+  return true;
+}
+__device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap* map, uint32_t bar, int x, int y) {
+  asm volatile(
+      "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];" ::"r"(dst),
+      "l"(reinterpret_cast<uint64_t>(map)), "r"(bar), "r"(x), "r"(y)
+      : "memory");
+}
+__device__ __forceinline__ void tmem_alloc(uint32_t dst_smem, uint32_t cols) {
+  asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(dst_smem), "r"(cols) : "memory");
+  asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+}
+__device__ __forceinline__ void tmem_dealloc(uint32_t taddr, uint32_t cols) {
+  asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(taddr), "r"(cols) : "memory");
+}
+__device__ __forceinline__ void umma_bf16(uint32_t tmem_d, uint64_t desc_a, uint64_t desc_b, uint32_t idesc, uint32_t accumulate) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "setp.ne.b32 p, %4, 0;\n\t"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}" ::"r"(tmem_d),
+      "l"(desc_a), "l"(desc_b), "r"(idesc), "r"(accumulate)
+      : "memory");
+}
+__device__ __forceinline__ void umma_commit(uint32_t bar) {
+  asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
+}
+__device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void tmem_load16(uint32_t taddr, float* v) {
+  uint32_t r[16];
+  asm volatile(
+      "tcgen05.ld.sync.aligned.32x32b.x16.b32 {%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15}, [%16];"
+      : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]),
+        "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15])
+      : "r"(taddr)
+      : "memory");
+  asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+#pragma unroll
+  for (int i = 0; i < 16; ++i) v[i] = __uint_as_float(r[i]);
+}
+
+// Shared-memory matrix descriptor of a K-major tile in the 128-byte swizzle: rows of 128 bytes,
+// groups of eight rows 1024 bytes apart; `byte_offset` steps along K inside the swizzle row.
+__device__ __forceinline__ uint64_t smem_desc_sw128(uint32_t smem_addr) {
+  uint64_t d = 0;
+  d |= static_cast<uint64_t>((smem_addr & 0x3FFFF) >> 4);  // start address
+  d |= static_cast<uint64_t>(0) << 16;                     // leading byte offset: unused for swizzled K-major
+  d |= static_cast<uint64_t>(1024 >> 4) << 32;             // stride byte offset between 8-row groups
+  d |= static_cast<uint64_t>(1) << 46;                     // descriptor version of sm_100
+  d |= static_cast<uint64_t>(2) << 61;                     // layout: 128-byte swizzle
+  return d;
+}
+// Instruction descriptor: D float32, A and B bfloat16, both K-major, M = 128, N = n.
+__device__ __forceinline__ uint32_t instr_desc(int n) {
+  return (1u << 4) | (1u << 7) | (1u << 10) | (static_cast<uint32_t>(n >> 3) << 17) | (static_cast<uint32_t>(kTileM >> 4) << 24);
+}
+
+struct GemmParams {
+  float* out;           // kStore / kAdd: float32 [N, ldo]; kSwiglu: bfloat16 [N, ldo]
+  int64_t ldo;
+  int64_t split_stride;  // elements between split-K partial buffers
+  int M, N, K;
+  int block_n;           // BN
+  int stages;
+  int kblocks_per_split;
+  int half_rows;         // kSwiglu: rows of the gate half (intermediate size); W is [2 * half_rows, K]
+  int* status;
+};
+
+template <int EPI>
+__global__ void __launch_bounds__(kThreads, 1)
+gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUtensorMap map_x, const GemmParams p) {
+  extern __shared__ __align__(1024) uint8_t smem_raw[];
+  __shared__ __align__(8) uint64_t full_bar[kMaxStages];
+  __shared__ __align__(8) uint64_t empty_bar[kMaxStages];
+  __shared__ __align__(8) uint64_t accum_bar;
+  __shared__ uint32_t tmem_base_s;
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int BN = p.block_n;
+  const int stage_b = BN * 128;
+  const int stage_bytes = kStageA + stage_b;
+  // Dynamic shared memory is only guaranteed 16-byte alignment: round up to the swizzle's 1024.
+  const uint32_t smem0 = (smem_u32(smem_raw) + 1023u) & ~1023u;
+  const int tile_m = blockIdx.x, tile_n = blockIdx.y, split = blockIdx.z;
+  const int kblocks = (p.K + kTileK - 1) / kTileK;
+  const int kb0 = split * p.kblocks_per_split;
+  const int kb1 = min(kblocks, kb0 + p.kblocks_per_split);
+  const int iters = kb1 - kb0;
+  const uint32_t tmem_cols = BN < 32 ? 32 : BN;
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < p.stages; ++s) {
+      mbar_init(smem_u32(&full_bar[s]), 1);
+      mbar_init(smem_u32(&empty_bar[s]), 1);
+    }
+    mbar_init(smem_u32(&accum_bar), 1);
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+  }
+  if (warp == 1) tmem_alloc(smem_u32(&tmem_base_s), tmem_cols);
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = tmem_base_s;
+
+  if (warp == 0) {
+    if (lane == 0) {
+      // ---------------- producer: TMA loads
+      const int row_w = EPI == kSwiglu ? tile_m * 64 : tile_m * kTileM;
+      for (int i = 0; i < iters; ++i) {
+        const int s = i % p.stages;
+        if (i >= p.stages) mbar_wait(smem_u32(&empty_bar[s]), ((i / p.stages) - 1) & 1, p.status, 1);
+        const uint32_t bar = smem_u32(&full_bar[s]);
+        const uint32_t a = smem0 + s * stage_bytes, b = a + kStageA;
+        mbar_expect_tx(bar, stage_bytes);
+        const int k = (kb0 + i) * kTileK;
+        if (EPI == kSwiglu) {
+          tma_load_2d(a, &map_w, bar, k, row_w);
+          tma_load_2d(a + kStageA / 2, &map_w, bar, k, p.half_rows + row_w);
+        } else {
+          tma_load_2d(a, &map_w, bar, k, row_w);
+        }
+        tma_load_2d(b, &map_x, bar, k, tile_n * BN);
+      }
+    }
+  } else if (warp == 1) {
+    if (lane == 0) {
+      // ---------------- MMA issuer
+      const uint32_t idesc = instr_desc(BN);
+      for (int i = 0; i < iters; ++i) {
+        const int s = i % p.stages;
+        mbar_wait(smem_u32(&full_bar[s]), (i / p.stages) & 1, p.status, 2);
+        tc_fence_after();
+        const uint32_t a = smem0 + s * stage_bytes, b = a + kStageA;
+        const uint64_t da = smem_desc_sw128(a), db = smem_desc_sw128(b);
+#pragma unroll
+        for (int k = 0; k < kTileK / 16; ++k) {
+          // 16 elements = 32 bytes along K: +2 in the descriptor's 16-byte address units
+          umma_bf16(tmem_base, da + 2 * k, db + 2 * k, idesc, (i > 0 || k > 0) ? 1u : 0u);
+        }
+        umma_commit(smem_u32(&empty_bar[s]));
+      }
+      umma_commit(smem_u32(&accum_bar));
+    }
+    __syncwarp();
+  } else {
+    // ---------------- epilogue: warps 2..5 own TMEM lanes 32 * (warp % 4) ..
+    const int quarter = warp & 3;
+    const bool ok = iters > 0 && mbar_wait(smem_u32(&accum_bar), 0, p.status, 3);
+    tc_fence_after();
+    const int n0 = tile_n * BN;
+    if (EPI == kSwiglu) {
+      // lanes 0..63 hold gate rows, lanes 64..127 the matching up rows
+      float* xch = reinterpret_cast<float*>(smem_raw + ((smem0 - smem_u32(smem_raw))));  // stage 0 is free by now
+      const int j = tile_m * 64 + (quarter & 1) * 32 + lane;  // output feature
+      bf16* out = reinterpret_cast<bf16*>(p.out);
+      for (int c0 = 0; c0 < BN; c0 += 16) {
+        float v[16];
+        tmem_load16(tmem_base + (static_cast<uint32_t>(quarter * 32) << 16) + c0, v);
+        if (quarter >= 2) {
+#pragma unroll
+          for (int c = 0; c < 16; ++c) xch[c * 64 + (quarter - 2) * 32 + lane] = v[c];
+        }
+        asm volatile("bar.sync 1, 128;" ::: "memory");
+        if (quarter < 2 && ok) {
+#pragma unroll
+          for (int c = 0; c < 16; ++c) {
+            const int n = n0 + c0 + c;
+            if (n < p.N && j < p.half_rows) {
+              const float g = v[c], u = xch[c * 64 + quarter * 32 + lane];
+              out[static_cast<int64_t>(n) * p.ldo + j] = __float2bfloat16_rn((g / (1.0f + expf(-g))) * u);
+            }
+          }
+        }
+        asm volatile("bar.sync 1, 128;" ::: "memory");
+      }
+    } else {
+      const int m = tile_m * kTileM + quarter * 32 + lane;
+      float* out = p.out + static_cast<int64_t>(split) * p.split_stride;
+      for (int c0 = 0; c0 < BN; c0 += 16) {
+        float v[16];
+        tmem_load16(tmem_base + (static_cast<uint32_t>(quarter * 32) << 16) + c0, v);
+        if (m < p.M && ok) {
+#pragma unroll
+          for (int c = 0; c < 16; ++c) {
+            const int n = n0 + c0 + c;
+            if (n < p.N) {
+              float* o = out + static_cast<int64_t>(n) * p.ldo + m;
+              *o = EPI == kAdd ? (*o + v[c]) : v[c];
+            }
+          }
+        }
+      }
+    }
+    tc_fence_before();
+  }
+  __syncthreads();
+  if (warp == 1) {
+    tc_fence_after();
+    tmem_dealloc(tmem_base, tmem_cols);
+  }
+}
+
+// ------------------------------------------------------------------ host side
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*,
+                                  const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
+                                  CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+EncodeTiledFn encode_fn() {
+  static EncodeTiledFn fn = nullptr;
+  static std::once_flag once;
+  std::call_once(once, [] {
+    void* ptr = nullptr;
+    cudaDriverEntryPointQueryResult res;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &ptr, cudaEnableDefault, &res) == cudaSuccess &&
+        res == cudaDriverEntryPointSuccess)
+      fn = reinterpret_cast<EncodeTiledFn>(ptr);
+  });
+  return fn;
+}
+
+// Tensor map of a row-major bfloat16 matrix [rows, cols] with leading dimension ld (elements) and a
+// box of box_rows x 64 elements in the 128-byte swizzle. Cached: the same buffers come back every step.
+bool tensor_map(const void* base, int64_t rows, int64_t cols, int64_t ld, int box_rows, CUtensorMap* out) {
+  using Key = std::tuple<const void*, int64_t, int64_t, int64_t, int>;
+  static std::map<Key, CUtensorMap> cache;
+  static std::mutex mu;
+  std::lock_guard<std::mutex> lock(mu);
+  const Key key{base, rows, cols, ld, box_rows};
+  auto it = cache.find(key);
+  if (it != cache.end()) {
+    *out = it->second;
+    return true;
+  }
+  EncodeTiledFn fn = encode_fn();
+  if (!fn) return false;
+  const cuuint64_t dims[2] = {static_cast<cuuint64_t>(cols), static_cast<cuuint64_t>(rows)};
+  const cuuint64_t strides[1] = {static_cast<cuuint64_t>(ld) * 2};
+  const cuuint32_t box[2] = {static_cast<cuuint32_t>(kTileK), static_cast<cuuint32_t>(box_rows)};
+  const cuuint32_t elem[2] = {1, 1};
+  CUtensorMap m;
+  const CUresult r = fn(&m, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(base), dims, strides, box, elem,
+                        CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                        CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (r != CUDA_SUCCESS) return false;
+  if (cache.size() > 4096) cache.clear();
+  cache[key] = m;
+  *out = m;
+  return true;
+}
+
+int* status_word() {
+  static int* word = nullptr;
+  static std::once_flag once;
+  std::call_once(once, [] {
+    if (cudaMalloc(&word, sizeof(int)) == cudaSuccess) cudaMemset(word, 0, sizeof(int));
+  });
+  return word;
+}
+
+}  // namespace
+
+// The number of K ranges this library uses for a [M, K] weight applied to n tokens: enough CTAs to
+// occupy the GPU when the weight alone gives too few tiles, limited so that the partial sums stay
+// small beside the weight. The caller sizes its partial buffer [splits, n, M] with it.
+SB_EXPORT int sb_gemm_tc_splits(int n, int M, int K) {
+  const int tiles_m = (M + kTileM - 1) / kTileM;
+  const int kblocks = (K + kTileK - 1) / kTileK;
+  if (n > 128) return 1;
+  const int n_pad = n <= 16 ? 16 : n <= 32 ? 32 : n <= 64 ? 64 : 128;
+  int splits = 148 / tiles_m;   // at most one wave of CTAs
+  splits = min(splits, K / (16 * n_pad));
+  splits = min(splits, kblocks / 2);
+  splits = max(splits, 1);
+  const int per = (kblocks + splits - 1) / splits;
+  return (kblocks + per - 1) / per;
+}
+
+// out = x . W^T on the tensor cores.
+//   epilogue 0: out float32 [n, ldo] (+ split * split_stride), `splits` K ranges (from sb_gemm_tc_splits, or 1)
+//   epilogue 1: out float32 [n, ldo] += result (splits must be 1)
+//   epilogue 2: W is [2 * half_rows, K] (gate rows then up rows); out bfloat16 [n, ldo] = silu(gate) * up
+SB_EXPORT int sb_gemm_tc(const void* x, int64_t ldx, const void* w, int64_t ldw, void* out, int64_t ldo, int n, int M, int K,
+                         int epilogue, int splits, int64_t split_stride, int half_rows, cudaStream_t stream) {
+  if (n <= 0 || M <= 0) return 0;
+  if (K <= 0 || K % 8 != 0 || ldx % 8 != 0 || ldw % 8 != 0)
+    return sb::fail("sb_gemm_tc: K %d and the leading dimensions (%lld, %lld) must be multiples of 8", K, (long long)ldx, (long long)ldw);
+  if ((reinterpret_cast<uintptr_t>(x) | reinterpret_cast<uintptr_t>(w)) & 15)
+    return sb::fail("sb_gemm_tc: operands must be 16-byte aligned");
+  if (epilogue < 0 || epilogue > 2) return sb::fail("sb_gemm_tc: unknown epilogue %d", epilogue);
+  if (epilogue != kStore && splits != 1) return sb::fail("sb_gemm_tc: only the plain store supports split-K");
+  if (epilogue == kSwiglu && (half_rows <= 0 || M != 2 * half_rows)) return sb::fail("sb_gemm_tc: swiglu needs M = 2 * half_rows");
+  const int kblocks = (K + kTileK - 1) / kTileK;
+  if (splits < 1 || splits > kblocks) return sb::fail("sb_gemm_tc: %d splits for %d blocks of K", splits, kblocks);
+  int* status = status_word();
+  if (!status) return sb::fail("sb_gemm_tc: cannot allocate the status word");
+
+  GemmParams p{};
+  p.out = static_cast<float*>(out);
+  p.ldo = ldo;
+  p.split_stride = split_stride;
+  p.M = M;
+  p.N = n;
+  p.K = K;
+  p.block_n = n <= 16 ? 16 : n <= 32 ? 32 : n <= 64 ? 64 : n <= 128 ? 128 : 256;
+  const int stage_bytes = kStageA + p.block_n * 128;
+  p.stages = min(kMaxStages, kSmemBudget / stage_bytes);
+  p.kblocks_per_split = (kblocks + splits - 1) / splits;
+  if ((kblocks + p.kblocks_per_split - 1) / p.kblocks_per_split != splits)
+    return sb::fail("sb_gemm_tc: %d splits leave an empty K range (use sb_gemm_tc_splits)", splits);
+  p.half_rows = half_rows;
+  p.status = status;
+
+  CUtensorMap map_w, map_x;
+  const int box_w = epilogue == kSwiglu ? 64 : kTileM;
+  if (!tensor_map(w, M, K, ldw, box_w, &map_w) || !tensor_map(x, n, K, ldx, p.block_n, &map_x))
+    return sb::fail("sb_gemm_tc: cuTensorMapEncodeTiled failed (M %d N %d K %d)", M, n, K);
+
+  const int tiles_m = epilogue == kSwiglu ? (half_rows + 63) / 64 : (M + kTileM - 1) / kTileM;
+  dim3 grid(tiles_m, (n + p.block_n - 1) / p.block_n, splits);
+  if (grid.y > 65535) return sb::fail("sb_gemm_tc: too many token tiles");
+  const size_t smem = static_cast<size_t>(p.stages) * stage_bytes + 1024;
+#define SB_LAUNCH(EPI)                                                                              \
+  do {                                                                                              \
+    static bool attr_set = false;                                                                   \
+    if (!attr_set) {                                                                                \
+      if (cudaFuncSetAttribute(gemm_tc_kernel<EPI>, cudaFuncAttributeMaxDynamicSharedMemorySize,    \
+                               kSmemBudget + 2048) != cudaSuccess)                                  \
+        return sb::fail("sb_gemm_tc: cannot raise the shared memory limit");                        \
+      attr_set = true;                                                                              \
+    }                                                                                               \
+    gemm_tc_kernel<EPI><<<grid, kThreads, smem, stream>>>(map_w, map_x, p);                        \
+  } while (0)
+  if (epilogue == kStore) SB_LAUNCH(kStore);
+  else if (epilogue == kAdd) SB_LAUNCH(kAdd);
+  else SB_LAUNCH(kSwiglu);
+#undef SB_LAUNCH
+  return sb::check_launch("sb_gemm_tc");
+}
+
+// Reads and clears the status word: 0 = every wait completed; 1, 2, 3 = the producer, the MMA issuer or
+// the epilogue gave up waiting. Synchronises the device.
+SB_EXPORT int sb_gemm_tc_status() {
+  int* status = status_word();
+  if (!status) return -1;
+  int host = 0;
+  if (cudaMemcpy(&host, status, sizeof(int), cudaMemcpyDeviceToHost) != cudaSuccess) return -2;
+  if (host != 0) cudaMemset(status, 0, sizeof(int));
+  return host;
+}

@@ -36,6 +36,7 @@ SOURCES = {
     "gemm_f32": "gemm_f32.cu",
     "attention_generic": "attention_generic.cu",
     "sampling": "sampling.cu",
+    "gemm_tc": "gemm_tc.cu",
 }
 
 _loaded: dict[str, ctypes.CDLL] = {}

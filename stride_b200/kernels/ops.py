@@ -162,3 +162,52 @@ def sample_temperature(logits, temperatures, seeds, lengths, tokens, values) -> 
                                                         c_void_p, c_void_p, c_void_p])
     _check(lib, fn(_ptr(logits), logits.stride(0), logits.shape[0], logits.shape[1], _ptr(temperatures), _ptr(seeds),
                    _ptr(lengths), _ptr(tokens), _ptr(values), _stream()))
+
+
+STORE, ADD, SWIGLU = 0, 1, 2
+
+
+def gemm_tc_splits(n: int, M: int, K: int) -> int:
+    """How many K ranges `gemm_tc` uses for a [M, K] weight and n tokens (sizes the partial buffer)."""
+    lib = library("gemm_tc")
+    lib.sb_gemm_tc_splits.argtypes = [c_int, c_int, c_int]
+    lib.sb_gemm_tc_splits.restype = c_int
+    return lib.sb_gemm_tc_splits(n, M, K)
+
+
+def gemm_tc(x: torch.Tensor, weight: torch.Tensor, out: torch.Tensor, epilogue: int = STORE, splits: int = 1,
+            half_rows: int = 0) -> None:
+    """out = x . weight^T on the tcgen05 tensor cores; x [n, K] and weight [M, K] bfloat16.
+
+    STORE: out float32 [n, M], or [splits, n, M] partial sums over K ranges when splits > 1.
+    ADD: out float32 [n, M] += result. SWIGLU: weight is [2 I, K] (gate rows, then up rows) and
+    out bfloat16 [n, I] = silu(x . gate^T) * (x . up^T).
+    """
+    _cuda(x, weight, out)
+    if x.dtype != torch.bfloat16 or weight.dtype != torch.bfloat16:
+        raise TypeError("gemm_tc takes bfloat16 operands")
+    want = torch.bfloat16 if epilogue == SWIGLU else torch.float32
+    if out.dtype != want:
+        raise TypeError(f"gemm_tc epilogue {epilogue} writes {want}")
+    lib, fn = _fn("gemm_tc", "sb_gemm_tc", [c_void_p, c_int64, c_void_p, c_int64, c_void_p, c_int64, c_int, c_int, c_int,
+                                            c_int, c_int, c_int64, c_int, c_void_p])
+    n, K = x.shape
+    M = weight.shape[0]
+    if weight.shape[1] != K:
+        raise ValueError(f"gemm_tc shapes: x {tuple(x.shape)}, weight {tuple(weight.shape)}")
+    if splits > 1:
+        if out.dim() != 3 or out.shape[0] != splits:
+            raise ValueError("gemm_tc with split-K writes [splits, n, M]")
+        ldo, split_stride = out.stride(1), out.stride(0)
+    else:
+        o2 = out[0] if out.dim() == 3 else out
+        ldo, split_stride = o2.stride(0), 0
+    _check(lib, fn(_ptr(x), x.stride(0), _ptr(weight), weight.stride(0), _ptr(out), ldo, n, M, K, epilogue, splits,
+                   split_stride, half_rows, _stream()))
+
+
+def gemm_tc_status() -> int:
+    """0 if every wait inside the tensor-core kernels completed since the last call; synchronises."""
+    lib = library("gemm_tc")
+    lib.sb_gemm_tc_status.restype = c_int
+    return lib.sb_gemm_tc_status()
