@@ -1,9 +1,14 @@
 """A linear layer without bias, out = x . W^T, with the kernel chosen by precision.
 
-float32 engine: true 32-bit FMA (`csrc/gemm_f32.cu`) on float32 activations; the
-weight stays as stored (bfloat16 is widened exactly inside the kernel).
-bfloat16 engine: bfloat16 activations and weights, float32 accumulation; the
-tensor-core kernel where the shape allows it, else the same SIMT kernel.
+float32 engine: true 32-bit FMA (`csrc/gemm_f32.cu`) on float32 activations; the weight stays
+as stored (bfloat16 is widened exactly inside the kernel).
+bfloat16 engine: bfloat16 activations and weights with float32 accumulation on the tcgen05
+tensor cores (`csrc/gemm_tc.cu`); a weight stored in float32, or a K that TMA cannot
+address (not a multiple of 8), falls back to the SIMT kernel, which takes any size.
+
+With few tokens the tensor-core kernel may cut K into ranges to fill the GPU and leave one
+partial sum per range; `forward_partials` and `forward_add` hand those to the consumer (the
+rotation kernel, the next norm), which adds them in ascending order.
 """
 from __future__ import annotations
 
@@ -19,16 +24,65 @@ class Linear:
         self.weight = weight.contiguous()
         self.out_features, self.in_features = weight.shape
         self.compute_dtype = compute_dtype
+        self.tensor_core = (compute_dtype == torch.bfloat16 and self.weight.dtype == torch.bfloat16
+                            and self.in_features % 8 == 0)
 
     def weight_bytes(self) -> int:
         return self.weight.numel() * self.weight.element_size()
 
+    def _tc(self, x: torch.Tensor) -> bool:
+        return self.tensor_core and x.dtype == torch.bfloat16 and x.stride(0) % 8 == 0
+
+    def partial_elems(self, max_tokens: int) -> int:
+        """Elements of the largest partial buffer `forward_partials` may need for up to max_tokens tokens."""
+        rows = max_tokens
+        if self.tensor_core:
+            for n in (16, 32, 64, 128):
+                if n <= max(16, max_tokens):
+                    rows = max(rows, n * ops.gemm_tc_splits(n, self.out_features, self.in_features))
+        return rows * self.out_features
+
     def forward(self, x: torch.Tensor, out: torch.Tensor) -> None:
         """out[n, out_features] float32 = x . W^T."""
-        ops.gemm_f32(x, self.weight, out, accumulate=False)
+        if self._tc(x):
+            ops.gemm_tc(x, self.weight, out, ops.STORE)
+        else:
+            ops.gemm_f32(x, self.weight, out, accumulate=False)
 
-    def forward_add(self, x: torch.Tensor, stream) -> None:
-        """stream += x . W^T (the residual add)."""
-        if stream.pending is not None:
+    def forward_partials(self, x: torch.Tensor, flat: torch.Tensor) -> torch.Tensor:
+        """x . W^T as [S, n, out_features] float32 partial sums (S >= 1) carved from the flat buffer `flat`."""
+        n, M = x.shape[0], self.out_features
+        S = ops.gemm_tc_splits(n, M, self.in_features) if self._tc(x) else 1
+        out = flat[:S * n * M].view(S, n, M)
+        if self._tc(x):
+            ops.gemm_tc(x, self.weight, out, ops.STORE, splits=S)
+        else:
+            ops.gemm_f32(x, self.weight, out[0], accumulate=False)
+        return out
+
+    def forward_add(self, x: torch.Tensor, stream, flat: torch.Tensor = None) -> None:
+        """stream += x . W^T (the residual add); with `flat` given, split-K partials may be left pending."""
+        if self._tc(x):
+            n, M = x.shape[0], self.out_features
+            S = ops.gemm_tc_splits(n, M, self.in_features) if flat is not None else 1
+            if S > 1:
+                parts = flat[:S * n * M].view(S, n, M)
+                ops.gemm_tc(x, self.weight, parts, ops.STORE, splits=S)
+                stream.set_pending(parts)
+                return
             stream.fold()
-        ops.gemm_f32(x, self.weight, stream.h, accumulate=True)
+            ops.gemm_tc(x, self.weight, stream.h, ops.ADD)
+        else:
+            stream.fold()
+            ops.gemm_f32(x, self.weight, stream.h, accumulate=True)
+
+    def forward_swiglu(self, x: torch.Tensor, z: torch.Tensor, scratch_fn) -> None:
+        """W = [gate rows; up rows]: z[n, I] = silu(x . gate^T) * (x . up^T). `scratch_fn()` gives a
+        float32 [n, 2 I] buffer for the unfused path."""
+        I = self.out_features // 2
+        if self._tc(x) and z.dtype == torch.bfloat16:
+            ops.gemm_tc(x, self.weight, z, ops.SWIGLU, half_rows=I)
+        else:
+            gate_up = scratch_fn()
+            ops.gemm_f32(x, self.weight, gate_up, accumulate=False)
+            ops.swiglu(gate_up, z)

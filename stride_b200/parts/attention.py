@@ -77,12 +77,11 @@ class AttentionMixer(Mixer):
 
     def forward(self, ctx, x, stream, cache):
         n, ws, D = ctx.n, ctx.workspace, self.head_dim
-        qkv = ws.get("attn.qkv", n, (self.qkv_width,), torch.float32)
-        self.qkv.forward(x, qkv)
+        qkv = self.qkv.forward_partials(x, ws.raw("attn.qkv", (self.qkv.partial_elems(ws.max_tokens),), torch.float32))
         q = ws.get("attn.q", n, (self.num_heads * D,), ctx.act_dtype)
         ops.rope_append(qkv, ctx.positions, ctx.slots, self._cos_sin, self._rotary, q, cache.pages, cache.block_table,
                         self.num_heads, self.num_kv_heads, D, write_kv=cache.writes)
         mixed = ws.get("attn.out", n, (self.num_heads * D,), ctx.act_dtype)
         ops.attention_generic(q, mixed, cache.pages, cache.block_table, ctx.positions, ctx.slots,
                               self.num_heads, self.num_kv_heads, D, self.window, self.scale)
-        self.o.forward_add(mixed, stream)
+        self.o.forward_add(mixed, stream, ws.raw("attn.o_partials", (self.o.partial_elems(ws.max_tokens),), torch.float32))

@@ -40,8 +40,6 @@ class SwiGLU(FeedForward):
 
     def forward(self, ctx, x, stream):
         n, ws = ctx.n, ctx.workspace
-        gate_up = ws.get("mlp.gate_up", n, (2 * self.intermediate,), torch.float32)
-        self.gate_up.forward(x, gate_up)
         z = ws.get("mlp.z", n, (self.intermediate,), ctx.act_dtype)
-        ops.swiglu(gate_up, z)
-        self.down.forward_add(z, stream)
+        self.gate_up.forward_swiglu(x, z, lambda: ws.get("mlp.gate_up", n, (2 * self.intermediate,), torch.float32))
+        self.down.forward_add(z, stream, ws.raw("mlp.down_partials", (self.down.partial_elems(ws.max_tokens),), torch.float32))
