@@ -84,7 +84,8 @@ class Engine:
         self.max_context = o.max_context or self.spec.max_positions
         self.compute_dtype = _DTYPES[o.dtype]
         env = BuildEnv(device=self.device, compute_dtype=self.compute_dtype, max_tokens=o.max_rows,
-                       max_positions=self.max_context, max_logit_rows=min(o.max_full_rows, o.max_rows))
+                       max_positions=self.max_context, max_logit_rows=min(o.max_full_rows, o.max_rows),
+                       max_requests=o.max_slots)
         self.env = env
         self.model = DecoderModel(self.spec, env)
         plan = self.model.tensor_plan()
@@ -108,6 +109,14 @@ class Engine:
         self._device_ints = torch.zeros(self._ints, dtype=torch.int32, device=self.device)
         self._copied = torch.cuda.Event()
         self._copy_pending = False
+        # A second staging area for small integer tables that parts make during a step (work lists).
+        self._aux_ints = 4 * o.max_rows + 64
+        self._aux_staging = torch.empty(self._aux_ints, dtype=torch.int32, pin_memory=True)
+        self._aux_np = self._aux_staging.numpy()
+        self._aux_device = torch.zeros(self._aux_ints, dtype=torch.int32, device=self.device)
+        self._aux_used = 0
+        self._aux_copied = torch.cuda.Event()
+        self._aux_pending = False
         self.steps = 0
 
     @classmethod
@@ -116,6 +125,19 @@ class Engine:
         from ..weights.random_init import random_tensors
         o = options or EngineOptions()
         return cls(None, o, config=config, tensors=random_tensors(config, seed, o.device))
+
+    def _upload_ints(self, values) -> torch.Tensor:
+        """Copy a small int32 array to the device for the current step; returns the device view."""
+        values = np.ascontiguousarray(values, dtype=np.int32).reshape(-1)
+        k, at = values.shape[0], self._aux_used
+        if at + k > self._aux_ints:
+            raise EngineError("the step's integer tables exceed the staging area")
+        self._aux_np[at:at + k] = values
+        self._aux_device[at:at + k].copy_(self._aux_staging[at:at + k], non_blocking=True)
+        self._aux_copied.record()
+        self._aux_pending = True
+        self._aux_used = at + ((k + 3) & ~3)
+        return self._aux_device[at:at + k]
 
     # ------------------------------------------------------------------ the step
     def step(self, entries: list) -> Optional[torch.Tensor]:
@@ -134,6 +156,10 @@ class Engine:
         R = o.max_rows
         if self._copy_pending:
             self._copied.synchronize()
+        if self._aux_pending:
+            self._aux_copied.synchronize()
+            self._aux_pending = False
+        self._aux_used = 0
         buf = self._staging_np
         tok, pos, slt, rows = buf[0:n], buf[R:R + n], buf[2 * R:2 * R + n], buf[3 * R:3 * R + count]
         meta = buf[4 * R:8 * R].reshape(4, R)
@@ -176,7 +202,7 @@ class Engine:
             compute_dtype=self.compute_dtype,
             entry_slots=[e.slot for e in entries], entry_first_row=[int(x) for x in meta[1, :E]],
             entry_length=[len(e.tokens) for e in entries], entry_first_pos=[e.first_pos for e in entries],
-            entry_meta=d[4 * R:8 * R].view(4, R)[:, :E])
+            entry_meta=d[4 * R:8 * R].view(4, R)[:, :E], upload_ints=self._upload_ints)
         logits = self.model.forward(ctx, self.caches, d[3 * R:3 * R + count], count)
         self.steps += 1
         return logits

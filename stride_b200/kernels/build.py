@@ -37,6 +37,7 @@ SOURCES = {
     "attention_generic": "attention_generic.cu",
     "sampling": "sampling.cu",
     "gemm_tc": "gemm_tc.cu",
+    "attention_tc": "attention_tc.cu",
 }
 
 _loaded: dict[str, ctypes.CDLL] = {}

@@ -211,3 +211,23 @@ def gemm_tc_status() -> int:
     lib = library("gemm_tc")
     lib.sb_gemm_tc_status.restype = c_int
     return lib.sb_gemm_tc_status()
+
+
+def attention_tc_scratch(items: int, num_kv_heads: int, chunks: int, head_dim: int) -> int:
+    """Floats of scratch `attention_tc` needs."""
+    return items * num_kv_heads * chunks * 16 * (head_dim + 2)
+
+
+def attention_tc(q, out, cache_layer, block_table, entry_meta, work, n_tiles: int, n_items: int, chunks: int,
+                 scratch, num_heads: int, num_kv_heads: int, head_dim: int, window: int, scale: float) -> None:
+    """Tensor-core paged attention (bfloat16, head_dim 64 or 128); see csrc/attention_tc.cu for `work`."""
+    _cuda(q, out, cache_layer, block_table, entry_meta, work, scratch)
+    if not (q.dtype == out.dtype == cache_layer.dtype == torch.bfloat16):
+        raise TypeError("attention_tc takes bfloat16 q, out and cache")
+    lib, fn = _fn("attention_tc", "sb_attention_tc",
+                  [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int64, c_int64, c_int64, c_void_p, c_int,
+                   c_void_p, c_int, c_int, c_int, c_void_p, c_int, c_int, c_int, c_int, c_float, c_void_p])
+    _check(lib, fn(_ptr(q), _ptr(out), _ptr(cache_layer), _ptr(block_table), block_table.shape[1], cache_layer.shape[3],
+                   cache_layer.stride(0), cache_layer.stride(1), cache_layer.stride(2), _ptr(entry_meta),
+                   entry_meta.stride(0), _ptr(work), n_tiles, n_items, chunks, _ptr(scratch), num_heads, num_kv_heads,
+                   head_dim, window, scale, _stream()))

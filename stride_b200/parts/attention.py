@@ -75,6 +75,28 @@ class AttentionMixer(Mixer):
         return CacheNeed("pages", kv_heads=self.num_kv_heads, head_dim=self.head_dim, window=self.window,
                          dtype=self.env.act_dtype)
 
+    @staticmethod
+    def _tc_plan(ctx, G: int):
+        """(work list on the device, tiles, items, chunks) of the tensor-core attention kernels for this
+        step: entries of at most 16 // G tokens go to the decode kernel (one item each), longer ones are
+        cut into tiles of 64 // G positions. Made once per step and shared by all layers of this ratio."""
+        key = ("attention_tc_plan", G)
+        plan = ctx.shared.get(key)
+        if plan is None:
+            ppt, short = 64 // G, 16 // G
+            tiles, items, last = [], [], 0
+            for e, (L, p0) in enumerate(zip(ctx.entry_length, ctx.entry_first_pos)):
+                if L <= short:
+                    items.append(e)
+                    last = max(last, p0 + L - 1)
+                else:
+                    for t in range((L + ppt - 1) // ppt):
+                        tiles += [e, t]
+            work = ctx.upload_ints(np.asarray(tiles + items, dtype=np.int32))
+            plan = (work, len(tiles) // 2, len(items), last // 256 + 1 if items else 0)
+            ctx.shared[key] = plan
+        return plan
+
     def forward(self, ctx, x, stream, cache):
         n, ws, D = ctx.n, ctx.workspace, self.head_dim
         qkv = self.qkv.forward_partials(x, ws.raw("attn.qkv", (self.qkv.partial_elems(ws.max_tokens),), torch.float32))
@@ -82,6 +104,13 @@ class AttentionMixer(Mixer):
         ops.rope_append(qkv, ctx.positions, ctx.slots, self._cos_sin, self._rotary, q, cache.pages, cache.block_table,
                         self.num_heads, self.num_kv_heads, D, write_kv=cache.writes)
         mixed = ws.get("attn.out", n, (self.num_heads * D,), ctx.act_dtype)
-        ops.attention_generic(q, mixed, cache.pages, cache.block_table, ctx.positions, ctx.slots,
-                              self.num_heads, self.num_kv_heads, D, self.window, self.scale)
+        G = self.num_heads // self.num_kv_heads
+        if ctx.act_dtype == torch.bfloat16 and D in (64, 128) and G <= 16:
+            plan = self._tc_plan(ctx, G)
+            scratch = ws.grow("attn.scratch", ops.attention_tc_scratch(plan[2], self.num_kv_heads, plan[3], D), torch.float32)
+            ops.attention_tc(q, mixed, cache.pages, cache.block_table, ctx.entry_meta, plan[0], plan[1], plan[2], plan[3],
+                             scratch, self.num_heads, self.num_kv_heads, D, self.window, self.scale)
+        else:
+            ops.attention_generic(q, mixed, cache.pages, cache.block_table, ctx.positions, ctx.slots,
+                                  self.num_heads, self.num_kv_heads, D, self.window, self.scale)
         self.o.forward_add(mixed, stream, ws.raw("attn.o_partials", (self.o.partial_elems(ws.max_tokens),), torch.float32))

@@ -36,6 +36,16 @@ class Workspace:
             self._buffers[key] = buf
         return buf
 
+    def grow(self, name: str, numel: int, dtype: torch.dtype) -> torch.Tensor:
+        """A flat buffer of at least `numel` elements; reallocated (with headroom) when too small.
+        Its address may change when it grows, so size it before a CUDA graph is captured."""
+        key = (name, "grow", dtype)
+        buf = self._buffers.get(key)
+        if buf is None or buf.numel() < numel:
+            buf = torch.zeros(max(numel, 1) * 3 // 2 + 16, dtype=dtype, device=self.device)
+            self._buffers[key] = buf
+        return buf
+
     def bytes(self) -> int:
         return sum(b.numel() * b.element_size() for b in self._buffers.values())
 
@@ -85,6 +95,8 @@ class StepContext:
     entry_length: list = field(default_factory=list)
     entry_first_pos: list = field(default_factory=list)
     entry_meta: Optional[torch.Tensor] = None              # [4, E] int32 on the device: slot, first row, length, first position
+    upload_ints: Optional[object] = None                   # callable(np.ndarray int32) -> device tensor, valid for this step
+    shared: dict = field(default_factory=dict)             # what parts compute once per step and share between layers
 
     @property
     def act_dtype(self) -> torch.dtype:

@@ -51,7 +51,13 @@ TINY_C = {
                      "original_max_position_embeddings": 32},
     "rms_norm_eps": 3e-4, "max_position_embeddings": 192,
 }
-TINY = {"A": (TINY_A, 0, 64), "B": (TINY_B, 2, 8), "C": (TINY_C, 5, 16)}   # config, weight seed, page size
+# Head size 64 and ratio 4: the shapes the tensor-core attention kernels of the bfloat16 path take.
+TINY_D = {
+    "architectures": ["LlamaForCausalLM"], "hidden_size": 256, "intermediate_size": 384, "num_hidden_layers": 2,
+    "num_attention_heads": 8, "num_key_value_heads": 2, "head_dim": 64, "vocab_size": 512, "rope_theta": 10000.0,
+    "tie_word_embeddings": True, "rms_norm_eps": 1e-5, "max_position_embeddings": 640,
+}
+TINY = {"A": (TINY_A, 0, 64), "B": (TINY_B, 2, 8), "C": (TINY_C, 5, 16), "D": (TINY_D, 9, 16)}   # config, weight seed, page size
 
 # Weights N(0, 0.2) and gains 1 + 0.2 N(0, 1): large enough that attention is far from uniform and
 # every part changes the logits, as arhaamatiq/stride's own tiny model does (tests/make_tiny_model.py:19-54).
@@ -108,17 +114,33 @@ class TraceRun:
         return rc
 
 
-def logit_tolerance(dtype: str, reference: torch.Tensor) -> float:
+def logit_tolerance(dtype: str, reference: torch.Tensor, noise: float | None = None) -> float:
     """Largest allowed |engine - plain| over a set of logits.
 
     float32: 2e-4 absolute at logits of rms ~1-2, the bound arhaamatiq/stride's own suite uses
     for its exact path (tests/test_correctness.py:21), scaled with the rms for other magnitudes.
-    bfloat16: compared with the plain implementation rounding to bfloat16 at the same places; what is
-    left are sums taken in another order that flip a rounding now and then, each flip worth 2^-8
-    of one activation. 3% of the logits' rms bounds that for these depths and is far below what a
-    wrong key, page or position costs (tens of percent).
+
+    bfloat16: the engine is compared with the plain implementation rounding to bfloat16 at the same
+    places, so what is left are sums taken in another order, which now and then round an activation
+    to the neighbouring bfloat16 value. The tensor cores accumulate with truncation (measured on
+    B200: mean error 2e-6 of the result at K = 2048 against 3e-7 for a float32 FMA chain), so such
+    flips are several times more frequent than between two float32 implementations. The yardstick
+    is therefore bfloat16's own rounding noise on the same model and tokens, `noise` =
+    max |plain(bfloat16 rounding) - plain(float32)|: the engine has to stay within a quarter of it.
+    A wrong key, page, position or weight moves logits by the whole noise or more, and the same
+    code paths are held to 2e-4 in float32. Without `noise`, 3% of the logits' rms.
     """
     rms = float(reference.float().pow(2).mean().sqrt())
     if dtype == "float32":
         return 2e-4 * max(rms, 1.0)
+    if noise is not None:
+        return 0.25 * noise
     return 3e-2 * rms
+
+
+def bf16_noise(cfg, weights, tokens) -> float:
+    """max |plain with bfloat16 rounding - plain in float32| over all logits of the sequence."""
+    import plain_llama as plain
+    a = plain.forward(cfg, weights, tokens, torch.float32, torch.bfloat16)
+    b = plain.forward(cfg, weights, tokens, torch.float32, None)
+    return float((a - b).abs().max())

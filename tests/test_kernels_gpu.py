@@ -84,3 +84,217 @@ def test_gemm_tc_does_not_depend_on_the_batch():
         outs.append(out[0].clone())
     assert ops.gemm_tc_status() == 0
     assert torch.equal(outs[0], outs[1]) and torch.equal(outs[0], outs[2])
+
+
+# ---------------------------------------------------------------------------- attention
+def _paged_case(lengths_new, lengths_old, Hq, Hkv, D, page, dtype, seed=0, peak=None):
+    """A step with one entry per request: request i has lengths_old[i] cached tokens and brings
+    lengths_new[i] new ones. Returns the tensors the attention kernels take plus per-request q, k, v."""
+    g = torch.Generator().manual_seed(seed)
+    E = len(lengths_new)
+    total = [a + b for a, b in zip(lengths_old, lengths_new)]
+    max_pages = max(-(-t // page) for t in total) + 1
+    n_pages = sum(-(-t // page) for t in total) + 3
+    perm = torch.randperm(n_pages, generator=g).tolist()
+    cache = torch.zeros(n_pages, 2, Hkv, page, D, dtype=dtype)
+    table = torch.full((E, max_pages), -1, dtype=torch.int32)
+    ks, vs, qs = [], [], []
+    rows_q, positions, slots = [], [], []
+    meta = torch.zeros(4, E, dtype=torch.int32)
+    at = 0
+    for i in range(E):
+        T = total[i]
+        k = torch.randn(T, Hkv, D, generator=g).to(dtype)
+        v = torch.randn(T, Hkv, D, generator=g).to(dtype)
+        q = torch.randn(lengths_new[i], Hq, D, generator=g).to(dtype)
+        if peak is not None and i == peak[0]:
+            # one far key stands out for the last query of this request: a kernel that skips it is far off
+            key = peak[1]
+            k[key] = 0
+            k[key, :, 0] = 8.0
+            q[-1] = 0
+            q[-1, :, 0] = 8.0
+            v[key] = 5.0
+        for t in range(T):
+            pi = t // page
+            if table[i, pi] < 0:
+                table[i, pi] = perm.pop()
+            cache[table[i, pi], 0, :, t % page] = k[t]
+            cache[table[i, pi], 1, :, t % page] = v[t]
+        ks.append(k), vs.append(v), qs.append(q)
+        meta[:, i] = torch.tensor([i, at, lengths_new[i], lengths_old[i]])
+        positions += list(range(lengths_old[i], T))
+        slots += [i] * lengths_new[i]
+        at += lengths_new[i]
+    q_all = torch.cat(qs).reshape(at, Hq * D)
+    dev = lambda t: t.to(DEV)
+    return dict(q=dev(q_all), cache=dev(cache), table=dev(table), meta=dev(meta), positions=dev(torch.tensor(positions, dtype=torch.int32)),
+                slots=dev(torch.tensor(slots, dtype=torch.int32)), qs=qs, ks=ks, vs=vs, old=lengths_old, new=lengths_new)
+
+
+def _attention_reference(case, Hq, Hkv, D, window=0):
+    import plain_llama as plain
+    outs = []
+    scale_fix = 1.0
+    for q, k, v, old, new in zip(case["qs"], case["ks"], case["vs"], case["old"], case["new"]):
+        T = old + new
+        qq = torch.zeros(T, Hq, D)
+        qq[old:] = q.float()
+        o = plain.attention(qq, k.float(), v.float(), torch.arange(T), window)
+        outs.append(o[old:])
+    return torch.cat(outs)
+
+
+@pytest.mark.parametrize("D,Hq,Hkv,page,window", [(64, 8, 2, 16, 0), (128, 6, 2, 64, 0), (64, 4, 4, 8, 0), (64, 12, 4, 32, 100),
+                                                  (128, 16, 1, 128, 0)])
+def test_attention_tc_against_plain(D, Hq, Hkv, page, window):
+    """Portions and decoded tokens in one step, keys spread over shuffled pages, sequences that cross the
+    256-key chunk and 64-key tile edges."""
+    from stride_b200.kernels import ops
+    new = [1, 77, 1, 3, 200, 1, 2, 64]
+    old = [300, 0, 255, 256, 100, 0, 510, 63]
+    case = _paged_case(new, old, Hq, Hkv, D, page, torch.bfloat16, seed=D + page, peak=(0, 3))
+    G = Hq // Hkv
+    ppt, short = 64 // G, 16 // G
+    tiles, items, last = [], [], 0
+    for e, (L, p0) in enumerate(zip(new, old)):
+        if L <= short:
+            items.append(e)
+            last = max(last, p0 + L - 1)
+        else:
+            for t in range(-(-L // ppt)):
+                tiles += [e, t]
+    work = torch.tensor(tiles + items, dtype=torch.int32, device=DEV)
+    chunks = last // 256 + 1
+    scratch = torch.zeros(ops.attention_tc_scratch(len(items), Hkv, chunks, D), device=DEV)
+    out = torch.full_like(case["q"], float("nan"))
+    scale = 1.0 / math.sqrt(D)
+    ops.attention_tc(case["q"], out, case["cache"], case["table"], case["meta"], work, len(tiles) // 2, len(items), chunks,
+                     scratch, Hq, Hkv, D, window, scale)
+    ref = _attention_reference(case, Hq, Hkv, D, window)
+    got = out.float().cpu()
+    assert torch.isfinite(got).all()
+    # bfloat16 probabilities and output: 2^-8 relative on values of order 1
+    assert (got - ref).abs().max() <= 2e-2 * max(1.0, float(ref.abs().max()))
+    # the generic kernel on the same case
+    out2 = torch.full_like(case["q"], float("nan"))
+    ops.attention_generic(case["q"], out2, case["cache"], case["table"], case["positions"], case["slots"], Hq, Hkv, D, window, scale)
+    assert (out2.float().cpu() - ref).abs().max() <= 1e-2 * max(1.0, float(ref.abs().max()))
+
+
+@pytest.mark.parametrize("D,Hq,Hkv,page,window", [(48, 3, 3, 16, 0), (16, 4, 2, 64, 0), (80, 10, 2, 8, 37), (256, 2, 1, 32, 0)])
+def test_attention_generic_float32(D, Hq, Hkv, page, window):
+    from stride_b200.kernels import ops
+    new = [1, 50, 1, 130, 2]
+    old = [200, 0, 127, 5, 128]
+    case = _paged_case(new, old, Hq, Hkv, D, page, torch.float32, seed=D, peak=(0, 1))
+    out = torch.full_like(case["q"], float("nan"))
+    ops.attention_generic(case["q"], out, case["cache"], case["table"], case["positions"], case["slots"], Hq, Hkv, D, window, D ** -0.5)
+    ref = _attention_reference(case, Hq, Hkv, D, window)
+    assert (out.cpu() - ref).abs().max() <= 2e-5 * max(1.0, float(ref.abs().max()))
+
+
+# ---------------------------------------------------------------------------- the small kernels
+@pytest.mark.parametrize("n,H", [(1, 64), (7, 88), (33, 2048), (4, 5000)])
+def test_rmsnorm_with_partials(n, H):
+    from stride_b200.kernels import ops
+    h = _rand(n, H, seed=1)
+    parts = _rand(3, n, H, seed=2)
+    w = _rand(H, seed=3, dtype=torch.bfloat16)
+    for out_dtype in (torch.float32, torch.bfloat16):
+        hh = h.clone()
+        out = torch.zeros(n, H, dtype=out_dtype, device=DEV)
+        ops.rmsnorm(hh, w, 1e-5, out, partials=parts)
+        x = ((h + parts[0]) + parts[1]) + parts[2]
+        assert torch.equal(hh, x)
+        ref = w.float() * (x * (1.0 / torch.sqrt((x * x).sum(-1, keepdim=True) / H + 1e-5)))
+        tol = 1e-5 if out_dtype == torch.float32 else 1e-2
+        assert (out.float() - ref).abs().max() <= tol * float(ref.abs().max())
+
+
+def test_embed_swiglu_gather():
+    from stride_b200.kernels import ops
+    table = _rand(333, 88, seed=1, dtype=torch.bfloat16)
+    tok = torch.tensor([0, 332, 17, 17, 5], dtype=torch.int32, device=DEV)
+    out = torch.zeros(5, 88, device=DEV)
+    ops.embed(tok, table, out)
+    assert torch.equal(out, table.float()[tok.long()])
+    gu = _rand(9, 2 * 136, seed=2)
+    z = torch.zeros(9, 136, device=DEV)
+    ops.swiglu(gu, z)
+    a, b = gu[:, :136], gu[:, 136:]
+    assert (z - (a / (1 + torch.exp(-a))) * b).abs().max() <= 1e-6
+    rows = torch.tensor([8, 0, 3], dtype=torch.int32, device=DEV)
+    parts = _rand(2, 9, 272, seed=3)
+    got = torch.zeros(3, 272, device=DEV)
+    ops.gather_rows(gu, rows, got, partials=parts)
+    assert torch.equal(got, ((gu + parts[0]) + parts[1])[rows.long()])
+
+
+@pytest.mark.parametrize("n,M,K,wdtype", [(5, 77, 33, torch.float32), (70, 130, 200, torch.bfloat16), (1, 1000, 64, torch.bfloat16)])
+def test_gemm_f32(n, M, K, wdtype):
+    from stride_b200.kernels import ops
+    x = _rand(n, K, seed=1)
+    w = _rand(M, K, seed=2, dtype=wdtype)
+    ref = (x.double() @ w.double().T)
+    out = torch.zeros(n, M, device=DEV)
+    ops.gemm_f32(x, w, out)
+    assert (out.double() - ref).abs().max() <= 2e-6 * float(ref.abs().max()) * math.sqrt(K)
+    base = _rand(n, M, seed=3)
+    acc = base.clone()
+    ops.gemm_f32(x, w, acc, accumulate=True)
+    assert (acc.double() - (base.double() + ref)).abs().max() <= 2e-6 * float(ref.abs().max()) * math.sqrt(K)
+
+
+def test_rope_append_partial_rotation_and_pages():
+    """Rotation of the first rotary_dim elements only, q stored, k and v appended at (slot, pos) through the table."""
+    from stride_b200.kernels import ops
+    Hq, Hkv, D, rot, page, n = 3, 1, 24, 16, 4, 6
+    qkv = _rand(2, n, (Hq + 2 * Hkv) * D, seed=1)
+    pos = torch.tensor([0, 1, 2, 9, 10, 5], dtype=torch.int32, device=DEV)
+    slots = torch.tensor([1, 1, 1, 0, 0, 2], dtype=torch.int32, device=DEV)
+    table = torch.tensor([[3, 5, 1], [0, 6, 2], [7, 4, 8]], dtype=torch.int32, device=DEV)
+    ang = (torch.arange(32, dtype=torch.float32)[:, None] * torch.linspace(1.0, 0.1, rot // 2)[None]).double()
+    cos_sin = torch.stack([torch.cos(ang), torch.sin(ang)], -1).float().to(DEV)
+    cache = torch.zeros(9, 2, Hkv, page, D, device=DEV)
+    q_out = torch.zeros(n, Hq * D, device=DEV)
+    ops.rope_append(qkv, pos, slots, cos_sin, rot, q_out, cache, table, Hq, Hkv, D)
+    full = (qkv[0] + qkv[1]).reshape(n, Hq + 2 * Hkv, D).cpu()
+    c, s = cos_sin.cpu()[pos.cpu().long(), :, 0][:, None], cos_sin.cpu()[pos.cpu().long(), :, 1][:, None]
+
+    def rotate(x):
+        a, b = x[..., :rot // 2], x[..., rot // 2:rot]
+        return torch.cat([a * c - b * s, b * c + a * s, x[..., rot:]], -1)
+
+    assert (q_out.cpu().reshape(n, Hq, D) - rotate(full[:, :Hq])).abs().max() <= 1e-6
+    k_ref, v_ref = rotate(full[:, Hq:Hq + Hkv]), full[:, Hq + Hkv:]
+    for i in range(n):
+        pg = int(table[slots[i], pos[i] // page])
+        assert (cache[pg, 0, :, int(pos[i]) % page].cpu() - k_ref[i]).abs().max() <= 1e-6
+        assert torch.equal(cache[pg, 1, :, int(pos[i]) % page].cpu(), v_ref[i])
+    assert float(cache.abs().sum()) > 0 and int((cache.abs().sum(dim=(1, 2, 4)) > 0).sum()) == n
+
+
+def test_argmax_and_temperature_sampling():
+    import plain_llama as plain
+    from stride_b200.kernels import ops
+    rows, V = 6, 3001
+    logits = _rand(rows, V, seed=4, scale=3.0)
+    logits[1, 100] = logits[1, 2000] = logits[1].max() + 1      # a tie: the smaller index wins
+    logits[2, 5] = float("nan")
+    tok = torch.zeros(rows, dtype=torch.int32, device=DEV)
+    val = torch.zeros(rows, device=DEV)
+    ops.argmax(logits, tok, val)
+    clean = torch.nan_to_num(logits, nan=-float("inf")).cpu()
+    for r in range(rows):
+        want, _ = plain.choose_token(clean[r], 0.0, 1.0, 0, 0, 1)
+        assert int(tok[r]) == want and float(val[r]) == float(clean[r, want])
+    temps = torch.tensor([0.8, 1.0, 0.5, 2.0, 0.05, 1.3], device=DEV)
+    seeds = torch.tensor([1, 2**62 + 5, 3, -7, 5, 6], dtype=torch.int64, device=DEV)
+    for length in (1, 17, 300, 4097):
+        lengths = torch.full((rows,), length, dtype=torch.int32, device=DEV)
+        ops.sample_temperature(torch.nan_to_num(logits, nan=-1e30), temps, seeds, lengths, tok, val)
+        for r in range(rows):
+            l = torch.nan_to_num(logits[r], nan=-1e30).cpu()
+            want, wv = plain.choose_token(l, float(temps[r]), 1.0, 0, int(seeds[r]) & (2**64 - 1), length)
+            assert int(tok[r]) == want and float(val[r]) == wv

@@ -8,11 +8,12 @@ import pytest
 import torch
 
 import plain_llama as plain
-from conftest import TINY, TraceRun, logit_tolerance, random_tokens
+from conftest import TINY, TraceRun, bf16_noise, logit_tolerance, random_tokens
 
 pytestmark = pytest.mark.gpu
 
-LENGTHS = {"A": [70, 100, 45, 120, 33], "B": [150, 41, 97, 200, 64], "C": [48, 130, 17, 99, 64]}
+LENGTHS = {"A": [70, 100, 45, 120, 33], "B": [150, 41, 97, 200, 64], "C": [48, 130, 17, 99, 64],
+           "D": [300, 65, 530, 129, 40]}
 
 
 def _requests(name):
@@ -21,13 +22,15 @@ def _requests(name):
 
 
 def _plain_logits(model_dir, requests, dtype):
+    """Per request: (logits of the plain implementation, bfloat16 rounding noise of the request or None)."""
     cfg, w = plain.load_plain(model_dir)
-    act = torch.bfloat16 if dtype == "bfloat16" else None
-    return [plain.forward(cfg, w, r, torch.float32, act) for r in requests]
+    if dtype == "float32":
+        return [(plain.forward(cfg, w, r, torch.float32, None), None) for r in requests]
+    return [(plain.forward(cfg, w, r, torch.float32, torch.bfloat16), bf16_noise(cfg, w, r)) for r in requests]
 
 
-def _compare(got, want, dtype, what):
-    tol = logit_tolerance(dtype, want)
+def _compare(got, want, dtype, what, noise=None):
+    tol = logit_tolerance(dtype, want, noise)
     diff = (got - want).abs()
     worst = int(diff.max(dim=1).values.argmax())
     assert diff.max() <= tol, f"{what}: max |diff| {diff.max():.3e} > {tol:.3e}, first bad place {int((diff.max(dim=1).values > tol).nonzero()[0])}, worst {worst}"
@@ -46,7 +49,7 @@ def _portions(n, sizes):
 
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
-@pytest.mark.parametrize("name", ["A", "B", "C"])
+@pytest.mark.parametrize("name", ["A", "B", "C", "D"])
 def test_replay_modes(name, dtype, model_dirs, tmp_path):
     cfg, _, page = TINY[name]
     vocab = cfg["vocab_size"]
@@ -61,21 +64,21 @@ def test_replay_modes(name, dtype, model_dirs, tmp_path):
         # 1. each request alone and whole, logits at every place
         for i, r in enumerate(reqs):
             s = tr.run([(f"w{i}", r, range(len(r)))], end=[f"w{i}"])
-            _compare(tr.logits(s, vocab), want[i], dtype, f"{name} whole request {i}")
+            _compare(tr.logits(s, vocab), want[i][0], dtype, f"{name} whole request {i}", want[i][1])
         # 2. all but the last 32 tokens in one step, then one by one
         for i, r in enumerate(reqs):
             cut = max(1, len(r) - 32)
             s = tr.run([(f"d{i}", r[:cut], [cut - 1])])
-            _compare(tr.logits(s, vocab), want[i][cut - 1:cut], dtype, f"{name} request {i} prefill end")
+            _compare(tr.logits(s, vocab), want[i][0][cut - 1:cut], dtype, f"{name} request {i} prefill end", want[i][1])
             for p in range(cut, len(r)):
                 s = tr.run([(f"d{i}", r[p:p + 1], [0])], end=[f"d{i}"] if p == len(r) - 1 else [])
-                _compare(tr.logits(s, vocab), want[i][p:p + 1], dtype, f"{name} request {i} decode at {p}")
+                _compare(tr.logits(s, vocab), want[i][0][p:p + 1], dtype, f"{name} request {i} decode at {p}", want[i][1])
         # 3. portions of changing size, down to two tokens
         for i, r in enumerate(reqs):
             cuts = _portions(len(r), [7, 2, 19, 3, 2, 31, 5])
             for j, (a, b) in enumerate(cuts):
                 s = tr.run([(f"p{i}", r[a:b], range(b - a))], end=[f"p{i}"] if j == len(cuts) - 1 else [])
-                _compare(tr.logits(s, vocab), want[i][a:b], dtype, f"{name} request {i} portion {a}:{b}")
+                _compare(tr.logits(s, vocab), want[i][0][a:b], dtype, f"{name} request {i} portion {a}:{b}", want[i][1])
         # 4. mixed: requests start at different steps, portions beside single tokens, pages reused
         fed = [0] * len(reqs)
         sizes = [[9, 1, 1, 4, 1], [2, 13, 1, 1, 1, 6], [5, 1, 1, 1], [17, 1, 2, 1, 1], [3, 1, 8, 1]]
@@ -102,7 +105,7 @@ def test_replay_modes(name, dtype, model_dirs, tmp_path):
             got = tr.logits(s, vocab)
             at = 0
             for i, a, b in spans:
-                _compare(got[at:at + b - a], want[i][a:b], dtype, f"{name} mixed step {steps} request {i} {a}:{b}")
+                _compare(got[at:at + b - a], want[i][0][a:b], dtype, f"{name} mixed step {steps} request {i} {a}:{b}", want[i][1])
                 at += b - a
             steps += 1
     finally:
