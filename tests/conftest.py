@@ -57,7 +57,8 @@ TINY_D = {
     "num_attention_heads": 8, "num_key_value_heads": 2, "head_dim": 64, "vocab_size": 512, "rope_theta": 10000.0,
     "tie_word_embeddings": True, "rms_norm_eps": 1e-5, "max_position_embeddings": 640,
 }
-TINY = {"A": (TINY_A, 0, 64), "B": (TINY_B, 2, 8), "C": (TINY_C, 5, 16), "D": (TINY_D, 9, 16)}   # config, weight seed, page size
+TINY = {"A": (TINY_A, 0, 64), "B": (TINY_B, 2, 8), "C": (TINY_C, 5, 16), "D": (TINY_D, 9, 16),
+        "U": (TINY_D, 13, 32)}   # config, weight seed, page size
 
 # Weights N(0, 0.2) and gains 1 + 0.2 N(0, 1): large enough that attention is far from uniform and
 # every part changes the logits, as arhaamatiq/stride's own tiny model does (tests/make_tiny_model.py:19-54).
@@ -71,7 +72,23 @@ def model_dirs(tmp_path_factory):
     root = tmp_path_factory.mktemp("models")
     out = {}
     for name, (cfg, seed, _) in TINY.items():
+        if name == "U":
+            continue
         out[name] = write_random_model(root / name, cfg, seed, std=TEST_STD, gain_std=TEST_GAIN_STD)
+    # "U": the shape of D with query and key projections scaled down, so that attention is close to
+    # uniform and EVERY key, however far, carries weight 1/T: a kernel that loses one shows in float32.
+    import json
+    from stride_b200.weights.random_init import random_tensors
+    from stride_b200.weights.safetensors_io import write_safetensors
+    cfg, seed, _ = TINY["U"]
+    tensors = random_tensors(cfg, seed, std=TEST_STD, gain_std=TEST_GAIN_STD)
+    for n in tensors:
+        if n.endswith("q_proj.weight") or n.endswith("k_proj.weight"):
+            tensors[n] = (tensors[n].float() * 0.05).to(torch.bfloat16)
+    (root / "U").mkdir()
+    (root / "U" / "config.json").write_text(json.dumps(cfg))
+    write_safetensors(root / "U" / "model.safetensors", tensors)
+    out["U"] = root / "U"
     return out
 
 
@@ -121,20 +138,24 @@ def logit_tolerance(dtype: str, reference: torch.Tensor, noise: float | None = N
     for its exact path (tests/test_correctness.py:21), scaled with the rms for other magnitudes.
 
     bfloat16: the engine is compared with the plain implementation rounding to bfloat16 at the same
-    places, so what is left are sums taken in another order, which now and then round an activation
-    to the neighbouring bfloat16 value. The tensor cores accumulate with truncation (measured on
-    B200: mean error 2e-6 of the result at K = 2048 against 3e-7 for a float32 FMA chain), so such
-    flips are several times more frequent than between two float32 implementations. The yardstick
-    is therefore bfloat16's own rounding noise on the same model and tokens, `noise` =
-    max |plain(bfloat16 rounding) - plain(float32)|: the engine has to stay within a quarter of it.
-    A wrong key, page, position or weight moves logits by the whole noise or more, and the same
-    code paths are held to 2e-4 in float32. Without `noise`, 3% of the logits' rms.
+    places. What is left: (1) sums taken in another order, which now and then round an activation to
+    the neighbouring bfloat16 value; the tensor cores accumulate with truncation (measured on B200:
+    mean error 2e-6 of the result at K = 2048 against 3e-7 for a float32 FMA chain), so such flips are
+    several times more frequent than between two float32 implementations; (2) the tensor-core
+    attention kernels round the softmax weights to bfloat16 for the value product (the sums and the
+    maximum stay float32), one rounding the plain implementation does not have. Measured on tiny
+    configuration D (300 tokens): mean deviation 0.006 with neither, 0.012 with (1), 0.025 with both,
+    against a mean of 0.082 and a maximum of 1.02 for bfloat16's own rounding noise on the same
+    tokens, `noise` = max |plain(bfloat16 rounding) - plain(float32)|. The yardstick is that noise:
+    the engine has to stay within half of it. A dropped key, a wrong page, position or weight moves
+    logits by more than the noise itself (tests/test_plain.py checks that for a single dropped key),
+    and the same code paths are held to 2e-4 in float32. Without `noise`, 3% of the logits' rms.
     """
     rms = float(reference.float().pow(2).mean().sqrt())
     if dtype == "float32":
         return 2e-4 * max(rms, 1.0)
     if noise is not None:
-        return 0.25 * noise
+        return 0.5 * noise
     return 3e-2 * rms
 
 

@@ -13,7 +13,7 @@ from conftest import TINY, TraceRun, bf16_noise, logit_tolerance, random_tokens
 pytestmark = pytest.mark.gpu
 
 LENGTHS = {"A": [70, 100, 45, 120, 33], "B": [150, 41, 97, 200, 64], "C": [48, 130, 17, 99, 64],
-           "D": [300, 65, 530, 129, 40]}
+           "D": [300, 65, 530, 129, 40], "U": [520, 257, 64, 300, 31]}
 
 
 def _requests(name):
@@ -49,7 +49,7 @@ def _portions(n, sizes):
 
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
-@pytest.mark.parametrize("name", ["A", "B", "C", "D"])
+@pytest.mark.parametrize("name", ["A", "B", "C", "D", "U"])
 def test_replay_modes(name, dtype, model_dirs, tmp_path):
     cfg, _, page = TINY[name]
     vocab = cfg["vocab_size"]
