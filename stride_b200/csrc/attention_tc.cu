@@ -1,5 +1,6 @@
 // Paged causal attention of the bfloat16 path on tensor cores (mma.sync m16n8k16, float32
-// accumulation, float32 softmax), for head sizes 64 and 128 and any group ratio up to 16.
+// accumulation, float32 softmax whose weights enter the value product as two bfloat16 parts), for
+// head sizes 64 and 128 and any group ratio up to 16.
 //
 // The query heads that share a key/value head are stacked as rows of one tile: row r of a
 // tile is (position r / G, head r % G), G = Hq / Hkv, so a key/value tile read once serves
@@ -117,23 +118,31 @@ __device__ __forceinline__ void qk_tile(float (*s)[4], const uint32_t (*qf)[4], 
 }
 
 // O[16 x D] += P[16 x 64] V[64 x D]; P given as the float accumulators of qk_tile after exponentiation.
+// The softmax weights stay (nearly) 32-bit: each is split into a bfloat16 head and a bfloat16 remainder,
+// p = hi + lo with |p - hi - lo| <= 2^-17 p, and both parts are multiplied with V. With the head alone the
+// weights would carry a rounding of 2^-9 that the 32-bit softmax of the reference does not have.
 template <int D>
 __device__ __forceinline__ void pv_tile(float (*o)[4], const float (*s)[4], const bf16* sV, int lane) {
   constexpr int LD = D + 8;
   const int mi = lane >> 3, rr = lane & 7;
 #pragma unroll
   for (int kk = 0; kk < 4; ++kk) {
-    uint32_t a[4];
-    a[0] = pack_bf16(s[2 * kk][0], s[2 * kk][1]);
-    a[1] = pack_bf16(s[2 * kk][2], s[2 * kk][3]);
-    a[2] = pack_bf16(s[2 * kk + 1][0], s[2 * kk + 1][1]);
-    a[3] = pack_bf16(s[2 * kk + 1][2], s[2 * kk + 1][3]);
+    uint32_t hi[4], lo[4];
+#pragma unroll
+    for (int x = 0; x < 4; ++x) {
+      const float p0 = s[2 * kk + (x >> 1)][(x & 1) * 2], p1 = s[2 * kk + (x >> 1)][(x & 1) * 2 + 1];
+      const __nv_bfloat162 h = __floats2bfloat162_rn(p0, p1);
+      hi[x] = *reinterpret_cast<const uint32_t*>(&h);
+      lo[x] = pack_bf16(p0 - __low2float(h), p1 - __high2float(h));
+    }
 #pragma unroll
     for (int dt = 0; dt < D / 8; dt += 2) {
       uint32_t b[4];
       ldsm_x4_trans(b, smem_u32(sV + (kk * 16 + (mi & 1) * 8 + rr) * LD + (dt + (mi >> 1)) * 8));
-      mma_16816(o[dt], a, b[0], b[1]);
-      mma_16816(o[dt + 1], a, b[2], b[3]);
+      mma_16816(o[dt], hi, b[0], b[1]);
+      mma_16816(o[dt], lo, b[0], b[1]);
+      mma_16816(o[dt + 1], hi, b[2], b[3]);
+      mma_16816(o[dt + 1], lo, b[2], b[3]);
     }
   }
 }

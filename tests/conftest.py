@@ -138,14 +138,12 @@ def logit_tolerance(dtype: str, reference: torch.Tensor, noise: float | None = N
     for its exact path (tests/test_correctness.py:21), scaled with the rms for other magnitudes.
 
     bfloat16: the engine is compared with the plain implementation rounding to bfloat16 at the same
-    places. What is left: (1) sums taken in another order, which now and then round an activation to
+    places. What is left: sums taken in another order, which now and then round an activation to
     the neighbouring bfloat16 value; the tensor cores accumulate with truncation (measured on B200:
     mean error 2e-6 of the result at K = 2048 against 3e-7 for a float32 FMA chain), so such flips are
-    several times more frequent than between two float32 implementations; (2) the tensor-core
-    attention kernels round the softmax weights to bfloat16 for the value product (the sums and the
-    maximum stay float32), one rounding the plain implementation does not have. Measured on tiny
-    configuration D (300 tokens): mean deviation 0.006 with neither, 0.012 with (1), 0.025 with both,
-    against a mean of 0.082 and a maximum of 1.02 for bfloat16's own rounding noise on the same
+    several times more frequent than between two float32 implementations. Measured on tiny
+    configuration D (300 tokens): mean deviation 0.006 with SIMT contractions, 0.012 on the tensor
+    cores, against a mean of 0.082 and a maximum of 1.02 for bfloat16's own rounding noise on the same
     tokens, `noise` = max |plain(bfloat16 rounding) - plain(float32)|. The yardstick is that noise:
     the engine has to stay within half of it. A dropped key, a wrong page, position or weight moves
     logits by more than the noise itself (tests/test_plain.py checks that for a single dropped key),

@@ -51,6 +51,8 @@ def _portions(n, sizes):
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
 @pytest.mark.parametrize("name", ["A", "B", "C", "D", "U"])
 def test_replay_modes(name, dtype, model_dirs, tmp_path):
+    if name == "U" and dtype == "bfloat16":
+        pytest.skip("U makes every key carry weight 1/T; losing one moves logits by ~1e-3, which float32 shows and bfloat16 cannot resolve")
     cfg, _, page = TINY[name]
     vocab = cfg["vocab_size"]
     reqs = _requests(name)
