@@ -87,6 +87,9 @@ class CacheManager:
         self.entry_shared: dict = {}    # schedule entry -> entry whose cache it reads
         self.states: dict = {}          # schedule entry -> state arena
         self._dirty: set = set()        # (group, slot) rows to upload
+        # One slot and one page per group beyond those handed out: padding rows of a fixed-size batch
+        # (a step recorded as a CUDA graph) write their key and value there.
+        self.pad_slot = max_slots
         self.free_slots = list(range(max_slots - 1, -1, -1))
         self.live_slots: set = set()
         self.length = [0] * max_slots   # tokens the slot's pages have been ensured for
@@ -98,7 +101,7 @@ class CacheManager:
                 self.entry_shared[i] = need[1]
                 continue
             if need.kind == "state":
-                self.states[i] = torch.zeros((max_slots, *need.state_shape), dtype=need.state_dtype, device=self.device)
+                self.states[i] = torch.zeros((max_slots + 1, *need.state_shape), dtype=need.state_dtype, device=self.device)
                 continue
             if need.kind != "pages":
                 raise CacheError(f"unknown cache need kind '{need.kind}'")
@@ -126,9 +129,10 @@ class CacheManager:
                 raise CacheError("the cache pool is smaller than one page")
         for g in self.groups:
             g.num_pages = num_pages
-            g.arena = torch.zeros((num_pages, len(g.entries), 2, g.kv_heads, page_size, g.head_dim), dtype=g.dtype, device=self.device)
-            g.table_host = np.full((max_slots, self.max_pages_per_seq), NO_PAGE, dtype=np.int32)
-            g.table_device = torch.full((max_slots, self.max_pages_per_seq), NO_PAGE, dtype=torch.int32, device=self.device)
+            g.arena = torch.zeros((num_pages + 1, len(g.entries), 2, g.kv_heads, page_size, g.head_dim), dtype=g.dtype, device=self.device)
+            g.table_host = np.full((max_slots + 1, self.max_pages_per_seq), NO_PAGE, dtype=np.int32)
+            g.table_host[self.pad_slot, 0] = num_pages
+            g.table_device = torch.from_numpy(g.table_host).to(self.device)
             g.free = list(range(num_pages - 1, -1, -1))     # page 0 is handed out first
             if self._rng:
                 self._rng.shuffle(g.free)
@@ -246,6 +250,8 @@ class CacheManager:
                 if p in seen:
                     raise CacheError(f"page {p} is on the free list twice")
                 seen[p] = "free"
+            if g.table_host[self.pad_slot, 0] != g.num_pages:
+                raise CacheError("the padding slot lost its page")
             for slot, held in enumerate(g.held):
                 if held and slot not in self.live_slots:
                     raise CacheError(f"slot {slot} holds pages but is not live")

@@ -43,6 +43,7 @@ class EngineOptions:
     page_size: int = 64                # tokens per page
     max_context: int = 0               # longest sequence (0: config.json's max_position_embeddings)
     kv_shuffle_seed: int = 0           # tests: hand out pages in random order
+    cuda_graphs: bool = True           # replay decode-only steps from CUDA graphs (one per batch and context bucket)
     device: str = "cuda:0"
 
 
@@ -118,6 +119,11 @@ class Engine:
         self._aux_copied = torch.cuda.Event()
         self._aux_pending = False
         self.steps = 0
+        self.graph_replays = 0
+        self._graphs: dict = {}
+        self._graph_generation = 0
+        # Padding rows of a graph step write their key and value to the cache manager's spare slot.
+        self._pad_slot = self.cache.pad_slot if o.cuda_graphs else -1
 
     @classmethod
     def from_random(cls, config: dict, seed: int, options: Optional[EngineOptions] = None) -> "Engine":
@@ -148,6 +154,10 @@ class Engine:
         n = sum(len(e.tokens) for e in entries)
         if n == 0:
             return None
+        if o.cuda_graphs and n == len(entries):
+            logits = self._graph_step(entries)
+            if logits is not None:
+                return logits
         if n > o.max_rows:
             raise EngineError(f"step of {n} tokens exceeds max_rows {o.max_rows}")
         count = sum(len(e.want) for e in entries)
@@ -206,6 +216,89 @@ class Engine:
         logits = self.model.forward(ctx, self.caches, d[3 * R:3 * R + count], count)
         self.steps += 1
         return logits
+
+    # ------------------------------------------------------------------ decode steps as CUDA graphs
+    def _graph_step(self, entries: list) -> Optional[torch.Tensor]:
+        """A step in which every entry is one decoded token whose logits are wanted: padded to a batch
+        bucket, run from a CUDA graph recorded for (batch bucket, context bucket). Returns None if the step
+        does not qualify."""
+        o = self.options
+        E = len(entries)
+        if self._pad_slot < 0 or E == 0 or E > self.env.max_logit_rows:
+            return None
+        for e in entries:
+            if len(e.tokens) != 1 or e.want != [0]:
+                return None
+        B = 1
+        while B < E:
+            B *= 2
+        if B > min(o.max_rows, self.env.max_logit_rows):
+            B = E
+        last = max(e.first_pos for e in entries)
+        keys = 256
+        while keys <= last:
+            keys *= 2
+        R, vocab = o.max_rows, self.spec.vocab_size
+        if self._copy_pending:
+            self._copied.synchronize()
+        buf = self._staging_np
+        meta = buf[4 * R:8 * R].reshape(4, R)
+        seen = set()
+        for i, e in enumerate(entries):
+            if e.slot in seen or e.slot not in self.cache.live_slots or e.slot == self._pad_slot:
+                raise EngineError(f"slot {e.slot} appears twice in one step or is not held by a request")
+            seen.add(e.slot)
+            if e.first_pos < 0 or e.first_pos + 1 > self.cache.length[e.slot]:
+                raise EngineError(f"slot {e.slot}: token {e.first_pos} has no page (ensured up to {self.cache.length[e.slot]})")
+            t = int(e.tokens[0])
+            if not 0 <= t < vocab:
+                raise EngineError(f"token id {t} out of range 0..{vocab - 1}")
+            buf[i], buf[R + i], buf[2 * R + i] = t, e.first_pos, e.slot
+            meta[0, i], meta[1, i], meta[2, i], meta[3, i] = e.slot, i, 1, e.first_pos
+        for i in range(E, B):
+            buf[i], buf[R + i], buf[2 * R + i] = 0, 0, self._pad_slot
+            meta[0, i], meta[1, i], meta[2, i], meta[3, i] = self._pad_slot, i, 1, 0
+        buf[3 * R:3 * R + B] = np.arange(B)
+        self._device_ints.copy_(self._staging, non_blocking=True)
+        self._copied.record()
+        self._copy_pending = True
+        self.cache.sync()
+        if self._graph_generation != self.workspace.generation:
+            self._graphs.clear()
+            self._graph_generation = self.workspace.generation
+        key = (B, keys)
+        graph = self._graphs.get(key)
+        d = self._device_ints
+
+        def run():
+            ctx = StepContext(
+                n=B, token_ids=d[0:B], positions=d[R:R + B], slots=d[2 * R:2 * R + B], workspace=self.workspace,
+                compute_dtype=self.compute_dtype, entry_slots=[0] * B, entry_first_row=list(range(B)),
+                entry_length=[1] * B, entry_first_pos=[0] * B, entry_meta=d[4 * R:8 * R].view(4, R)[:, :B],
+                upload_ints=None, static_keys=keys)
+            return self.model.forward(ctx, self.caches, d[3 * R:3 * R + B], B)
+
+        if graph is None:
+            logits = run()                      # allocates what the step needs and gives this step's result
+            if self._graph_generation != self.workspace.generation:
+                self._graphs.clear()
+                self._graph_generation = self.workspace.generation
+            torch.cuda.synchronize()
+            g = torch.cuda.CUDAGraph()
+            from ..kernels import ops
+            before = ops.launches
+            with torch.cuda.graph(g):
+                static_logits = run()
+            self._graphs[key] = (g, static_logits, ops.launches - before)
+            logits = static_logits              # recorded, not run: the eager run above left the same buffer filled
+        else:
+            graph[0].replay()
+            logits = graph[1]
+            self.graph_replays += 1
+            from ..kernels import ops
+            ops.launches += graph[2]
+        self.steps += 1
+        return logits[:E]
 
     def weight_bytes_per_step(self) -> int:
         return self.model.weight_bytes()

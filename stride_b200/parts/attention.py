@@ -82,6 +82,10 @@ class AttentionMixer(Mixer):
         cut into tiles of 64 // G positions. Made once per step and shared by all layers of this ratio."""
         key = ("attention_tc_plan", G)
         plan = ctx.shared.get(key)
+        if plan is None and ctx.static_keys:
+            E = len(ctx.entry_length)
+            plan = (ctx.workspace.iota(E), 0, E, (ctx.static_keys + 255) // 256)
+            ctx.shared[key] = plan
         if plan is None:
             ppt, short = 64 // G, 16 // G
             tiles, items, last = [], [], 0

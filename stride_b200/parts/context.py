@@ -16,6 +16,8 @@ class Workspace:
         self.device = torch.device(device)
         self.max_tokens = max_tokens
         self._buffers: dict = {}
+        self.generation = 0          # bumped whenever a buffer that `grow` handed out moves
+        self._iota = None
 
     def get(self, name: str, rows: int, tail: tuple, dtype: torch.dtype) -> torch.Tensor:
         """A `[rows, *tail]` view of the buffer `name` (rows <= max_tokens)."""
@@ -42,9 +44,17 @@ class Workspace:
         key = (name, "grow", dtype)
         buf = self._buffers.get(key)
         if buf is None or buf.numel() < numel:
+            if buf is not None:
+                self.generation += 1
             buf = torch.zeros(max(numel, 1) * 3 // 2 + 16, dtype=dtype, device=self.device)
             self._buffers[key] = buf
         return buf
+
+    def iota(self, n: int) -> torch.Tensor:
+        """[0, 1, ..., n-1] int32 on the device (a view of one cached tensor)."""
+        if self._iota is None or self._iota.numel() < n:
+            self._iota = torch.arange(max(n, self.max_tokens), dtype=torch.int32, device=self.device)
+        return self._iota[:n]
 
     def bytes(self) -> int:
         return sum(b.numel() * b.element_size() for b in self._buffers.values())
@@ -97,6 +107,10 @@ class StepContext:
     entry_meta: Optional[torch.Tensor] = None              # [4, E] int32 on the device: slot, first row, length, first position
     upload_ints: Optional[object] = None                   # callable(np.ndarray int32) -> device tensor, valid for this step
     shared: dict = field(default_factory=dict)             # what parts compute once per step and share between layers
+    # Set for a step that is recorded into a CUDA graph: every entry is one decoded token, the batch is
+    # padded to a fixed size, and no key lies at or beyond `static_keys`. Parts must then launch the same
+    # kernels with the same arguments whatever the positions are, and must not copy from the host.
+    static_keys: int = 0
 
     @property
     def act_dtype(self) -> torch.dtype:
