@@ -45,6 +45,8 @@ __global__ void __launch_bounds__(kTile) attention_generic_kernel(AttnParams p) 
   __shared__ int64_t koff[kTile];  // element offset of each key row of the tile
   __shared__ float red[32];
 
+  sb::grid_launch_dependents();
+  sb::grid_dependency_wait();
   const int row = blockIdx.x, head = blockIdx.y, t = threadIdx.x;
   const int D = p.D;
   const int kvh = head / (p.Hq / p.Hkv);
@@ -121,8 +123,8 @@ SB_EXPORT int sb_attention_generic(const void* q, void* out, int dtype, const vo
                positions, slots, Hq, Hkv, D, window, scale};
   dim3 grid(n, Hq);
   const size_t smem = static_cast<size_t>(D + kTile) * sizeof(float);
-  if (dtype == 0) attention_generic_kernel<float, float, float><<<grid, kTile, smem, stream>>>(p);
-  else if (dtype == 1) attention_generic_kernel<bf16, bf16, bf16><<<grid, kTile, smem, stream>>>(p);
+  if (dtype == 0) sb::launch_pdl(attention_generic_kernel<float, float, float>, grid, dim3(kTile), smem, stream, p);
+  else if (dtype == 1) sb::launch_pdl(attention_generic_kernel<bf16, bf16, bf16>, grid, dim3(kTile), smem, stream, p);
   else return sb::fail("sb_attention_generic: unsupported dtype %d", dtype);
   return sb::check_launch("sb_attention_generic");
 }

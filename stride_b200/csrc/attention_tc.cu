@@ -156,6 +156,8 @@ __global__ void __launch_bounds__(128) attn_chunk_kernel(const AttnTcParams p) {
   bf16* sK = sQ + 64 * LD;                       // [2][64][LD]
   bf16* sV = sK + 2 * 64 * LD;                   // [2][64][LD]
 
+  sb::grid_launch_dependents();
+  sb::grid_dependency_wait();
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31, gid = lane >> 2, tq = lane & 3;
   const int g = blockIdx.y;
   const int G = p.Hq / p.Hkv, ppt = 64 / G;
@@ -284,6 +286,8 @@ __global__ void __launch_bounds__(128) attn_decode_kernel(const AttnTcParams p) 
   float* sO = reinterpret_cast<float*>(sKV + 4 * 2 * 64 * LD);  // [4][16][D]
   float* sML = sO + 4 * 16 * D;                           // [4][16][2]
 
+  sb::grid_launch_dependents();
+  sb::grid_dependency_wait();
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31, gid = lane >> 2, tq = lane & 3;
   const int item = blockIdx.x, g = blockIdx.y, chunk = blockIdx.z;
   const int G = p.Hq / p.Hkv;
@@ -408,6 +412,8 @@ __global__ void __launch_bounds__(128) attn_decode_kernel(const AttnTcParams p) 
 
 template <int D>
 __global__ void __launch_bounds__(D) attn_combine_kernel(const AttnTcParams p) {
+  sb::grid_launch_dependents();
+  sb::grid_dependency_wait();
   const int item = blockIdx.x, g = blockIdx.y, d = threadIdx.x;
   const int G = p.Hq / p.Hkv;
   const int e = p.work[item];
@@ -440,7 +446,7 @@ int launch(const AttnTcParams& p, int n_tiles, int n_items, cudaStream_t stream)
         return sb::fail("sb_attention_tc: cannot raise the shared memory limit");
       set = true;
     }
-    attn_chunk_kernel<D><<<dim3(n_tiles, p.Hkv), 128, smem, stream>>>(p);
+    sb::launch_pdl(attn_chunk_kernel<D>, dim3(n_tiles, p.Hkv), dim3(128), smem, stream, p);
   }
   if (n_items > 0) {
     const size_t smem = static_cast<size_t>(16 * LD + 8 * 64 * LD) * sizeof(bf16) + static_cast<size_t>(4 * 16 * D + 4 * 16 * 2) * sizeof(float);
@@ -452,8 +458,8 @@ int launch(const AttnTcParams& p, int n_tiles, int n_items, cudaStream_t stream)
     }
     AttnTcParams pd = p;
     pd.work = p.work + 2 * n_tiles;
-    attn_decode_kernel<D><<<dim3(n_items, p.Hkv, p.chunks), 128, smem, stream>>>(pd);
-    attn_combine_kernel<D><<<dim3(n_items, p.Hkv), D, 0, stream>>>(pd);
+    sb::launch_pdl(attn_decode_kernel<D>, dim3(n_items, p.Hkv, p.chunks), dim3(128), smem, stream, pd);
+    sb::launch_pdl(attn_combine_kernel<D>, dim3(n_items, p.Hkv), dim3(D), 0, stream, pd);
   }
   return sb::check_launch("sb_attention_tc");
 }

@@ -36,6 +36,29 @@ inline int check_launch(const char* what) {
   return 0;
 }
 
+// Programmatic dependent launch: a kernel launched with `launch_pdl` may start while its predecessor
+// in the stream still runs. `grid_dependency_wait()` returns once the predecessor has finished and its
+// writes are visible; every kernel calls it before its first read of data another kernel wrote and
+// before its first global write, so completion of a kernel implies completion of all before it.
+// `grid_launch_dependents()` lets the successor's blocks be scheduled (they then sit in their own wait).
+__device__ __forceinline__ void grid_dependency_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+__device__ __forceinline__ void grid_launch_dependents() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+
+template <class... KArgs, class... Args>
+inline void launch_pdl(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t stream, Args&&... args) {
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = grid;
+  cfg.blockDim = block;
+  cfg.dynamicSmemBytes = smem;
+  cfg.stream = stream;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = 1;
+  cudaLaunchKernelEx(&cfg, kernel, KArgs(args)...);   // errors surface through check_launch()
+}
+
 __device__ __forceinline__ float widen(float v) { return v; }
 __device__ __forceinline__ float widen(__nv_bfloat16 v) { return __bfloat162float(v); }
 

@@ -20,6 +20,8 @@ using bf16 = __nv_bfloat16;
 template <class TW>
 __global__ void embed_kernel(const int32_t* __restrict__ tokens, const TW* __restrict__ table,
                              float* __restrict__ out, int H, int vocab) {
+  sb::grid_launch_dependents();
+  sb::grid_dependency_wait();
   const int row = blockIdx.x;
   const int tok = tokens[row];
   const bool ok = tok >= 0 && tok < vocab;
@@ -31,22 +33,51 @@ __global__ void embed_kernel(const int32_t* __restrict__ tokens, const TW* __res
 // ------------------------------------------------------------------ rmsnorm
 // One block per row. The row is (h + partial_0 + partial_1 + ...), summed left to
 // right; when partials are given the sum is written back to h. Then
-// r = 1/sqrt(sum(x^2)/H + eps) and out = w * (x * r).
-template <class TW, class TO>
+// r = 1/sqrt(sum(x^2)/H + eps) and out = w * (x * r). VEC = 4 reads float4 (H % 4 == 0);
+// the partials are fetched four at a time so that their loads overlap.
+template <int VEC>
+struct VecF;
+template <>
+struct VecF<4> { using type = float4; };
+template <>
+struct VecF<1> { using type = float; };
+
+__device__ __forceinline__ float4 add4(float4 a, float4 b) { return make_float4(a.x + b.x, a.y + b.y, a.z + b.z, a.w + b.w); }
+__device__ __forceinline__ float add4(float a, float b) { return a + b; }
+
+template <class TW, class TO, int VEC>
 __global__ void rmsnorm_kernel(float* __restrict__ h, const float* __restrict__ partials, int n_partials,
                                int64_t partial_stride, const TW* __restrict__ weight, TO* __restrict__ out,
                                int H, float eps) {
-  extern __shared__ float row[];
+  using V = typename VecF<VEC>::type;
+  extern __shared__ __align__(16) float row[];
   __shared__ float red[32];
+  sb::grid_launch_dependents();
+  sb::grid_dependency_wait();
   const int r = blockIdx.x;
-  float* hr = h + static_cast<int64_t>(r) * H;
+  V* hr = reinterpret_cast<V*>(h + static_cast<int64_t>(r) * H);
+  const int units = H / VEC;
   float ss = 0.0f;
-  for (int i = threadIdx.x; i < H; i += blockDim.x) {
-    float v = hr[i];
-    for (int s = 0; s < n_partials; ++s) v += partials[s * partial_stride + static_cast<int64_t>(r) * H + i];
+  for (int i = threadIdx.x; i < units; i += blockDim.x) {
+    V v = hr[i];
+    const V* p = reinterpret_cast<const V*>(partials + static_cast<int64_t>(r) * H) + i;
+    const int64_t ps = partial_stride / VEC;
+    int s = 0;
+    for (; s + 4 <= n_partials; s += 4) {
+      const V a = p[s * ps], b = p[(s + 1) * ps], c = p[(s + 2) * ps], d = p[(s + 3) * ps];
+      v = add4(add4(add4(add4(v, a), b), c), d);
+    }
+    for (; s < n_partials; ++s) v = add4(v, p[s * ps]);
     if (n_partials > 0) hr[i] = v;
-    row[i] = v;
-    ss = fmaf(v, v, ss);
+    reinterpret_cast<V*>(row)[i] = v;
+    if constexpr (VEC == 4) {
+      ss = fmaf(v.x, v.x, ss);
+      ss = fmaf(v.y, v.y, ss);
+      ss = fmaf(v.z, v.z, ss);
+      ss = fmaf(v.w, v.w, ss);
+    } else {
+      ss = fmaf(v, v, ss);
+    }
   }
   const float total = sb::block_sum(ss, red);
   const float scale = 1.0f / sqrtf(total / static_cast<float>(H) + eps);
@@ -75,60 +106,77 @@ struct RopeAppendParams {
   int write_kv;
 };
 
+// One thread per (head, rotation pair) of a token; blockIdx.y walks the token's pairs.
 template <class TQ, class TKV>
 __global__ void rope_append_kernel(RopeAppendParams p) {
+  sb::grid_launch_dependents();
+  sb::grid_dependency_wait();
   const int row = blockIdx.x;
-  const int pos = p.positions[row];
-  const int slot = p.slots[row];
   const int D = p.D, half = D / 2, rh = p.rotary_dim / 2;
   const int heads = p.Hq + 2 * p.Hkv;
+  const int item = blockIdx.y * blockDim.x + threadIdx.x;
+  if (item >= heads * half) return;
+  const int pos = p.positions[row];
+  const int slot = p.slots[row];
   const int width = heads * D;
-  const float* cs = p.cos_sin + static_cast<int64_t>(pos) * rh * 2;
-  int64_t kv_at = 0;
-  if (p.write_kv) {
-    const int page = p.block_table[static_cast<int64_t>(slot) * p.max_pages + pos / p.page_size];
-    kv_at = static_cast<int64_t>(page) * p.page_stride + static_cast<int64_t>(pos % p.page_size) * D;
+  const int head = item / half, j = item % half;
+  int d0, d1;
+  if (j < rh) {
+    d0 = j;
+    d1 = j + rh;
+  } else {
+    d0 = p.rotary_dim + 2 * (j - rh);
+    d1 = d0 + 1;
   }
-  for (int item = threadIdx.x; item < heads * half; item += blockDim.x) {
-    const int head = item / half, j = item % half;
-    int d0, d1;
-    if (j < rh) {
-      d0 = j;
-      d1 = j + rh;
-    } else {
-      d0 = p.rotary_dim + 2 * (j - rh);
-      d1 = d0 + 1;
-    }
-    const int64_t at = static_cast<int64_t>(row) * width + static_cast<int64_t>(head) * D;
-    float a = p.qkv[at + d0], b = p.qkv[at + d1];
-    for (int s = 1; s < p.n_partials; ++s) {
-      a += p.qkv[s * p.partial_stride + at + d0];
-      b += p.qkv[s * p.partial_stride + at + d1];
-    }
-    const bool is_v = head >= p.Hq + p.Hkv;
-    if (j < rh && !is_v) {
-      const float c = cs[2 * j], s = cs[2 * j + 1];
-      const float ra = __fsub_rn(__fmul_rn(a, c), __fmul_rn(b, s));
-      const float rb = __fadd_rn(__fmul_rn(b, c), __fmul_rn(a, s));
-      a = ra;
-      b = rb;
-    }
-    if (head < p.Hq) {
-      TQ* q = static_cast<TQ*>(p.q_out) + static_cast<int64_t>(row) * p.Hq * D + static_cast<int64_t>(head) * D;
-      q[d0] = sb::narrow<TQ>(a);
-      q[d1] = sb::narrow<TQ>(b);
-    } else if (p.write_kv) {
-      const int kvh = is_v ? head - p.Hq - p.Hkv : head - p.Hq;
-      TKV* dst = static_cast<TKV*>(p.k_base) + kv_at + static_cast<int64_t>(kvh) * p.head_stride + (is_v ? p.v_offset : 0);
-      dst[d0] = sb::narrow<TKV>(a);
-      dst[d1] = sb::narrow<TKV>(b);
-    }
+  const bool is_v = head >= p.Hq + p.Hkv;
+  const bool rotate = j < rh && !is_v;
+  float c = 1.0f, sn = 0.0f;
+  if (rotate) {
+    const float2 cs = *reinterpret_cast<const float2*>(p.cos_sin + (static_cast<int64_t>(pos) * rh + j) * 2);
+    c = cs.x;
+    sn = cs.y;
+  }
+  int page = 0;
+  if (p.write_kv && head >= p.Hq) page = p.block_table[static_cast<int64_t>(slot) * p.max_pages + pos / p.page_size];
+  const float* src = p.qkv + static_cast<int64_t>(row) * width + static_cast<int64_t>(head) * D;
+  float a = src[d0], b = src[d1];
+  int s = 1;
+  for (; s + 4 <= p.n_partials; s += 4) {
+    const float* q0 = src + s * p.partial_stride;
+    const float a0 = q0[d0], b0 = q0[d1], a1 = q0[p.partial_stride + d0], b1 = q0[p.partial_stride + d1];
+    const float a2 = q0[2 * p.partial_stride + d0], b2 = q0[2 * p.partial_stride + d1];
+    const float a3 = q0[3 * p.partial_stride + d0], b3 = q0[3 * p.partial_stride + d1];
+    a = (((a + a0) + a1) + a2) + a3;
+    b = (((b + b0) + b1) + b2) + b3;
+  }
+  for (; s < p.n_partials; ++s) {
+    a += src[s * p.partial_stride + d0];
+    b += src[s * p.partial_stride + d1];
+  }
+  if (rotate) {
+    const float ra = __fsub_rn(__fmul_rn(a, c), __fmul_rn(b, sn));
+    const float rb = __fadd_rn(__fmul_rn(b, c), __fmul_rn(a, sn));
+    a = ra;
+    b = rb;
+  }
+  if (head < p.Hq) {
+    TQ* q = static_cast<TQ*>(p.q_out) + static_cast<int64_t>(row) * p.Hq * D + static_cast<int64_t>(head) * D;
+    q[d0] = sb::narrow<TQ>(a);
+    q[d1] = sb::narrow<TQ>(b);
+  } else if (p.write_kv) {
+    const int kvh = is_v ? head - p.Hq - p.Hkv : head - p.Hq;
+    TKV* dst = static_cast<TKV*>(p.k_base) + static_cast<int64_t>(page) * p.page_stride +
+               static_cast<int64_t>(pos % p.page_size) * D + static_cast<int64_t>(kvh) * p.head_stride + (is_v ? p.v_offset : 0);
+    dst[d0] = sb::narrow<TKV>(a);
+    dst[d1] = sb::narrow<TKV>(b);
   }
 }
 
 // ------------------------------------------------------------------ swiglu
 template <class TO>
 __global__ void swiglu_kernel(const float* __restrict__ gate_up, TO* __restrict__ out, int n, int I) {
+  sb::grid_launch_dependents();
+  sb::grid_dependency_wait();
   const int64_t total = static_cast<int64_t>(n) * I;
   for (int64_t i = blockIdx.x * static_cast<int64_t>(blockDim.x) + threadIdx.x; i < total;
        i += static_cast<int64_t>(gridDim.x) * blockDim.x) {
@@ -142,6 +190,8 @@ __global__ void swiglu_kernel(const float* __restrict__ gate_up, TO* __restrict_
 __global__ void gather_rows_kernel(const float* __restrict__ in, const float* __restrict__ partials, int n_partials,
                                    int64_t partial_stride, const int32_t* __restrict__ rows,
                                    float* __restrict__ out, int H) {
+  sb::grid_launch_dependents();
+  sb::grid_dependency_wait();
   const int src = rows[blockIdx.x];
   for (int i = threadIdx.x; i < H; i += blockDim.x) {
     float v = in[static_cast<int64_t>(src) * H + i];
@@ -158,9 +208,9 @@ SB_EXPORT int sb_embed(const int32_t* tokens, const void* table, int table_dtype
                        cudaStream_t stream) {
   if (n <= 0) return 0;
   if (table_dtype == 0)
-    embed_kernel<float><<<n, 256, 0, stream>>>(tokens, static_cast<const float*>(table), out, H, vocab);
+    sb::launch_pdl(embed_kernel<float>, n, 256, 0, stream, tokens, static_cast<const float*>(table), out, H, vocab);
   else if (table_dtype == 1)
-    embed_kernel<bf16><<<n, 256, 0, stream>>>(tokens, static_cast<const bf16*>(table), out, H, vocab);
+    sb::launch_pdl(embed_kernel<bf16>, n, 256, 0, stream, tokens, static_cast<const bf16*>(table), out, H, vocab);
   else
     return sb::fail("sb_embed: unsupported table dtype %d", table_dtype);
   return sb::check_launch("sb_embed");
@@ -171,13 +221,20 @@ SB_EXPORT int sb_rmsnorm(float* h, const float* partials, int n_partials, int64_
   if (n <= 0) return 0;
   const size_t smem = static_cast<size_t>(H) * sizeof(float);
   if (smem > 200 * 1024) return sb::fail("sb_rmsnorm: width %d does not fit the row buffer (max 51200)", H);
-  const int threads = H >= 1024 ? 256 : 128;
-#define SB_NORM(TW, TO)                                                                                          \
+  const bool vec = H % 4 == 0 && partial_stride % 4 == 0 && ((reinterpret_cast<uintptr_t>(h) | reinterpret_cast<uintptr_t>(partials)) & 15) == 0;
+  const int units = vec ? H / 4 : H;
+  const int threads = units >= 1024 ? 1024 : units >= 512 ? 512 : units >= 256 ? 256 : 128;
+#define SB_NORM_V(TW, TO, VEC)                                                                                   \
   do {                                                                                                           \
     if (smem > 48 * 1024)                                                                                        \
-      cudaFuncSetAttribute(rmsnorm_kernel<TW, TO>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);      \
-    rmsnorm_kernel<TW, TO><<<n, threads, smem, stream>>>(h, partials, n_partials, partial_stride,               \
-                                                         static_cast<const TW*>(weight), static_cast<TO*>(out), H, eps); \
+      cudaFuncSetAttribute(rmsnorm_kernel<TW, TO, VEC>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem); \
+    sb::launch_pdl(rmsnorm_kernel<TW, TO, VEC>, n, threads, smem, stream, h, partials, n_partials, partial_stride, \
+                   static_cast<const TW*>(weight), static_cast<TO*>(out), H, eps);                              \
+  } while (0)
+#define SB_NORM(TW, TO)          \
+  do {                           \
+    if (vec) SB_NORM_V(TW, TO, 4); \
+    else SB_NORM_V(TW, TO, 1);   \
   } while (0)
   if (weight_dtype == 0 && out_dtype == 0) SB_NORM(float, float);
   else if (weight_dtype == 0 && out_dtype == 1) SB_NORM(float, bf16);
@@ -185,6 +242,7 @@ SB_EXPORT int sb_rmsnorm(float* h, const float* partials, int n_partials, int64_
   else if (weight_dtype == 1 && out_dtype == 1) SB_NORM(bf16, bf16);
   else return sb::fail("sb_rmsnorm: unsupported dtypes weight=%d out=%d", weight_dtype, out_dtype);
 #undef SB_NORM
+#undef SB_NORM_V
   return sb::check_launch("sb_rmsnorm");
 }
 
@@ -199,11 +257,12 @@ SB_EXPORT int sb_rope_append(const float* qkv, int n_partials, int64_t partial_s
   if (n_partials < 1) return sb::fail("sb_rope_append: n_partials must be >= 1");
   RopeAppendParams p{qkv, n_partials, partial_stride, positions, slots, cos_sin, rotary_dim, q_out, k_base,
                      block_table, max_pages, page_size, page_stride, v_offset, head_stride, Hq, Hkv, D, write_kv};
-  const int threads = 256;
-  if (q_dtype == 0 && kv_dtype == 0) rope_append_kernel<float, float><<<n, threads, 0, stream>>>(p);
-  else if (q_dtype == 1 && kv_dtype == 1) rope_append_kernel<bf16, bf16><<<n, threads, 0, stream>>>(p);
-  else if (q_dtype == 0 && kv_dtype == 1) rope_append_kernel<float, bf16><<<n, threads, 0, stream>>>(p);
-  else if (q_dtype == 1 && kv_dtype == 0) rope_append_kernel<bf16, float><<<n, threads, 0, stream>>>(p);
+  const int threads = 128;
+  const dim3 grid(n, ((Hq + 2 * Hkv) * (D / 2) + threads - 1) / threads);
+  if (q_dtype == 0 && kv_dtype == 0) sb::launch_pdl(rope_append_kernel<float, float>, grid, threads, 0, stream, p);
+  else if (q_dtype == 1 && kv_dtype == 1) sb::launch_pdl(rope_append_kernel<bf16, bf16>, grid, threads, 0, stream, p);
+  else if (q_dtype == 0 && kv_dtype == 1) sb::launch_pdl(rope_append_kernel<float, bf16>, grid, threads, 0, stream, p);
+  else if (q_dtype == 1 && kv_dtype == 0) sb::launch_pdl(rope_append_kernel<bf16, float>, grid, threads, 0, stream, p);
   else return sb::fail("sb_rope_append: unsupported dtypes q=%d kv=%d", q_dtype, kv_dtype);
   return sb::check_launch("sb_rope_append");
 }
@@ -212,8 +271,8 @@ SB_EXPORT int sb_swiglu(const float* gate_up, void* out, int out_dtype, int n, i
   if (n <= 0) return 0;
   const int64_t total = static_cast<int64_t>(n) * I;
   const int blocks = static_cast<int>((total + 255) / 256 < 148 * 16 ? (total + 255) / 256 : 148 * 16);
-  if (out_dtype == 0) swiglu_kernel<float><<<blocks, 256, 0, stream>>>(gate_up, static_cast<float*>(out), n, I);
-  else if (out_dtype == 1) swiglu_kernel<bf16><<<blocks, 256, 0, stream>>>(gate_up, static_cast<bf16*>(out), n, I);
+  if (out_dtype == 0) sb::launch_pdl(swiglu_kernel<float>, blocks, 256, 0, stream, gate_up, static_cast<float*>(out), n, I);
+  else if (out_dtype == 1) sb::launch_pdl(swiglu_kernel<bf16>, blocks, 256, 0, stream, gate_up, static_cast<bf16*>(out), n, I);
   else return sb::fail("sb_swiglu: unsupported out dtype %d", out_dtype);
   return sb::check_launch("sb_swiglu");
 }
@@ -221,6 +280,6 @@ SB_EXPORT int sb_swiglu(const float* gate_up, void* out, int out_dtype, int n, i
 SB_EXPORT int sb_gather_rows(const float* in, const float* partials, int n_partials, int64_t partial_stride,
                              const int32_t* rows, float* out, int count, int H, cudaStream_t stream) {
   if (count <= 0) return 0;
-  gather_rows_kernel<<<count, 256, 0, stream>>>(in, partials, n_partials, partial_stride, rows, out, H);
+  sb::launch_pdl(gather_rows_kernel, count, 256, 0, stream, in, partials, n_partials, partial_stride, rows, out, H);
   return sb::check_launch("sb_gather_rows");
 }

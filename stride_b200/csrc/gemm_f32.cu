@@ -24,6 +24,8 @@ __global__ void __launch_bounds__(256) gemm_f32_kernel(const TX* __restrict__ x,
                                                         float* __restrict__ out, int64_t ldo, int n, int M, int K) {
   __shared__ float xs[TK][TM + 4];
   __shared__ float ws[TK][TN + 4];
+  sb::grid_launch_dependents();
+  sb::grid_dependency_wait();
   const int t = threadIdx.x;
   const int row0 = blockIdx.y * TM, col0 = blockIdx.x * TN;
   const int ty = t / 16, tx = t % 16;  // 16 x 16 threads, each 4 x 4 outputs
@@ -84,8 +86,8 @@ SB_EXPORT int sb_gemm_f32(const void* x, int x_dtype, int64_t ldx, const void* w
   dim3 grid((M + TN - 1) / TN, (n + TM - 1) / TM);
   if (grid.y > 65535) return sb::fail("sb_gemm_f32: %d rows exceed the grid (max %d)", n, 65535 * TM);
 #define SB_GEMM(TX, TW, ACC)                                                                          \
-  gemm_f32_kernel<TX, TW, ACC><<<grid, 256, 0, stream>>>(static_cast<const TX*>(x), ldx, static_cast<const TW*>(w), \
-                                                          ldw, out, ldo, n, M, K)
+  sb::launch_pdl(gemm_f32_kernel<TX, TW, ACC>, grid, dim3(256), 0, stream, static_cast<const TX*>(x), ldx,         \
+                 static_cast<const TW*>(w), ldw, out, ldo, n, M, K)
 #define SB_GEMM_W(TX)                                                     \
   do {                                                                    \
     if (weight_dtype == 0 && accumulate) SB_GEMM(TX, float, true);        \

@@ -183,15 +183,17 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
   tc_fence_after();
   const uint32_t tmem_base = tmem_base_s;
 
+  sb::grid_launch_dependents();
   if (warp == 0) {
     if (lane == 0) {
-      // ---------------- producer: TMA loads
+      // ---------------- producer: TMA loads. The weights do not depend on the kernels before this one,
+      // so the first ring of weight tiles is requested before waiting for them to finish; the tokens'
+      // tiles follow once their producer is done.
       const int row_w = EPI == kSwiglu ? tile_m * 64 : tile_m * kTileM;
-      for (int i = 0; i < iters; ++i) {
+      auto load_w = [&](int i) {
         const int s = i % p.stages;
-        if (i >= p.stages) mbar_wait(smem_u32(&empty_bar[s]), ((i / p.stages) - 1) & 1, p.status, 1);
         const uint32_t bar = smem_u32(&full_bar[s]);
-        const uint32_t a = smem0 + s * stage_bytes, b = a + kStageA;
+        const uint32_t a = smem0 + s * stage_bytes;
         mbar_expect_tx(bar, stage_bytes);
         const int k = (kb0 + i) * kTileK;
         if (EPI == kSwiglu) {
@@ -200,7 +202,19 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
         } else {
           tma_load_2d(a, &map_w, bar, k, row_w);
         }
-        tma_load_2d(b, &map_x, bar, k, tile_n * BN);
+      };
+      auto load_x = [&](int i) {
+        const int s = i % p.stages;
+        tma_load_2d(smem0 + s * stage_bytes + kStageA, &map_x, smem_u32(&full_bar[s]), (kb0 + i) * kTileK, tile_n * BN);
+      };
+      const int ahead = min(iters, p.stages);
+      for (int i = 0; i < ahead; ++i) load_w(i);
+      sb::grid_dependency_wait();
+      for (int i = 0; i < ahead; ++i) load_x(i);
+      for (int i = ahead; i < iters; ++i) {
+        mbar_wait(smem_u32(&empty_bar[i % p.stages]), ((i / p.stages) - 1) & 1, p.status, 1);
+        load_w(i);
+        load_x(i);
       }
     }
   } else if (warp == 1) {
@@ -226,6 +240,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
   } else {
     // ---------------- epilogue: warps 2..5 own TMEM lanes 32 * (warp % 4) ..
     const int quarter = warp & 3;
+    sb::grid_dependency_wait();
     const bool ok = iters > 0 && mbar_wait(smem_u32(&accum_bar), 0, p.status, 3);
     tc_fence_after();
     const int n0 = tile_n * BN;
@@ -409,7 +424,7 @@ SB_EXPORT int sb_gemm_tc(const void* x, int64_t ldx, const void* w, int64_t ldw,
         return sb::fail("sb_gemm_tc: cannot raise the shared memory limit");                        \
       attr_set = true;                                                                              \
     }                                                                                               \
-    gemm_tc_kernel<EPI><<<grid, kThreads, smem, stream>>>(map_w, map_x, p);                        \
+    sb::launch_pdl(gemm_tc_kernel<EPI>, grid, dim3(kThreads), smem, stream, map_w, map_x, p);       \
   } while (0)
   if (epilogue == kStore) SB_LAUNCH(kStore);
   else if (epilogue == kAdd) SB_LAUNCH(kAdd);

@@ -40,6 +40,8 @@ __device__ __forceinline__ unsigned long long pack_best(float v, int idx) {
 __global__ void __launch_bounds__(kThreads) argmax_kernel(const float* __restrict__ logits, int64_t ld, int vocab,
                                                            int32_t* __restrict__ tokens, float* __restrict__ values) {
   __shared__ unsigned long long best_s[32];
+  sb::grid_launch_dependents();
+  sb::grid_dependency_wait();
   const float* l = logits + static_cast<int64_t>(blockIdx.x) * ld;
   unsigned long long best = 0;
   for (int i = threadIdx.x; i < vocab; i += kThreads) {
@@ -74,6 +76,8 @@ __global__ void __launch_bounds__(kThreads) sample_temperature_kernel(
   __shared__ uint32_t prefix_s;
   __shared__ double u_s;
   __shared__ int found_s;
+  sb::grid_launch_dependents();
+  sb::grid_dependency_wait();
   const int row = blockIdx.x, t = threadIdx.x;
   const float* l = logits + static_cast<int64_t>(row) * ld;
   const double T = static_cast<double>(temperatures[row]);
@@ -181,7 +185,7 @@ SB_EXPORT int sb_argmax(const float* logits, int64_t ld, int rows, int vocab, in
                         cudaStream_t stream) {
   if (rows <= 0) return 0;
   if (vocab <= 0) return sb::fail("sb_argmax: empty vocabulary");
-  argmax_kernel<<<rows, kThreads, 0, stream>>>(logits, ld, vocab, tokens, values);
+  sb::launch_pdl(argmax_kernel, dim3(rows), dim3(kThreads), 0, stream, logits, ld, vocab, tokens, values);
   return sb::check_launch("sb_argmax");
 }
 
@@ -190,6 +194,6 @@ SB_EXPORT int sb_sample_temperature(const float* logits, int64_t ld, int rows, i
                                     float* values, cudaStream_t stream) {
   if (rows <= 0) return 0;
   if (vocab <= 0) return sb::fail("sb_sample_temperature: empty vocabulary");
-  sample_temperature_kernel<<<rows, kThreads, 0, stream>>>(logits, ld, vocab, temperatures, seeds, lengths, tokens, values);
+  sb::launch_pdl(sample_temperature_kernel, dim3(rows), dim3(kThreads), 0, stream, logits, ld, vocab, temperatures, seeds, lengths, tokens, values);
   return sb::check_launch("sb_sample_temperature");
 }
