@@ -22,6 +22,7 @@
 // Counterparts in arhaamatiq/stride: AttentionPage / AttentionCombine with KvT = bfloat16
 // (src/kernel_common.h:90-309), which are scalar.
 #include "common.cuh"
+#include "noalloc.h"
 
 SB_DEFINE_LAST_ERROR()
 
@@ -508,4 +509,53 @@ SB_EXPORT int sb_attention_tc(const void* q, void* out, const void* k_base, cons
   if (D == 64) return launch<64>(p, n_tiles, n_items, stream);
   if (D == 128) return launch<128>(p, n_tiles, n_items, stream);
   return sb::fail("sb_attention_tc: head_dim %d has no tensor-core kernel (64 or 128)", D);
+}
+
+
+// ------------------------------------------------------------------ the entry point that allocates nothing
+namespace {
+
+// Scratch of sb_attention_decode_noalloc: the chunk records of the decode kernel. Every GPU that loads
+// this library holds these 16 MiB from load to exit, whether the entry point is used or not.
+static __device__ __align__(256) float g_noalloc_scratch[SB_NOALLOC_SCRATCH_FLOATS];
+
+constexpr int kMaxDevices = 64;
+float* g_noalloc_scratch_ptr[kMaxDevices] = {nullptr};
+
+// In host code `g_noalloc_scratch` is only a handle for the runtime, not an address a kernel can use; the
+// device address has to be asked for, once per device, with that device current.
+int noalloc_scratch(float** out) {
+  int dev = -1;
+  cudaError_t e = cudaGetDevice(&dev);
+  if (e != cudaSuccess) return sb::fail("sb_attention_decode_noalloc: cudaGetDevice: %s", cudaGetErrorString(e));
+  if (dev < 0 || dev >= kMaxDevices) return sb::fail("sb_attention_decode_noalloc: device %d is beyond the %d this library tracks", dev, kMaxDevices);
+  if (g_noalloc_scratch_ptr[dev] == nullptr) {
+    float* ptr = nullptr;
+    e = cudaGetSymbolAddress(reinterpret_cast<void**>(&ptr), g_noalloc_scratch);
+    if (e != cudaSuccess || ptr == nullptr)
+      return sb::fail("sb_attention_decode_noalloc: cudaGetSymbolAddress: %s", cudaGetErrorString(e));
+    g_noalloc_scratch_ptr[dev] = ptr;
+  }
+  *out = g_noalloc_scratch_ptr[dev];
+  return 0;
+}
+
+}  // namespace
+
+SB_EXPORT int sb_attention_decode_noalloc(const void* q, void* out, const void* k_base, const int32_t* block_table,
+                                          int max_pages, int page_size, int64_t page_stride, int64_t v_offset,
+                                          int64_t head_stride, const int32_t* meta, int meta_stride, const int32_t* items,
+                                          int n_items, int chunks, int Hq, int Hkv, int D, int window, float scale,
+                                          cudaStream_t stream) {
+  if (n_items <= 0) return 0;
+  if (chunks <= 0 || Hkv <= 0) return sb::fail("sb_attention_decode_noalloc: chunks and Hkv must be positive");
+  const int64_t need = sb_attention_tc_scratch(n_items, Hkv, chunks, D);
+  if (need > SB_NOALLOC_SCRATCH_FLOATS)
+    return sb::fail("sb_attention_decode_noalloc: %d entries x %d kv heads x %d chunks x head_dim %d need %lld floats of scratch; "
+                    "the built-in array holds %lld (use sb_attention_tc with your own scratch for larger steps)",
+                    n_items, Hkv, chunks, D, (long long)need, (long long)SB_NOALLOC_SCRATCH_FLOATS);
+  float* scratch = nullptr;
+  if (int rc = noalloc_scratch(&scratch)) return rc;
+  return sb_attention_tc(q, out, k_base, block_table, max_pages, page_size, page_stride, v_offset, head_stride, meta,
+                         meta_stride, items, 0, n_items, chunks, scratch, Hq, Hkv, D, window, scale, stream);
 }

@@ -73,7 +73,7 @@ def _build_dir() -> Path:
 def _digest(src: Path) -> str:
     h = hashlib.sha256()
     h.update(src.read_bytes())
-    for header in sorted(CSRC.glob("*.cuh")):
+    for header in sorted(list(CSRC.glob("*.cuh")) + list(CSRC.glob("*.h"))):
         h.update(header.read_bytes())
     h.update(" ".join(ARCH_FLAGS + NVCC_FLAGS).encode())
     return h.hexdigest()[:12]
