@@ -123,7 +123,7 @@ class Engine:
         self._graphs: dict = {}
         self._graph_generation = 0
         # Padding rows of a graph step write their key and value to the cache manager's spare slot.
-        self._pad_slot = self.cache.pad_slot if o.cuda_graphs else -1
+        self._pad_slot = self.cache.pad_slot if (o.cuda_graphs and self.model.graph_safe) else -1
 
     @classmethod
     def from_random(cls, config: dict, seed: int, options: Optional[EngineOptions] = None) -> "Engine":
@@ -154,7 +154,7 @@ class Engine:
         n = sum(len(e.tokens) for e in entries)
         if n == 0:
             return None
-        if o.cuda_graphs and n == len(entries):
+        if self._pad_slot >= 0 and n == len(entries):
             logits = self._graph_step(entries)
             if logits is not None:
                 return logits

@@ -27,6 +27,8 @@ class AttentionMixer(Mixer):
     """params: hidden_size, num_heads, num_kv_heads, head_dim, window (0 = all keys),
     position (a PartSpec of category "position", or None), scale (default head_dim ** -0.5).
     tensors: q, k, v, o."""
+    graph_safe = True
+
 
     def __init__(self, spec, env):
         super().__init__(spec, env)

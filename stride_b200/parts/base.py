@@ -83,6 +83,12 @@ class CacheNeed:
 
 
 class Part:
+    # True if `forward` launches the same kernels with the same arguments for every decode-only step of a
+    # given batch size (no host-side branching on positions, no host-to-device copies), so that the step can be
+    # recorded once as a CUDA graph and replayed. Parts written with host logic leave it False, and the
+    # engine then runs every step directly.
+    graph_safe = False
+
     def __init__(self, spec: PartSpec, env: BuildEnv):
         self.spec = spec
         self.env = env
@@ -147,6 +153,10 @@ class Block(Part):
 
     def weight_bytes(self) -> int:
         return sum(p.weight_bytes() for p in self.parts())
+
+    @property
+    def all_graph_safe(self) -> bool:
+        return self.graph_safe and all(p.graph_safe for p in self.parts())
 
     def forward(self, ctx, stream, cache) -> None:
         raise NotImplementedError

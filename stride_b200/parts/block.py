@@ -7,6 +7,8 @@ from .base import Block, register_part
 
 @register_part("block", "prenorm")
 class PreNormBlock(Block):
+    graph_safe = True
+
     def forward(self, ctx, stream, cache):
         width = stream.h.shape[1]
         x = ctx.workspace.get("block.x", ctx.n, (width,), ctx.act_dtype)

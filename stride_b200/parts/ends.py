@@ -17,6 +17,8 @@ from .spec import TensorPlan
 @register_part("embedding", "lookup")
 class Embedding(Part):
     """params: vocab_size, hidden_size. tensors: weight."""
+    graph_safe = True
+
 
     def __init__(self, spec, env):
         super().__init__(spec, env)
@@ -41,6 +43,8 @@ class Embedding(Part):
 class LinearHead(Part):
     """params: vocab_size, hidden_size, tied (True: always the embedding table; False: its own
     matrix is required; None: its own matrix if the checkpoint has one). tensors: weight, tied_to."""
+    graph_safe = True
+
 
     def __init__(self, spec, env):
         super().__init__(spec, env)

@@ -14,6 +14,8 @@ from .spec import TensorPlan
 @register_part("feed_forward", "swiglu")
 class SwiGLU(FeedForward):
     """params: hidden_size, intermediate_size. tensors: gate, up, down."""
+    graph_safe = True
+
 
     def __init__(self, spec, env):
         super().__init__(spec, env)

@@ -29,6 +29,11 @@ class DecoderModel:
             if e.cache_of is not None and not 0 <= e.cache_of < i:
                 raise ValueError(f"schedule entry {i} reads the cache of entry {e.cache_of}, which does not run before it")
 
+    @property
+    def graph_safe(self) -> bool:
+        return (self.embedding.graph_safe and self.final_norm.graph_safe and self.head.graph_safe
+                and all(b.all_graph_safe for b in self.blocks))
+
     def _parts(self):
         return [self.embedding, *self.blocks, self.final_norm, self.head]
 

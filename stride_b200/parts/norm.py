@@ -10,6 +10,8 @@ from .spec import TensorPlan
 @register_part("norm", "rmsnorm")
 class RMSNorm(Norm):
     """params: size, eps. tensors: weight."""
+    graph_safe = True
+
 
     def __init__(self, spec, env):
         super().__init__(spec, env)

@@ -43,6 +43,8 @@ def inverse_frequencies(rotary_dim: int, theta: float, scaling: dict) -> np.ndar
 @register_part("position", "rope")
 class RotaryEncoding(PositionEncoding):
     """params: head_dim, rotary_dim (default head_dim), theta, scaling (dict with rope_type and its factors)."""
+    graph_safe = True
+
 
     def __init__(self, spec, env):
         super().__init__(spec, env)

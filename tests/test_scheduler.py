@@ -1,0 +1,168 @@
+"""The scheduler's decisions on the CPU, against a fake engine whose "model" is a hash of the tokens a
+slot has been fed: any token fed twice, skipped, or at a wrong position changes what is generated."""
+from __future__ import annotations
+
+import hashlib
+import threading
+from types import SimpleNamespace
+
+import pytest
+import torch
+
+from stride_b200.cache.manager import CacheManager
+from stride_b200.engine.engine import EngineError
+from stride_b200.engine.scheduler import GenRequest, Scheduler, SchedulerOptions
+from stride_b200.parts import CacheNeed
+from stride_b200.sampling.sampler import SamplingParams
+
+VOCAB = 97
+
+
+class FakeEngine:
+    def __init__(self, pages=64, page_size=4, max_slots=8, max_rows=16, max_context=64):
+        need = CacheNeed("pages", kv_heads=1, head_dim=2, dtype=torch.float32)
+        self.cache = CacheManager([need], device="cpu", max_slots=max_slots, max_context=max_context, page_size=page_size, num_pages=pages)
+        self.options = SimpleNamespace(max_rows=max_rows)
+        self.env = SimpleNamespace(max_logit_rows=max_rows)
+        self.spec = SimpleNamespace(eos_token_ids=(), vocab_size=VOCAB)
+        self.max_context = max_context
+        self.device = "cpu"
+        self.fed = {}              # slot -> tokens fed so far
+        self.batches = []          # per step: [(slot, first_pos, n tokens, wants logits)]
+
+    def step(self, entries):
+        assert sum(len(e.tokens) for e in entries) <= self.options.max_rows
+        out = []
+        self.batches.append([(e.slot, e.first_pos, len(e.tokens), bool(e.want)) for e in entries])
+        for e in entries:
+            seq = self.fed.setdefault(e.slot, [])
+            if e.first_pos == 0:
+                seq.clear()                       # a (re)started request
+            assert e.first_pos == len(seq), "tokens must continue the slot's sequence"
+            assert self.cache.length[e.slot] >= e.first_pos + len(e.tokens), "pages must be ensured"
+            seq.extend(e.tokens)
+            for j in e.want:
+                assert j == len(e.tokens) - 1
+                out.append(list(seq))
+        return out or None
+
+
+class HashSampler:
+    def choose(self, logits, params, lengths):
+        toks = []
+        for seq, n in zip(logits, lengths):
+            assert len(seq) == n
+            toks.append(int.from_bytes(hashlib.sha256(repr(seq).encode()).digest()[:4], "little") % VOCAB)
+        return toks, [float(t) for t in toks]
+
+
+def _run(engine, prompts, max_new=12, opts=None, stops=()):
+    sched = Scheduler(engine, opts or SchedulerOptions(max_seqs=8, max_rows=16, prefill_chunk=5), sampler=HashSampler())
+    outs = [dict(tokens=[], finish=None) for _ in prompts]
+
+    def cb(i):
+        def on_token(ev, logits):
+            if ev.token >= 0:
+                assert ev.index == len(outs[i]["tokens"])
+                outs[i]["tokens"].append(ev.token)
+            if ev.finished:
+                outs[i]["finish"] = ev.finish_reason
+        return on_token
+    for i, p in enumerate(prompts):
+        sched.submit(GenRequest(prompt=p, max_new_tokens=max_new, stop_tokens=stops, on_token=cb(i)))
+    sched.run()
+    assert sched.idle()
+    engine.cache.check()
+    assert engine.cache.free_pages() == engine.cache.total_pages()
+    return outs, sched
+
+
+PROMPTS = [[1, 2, 3, 4, 5, 6, 7], [9], [11, 12, 13], list(range(20, 33)), [40, 41], [50, 51, 52, 53, 54, 55]]
+
+
+def _solo():
+    return [_run(FakeEngine(), [p])[0][0] for p in PROMPTS]
+
+
+def test_batches_obey_budget_order_and_chunking():
+    eng = FakeEngine()
+    outs, sched = _run(eng, PROMPTS)
+    assert [o["tokens"] for o in outs] == [o["tokens"] for o in _solo()]
+    assert all(o["finish"] == "length" and len(o["tokens"]) == 12 for o in outs)
+    for batch in eng.batches:
+        assert sum(n for _, _, n, _ in batch) <= 16
+        kinds = [n == 1 and want for _, _, n, want in batch]
+        # decode rows come first, portions after them, none longer than prefill_chunk
+        assert kinds == sorted(kinds, reverse=True) or all(n <= 5 for _, _, n, _ in batch)
+        assert all(n <= 5 for _, _, n, _ in batch)
+    # the 13-token prompt was cut into 5 + 5 + 3 and only the last portion asked for logits
+    slot13 = [b for batch in eng.batches for b in batch if b[1] in (0, 5, 10) and b[2] in (5, 3)]
+    assert sched.stats.generated == 72 and sched.stats.preemptions == 0 and sched.stats.peak_seqs == 6
+    assert sched.stats.rows == sum(n for batch in eng.batches for _, _, n, _ in batch)
+
+
+def test_running_out_of_pages_preempts_the_youngest_and_replays():
+    solo = _solo()
+    eng = FakeEngine(pages=9, page_size=4)              # 36 tokens of cache for requests that grow to 7+12, 13+12, ...
+    outs, sched = _run(eng, PROMPTS, opts=SchedulerOptions(max_seqs=6, max_rows=16, prefill_chunk=5))
+    assert sched.stats.preemptions > 0 and sched.stats.replayed_rows > 0
+    assert [o["tokens"] for o in outs] == [o["tokens"] for o in solo]
+    assert sched.stats.peak_blocks <= 9
+    # a restarted request begins again at position 0 with a portion, never in the middle
+    restarts = [b for batch in eng.batches for b in batch if b[1] == 0]
+    # (a request preempted before it ever ran restarts nothing)
+    assert len(PROMPTS) < len(restarts) <= len(PROMPTS) + sched.stats.preemptions
+
+
+def test_a_single_request_that_cannot_fit_raises():
+    eng = FakeEngine(pages=3, page_size=4)
+    sched = Scheduler(eng, SchedulerOptions(max_seqs=2, max_rows=16, prefill_chunk=16), sampler=HashSampler())
+    sched.submit(GenRequest(prompt=list(range(10)), max_new_tokens=20))
+    with pytest.raises(EngineError, match="too small for one sequence"):
+        sched.run()
+
+
+def test_admission_keeps_room_for_growth():
+    eng = FakeEngine(pages=8, page_size=4, max_rows=32)
+    sched = Scheduler(eng, SchedulerOptions(max_seqs=8, max_rows=32, prefill_chunk=16), sampler=HashSampler())
+    for p in ([1] * 12, [2] * 8):
+        sched.submit(GenRequest(prompt=p, max_new_tokens=3))
+    sched.step()                                  # both admitted and prefilled: 3 + 2 pages held, 3 free
+    assert len(sched._running) == 2 and eng.cache.free_pages() == [3]
+    sched.submit(GenRequest(prompt=[3] * 4, max_new_tokens=3))
+    sched.step()
+    # the third needs 1 page + one page of growth for each of the 2 running + 1 = 4 > 3 free: it waits
+    assert len(sched._running) == 2 and len(sched._waiting) == 1
+    sched.run()
+    assert sched.stats.generated == 9 and sched.stats.preemptions == 0
+
+
+def test_stop_tokens_limits_and_cancellation():
+    solo = _solo()
+    stop = solo[0]["tokens"][4]
+    outs, _ = _run(FakeEngine(), [PROMPTS[0]], stops=(stop,))
+    k = solo[0]["tokens"].index(stop)
+    assert outs[0]["tokens"] == solo[0]["tokens"][:k + 1] and outs[0]["finish"] == "stop"
+    eng = FakeEngine(max_context=16)
+    outs, _ = _run(eng, [[], list(range(16)), list(range(10))], max_new=50)
+    assert (outs[0]["finish"], outs[1]["finish"]) == ("empty_prompt", "context_length")
+    assert outs[2]["finish"] == "length" and len(outs[2]["tokens"]) == 6          # clamped to the room left
+    eng = FakeEngine()
+    sched = Scheduler(eng, SchedulerOptions(max_seqs=4, max_rows=16, prefill_chunk=8), sampler=HashSampler())
+    flag = threading.Event()
+    got = []
+    sched.submit(GenRequest(prompt=[1, 2, 3], max_new_tokens=100, cancelled=flag, on_token=lambda ev, l: got.append(ev.token)))
+    sched.submit(GenRequest(prompt=[4, 5], max_new_tokens=5))
+    for _ in range(4):
+        sched.step()
+    flag.set()
+    sched.run()
+    assert 0 < len(got) < 100 and sched.idle()
+    eng.cache.check()
+    assert eng.cache.free_pages() == eng.cache.total_pages()
+
+
+def test_batch_order_shuffle_changes_nothing():
+    solo = _solo()
+    outs, _ = _run(FakeEngine(), PROMPTS, opts=SchedulerOptions(max_seqs=4, max_rows=9, prefill_chunk=3, row_shuffle_seed=5))
+    assert [o["tokens"] for o in outs] == [o["tokens"] for o in solo]

@@ -1,0 +1,167 @@
+"""A toy architecture defined here, without touching the framework's files: a mixer with state of its own
+(an exponential moving average of its inputs per request), registered as a part, mixed with attention
+layers in one model; a schedule that runs one layer twice, the second time reading the first call's
+cache; and a windowed attention layer whose pages are given back as the window passes. The model is built
+by the registry, stepped through the engine in portions and single tokens beside other requests, and
+compared with a plain whole-sequence computation written out below."""
+from __future__ import annotations
+
+import pytest
+import torch
+
+import plain_llama as plain
+from conftest import random_tokens
+from stride_b200 import Engine, EngineOptions, StepEntry
+from stride_b200.config import Architecture, register_architecture
+from stride_b200.parts import (CacheNeed, LayerSpec, Mixer, ModelSpec, PartSpec, ScheduleEntry, TensorPlan, register_part)
+
+pytestmark = pytest.mark.gpu
+
+H, V, D, HQ, HKV, I, WINDOW, DECAY = 48, 101, 16, 3, 1, 64, 11, 0.75
+
+
+@register_part("mixer", "toy_ema")
+class EmaMixer(Mixer):
+    """state_t = decay * state_{t-1} + (1 - decay) * x_t per request; output = W state_t. Written with torch
+    operations and host loops (it is a test double, not a kernel), so it is not graph-safe."""
+
+    def __init__(self, spec, env):
+        super().__init__(spec, env)
+        self.size, self.decay = spec.params["hidden_size"], spec.params["decay"]
+
+    def tensor_plan(self):
+        return {self.spec.tensors["w"]: TensorPlan((self.size, self.size))}
+
+    def bind(self, tensors):
+        self.w = tensors[self.spec.tensors["w"]].float()
+
+    def cache_need(self):
+        return CacheNeed("state", state_shape=(self.size,), state_dtype=torch.float32)
+
+    def forward(self, ctx, x, stream, cache):
+        out = torch.zeros(ctx.n, self.size, device=x.device)
+        for slot, row, length in zip(ctx.entry_slots, ctx.entry_first_row, ctx.entry_length):
+            state = cache.state[slot].clone()
+            for t in range(length):
+                state = self.decay * state + (1.0 - self.decay) * x[row + t].float()
+                out[row + t] = self.w @ state
+            cache.state[slot] = state
+        stream.add_(out)
+
+
+def _spec(cfg: dict) -> ModelSpec:
+    rope = PartSpec("rope", {"head_dim": D, "theta": 10000.0, "scaling": {}})
+    norm = lambda name: PartSpec("rmsnorm", {"size": H, "eps": 1e-5}, {"weight": name})
+    ff = lambda i: PartSpec("swiglu", {"hidden_size": H, "intermediate_size": I},
+                            {"gate": f"l{i}.gate", "up": f"l{i}.up", "down": f"l{i}.down"})
+    layers = []
+    for i, kind in enumerate(cfg["mixers"]):
+        if kind == "ema":
+            mixer = PartSpec("toy_ema", {"hidden_size": H, "decay": DECAY}, {"w": f"l{i}.ema"})
+        else:
+            mixer = PartSpec("attention", {"hidden_size": H, "num_heads": HQ, "num_kv_heads": HKV, "head_dim": D,
+                                           "window": WINDOW if kind == "window" else 0, "position": rope},
+                             {"q": f"l{i}.q", "k": f"l{i}.k", "v": f"l{i}.v", "o": f"l{i}.o"})
+        layers.append(LayerSpec(mixer, ff(i), norm(f"l{i}.n1"), norm(f"l{i}.n2")))
+    schedule = tuple(ScheduleEntry(l, c) for l, c in cfg["schedule"])
+    return ModelSpec(vocab_size=V, hidden_size=H, embedding=PartSpec("lookup", {"vocab_size": V, "hidden_size": H}, {"weight": "emb"}),
+                     layers=tuple(layers), schedule=schedule, final_norm=norm("final"),
+                     head=PartSpec("linear", {"vocab_size": V, "hidden_size": H, "tied": True}, {"weight": "head", "tied_to": "emb"}),
+                     max_positions=256)
+
+
+register_architecture(Architecture("ToyEmaForCausalLM", lambda d: d, _spec))
+
+CONFIG = {"architectures": ["ToyEmaForCausalLM"], "mixers": ["ema", "full", "window", "ema"],
+          # layer 1 (attention over all keys) runs twice; its second call reads the first call's cache
+          "schedule": [[0, None], [1, None], [2, None], [1, 1], [3, None]]}
+
+
+def _weights():
+    g = torch.Generator().manual_seed(0)
+    r = lambda *s: (torch.randn(*s, generator=g) * 0.2).to(torch.bfloat16)
+    gain = lambda: (1 + 0.2 * torch.randn(H, generator=g)).to(torch.bfloat16)
+    w = {"emb": r(V, H), "final": gain()}
+    for i, kind in enumerate(CONFIG["mixers"]):
+        w.update({f"l{i}.n1": gain(), f"l{i}.n2": gain(), f"l{i}.gate": r(I, H), f"l{i}.up": r(I, H), f"l{i}.down": r(H, I)})
+        if kind == "ema":
+            w[f"l{i}.ema"] = r(H, H)
+        else:
+            w.update({f"l{i}.q": r(HQ * D, H), f"l{i}.k": r(HKV * D, H), f"l{i}.v": r(HKV * D, H), f"l{i}.o": r(H, HQ * D)})
+    return w
+
+
+def _plain_forward(w, tokens):
+    T = len(tokens)
+    pos = torch.arange(T)
+    cfg = plain.PlainConfig(hidden_size=H, intermediate_size=I, num_hidden_layers=1, num_attention_heads=HQ, vocab_size=V,
+                            num_key_value_heads=HKV, head_dim=D)
+    cos, sin = plain.rope_table(cfg, pos)
+    h = plain.embedding(torch.tensor(tokens), w["emb"])
+    kv_of = {}
+    for e, (l, cache_of) in enumerate(CONFIG["schedule"]):
+        kind = CONFIG["mixers"][l]
+        x = plain.rms_norm(h, w[f"l{l}.n1"], 1e-5)
+        if kind == "ema":
+            state, ys = torch.zeros(H), []
+            for t in range(T):
+                state = DECAY * state + (1 - DECAY) * x[t]
+                ys.append(w[f"l{l}.ema"].float() @ state)
+            h = h + torch.stack(ys)
+        else:
+            q = plain.rope_apply((x @ w[f"l{l}.q"].float().T).reshape(T, HQ, D), cos, sin)
+            if cache_of is None:
+                k = plain.rope_apply((x @ w[f"l{l}.k"].float().T).reshape(T, HKV, D), cos, sin)
+                v = (x @ w[f"l{l}.v"].float().T).reshape(T, HKV, D)
+                kv_of[e] = (k, v)
+            else:
+                k, v = kv_of[cache_of]
+            h = h + plain.attention(q, k, v, pos, WINDOW if kind == "window" else 0) @ w[f"l{l}.o"].float().T
+        x = plain.rms_norm(h, w[f"l{l}.n2"], 1e-5)
+        h = h + plain.swiglu(x, w[f"l{l}.gate"], w[f"l{l}.up"]) @ w[f"l{l}.down"].float().T
+    return plain.rms_norm(h, w["final"], 1e-5) @ w["emb"].float().T
+
+
+def test_toy_architecture_is_registered_built_and_stepped():
+    w = _weights()
+    eng = Engine(None, EngineOptions(dtype="float32", max_rows=64, max_full_rows=64, max_slots=4, kv_pages=40, page_size=4,
+                                     max_context=256), config=CONFIG, tensors=w)
+    assert eng.architecture.name == "ToyEmaForCausalLM" and not eng.model.graph_safe
+    cm = eng.cache
+    # attention over all keys (entries 1 and 3 share a cache) and the windowed layer get groups of their own; the two
+    # state mixers get one record per request each
+    assert len(cm.groups) == 2 and sorted(g.window for g in cm.groups) == [0, WINDOW]
+    assert set(cm.states) == {0, 4} and cm.entry_shared == {3: 1}
+    reqs = [random_tokens(V, n, 7 + n) for n in (90, 33, 61)]
+    want = [_plain_forward(w, r) for r in reqs]
+    slots = [cm.acquire_slot() for _ in reqs]
+    fed = [0, 0, 0]
+    sizes = [[13, 1, 1, 7, 2], [5, 1, 1, 1], [30, 1, 3]]
+    step = 0
+    while any(f < len(r) for f, r in zip(fed, reqs)):
+        entries, spans = [], []
+        for i, r in enumerate(reqs):
+            if fed[i] >= len(r) or (step + i) % 4 == 3:
+                continue
+            n = min(sizes[i][step % len(sizes[i])], len(r) - fed[i])
+            assert cm.ensure(slots[i], fed[i] + n)
+            entries.append(StepEntry(slots[i], fed[i], r[fed[i]:fed[i] + n], list(range(n))))
+            spans.append((i, fed[i], fed[i] + n))
+            fed[i] += n
+        if entries:
+            logits = eng.step(entries).cpu()
+            at = 0
+            for i, a, b in spans:
+                ref = want[i][a:b]
+                assert (logits[at:at + b - a] - ref).abs().max() <= 2e-4 * max(1.0, float(ref.pow(2).mean().sqrt())), (step, i, a, b)
+                at += b - a
+            for i, _, _ in spans:
+                cm.trim(slots[i])
+        step += 1
+    # the windowed group gave pages back as the window passed: far fewer than the 90 tokens' 23 pages are held
+    win = next(g for g in cm.groups if g.window)
+    assert len(win.held[slots[0]]) <= WINDOW // 4 + 2 < 23
+    for s in slots:
+        cm.release_slot(s)
+    cm.check()
+    assert cm.free_pages() == cm.total_pages()
