@@ -124,7 +124,7 @@ def _plain_forward(w, tokens):
 
 def test_toy_architecture_is_registered_built_and_stepped():
     w = _weights()
-    eng = Engine(None, EngineOptions(dtype="float32", max_rows=64, max_full_rows=64, max_slots=4, kv_pages=40, page_size=4,
+    eng = Engine(None, EngineOptions(dtype="float32", max_rows=64, max_full_rows=64, max_slots=4, kv_pages=60, page_size=4,
                                      max_context=256), config=CONFIG, tensors=w)
     assert eng.architecture.name == "ToyEmaForCausalLM" and not eng.model.graph_safe
     cm = eng.cache
