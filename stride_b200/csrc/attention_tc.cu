@@ -51,6 +51,7 @@ struct AttnTcParams {
   float* part_o;         // [items][Hkv][chunks][16][D]
   float* part_ml;        // [items][Hkv][chunks][16][2]
   int chunks;
+  int* counters;         // [items][Hkv], zero between launches; null: the chunks are folded by attn_combine_kernel
 };
 
 __device__ __forceinline__ uint32_t smem_u32(const void* p) { return static_cast<uint32_t>(__cvta_generic_to_shared(p)); }
@@ -284,8 +285,9 @@ __global__ void __launch_bounds__(128) attn_decode_kernel(const AttnTcParams p) 
   extern __shared__ __align__(16) uint8_t smem_raw[];
   bf16* sQ = reinterpret_cast<bf16*>(smem_raw);           // [16][LD]
   bf16* sKV = sQ + 16 * LD;                               // [4 warps][K, V][64][LD]
-  float* sO = reinterpret_cast<float*>(sKV + 4 * 2 * 64 * LD);  // [4][16][D]
+  float* sO = reinterpret_cast<float*>(sKV);               // [4][16][D], over the key/value tiles once they are used up
   float* sML = sO + 4 * 16 * D;                           // [4][16][2]
+  __shared__ int is_last_s;
 
   sb::grid_launch_dependents();
   sb::grid_dependency_wait();
@@ -375,6 +377,7 @@ __global__ void __launch_bounds__(128) attn_decode_kernel(const AttnTcParams p) 
     pv_tile<D>(o, s, sV, lane);
   }
   // every warp leaves (m, l, O) of its 64 keys; they are merged in warp order
+  __syncthreads();   // all warps are done with their key/value tiles, whose space the results take
 #pragma unroll
   for (int h = 0; h < 2; ++h) {
     const int r = gid + 8 * h;
@@ -408,6 +411,33 @@ __global__ void __launch_bounds__(128) attn_decode_kernel(const AttnTcParams p) 
       p.part_ml[(rec * 16 + r) * 2] = mm;
       p.part_ml[(rec * 16 + r) * 2 + 1] = ll;
     }
+  }
+  if (p.counters == nullptr) return;
+  // The CTA that finishes an entry's last chunk folds all of them, in ascending order, and writes the rows.
+  const int c0 = key_lo / kChunk, c1 = pos_hi / kChunk;
+  __threadfence();
+  __syncthreads();
+  if (tid == 0) {
+    int* counter = p.counters + item * p.Hkv + g;
+    const int ticket = atomicAdd(counter, 1);
+    is_last_s = ticket == c1 - c0;
+    if (is_last_s) *counter = 0;
+  }
+  __syncthreads();
+  if (!is_last_s) return;
+  __threadfence();
+  const int64_t rec0 = (static_cast<int64_t>(item) * p.Hkv + g) * p.chunks;
+  for (int idx = tid; idx < rows * D; idx += 128) {
+    const int r = idx / D, d = idx % D;
+    float mm = -INFINITY;
+    for (int c = c0; c <= c1; ++c) mm = fmaxf(mm, __ldcg(&p.part_ml[((rec0 + c) * 16 + r) * 2]));
+    float acc = 0.0f, ll = 0.0f;
+    for (int c = c0; c <= c1; ++c) {
+      const float f = exp2f(__ldcg(&p.part_ml[((rec0 + c) * 16 + r) * 2]) - mm);
+      acc += __ldcg(&p.part_o[(rec0 + c) * 16 * D + r * D + d]) * f;
+      ll += __ldcg(&p.part_ml[((rec0 + c) * 16 + r) * 2 + 1]) * f;
+    }
+    p.out[(static_cast<int64_t>(first_row + r / G) * p.Hq + g * G + r % G) * D + d] = __float2bfloat16_rn(acc / ll);
   }
 }
 
@@ -450,7 +480,7 @@ int launch(const AttnTcParams& p, int n_tiles, int n_items, cudaStream_t stream)
     sb::launch_pdl(attn_chunk_kernel<D>, dim3(n_tiles, p.Hkv), dim3(128), smem, stream, p);
   }
   if (n_items > 0) {
-    const size_t smem = static_cast<size_t>(16 * LD + 8 * 64 * LD) * sizeof(bf16) + static_cast<size_t>(4 * 16 * D + 4 * 16 * 2) * sizeof(float);
+    const size_t smem = static_cast<size_t>(16 * LD + 8 * 64 * LD) * sizeof(bf16);   // results (4 x 16 x (D + 2) floats) reuse the tiles
     static bool set = false;
     if (!set) {
       if (cudaFuncSetAttribute(attn_decode_kernel<D>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess)
@@ -460,7 +490,7 @@ int launch(const AttnTcParams& p, int n_tiles, int n_items, cudaStream_t stream)
     AttnTcParams pd = p;
     pd.work = p.work + 2 * n_tiles;
     sb::launch_pdl(attn_decode_kernel<D>, dim3(n_items, p.Hkv, p.chunks), dim3(128), smem, stream, pd);
-    sb::launch_pdl(attn_combine_kernel<D>, dim3(n_items, p.Hkv), dim3(D), 0, stream, pd);
+    if (pd.counters == nullptr) sb::launch_pdl(attn_combine_kernel<D>, dim3(n_items, p.Hkv), dim3(D), 0, stream, pd);
   }
   return sb::check_launch("sb_attention_tc");
 }
@@ -478,7 +508,7 @@ SB_EXPORT int64_t sb_attention_tc_scratch(int items, int Hkv, int chunks, int D)
 SB_EXPORT int sb_attention_tc(const void* q, void* out, const void* k_base, const int32_t* block_table, int max_pages,
                               int page_size, int64_t page_stride, int64_t v_offset, int64_t head_stride,
                               const int32_t* meta, int meta_stride, const int32_t* work, int n_tiles, int n_items,
-                              int chunks, float* scratch, int Hq, int Hkv, int D, int window, float scale,
+                              int chunks, float* scratch, int* counters, int Hq, int Hkv, int D, int window, float scale,
                               cudaStream_t stream) {
   if (n_tiles <= 0 && n_items <= 0) return 0;
   if (Hkv <= 0 || Hq % Hkv != 0 || Hq / Hkv > 16)
@@ -506,6 +536,7 @@ SB_EXPORT int sb_attention_tc(const void* q, void* out, const void* k_base, cons
   p.chunks = chunks;
   p.part_o = scratch;
   p.part_ml = scratch + static_cast<int64_t>(n_items) * Hkv * chunks * 16 * D;
+  p.counters = counters;
   if (D == 64) return launch<64>(p, n_tiles, n_items, stream);
   if (D == 128) return launch<128>(p, n_tiles, n_items, stream);
   return sb::fail("sb_attention_tc: head_dim %d has no tensor-core kernel (64 or 128)", D);
@@ -557,5 +588,5 @@ SB_EXPORT int sb_attention_decode_noalloc(const void* q, void* out, const void* 
   float* scratch = nullptr;
   if (int rc = noalloc_scratch(&scratch)) return rc;
   return sb_attention_tc(q, out, k_base, block_table, max_pages, page_size, page_stride, v_offset, head_stride, meta,
-                         meta_stride, items, 0, n_items, chunks, scratch, Hq, Hkv, D, window, scale, stream);
+                         meta_stride, items, 0, n_items, chunks, scratch, nullptr, Hq, Hkv, D, window, scale, stream);
 }

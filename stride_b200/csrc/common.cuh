@@ -12,6 +12,8 @@
 
 #include <cstdarg>
 #include <cstdio>
+#include <mutex>
+#include <set>
 
 #define SB_EXPORT extern "C" __attribute__((visibility("default")))
 
@@ -44,8 +46,19 @@ inline int check_launch(const char* what) {
 __device__ __forceinline__ void grid_dependency_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
 __device__ __forceinline__ void grid_launch_dependents() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
 
+// Every kernel asks for the largest shared-memory carve-out, so that consecutive kernels of a step do not
+// make the SMs switch their L1 / shared split (which would keep a successor from becoming resident early).
+inline void prefer_max_shared(const void* kernel) {
+  static std::mutex mu;
+  static std::set<const void*> done;
+  std::lock_guard<std::mutex> lock(mu);
+  if (done.insert(kernel).second)
+    cudaFuncSetAttribute(kernel, cudaFuncAttributePreferredSharedMemoryCarveout, cudaSharedmemCarveoutMaxShared);
+}
+
 template <class... KArgs, class... Args>
 inline void launch_pdl(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t stream, Args&&... args) {
+  prefer_max_shared(reinterpret_cast<const void*>(kernel));
   cudaLaunchConfig_t cfg = {};
   cfg.gridDim = grid;
   cfg.blockDim = block;

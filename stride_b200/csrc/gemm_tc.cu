@@ -148,7 +148,7 @@ struct GemmParams {
 };
 
 template <int EPI>
-__global__ void __launch_bounds__(kThreads, 1)
+__global__ void __launch_bounds__(kThreads)
 gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUtensorMap map_x, const GemmParams p) {
   extern __shared__ __align__(1024) uint8_t smem_raw[];
   __shared__ __align__(8) uint64_t full_bar[kMaxStages];
@@ -400,6 +400,16 @@ SB_EXPORT int sb_gemm_tc(const void* x, int64_t ldx, const void* w, int64_t ldw,
   p.block_n = n <= 16 ? 16 : n <= 32 ? 32 : n <= 64 ? 64 : n <= 128 ? 128 : 256;
   const int stage_bytes = kStageA + p.block_n * 128;
   p.stages = min(kMaxStages, kSmemBudget / stage_bytes);
+  {
+    // More CTAs than SMs: take fewer stages so that two or three CTAs share an SM and one's prologue and
+    // epilogue overlap with the others' streaming (tensor memory allows 512 / BN of them).
+    const int tiles_m = epilogue == kSwiglu ? (half_rows + 63) / 64 : (M + kTileM - 1) / kTileM;
+    const long long ctas = static_cast<long long>(tiles_m) * ((n + p.block_n - 1) / p.block_n) * splits;
+    if (ctas > 2 * 148) {
+      const int per_sm = p.block_n <= 64 ? 3 : 2;
+      p.stages = max(2, min(p.stages, (kSmemBudget + 16 * 1024) / per_sm / stage_bytes));
+    }
+  }
   p.kblocks_per_split = (kblocks + splits - 1) / splits;
   if ((kblocks + p.kblocks_per_split - 1) / p.kblocks_per_split != splits)
     return sb::fail("sb_gemm_tc: %d splits leave an empty K range (use sb_gemm_tc_splits)", splits);

@@ -219,15 +219,17 @@ def attention_tc_scratch(items: int, num_kv_heads: int, chunks: int, head_dim: i
 
 
 def attention_tc(q, out, cache_layer, block_table, entry_meta, work, n_tiles: int, n_items: int, chunks: int,
-                 scratch, num_heads: int, num_kv_heads: int, head_dim: int, window: int, scale: float) -> None:
-    """Tensor-core paged attention (bfloat16, head_dim 64 or 128); see csrc/attention_tc.cu for `work`."""
-    _cuda(q, out, cache_layer, block_table, entry_meta, work, scratch)
+                 scratch, num_heads: int, num_kv_heads: int, head_dim: int, window: int, scale: float,
+                 counters=None) -> None:
+    """Tensor-core paged attention (bfloat16, head_dim 64 or 128); see csrc/attention_tc.cu for `work`.
+    `counters`: int32 zeros, one per (decode entry, kv head); with them the decode kernel folds its own chunks."""
+    _cuda(q, out, cache_layer, block_table, entry_meta, work, scratch, counters)
     if not (q.dtype == out.dtype == cache_layer.dtype == torch.bfloat16):
         raise TypeError("attention_tc takes bfloat16 q, out and cache")
     lib, fn = _fn("attention_tc", "sb_attention_tc",
                   [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int64, c_int64, c_int64, c_void_p, c_int,
-                   c_void_p, c_int, c_int, c_int, c_void_p, c_int, c_int, c_int, c_int, c_float, c_void_p])
+                   c_void_p, c_int, c_int, c_int, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_float, c_void_p])
     _check(lib, fn(_ptr(q), _ptr(out), _ptr(cache_layer), _ptr(block_table), block_table.shape[1], cache_layer.shape[3],
                    cache_layer.stride(0), cache_layer.stride(1), cache_layer.stride(2), _ptr(entry_meta),
-                   entry_meta.stride(0), _ptr(work), n_tiles, n_items, chunks, _ptr(scratch), num_heads, num_kv_heads,
+                   entry_meta.stride(0), _ptr(work), n_tiles, n_items, chunks, _ptr(scratch), _ptr(counters), num_heads, num_kv_heads,
                    head_dim, window, scale, _stream()))

@@ -114,8 +114,9 @@ class AttentionMixer(Mixer):
         if ctx.act_dtype == torch.bfloat16 and D in (64, 128) and G <= 16:
             plan = self._tc_plan(ctx, G)
             scratch = ws.grow("attn.scratch", ops.attention_tc_scratch(plan[2], self.num_kv_heads, plan[3], D), torch.float32)
+            counters = ws.raw("attn.counters", (ws.max_tokens * self.num_kv_heads,), torch.int32)
             ops.attention_tc(q, mixed, cache.pages, cache.block_table, ctx.entry_meta, plan[0], plan[1], plan[2], plan[3],
-                             scratch, self.num_heads, self.num_kv_heads, D, self.window, self.scale)
+                             scratch, self.num_heads, self.num_kv_heads, D, self.window, self.scale, counters=counters)
         else:
             ops.attention_generic(q, mixed, cache.pages, cache.block_table, ctx.positions, ctx.slots,
                                   self.num_heads, self.num_kv_heads, D, self.window, self.scale)

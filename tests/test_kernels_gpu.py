@@ -176,6 +176,13 @@ def test_attention_tc_against_plain(D, Hq, Hkv, page, window):
     assert torch.isfinite(got).all()
     # bfloat16 probabilities and output: 2^-8 relative on values of order 1
     assert (got - ref).abs().max() <= 2e-2 * max(1.0, float(ref.abs().max()))
+    # the decode kernel folding its own chunks (counters) gives the same bits as the separate combine kernel
+    counters = torch.zeros(len(items) * Hkv, dtype=torch.int32, device=DEV)
+    out3 = torch.full_like(case["q"], float("nan"))
+    for _ in range(2):       # twice: the counters must be back at zero after a launch
+        ops.attention_tc(case["q"], out3, case["cache"], case["table"], case["meta"], work, len(tiles) // 2, len(items), chunks,
+                         scratch, Hq, Hkv, D, window, scale, counters=counters)
+        assert torch.equal(out3, out) and int(counters.abs().sum()) == 0
     # the generic kernel on the same case
     out2 = torch.full_like(case["q"], float("nan"))
     ops.attention_generic(case["q"], out2, case["cache"], case["table"], case["positions"], case["slots"], Hq, Hkv, D, window, scale)
