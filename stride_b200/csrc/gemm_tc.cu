@@ -26,6 +26,7 @@
 // (src/kernels_tc.cu:347-655).
 #include <cuda.h>
 
+#include <cstdlib>
 #include <map>
 #include <mutex>
 #include <tuple>
@@ -143,38 +144,41 @@ struct GemmParams {
   int block_n;           // BN
   int stages;
   int kblocks_per_split;
+  int tiles_m, tiles_n, splits;
   int half_rows;         // kSwiglu: rows of the gate half (intermediate size); W is [2 * half_rows, K]
   int* status;
 };
 
-template <int EPI>
+template <int EPI, bool MULTI>   // MULTI: a CTA may walk several tiles (two accumulators); else exactly one
 __global__ void __launch_bounds__(kThreads)
 gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUtensorMap map_x, const GemmParams p) {
   extern __shared__ __align__(1024) uint8_t smem_raw[];
   __shared__ __align__(8) uint64_t full_bar[kMaxStages];
   __shared__ __align__(8) uint64_t empty_bar[kMaxStages];
-  __shared__ __align__(8) uint64_t accum_bar;
+  __shared__ __align__(8) uint64_t accum_full[2];
+  __shared__ __align__(8) uint64_t accum_empty[2];
   __shared__ uint32_t tmem_base_s;
+  __shared__ float xch[EPI == kSwiglu ? 16 * 64 : 1];   // gate/up exchange of the SwiGLU epilogue
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int BN = p.block_n;
-  const int stage_b = BN * 128;
-  const int stage_bytes = kStageA + stage_b;
+  const int stage_bytes = kStageA + BN * 128;
   // Dynamic shared memory is only guaranteed 16-byte alignment: round up to the swizzle's 1024.
   const uint32_t smem0 = (smem_u32(smem_raw) + 1023u) & ~1023u;
-  const int tile_m = blockIdx.x, tile_n = blockIdx.y, split = blockIdx.z;
   const int kblocks = (p.K + kTileK - 1) / kTileK;
-  const int kb0 = split * p.kblocks_per_split;
-  const int kb1 = min(kblocks, kb0 + p.kblocks_per_split);
-  const int iters = kb1 - kb0;
-  const uint32_t tmem_cols = BN < 32 ? 32 : BN;
+  // Tiles are numbered with the weight tile fastest, so CTAs that run together share token tiles in L2.
+  const int total_tiles = p.tiles_m * p.tiles_n * p.splits;
+  const uint32_t tmem_cols = (MULTI ? 2 : 1) * BN < 32 ? 32 : (MULTI ? 2 : 1) * BN;   // MULTI: one accumulator fills while the other drains
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < p.stages; ++s) {
       mbar_init(smem_u32(&full_bar[s]), 1);
       mbar_init(smem_u32(&empty_bar[s]), 1);
     }
-    mbar_init(smem_u32(&accum_bar), 1);
+    for (int a = 0; a < 2; ++a) {
+      mbar_init(smem_u32(&accum_full[a]), 1);
+      mbar_init(smem_u32(&accum_empty[a]), 4);   // one arrival per epilogue warp
+    }
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
   }
   if (warp == 1) tmem_alloc(smem_u32(&tmem_base_s), tmem_cols);
@@ -189,102 +193,144 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
       // ---------------- producer: TMA loads. The weights do not depend on the kernels before this one,
       // so the first ring of weight tiles is requested before waiting for them to finish; the tokens'
       // tiles follow once their producer is done.
-      const int row_w = EPI == kSwiglu ? tile_m * 64 : tile_m * kTileM;
-      auto load_w = [&](int i) {
-        const int s = i % p.stages;
-        const uint32_t bar = smem_u32(&full_bar[s]);
-        const uint32_t a = smem0 + s * stage_bytes;
-        mbar_expect_tx(bar, stage_bytes);
-        const int k = (kb0 + i) * kTileK;
-        if (EPI == kSwiglu) {
-          tma_load_2d(a, &map_w, bar, k, row_w);
-          tma_load_2d(a + kStageA / 2, &map_w, bar, k, p.half_rows + row_w);
-        } else {
-          tma_load_2d(a, &map_w, bar, k, row_w);
+      int it = 0;          // k-blocks issued so far, over all tiles of this CTA
+      bool waited = false;
+      for (int tile = blockIdx.x; tile < total_tiles; tile += MULTI ? gridDim.x : total_tiles) {
+        const int tile_m = tile % p.tiles_m, rest = tile / p.tiles_m;
+        const int tile_n = rest % p.tiles_n, split = rest / p.tiles_n;
+        const int kb0 = split * p.kblocks_per_split;
+        const int iters = min(kblocks, kb0 + p.kblocks_per_split) - kb0;
+        const int row_w = EPI == kSwiglu ? tile_m * 64 : tile_m * kTileM;
+        auto load_w = [&](int i, int slot) {
+          const uint32_t bar = smem_u32(&full_bar[slot]);
+          const uint32_t a = smem0 + slot * stage_bytes;
+          mbar_expect_tx(bar, stage_bytes);
+          const int k = (kb0 + i) * kTileK;
+          if (EPI == kSwiglu) {
+            tma_load_2d(a, &map_w, bar, k, row_w);
+            tma_load_2d(a + kStageA / 2, &map_w, bar, k, p.half_rows + row_w);
+          } else {
+            tma_load_2d(a, &map_w, bar, k, row_w);
+          }
+        };
+        auto load_x = [&](int i, int slot) {
+          tma_load_2d(smem0 + slot * stage_bytes + kStageA, &map_x, smem_u32(&full_bar[slot]), (kb0 + i) * kTileK, tile_n * BN);
+        };
+        int i = 0;
+        if (!waited) {
+          const int ahead = min(iters, p.stages);
+          for (int j = 0; j < ahead; ++j) load_w(j, j);
+          sb::grid_dependency_wait();
+          waited = true;
+          for (int j = 0; j < ahead; ++j) load_x(j, j);
+          i = ahead;
+          it = ahead;
         }
-      };
-      auto load_x = [&](int i) {
-        const int s = i % p.stages;
-        tma_load_2d(smem0 + s * stage_bytes + kStageA, &map_x, smem_u32(&full_bar[s]), (kb0 + i) * kTileK, tile_n * BN);
-      };
-      const int ahead = min(iters, p.stages);
-      for (int i = 0; i < ahead; ++i) load_w(i);
-      sb::grid_dependency_wait();
-      for (int i = 0; i < ahead; ++i) load_x(i);
-      for (int i = ahead; i < iters; ++i) {
-        mbar_wait(smem_u32(&empty_bar[i % p.stages]), ((i / p.stages) - 1) & 1, p.status, 1);
-        load_w(i);
-        load_x(i);
+        for (; i < iters; ++i, ++it) {
+          const int slot = it % p.stages;
+          if (it >= p.stages) mbar_wait(smem_u32(&empty_bar[slot]), ((it / p.stages) - 1) & 1, p.status, 1);
+          load_w(i, slot);
+          load_x(i, slot);
+        }
       }
     }
   } else if (warp == 1) {
     if (lane == 0) {
       // ---------------- MMA issuer
       const uint32_t idesc = instr_desc(BN);
-      for (int i = 0; i < iters; ++i) {
-        const int s = i % p.stages;
-        mbar_wait(smem_u32(&full_bar[s]), (i / p.stages) & 1, p.status, 2);
+      int it = 0, ti = 0;
+      for (int tile = blockIdx.x; tile < total_tiles; tile += MULTI ? gridDim.x : total_tiles, ++ti) {
+        const int split = tile / (p.tiles_m * p.tiles_n);
+        const int kb0 = split * p.kblocks_per_split;
+        const int iters = min(kblocks, kb0 + p.kblocks_per_split) - kb0;
+        const int acc = ti & 1;
+        // the epilogue must have drained this accumulator (tile ti - 2) before it is overwritten
+        if (MULTI && ti >= 2) mbar_wait(smem_u32(&accum_empty[acc]), ((ti >> 1) - 1) & 1, p.status, 4);
         tc_fence_after();
-        const uint32_t a = smem0 + s * stage_bytes, b = a + kStageA;
-        const uint64_t da = smem_desc_sw128(a), db = smem_desc_sw128(b);
+        const uint32_t tmem_d = tmem_base + acc * BN;
+        for (int i = 0; i < iters; ++i, ++it) {
+          const int slot = it % p.stages;
+          mbar_wait(smem_u32(&full_bar[slot]), (it / p.stages) & 1, p.status, 2);
+          tc_fence_after();
+          const uint32_t a = smem0 + slot * stage_bytes, b = a + kStageA;
+          const uint64_t da = smem_desc_sw128(a), db = smem_desc_sw128(b);
 #pragma unroll
-        for (int k = 0; k < kTileK / 16; ++k) {
-          // 16 elements = 32 bytes along K: +2 in the descriptor's 16-byte address units
-          umma_bf16(tmem_base, da + 2 * k, db + 2 * k, idesc, (i > 0 || k > 0) ? 1u : 0u);
+          for (int k = 0; k < kTileK / 16; ++k) {
+            // 16 elements = 32 bytes along K: +2 in the descriptor's 16-byte address units
+            umma_bf16(tmem_d, da + 2 * k, db + 2 * k, idesc, (i > 0 || k > 0) ? 1u : 0u);
+          }
+          umma_commit(smem_u32(&empty_bar[slot]));
         }
-        umma_commit(smem_u32(&empty_bar[s]));
+        umma_commit(smem_u32(&accum_full[acc]));
       }
-      umma_commit(smem_u32(&accum_bar));
     }
     __syncwarp();
   } else {
     // ---------------- epilogue: warps 2..5 own TMEM lanes 32 * (warp % 4) ..
     const int quarter = warp & 3;
     sb::grid_dependency_wait();
-    const bool ok = iters > 0 && mbar_wait(smem_u32(&accum_bar), 0, p.status, 3);
-    tc_fence_after();
-    const int n0 = tile_n * BN;
-    if (EPI == kSwiglu) {
-      // lanes 0..63 hold gate rows, lanes 64..127 the matching up rows
-      float* xch = reinterpret_cast<float*>(smem_raw + ((smem0 - smem_u32(smem_raw))));  // stage 0 is free by now
-      const int j = tile_m * 64 + (quarter & 1) * 32 + lane;  // output feature
-      bf16* out = reinterpret_cast<bf16*>(p.out);
-      for (int c0 = 0; c0 < BN; c0 += 16) {
-        float v[16];
-        tmem_load16(tmem_base + (static_cast<uint32_t>(quarter * 32) << 16) + c0, v);
-        if (quarter >= 2) {
+    int ti = 0;
+    for (int tile = blockIdx.x; tile < total_tiles; tile += MULTI ? gridDim.x : total_tiles, ++ti) {
+      const int tile_m = tile % p.tiles_m, rest = tile / p.tiles_m;
+      const int tile_n = rest % p.tiles_n, split = rest / p.tiles_n;
+      const int acc = ti & 1;
+      const bool ok = mbar_wait(smem_u32(&accum_full[acc]), (ti >> 1) & 1, p.status, 3);
+      tc_fence_after();
+      const uint32_t tmem_d = tmem_base + acc * BN + (static_cast<uint32_t>(quarter * 32) << 16);
+      const int n0 = tile_n * BN;
+      if (EPI == kSwiglu) {
+        // lanes 0..63 hold gate rows, lanes 64..127 the matching up rows
+        const int j = tile_m * 64 + (quarter & 1) * 32 + lane;  // output feature
+        bf16* out = reinterpret_cast<bf16*>(p.out);
+        for (int c0 = 0; c0 < BN; c0 += 16) {
+          float v[16];
+          tmem_load16(tmem_d + c0, v);
+          if (quarter >= 2) {
 #pragma unroll
-          for (int c = 0; c < 16; ++c) xch[c * 64 + (quarter - 2) * 32 + lane] = v[c];
+            for (int c = 0; c < 16; ++c) xch[c * 64 + (quarter - 2) * 32 + lane] = v[c];
+          }
+          asm volatile("bar.sync 1, 128;" ::: "memory");
+          if (quarter < 2 && ok) {
+#pragma unroll
+            for (int c = 0; c < 16; ++c) {
+              const int n = n0 + c0 + c;
+              if (n < p.N && j < p.half_rows) {
+                const float g = v[c], u = xch[c * 64 + quarter * 32 + lane];
+                out[static_cast<int64_t>(n) * p.ldo + j] = __float2bfloat16_rn((g / (1.0f + expf(-g))) * u);
+              }
+            }
+          }
+          asm volatile("bar.sync 1, 128;" ::: "memory");
         }
-        asm volatile("bar.sync 1, 128;" ::: "memory");
-        if (quarter < 2 && ok) {
+      } else {
+        const int m = tile_m * kTileM + quarter * 32 + lane;
+        float* out = p.out + static_cast<int64_t>(split) * p.split_stride;
+        for (int c0 = 0; c0 < BN; c0 += 16) {
+          float v[16];
+          tmem_load16(tmem_d + c0, v);
+          if (m < p.M && ok) {
+            float* o = out + static_cast<int64_t>(n0 + c0) * p.ldo + m;
+            if (EPI == kAdd) {
+              // all loads of the residual first, then the sums and stores: sixteen independent round trips
+              float old[16];
 #pragma unroll
-          for (int c = 0; c < 16; ++c) {
-            const int n = n0 + c0 + c;
-            if (n < p.N && j < p.half_rows) {
-              const float g = v[c], u = xch[c * 64 + quarter * 32 + lane];
-              out[static_cast<int64_t>(n) * p.ldo + j] = __float2bfloat16_rn((g / (1.0f + expf(-g))) * u);
+              for (int c = 0; c < 16; ++c) old[c] = (n0 + c0 + c < p.N) ? o[static_cast<int64_t>(c) * p.ldo] : 0.0f;
+#pragma unroll
+              for (int c = 0; c < 16; ++c)
+                if (n0 + c0 + c < p.N) o[static_cast<int64_t>(c) * p.ldo] = old[c] + v[c];
+            } else {
+#pragma unroll
+              for (int c = 0; c < 16; ++c)
+                if (n0 + c0 + c < p.N) o[static_cast<int64_t>(c) * p.ldo] = v[c];
             }
           }
         }
-        asm volatile("bar.sync 1, 128;" ::: "memory");
       }
-    } else {
-      const int m = tile_m * kTileM + quarter * 32 + lane;
-      float* out = p.out + static_cast<int64_t>(split) * p.split_stride;
-      for (int c0 = 0; c0 < BN; c0 += 16) {
-        float v[16];
-        tmem_load16(tmem_base + (static_cast<uint32_t>(quarter * 32) << 16) + c0, v);
-        if (m < p.M && ok) {
-#pragma unroll
-          for (int c = 0; c < 16; ++c) {
-            const int n = n0 + c0 + c;
-            if (n < p.N) {
-              float* o = out + static_cast<int64_t>(n) * p.ldo + m;
-              *o = EPI == kAdd ? (*o + v[c]) : v[c];
-            }
-          }
-        }
+      // this warp has read its part of the accumulator: let the MMA issuer reuse it
+      if (MULTI) {
+        tc_fence_before();
+        __syncwarp();
+        if (lane == 0) asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(&accum_empty[acc])) : "memory");
       }
     }
     tc_fence_before();
@@ -364,7 +410,7 @@ SB_EXPORT int sb_gemm_tc_splits(int n, int M, int K) {
   if (n > 128) return 1;
   const int n_pad = n <= 16 ? 16 : n <= 32 ? 32 : n <= 64 ? 64 : 128;
   int splits = 148 / tiles_m;   // at most one wave of CTAs
-  splits = min(splits, K / (16 * n_pad));
+  (void)n_pad;                  // the partial sums stay in L2 until their consumer reads them, whatever n is
   splits = min(splits, kblocks / 2);
   splits = max(splits, 1);
   const int per = (kblocks + splits - 1) / splits;
@@ -401,14 +447,13 @@ SB_EXPORT int sb_gemm_tc(const void* x, int64_t ldx, const void* w, int64_t ldw,
   const int stage_bytes = kStageA + p.block_n * 128;
   p.stages = min(kMaxStages, kSmemBudget / stage_bytes);
   {
-    // More CTAs than SMs: take fewer stages so that two or three CTAs share an SM and one's prologue and
-    // epilogue overlap with the others' streaming (tensor memory allows 512 / BN of them).
-    const int tiles_m = epilogue == kSwiglu ? (half_rows + 63) / 64 : (M + kTileM - 1) / kTileM;
-    const long long ctas = static_cast<long long>(tiles_m) * ((n + p.block_n - 1) / p.block_n) * splits;
-    if (ctas > 2 * 148) {
-      const int per_sm = p.block_n <= 64 ? 3 : 2;
-      p.stages = max(2, min(p.stages, (kSmemBudget + 16 * 1024) / per_sm / stage_bytes));
-    }
+    // Many tiles and few tokens (a bandwidth-bound stream such as the head): three CTAs an SM with shorter
+    // rings, so that one's prologue and epilogue overlap with the others' streaming. Many tiles and many
+    // tokens: one CTA an SM with the deepest ring; its two accumulators overlap epilogue and main loop.
+    const long long tiles = static_cast<long long>(epilogue == kSwiglu ? (half_rows + 63) / 64 : (M + kTileM - 1) / kTileM) *
+                            ((n + p.block_n - 1) / p.block_n) * splits;
+    if (tiles > 2 * 148 && p.block_n <= 64) p.stages = max(2, min(p.stages, (kSmemBudget + 16 * 1024) / 3 / stage_bytes));
+    if (const char* e = getenv("SB_GEMM_STAGES")) p.stages = max(2, min(p.stages, atoi(e)));
   }
   p.kblocks_per_split = (kblocks + splits - 1) / splits;
   if ((kblocks + p.kblocks_per_split - 1) / p.kblocks_per_split != splits)
@@ -421,25 +466,39 @@ SB_EXPORT int sb_gemm_tc(const void* x, int64_t ldx, const void* w, int64_t ldw,
   if (!tensor_map(w, M, K, ldw, box_w, &map_w) || !tensor_map(x, n, K, ldx, p.block_n, &map_x))
     return sb::fail("sb_gemm_tc: cuTensorMapEncodeTiled failed (M %d N %d K %d)", M, n, K);
 
-  const int tiles_m = epilogue == kSwiglu ? (half_rows + 63) / 64 : (M + kTileM - 1) / kTileM;
-  dim3 grid(tiles_m, (n + p.block_n - 1) / p.block_n, splits);
-  if (grid.y > 65535) return sb::fail("sb_gemm_tc: too many token tiles");
+  p.tiles_m = epilogue == kSwiglu ? (half_rows + 63) / 64 : (M + kTileM - 1) / kTileM;
+  p.tiles_n = (n + p.block_n - 1) / p.block_n;
+  p.splits = splits;
+  const long long total_tiles = static_cast<long long>(p.tiles_m) * p.tiles_n * splits;
+  if (total_tiles > (1ll << 30)) return sb::fail("sb_gemm_tc: too many tiles");
   const size_t smem = static_cast<size_t>(p.stages) * stage_bytes + 1024;
-#define SB_LAUNCH(EPI)                                                                              \
-  do {                                                                                              \
-    static bool attr_set = false;                                                                   \
-    if (!attr_set) {                                                                                \
-      if (cudaFuncSetAttribute(gemm_tc_kernel<EPI>, cudaFuncAttributeMaxDynamicSharedMemorySize,    \
-                               kSmemBudget + 2048) != cudaSuccess)                                  \
-        return sb::fail("sb_gemm_tc: cannot raise the shared memory limit");                        \
-      attr_set = true;                                                                              \
-    }                                                                                               \
-    sb::launch_pdl(gemm_tc_kernel<EPI>, grid, dim3(kThreads), smem, stream, map_w, map_x, p);       \
+  // Persistent CTAs: as many as fit the GPU at once (by shared and tensor memory), each walking tiles.
+  int per_sm = static_cast<int>((227 * 1024) / (smem + 2048));
+  per_sm = max(1, min(per_sm, 512 / max(32, 2 * p.block_n)));
+  const long long resident = 148ll * per_sm;
+  const bool multi = total_tiles > resident;
+  const dim3 grid(static_cast<unsigned>(multi ? resident : total_tiles));
+#define SB_LAUNCH_M(EPI, MULTI)                                                                         \
+  do {                                                                                                  \
+    static bool attr_set = false;                                                                       \
+    if (!attr_set) {                                                                                    \
+      if (cudaFuncSetAttribute(gemm_tc_kernel<EPI, MULTI>, cudaFuncAttributeMaxDynamicSharedMemorySize, \
+                               kSmemBudget + 2048) != cudaSuccess)                                      \
+        return sb::fail("sb_gemm_tc: cannot raise the shared memory limit");                            \
+      attr_set = true;                                                                                  \
+    }                                                                                                   \
+    sb::launch_pdl(gemm_tc_kernel<EPI, MULTI>, grid, dim3(kThreads), smem, stream, map_w, map_x, p);    \
+  } while (0)
+#define SB_LAUNCH(EPI)                  \
+  do {                                  \
+    if (multi) SB_LAUNCH_M(EPI, true);  \
+    else SB_LAUNCH_M(EPI, false);       \
   } while (0)
   if (epilogue == kStore) SB_LAUNCH(kStore);
   else if (epilogue == kAdd) SB_LAUNCH(kAdd);
   else SB_LAUNCH(kSwiglu);
 #undef SB_LAUNCH
+#undef SB_LAUNCH_M
   return sb::check_launch("sb_gemm_tc");
 }
 
