@@ -136,6 +136,37 @@ __device__ __forceinline__ uint32_t instr_desc(int n) {
   return (1u << 4) | (1u << 7) | (1u << 10) | (static_cast<uint32_t>(n >> 3) << 17) | (static_cast<uint32_t>(kTileM >> 4) << 24);
 }
 
+// Rows of one accumulator tile to global memory: out[n, m] = d (kStore) or out[n, m] += d (kAdd). Each thread
+// owns output feature m and walks the tile's tokens sixteen at a time; for kAdd the residual values of the
+// next sixteen are requested before the current sixteen are summed and stored.
+template <int EPI>
+__device__ __forceinline__ void store_tile(uint32_t tmem_row, float* out, int m, int M, int n0, int N, int64_t ldo, int BN, bool ok) {
+  const bool live = m < M && ok;
+  float nxt[16];
+  if (EPI == kAdd && live) {
+#pragma unroll
+    for (int c = 0; c < 16; ++c) nxt[c] = (n0 + c < N) ? out[static_cast<int64_t>(n0 + c) * ldo + m] : 0.0f;
+  }
+  for (int c0 = 0; c0 < BN; c0 += 16) {
+    float v[16], old[16];
+    float* o = out + static_cast<int64_t>(n0 + c0) * ldo + m;
+    if (EPI == kAdd && live) {
+#pragma unroll
+      for (int c = 0; c < 16; ++c) old[c] = nxt[c];
+      if (c0 + 16 < BN) {
+#pragma unroll
+        for (int c = 0; c < 16; ++c) nxt[c] = (n0 + c0 + 16 + c < N) ? o[static_cast<int64_t>(16 + c) * ldo] : 0.0f;
+      }
+    }
+    tmem_load16(tmem_row + c0, v);
+    if (live) {
+#pragma unroll
+      for (int c = 0; c < 16; ++c)
+        if (n0 + c0 + c < N) o[static_cast<int64_t>(c) * ldo] = EPI == kAdd ? old[c] + v[c] : v[c];
+    }
+  }
+}
+
 struct GemmParams {
   float* out;           // kStore / kAdd: float32 [N, ldo]; kSwiglu: bfloat16 [N, ldo]
   int64_t ldo;
@@ -148,6 +179,149 @@ struct GemmParams {
   int half_rows;         // kSwiglu: rows of the gate half (intermediate size); W is [2 * half_rows, K]
   int* status;
 };
+
+// One tile per CTA: the lean form used when every tile has a CTA of its own (every decode-sized launch).
+// blockIdx = (weight tile, token tile, K range).
+template <int EPI>
+__global__ void __launch_bounds__(kThreads, 1)
+gemm_tc_single_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUtensorMap map_x, const GemmParams p) {
+  extern __shared__ __align__(1024) uint8_t smem_raw[];
+  __shared__ __align__(8) uint64_t full_bar[kMaxStages];
+  __shared__ __align__(8) uint64_t empty_bar[kMaxStages];
+  __shared__ __align__(8) uint64_t accum_bar;
+  __shared__ uint32_t tmem_base_s;
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int BN = p.block_n;
+  const int stage_b = BN * 128;
+  const int stage_bytes = kStageA + stage_b;
+  // Dynamic shared memory is only guaranteed 16-byte alignment: round up to the swizzle's 1024.
+  const uint32_t smem0 = (smem_u32(smem_raw) + 1023u) & ~1023u;
+  const int tile_m = blockIdx.x, tile_n = blockIdx.y, split = blockIdx.z;
+  const int kblocks = (p.K + kTileK - 1) / kTileK;
+  const int kb0 = split * p.kblocks_per_split;
+  const int kb1 = min(kblocks, kb0 + p.kblocks_per_split);
+  const int iters = kb1 - kb0;
+  const uint32_t tmem_cols = BN < 32 ? 32 : BN;
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < p.stages; ++s) {
+      mbar_init(smem_u32(&full_bar[s]), 1);
+      mbar_init(smem_u32(&empty_bar[s]), 1);
+    }
+    mbar_init(smem_u32(&accum_bar), 1);
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+  }
+  if (warp == 1) tmem_alloc(smem_u32(&tmem_base_s), tmem_cols);
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = tmem_base_s;
+
+  sb::grid_launch_dependents();
+  if (warp == 0) {
+    if (lane == 0) {
+      // ---------------- producer: TMA loads. The weights do not depend on the kernels before this one,
+      // so the first ring of weight tiles is requested before waiting for them to finish; the tokens'
+      // tiles follow once their producer is done.
+      const int row_w = EPI == kSwiglu ? tile_m * 64 : tile_m * kTileM;
+      auto load_w = [&](int i) {
+        const int s = i % p.stages;
+        const uint32_t bar = smem_u32(&full_bar[s]);
+        const uint32_t a = smem0 + s * stage_bytes;
+        mbar_expect_tx(bar, stage_bytes);
+        const int k = (kb0 + i) * kTileK;
+        if (EPI == kSwiglu) {
+          tma_load_2d(a, &map_w, bar, k, row_w);
+          tma_load_2d(a + kStageA / 2, &map_w, bar, k, p.half_rows + row_w);
+        } else {
+          tma_load_2d(a, &map_w, bar, k, row_w);
+        }
+      };
+      auto load_x = [&](int i) {
+        const int s = i % p.stages;
+        tma_load_2d(smem0 + s * stage_bytes + kStageA, &map_x, smem_u32(&full_bar[s]), (kb0 + i) * kTileK, tile_n * BN);
+      };
+      const int ahead = min(iters, p.stages);
+      for (int i = 0; i < ahead; ++i) load_w(i);
+      sb::grid_dependency_wait();
+      for (int i = 0; i < ahead; ++i) load_x(i);
+      for (int i = ahead; i < iters; ++i) {
+        mbar_wait(smem_u32(&empty_bar[i % p.stages]), ((i / p.stages) - 1) & 1, p.status, 1);
+        load_w(i);
+        load_x(i);
+      }
+    }
+  } else if (warp == 1) {
+    if (lane == 0) {
+      // ---------------- MMA issuer
+      const uint32_t idesc = instr_desc(BN);
+      for (int i = 0; i < iters; ++i) {
+        const int s = i % p.stages;
+        mbar_wait(smem_u32(&full_bar[s]), (i / p.stages) & 1, p.status, 2);
+        tc_fence_after();
+        const uint32_t a = smem0 + s * stage_bytes, b = a + kStageA;
+        const uint64_t da = smem_desc_sw128(a), db = smem_desc_sw128(b);
+#pragma unroll
+        for (int k = 0; k < kTileK / 16; ++k) {
+          // 16 elements = 32 bytes along K: +2 in the descriptor's 16-byte address units
+          umma_bf16(tmem_base, da + 2 * k, db + 2 * k, idesc, (i > 0 || k > 0) ? 1u : 0u);
+        }
+        umma_commit(smem_u32(&empty_bar[s]));
+      }
+      umma_commit(smem_u32(&accum_bar));
+    }
+    __syncwarp();
+  } else {
+    // ---------------- epilogue: warps 2..5 own TMEM lanes 32 * (warp % 4) ..
+    const int quarter = warp & 3;
+    sb::grid_dependency_wait();
+    const bool ok = iters > 0 && mbar_wait(smem_u32(&accum_bar), 0, p.status, 3);
+    tc_fence_after();
+    const int n0 = tile_n * BN;
+    if (EPI == kSwiglu) {
+      // lanes 0..63 hold gate rows, lanes 64..127 the matching up rows
+      float* xch = reinterpret_cast<float*>(smem_raw + ((smem0 - smem_u32(smem_raw))));  // stage 0 is free by now
+      const int j = tile_m * 64 + (quarter & 1) * 32 + lane;  // output feature
+      bf16* out = reinterpret_cast<bf16*>(p.out);
+      for (int c0 = 0; c0 < BN; c0 += 16) {
+        float v[16];
+        tmem_load16(tmem_base + (static_cast<uint32_t>(quarter * 32) << 16) + c0, v);
+        // gate warps hand over columns 8..15, up warps columns 0..7: every warp then finishes eight columns
+        if (quarter >= 2) {
+#pragma unroll
+          for (int c = 0; c < 8; ++c) xch[c * 64 + (quarter - 2) * 32 + lane] = v[c];
+        } else {
+#pragma unroll
+          for (int c = 0; c < 8; ++c) xch[(8 + c) * 64 + quarter * 32 + lane] = v[8 + c];
+        }
+        asm volatile("bar.sync 1, 128;" ::: "memory");
+        if (ok && j < p.half_rows) {
+          const int cb = quarter >= 2 ? 8 : 0;
+#pragma unroll
+          for (int c = 0; c < 8; ++c) {
+            const int n = n0 + c0 + cb + c;
+            if (n < p.N) {
+              const float other = xch[(cb + c) * 64 + (quarter & 1) * 32 + lane];
+              const float g = quarter >= 2 ? other : v[c], u = quarter >= 2 ? v[8 + c] : other;
+              out[static_cast<int64_t>(n) * p.ldo + j] = __float2bfloat16_rn((g / (1.0f + __expf(-g))) * u);
+            }
+          }
+        }
+        asm volatile("bar.sync 1, 128;" ::: "memory");
+      }
+    } else {
+      store_tile<EPI>(tmem_base + (static_cast<uint32_t>(quarter * 32) << 16), p.out + static_cast<int64_t>(split) * p.split_stride,
+                      tile_m * kTileM + quarter * 32 + lane, p.M, n0, p.N, p.ldo, BN, ok);
+    }
+    tc_fence_before();
+  }
+  __syncthreads();
+  if (warp == 1) {
+    tc_fence_after();
+    tmem_dealloc(tmem_base, tmem_cols);
+  }
+}
 
 template <int EPI, bool MULTI>   // MULTI: a CTA may walk several tiles (two accumulators); else exactly one
 __global__ void __launch_bounds__(kThreads)
@@ -285,46 +459,32 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
         for (int c0 = 0; c0 < BN; c0 += 16) {
           float v[16];
           tmem_load16(tmem_d + c0, v);
+          // gate warps hand over columns 8..15, up warps columns 0..7: every warp then finishes eight columns
           if (quarter >= 2) {
-#pragma unroll
-            for (int c = 0; c < 16; ++c) xch[c * 64 + (quarter - 2) * 32 + lane] = v[c];
+  #pragma unroll
+            for (int c = 0; c < 8; ++c) xch[c * 64 + (quarter - 2) * 32 + lane] = v[c];
+          } else {
+  #pragma unroll
+            for (int c = 0; c < 8; ++c) xch[(8 + c) * 64 + quarter * 32 + lane] = v[8 + c];
           }
           asm volatile("bar.sync 1, 128;" ::: "memory");
-          if (quarter < 2 && ok) {
-#pragma unroll
-            for (int c = 0; c < 16; ++c) {
-              const int n = n0 + c0 + c;
-              if (n < p.N && j < p.half_rows) {
-                const float g = v[c], u = xch[c * 64 + quarter * 32 + lane];
-                out[static_cast<int64_t>(n) * p.ldo + j] = __float2bfloat16_rn((g / (1.0f + expf(-g))) * u);
+          if (ok && j < p.half_rows) {
+            const int cb = quarter >= 2 ? 8 : 0;
+  #pragma unroll
+            for (int c = 0; c < 8; ++c) {
+              const int n = n0 + c0 + cb + c;
+              if (n < p.N) {
+                const float other = xch[(cb + c) * 64 + (quarter & 1) * 32 + lane];
+                const float g = quarter >= 2 ? other : v[c], u = quarter >= 2 ? v[8 + c] : other;
+                out[static_cast<int64_t>(n) * p.ldo + j] = __float2bfloat16_rn((g / (1.0f + __expf(-g))) * u);
               }
             }
           }
           asm volatile("bar.sync 1, 128;" ::: "memory");
         }
       } else {
-        const int m = tile_m * kTileM + quarter * 32 + lane;
-        float* out = p.out + static_cast<int64_t>(split) * p.split_stride;
-        for (int c0 = 0; c0 < BN; c0 += 16) {
-          float v[16];
-          tmem_load16(tmem_d + c0, v);
-          if (m < p.M && ok) {
-            float* o = out + static_cast<int64_t>(n0 + c0) * p.ldo + m;
-            if (EPI == kAdd) {
-              // all loads of the residual first, then the sums and stores: sixteen independent round trips
-              float old[16];
-#pragma unroll
-              for (int c = 0; c < 16; ++c) old[c] = (n0 + c0 + c < p.N) ? o[static_cast<int64_t>(c) * p.ldo] : 0.0f;
-#pragma unroll
-              for (int c = 0; c < 16; ++c)
-                if (n0 + c0 + c < p.N) o[static_cast<int64_t>(c) * p.ldo] = old[c] + v[c];
-            } else {
-#pragma unroll
-              for (int c = 0; c < 16; ++c)
-                if (n0 + c0 + c < p.N) o[static_cast<int64_t>(c) * p.ldo] = v[c];
-            }
-          }
-        }
+        store_tile<EPI>(tmem_d, p.out + static_cast<int64_t>(split) * p.split_stride, tile_m * kTileM + quarter * 32 + lane,
+                        p.M, n0, p.N, p.ldo, BN, ok);
       }
       // this warp has read its part of the accumulator: let the MMA issuer reuse it
       if (MULTI) {
@@ -477,6 +637,7 @@ SB_EXPORT int sb_gemm_tc(const void* x, int64_t ldx, const void* w, int64_t ldw,
   per_sm = max(1, min(per_sm, 512 / max(32, 2 * p.block_n)));
   const long long resident = 148ll * per_sm;
   const bool multi = total_tiles > resident;
+  if (!multi && (p.tiles_n > 65535 || splits > 65535)) return sb::fail("sb_gemm_tc: grid too large");
   const dim3 grid(static_cast<unsigned>(multi ? resident : total_tiles));
 #define SB_LAUNCH_M(EPI, MULTI)                                                                         \
   do {                                                                                                  \
@@ -489,15 +650,27 @@ SB_EXPORT int sb_gemm_tc(const void* x, int64_t ldx, const void* w, int64_t ldw,
     }                                                                                                   \
     sb::launch_pdl(gemm_tc_kernel<EPI, MULTI>, grid, dim3(kThreads), smem, stream, map_w, map_x, p);    \
   } while (0)
+#define SB_LAUNCH_S(EPI)                                                                                \
+  do {                                                                                                  \
+    static bool attr_set = false;                                                                       \
+    if (!attr_set) {                                                                                    \
+      if (cudaFuncSetAttribute(gemm_tc_single_kernel<EPI>, cudaFuncAttributeMaxDynamicSharedMemorySize, \
+                               kSmemBudget + 2048) != cudaSuccess)                                      \
+        return sb::fail("sb_gemm_tc: cannot raise the shared memory limit");                            \
+      attr_set = true;                                                                                  \
+    }                                                                                                   \
+    sb::launch_pdl(gemm_tc_single_kernel<EPI>, dim3(p.tiles_m, p.tiles_n, splits), dim3(kThreads), smem, stream, map_w, map_x, p); \
+  } while (0)
 #define SB_LAUNCH(EPI)                  \
   do {                                  \
     if (multi) SB_LAUNCH_M(EPI, true);  \
-    else SB_LAUNCH_M(EPI, false);       \
+    else SB_LAUNCH_S(EPI);              \
   } while (0)
   if (epilogue == kStore) SB_LAUNCH(kStore);
   else if (epilogue == kAdd) SB_LAUNCH(kAdd);
   else SB_LAUNCH(kSwiglu);
 #undef SB_LAUNCH
+#undef SB_LAUNCH_S
 #undef SB_LAUNCH_M
   return sb::check_launch("sb_gemm_tc");
 }
