@@ -34,12 +34,19 @@ constexpr int kKeys = 64;        // keys per tile
 constexpr int kChunk = 256;      // keys per decode chunk (4 warps x 64)
 constexpr float kLog2e = 1.4426950408889634f;
 
+// 2^x by the hardware's approximation (two units in the last place); exp2f adds a slow path for subnormals.
+__device__ __forceinline__ float fast_exp2(float x) {
+  float y;
+  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+  return y;
+}
+
 struct AttnTcParams {
   const bf16* q;     // [n][Hq * D]
   bf16* out;         // [n][Hq * D]
   const bf16* k_base;
   const int32_t* block_table;
-  int max_pages, page_size;
+  int max_pages, page_size, page_shift;   // page_shift: log2(page_size), or -1 if it is no power of two
   int64_t page_stride, v_offset, head_stride;
   const int32_t* meta;   // [4][meta_stride]: slot, first row, length, first position of every entry
   int meta_stride;
@@ -79,21 +86,28 @@ __device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) {
   return *reinterpret_cast<uint32_t*>(&v);
 }
 
-// Copies keys (or values) [key0, key0 + 64) of one kv head into dst[64][D + 8]; keys outside
-// [key_lo, key_hi] are zero-filled. `threads` threads of the caller take part (tid in 0..threads-1).
+// Copies keys and values [key0, key0 + 64) of one kv head into dstK and dstV ([64][D + 8] each); keys outside
+// [key_lo, key_hi] are zero-filled. `threads` threads of the caller take part (tid in 0..threads-1): D / 8
+// threads share a key (one 16-byte piece each), so the page is looked up once for a key's key and value rows.
 template <int D>
-__device__ __forceinline__ void load_kv_tile(bf16* dst, const bf16* plane, const int32_t* table, int page_size,
-                                             int64_t page_stride, int key0, int key_lo, int key_hi, int tid, int threads) {
+__device__ __forceinline__ void load_kv_tiles(bf16* dstK, bf16* dstV, const bf16* kplane, int64_t v_offset,
+                                              const int32_t* table, int page_size, int page_shift, int64_t page_stride,
+                                              int key0, int key_lo, int key_hi, int tid, int threads) {
   constexpr int LD = D + 8, CH = D / 8;
-  for (int idx = tid; idx < kKeys * CH; idx += threads) {
-    const int i = idx / CH, c = idx % CH;
+  const int c = tid % CH;
+  for (int i = tid / CH; i < kKeys; i += threads / CH) {
     const int key = key0 + i;
-    bf16* d = dst + i * LD + c * 8;
+    bf16* dk = dstK + i * LD + c * 8;
+    bf16* dv = dstV + i * LD + c * 8;
     if (key >= key_lo && key <= key_hi) {
-      const int page = table[key / page_size];
-      cp_async16(smem_u32(d), plane + static_cast<int64_t>(page) * page_stride + static_cast<int64_t>(key % page_size) * D + c * 8);
+      const int pi = page_shift >= 0 ? key >> page_shift : key / page_size;
+      const int in_page = page_shift >= 0 ? key & (page_size - 1) : key % page_size;
+      const bf16* src = kplane + static_cast<int64_t>(table[pi]) * page_stride + in_page * D + c * 8;
+      cp_async16(smem_u32(dk), src);
+      cp_async16(smem_u32(dv), src + v_offset);
     } else {
-      *reinterpret_cast<uint4*>(d) = make_uint4(0, 0, 0, 0);
+      *reinterpret_cast<uint4*>(dk) = make_uint4(0, 0, 0, 0);
+      *reinterpret_cast<uint4*>(dv) = make_uint4(0, 0, 0, 0);
     }
   }
 }
@@ -172,7 +186,6 @@ __global__ void __launch_bounds__(128) attn_chunk_kernel(const AttnTcParams p) {
   const int key_lo = p.window > 0 ? max(0, pos0 - p.window + 1) : 0;
   const int32_t* table = p.block_table + static_cast<int64_t>(slot) * p.max_pages;
   const bf16* kplane = p.k_base + static_cast<int64_t>(g) * p.head_stride;
-  const bf16* vplane = kplane + p.v_offset;
 
   // Q tile: row r = (position r / G, head g * G + r % G)
   for (int idx = tid; idx < 64 * CH; idx += 128) {
@@ -185,8 +198,7 @@ __global__ void __launch_bounds__(128) attn_chunk_kernel(const AttnTcParams p) {
       *reinterpret_cast<uint4*>(d) = make_uint4(0, 0, 0, 0);
   }
   const int kt0 = key_lo / kKeys, kt1 = pos_hi / kKeys;
-  load_kv_tile<D>(sK, kplane, table, p.page_size, p.page_stride, kt0 * kKeys, key_lo, pos_hi, tid, 128);
-  load_kv_tile<D>(sV, vplane, table, p.page_size, p.page_stride, kt0 * kKeys, key_lo, pos_hi, tid, 128);
+  load_kv_tiles<D>(sK, sV, kplane, p.v_offset, table, p.page_size, p.page_shift, p.page_stride, kt0 * kKeys, key_lo, pos_hi, tid, 128);
   cp_commit();
 
   // rows of this thread: warp * 16 + gid and + 8
@@ -216,8 +228,8 @@ __global__ void __launch_bounds__(128) attn_chunk_kernel(const AttnTcParams p) {
         ldsm_x4(qf[ks], smem_u32(sQ + (warp * 16 + (lane & 15)) * LD + ks * 16 + (lane >> 4) * 8));
     }
     if (kt < kt1) {
-      load_kv_tile<D>(sK + (buf ^ 1) * 64 * LD, kplane, table, p.page_size, p.page_stride, (kt + 1) * kKeys, key_lo, pos_hi, tid, 128);
-      load_kv_tile<D>(sV + (buf ^ 1) * 64 * LD, vplane, table, p.page_size, p.page_stride, (kt + 1) * kKeys, key_lo, pos_hi, tid, 128);
+      load_kv_tiles<D>(sK + (buf ^ 1) * 64 * LD, sV + (buf ^ 1) * 64 * LD, kplane, p.v_offset, table, p.page_size, p.page_shift,
+                       p.page_stride, (kt + 1) * kKeys, key_lo, pos_hi, tid, 128);
       cp_commit();
     }
     float s[8][4];
@@ -241,7 +253,7 @@ __global__ void __launch_bounds__(128) attn_chunk_kernel(const AttnTcParams p) {
       mx[h] = fmaxf(mx[h], __shfl_xor_sync(0xffffffffu, mx[h], 2));
       const float m_new = fmaxf(m[h], mx[h]);
       m_use[h] = m_new == -INFINITY ? 0.0f : m_new;
-      alpha[h] = exp2f(m[h] - m_use[h]);
+      alpha[h] = fast_exp2(m[h] - m_use[h]);
       m[h] = m_new;
       l[h] *= alpha[h];
     }
@@ -249,7 +261,7 @@ __global__ void __launch_bounds__(128) attn_chunk_kernel(const AttnTcParams p) {
     for (int nt = 0; nt < 8; ++nt)
 #pragma unroll
       for (int x = 0; x < 4; ++x) {
-        const float e2 = exp2f(s[nt][x] - m_use[x >> 1]);
+        const float e2 = fast_exp2(s[nt][x] - m_use[x >> 1]);
         s[nt][x] = e2;
         l[x >> 1] += e2;
       }
@@ -302,7 +314,6 @@ __global__ void __launch_bounds__(128) attn_decode_kernel(const AttnTcParams p) 
   if (chunk * kChunk > pos_hi || chunk * kChunk + kChunk - 1 < key_lo) return;   // no key of this chunk is visible
   const int32_t* table = p.block_table + static_cast<int64_t>(slot) * p.max_pages;
   const bf16* kplane = p.k_base + static_cast<int64_t>(g) * p.head_stride;
-  const bf16* vplane = kplane + p.v_offset;
   const int rows = L * G;
 
   for (int idx = tid; idx < 16 * CH; idx += 128) {
@@ -318,8 +329,7 @@ __global__ void __launch_bounds__(128) attn_decode_kernel(const AttnTcParams p) 
   const int key0 = chunk * kChunk + warp * kKeys;
   const bool any = key0 <= pos_hi && key0 + kKeys - 1 >= key_lo;
   if (any) {
-    load_kv_tile<D>(sK, kplane, table, p.page_size, p.page_stride, key0, key_lo, pos_hi, lane, 32);
-    load_kv_tile<D>(sV, vplane, table, p.page_size, p.page_stride, key0, key_lo, pos_hi, lane, 32);
+    load_kv_tiles<D>(sK, sV, kplane, p.v_offset, table, p.page_size, p.page_shift, p.page_stride, key0, key_lo, pos_hi, lane, 32);
   }
   cp_commit();
   cp_wait<0>();
@@ -365,7 +375,7 @@ __global__ void __launch_bounds__(128) attn_decode_kernel(const AttnTcParams p) 
 #pragma unroll
       for (int x = 0; x < 4; ++x) {
         const float mu = m[x >> 1] == -INFINITY ? 0.0f : m[x >> 1];
-        const float e2 = exp2f(s[nt][x] - mu);
+        const float e2 = fast_exp2(s[nt][x] - mu);
         s[nt][x] = e2;
         l[x >> 1] += e2;
       }
@@ -402,7 +412,7 @@ __global__ void __launch_bounds__(128) attn_decode_kernel(const AttnTcParams p) 
     float acc = 0.0f, ll = 0.0f;
 #pragma unroll
     for (int w = 0; w < 4; ++w) {
-      const float f = exp2f(sML[(w * 16 + r) * 2] - mu);
+      const float f = fast_exp2(sML[(w * 16 + r) * 2] - mu);
       acc += sO[(w * 16 + r) * D + d] * f;
       ll += sML[(w * 16 + r) * 2 + 1] * f;
     }
@@ -415,9 +425,9 @@ __global__ void __launch_bounds__(128) attn_decode_kernel(const AttnTcParams p) 
   if (p.counters == nullptr) return;
   // The CTA that finishes an entry's last chunk folds all of them, in ascending order, and writes the rows.
   const int c0 = key_lo / kChunk, c1 = pos_hi / kChunk;
-  __threadfence();
   __syncthreads();
   if (tid == 0) {
+    __threadfence();   // the CTA's records (made visible to this thread by the barrier) before the ticket
     int* counter = p.counters + item * p.Hkv + g;
     const int ticket = atomicAdd(counter, 1);
     is_last_s = ticket == c1 - c0;
@@ -433,7 +443,7 @@ __global__ void __launch_bounds__(128) attn_decode_kernel(const AttnTcParams p) 
     for (int c = c0; c <= c1; ++c) mm = fmaxf(mm, __ldcg(&p.part_ml[((rec0 + c) * 16 + r) * 2]));
     float acc = 0.0f, ll = 0.0f;
     for (int c = c0; c <= c1; ++c) {
-      const float f = exp2f(__ldcg(&p.part_ml[((rec0 + c) * 16 + r) * 2]) - mm);
+      const float f = fast_exp2(__ldcg(&p.part_ml[((rec0 + c) * 16 + r) * 2]) - mm);
       acc += __ldcg(&p.part_o[(rec0 + c) * 16 * D + r * D + d]) * f;
       ll += __ldcg(&p.part_ml[((rec0 + c) * 16 + r) * 2 + 1]) * f;
     }
@@ -458,7 +468,7 @@ __global__ void __launch_bounds__(D) attn_combine_kernel(const AttnTcParams p) {
     for (int c = c0; c <= c1; ++c) mm = fmaxf(mm, p.part_ml[((rec0 + c) * 16 + r) * 2]);
     float acc = 0.0f, ll = 0.0f;
     for (int c = c0; c <= c1; ++c) {
-      const float f = exp2f(p.part_ml[((rec0 + c) * 16 + r) * 2] - mm);
+      const float f = fast_exp2(p.part_ml[((rec0 + c) * 16 + r) * 2] - mm);
       acc += p.part_o[(rec0 + c) * 16 * D + r * D + d] * f;
       ll += p.part_ml[((rec0 + c) * 16 + r) * 2 + 1] * f;
     }
@@ -523,6 +533,9 @@ SB_EXPORT int sb_attention_tc(const void* q, void* out, const void* k_base, cons
   p.block_table = block_table;
   p.max_pages = max_pages;
   p.page_size = page_size;
+  p.page_shift = -1;
+  for (int b = 0; b < 31; ++b)
+    if ((1 << b) == page_size) p.page_shift = b;
   p.page_stride = page_stride;
   p.v_offset = v_offset;
   p.head_stride = head_stride;
