@@ -5,6 +5,8 @@ workloads that the ncu summaries under profiles/ were captured on.
     python -m stride_b200.kernels.microbench gemm --tokens 2048 --rows 2048 --cols 8192 --epilogue add
     python -m stride_b200.kernels.microbench attention --batch 64 --context 512          # decode
     python -m stride_b200.kernels.microbench attention --batch 1 --new 2048 --context 0  # one prompt
+    python -m stride_b200.kernels.microbench step --batch 8                              # timeline of a decode step
+    python -m stride_b200.kernels.microbench step --prefill 2048                         # timeline of a 2,048-token prompt
 
 Weights are cycled through `--copies` buffers larger than L2 in total, so every launch streams from HBM.
 """
@@ -87,6 +89,75 @@ def attention(a) -> dict:
             "kv_GBps": round(kv_bytes / us / 1e3, 1), "TFLOPs": round(flops / us / 1e6, 2)}
 
 
+LLAMA_1B_SHAPE = {
+    "architectures": ["LlamaForCausalLM"], "hidden_size": 2048, "intermediate_size": 8192, "num_hidden_layers": 16,
+    "num_attention_heads": 32, "num_key_value_heads": 8, "head_dim": 64, "vocab_size": 128256, "rope_theta": 500000.0,
+    "rope_scaling": {"rope_type": "llama3", "factor": 32.0, "low_freq_factor": 1.0, "high_freq_factor": 4.0,
+                     "original_max_position_embeddings": 8192},
+    "tie_word_embeddings": True, "rms_norm_eps": 1e-5, "max_position_embeddings": 4096,
+}
+
+
+def step(a) -> dict:
+    """Kernel timeline of one engine step (Llama 3.2 1B shape, random weights) from torch.profiler: a decode step of
+    `batch` requests replayed from its CUDA graph, or a prompt of `prefill` tokens. Kernels overlap under programmatic
+    dependent launch, so each kernel is charged the time from its predecessor's end to its own end."""
+    import collections
+    import re
+
+    from torch.profiler import ProfilerActivity, profile
+
+    from .. import Engine, EngineOptions, StepEntry
+    cfg = dict(LLAMA_1B_SHAPE, num_hidden_layers=a.layers)
+    B, T = a.batch, a.prefill
+    opts = EngineOptions(dtype="bfloat16", max_rows=max(512, B, T), max_full_rows=max(B, 1), max_slots=B + 2,
+                         kv_pages=B * 8 + T // 64 + 48, page_size=64, max_context=4096)
+    eng = Engine.from_random(cfg, 0, opts)
+    gen = torch.Generator().manual_seed(1)
+    slots = [eng.cache.acquire_slot() for _ in range(B)]
+    for s in slots:
+        eng.cache.ensure(s, a.context)
+        eng.step([StepEntry(s, 0, torch.randint(0, 1000, (a.context,), generator=gen).tolist(), [])])
+
+    def decode(k):
+        entries = []
+        for s in slots:
+            eng.cache.ensure(s, a.context + k + 1)
+            entries.append(StepEntry(s, a.context + k, [5], [0]))
+        eng.step(entries)
+
+    def prefill():
+        s = eng.cache.acquire_slot()
+        eng.cache.ensure(s, T)
+        eng.step([StepEntry(s, 0, torch.randint(0, 1000, (T,), generator=gen).tolist(), [T - 1])])
+        torch.cuda.synchronize()
+        eng.cache.release_slot(s)
+
+    run = prefill if T else (lambda: decode(step.k))
+    step.k = 0
+    for _ in range(4):
+        run()
+        step.k += 1
+    torch.cuda.synchronize()
+    with profile(activities=[ProfilerActivity.CUDA]) as prof:
+        run()
+        torch.cuda.synchronize()
+    ks = sorted(((ev.name, ev.time_range.start, ev.time_range.end) for ev in prof.events()
+                 if ev.device_type == torch.autograd.DeviceType.CUDA and "Memcpy" not in ev.name and "Memset" not in ev.name),
+                key=lambda k: k[1])
+    first = max(i for i, k in enumerate(ks) if "embed" in k[0])
+    ks = ks[first:]
+    agg, prev = collections.defaultdict(lambda: [0, 0.0]), None
+    for name, s, e in ks:
+        short = re.sub(r"\(.*", "", name.replace("(anonymous namespace)::", "")).replace("void ", "")
+        agg[short][0] += 1
+        agg[short][1] += (e - prev) if prev is not None else (e - s)
+        prev = max(prev or 0, e)
+    return {"step": "prefill" if T else "decode", "batch": B, "context": a.context, "prefill": T, "layers": a.layers,
+            "wall_us": round(ks[-1][2] - ks[0][1], 1), "kernels": len(ks),
+            "by_kernel": {k: {"launches": c, "critical_us": round(v, 1)} for k, (c, v) in sorted(agg.items(), key=lambda x: -x[1][1])}}
+
+
 def main(argv=None) -> int:
     ap = argparse.ArgumentParser(description=__doc__, formatter_class=argparse.RawDescriptionHelpFormatter)
     sub = ap.add_subparsers(dest="what", required=True)
@@ -106,8 +177,13 @@ def main(argv=None) -> int:
     t.add_argument("--head-dim", type=int, default=64)
     t.add_argument("--page", type=int, default=64)
     t.add_argument("--reps", type=int, default=50)
+    st = sub.add_parser("step")
+    st.add_argument("--batch", type=int, default=8)
+    st.add_argument("--context", type=int, default=256)
+    st.add_argument("--prefill", type=int, default=0, help="time one prompt of this many tokens instead of a decode step")
+    st.add_argument("--layers", type=int, default=16)
     a = ap.parse_args(argv)
-    print(json.dumps({"gemm": gemm, "attention": attention}[a.what](a)))
+    print(json.dumps({"gemm": gemm, "attention": attention, "step": step}[a.what](a), indent=1 if a.what == "step" else None))
     return 0
 
 
