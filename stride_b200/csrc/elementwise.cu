@@ -85,6 +85,52 @@ __global__ void rmsnorm_kernel(float* __restrict__ h, const float* __restrict__ 
   for (int i = threadIdx.x; i < H; i += blockDim.x) o[i] = sb::narrow<TO>(sb::widen(weight[i]) * (row[i] * scale));
 }
 
+// Many rows (a prompt portion): one warp per row, eight rows per block, no shared memory and no block barrier.
+// Pass 1 folds the partials (written back to h) and sums the squares with the lanes' sums combined by xor
+// shuffles; pass 2 re-reads the row (it is in L2) and writes the normed values. H % 4 == 0.
+template <class TW, class TO>
+__global__ void __launch_bounds__(256) rmsnorm_rows_kernel(float* __restrict__ h, const float* __restrict__ partials,
+                                                           int n_partials, int64_t partial_stride,
+                                                           const TW* __restrict__ weight, TO* __restrict__ out, int n, int H,
+                                                           float eps) {
+  sb::grid_launch_dependents();
+  sb::grid_dependency_wait();
+  const int r = blockIdx.x * 8 + (threadIdx.x >> 5), lane = threadIdx.x & 31;
+  if (r >= n) return;
+  float4* hr = reinterpret_cast<float4*>(h + static_cast<int64_t>(r) * H);
+  const int units = H / 4;
+  const int64_t ps = partial_stride / 4;
+  float ss = 0.0f;
+  for (int i = lane; i < units; i += 32) {
+    float4 v = hr[i];
+    const float4* p = reinterpret_cast<const float4*>(partials + static_cast<int64_t>(r) * H) + i;
+    for (int s = 0; s < n_partials; ++s) v = add4(v, p[s * ps]);
+    if (n_partials > 0) hr[i] = v;
+    ss = fmaf(v.x, v.x, ss);
+    ss = fmaf(v.y, v.y, ss);
+    ss = fmaf(v.z, v.z, ss);
+    ss = fmaf(v.w, v.w, ss);
+  }
+  for (int o = 16; o > 0; o >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, o);
+  const float scale = 1.0f / sqrtf(ss / static_cast<float>(H) + eps);
+  TO* o = out + static_cast<int64_t>(r) * H;
+  for (int i = lane; i < units; i += 32) {
+    const float4 v = hr[i];
+    const float w0 = sb::widen(weight[4 * i]), w1 = sb::widen(weight[4 * i + 1]), w2 = sb::widen(weight[4 * i + 2]),
+                w3 = sb::widen(weight[4 * i + 3]);
+    if constexpr (sizeof(TO) == 2) {
+      __nv_bfloat162 lo = __floats2bfloat162_rn(w0 * (v.x * scale), w1 * (v.y * scale));
+      __nv_bfloat162 hi = __floats2bfloat162_rn(w2 * (v.z * scale), w3 * (v.w * scale));
+      uint2 packed;
+      packed.x = *reinterpret_cast<uint32_t*>(&lo);
+      packed.y = *reinterpret_cast<uint32_t*>(&hi);
+      *reinterpret_cast<uint2*>(o + 4 * i) = packed;
+    } else {
+      *reinterpret_cast<float4*>(o + 4 * i) = make_float4(w0 * (v.x * scale), w1 * (v.y * scale), w2 * (v.z * scale), w3 * (v.w * scale));
+    }
+  }
+}
+
 // ------------------------------------------------------------------ rope + append
 struct RopeAppendParams {
   const float* qkv;          // [n_partials][n][(Hq + 2 Hkv) D], partials summed left to right
@@ -172,6 +218,70 @@ __global__ void rope_append_kernel(RopeAppendParams p) {
   }
 }
 
+// The common case (the whole head is rotated, D % 8 == 0): one thread per (head, four adjacent rotation pairs),
+// 16-byte loads of both halves and of cos/sin, 8- or 16-byte stores. Same arithmetic as rope_append_kernel.
+template <class T>
+__device__ __forceinline__ void store4(T* dst, float a, float b, float c, float d);
+template <>
+__device__ __forceinline__ void store4<float>(float* dst, float a, float b, float c, float d) {
+  *reinterpret_cast<float4*>(dst) = make_float4(a, b, c, d);
+}
+template <>
+__device__ __forceinline__ void store4<bf16>(bf16* dst, float a, float b, float c, float d) {
+  __nv_bfloat162 lo = __floats2bfloat162_rn(a, b), hi = __floats2bfloat162_rn(c, d);
+  uint2 packed;
+  packed.x = *reinterpret_cast<uint32_t*>(&lo);
+  packed.y = *reinterpret_cast<uint32_t*>(&hi);
+  *reinterpret_cast<uint2*>(dst) = packed;
+}
+
+template <class TQ, class TKV>
+__global__ void rope_append_vec_kernel(RopeAppendParams p) {
+  sb::grid_launch_dependents();
+  sb::grid_dependency_wait();
+  const int row = blockIdx.x;
+  const int D = p.D, half = D / 2, quads = half / 4;
+  const int heads = p.Hq + 2 * p.Hkv;
+  const int item = blockIdx.y * blockDim.x + threadIdx.x;
+  if (item >= heads * quads) return;
+  const int pos = p.positions[row];
+  const int slot = p.slots[row];
+  const int head = item / quads, j = (item % quads) * 4;
+  const bool is_v = head >= p.Hq + p.Hkv;
+  int page = 0;
+  if (p.write_kv && head >= p.Hq) page = p.block_table[static_cast<int64_t>(slot) * p.max_pages + pos / p.page_size];
+  const float* src = p.qkv + static_cast<int64_t>(row) * heads * D + static_cast<int64_t>(head) * D;
+  float4 a = *reinterpret_cast<const float4*>(src + j), b = *reinterpret_cast<const float4*>(src + half + j);
+  for (int s = 1; s < p.n_partials; ++s) {
+    a = add4(a, *reinterpret_cast<const float4*>(src + s * p.partial_stride + j));
+    b = add4(b, *reinterpret_cast<const float4*>(src + s * p.partial_stride + half + j));
+  }
+  if (!is_v) {
+    const float4* cs = reinterpret_cast<const float4*>(p.cos_sin + (static_cast<int64_t>(pos) * half + j) * 2);
+    const float4 c01 = cs[0], c23 = cs[1];   // (cos, sin) of pairs j, j+1 and j+2, j+3
+    const float ax = a.x, ay = a.y, az = a.z, aw = a.w;
+    a.x = __fsub_rn(__fmul_rn(ax, c01.x), __fmul_rn(b.x, c01.y));
+    b.x = __fadd_rn(__fmul_rn(b.x, c01.x), __fmul_rn(ax, c01.y));
+    a.y = __fsub_rn(__fmul_rn(ay, c01.z), __fmul_rn(b.y, c01.w));
+    b.y = __fadd_rn(__fmul_rn(b.y, c01.z), __fmul_rn(ay, c01.w));
+    a.z = __fsub_rn(__fmul_rn(az, c23.x), __fmul_rn(b.z, c23.y));
+    b.z = __fadd_rn(__fmul_rn(b.z, c23.x), __fmul_rn(az, c23.y));
+    a.w = __fsub_rn(__fmul_rn(aw, c23.z), __fmul_rn(b.w, c23.w));
+    b.w = __fadd_rn(__fmul_rn(b.w, c23.z), __fmul_rn(aw, c23.w));
+  }
+  if (head < p.Hq) {
+    TQ* q = static_cast<TQ*>(p.q_out) + static_cast<int64_t>(row) * p.Hq * D + static_cast<int64_t>(head) * D;
+    store4<TQ>(q + j, a.x, a.y, a.z, a.w);
+    store4<TQ>(q + half + j, b.x, b.y, b.z, b.w);
+  } else if (p.write_kv) {
+    const int kvh = is_v ? head - p.Hq - p.Hkv : head - p.Hq;
+    TKV* dst = static_cast<TKV*>(p.k_base) + static_cast<int64_t>(page) * p.page_stride +
+               static_cast<int64_t>(pos % p.page_size) * D + static_cast<int64_t>(kvh) * p.head_stride + (is_v ? p.v_offset : 0);
+    store4<TKV>(dst + j, a.x, a.y, a.z, a.w);
+    store4<TKV>(dst + half + j, b.x, b.y, b.z, b.w);
+  }
+}
+
 // ------------------------------------------------------------------ swiglu
 template <class TO>
 __global__ void swiglu_kernel(const float* __restrict__ gate_up, TO* __restrict__ out, int n, int I) {
@@ -222,6 +332,17 @@ SB_EXPORT int sb_rmsnorm(float* h, const float* partials, int n_partials, int64_
   const size_t smem = static_cast<size_t>(H) * sizeof(float);
   if (smem > 200 * 1024) return sb::fail("sb_rmsnorm: width %d does not fit the row buffer (max 51200)", H);
   const bool vec = H % 4 == 0 && partial_stride % 4 == 0 && ((reinterpret_cast<uintptr_t>(h) | reinterpret_cast<uintptr_t>(partials)) & 15) == 0;
+  if (vec && n > 64 && (reinterpret_cast<uintptr_t>(out) & 15) == 0) {
+    // Note: the block sums of rmsnorm_kernel and the warp sums here add the squares in different orders; a row's
+    // normed values can differ in the last bit between a decode-sized and a prompt-sized step.
+    const dim3 grid((n + 7) / 8);
+    if (weight_dtype == 0 && out_dtype == 0) sb::launch_pdl(rmsnorm_rows_kernel<float, float>, grid, dim3(256), 0, stream, h, partials, n_partials, partial_stride, static_cast<const float*>(weight), static_cast<float*>(out), n, H, eps);
+    else if (weight_dtype == 0 && out_dtype == 1) sb::launch_pdl(rmsnorm_rows_kernel<float, bf16>, grid, dim3(256), 0, stream, h, partials, n_partials, partial_stride, static_cast<const float*>(weight), static_cast<bf16*>(out), n, H, eps);
+    else if (weight_dtype == 1 && out_dtype == 0) sb::launch_pdl(rmsnorm_rows_kernel<bf16, float>, grid, dim3(256), 0, stream, h, partials, n_partials, partial_stride, static_cast<const bf16*>(weight), static_cast<float*>(out), n, H, eps);
+    else if (weight_dtype == 1 && out_dtype == 1) sb::launch_pdl(rmsnorm_rows_kernel<bf16, bf16>, grid, dim3(256), 0, stream, h, partials, n_partials, partial_stride, static_cast<const bf16*>(weight), static_cast<bf16*>(out), n, H, eps);
+    else return sb::fail("sb_rmsnorm: unsupported dtypes weight=%d out=%d", weight_dtype, out_dtype);
+    return sb::check_launch("sb_rmsnorm");
+  }
   const int units = vec ? H / 4 : H;
   const int threads = units >= 1024 ? 1024 : units >= 512 ? 512 : units >= 256 ? 256 : 128;
 #define SB_NORM_V(TW, TO, VEC)                                                                                   \
@@ -258,6 +379,18 @@ SB_EXPORT int sb_rope_append(const float* qkv, int n_partials, int64_t partial_s
   RopeAppendParams p{qkv, n_partials, partial_stride, positions, slots, cos_sin, rotary_dim, q_out, k_base,
                      block_table, max_pages, page_size, page_stride, v_offset, head_stride, Hq, Hkv, D, write_kv};
   const int threads = 128;
+  const bool aligned = ((reinterpret_cast<uintptr_t>(qkv) | reinterpret_cast<uintptr_t>(q_out) | reinterpret_cast<uintptr_t>(k_base) |
+                         reinterpret_cast<uintptr_t>(cos_sin)) & 15) == 0;
+  if (rotary_dim == D && D % 8 == 0 && aligned && partial_stride % 4 == 0 && page_stride % 8 == 0 && v_offset % 8 == 0 &&
+      head_stride % 8 == 0) {
+    const dim3 vgrid(n, ((Hq + 2 * Hkv) * (D / 8) + threads - 1) / threads);
+    if (q_dtype == 0 && kv_dtype == 0) sb::launch_pdl(rope_append_vec_kernel<float, float>, vgrid, threads, 0, stream, p);
+    else if (q_dtype == 1 && kv_dtype == 1) sb::launch_pdl(rope_append_vec_kernel<bf16, bf16>, vgrid, threads, 0, stream, p);
+    else if (q_dtype == 0 && kv_dtype == 1) sb::launch_pdl(rope_append_vec_kernel<float, bf16>, vgrid, threads, 0, stream, p);
+    else if (q_dtype == 1 && kv_dtype == 0) sb::launch_pdl(rope_append_vec_kernel<bf16, float>, vgrid, threads, 0, stream, p);
+    else return sb::fail("sb_rope_append: unsupported dtypes q=%d kv=%d", q_dtype, kv_dtype);
+    return sb::check_launch("sb_rope_append");
+  }
   const dim3 grid(n, ((Hq + 2 * Hkv) * (D / 2) + threads - 1) / threads);
   if (q_dtype == 0 && kv_dtype == 0) sb::launch_pdl(rope_append_kernel<float, float>, grid, threads, 0, stream, p);
   else if (q_dtype == 1 && kv_dtype == 1) sb::launch_pdl(rope_append_kernel<bf16, bf16>, grid, threads, 0, stream, p);

@@ -202,7 +202,7 @@ def test_attention_generic_float32(D, Hq, Hkv, page, window):
 
 
 # ---------------------------------------------------------------------------- the small kernels
-@pytest.mark.parametrize("n,H", [(1, 64), (7, 88), (33, 2048), (4, 5000)])
+@pytest.mark.parametrize("n,H", [(1, 64), (7, 88), (33, 2048), (4, 5000), (130, 264), (300, 2048), (77, 90)])
 def test_rmsnorm_with_partials(n, H):
     from stride_b200.kernels import ops
     h = _rand(n, H, seed=1)
@@ -253,10 +253,12 @@ def test_gemm_f32(n, M, K, wdtype):
     assert (acc.double() - (base.double() + ref)).abs().max() <= 2e-6 * float(ref.abs().max()) * math.sqrt(K)
 
 
-def test_rope_append_partial_rotation_and_pages():
-    """Rotation of the first rotary_dim elements only, q stored, k and v appended at (slot, pos) through the table."""
+@pytest.mark.parametrize("Hq,Hkv,D,rot", [(3, 1, 24, 16), (5, 2, 32, 32), (2, 1, 72, 72)])
+def test_rope_append_partial_rotation_and_pages(Hq, Hkv, D, rot):
+    """Rotation of the first rotary_dim elements only (or of the whole head, the vectorised kernel), q stored, k and v
+    appended at (slot, pos) through the table."""
     from stride_b200.kernels import ops
-    Hq, Hkv, D, rot, page, n = 3, 1, 24, 16, 4, 6
+    page, n = 4, 6
     qkv = _rand(2, n, (Hq + 2 * Hkv) * D, seed=1)
     pos = torch.tensor([0, 1, 2, 9, 10, 5], dtype=torch.int32, device=DEV)
     slots = torch.tensor([1, 1, 1, 0, 0, 2], dtype=torch.int32, device=DEV)
