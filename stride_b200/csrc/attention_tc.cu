@@ -92,7 +92,14 @@ __device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) {
 template <int D>
 __device__ __forceinline__ void load_kv_tiles(bf16* dstK, bf16* dstV, const bf16* kplane, int64_t v_offset,
                                               const int32_t* table, int page_size, int page_shift, int64_t page_stride,
-                                              int key0, int key_lo, int key_hi, int tid, int threads) {
+                                              int key0, int key_lo, int key_hi, int tid, int threads,
+                                              int zero_lo = 0, int zero_hi = -1) {
+  // keys in [key_lo, key_hi] are copied; keys outside [zero_lo, zero_hi] (by default: outside the copied range) are
+  // zero-filled; keys in between are left for a later call
+  if (zero_hi < zero_lo) {
+    zero_lo = key_lo;
+    zero_hi = key_hi;
+  }
   constexpr int LD = D + 8, CH = D / 8;
   const int c = tid % CH;
   for (int i = tid / CH; i < kKeys; i += threads / CH) {
@@ -105,7 +112,7 @@ __device__ __forceinline__ void load_kv_tiles(bf16* dstK, bf16* dstV, const bf16
       const bf16* src = kplane + static_cast<int64_t>(table[pi]) * page_stride + in_page * D + c * 8;
       cp_async16(smem_u32(dk), src);
       cp_async16(smem_u32(dv), src + v_offset);
-    } else {
+    } else if (key < zero_lo || key > zero_hi) {
       *reinterpret_cast<uint4*>(dk) = make_uint4(0, 0, 0, 0);
       *reinterpret_cast<uint4*>(dv) = make_uint4(0, 0, 0, 0);
     }
@@ -302,7 +309,6 @@ __global__ void __launch_bounds__(128) attn_decode_kernel(const AttnTcParams p) 
   __shared__ int is_last_s;
 
   sb::grid_launch_dependents();
-  sb::grid_dependency_wait();
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31, gid = lane >> 2, tq = lane & 3;
   const int item = blockIdx.x, g = blockIdx.y, chunk = blockIdx.z;
   const int G = p.Hq / p.Hkv;
@@ -311,11 +317,23 @@ __global__ void __launch_bounds__(128) attn_decode_kernel(const AttnTcParams p) 
             first_pos = p.meta[3 * p.meta_stride + e];
   const int pos_hi = first_pos + L - 1;
   const int key_lo = p.window > 0 ? max(0, first_pos - p.window + 1) : 0;
-  if (chunk * kChunk > pos_hi || chunk * kChunk + kChunk - 1 < key_lo) return;   // no key of this chunk is visible
+  if (chunk * kChunk > pos_hi || chunk * kChunk + kChunk - 1 < key_lo) {   // no key of this chunk is visible
+    sb::grid_dependency_wait();
+    return;
+  }
   const int32_t* table = p.block_table + static_cast<int64_t>(slot) * p.max_pages;
   const bf16* kplane = p.k_base + static_cast<int64_t>(g) * p.head_stride;
   const int rows = L * G;
 
+  bf16* sK = sKV + warp * 2 * 64 * LD;
+  bf16* sV = sK + 64 * LD;
+  const int key0 = chunk * kChunk + warp * kKeys;
+  const bool any = key0 <= pos_hi && key0 + kKeys - 1 >= key_lo;
+  // Keys before this step's first position were written by earlier steps: their tiles are requested before
+  // waiting for the kernels in front (which write this step's keys and the queries).
+  if (any) load_kv_tiles<D>(sK, sV, kplane, p.v_offset, table, p.page_size, p.page_shift, p.page_stride, key0, key_lo, first_pos - 1,
+                            lane, 32, key_lo, pos_hi);
+  sb::grid_dependency_wait();
   for (int idx = tid; idx < 16 * CH; idx += 128) {
     const int r = idx / CH, c = idx % CH;
     bf16* d = sQ + r * LD + c * 8;
@@ -324,13 +342,9 @@ __global__ void __launch_bounds__(128) attn_decode_kernel(const AttnTcParams p) 
     else
       *reinterpret_cast<uint4*>(d) = make_uint4(0, 0, 0, 0);
   }
-  bf16* sK = sKV + warp * 2 * 64 * LD;
-  bf16* sV = sK + 64 * LD;
-  const int key0 = chunk * kChunk + warp * kKeys;
-  const bool any = key0 <= pos_hi && key0 + kKeys - 1 >= key_lo;
-  if (any) {
-    load_kv_tiles<D>(sK, sV, kplane, p.v_offset, table, p.page_size, p.page_shift, p.page_stride, key0, key_lo, pos_hi, lane, 32);
-  }
+  if (any && key0 + kKeys - 1 >= first_pos)
+    load_kv_tiles<D>(sK, sV, kplane, p.v_offset, table, p.page_size, p.page_shift, p.page_stride, key0, max(first_pos, key_lo), pos_hi,
+                     lane, 32, key_lo, pos_hi);
   cp_commit();
   cp_wait<0>();
   __syncthreads();

@@ -53,10 +53,16 @@ __global__ void rmsnorm_kernel(float* __restrict__ h, const float* __restrict__ 
   extern __shared__ __align__(16) float row[];
   __shared__ float red[32];
   sb::grid_launch_dependents();
-  sb::grid_dependency_wait();
   const int r = blockIdx.x;
-  V* hr = reinterpret_cast<V*>(h + static_cast<int64_t>(r) * H);
   const int units = H / VEC;
+  // The gain does not depend on the kernels before this one: fetch this thread's first piece of it before waiting.
+  float w_first[VEC];
+  if (threadIdx.x < units) {
+#pragma unroll
+    for (int e = 0; e < VEC; ++e) w_first[e] = sb::widen(weight[threadIdx.x * VEC + e]);
+  }
+  sb::grid_dependency_wait();
+  V* hr = reinterpret_cast<V*>(h + static_cast<int64_t>(r) * H);
   float ss = 0.0f;
   for (int i = threadIdx.x; i < units; i += blockDim.x) {
     V v = hr[i];
@@ -82,7 +88,13 @@ __global__ void rmsnorm_kernel(float* __restrict__ h, const float* __restrict__ 
   const float total = sb::block_sum(ss, red);
   const float scale = 1.0f / sqrtf(total / static_cast<float>(H) + eps);
   TO* o = out + static_cast<int64_t>(r) * H;
-  for (int i = threadIdx.x; i < H; i += blockDim.x) o[i] = sb::narrow<TO>(sb::widen(weight[i]) * (row[i] * scale));
+  for (int i = threadIdx.x; i < units; i += blockDim.x) {
+#pragma unroll
+    for (int e = 0; e < VEC; ++e) {
+      const float w = i == static_cast<int>(threadIdx.x) ? w_first[e] : sb::widen(weight[i * VEC + e]);
+      o[i * VEC + e] = sb::narrow<TO>(w * (row[i * VEC + e] * scale));
+    }
+  }
 }
 
 // Many rows (a prompt portion): one warp per row, eight rows per block, no shared memory and no block barrier.
@@ -156,7 +168,6 @@ struct RopeAppendParams {
 template <class TQ, class TKV>
 __global__ void rope_append_kernel(RopeAppendParams p) {
   sb::grid_launch_dependents();
-  sb::grid_dependency_wait();
   const int row = blockIdx.x;
   const int D = p.D, half = D / 2, rh = p.rotary_dim / 2;
   const int heads = p.Hq + 2 * p.Hkv;
@@ -184,6 +195,8 @@ __global__ void rope_append_kernel(RopeAppendParams p) {
   }
   int page = 0;
   if (p.write_kv && head >= p.Hq) page = p.block_table[static_cast<int64_t>(slot) * p.max_pages + pos / p.page_size];
+  // positions, slots, the block table and the cos/sin table are inputs of the step; only qkv comes from the kernel before
+  sb::grid_dependency_wait();
   const float* src = p.qkv + static_cast<int64_t>(row) * width + static_cast<int64_t>(head) * D;
   float a = src[d0], b = src[d1];
   int s = 1;
@@ -238,18 +251,27 @@ __device__ __forceinline__ void store4<bf16>(bf16* dst, float a, float b, float 
 template <class TQ, class TKV>
 __global__ void rope_append_vec_kernel(RopeAppendParams p) {
   sb::grid_launch_dependents();
-  sb::grid_dependency_wait();
   const int row = blockIdx.x;
   const int D = p.D, half = D / 2, quads = half / 4;
   const int heads = p.Hq + 2 * p.Hkv;
   const int item = blockIdx.y * blockDim.x + threadIdx.x;
-  if (item >= heads * quads) return;
+  if (item >= heads * quads) {
+    sb::grid_dependency_wait();
+    return;
+  }
   const int pos = p.positions[row];
   const int slot = p.slots[row];
   const int head = item / quads, j = (item % quads) * 4;
   const bool is_v = head >= p.Hq + p.Hkv;
   int page = 0;
   if (p.write_kv && head >= p.Hq) page = p.block_table[static_cast<int64_t>(slot) * p.max_pages + pos / p.page_size];
+  float4 c01 = make_float4(1.0f, 0.0f, 1.0f, 0.0f), c23 = c01;   // (cos, sin) of pairs j, j+1 and j+2, j+3
+  if (!is_v) {
+    const float4* cs = reinterpret_cast<const float4*>(p.cos_sin + (static_cast<int64_t>(pos) * half + j) * 2);
+    c01 = cs[0];
+    c23 = cs[1];
+  }
+  sb::grid_dependency_wait();   // everything above is an input of the step; qkv comes from the kernel before
   const float* src = p.qkv + static_cast<int64_t>(row) * heads * D + static_cast<int64_t>(head) * D;
   float4 a = *reinterpret_cast<const float4*>(src + j), b = *reinterpret_cast<const float4*>(src + half + j);
   for (int s = 1; s < p.n_partials; ++s) {
@@ -257,8 +279,6 @@ __global__ void rope_append_vec_kernel(RopeAppendParams p) {
     b = add4(b, *reinterpret_cast<const float4*>(src + s * p.partial_stride + half + j));
   }
   if (!is_v) {
-    const float4* cs = reinterpret_cast<const float4*>(p.cos_sin + (static_cast<int64_t>(pos) * half + j) * 2);
-    const float4 c01 = cs[0], c23 = cs[1];   // (cos, sin) of pairs j, j+1 and j+2, j+3
     const float ax = a.x, ay = a.y, az = a.z, aw = a.w;
     a.x = __fsub_rn(__fmul_rn(ax, c01.x), __fmul_rn(b.x, c01.y));
     b.x = __fadd_rn(__fmul_rn(b.x, c01.x), __fmul_rn(ax, c01.y));

@@ -87,6 +87,9 @@ __device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap* map
       "l"(reinterpret_cast<uint64_t>(map)), "r"(bar), "r"(x), "r"(y)
       : "memory");
 }
+__device__ __forceinline__ void prefetch_tensormap(const CUtensorMap* map) {
+  asm volatile("prefetch.tensormap [%0];" ::"l"(reinterpret_cast<uint64_t>(map)) : "memory");
+}
 __device__ __forceinline__ void tmem_alloc(uint32_t dst_smem, uint32_t cols) {
   asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(dst_smem), "r"(cols) : "memory");
   asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
@@ -205,6 +208,8 @@ gemm_tc_single_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_co
   const uint32_t tmem_cols = BN < 32 ? 32 : BN;
 
   if (threadIdx.x == 0) {
+    prefetch_tensormap(&map_w);
+    prefetch_tensormap(&map_x);
     for (int s = 0; s < p.stages; ++s) {
       mbar_init(smem_u32(&full_bar[s]), 1);
       mbar_init(smem_u32(&empty_bar[s]), 1);
@@ -345,6 +350,8 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
   const uint32_t tmem_cols = (MULTI ? 2 : 1) * BN < 32 ? 32 : (MULTI ? 2 : 1) * BN;   // MULTI: one accumulator fills while the other drains
 
   if (threadIdx.x == 0) {
+    prefetch_tensormap(&map_w);
+    prefetch_tensormap(&map_x);
     for (int s = 0; s < p.stages; ++s) {
       mbar_init(smem_u32(&full_bar[s]), 1);
       mbar_init(smem_u32(&empty_bar[s]), 1);
