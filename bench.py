@@ -184,12 +184,11 @@ def main() -> int:
         for p in prompts:
             sched.submit(GenRequest(prompt=p, max_new_tokens=warmup + steps + 4))
         while sched.stats.generated < batch * warmup:
-            sched.step()
+            sched.run(steps=1)
         torch.cuda.synchronize()
         t0 = time.perf_counter()
         g0 = sched.stats.generated
-        for _ in range(steps):
-            sched.step()
+        sched.run(steps=steps)          # every step: pinned H2D of its inputs, D2H of its sampled tokens
         torch.cuda.synchronize()
         dt = time.perf_counter() - t0
         made = sched.stats.generated - g0

@@ -45,6 +45,7 @@ class CacheGroup:
     entries: list = field(default_factory=list)      # schedule entries served, in order
     arena: Optional[torch.Tensor] = None             # [pages, len(entries), 2, kv_heads, page_size, head_dim]
     table_host: Optional[np.ndarray] = None          # [slots, max_pages] int32, NO_PAGE where nothing is held
+    table_pinned: Optional[torch.Tensor] = None      # the tensor behind table_host (pinned when the arena is on a GPU)
     table_device: Optional[torch.Tensor] = None
     free: list = field(default_factory=list)
     held: list = field(default_factory=list)         # per slot: {page index in the sequence: page id}
@@ -130,9 +131,11 @@ class CacheManager:
         for g in self.groups:
             g.num_pages = num_pages
             g.arena = torch.zeros((num_pages + 1, len(g.entries), 2, g.kv_heads, page_size, g.head_dim), dtype=g.dtype, device=self.device)
-            g.table_host = np.full((max_slots + 1, self.max_pages_per_seq), NO_PAGE, dtype=np.int32)
+            pin = self.device.type == "cuda"
+            g.table_pinned = torch.full((max_slots + 1, self.max_pages_per_seq), NO_PAGE, dtype=torch.int32, pin_memory=pin)
+            g.table_host = g.table_pinned.numpy()        # a view: host edits go straight into the pinned copy
             g.table_host[self.pad_slot, 0] = num_pages
-            g.table_device = torch.from_numpy(g.table_host).to(self.device)
+            g.table_device = g.table_pinned.to(self.device)
             g.free = list(range(num_pages - 1, -1, -1))     # page 0 is handed out first
             if self._rng:
                 self._rng.shuffle(g.free)
@@ -206,11 +209,12 @@ class CacheManager:
         self.length[slot] = max(self.length[slot], end)
         return True
 
-    def trim(self, slot: int) -> int:
-        """Give back the pages of windowed groups that no later token of the slot can see.
-        Call after the step that processed the slot's tokens up to `length`. Returns pages freed."""
+    def trim(self, slot: int, length: Optional[int] = None) -> int:
+        """Give back the pages of windowed groups that no token of the slot at position `length` or later can
+        see (`length` defaults to all tokens the slot has pages for). Call it once the steps that processed the
+        tokens before `length` have finished on the GPU. Returns pages freed."""
         freed = 0
-        n = self.length[slot]
+        n = self.length[slot] if length is None else min(length, self.length[slot])
         for gi, g in enumerate(self.groups):
             if g.window <= 0:
                 continue
@@ -228,7 +232,9 @@ class CacheManager:
         """Upload the block-table rows that changed since the last call."""
         for gi, slot in sorted(self._dirty):
             g = self.groups[gi]
-            g.table_device[slot].copy_(torch.from_numpy(g.table_host[slot]), non_blocking=False)
+            # From pinned memory and without waiting: a row that changes again before the copy runs only delivers
+            # the later content early, which adds pages that no token of an earlier step looks at.
+            g.table_device[slot].copy_(g.table_pinned[slot], non_blocking=True)
         self._dirty.clear()
 
     # ------------------------------------------------------------------ views

@@ -17,13 +17,18 @@ namespace {
 using bf16 = __nv_bfloat16;
 
 // ------------------------------------------------------------------ embedding
+// A token id of -1 stands for "the token last sampled for this row's request": it is read from
+// sampled[slots[row]], which the sampling kernels of the step before wrote, so a decode step can be launched
+// before the host has seen its input token.
 template <class TW>
 __global__ void embed_kernel(const int32_t* __restrict__ tokens, const TW* __restrict__ table,
-                             float* __restrict__ out, int H, int vocab) {
+                             float* __restrict__ out, int H, int vocab, const int32_t* __restrict__ slots,
+                             const int32_t* __restrict__ sampled) {
   sb::grid_launch_dependents();
   sb::grid_dependency_wait();
   const int row = blockIdx.x;
-  const int tok = tokens[row];
+  int tok = tokens[row];
+  if (tok == -1 && sampled != nullptr) tok = sampled[slots[row]];
   const bool ok = tok >= 0 && tok < vocab;
   const TW* src = table + static_cast<int64_t>(ok ? tok : 0) * H;
   float* dst = out + static_cast<int64_t>(row) * H;
@@ -335,12 +340,12 @@ __global__ void gather_rows_kernel(const float* __restrict__ in, const float* __
 // dtype codes shared with the Python side: 0 = float32, 1 = bfloat16.
 
 SB_EXPORT int sb_embed(const int32_t* tokens, const void* table, int table_dtype, float* out, int n, int H, int vocab,
-                       cudaStream_t stream) {
+                       const int32_t* slots, const int32_t* sampled, cudaStream_t stream) {
   if (n <= 0) return 0;
   if (table_dtype == 0)
-    sb::launch_pdl(embed_kernel<float>, n, 256, 0, stream, tokens, static_cast<const float*>(table), out, H, vocab);
+    sb::launch_pdl(embed_kernel<float>, n, 256, 0, stream, tokens, static_cast<const float*>(table), out, H, vocab, slots, sampled);
   else if (table_dtype == 1)
-    sb::launch_pdl(embed_kernel<bf16>, n, 256, 0, stream, tokens, static_cast<const bf16*>(table), out, H, vocab);
+    sb::launch_pdl(embed_kernel<bf16>, n, 256, 0, stream, tokens, static_cast<const bf16*>(table), out, H, vocab, slots, sampled);
   else
     return sb::fail("sb_embed: unsupported table dtype %d", table_dtype);
   return sb::check_launch("sb_embed");

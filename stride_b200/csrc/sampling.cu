@@ -37,8 +37,12 @@ __device__ __forceinline__ unsigned long long pack_best(float v, int idx) {
   return (static_cast<unsigned long long>(order_key(v)) << 32) | (0xFFFFFFFFu - static_cast<uint32_t>(idx));
 }
 
+// `scatter` (optional): the chosen token is also stored at scatter[scatter_index[row]] (the request's slot), where
+// the next step's embedding looks for it.
 __global__ void __launch_bounds__(kThreads) argmax_kernel(const float* __restrict__ logits, int64_t ld, int vocab,
-                                                           int32_t* __restrict__ tokens, float* __restrict__ values) {
+                                                           int32_t* __restrict__ tokens, float* __restrict__ values,
+                                                           const int32_t* __restrict__ scatter_index,
+                                                           int32_t* __restrict__ scatter) {
   __shared__ unsigned long long best_s[32];
   sb::grid_launch_dependents();
   sb::grid_dependency_wait();
@@ -62,13 +66,14 @@ __global__ void __launch_bounds__(kThreads) argmax_kernel(const float* __restric
     const int idx = best == 0 ? 0 : static_cast<int>(0xFFFFFFFFu - static_cast<uint32_t>(best & 0xFFFFFFFFu));
     tokens[blockIdx.x] = idx;
     values[blockIdx.x] = l[idx];
+    if (scatter != nullptr) scatter[scatter_index[blockIdx.x]] = idx;
   }
 }
 
 __global__ void __launch_bounds__(kThreads) sample_temperature_kernel(
     const float* __restrict__ logits, int64_t ld, int vocab, const float* __restrict__ temperatures,
     const unsigned long long* __restrict__ seeds, const int32_t* __restrict__ lengths, int32_t* __restrict__ tokens,
-    float* __restrict__ values) {
+    float* __restrict__ values, const int32_t* __restrict__ scatter_index, int32_t* __restrict__ scatter) {
   __shared__ double hist[256];
   __shared__ int count[256];
   __shared__ float red[32];
@@ -80,6 +85,7 @@ __global__ void __launch_bounds__(kThreads) sample_temperature_kernel(
   sb::grid_dependency_wait();
   const int row = blockIdx.x, t = threadIdx.x;
   const float* l = logits + static_cast<int64_t>(row) * ld;
+  if (!(temperatures[row] > 0.0f)) return;     // a greedy row: the argmax kernel has chosen its token
   const double T = static_cast<double>(temperatures[row]);
 
   float mx = -INFINITY;
@@ -159,6 +165,7 @@ __global__ void __launch_bounds__(kThreads) sample_temperature_kernel(
       if (v == v && order_key(v) == key) {
         tokens[row] = i;
         values[row] = v;
+        if (scatter != nullptr) scatter[scatter_index[row]] = i;
       }
     }
   } else if (t == 0) {
@@ -176,24 +183,26 @@ __global__ void __launch_bounds__(kThreads) sample_temperature_kernel(
     }
     tokens[row] = pick;
     values[row] = l[pick];
+    if (scatter != nullptr) scatter[scatter_index[row]] = pick;
   }
 }
 
 }  // namespace
 
 SB_EXPORT int sb_argmax(const float* logits, int64_t ld, int rows, int vocab, int32_t* tokens, float* values,
-                        cudaStream_t stream) {
+                        const int32_t* scatter_index, int32_t* scatter, cudaStream_t stream) {
   if (rows <= 0) return 0;
   if (vocab <= 0) return sb::fail("sb_argmax: empty vocabulary");
-  sb::launch_pdl(argmax_kernel, dim3(rows), dim3(kThreads), 0, stream, logits, ld, vocab, tokens, values);
+  sb::launch_pdl(argmax_kernel, dim3(rows), dim3(kThreads), 0, stream, logits, ld, vocab, tokens, values, scatter_index, scatter);
   return sb::check_launch("sb_argmax");
 }
 
 SB_EXPORT int sb_sample_temperature(const float* logits, int64_t ld, int rows, int vocab, const float* temperatures,
                                     const unsigned long long* seeds, const int32_t* lengths, int32_t* tokens,
-                                    float* values, cudaStream_t stream) {
+                                    float* values, const int32_t* scatter_index, int32_t* scatter, cudaStream_t stream) {
   if (rows <= 0) return 0;
   if (vocab <= 0) return sb::fail("sb_sample_temperature: empty vocabulary");
-  sb::launch_pdl(sample_temperature_kernel, dim3(rows), dim3(kThreads), 0, stream, logits, ld, vocab, temperatures, seeds, lengths, tokens, values);
+  sb::launch_pdl(sample_temperature_kernel, dim3(rows), dim3(kThreads), 0, stream, logits, ld, vocab, temperatures, seeds, lengths, tokens, values, scatter_index,
+                 scatter);
   return sb::check_launch("sb_sample_temperature");
 }

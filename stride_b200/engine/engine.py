@@ -103,8 +103,8 @@ class Engine:
         self.caches = [self.cache.layer_cache(i) for i in range(len(self.spec.schedule))]
         self.workspace = Workspace(self.device, o.max_rows)
         # One pinned staging buffer and one device buffer for all integer inputs of a step:
-        # tokens, positions, slots, logit rows (max_rows each) and entry records (4 x max_rows).
-        self._ints = 8 * o.max_rows
+        # tokens, positions, slots, logit rows (max_rows each), entry records (4 x max_rows), and the slot of every logit row.
+        self._ints = 9 * o.max_rows
         self._staging = torch.empty(self._ints, dtype=torch.int32, pin_memory=True)
         self._staging_np = self._staging.numpy()
         self._device_ints = torch.zeros(self._ints, dtype=torch.int32, device=self.device)
@@ -118,6 +118,10 @@ class Engine:
         self._aux_used = 0
         self._aux_copied = torch.cuda.Event()
         self._aux_pending = False
+        # Each request's last sampled token, written by the sampling kernels: a step may name a token as -1 and the
+        # embedding then reads it from here, so the step can be queued before the host has seen the token.
+        self.sampled = torch.zeros(o.max_slots + 1, dtype=torch.int32, device=self.device)
+        self.logit_slots = None        # device view: the slot of every logit row of the last step
         self.steps = 0
         self.graph_replays = 0
         self._graphs: dict = {}
@@ -189,7 +193,7 @@ class Engine:
                 raise EngineError(f"slot {e.slot}: tokens {e.first_pos}..{e.first_pos + L - 1} have no pages "
                                   f"(ensured up to {self.cache.length[e.slot]})")
             t = np.asarray(e.tokens, dtype=np.int64)
-            if t.min() < 0 or t.max() >= vocab:
+            if (t.min() < 0 and not (L == 1 and t[0] == -1)) or t.max() >= vocab:
                 raise EngineError(f"token id out of range 0..{vocab - 1} in the entry of slot {e.slot}")
             tok[at:at + L] = t
             pos[at:at + L] = np.arange(e.first_pos, e.first_pos + L)
@@ -198,6 +202,7 @@ class Engine:
                 if not 0 <= j < L:
                     raise EngineError(f"wanted place {j} is outside the entry's {L} tokens")
                 rows[w] = at + j
+                buf[8 * R + w] = e.slot
                 w += 1
             meta[0, i], meta[1, i], meta[2, i], meta[3, i] = e.slot, at, L, e.first_pos
             at += L
@@ -212,8 +217,9 @@ class Engine:
             compute_dtype=self.compute_dtype,
             entry_slots=[e.slot for e in entries], entry_first_row=[int(x) for x in meta[1, :E]],
             entry_length=[len(e.tokens) for e in entries], entry_first_pos=[e.first_pos for e in entries],
-            entry_meta=d[4 * R:8 * R].view(4, R)[:, :E], upload_ints=self._upload_ints)
+            entry_meta=d[4 * R:8 * R].view(4, R)[:, :E], upload_ints=self._upload_ints, sampled=self.sampled)
         logits = self.model.forward(ctx, self.caches, d[3 * R:3 * R + count], count)
+        self.logit_slots = d[8 * R:8 * R + count]
         self.steps += 1
         return logits
 
@@ -251,12 +257,12 @@ class Engine:
             if e.first_pos < 0 or e.first_pos + 1 > self.cache.length[e.slot]:
                 raise EngineError(f"slot {e.slot}: token {e.first_pos} has no page (ensured up to {self.cache.length[e.slot]})")
             t = int(e.tokens[0])
-            if not 0 <= t < vocab:
+            if not -1 <= t < vocab:
                 raise EngineError(f"token id {t} out of range 0..{vocab - 1}")
-            buf[i], buf[R + i], buf[2 * R + i] = t, e.first_pos, e.slot
+            buf[i], buf[R + i], buf[2 * R + i], buf[8 * R + i] = t, e.first_pos, e.slot, e.slot
             meta[0, i], meta[1, i], meta[2, i], meta[3, i] = e.slot, i, 1, e.first_pos
         for i in range(E, B):
-            buf[i], buf[R + i], buf[2 * R + i] = 0, 0, self._pad_slot
+            buf[i], buf[R + i], buf[2 * R + i], buf[8 * R + i] = 0, 0, self._pad_slot, self._pad_slot
             meta[0, i], meta[1, i], meta[2, i], meta[3, i] = self._pad_slot, i, 1, 0
         buf[3 * R:3 * R + B] = np.arange(B)
         self._device_ints.copy_(self._staging, non_blocking=True)
@@ -275,7 +281,7 @@ class Engine:
                 n=B, token_ids=d[0:B], positions=d[R:R + B], slots=d[2 * R:2 * R + B], workspace=self.workspace,
                 compute_dtype=self.compute_dtype, entry_slots=[0] * B, entry_first_row=list(range(B)),
                 entry_length=[1] * B, entry_first_pos=[0] * B, entry_meta=d[4 * R:8 * R].view(4, R)[:, :B],
-                upload_ints=None, static_keys=keys)
+                upload_ints=None, static_keys=keys, sampled=self.sampled)
             return self.model.forward(ctx, self.caches, d[3 * R:3 * R + B], B)
 
         if graph is None:
@@ -297,6 +303,7 @@ class Engine:
             self.graph_replays += 1
             from ..kernels import ops
             ops.launches += graph[2]
+        self.logit_slots = d[8 * R:8 * R + E]
         self.steps += 1
         return logits[:E]
 

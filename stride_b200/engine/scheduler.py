@@ -85,7 +85,8 @@ class SchedulerStats:
 
 
 class _Seq:
-    __slots__ = ("req", "tokens", "prompt_len", "next_pos", "generated", "slot", "arrival", "fingerprint", "done")
+    __slots__ = ("req", "tokens", "prompt_len", "next_pos", "generated", "slot", "arrival", "fingerprint", "done",
+                 "inflight", "launched", "closing")
 
     def __init__(self, req: GenRequest, arrival: int):
         self.req = req
@@ -97,6 +98,12 @@ class _Seq:
         self.arrival = arrival
         self.fingerprint = _FNV_OFFSET
         self.done = False
+        self.inflight = 0       # pipelined mode: steps launched for this request whose tokens the host has not read yet
+        self.launched = 0       # tokens whose sampling has been launched (>= generated)
+        self.closing = False    # no further step is to be launched for it (it finishes with a token already launched)
+
+
+_DRAIN = object()      # plan(): the steps in flight have to be read back before a decision can be taken
 
 
 class Scheduler:
@@ -184,12 +191,12 @@ class Scheduler:
             plan = []
             budget = self.opts.max_rows
             for s in self._running:
-                if len(s.tokens) - s.next_pos == 1 and budget > 0:
+                if len(s.tokens) - s.next_pos == 1 and budget > 0 and not s.closing:
                     plan.append((s, 1))
                     budget -= 1
             for s in self._running:
                 remaining = len(s.tokens) - s.next_pos
-                if remaining > 1 and budget > 0:
+                if remaining > 1 and budget > 0 and not s.closing:
                     chunk = min(remaining, self.opts.prefill_chunk, budget)
                     plan.append((s, chunk))
                     budget -= chunk
@@ -200,6 +207,8 @@ class Scheduler:
                 for g, k in enumerate(cache.pages_needed(s.slot, s.next_pos + count)):
                     need[g] += k
             if any(n > f for n, f in zip(need, cache.free_pages())):
+                if any(s.inflight for s in self._running):
+                    return _DRAIN       # pages of a request with a step in flight cannot be taken away yet
                 if len(self._running) <= 1:
                     raise EngineError("the cache pool is too small for one sequence")
                 self._preempt_youngest()
@@ -265,6 +274,122 @@ class Scheduler:
         self._running = [s for s in self._running if not s.done]
         return True
 
-    def run(self) -> None:
-        while self.step():
-            pass
+    # ------------------------------------------------------------------ pipelined running
+    def _can_pipeline(self) -> bool:
+        return isinstance(self._sampler, Sampler) and getattr(self.engine, "sampled", None) is not None
+
+    def _launch(self):
+        """Queue one step on the GPU without waiting for its tokens: rows whose input token is not known yet (it is
+        being sampled by the step before) carry -1 and read it on the device. Returns a record for `_collect`, None
+        when there is nothing to run, or _DRAIN when the steps in flight have to be read back first."""
+        cache = self.engine.cache
+        for s in list(self._running):
+            if s.req.cancelled is not None and s.req.cancelled.is_set():
+                if s.inflight:
+                    return _DRAIN
+                cache.release_slot(s.slot)
+                self._running.remove(s)
+        self._admit()
+        plan = self.plan()
+        if plan is None or plan is _DRAIN:
+            return plan
+        entries, wanted, ends = [], [], []
+        for s, count in plan:
+            a = s.next_pos
+            last = a + count == len(s.tokens)
+            entries.append(StepEntry(slot=s.slot, first_pos=a, tokens=s.tokens[a:a + count], want=[count - 1] if last else []))
+            if last:
+                wanted.append(s)
+            s.next_pos += count
+            ends.append((s, s.next_pos))
+        pipelined = all(Sampler.on_device(s.req.sampling) and not s.req.full_logits for s in wanted)
+        logits = self.engine.step(entries)
+        self.stats.steps += 1
+        self.stats.rows += sum(c for _, c in plan)
+        used = max((t - f for t, f in zip(cache.total_pages(), cache.free_pages())), default=0)
+        self.stats.peak_blocks = max(self.stats.peak_blocks, used)
+        ticket, full = None, None
+        if wanted:
+            ticket = self._sampler.launch(logits, [s.req.sampling for s in wanted], [len(s.tokens) for s in wanted],
+                                          self.engine.logit_slots, self.engine.sampled)
+            if any(s.req.full_logits and s.req.on_token for s in wanted):
+                full = logits.to("cpu").numpy()             # synchronises: such a step is not pipelined
+            for s in wanted:
+                s.tokens.append(-1)                          # stands for the token being sampled
+                s.inflight += 1
+                s.launched += 1
+                if s.launched >= s.req.max_new_tokens:
+                    s.closing = True                         # that token is its last ("length")
+        return (wanted, ticket, full, ends, pipelined)
+
+    def _collect(self, record) -> None:
+        """Read back the tokens of a launched step and do the bookkeeping `step()` does after sampling."""
+        wanted, ticket, full, ends, _ = record
+        cache = self.engine.cache
+        if ticket is not None:
+            tokens, values = self._sampler.collect(ticket)
+            for i, s in enumerate(wanted):
+                s.inflight -= 1
+                if s.done:                                   # finished by a stop token a step ago: this row was surplus
+                    if s.inflight == 0 and s.slot >= 0:
+                        self._finish(s)
+                    continue
+                tok, val = int(tokens[i]), float(values[i])
+                s.fingerprint = _fnv_mix(_fnv_mix(s.fingerprint, tok & 0xFFFFFFFF), _float_bits(val))
+                s.tokens[s.prompt_len + s.generated] = tok   # the oldest placeholder
+                s.generated += 1
+                self.stats.generated += 1
+                ev = TokenEvent(token=tok, value=val, index=s.generated - 1, fingerprint=s.fingerprint)
+                if tok in s.req.stop_tokens:
+                    ev.finished, ev.finish_reason = True, "stop"
+                elif s.generated >= s.req.max_new_tokens:
+                    ev.finished, ev.finish_reason = True, "length"
+                if s.req.on_token:
+                    s.req.on_token(ev, full[i] if (full is not None and s.req.full_logits) else None)
+                if ev.finished:
+                    s.done = s.closing = True
+                    if s.inflight == 0:
+                        self._finish(s)                      # else its slot is given back when the surplus step is read
+        windowed = any(g.window > 0 for g in cache.groups)
+        if ticket is None and windowed:
+            import torch
+            torch.cuda.current_stream().synchronize()      # pages are only given back once the step has run
+        if windowed:
+            for s, end in ends:
+                if s.slot >= 0 and not s.done:
+                    cache.trim(s.slot, end)
+        self._running = [s for s in self._running if not (s.done and s.slot < 0)]
+
+    def run(self, steps: Optional[int] = None) -> int:
+        """Run until nothing is queued or running, or for `steps` engine steps. With a GPU engine the next step is
+        queued before the tokens of the current one are read (see `_launch`), so the host's work per step overlaps
+        the GPU's. Returns the number of steps run."""
+        if not self._can_pipeline():
+            n = 0
+            while (steps is None or n < steps) and self.step():
+                n += 1
+            return n
+        n, pending = 0, None
+        while True:
+            launched = None
+            if steps is None or n < steps:
+                launched = self._launch()
+                if launched is _DRAIN:
+                    if pending is None:
+                        raise EngineError("the scheduler asked to drain an empty pipeline")
+                    self._collect(pending)
+                    pending = None
+                    continue
+            if launched is None and pending is None:
+                return n
+            if launched is not None:
+                n += 1
+                if not launched[4]:                          # a step that needs its logits on the host: no overlap
+                    if pending is not None:
+                        self._collect(pending)
+                        pending = None
+                    self._collect(launched)
+                    continue
+            if pending is not None:
+                self._collect(pending)
+            pending = launched

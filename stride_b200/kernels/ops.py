@@ -56,16 +56,23 @@ def _ptr(t) -> int:
     return 0 if t is None else t.data_ptr()
 
 
+_raw_stream = getattr(torch._C, "_cuda_getCurrentRawStream", None)
+
+
 def _stream() -> int:
+    """The current torch stream's handle (kernels are launched on it, so they order with torch's own work)."""
+    if _raw_stream is not None:
+        return _raw_stream(torch.cuda.current_device())
     return torch.cuda.current_stream().cuda_stream
 
 
-def embed(tokens: torch.Tensor, table: torch.Tensor, out: torch.Tensor) -> None:
-    """out[i, :] = float32(table[tokens[i], :])."""
-    _cuda(tokens, table, out)
-    lib, fn = _fn("elementwise", "sb_embed", [c_void_p, c_void_p, c_int, c_void_p, c_int, c_int, c_int, c_void_p])
+def embed(tokens: torch.Tensor, table: torch.Tensor, out: torch.Tensor, slots=None, sampled=None) -> None:
+    """out[i, :] = float32(table[tokens[i], :]); a token of -1 means sampled[slots[i]] (the request's last sampled token)."""
+    _cuda(tokens, table, out, slots, sampled)
+    lib, fn = _fn("elementwise", "sb_embed", [c_void_p, c_void_p, c_int, c_void_p, c_int, c_int, c_int, c_void_p, c_void_p, c_void_p])
     n, H = out.shape
-    _check(lib, fn(_ptr(tokens), _ptr(table), dtype_code(table.dtype), _ptr(out), n, H, table.shape[0], _stream()))
+    _check(lib, fn(_ptr(tokens), _ptr(table), dtype_code(table.dtype), _ptr(out), n, H, table.shape[0], _ptr(slots),
+                   _ptr(sampled) if slots is not None else 0, _stream()))
 
 
 def rmsnorm(h: torch.Tensor, weight: torch.Tensor, eps: float, out: torch.Tensor, partials=None) -> None:
@@ -148,20 +155,24 @@ def attention_generic(q, out, cache_layer, block_table, positions, slots, num_he
                    _ptr(positions), _ptr(slots), q.shape[0], num_heads, num_kv_heads, head_dim, window, scale, _stream()))
 
 
-def argmax(logits: torch.Tensor, tokens: torch.Tensor, values: torch.Tensor) -> None:
-    """tokens[i] = index of the largest logit of row i (smallest index among equals); values[i] = that logit."""
-    _cuda(logits, tokens, values)
-    lib, fn = _fn("sampling", "sb_argmax", [c_void_p, c_int64, c_int, c_int, c_void_p, c_void_p, c_void_p])
-    _check(lib, fn(_ptr(logits), logits.stride(0), logits.shape[0], logits.shape[1], _ptr(tokens), _ptr(values), _stream()))
+def argmax(logits: torch.Tensor, tokens: torch.Tensor, values: torch.Tensor, scatter_index=None, scatter=None) -> None:
+    """tokens[i] = index of the largest logit of row i (smallest index among equals); values[i] = that logit.
+    With `scatter`, also scatter[scatter_index[i]] = tokens[i]."""
+    _cuda(logits, tokens, values, scatter_index, scatter)
+    lib, fn = _fn("sampling", "sb_argmax", [c_void_p, c_int64, c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p])
+    _check(lib, fn(_ptr(logits), logits.stride(0), logits.shape[0], logits.shape[1], _ptr(tokens), _ptr(values),
+                   _ptr(scatter_index), _ptr(scatter) if scatter_index is not None else 0, _stream()))
 
 
-def sample_temperature(logits, temperatures, seeds, lengths, tokens, values) -> None:
-    """Temperature sampling keyed on (seed, sequence length) for every row; see csrc/sampling.cu."""
-    _cuda(logits, temperatures, seeds, lengths, tokens, values)
+def sample_temperature(logits, temperatures, seeds, lengths, tokens, values, scatter_index=None, scatter=None) -> None:
+    """Temperature sampling keyed on (seed, sequence length) for every row with temperature > 0 (other rows are left
+    alone); see csrc/sampling.cu. With `scatter`, also scatter[scatter_index[i]] = tokens[i]."""
+    _cuda(logits, temperatures, seeds, lengths, tokens, values, scatter_index, scatter)
     lib, fn = _fn("sampling", "sb_sample_temperature", [c_void_p, c_int64, c_int, c_int, c_void_p, c_void_p, c_void_p,
-                                                        c_void_p, c_void_p, c_void_p])
+                                                        c_void_p, c_void_p, c_void_p, c_void_p, c_void_p])
     _check(lib, fn(_ptr(logits), logits.stride(0), logits.shape[0], logits.shape[1], _ptr(temperatures), _ptr(seeds),
-                   _ptr(lengths), _ptr(tokens), _ptr(values), _stream()))
+                   _ptr(lengths), _ptr(tokens), _ptr(values), _ptr(scatter_index),
+                   _ptr(scatter) if scatter_index is not None else 0, _stream()))
 
 
 STORE, ADD, SWIGLU = 0, 1, 2

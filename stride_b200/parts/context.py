@@ -106,6 +106,7 @@ class StepContext:
     entry_first_pos: list = field(default_factory=list)
     entry_meta: Optional[torch.Tensor] = None              # [4, E] int32 on the device: slot, first row, length, first position
     upload_ints: Optional[object] = None                   # callable(np.ndarray int32) -> device tensor, valid for this step
+    sampled: Optional[torch.Tensor] = None                 # [slots] int32: each request's last sampled token (a token id of -1 reads it)
     shared: dict = field(default_factory=dict)             # what parts compute once per step and share between layers
     # Set for a step that is recorded into a CUDA graph: every entry is one decoded token, the batch is
     # padded to a fixed size, and no key lies at or beyond `static_keys`. Parts must then launch the same

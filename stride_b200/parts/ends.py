@@ -36,7 +36,7 @@ class Embedding(Part):
         return 0   # a step reads one row per token, not the table
 
     def forward(self, ctx, out):
-        ops.embed(ctx.token_ids, self.weight, out)
+        ops.embed(ctx.token_ids, self.weight, out, ctx.slots if ctx.sampled is not None else None, ctx.sampled)
 
 
 @register_part("head", "linear")

@@ -77,7 +77,15 @@ def choose_token_host(logits: np.ndarray, params: SamplingParams, length: int):
 
 
 class Sampler:
-    """Chooses tokens for the rows of one step's logits."""
+    """Chooses tokens for the rows of one step's logits.
+
+    `choose` is the whole thing at once. `launch` + `collect` split it, so that a caller can queue the next
+    step on the GPU before reading this step's tokens: `launch` enqueues the kernels and the copies of their
+    results into pinned host memory (two sets of buffers, used alternately) and returns a ticket; `collect`
+    waits for that ticket's copies. Rows with top_k or top_p need their logits on the host, so a launch that
+    has such rows synchronises by itself. With `scatter`, the device kernels also leave every row's token at
+    scatter[scatter_index[row]] (the engine's per-request table that the next step's embedding reads).
+    """
 
     def __init__(self, device, max_rows: int):
         self.device = torch.device(device)
@@ -87,35 +95,61 @@ class Sampler:
         self._temps = torch.zeros(max_rows, dtype=torch.float32, device=self.device)
         self._seeds = torch.zeros(max_rows, dtype=torch.int64, device=self.device)
         self._lengths = torch.zeros(max_rows, dtype=torch.int32, device=self.device)
-        self._host_tokens = torch.zeros(2, max_rows, dtype=torch.int32, pin_memory=True)
-        self._host_values = torch.zeros(2, max_rows, dtype=torch.float32, pin_memory=True)
+        self._host_tokens = [torch.zeros(2, max_rows, dtype=torch.int32, pin_memory=True) for _ in range(2)]
+        self._host_values = [torch.zeros(2, max_rows, dtype=torch.float32, pin_memory=True) for _ in range(2)]
+        self._host_temps = [torch.zeros(max_rows, dtype=torch.float32, pin_memory=True) for _ in range(2)]
+        self._host_seeds = [torch.zeros(max_rows, dtype=torch.int64, pin_memory=True) for _ in range(2)]
+        self._host_lengths = [torch.zeros(max_rows, dtype=torch.int32, pin_memory=True) for _ in range(2)]
+        self._events = [torch.cuda.Event(), torch.cuda.Event()]
+        self._turn = 0
+
+    @staticmethod
+    def on_device(p: SamplingParams) -> bool:
+        """True if the row's token is chosen by a CUDA kernel (greedy, or temperature without top_k / top_p)."""
+        return p.temperature <= 0.0 or (p.top_k <= 0 and p.top_p >= 1.0)
+
+    def launch(self, logits: torch.Tensor, params: list, lengths: list, scatter_index=None, scatter=None):
+        rows = logits.shape[0]
+        if rows > self.max_rows:
+            raise ValueError(f"{rows} rows exceed the sampler's {self.max_rows}")
+        ops.argmax(logits, self._tokens[0, :rows], self._values[0, :rows], scatter_index, scatter)
+        device_rows = [i for i, p in enumerate(params) if p.temperature > 0.0 and p.top_k <= 0 and p.top_p >= 1.0]
+        host_rows = [i for i, p in enumerate(params) if p.temperature > 0.0 and not (p.top_k <= 0 and p.top_p >= 1.0)]
+        turn = self._turn
+        self._turn ^= 1
+        self._events[turn].synchronize()       # the launch that used this set of host buffers two turns ago is done
+        if device_rows:
+            ht, hs, hl = self._host_temps[turn].numpy(), self._host_seeds[turn].numpy(), self._host_lengths[turn].numpy()
+            on = set(device_rows)
+            for i, p in enumerate(params):
+                ht[i] = p.temperature if i in on else 0.0        # rows not sampled on the device are skipped by the kernel
+                hs[i] = np.uint64(p.seed & _MASK).astype(np.int64)
+                hl[i] = lengths[i]
+            self._temps[:rows].copy_(self._host_temps[turn][:rows], non_blocking=True)
+            self._seeds[:rows].copy_(self._host_seeds[turn][:rows], non_blocking=True)
+            self._lengths[:rows].copy_(self._host_lengths[turn][:rows], non_blocking=True)
+            ops.sample_temperature(logits, self._temps[:rows], self._seeds[:rows], self._lengths[:rows],
+                                   self._tokens[1, :rows], self._values[1, :rows], scatter_index, scatter)
+        self._host_tokens[turn][:, :rows].copy_(self._tokens[:, :rows], non_blocking=True)
+        self._host_values[turn][:, :rows].copy_(self._values[:, :rows], non_blocking=True)
+        host_logits = logits[host_rows].to("cpu") if host_rows else None      # synchronises
+        self._events[turn].record()
+        return (turn, rows, device_rows, host_rows, host_logits, params, lengths)
+
+    def collect(self, ticket):
+        """(tokens list, values list) of a launch."""
+        turn, rows, device_rows, host_rows, host_logits, params, lengths = ticket
+        self._events[turn].synchronize()
+        tokens = self._host_tokens[turn][0, :rows].tolist()
+        values = self._host_values[turn][0, :rows].tolist()
+        for i in device_rows:
+            tokens[i] = int(self._host_tokens[turn][1, i])
+            values[i] = float(self._host_values[turn][1, i])
+        for k, i in enumerate(host_rows):
+            tokens[i], values[i] = choose_token_host(host_logits[k].numpy(), params[i], lengths[i])
+        return tokens, values
 
     def choose(self, logits: torch.Tensor, params: list, lengths: list):
         """logits [rows, vocab] on the device; params[i], lengths[i] belong to row i (length = tokens the
         sequence has before the new one). Returns (tokens list, values list)."""
-        rows = logits.shape[0]
-        if rows > self.max_rows:
-            raise ValueError(f"{rows} rows exceed the sampler's {self.max_rows}")
-        ops.argmax(logits, self._tokens[0, :rows], self._values[0, :rows])
-        device_rows = [i for i, p in enumerate(params) if p.temperature > 0.0 and p.top_k <= 0 and p.top_p >= 1.0]
-        host_rows = [i for i, p in enumerate(params) if p.temperature > 0.0 and not (p.top_k <= 0 and p.top_p >= 1.0)]
-        if device_rows:
-            temps = torch.tensor([max(p.temperature, 1e-30) if p.temperature > 0 else 1.0 for p in params], dtype=torch.float32)
-            seeds = torch.tensor([np.uint64(p.seed & _MASK).astype(np.int64) for p in params], dtype=torch.int64)
-            self._temps[:rows].copy_(temps)
-            self._seeds[:rows].copy_(seeds)
-            self._lengths[:rows].copy_(torch.tensor(lengths, dtype=torch.int32))
-            ops.sample_temperature(logits, self._temps[:rows], self._seeds[:rows], self._lengths[:rows],
-                                   self._tokens[1, :rows], self._values[1, :rows])
-        self._host_tokens[:, :rows].copy_(self._tokens[:, :rows], non_blocking=True)
-        self._host_values[:, :rows].copy_(self._values[:, :rows], non_blocking=True)
-        host_logits = logits[host_rows].to("cpu") if host_rows else None
-        torch.cuda.current_stream().synchronize()
-        tokens = self._host_tokens[0, :rows].tolist()
-        values = self._host_values[0, :rows].tolist()
-        for i in device_rows:
-            tokens[i] = int(self._host_tokens[1, i])
-            values[i] = float(self._host_values[1, i])
-        for k, i in enumerate(host_rows):
-            tokens[i], values[i] = choose_token_host(host_logits[k].numpy(), params[i], lengths[i])
-        return tokens, values
+        return self.collect(self.launch(logits, params, lengths))
