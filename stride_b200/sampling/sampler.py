@@ -130,8 +130,10 @@ class Sampler:
             self._lengths[:rows].copy_(self._host_lengths[turn][:rows], non_blocking=True)
             ops.sample_temperature(logits, self._temps[:rows], self._seeds[:rows], self._lengths[:rows],
                                    self._tokens[1, :rows], self._values[1, :rows], scatter_index, scatter)
-        self._host_tokens[turn][:, :rows].copy_(self._tokens[:, :rows], non_blocking=True)
-        self._host_values[turn][:, :rows].copy_(self._values[:, :rows], non_blocking=True)
+        # contiguous pieces only: a strided device-to-host copy would go through a staging buffer and block
+        for k in ((0, 1) if device_rows else (0,)):
+            self._host_tokens[turn][k, :rows].copy_(self._tokens[k, :rows], non_blocking=True)
+            self._host_values[turn][k, :rows].copy_(self._values[k, :rows], non_blocking=True)
         host_logits = logits[host_rows].to("cpu") if host_rows else None      # synchronises
         self._events[turn].record()
         return (turn, rows, device_rows, host_rows, host_logits, params, lengths)
