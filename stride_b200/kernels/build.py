@@ -38,6 +38,7 @@ SOURCES = {
     "sampling": "sampling.cu",
     "gemm_tc": "gemm_tc.cu",
     "attention_tc": "attention_tc.cu",
+    "attention_tc5": "attention_tc5.cu",
 }
 
 _loaded: dict[str, ctypes.CDLL] = {}

@@ -71,6 +71,9 @@ def attention(a) -> dict:
     meta = torch.tensor([[i, i * new, new, old] for i in range(B)], dtype=torch.int32).T.contiguous().cuda()
     G = Hq // Hkv
     ppt, short = 64 // G, 16 // G
+    tc5 = new > short and not a.mma_sync and ops.attention_tc5_supported(Hq, Hkv, D, page)
+    if tc5:
+        ppt = 128 // G
     if new <= short:
         tiles, items, chunks = [], list(range(B)), (total - 1) // 256 + 1
     else:
@@ -80,12 +83,17 @@ def attention(a) -> dict:
     counters = torch.zeros(max(1, len(items) * Hkv), dtype=torch.int32, device="cuda")
 
     def run():
-        ops.attention_tc(q, out, cache, table, meta, work, len(tiles) // 2, len(items), chunks, scratch, Hq, Hkv, D, 0,
-                         D ** -0.5, counters=counters)
+        if tc5:
+            ops.attention_tc5(q, out, cache, table, meta, work, len(tiles) // 2, Hq, Hkv, D, 0, D ** -0.5)
+        else:
+            ops.attention_tc(q, out, cache, table, meta, work, len(tiles) // 2, len(items), chunks, scratch, Hq, Hkv, D, 0,
+                             D ** -0.5, counters=counters)
     us = _time(run, a.reps)
+    if tc5 and ops.attention_tc5_status() != 0:
+        raise RuntimeError("a wait inside the tcgen05 attention kernel timed out")
     kv_bytes = B * total * Hkv * D * 2 * 2
     flops = 4.0 * B * Hq * D * (new * old + new * (new + 1) / 2)
-    return {"kernel": "attention_tc", "batch": B, "context": old, "new": new, "us": round(us, 2),
+    return {"kernel": "attention_tc5" if tc5 else "attention_tc", "batch": B, "context": old, "new": new, "us": round(us, 2),
             "kv_GBps": round(kv_bytes / us / 1e3, 1), "TFLOPs": round(flops / us / 1e6, 2)}
 
 
@@ -177,6 +185,7 @@ def main(argv=None) -> int:
     t.add_argument("--head-dim", type=int, default=64)
     t.add_argument("--page", type=int, default=64)
     t.add_argument("--reps", type=int, default=50)
+    t.add_argument("--mma-sync", action="store_true", help="prompt portions on the mma.sync kernel instead of tcgen05")
     st = sub.add_parser("step")
     st.add_argument("--batch", type=int, default=8)
     st.add_argument("--context", type=int, default=256)

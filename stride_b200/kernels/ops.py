@@ -244,3 +244,32 @@ def attention_tc(q, out, cache_layer, block_table, entry_meta, work, n_tiles: in
                    cache_layer.stride(0), cache_layer.stride(1), cache_layer.stride(2), _ptr(entry_meta),
                    entry_meta.stride(0), _ptr(work), n_tiles, n_items, chunks, _ptr(scratch), _ptr(counters), num_heads, num_kv_heads,
                    head_dim, window, scale, _stream()))
+
+
+def attention_tc5_supported(num_heads: int, num_kv_heads: int, head_dim: int, page_size: int) -> bool:
+    """True if the tcgen05 prompt-attention kernel takes this shape (head size 64, pages of a power of two >= 8)."""
+    if head_dim != 64 or num_kv_heads <= 0 or num_heads % num_kv_heads or num_heads // num_kv_heads > 128:
+        return False
+    return page_size >= 8 and page_size & (page_size - 1) == 0
+
+
+def attention_tc5(q, out, cache_layer, block_table, entry_meta, work, n_tiles: int, num_heads: int, num_kv_heads: int,
+                  head_dim: int, window: int, scale: float) -> None:
+    """Prompt-portion attention on the tcgen05 tensor cores; `work` is [n_tiles, 2] = (entry, tile of 128 // G positions)."""
+    _cuda(q, out, cache_layer, block_table, entry_meta, work)
+    if not (q.dtype == out.dtype == cache_layer.dtype == torch.bfloat16):
+        raise TypeError("attention_tc5 takes bfloat16 q, out and cache")
+    lib, fn = _fn("attention_tc5", "sb_attention_tc5",
+                  [c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_int, c_int, c_int64, c_int64, c_int64, c_void_p, c_int,
+                   c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_float, c_void_p])
+    _check(lib, fn(_ptr(q), _ptr(out), _ptr(cache_layer), cache_layer.shape[0], _ptr(block_table), block_table.shape[1],
+                   cache_layer.shape[3], cache_layer.stride(0), cache_layer.stride(1), cache_layer.stride(2), _ptr(entry_meta),
+                   entry_meta.stride(0), _ptr(work), n_tiles, q.shape[0], num_heads, num_kv_heads, head_dim, window, scale,
+                   _stream()))
+
+
+def attention_tc5_status() -> int:
+    """0 if every wait inside the tcgen05 attention kernel completed since the last call; synchronises."""
+    lib = library("attention_tc5")
+    lib.sb_attention_tc5_status.restype = c_int
+    return lib.sb_attention_tc5_status()

@@ -78,18 +78,18 @@ class AttentionMixer(Mixer):
                          dtype=self.env.act_dtype)
 
     @staticmethod
-    def _tc_plan(ctx, G: int):
+    def _tc_plan(ctx, G: int, tile_rows: int = 64):
         """(work list on the device, tiles, items, chunks) of the tensor-core attention kernels for this
         step: entries of at most 16 // G tokens go to the decode kernel (one item each), longer ones are
-        cut into tiles of 64 // G positions. Made once per step and shared by all layers of this ratio."""
-        key = ("attention_tc_plan", G)
+        cut into tiles of tile_rows // G positions. Made once per step and shared by all layers of this ratio."""
+        key = ("attention_tc_plan", G, tile_rows)
         plan = ctx.shared.get(key)
         if plan is None and ctx.static_keys:
             E = len(ctx.entry_length)
             plan = (ctx.workspace.iota(E), 0, E, (ctx.static_keys + 255) // 256)
             ctx.shared[key] = plan
         if plan is None:
-            ppt, short = 64 // G, 16 // G
+            ppt, short = tile_rows // G, 16 // G
             tiles, items, last = [], [], 0
             for e, (L, p0) in enumerate(zip(ctx.entry_length, ctx.entry_first_pos)):
                 if L <= short:
@@ -112,11 +112,20 @@ class AttentionMixer(Mixer):
         mixed = ws.get("attn.out", n, (self.num_heads * D,), ctx.act_dtype)
         G = self.num_heads // self.num_kv_heads
         if ctx.act_dtype == torch.bfloat16 and D in (64, 128) and G <= 16:
-            plan = self._tc_plan(ctx, G)
-            scratch = ws.grow("attn.scratch", ops.attention_tc_scratch(plan[2], self.num_kv_heads, plan[3], D), torch.float32)
-            counters = ws.raw("attn.counters", (ws.max_tokens * self.num_kv_heads,), torch.int32)
-            ops.attention_tc(q, mixed, cache.pages, cache.block_table, ctx.entry_meta, plan[0], plan[1], plan[2], plan[3],
-                             scratch, self.num_heads, self.num_kv_heads, D, self.window, self.scale, counters=counters)
+            # prompt portions: the tcgen05 kernel where the shape allows it (tiles of 128 rows), else mma.sync (64 rows);
+            # decoded tokens and very short portions: the split-key decode kernel
+            tc5 = ops.attention_tc5_supported(self.num_heads, self.num_kv_heads, D, cache.page_size)
+            plan = self._tc_plan(ctx, G, 128 if tc5 else 64)
+            work, n_tiles, n_items, chunks = plan
+            if tc5 and n_tiles:
+                ops.attention_tc5(q, mixed, cache.pages, cache.block_table, ctx.entry_meta, work, n_tiles, self.num_heads,
+                                  self.num_kv_heads, D, self.window, self.scale)
+                work, n_tiles = work[2 * n_tiles:], 0
+            if n_tiles or n_items:
+                scratch = ws.grow("attn.scratch", ops.attention_tc_scratch(n_items, self.num_kv_heads, chunks, D), torch.float32)
+                counters = ws.raw("attn.counters", (ws.max_tokens * self.num_kv_heads,), torch.int32)
+                ops.attention_tc(q, mixed, cache.pages, cache.block_table, ctx.entry_meta, work, n_tiles, n_items, chunks,
+                                 scratch, self.num_heads, self.num_kv_heads, D, self.window, self.scale, counters=counters)
         else:
             ops.attention_generic(q, mixed, cache.pages, cache.block_table, ctx.positions, ctx.slots,
                                   self.num_heads, self.num_kv_heads, D, self.window, self.scale)

@@ -307,3 +307,27 @@ def test_argmax_and_temperature_sampling():
             l = torch.nan_to_num(logits[r], nan=-1e30).cpu()
             want, wv = plain.choose_token(l, float(temps[r]), 1.0, 0, int(seeds[r]) & (2**64 - 1), length)
             assert int(tok[r]) == want and float(val[r]) == wv
+
+
+@pytest.mark.parametrize("Hq,Hkv,page,window", [(8, 2, 16, 0), (4, 4, 8, 0), (12, 4, 64, 100), (16, 1, 128, 0), (6, 2, 256, 0), (32, 8, 64, 0)])
+def test_attention_tc5_against_plain(Hq, Hkv, page, window):
+    """The tcgen05 prompt-attention kernel: portions with and without cached history, several key tiles, shuffled pages,
+    ratios that do and do not divide 128, one far key that dominates a query."""
+    from stride_b200.kernels import ops
+    D = 64
+    assert ops.attention_tc5_supported(Hq, Hkv, D, page)
+    new = [77, 200, 40, 130, 64, 300]
+    old = [0, 100, 510, 5, 63, 0]
+    case = _paged_case(new, old, Hq, Hkv, D, page, torch.bfloat16, seed=Hq + page, peak=(2, 3))
+    G = Hq // Hkv
+    ppt = 128 // G
+    tiles = [x for e, L in enumerate(new) for t in range(-(-L // ppt)) for x in (e, t)]
+    work = torch.tensor(tiles, dtype=torch.int32, device=DEV)
+    out = torch.full_like(case["q"], float("nan"))
+    scale = 1.0 / math.sqrt(D)
+    ops.attention_tc5(case["q"], out, case["cache"], case["table"], case["meta"], work, len(tiles) // 2, Hq, Hkv, D, window, scale)
+    assert ops.attention_tc5_status() == 0
+    ref = _attention_reference(case, Hq, Hkv, D, window)
+    got = out.float().cpu()
+    assert torch.isfinite(got).all()
+    assert (got - ref).abs().max() <= 2e-2 * max(1.0, float(ref.abs().max()))
