@@ -5,12 +5,12 @@
 // positions. The CTA walks the key tiles [128 t, 128 t + 128) its rows can see:
 //
 //   control warp (one thread): TMA loads of the query tile (a 3-D box over [token][head][64]) and of the key
-//     and value tiles, page by page through the block table, into 128-byte-swizzled shared memory (two
+//     and value tiles, page by page through the block table, into 128-byte-swizzled shared memory (three
 //     buffers); S = Q K^T by tcgen05.mma (M 128, N 128, K 64) into one of two TMEM accumulators, issued one
 //     tile ahead so that it runs under the softmax of the tile before; O_t = P V by tcgen05.mma (M 128, N 64,
 //     K 128, V as an MN-major operand straight from its [key][64] page layout).
-//   four softmax warps (thread = row, TMEM lane = row): read S with tcgen05.ld, scale, mask by position, keep
-//     the running maximum and sum in float32, write the weights to shared memory as two bfloat16 parts
+//   eight softmax warps (two threads per row, TMEM lane = row, each with half of the tile's keys and half of the
+//     output): read S with tcgen05.ld, scale, mask by position, keep the running maximum and sum in float32, write the weights to shared memory as two bfloat16 parts
 //     (p = hi + lo, so the value product sees nearly 32-bit weights, as the reference's 32-bit softmax does),
 //     then fold O_t into the row's float32 output registers: o = o * 2^(m_old - m_new) + O_t.
 //
@@ -30,10 +30,14 @@ constexpr int kD = 64;
 constexpr int kRows = 128;
 constexpr int kKeys = 128;
 constexpr int kTileBytes = 128 * 128;   // 128 rows of 64 bfloat16
-constexpr int kThreads = 160;
+constexpr int kSoftmaxThreads = 256;    // two threads per row: each takes 64 of the tile's 128 keys and 32 of the 64 outputs
+constexpr int kThreads = kSoftmaxThreads + 32;
 constexpr float kLog2e = 1.4426950408889634f;
-// shared memory: Q | K0 K1 | V0 V1 | P hi (two 64-key halves) | P lo
-constexpr int kSmemBytes = 9 * kTileBytes;
+constexpr int kStages = 3;              // key/value tiles in flight
+// shared memory: Q | K x kStages | V x kStages | P hi (two 64-key halves) | P lo
+constexpr int kPhiTile = 1 + 2 * kStages, kPloTile = kPhiTile + 2;
+constexpr int kSmemBytes = (kPloTile + 2) * kTileBytes;
+constexpr int kPagesCached = 512;       // block-table entries of the request kept in shared memory
 constexpr uint32_t kTmemCols = 512;     // S0 [0,128) S1 [128,256) O_t [256,320)
 
 __device__ __forceinline__ float fast_exp2(float x) {
@@ -41,6 +45,7 @@ __device__ __forceinline__ float fast_exp2(float x) {
   asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
   return y;
 }
+__device__ __forceinline__ void softmax_barrier() { asm volatile("bar.sync 1, 256;" ::: "memory"); }
 
 struct Fa5Params {
   bf16* out;
@@ -59,14 +64,16 @@ struct Fa5Params {
 __global__ void __launch_bounds__(kThreads, 1)
 attn_prefill_tc5_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_kv, const Fa5Params p) {
   extern __shared__ __align__(1024) uint8_t smem_raw[];
-  __shared__ __align__(8) uint64_t q_full, kv_full[2], s_full[2], p_full, o_full;
+  __shared__ __align__(8) uint64_t q_full, kv_full[kStages], s_full[2], p_full, o_full;
   __shared__ uint32_t tmem_base_s;
+  __shared__ int32_t pages_s[kPagesCached];
+  __shared__ float xch[2][kRows];          // the two halves of a row exchange their maximum, and at the end their sum
 
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   const uint32_t smem0 = (smem_u32(smem_raw) + 1023u) & ~1023u;
   uint8_t* smem = smem_raw + (smem0 - smem_u32(smem_raw));
-  const uint32_t sQ = smem0, sK = smem0 + kTileBytes, sV = smem0 + 3 * kTileBytes, sPhi = smem0 + 5 * kTileBytes,
-                 sPlo = smem0 + 7 * kTileBytes;
+  const uint32_t sQ = smem0, sK = smem0 + kTileBytes, sV = smem0 + (1 + kStages) * kTileBytes,
+                 sPhi = smem0 + kPhiTile * kTileBytes, sPlo = smem0 + kPloTile * kTileBytes;
 
   const int g = blockIdx.y;
   const int G = p.Hq / p.Hkv, ppt = kRows / G;
@@ -81,15 +88,13 @@ attn_prefill_tc5_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_
 
   if (tid == 0) {
     mbar_init(smem_u32(&q_full), 1);
-    for (int i = 0; i < 2; ++i) {
-      mbar_init(smem_u32(&kv_full[i]), 1);
-      mbar_init(smem_u32(&s_full[i]), 1);
-    }
-    mbar_init(smem_u32(&p_full), 128);
+    for (int i = 0; i < kStages; ++i) mbar_init(smem_u32(&kv_full[i]), 1);
+    for (int i = 0; i < 2; ++i) mbar_init(smem_u32(&s_full[i]), 1);
+    mbar_init(smem_u32(&p_full), kSoftmaxThreads);
     mbar_init(smem_u32(&o_full), 1);
     mbar_init_fence();
   }
-  if (warp == 4) tmem_alloc(smem_u32(&tmem_base_s), kTmemCols);
+  if (warp == 8) tmem_alloc(smem_u32(&tmem_base_s), kTmemCols);
   // rows of the query tile that no (position, head) pair fills (G does not divide 128) must still be finite
   for (int i = ppt * G * 8 + tid; i < kRows * 8; i += kThreads) *reinterpret_cast<uint4*>(smem + i * 16) = make_uint4(0, 0, 0, 0);
   fence_async_smem();
@@ -101,144 +106,192 @@ attn_prefill_tc5_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_
   sb::grid_launch_dependents();
   sb::grid_dependency_wait();
 
-  if (warp == 4) {
+  if (warp == 8) {
+    // the request's block-table entries for the keys this CTA reads, fetched by the whole warp at once
+    const int32_t* table = p.block_table + static_cast<int64_t>(slot) * p.max_pages;
+    const int page_first = (kt0 * kKeys) >> p.page_shift, page_last = pos_hi >> p.page_shift;
+    const bool cached = page_last - page_first < kPagesCached;
+    if (cached)
+      for (int i = page_first + lane; i <= page_last; i += 32) pages_s[i - page_first] = table[i];
+    __syncwarp();
     if (lane == 0) {
       // ------------------------------------------------ control: TMA and MMA issue
       prefetch_tensormap(&map_q);
       prefetch_tensormap(&map_kv);
-      const int32_t* table = p.block_table + static_cast<int64_t>(slot) * p.max_pages;
       auto load_kv = [&](int i) {
-        const int buf = i & 1;
+        const int buf = i % kStages;
         const uint32_t bar = smem_u32(&kv_full[buf]);
         mbar_expect_tx(bar, 2 * kTileBytes);
         for (int sub = 0; sub < kKeys / p.box_rows; ++sub) {
           const int key = (kt0 + i) * kKeys + sub * p.box_rows;
-          const int key_c = min(key, pos_hi);                 // past the end: the request's last page again
-          const int page = table[key_c >> p.page_shift];
+          const int pidx = min(key, pos_hi) >> p.page_shift;       // past the end: the request's last page again
+          const int page = cached ? pages_s[pidx - page_first] : table[pidx];
           const int in_page = p.page_size > p.box_rows ? (key & (p.page_size - 1)) : 0;
           const int row = page * p.rows_per_page + g * p.rows_head + in_page;
           tma_load_2d(sK + buf * kTileBytes + sub * p.box_rows * 128, &map_kv, bar, 0, row);
           tma_load_2d(sV + buf * kTileBytes + sub * p.box_rows * 128, &map_kv, bar, 0, row + p.rows_v);
         }
       };
+      // descriptors are built once; a tile, a 64-key half or a K step only adds to the start-address field
+      const uint32_t idesc_qk = instr_desc(kRows, kKeys, false), idesc_pv = instr_desc(kRows, kD, true);
+      const uint64_t dQ = smem_desc_sw128(sQ), dK = smem_desc_sw128(sK), dV = smem_desc_sw128(sV);
+      const uint64_t dPhi = smem_desc_sw128(sPhi), dPlo = smem_desc_sw128(sPlo);
+      constexpr uint64_t kTileStep = kTileBytes >> 4, kVStep = 2048 >> 4;
       auto issue_qk = [&](int i) {
-        const uint32_t idesc = instr_desc(kRows, kKeys, false);
-        const uint64_t da = smem_desc_sw128(sQ), db = smem_desc_sw128(sK + (i & 1) * kTileBytes);
+        const uint64_t db = dK + (i % kStages) * kTileStep;
 #pragma unroll
-        for (int k = 0; k < kD / 16; ++k) umma_bf16(tmem_base + (i & 1) * kKeys, da + 2 * k, db + 2 * k, idesc, k > 0 ? 1u : 0u);
+        for (int k = 0; k < kD / 16; ++k) umma_bf16(tmem_base + (i & 1) * kKeys, dQ + 2 * k, db + 2 * k, idesc_qk, k > 0 ? 1u : 0u);
         umma_commit(smem_u32(&s_full[i & 1]));
       };
       mbar_expect_tx(smem_u32(&q_full), ppt * G * 128);
       tma_load_3d(sQ, &map_q, smem_u32(&q_full), 0, g * G, row0);
-      load_kv(0);
-      if (T > 1) load_kv(1);
+      for (int i = 0; i < kStages && i < T; ++i) load_kv(i);
       mbar_wait(smem_u32(&q_full), 0, p.status, 1);
       mbar_wait(smem_u32(&kv_full[0]), 0, p.status, 2);
       fence_after_sync();
       issue_qk(0);
-      const uint32_t idesc_pv = instr_desc(kRows, kD, true);
       for (int i = 0; i < T; ++i) {
         if (i + 1 < T) {
-          mbar_wait(smem_u32(&kv_full[(i + 1) & 1]), ((i + 1) >> 1) & 1, p.status, 2);
+          mbar_wait(smem_u32(&kv_full[(i + 1) % kStages]), ((i + 1) / kStages) & 1, p.status, 2);
           fence_after_sync();
           issue_qk(i + 1);
         }
         mbar_wait(smem_u32(&p_full), i & 1, p.status, 3);
         fence_after_sync();
-        const uint32_t v = sV + (i & 1) * kTileBytes;
+        const uint64_t dv = dV + (i % kStages) * kTileStep;
 #pragma unroll
         for (int ks = 0; ks < kKeys / 16; ++ks) {
-          const uint32_t off = (ks >> 2) * kTileBytes;     // which 64-key half of P
-          const uint64_t db = smem_desc_sw128(v + ks * 2048);
-          umma_bf16(tmem_base + 2 * kKeys, smem_desc_sw128(sPhi + off) + 2 * (ks & 3), db, idesc_pv, ks > 0 ? 1u : 0u);
-          umma_bf16(tmem_base + 2 * kKeys, smem_desc_sw128(sPlo + off) + 2 * (ks & 3), db, idesc_pv, 1u);
+          const uint64_t pa = (ks >> 2) * kTileStep + 2 * (ks & 3);     // the 64-key half of P, the K step inside it
+          umma_bf16(tmem_base + 2 * kKeys, dPhi + pa, dv + ks * kVStep, idesc_pv, ks > 0 ? 1u : 0u);
+          umma_bf16(tmem_base + 2 * kKeys, dPlo + pa, dv + ks * kVStep, idesc_pv, 1u);
         }
         umma_commit(smem_u32(&o_full));
         mbar_wait(smem_u32(&o_full), i & 1, p.status, 4);     // then this tile's key/value buffers are free
-        if (i + 2 < T) load_kv(i + 2);
+        if (i + kStages < T) load_kv(i + kStages);
       }
     }
     __syncwarp();
   } else {
-    // ------------------------------------------------ softmax: thread = row of the tile = TMEM lane
-    const int r = tid;
+    // ------------------------------------------------ softmax: two threads per row of the tile (= TMEM lane);
+    // thread `half` takes keys [64 half, 64 half + 64) of every key tile and outputs [32 half, 32 half + 32)
+    const int r = tid & (kRows - 1), half = tid >> 7;
     const int pi = r / G, hh = r % G;
     const bool valid = pi < npos;
     const int row_pos = valid ? pos0 + pi : -1;
     const int row_lo = p.window > 0 ? row_pos - p.window + 1 : 0;
-    const uint32_t lane_addr = static_cast<uint32_t>(warp * 32) << 16;
+    const uint32_t lane_addr = static_cast<uint32_t>((warp & 3) * 32) << 16;
     float m = -INFINITY, l = 0.0f;
-    float o[kD];
+    float o[kD / 2];
 #pragma unroll
-    for (int d = 0; d < kD; ++d) o[d] = 0.0f;
-    for (int i = 0; i < T; ++i) {
+    for (int d = 0; d < kD / 2; ++d) o[d] = 0.0f;
+
+    // Pass 1 of tile i: this thread's maximum over its 64 scores, left in xch[half][r] for the other half.
+    auto pass1 = [&](int i) {
       mbar_wait(smem_u32(&s_full[i & 1]), (i >> 1) & 1, p.status, 5);
       fence_after_sync();
-      const uint32_t s_addr = tmem_base + (i & 1) * kKeys + lane_addr;
-      const int key0 = (kt0 + i) * kKeys;
-      float mx = -INFINITY;
+      const uint32_t s_addr = tmem_base + (i & 1) * kKeys + lane_addr + half * 64;
+      const int key0 = (kt0 + i) * kKeys + half * 64;
+      const bool masked = (kt0 + i) * kKeys + kKeys - 1 > pos0 || (p.window > 0 && (kt0 + i) * kKeys < pos_hi - p.window + 1) ||
+                          npos * G < kRows;
+      float mx0 = -INFINITY, mx1 = -INFINITY, mx2 = -INFINITY, mx3 = -INFINITY;
 #pragma unroll 1
-      for (int c = 0; c < 4; ++c) {
+      for (int c = 0; c < 2; ++c) {
         float v[32];
         tmem_load32(s_addr + c * 32, v);
+        if (masked) {
 #pragma unroll
-        for (int j = 0; j < 32; ++j) {
-          const int key = key0 + c * 32 + j;
-          if (key <= row_pos && key >= row_lo) mx = fmaxf(mx, v[j] * p.scale_log2);
+          for (int j = 0; j < 32; ++j) {
+            const int key = key0 + c * 32 + j;
+            if (!(key <= row_pos && key >= row_lo)) v[j] = -INFINITY;
+          }
+        }
+#pragma unroll
+        for (int j = 0; j < 32; j += 4) {
+          mx0 = fmaxf(mx0, v[j]);
+          mx1 = fmaxf(mx1, v[j + 1]);
+          mx2 = fmaxf(mx2, v[j + 2]);
+          mx3 = fmaxf(mx3, v[j + 3]);
         }
       }
+      xch[half][r] = fmaxf(fmaxf(mx0, mx1), fmaxf(mx2, mx3));
+    };
+
+    pass1(0);
+    for (int i = 0; i < T; ++i) {
+      // (the scores of tile i have been read once already: pass 1 ran before or during the value product of tile i - 1)
+      softmax_barrier();
+      const float mx = fmaxf(xch[0][r], xch[1][r]) * p.scale_log2;   // the scale is positive
+      softmax_barrier();                                              // xch is free again for pass 1 of the next tile
       const float m_new = fmaxf(m, mx);
       const float m_use = m_new == -INFINITY ? 0.0f : m_new;
       const float alpha = fast_exp2(m - m_use);
-      l *= alpha;
+      const uint32_t s_addr = tmem_base + (i & 1) * kKeys + lane_addr + half * 64;
+      const int key0 = (kt0 + i) * kKeys + half * 64;
+      const bool masked = (kt0 + i) * kKeys + kKeys - 1 > pos0 || (p.window > 0 && (kt0 + i) * kKeys < pos_hi - p.window + 1) ||
+                          npos * G < kRows;
+      float l0 = 0.0f, l1 = 0.0f, l2 = 0.0f, l3 = 0.0f;
 #pragma unroll 1
-      for (int c = 0; c < 4; ++c) {
+      for (int c = 0; c < 2; ++c) {
         float v[32];
         tmem_load32(s_addr + c * 32, v);
         uint32_t hi[16], lo[16];
 #pragma unroll
         for (int j = 0; j < 32; j += 2) {
-          float pj[2];
-#pragma unroll
-          for (int u = 0; u < 2; ++u) {
-            const int key = key0 + c * 32 + j + u;
-            pj[u] = (key <= row_pos && key >= row_lo) ? fast_exp2(v[j + u] * p.scale_log2 - m_use) : 0.0f;
-            l += pj[u];
+          float p0 = fast_exp2(fmaf(v[j], p.scale_log2, -m_use)), p1 = fast_exp2(fmaf(v[j + 1], p.scale_log2, -m_use));
+          if (masked) {
+            const int key = key0 + c * 32 + j;
+            if (!(key <= row_pos && key >= row_lo)) p0 = 0.0f;
+            if (!(key + 1 <= row_pos && key + 1 >= row_lo)) p1 = 0.0f;
           }
-          const __nv_bfloat162 h = __floats2bfloat162_rn(pj[0], pj[1]);
-          const __nv_bfloat162 w = __floats2bfloat162_rn(pj[0] - __low2float(h), pj[1] - __high2float(h));
-          hi[j >> 1] = *reinterpret_cast<const uint32_t*>(&h);
-          lo[j >> 1] = *reinterpret_cast<const uint32_t*>(&w);
+          if (j & 2) {
+            l2 += p0;
+            l3 += p1;
+          } else {
+            l0 += p0;
+            l1 += p1;
+          }
+          // p = hi + lo (+ less than 2^-16 p): hi is p cut to its upper 16 bits, a bfloat16 exactly; lo is the
+          // remainder p - hi, exact in float32, cut the same way. Bit moves only: no conversion instruction.
+          const uint32_t b0 = __float_as_uint(p0), b1 = __float_as_uint(p1);
+          hi[j >> 1] = __byte_perm(b0, b1, 0x7632);
+          const uint32_t r0 = __float_as_uint(p0 - __uint_as_float(b0 & 0xFFFF0000u));
+          const uint32_t r1 = __float_as_uint(p1 - __uint_as_float(b1 & 0xFFFF0000u));
+          lo[j >> 1] = __byte_perm(r0, r1, 0x7632);
         }
-        // 32 keys = four 16-byte pieces of this row in the 64-key half c / 2, at pieces (c % 2) * 4 .. + 3
-        const uint32_t row_off = (c >> 1) * kTileBytes + r * 128;
+        // 32 keys = four 16-byte pieces of this row in the 64-key half `half`, at pieces c * 4 .. + 3
+        const uint32_t row_off = half * kTileBytes + r * 128;
 #pragma unroll
         for (int q = 0; q < 4; ++q) {
-          const uint32_t piece = (((c & 1) * 4 + q) ^ (r & 7)) * 16;
-          *reinterpret_cast<uint4*>(smem + 5 * kTileBytes + row_off + piece) = make_uint4(hi[4 * q], hi[4 * q + 1], hi[4 * q + 2], hi[4 * q + 3]);
-          *reinterpret_cast<uint4*>(smem + 7 * kTileBytes + row_off + piece) = make_uint4(lo[4 * q], lo[4 * q + 1], lo[4 * q + 2], lo[4 * q + 3]);
+          const uint32_t piece = ((c * 4 + q) ^ (r & 7)) * 16;
+          *reinterpret_cast<uint4*>(smem + kPhiTile * kTileBytes + row_off + piece) = make_uint4(hi[4 * q], hi[4 * q + 1], hi[4 * q + 2], hi[4 * q + 3]);
+          *reinterpret_cast<uint4*>(smem + kPloTile * kTileBytes + row_off + piece) = make_uint4(lo[4 * q], lo[4 * q + 1], lo[4 * q + 2], lo[4 * q + 3]);
         }
       }
+      l = l * alpha + ((l0 + l1) + (l2 + l3));
       fence_before_sync();
       fence_async_smem();
       mbar_arrive(smem_u32(&p_full));
+      if (i + 1 < T) pass1(i + 1);           // under the value product of tile i
       mbar_wait(smem_u32(&o_full), i & 1, p.status, 6);
       fence_after_sync();
-#pragma unroll
-      for (int c = 0; c < 2; ++c) {
+      {
         float v[32];
-        tmem_load32(tmem_base + 2 * kKeys + lane_addr + c * 32, v);
+        tmem_load32(tmem_base + 2 * kKeys + lane_addr + half * 32, v);
 #pragma unroll
-        for (int j = 0; j < 32; ++j) o[c * 32 + j] = o[c * 32 + j] * alpha + v[j];
+        for (int j = 0; j < 32; ++j) o[j] = o[j] * alpha + v[j];
       }
       m = m_new;
       fence_before_sync();
     }
+    softmax_barrier();
+    // the row's sum: this half's part plus the other half's (xch was last read before both halves arrived at p_full)
+    xch[half][r] = l;
+    softmax_barrier();
     if (valid) {
-      const float inv = 1.0f / l;
-      bf16* dst = p.out + (static_cast<int64_t>(row0 + pi) * p.Hq + g * G + hh) * kD;
+      const float inv = 1.0f / (xch[0][r] + xch[1][r]);
+      bf16* dst = p.out + (static_cast<int64_t>(row0 + pi) * p.Hq + g * G + hh) * kD + half * 32;
 #pragma unroll
-      for (int c = 0; c < kD / 8; ++c) {
+      for (int c = 0; c < 4; ++c) {
         uint32_t w[4];
 #pragma unroll
         for (int j = 0; j < 4; ++j) {
@@ -251,7 +304,7 @@ attn_prefill_tc5_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_
   }
   fence_before_sync();
   __syncthreads();
-  if (warp == 4) {
+  if (warp == 8) {
     fence_after_sync();
     tmem_dealloc(tmem_base, kTmemCols);
   }
