@@ -24,19 +24,13 @@
 //
 // Counterparts in arhaamatiq/stride: TcQkv, TcGemmResidual, TcMlp13, TcLmFull on wmma
 // (src/kernels_tc.cu:347-655).
-#include <cuda.h>
-
-#include <cstdlib>
-#include <map>
-#include <mutex>
-#include <tuple>
-
-#include "common.cuh"
+#include "tc5.cuh"
 
 SB_DEFINE_LAST_ERROR()
 
 namespace {
 
+using namespace sb::tc5;
 using bf16 = __nv_bfloat16;
 
 constexpr int kTileM = 128;
@@ -45,71 +39,10 @@ constexpr int kStageA = kTileM * 128;  // bytes
 constexpr int kMaxStages = 8;
 constexpr int kThreads = 192;
 constexpr int kSmemBudget = 200 * 1024;
-constexpr long long kWaitCycles = 2000000000LL;
 
 enum Epilogue { kStore = 0, kAdd = 1, kSwiglu = 2 };
 
-// ------------------------------------------------------------------ PTX wrappers
-__device__ __forceinline__ uint32_t smem_u32(const void* p) { return static_cast<uint32_t>(__cvta_generic_to_shared(p)); }
-
-__device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
-  asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count));
-}
-__device__ __forceinline__ void mbar_expect_tx(uint32_t bar, uint32_t bytes) {
-  asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
-}
-__device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
-  uint32_t ok;
-  asm volatile(
-      "{\n\t.reg .pred p;\n\t"
-      "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
-      "selp.u32 %0, 1, 0, p;\n\t}"
-      : "=r"(ok)
-      : "r"(bar), "r"(parity)
-      : "memory");
-  return ok != 0;
-}
-// Bounded wait: gives up after kWaitCycles, records `code` and returns false.
-__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, int* status, int code) {
-  if (mbar_try_wait(bar, parity)) return true;
-  const long long t0 = clock64();
-  while (!mbar_try_wait(bar, parity)) {
-    if (clock64() - t0 > kWaitCycles) {
-      atomicCAS(status, 0, code);
-      return false;
-    }
-  }
-  return true;
-}
-__device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap* map, uint32_t bar, int x, int y) {
-  asm volatile(
-      "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];" ::"r"(dst),
-      "l"(reinterpret_cast<uint64_t>(map)), "r"(bar), "r"(x), "r"(y)
-      : "memory");
-}
-__device__ __forceinline__ void prefetch_tensormap(const CUtensorMap* map) {
-  asm volatile("prefetch.tensormap [%0];" ::"l"(reinterpret_cast<uint64_t>(map)) : "memory");
-}
-__device__ __forceinline__ void tmem_alloc(uint32_t dst_smem, uint32_t cols) {
-  asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(dst_smem), "r"(cols) : "memory");
-  asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
-}
-__device__ __forceinline__ void tmem_dealloc(uint32_t taddr, uint32_t cols) {
-  asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(taddr), "r"(cols) : "memory");
-}
-__device__ __forceinline__ void umma_bf16(uint32_t tmem_d, uint64_t desc_a, uint64_t desc_b, uint32_t idesc, uint32_t accumulate) {
-  asm volatile(
-      "{\n\t.reg .pred p;\n\t"
-      "setp.ne.b32 p, %4, 0;\n\t"
-      "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}" ::"r"(tmem_d),
-      "l"(desc_a), "l"(desc_b), "r"(idesc), "r"(accumulate)
-      : "memory");
-}
-__device__ __forceinline__ void umma_commit(uint32_t bar) {
-  asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
-}
-__device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
-__device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
+// ------------------------------------------------------------------ helpers on top of tc5.cuh
 __device__ __forceinline__ void tmem_load16(uint32_t taddr, float* v) {
   uint32_t r[16];
   asm volatile(
@@ -118,26 +51,14 @@ __device__ __forceinline__ void tmem_load16(uint32_t taddr, float* v) {
         "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15])
       : "r"(taddr)
       : "memory");
-  asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+  tmem_load_wait();
 #pragma unroll
   for (int i = 0; i < 16; ++i) v[i] = __uint_as_float(r[i]);
 }
-
-// Shared-memory matrix descriptor of a K-major tile in the 128-byte swizzle: rows of 128 bytes,
-// groups of eight rows 1024 bytes apart; `byte_offset` steps along K inside the swizzle row.
-__device__ __forceinline__ uint64_t smem_desc_sw128(uint32_t smem_addr) {
-  uint64_t d = 0;
-  d |= static_cast<uint64_t>((smem_addr & 0x3FFFF) >> 4);  // start address
-  d |= static_cast<uint64_t>(0) << 16;                     // leading byte offset: unused for swizzled K-major
-  d |= static_cast<uint64_t>(1024 >> 4) << 32;             // stride byte offset between 8-row groups
-  d |= static_cast<uint64_t>(1) << 46;                     // descriptor version of sm_100
-  d |= static_cast<uint64_t>(2) << 61;                     // layout: 128-byte swizzle
-  return d;
-}
+__device__ __forceinline__ void tc_fence_before() { fence_before_sync(); }
+__device__ __forceinline__ void tc_fence_after() { fence_after_sync(); }
 // Instruction descriptor: D float32, A and B bfloat16, both K-major, M = 128, N = n.
-__device__ __forceinline__ uint32_t instr_desc(int n) {
-  return (1u << 4) | (1u << 7) | (1u << 10) | (static_cast<uint32_t>(n >> 3) << 17) | (static_cast<uint32_t>(kTileM >> 4) << 24);
-}
+__device__ __forceinline__ uint32_t instr_desc(int n) { return sb::tc5::instr_desc(kTileM, n, false); }
 
 // Rows of one accumulator tile to global memory: out[n, m] = d (kStore) or out[n, m] += d (kAdd). Each thread
 // owns output feature m and walks the tile's tokens sixteen at a time; for kAdd the residual values of the
@@ -510,60 +431,12 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
 }
 
 // ------------------------------------------------------------------ host side
-typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*,
-                                  const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
-                                  CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
-
-EncodeTiledFn encode_fn() {
-  static EncodeTiledFn fn = nullptr;
-  static std::once_flag once;
-  std::call_once(once, [] {
-    void* ptr = nullptr;
-    cudaDriverEntryPointQueryResult res;
-    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &ptr, cudaEnableDefault, &res) == cudaSuccess &&
-        res == cudaDriverEntryPointSuccess)
-      fn = reinterpret_cast<EncodeTiledFn>(ptr);
-  });
-  return fn;
-}
-
-// Tensor map of a row-major bfloat16 matrix [rows, cols] with leading dimension ld (elements) and a
-// box of box_rows x 64 elements in the 128-byte swizzle. Cached: the same buffers come back every step.
+// Tensor map of a row-major bfloat16 matrix [rows, cols] with leading dimension ld (elements) and a box of
+// box_rows x 64 elements in the 128-byte swizzle.
 bool tensor_map(const void* base, int64_t rows, int64_t cols, int64_t ld, int box_rows, CUtensorMap* out) {
-  using Key = std::tuple<const void*, int64_t, int64_t, int64_t, int>;
-  static std::map<Key, CUtensorMap> cache;
-  static std::mutex mu;
-  std::lock_guard<std::mutex> lock(mu);
-  const Key key{base, rows, cols, ld, box_rows};
-  auto it = cache.find(key);
-  if (it != cache.end()) {
-    *out = it->second;
-    return true;
-  }
-  EncodeTiledFn fn = encode_fn();
-  if (!fn) return false;
-  const cuuint64_t dims[2] = {static_cast<cuuint64_t>(cols), static_cast<cuuint64_t>(rows)};
-  const cuuint64_t strides[1] = {static_cast<cuuint64_t>(ld) * 2};
-  const cuuint32_t box[2] = {static_cast<cuuint32_t>(kTileK), static_cast<cuuint32_t>(box_rows)};
-  const cuuint32_t elem[2] = {1, 1};
-  CUtensorMap m;
-  const CUresult r = fn(&m, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(base), dims, strides, box, elem,
-                        CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
-                        CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
-  if (r != CUDA_SUCCESS) return false;
-  if (cache.size() > 4096) cache.clear();
-  cache[key] = m;
-  *out = m;
-  return true;
-}
-
-int* status_word() {
-  static int* word = nullptr;
-  static std::once_flag once;
-  std::call_once(once, [] {
-    if (cudaMalloc(&word, sizeof(int)) == cudaSuccess) cudaMemset(word, 0, sizeof(int));
-  });
-  return word;
+  const int64_t dims[2] = {cols, rows}, strides[2] = {1, ld};
+  const int box[2] = {kTileK, box_rows};
+  return tensor_map_bf16(base, 2, dims, strides, box, out);
 }
 
 }  // namespace
@@ -620,7 +493,6 @@ SB_EXPORT int sb_gemm_tc(const void* x, int64_t ldx, const void* w, int64_t ldw,
     const long long tiles = static_cast<long long>(epilogue == kSwiglu ? (half_rows + 63) / 64 : (M + kTileM - 1) / kTileM) *
                             ((n + p.block_n - 1) / p.block_n) * splits;
     if (tiles > 2 * 148 && p.block_n <= 64) p.stages = max(2, min(p.stages, (kSmemBudget + 16 * 1024) / 3 / stage_bytes));
-    if (const char* e = getenv("SB_GEMM_STAGES")) p.stages = max(2, min(p.stages, atoi(e)));
   }
   p.kblocks_per_split = (kblocks + splits - 1) / splits;
   if ((kblocks + p.kblocks_per_split - 1) / p.kblocks_per_split != splits)

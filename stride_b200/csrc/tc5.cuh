@@ -92,6 +92,7 @@ __device__ __forceinline__ void umma_commit(uint32_t bar) {
   asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
 }
 
+__device__ __forceinline__ void tmem_load_wait() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
 // 32 consecutive columns of this thread's TMEM lane (the warp reads lanes 32 * (warp % 4) ..).
 __device__ __forceinline__ void tmem_load32(uint32_t taddr, float* v) {
   uint32_t r[32];
