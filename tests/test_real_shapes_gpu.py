@@ -1,0 +1,88 @@
+"""The layer sizes of the real models (Llama 3.2 1B / 3B, Llama 3.1 8B) with one or two layers and random weights:
+the same comparisons as for the tiny configurations, so that tile edges, split-K ranges, the large vocabulary, the
+head ratio 3 and head size 128 are exercised at the sizes that are served."""
+from __future__ import annotations
+
+import pytest
+import torch
+
+import plain_llama as plain
+from conftest import bf16_noise, logit_tolerance, random_tokens
+
+pytestmark = pytest.mark.gpu
+
+ROPE = {"rope_type": "llama3", "factor": 32.0, "low_freq_factor": 1.0, "high_freq_factor": 4.0,
+        "original_max_position_embeddings": 8192}
+SHAPES = {
+    "1b": {"architectures": ["LlamaForCausalLM"], "hidden_size": 2048, "intermediate_size": 8192, "num_hidden_layers": 2,
+           "num_attention_heads": 32, "num_key_value_heads": 8, "head_dim": 64, "vocab_size": 128256, "rope_theta": 500000.0,
+           "rope_scaling": ROPE, "tie_word_embeddings": True, "rms_norm_eps": 1e-5, "max_position_embeddings": 4096},
+    "3b": {"architectures": ["LlamaForCausalLM"], "hidden_size": 3072, "intermediate_size": 8192, "num_hidden_layers": 1,
+           "num_attention_heads": 24, "num_key_value_heads": 8, "head_dim": 128, "vocab_size": 128256, "rope_theta": 500000.0,
+           "rope_scaling": ROPE, "tie_word_embeddings": True, "rms_norm_eps": 1e-5, "max_position_embeddings": 4096},
+    "8b": {"architectures": ["LlamaForCausalLM"], "hidden_size": 4096, "intermediate_size": 14336, "num_hidden_layers": 1,
+           "num_attention_heads": 32, "num_key_value_heads": 8, "head_dim": 128, "vocab_size": 128256, "rope_theta": 500000.0,
+           "rope_scaling": dict(ROPE, factor=8.0), "tie_word_embeddings": False, "rms_norm_eps": 1e-5,
+           "max_position_embeddings": 8192},
+}
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("name", ["1b", "3b", "8b"])
+def test_real_layer_sizes(name, dtype):
+    from stride_b200 import Engine, EngineOptions, StepEntry
+    from stride_b200.weights.random_init import random_tensors
+    cfg_dict = SHAPES[name]
+    # weights N(0, 0.05) and gains 1 + 0.1 N: larger than the 0.02 of a fresh model, so that attention is not uniform
+    tensors = random_tensors(cfg_dict, seed=1, std=0.05, gain_std=0.1)
+    cfg = plain.PlainConfig.from_dict(cfg_dict)
+    reqs = [random_tokens(cfg.vocab_size, n, 30 + n) for n in (300, 160)]
+    act = torch.bfloat16 if dtype == "bfloat16" else None
+    want = [plain.forward(cfg, tensors, r, torch.float32, act) for r in reqs]
+    noise = [bf16_noise(cfg, tensors, r) if act is not None else None for r in reqs]
+    eng = Engine(None, EngineOptions(dtype=dtype, max_rows=320, max_full_rows=320, max_slots=4, kv_pages=12, page_size=64,
+                                     max_context=512), config=cfg_dict, tensors=tensors)
+    cm = eng.cache
+    slots = [cm.acquire_slot() for _ in reqs]
+
+    def check(logits, i, a, b, what):
+        ref = want[i][a:b]
+        got = logits.cpu()
+        tol = logit_tolerance(dtype, ref, noise[i])
+        assert (got - ref).abs().max() <= tol, f"{name} {dtype} {what}: {(got - ref).abs().max():.3e} > {tol:.3e}"
+
+    # request 0: 257 tokens in one step (two tcgen05 tiles and a bit), then a portion of 11 beside request 1's first 150,
+    # then both decode token by token, request 1 starting a step later
+    assert cm.ensure(slots[0], 257)
+    check(eng.step([StepEntry(slots[0], 0, reqs[0][:257], list(range(257)))]), 0, 0, 257, "prompt of 257")
+    assert cm.ensure(slots[0], 268) and cm.ensure(slots[1], 140)
+    lg = eng.step([StepEntry(slots[0], 257, reqs[0][257:268], list(range(11))), StepEntry(slots[1], 0, reqs[1][:140], [0, 70, 139])])
+    check(lg[:11], 0, 257, 268, "portion of 11")
+    assert (lg[11:].cpu() - want[1][[0, 70, 139]]).abs().max() <= logit_tolerance(dtype, want[1], noise[1])
+    fed = [268, 140]
+    for k in range(12):
+        entries = []
+        for i in (0, 1):
+            if i == 1 and k == 0:
+                continue
+            n = 1 if k % 5 else 2          # now and then two tokens at once
+            n = min(n, len(reqs[i]) - fed[i])
+            if n == 0:
+                continue
+            assert cm.ensure(slots[i], fed[i] + n)
+            entries.append((i, StepEntry(slots[i], fed[i], reqs[i][fed[i]:fed[i] + n], list(range(n)))))
+        lg = eng.step([e for _, e in entries])
+        at = 0
+        for i, e in entries:
+            n = len(e.tokens)
+            check(lg[at:at + n], i, fed[i], fed[i] + n, f"decode step {k}")
+            at += n
+            fed[i] += n
+    if dtype == "bfloat16":
+        from stride_b200.kernels import ops
+        assert ops.gemm_tc_status() == 0
+        if cfg.head_dim == 64:
+            assert ops.attention_tc5_status() == 0
+    for s in slots:
+        cm.release_slot(s)
+    cm.check()
