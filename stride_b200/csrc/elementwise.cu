@@ -36,8 +36,9 @@ __global__ void embed_kernel(const int32_t* __restrict__ tokens, const TW* __res
 }
 
 // ------------------------------------------------------------------ rmsnorm
-// One block per row. The row is (h + partial_0 + partial_1 + ...), summed left to
-// right; when partials are given the sum is written back to h. Then
+// One block per row. The row is h + (partial_0 + partial_1 + ...), the partials summed left to
+// right first (as the tensor-core kernel adds its K ranges when it does so itself) and then added
+// to h; when partials are given the sum is written back to h. Then
 // r = 1/sqrt(sum(x^2)/H + eps) and out = w * (x * r). VEC = 4 reads float4 (H % 4 == 0);
 // the partials are fetched four at a time so that their loads overlap.
 template <int VEC>
@@ -71,15 +72,19 @@ __global__ void rmsnorm_kernel(float* __restrict__ h, const float* __restrict__ 
   float ss = 0.0f;
   for (int i = threadIdx.x; i < units; i += blockDim.x) {
     V v = hr[i];
-    const V* p = reinterpret_cast<const V*>(partials + static_cast<int64_t>(r) * H) + i;
-    const int64_t ps = partial_stride / VEC;
-    int s = 0;
-    for (; s + 4 <= n_partials; s += 4) {
-      const V a = p[s * ps], b = p[(s + 1) * ps], c = p[(s + 2) * ps], d = p[(s + 3) * ps];
-      v = add4(add4(add4(add4(v, a), b), c), d);
+    if (n_partials > 0) {
+      const V* p = reinterpret_cast<const V*>(partials + static_cast<int64_t>(r) * H) + i;
+      const int64_t ps = partial_stride / VEC;
+      V sum = p[0];
+      int s = 1;
+      for (; s + 4 <= n_partials; s += 4) {
+        const V a = p[s * ps], b = p[(s + 1) * ps], c = p[(s + 2) * ps], d = p[(s + 3) * ps];
+        sum = add4(add4(add4(add4(sum, a), b), c), d);
+      }
+      for (; s < n_partials; ++s) sum = add4(sum, p[s * ps]);
+      v = add4(v, sum);
+      hr[i] = v;
     }
-    for (; s < n_partials; ++s) v = add4(v, p[s * ps]);
-    if (n_partials > 0) hr[i] = v;
     reinterpret_cast<V*>(row)[i] = v;
     if constexpr (VEC == 4) {
       ss = fmaf(v.x, v.x, ss);
@@ -103,9 +108,12 @@ __global__ void rmsnorm_kernel(float* __restrict__ h, const float* __restrict__ 
 }
 
 // Many rows (a prompt portion): one warp per row, eight rows per block, no shared memory and no block barrier.
-// Pass 1 folds the partials (written back to h) and sums the squares with the lanes' sums combined by xor
-// shuffles; pass 2 re-reads the row (it is in L2) and writes the normed values. H % 4 == 0.
-template <class TW, class TO>
+// Pass 1 folds the partials (written back to h) and sums the squares; pass 2 re-reads the row (it is in L2) and
+// writes the normed values. H % 4 == 0. The squares are added in the order of rmsnorm_kernel with 32 W threads, so
+// that a row's result has the same bits whichever kernel the size of the step selects: lane l stands for that
+// kernel's threads l, l + 32, .., one chain of fused multiply-adds each, the 32 chains of a warp are combined by
+// xor shuffles and the W warps' sums are added in ascending order.
+template <class TW, class TO, int W>
 __global__ void __launch_bounds__(256) rmsnorm_rows_kernel(float* __restrict__ h, const float* __restrict__ partials,
                                                            int n_partials, int64_t partial_stride,
                                                            const TW* __restrict__ weight, TO* __restrict__ out, int n, int H,
@@ -117,18 +125,36 @@ __global__ void __launch_bounds__(256) rmsnorm_rows_kernel(float* __restrict__ h
   float4* hr = reinterpret_cast<float4*>(h + static_cast<int64_t>(r) * H);
   const int units = H / 4;
   const int64_t ps = partial_stride / 4;
-  float ss = 0.0f;
-  for (int i = lane; i < units; i += 32) {
-    float4 v = hr[i];
-    const float4* p = reinterpret_cast<const float4*>(partials + static_cast<int64_t>(r) * H) + i;
-    for (int s = 0; s < n_partials; ++s) v = add4(v, p[s * ps]);
-    if (n_partials > 0) hr[i] = v;
-    ss = fmaf(v.x, v.x, ss);
-    ss = fmaf(v.y, v.y, ss);
-    ss = fmaf(v.z, v.z, ss);
-    ss = fmaf(v.w, v.w, ss);
+  float chain[W];
+#pragma unroll
+  for (int w = 0; w < W; ++w) chain[w] = 0.0f;
+  for (int i0 = 0; i0 < units; i0 += 32 * W) {
+#pragma unroll
+    for (int w = 0; w < W; ++w) {
+      const int i = i0 + 32 * w + lane;
+      if (i < units) {
+        float4 v = hr[i];
+        if (n_partials > 0) {
+          const float4* p = reinterpret_cast<const float4*>(partials + static_cast<int64_t>(r) * H) + i;
+          float4 sum = p[0];
+          for (int s = 1; s < n_partials; ++s) sum = add4(sum, p[s * ps]);
+          v = add4(v, sum);
+          hr[i] = v;
+        }
+        chain[w] = fmaf(v.x, v.x, chain[w]);
+        chain[w] = fmaf(v.y, v.y, chain[w]);
+        chain[w] = fmaf(v.z, v.z, chain[w]);
+        chain[w] = fmaf(v.w, v.w, chain[w]);
+      }
+    }
   }
-  for (int o = 16; o > 0; o >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, o);
+  float ss = 0.0f;
+#pragma unroll
+  for (int w = 0; w < W; ++w) {
+    float c = chain[w];
+    for (int o = 16; o > 0; o >>= 1) c += __shfl_xor_sync(0xffffffffu, c, o);
+    ss = w == 0 ? c : ss + c;
+  }
   const float scale = 1.0f / sqrtf(ss / static_cast<float>(H) + eps);
   TO* o = out + static_cast<int64_t>(r) * H;
   for (int i = lane; i < units; i += 32) {
@@ -330,7 +356,11 @@ __global__ void gather_rows_kernel(const float* __restrict__ in, const float* __
   const int src = rows[blockIdx.x];
   for (int i = threadIdx.x; i < H; i += blockDim.x) {
     float v = in[static_cast<int64_t>(src) * H + i];
-    for (int s = 0; s < n_partials; ++s) v += partials[s * partial_stride + static_cast<int64_t>(src) * H + i];
+    if (n_partials > 0) {
+      float sum = partials[static_cast<int64_t>(src) * H + i];
+      for (int s = 1; s < n_partials; ++s) sum += partials[s * partial_stride + static_cast<int64_t>(src) * H + i];
+      v += sum;
+    }
     out[static_cast<int64_t>(blockIdx.x) * H + i] = v;
   }
 }
@@ -357,19 +387,30 @@ SB_EXPORT int sb_rmsnorm(float* h, const float* partials, int n_partials, int64_
   const size_t smem = static_cast<size_t>(H) * sizeof(float);
   if (smem > 200 * 1024) return sb::fail("sb_rmsnorm: width %d does not fit the row buffer (max 51200)", H);
   const bool vec = H % 4 == 0 && partial_stride % 4 == 0 && ((reinterpret_cast<uintptr_t>(h) | reinterpret_cast<uintptr_t>(partials)) & 15) == 0;
-  if (vec && n > 64 && (reinterpret_cast<uintptr_t>(out) & 15) == 0) {
-    // Note: the block sums of rmsnorm_kernel and the warp sums here add the squares in different orders; a row's
-    // normed values can differ in the last bit between a decode-sized and a prompt-sized step.
-    const dim3 grid((n + 7) / 8);
-    if (weight_dtype == 0 && out_dtype == 0) sb::launch_pdl(rmsnorm_rows_kernel<float, float>, grid, dim3(256), 0, stream, h, partials, n_partials, partial_stride, static_cast<const float*>(weight), static_cast<float*>(out), n, H, eps);
-    else if (weight_dtype == 0 && out_dtype == 1) sb::launch_pdl(rmsnorm_rows_kernel<float, bf16>, grid, dim3(256), 0, stream, h, partials, n_partials, partial_stride, static_cast<const float*>(weight), static_cast<bf16*>(out), n, H, eps);
-    else if (weight_dtype == 1 && out_dtype == 0) sb::launch_pdl(rmsnorm_rows_kernel<bf16, float>, grid, dim3(256), 0, stream, h, partials, n_partials, partial_stride, static_cast<const bf16*>(weight), static_cast<float*>(out), n, H, eps);
-    else if (weight_dtype == 1 && out_dtype == 1) sb::launch_pdl(rmsnorm_rows_kernel<bf16, bf16>, grid, dim3(256), 0, stream, h, partials, n_partials, partial_stride, static_cast<const bf16*>(weight), static_cast<bf16*>(out), n, H, eps);
-    else return sb::fail("sb_rmsnorm: unsupported dtypes weight=%d out=%d", weight_dtype, out_dtype);
-    return sb::check_launch("sb_rmsnorm");
-  }
   const int units = vec ? H / 4 : H;
   const int threads = units >= 1024 ? 1024 : units >= 512 ? 512 : units >= 256 ? 256 : 128;
+  if (vec && n > 64 && (reinterpret_cast<uintptr_t>(out) & 15) == 0) {
+    // the warp-per-row kernel adds the squares in the order of the block-per-row kernel with `threads` threads
+    const dim3 grid((n + 7) / 8);
+#define SB_ROWS_W(TW, TO, W) \
+  sb::launch_pdl(rmsnorm_rows_kernel<TW, TO, W>, grid, dim3(256), 0, stream, h, partials, n_partials, partial_stride, \
+                 static_cast<const TW*>(weight), static_cast<TO*>(out), n, H, eps)
+#define SB_ROWS(TW, TO)                          \
+  do {                                           \
+    if (threads == 1024) SB_ROWS_W(TW, TO, 32);  \
+    else if (threads == 512) SB_ROWS_W(TW, TO, 16); \
+    else if (threads == 256) SB_ROWS_W(TW, TO, 8);  \
+    else SB_ROWS_W(TW, TO, 4);                   \
+  } while (0)
+    if (weight_dtype == 0 && out_dtype == 0) SB_ROWS(float, float);
+    else if (weight_dtype == 0 && out_dtype == 1) SB_ROWS(float, bf16);
+    else if (weight_dtype == 1 && out_dtype == 0) SB_ROWS(bf16, float);
+    else if (weight_dtype == 1 && out_dtype == 1) SB_ROWS(bf16, bf16);
+    else return sb::fail("sb_rmsnorm: unsupported dtypes weight=%d out=%d", weight_dtype, out_dtype);
+#undef SB_ROWS
+#undef SB_ROWS_W
+    return sb::check_launch("sb_rmsnorm");
+  }
 #define SB_NORM_V(TW, TO, VEC)                                                                                   \
   do {                                                                                                           \
     if (smem > 48 * 1024)                                                                                        \

@@ -13,8 +13,13 @@
 //   kAdd     out[n, m] += d            (the residual add)
 //   kSwiglu  out[n, j]  = silu(g) * u  (bfloat16; the tile holds 64 gate rows and their
 //                                      64 up rows, exchanged through shared memory)
-// Split-K partials are summed by the consumer in ascending order, so the order of every
-// sum is fixed by the launch shape alone. Rows or columns of a tile that lie outside the
+// The K ranges of a weight depend on its shape alone (sb_gemm_tc_splits), never on the number of
+// tokens: every range is accumulated from zero in tensor memory and the ranges' sums are added in
+// float32 in ascending order, by the consumer of the partial buffers (up to 128 tokens: one CTA per
+// range, so that a few tokens still occupy the GPU) or inside gemm_tc_fold_kernel (more tokens: a
+// CTA walks a tile's ranges through two accumulators while eight epilogue warps add them up in
+// registers). A token's result therefore has the same bits whatever the size of its batch.
+// Rows or columns of a tile that lie outside the
 // matrix are zero-filled by TMA and masked in the epilogue, so M, N and K need not be
 // multiples of the tile (K must be a multiple of 8: TMA strides are multiples of 16 bytes).
 //
@@ -430,6 +435,150 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
   }
 }
 
+// Many tokens and a weight that is cut into K ranges: persistent CTAs, each walking tiles of 128 weight rows by
+// BN tokens; a tile's ranges go through the two accumulators in turn (each range accumulated from zero, as a CTA of
+// the single-tile kernel does it), and eight epilogue warps (a lane quarter and a half of the columns each) add the
+// ranges in ascending order in registers and store the sum (a residual add is left to the consumer, as with few
+// tokens: reading the old values here would stall the epilogue on their latency).
+constexpr int kFoldThreads = 64 + 256;
+constexpr int kFoldCols = 128;            // columns per epilogue thread: BN / 2 <= 128
+
+__global__ void __launch_bounds__(kFoldThreads, 1)
+gemm_tc_fold_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUtensorMap map_x, const GemmParams p) {
+  extern __shared__ __align__(1024) uint8_t smem_raw[];
+  __shared__ __align__(8) uint64_t full_bar[kMaxStages];
+  __shared__ __align__(8) uint64_t empty_bar[kMaxStages];
+  __shared__ __align__(8) uint64_t accum_full[2];
+  __shared__ __align__(8) uint64_t accum_empty[2];
+  __shared__ uint32_t tmem_base_s;
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int BN = p.block_n;
+  const int stage_bytes = kStageA + BN * 128;
+  const uint32_t smem0 = (smem_u32(smem_raw) + 1023u) & ~1023u;
+  const int kblocks = (p.K + kTileK - 1) / kTileK;
+  const int total_tiles = p.tiles_m * p.tiles_n;
+  const uint32_t tmem_cols = 2 * BN < 32 ? 32 : 2 * BN;
+
+  if (threadIdx.x == 0) {
+    prefetch_tensormap(&map_w);
+    prefetch_tensormap(&map_x);
+    for (int s = 0; s < p.stages; ++s) {
+      mbar_init(smem_u32(&full_bar[s]), 1);
+      mbar_init(smem_u32(&empty_bar[s]), 1);
+    }
+    for (int a = 0; a < 2; ++a) {
+      mbar_init(smem_u32(&accum_full[a]), 1);
+      mbar_init(smem_u32(&accum_empty[a]), 8);   // one arrival per epilogue warp
+    }
+    mbar_init_fence();
+  }
+  if (warp == 1) tmem_alloc(smem_u32(&tmem_base_s), tmem_cols);
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = tmem_base_s;
+
+  sb::grid_launch_dependents();
+  if (warp == 0) {
+    if (lane == 0) {
+      // ---------------- producer: the K blocks of a tile in ascending order (its ranges are consecutive)
+      sb::grid_dependency_wait();
+      int it = 0;
+      for (int tile = blockIdx.x; tile < total_tiles; tile += gridDim.x) {
+        const int tile_m = tile % p.tiles_m, tile_n = tile / p.tiles_m;
+        for (int i = 0; i < kblocks; ++i, ++it) {
+          const int slot = it % p.stages;
+          if (it >= p.stages) mbar_wait(smem_u32(&empty_bar[slot]), ((it / p.stages) - 1) & 1, p.status, 1);
+          const uint32_t bar = smem_u32(&full_bar[slot]);
+          const uint32_t a = smem0 + slot * stage_bytes;
+          mbar_expect_tx(bar, stage_bytes);
+          tma_load_2d(a, &map_w, bar, i * kTileK, tile_m * kTileM);
+          tma_load_2d(a + kStageA, &map_x, bar, i * kTileK, tile_n * BN);
+        }
+      }
+    }
+  } else if (warp == 1) {
+    if (lane == 0) {
+      // ---------------- MMA issuer: range q of this CTA (counted over all its tiles) fills accumulator q & 1
+      const uint32_t idesc = instr_desc(BN);
+      int it = 0, q = 0;
+      for (int tile = blockIdx.x; tile < total_tiles; tile += gridDim.x) {
+        for (int r = 0; r < p.splits; ++r, ++q) {
+          const int kb0 = r * p.kblocks_per_split;
+          const int iters = min(kblocks, kb0 + p.kblocks_per_split) - kb0;
+          const int acc = q & 1;
+          if (q >= 2) mbar_wait(smem_u32(&accum_empty[acc]), ((q >> 1) - 1) & 1, p.status, 4);
+          tc_fence_after();
+          const uint32_t tmem_d = tmem_base + acc * BN;
+          for (int i = 0; i < iters; ++i, ++it) {
+            const int slot = it % p.stages;
+            mbar_wait(smem_u32(&full_bar[slot]), (it / p.stages) & 1, p.status, 2);
+            tc_fence_after();
+            const uint32_t a = smem0 + slot * stage_bytes, b = a + kStageA;
+            const uint64_t da = smem_desc_sw128(a), db = smem_desc_sw128(b);
+#pragma unroll
+            for (int k = 0; k < kTileK / 16; ++k) umma_bf16(tmem_d, da + 2 * k, db + 2 * k, idesc, (i > 0 || k > 0) ? 1u : 0u);
+            umma_commit(smem_u32(&empty_bar[slot]));
+          }
+          umma_commit(smem_u32(&accum_full[acc]));
+        }
+      }
+    }
+    __syncwarp();
+  } else {
+    // ---------------- epilogue: warps 2..9; warp w reads TMEM lanes 32 * (w % 4) .. and columns [half * BN / 2, ..)
+    const int quarter = warp & 3, half = (warp - 2) >> 2;
+    const int cols = BN / 2;
+    sb::grid_dependency_wait();
+    int q = 0;
+    for (int tile = blockIdx.x; tile < total_tiles; tile += gridDim.x) {
+      const int tile_m = tile % p.tiles_m, tile_n = tile / p.tiles_m;
+      const int m = tile_m * kTileM + quarter * 32 + lane;
+      const int n0 = tile_n * BN + half * cols;
+      const bool live = m < p.M;
+      float* o = p.out + static_cast<int64_t>(n0) * p.ldo + m;
+      float run[kFoldCols];
+#pragma unroll 1
+      for (int r = 0; r < p.splits; ++r, ++q) {
+        const int acc = q & 1;
+        mbar_wait(smem_u32(&accum_full[acc]), (q >> 1) & 1, p.status, 3);
+        tc_fence_after();
+        const uint32_t tmem_d = tmem_base + acc * BN + half * cols + (static_cast<uint32_t>(quarter * 32) << 16);
+        if (r == 0) {
+#pragma unroll
+          for (int c0 = 0; c0 < kFoldCols; c0 += 16)
+            if (c0 < cols) tmem_load16(tmem_d + c0, run + c0);
+        } else {
+#pragma unroll
+          for (int c0 = 0; c0 < kFoldCols; c0 += 16) {
+            if (c0 < cols) {
+              float v[16];
+              tmem_load16(tmem_d + c0, v);
+#pragma unroll
+              for (int c = 0; c < 16; ++c) run[c0 + c] += v[c];
+            }
+          }
+        }
+        tc_fence_before();
+        __syncwarp();
+        if (lane == 0) mbar_arrive(smem_u32(&accum_empty[acc]));
+      }
+      if (live) {
+#pragma unroll
+        for (int c = 0; c < kFoldCols; ++c)
+          if (c < cols && n0 + c < p.N) o[static_cast<int64_t>(c) * p.ldo] = run[c];
+      }
+    }
+    tc_fence_before();
+  }
+  __syncthreads();
+  if (warp == 1) {
+    tc_fence_after();
+    tmem_dealloc(tmem_base, tmem_cols);
+  }
+}
+
 // ------------------------------------------------------------------ host side
 // Tensor map of a row-major bfloat16 matrix [rows, cols] with leading dimension ld (elements) and a box of
 // box_rows x 64 elements in the 128-byte swizzle.
@@ -441,25 +590,27 @@ bool tensor_map(const void* base, int64_t rows, int64_t cols, int64_t ld, int bo
 
 }  // namespace
 
-// The number of K ranges this library uses for a [M, K] weight applied to n tokens: enough CTAs to
-// occupy the GPU when the weight alone gives too few tiles, limited so that the partial sums stay
-// small beside the weight. The caller sizes its partial buffer [splits, n, M] with it.
-SB_EXPORT int sb_gemm_tc_splits(int n, int M, int K) {
+// The number of K ranges of a [M, K] weight: enough CTAs to occupy the GPU with a few tokens when the weight
+// alone gives too few tiles, limited so that the partial sums stay small beside the weight. It depends on the
+// weight's shape alone, so that a token's sums have the same order in every batch.
+SB_EXPORT int sb_gemm_tc_splits(int M, int K) {
   const int tiles_m = (M + kTileM - 1) / kTileM;
   const int kblocks = (K + kTileK - 1) / kTileK;
-  if (n > 128) return 1;
-  const int n_pad = n <= 16 ? 16 : n <= 32 ? 32 : n <= 64 ? 64 : 128;
   int splits = 148 / tiles_m;   // at most one wave of CTAs
-  (void)n_pad;                  // the partial sums stay in L2 until their consumer reads them, whatever n is
   splits = min(splits, kblocks / 2);
   splits = max(splits, 1);
   const int per = (kblocks + splits - 1) / splits;
   return (kblocks + per - 1) / per;
 }
 
+// The most tokens for which sb_gemm_tc leaves one partial buffer per K range; with more it adds the ranges itself.
+SB_EXPORT int sb_gemm_tc_partial_tokens() { return 128; }
+
 // out = x . W^T on the tensor cores.
-//   epilogue 0: out float32 [n, ldo] (+ split * split_stride), `splits` K ranges (from sb_gemm_tc_splits, or 1)
-//   epilogue 1: out float32 [n, ldo] += result (splits must be 1)
+//   epilogue 0: out float32 [n, ldo]; `splits` K ranges (sb_gemm_tc_splits, or 1). Up to sb_gemm_tc_partial_tokens()
+//               tokens, range s is stored at out + s * split_stride and the caller adds the ranges in ascending
+//               order; with more tokens the kernel adds them itself and stores the sum at out.
+//   epilogue 1: out float32 [n, ldo] += result (one range)
 //   epilogue 2: W is [2 * half_rows, K] (gate rows then up rows); out bfloat16 [n, ldo] = silu(gate) * up
 SB_EXPORT int sb_gemm_tc(const void* x, int64_t ldx, const void* w, int64_t ldw, void* out, int64_t ldo, int n, int M, int K,
                          int epilogue, int splits, int64_t split_stride, int half_rows, cudaStream_t stream) {
@@ -469,7 +620,9 @@ SB_EXPORT int sb_gemm_tc(const void* x, int64_t ldx, const void* w, int64_t ldw,
   if ((reinterpret_cast<uintptr_t>(x) | reinterpret_cast<uintptr_t>(w)) & 15)
     return sb::fail("sb_gemm_tc: operands must be 16-byte aligned");
   if (epilogue < 0 || epilogue > 2) return sb::fail("sb_gemm_tc: unknown epilogue %d", epilogue);
-  if (epilogue != kStore && splits != 1) return sb::fail("sb_gemm_tc: only the plain store supports split-K");
+  const bool fold = splits > 1 && n > 128;   // the kernel adds the ranges
+  if (epilogue == kSwiglu && splits != 1) return sb::fail("sb_gemm_tc: the SwiGLU epilogue takes no K ranges");
+  if (epilogue == kAdd && splits != 1) return sb::fail("sb_gemm_tc: the sum of K ranges is added to the residual by its consumer (plain store)");
   if (epilogue == kSwiglu && (half_rows <= 0 || M != 2 * half_rows)) return sb::fail("sb_gemm_tc: swiglu needs M = 2 * half_rows");
   const int kblocks = (K + kTileK - 1) / kTileK;
   if (splits < 1 || splits > kblocks) return sb::fail("sb_gemm_tc: %d splits for %d blocks of K", splits, kblocks);
@@ -508,9 +661,20 @@ SB_EXPORT int sb_gemm_tc(const void* x, int64_t ldx, const void* w, int64_t ldw,
   p.tiles_m = epilogue == kSwiglu ? (half_rows + 63) / 64 : (M + kTileM - 1) / kTileM;
   p.tiles_n = (n + p.block_n - 1) / p.block_n;
   p.splits = splits;
-  const long long total_tiles = static_cast<long long>(p.tiles_m) * p.tiles_n * splits;
+  const long long total_tiles = static_cast<long long>(p.tiles_m) * p.tiles_n * (fold ? 1 : splits);
   if (total_tiles > (1ll << 30)) return sb::fail("sb_gemm_tc: too many tiles");
   const size_t smem = static_cast<size_t>(p.stages) * stage_bytes + 1024;
+  if (fold) {
+    const dim3 grid(static_cast<unsigned>(min(total_tiles, 148ll)));
+    static bool attr_set = false;
+    if (!attr_set) {
+      if (cudaFuncSetAttribute(gemm_tc_fold_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBudget + 2048) != cudaSuccess)
+        return sb::fail("sb_gemm_tc: cannot raise the shared memory limit");
+      attr_set = true;
+    }
+    sb::launch_pdl(gemm_tc_fold_kernel, grid, dim3(kFoldThreads), smem, stream, map_w, map_x, p);
+    return sb::check_launch("sb_gemm_tc");
+  }
   // Persistent CTAs: as many as fit the GPU at once (by shared and tensor memory), each walking tiles.
   int per_sm = static_cast<int>((227 * 1024) / (smem + 2048));
   per_sm = max(1, min(per_sm, 512 / max(32, 2 * p.block_n)));

@@ -6,9 +6,11 @@ bfloat16 engine: bfloat16 activations and weights with float32 accumulation on t
 tensor cores (`csrc/gemm_tc.cu`); a weight stored in float32, or a K that TMA cannot
 address (not a multiple of 8), falls back to the SIMT kernel, which takes any size.
 
-With few tokens the tensor-core kernel may cut K into ranges to fill the GPU and leave one
-partial sum per range; `forward_partials` and `forward_add` hand those to the consumer (the
-rotation kernel, the next norm), which adds them in ascending order.
+The tensor-core kernel cuts the K of a small weight into ranges (a function of the weight's shape
+alone) whose sums are added in float32 in ascending order. With few tokens it leaves one partial
+sum per range, so that the ranges run on different SMs; `forward_partials` and `forward_add` hand
+those to the consumer (the rotation kernel, the next norm), which adds them. With many tokens the
+kernel adds them itself, in the same order: a token's result has the same bits either way.
 """
 from __future__ import annotations
 
@@ -26,6 +28,7 @@ class Linear:
         self.compute_dtype = compute_dtype
         self.tensor_core = (compute_dtype == torch.bfloat16 and self.weight.dtype == torch.bfloat16
                             and self.in_features % 8 == 0)
+        self.splits = ops.gemm_tc_splits(self.out_features, self.in_features) if self.tensor_core else 1
 
     def weight_bytes(self) -> int:
         return self.weight.numel() * self.weight.element_size()
@@ -37,13 +40,11 @@ class Linear:
         """Elements of the largest partial buffer `forward_partials` may need for up to max_tokens tokens."""
         rows = max_tokens
         if self.tensor_core:
-            for n in (16, 32, 64, 128):
-                if n <= max(16, max_tokens):
-                    rows = max(rows, n * ops.gemm_tc_splits(n, self.out_features, self.in_features))
+            rows = max(rows, min(max_tokens, ops.gemm_tc_partial_tokens()) * self.splits)
         return rows * self.out_features
 
     def forward(self, x: torch.Tensor, out: torch.Tensor) -> None:
-        """out[n, out_features] float32 = x . W^T."""
+        """out[n, out_features] float32 = x . W^T, K in one range whatever the weight's shape."""
         if self._tc(x):
             ops.gemm_tc(x, self.weight, out, ops.STORE)
         else:
@@ -52,22 +53,27 @@ class Linear:
     def forward_partials(self, x: torch.Tensor, flat: torch.Tensor) -> torch.Tensor:
         """x . W^T as [S, n, out_features] float32 partial sums (S >= 1) carved from the flat buffer `flat`."""
         n, M = x.shape[0], self.out_features
-        S = ops.gemm_tc_splits(n, M, self.in_features) if self._tc(x) else 1
-        out = flat[:S * n * M].view(S, n, M)
-        if self._tc(x):
-            ops.gemm_tc(x, self.weight, out, ops.STORE, splits=S)
-        else:
+        if not self._tc(x):
+            out = flat[:n * M].view(1, n, M)
             ops.gemm_f32(x, self.weight, out[0], accumulate=False)
+            return out
+        S = self.splits if n <= ops.gemm_tc_partial_tokens() else 1     # buffers left; the ranges stay the same
+        out = flat[:S * n * M].view(S, n, M)
+        ops.gemm_tc(x, self.weight, out if S > 1 else out[0], ops.STORE, splits=self.splits)
         return out
 
     def forward_add(self, x: torch.Tensor, stream, flat: torch.Tensor = None) -> None:
-        """stream += x . W^T (the residual add); with `flat` given, split-K partials may be left pending."""
+        """stream += x . W^T (the residual add). With `flat` given, K is cut into the weight's ranges and, for few
+        tokens, their partial sums are left pending on the stream; without it K stays one range. A call site
+        must choose one of the two for good: the order of the sums differs."""
         if self._tc(x):
-            n, M = x.shape[0], self.out_features
-            S = ops.gemm_tc_splits(n, M, self.in_features) if flat is not None else 1
+            n, M, S = x.shape[0], self.out_features, self.splits if flat is not None else 1
             if S > 1:
-                parts = flat[:S * n * M].view(S, n, M)
-                ops.gemm_tc(x, self.weight, parts, ops.STORE, splits=S)
+                # few tokens: one partial sum per range; many: the ranges' sum. Either way the stream's next
+                # consumer computes h + (range_0 + range_1 + ...).
+                P = S if n <= ops.gemm_tc_partial_tokens() else 1
+                parts = flat[:P * n * M].view(P, n, M)
+                ops.gemm_tc(x, self.weight, parts if P > 1 else parts[0], ops.STORE, splits=S)
                 stream.set_pending(parts)
                 return
             stream.fold()

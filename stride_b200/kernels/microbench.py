@@ -41,11 +41,11 @@ def gemm(a) -> dict:
     copies = a.copies or max(1, min(64, (2 * L2_BYTES) // (M * K * 2) + 1))
     ws = [(torch.randn(M, K, device="cuda") * 0.02).bfloat16() for _ in range(copies)]
     x = torch.randn(n, K, device="cuda").bfloat16()
-    S = ops.gemm_tc_splits(n, M, K) if epi == ops.STORE else 1
+    S = ops.gemm_tc_splits(M, K) if epi != ops.SWIGLU and (epi == ops.STORE or n > ops.gemm_tc_partial_tokens()) else 1
     if epi == ops.SWIGLU:
         out = torch.zeros(n, M // 2, device="cuda", dtype=torch.bfloat16)
     else:
-        out = torch.zeros((S, n, M) if S > 1 else (n, M), device="cuda")
+        out = torch.zeros((S, n, M) if S > 1 and n <= ops.gemm_tc_partial_tokens() else (n, M), device="cuda")
     state = {"i": 0}
 
     def run():

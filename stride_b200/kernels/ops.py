@@ -178,21 +178,30 @@ def sample_temperature(logits, temperatures, seeds, lengths, tokens, values, sca
 STORE, ADD, SWIGLU = 0, 1, 2
 
 
-def gemm_tc_splits(n: int, M: int, K: int) -> int:
-    """How many K ranges `gemm_tc` uses for a [M, K] weight and n tokens (sizes the partial buffer)."""
+def gemm_tc_splits(M: int, K: int) -> int:
+    """How many K ranges `gemm_tc` cuts a [M, K] weight into: a function of the weight's shape alone."""
     lib = library("gemm_tc")
-    lib.sb_gemm_tc_splits.argtypes = [c_int, c_int, c_int]
+    lib.sb_gemm_tc_splits.argtypes = [c_int, c_int]
     lib.sb_gemm_tc_splits.restype = c_int
-    return lib.sb_gemm_tc_splits(n, M, K)
+    return lib.sb_gemm_tc_splits(M, K)
+
+
+def gemm_tc_partial_tokens() -> int:
+    """Up to this many tokens `gemm_tc` leaves one partial buffer per K range; with more it adds the ranges itself."""
+    lib = library("gemm_tc")
+    lib.sb_gemm_tc_partial_tokens.restype = c_int
+    return lib.sb_gemm_tc_partial_tokens()
 
 
 def gemm_tc(x: torch.Tensor, weight: torch.Tensor, out: torch.Tensor, epilogue: int = STORE, splits: int = 1,
             half_rows: int = 0) -> None:
     """out = x . weight^T on the tcgen05 tensor cores; x [n, K] and weight [M, K] bfloat16.
 
-    STORE: out float32 [n, M], or [splits, n, M] partial sums over K ranges when splits > 1.
-    ADD: out float32 [n, M] += result. SWIGLU: weight is [2 I, K] (gate rows, then up rows) and
-    out bfloat16 [n, I] = silu(x . gate^T) * (x . up^T).
+    STORE: out float32 [n, M]. With splits > 1 (= gemm_tc_splits) and at most gemm_tc_partial_tokens() tokens, out is
+    [splits, n, M]: one partial sum per K range, to be added in ascending order; with more tokens the kernel adds the
+    ranges itself, in the same order, and out is [n, M].
+    ADD: out float32 [n, M] += result (one range only).
+    SWIGLU: weight is [2 I, K] (gate rows, then up rows) and out bfloat16 [n, I] = silu(x . gate^T) * (x . up^T).
     """
     _cuda(x, weight, out)
     if x.dtype != torch.bfloat16 or weight.dtype != torch.bfloat16:
@@ -206,9 +215,9 @@ def gemm_tc(x: torch.Tensor, weight: torch.Tensor, out: torch.Tensor, epilogue: 
     M = weight.shape[0]
     if weight.shape[1] != K:
         raise ValueError(f"gemm_tc shapes: x {tuple(x.shape)}, weight {tuple(weight.shape)}")
-    if splits > 1:
+    if splits > 1 and n <= gemm_tc_partial_tokens():
         if out.dim() != 3 or out.shape[0] != splits:
-            raise ValueError("gemm_tc with split-K writes [splits, n, M]")
+            raise ValueError("gemm_tc with K ranges and few tokens writes [splits, n, M]")
         ldo, split_stride = out.stride(1), out.stride(0)
     else:
         o2 = out[0] if out.dim() == 3 else out

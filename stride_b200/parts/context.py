@@ -81,9 +81,11 @@ class ResidualStream:
     def fold(self) -> None:
         """Add pending partial sums now (used by parts that want `h` itself)."""
         p = self.take_pending()
-        if p is not None:
-            for s in range(p.shape[0]):
-                self.h.add_(p[s])
+        if p is not None:      # h + (p0 + p1 + ...), the order of the kernels that fold partials themselves
+            total = p[0]
+            for s in range(1, p.shape[0]):
+                total = total + p[s]
+            self.h.add_(total)
 
     def add_(self, update: torch.Tensor) -> None:
         """h += update, for parts that compute their output as a separate tensor."""

@@ -34,12 +34,17 @@ def test_gemm_tc_store_and_add(n, M, K):
     ops.gemm_tc(x, w, acc, ops.ADD)
     assert ops.gemm_tc_status() == 0
     assert (acc - (base + ref)).abs().max() <= tol
-    splits = ops.gemm_tc_splits(n, M, K)
-    if splits > 1:
+    splits = ops.gemm_tc_splits(M, K)
+    if splits > 1 and n <= ops.gemm_tc_partial_tokens():
         parts = torch.full((splits, n, M), float("nan"), device=DEV)
         ops.gemm_tc(x, w, parts, ops.STORE, splits=splits)
         assert ops.gemm_tc_status() == 0
         assert (parts.sum(0) - ref).abs().max() <= tol
+    elif splits > 1:    # the kernel adds the ranges itself
+        out = torch.full((n, M), float("nan"), device=DEV)
+        ops.gemm_tc(x, w, out, ops.STORE, splits=splits)
+        assert ops.gemm_tc_status() == 0
+        assert (out - ref).abs().max() <= tol
 
 
 def test_gemm_tc_one_hot_positions():
@@ -71,19 +76,37 @@ def test_gemm_tc_swiglu(n, I, K):
     assert (out.float() - ref).abs().max() <= 1e-2 * float(ref.abs().max()) + 1e-4
 
 
-def test_gemm_tc_does_not_depend_on_the_batch():
-    """A token's result has the same bits alone, among 7 and among 200 other tokens (same split-K)."""
+@pytest.mark.parametrize("M,K", [(384, 1024), (2048, 2048), (200, 8192), (1000, 136)])
+def test_gemm_tc_does_not_depend_on_the_batch(M, K):
+    """A token's result has the same bits alone, among 7, 100, 200 and 700 other tokens, wherever it stands among
+    them: with K in one range, and with the weight's K ranges added by the caller (few tokens) or by the kernel (many)."""
     from stride_b200.kernels import ops
-    M, K = 384, 1024
     w = _rand(M, K, seed=7, scale=0.05, dtype=torch.bfloat16)
-    x = _rand(200, K, seed=8, dtype=torch.bfloat16)
-    outs = []
-    for n in (1, 8, 200):
+    x = _rand(700, K, seed=8, dtype=torch.bfloat16)
+    S, few = ops.gemm_tc_splits(M, K), ops.gemm_tc_partial_tokens()
+    one, ranged = [], []
+    for n, at in ((1, 0), (8, 5), (100, 77), (200, 130), (700, 699)):
+        xs = x[:n].clone()
+        xs[at] = x[0]
         out = torch.zeros(n, M, device=DEV)
-        ops.gemm_tc(x[:n].contiguous(), w, out, ops.STORE)
-        outs.append(out[0].clone())
+        ops.gemm_tc(xs, w, out, ops.STORE)
+        one.append(out[at].clone())
+        if S > 1:
+            if n <= few:
+                parts = torch.zeros(S, n, M, device=DEV)
+                ops.gemm_tc(xs, w, parts, ops.STORE, splits=S)
+                total = parts[0, at].clone()
+                for s in range(1, S):
+                    total += parts[s, at]
+            else:
+                out = torch.zeros(n, M, device=DEV)
+                ops.gemm_tc(xs, w, out, ops.STORE, splits=S)
+                total = out[at].clone()
+            ranged.append(total)
     assert ops.gemm_tc_status() == 0
-    assert torch.equal(outs[0], outs[1]) and torch.equal(outs[0], outs[2])
+    for group in (one, ranged):
+        for other in group[1:]:
+            assert torch.equal(group[0], other)
 
 
 # ---------------------------------------------------------------------------- attention
@@ -212,11 +235,29 @@ def test_rmsnorm_with_partials(n, H):
         hh = h.clone()
         out = torch.zeros(n, H, dtype=out_dtype, device=DEV)
         ops.rmsnorm(hh, w, 1e-5, out, partials=parts)
-        x = ((h + parts[0]) + parts[1]) + parts[2]
+        x = h + ((parts[0] + parts[1]) + parts[2])
         assert torch.equal(hh, x)
         ref = w.float() * (x * (1.0 / torch.sqrt((x * x).sum(-1, keepdim=True) / H + 1e-5)))
         tol = 1e-5 if out_dtype == torch.float32 else 1e-2
         assert (out.float() - ref).abs().max() <= tol * float(ref.abs().max())
+
+
+@pytest.mark.parametrize("H", [64, 264, 1024, 2048, 3072, 4096, 8192])
+def test_rmsnorm_does_not_depend_on_the_batch(H):
+    """A row's normed values have the same bits in a step of 3 rows (one block per row) and of 300 (one warp per row)."""
+    from stride_b200.kernels import ops
+    h = _rand(300, H, seed=4, scale=3.0)
+    parts = _rand(2, 300, H, seed=5)
+    w = _rand(H, seed=6, dtype=torch.bfloat16)
+    for out_dtype in (torch.float32, torch.bfloat16):
+        outs = []
+        for n in (3, 64, 65, 300):
+            hh = h[:n].clone()
+            out = torch.zeros(n, H, dtype=out_dtype, device=DEV)
+            ops.rmsnorm(hh, w, 1e-5, out, partials=parts[:, :n].contiguous())
+            outs.append(out[:3].clone())
+        for other in outs[1:]:
+            assert torch.equal(outs[0], other)
 
 
 def test_embed_swiglu_gather():
@@ -235,7 +276,7 @@ def test_embed_swiglu_gather():
     parts = _rand(2, 9, 272, seed=3)
     got = torch.zeros(3, 272, device=DEV)
     ops.gather_rows(gu, rows, got, partials=parts)
-    assert torch.equal(got, ((gu + parts[0]) + parts[1])[rows.long()])
+    assert torch.equal(got, (gu + (parts[0] + parts[1]))[rows.long()])
 
 
 @pytest.mark.parametrize("n,M,K,wdtype", [(5, 77, 33, torch.float32), (70, 130, 200, torch.bfloat16), (1, 1000, 64, torch.bfloat16)])

@@ -86,3 +86,52 @@ def test_real_layer_sizes(name, dtype):
     for s in slots:
         cm.release_slot(s)
     cm.check()
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_bits_do_not_depend_on_the_batch(dtype):
+    """With the 1B layer sizes (whose attention and down projections are cut into K ranges): a request fed in the same
+    portions has the same logits, bit for bit, alone and among other requests, whatever their number, their order in
+    the batch, the size of the step (2 tokens or 400) and the pages it gets."""
+    from stride_b200 import Engine, EngineOptions, StepEntry
+    from stride_b200.weights.random_init import random_tensors
+    cfg_dict = SHAPES["1b"]
+    tensors = random_tensors(cfg_dict, seed=2, std=0.05, gain_std=0.1)
+    vocab = cfg_dict["vocab_size"]
+    mine = random_tokens(vocab, 90, 5)
+    others = [random_tokens(vocab, 450, 6 + i) for i in range(5)]
+    cuts = [(0, 70), (70, 75), (75, 76), (76, 77), (77, 79), (79, 80)] + [(p, p + 1) for p in range(80, 90)]
+
+    def run(seed, company):
+        """company[k]: for step k a list of (other request, tokens it brings), placed before or after mine."""
+        eng = Engine(None, EngineOptions(dtype=dtype, max_rows=512, max_full_rows=96, max_slots=8, kv_pages=48, page_size=64,
+                                         max_context=512, kv_shuffle_seed=seed), config=cfg_dict, tensors=tensors)
+        cm = eng.cache
+        slots = {}
+        fed = {}
+        out = []
+        for k, (a, b) in enumerate(cuts):
+            entries = []
+            for j, n in company[k] if k < len(company) else []:
+                if j not in slots:
+                    slots[j], fed[j] = cm.acquire_slot(), 0
+                assert cm.ensure(slots[j], fed[j] + n)
+                entries.append(StepEntry(slots[j], fed[j], others[j][fed[j]:fed[j] + n], []))
+                fed[j] += n
+            if "me" not in slots:
+                slots["me"] = cm.acquire_slot()
+            assert cm.ensure(slots["me"], b)
+            me = StepEntry(slots["me"], a, mine[a:b], list(range(b - a)))
+            at = (k * 7 + seed) % (len(entries) + 1)
+            entries.insert(at, me)
+            out.append(eng.step(entries).clone())
+        return torch.cat(out)
+
+    alone = run(0, [])
+    decoders = [[(j, 40)] for j in range(3)]                         # three others start ..
+    decoders = [sum(decoders, [])] + [[(0, 1), (1, 1), (2, 1)]] * 20    # .. and then decode beside me
+    among_decoders = run(3, decoders)
+    big = [[(0, 150)], [(1, 300), (0, 1)], [(2, 60), (1, 1)], [(3, 399)], [(4, 130), (3, 1)]] + [[(0, 1), (4, 200)]] + [[(0, 1), (1, 1), (2, 1), (3, 1)]] * 12
+    among_prompts = run(11, big)
+    assert torch.equal(alone, among_decoders)
+    assert torch.equal(alone, among_prompts)

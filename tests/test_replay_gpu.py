@@ -36,6 +36,22 @@ def _compare(got, want, dtype, what, noise=None):
     assert diff.max() <= tol, f"{what}: max |diff| {diff.max():.3e} > {tol:.3e}, first bad place {int((diff.max(dim=1).values > tol).nonzero()[0])}, worst {worst}"
 
 
+class _Bits:
+    """Keeps the logits of the first replay of every request and checks that later replays, cut and batched in other
+    ways and lying in other pages, give the same bits: in 32-bit every kernel adds in an order that depends on the
+    token's own position alone."""
+
+    def __init__(self, exact):
+        self.exact, self.first = exact, {}
+
+    def check(self, i, a, got, what):
+        if not self.exact:
+            return
+        for k in range(got.shape[0]):
+            ref = self.first.setdefault((i, a + k), got[k].clone())
+            assert torch.equal(ref, got[k]), f"{what}: position {a + k} differs in bits from its first replay (max {(ref - got[k]).abs().max():.3e})"
+
+
 def _portions(n, sizes):
     """Cut range(n) into portions of the given sizes (cycled), the last one may be shorter but never 1 token
     unless n forces it."""
@@ -62,25 +78,30 @@ def test_replay_modes(name, dtype, model_dirs, tmp_path):
     longest = sorted((per(len(r)) for r in reqs), reverse=True)
     pool = max(longest[0] + longest[1] + page, 4 * page)
     tr = TraceRun(model_dirs[name], dtype, tmp_path, pool, page, extra=("--kv-shuffle", "7"))
+    bits = _Bits(dtype == "float32")
     try:
         # 1. each request alone and whole, logits at every place
         for i, r in enumerate(reqs):
             s = tr.run([(f"w{i}", r, range(len(r)))], end=[f"w{i}"])
             _compare(tr.logits(s, vocab), want[i][0], dtype, f"{name} whole request {i}", want[i][1])
+            bits.check(i, 0, tr.logits(s, vocab), f"{name} whole request {i}")
         # 2. all but the last 32 tokens in one step, then one by one
         for i, r in enumerate(reqs):
             cut = max(1, len(r) - 32)
             s = tr.run([(f"d{i}", r[:cut], [cut - 1])])
             _compare(tr.logits(s, vocab), want[i][0][cut - 1:cut], dtype, f"{name} request {i} prefill end", want[i][1])
+            bits.check(i, cut - 1, tr.logits(s, vocab), f"{name} request {i} prefill end")
             for p in range(cut, len(r)):
                 s = tr.run([(f"d{i}", r[p:p + 1], [0])], end=[f"d{i}"] if p == len(r) - 1 else [])
                 _compare(tr.logits(s, vocab), want[i][0][p:p + 1], dtype, f"{name} request {i} decode at {p}", want[i][1])
+                bits.check(i, p, tr.logits(s, vocab), f"{name} request {i} decode at {p}")
         # 3. portions of changing size, down to two tokens
         for i, r in enumerate(reqs):
             cuts = _portions(len(r), [7, 2, 19, 3, 2, 31, 5])
             for j, (a, b) in enumerate(cuts):
                 s = tr.run([(f"p{i}", r[a:b], range(b - a))], end=[f"p{i}"] if j == len(cuts) - 1 else [])
                 _compare(tr.logits(s, vocab), want[i][0][a:b], dtype, f"{name} request {i} portion {a}:{b}", want[i][1])
+                bits.check(i, a, tr.logits(s, vocab), f"{name} request {i} portion {a}:{b}")
         # 4. mixed: requests start at different steps, portions beside single tokens, pages reused
         fed = [0] * len(reqs)
         sizes = [[9, 1, 1, 4, 1], [2, 13, 1, 1, 1, 6], [5, 1, 1, 1], [17, 1, 2, 1, 1], [3, 1, 8, 1]]
@@ -108,6 +129,7 @@ def test_replay_modes(name, dtype, model_dirs, tmp_path):
             at = 0
             for i, a, b in spans:
                 _compare(got[at:at + b - a], want[i][0][a:b], dtype, f"{name} mixed step {steps} request {i} {a}:{b}", want[i][1])
+                bits.check(i, a, got[at:at + b - a], f"{name} mixed step {steps} request {i} {a}:{b}")
                 at += b - a
             steps += 1
     finally:
