@@ -8,19 +8,24 @@
 //
 // * attn_chunk_kernel: prompt portions. One CTA (4 warps, 16 rows each) per (64-row tile
 //   of an entry, key/value head); it walks the key tiles [64 t, 64 t + 64) that any of its
-//   rows can see, with the usual running maximum and sum, and writes the finished rows.
+//   rows can see and writes the finished rows.
 // * attn_decode_kernel: entries whose rows fit one 16-row tile (a decoded token, or a very
 //   short portion). One CTA per (entry, key/value head, chunk of 256 absolute key
-//   positions); each of its 4 warps takes 64 of the keys, the four results are merged in
-//   warp order, and the chunk's (max, sum, weighted values) go to scratch memory.
-//   attn_combine_kernel then folds an entry's chunks in ascending order and writes bfloat16.
-//   Chunks are cut by absolute position, never by page or by batch, so a token's arithmetic
-//   is the same whatever else the step holds.
+//   positions); each of its 4 warps takes one 64-key tile, the four results are folded in
+//   key order, and the chunk's (max, sum, weighted values) go to scratch memory. The CTA
+//   that finishes an entry's last chunk (or attn_combine_kernel) folds the chunks in
+//   ascending order and writes bfloat16.
+//
+// Both follow the arithmetic of attention_math.cuh (tiles of 64 keys, chunks of 256, cut by
+// absolute position, each folded from an empty state), as does the tcgen05 kernel of
+// attention_tc5.cu: a row's result has the same bits whichever kernel computes it, whatever
+// else the step holds and however the request was cut into steps.
 //
 // Keys and values come from the paged cache through the request's block table
 // ([pages][2][Hkv][page_size][D] per layer); a key tile may span several pages.
 // Counterparts in arhaamatiq/stride: AttentionPage / AttentionCombine with KvT = bfloat16
 // (src/kernel_common.h:90-309), which are scalar.
+#include "attention_math.cuh"
 #include "common.cuh"
 #include "noalloc.h"
 
@@ -30,16 +35,9 @@ namespace {
 
 using bf16 = __nv_bfloat16;
 
-constexpr int kKeys = 64;        // keys per tile
-constexpr int kChunk = 256;      // keys per decode chunk (4 warps x 64)
-constexpr float kLog2e = 1.4426950408889634f;
-
-// 2^x by the hardware's approximation (two units in the last place); exp2f adds a slow path for subnormals.
-__device__ __forceinline__ float fast_exp2(float x) {
-  float y;
-  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
-  return y;
-}
+using namespace sb::attn;
+constexpr int kKeys = kTileKeys;    // keys per tile
+constexpr int kChunk = kChunkKeys;  // keys per chunk (4 tiles; the decode kernel gives each warp one)
 
 struct AttnTcParams {
   const bf16* q;     // [n][Hq * D]
@@ -119,9 +117,9 @@ __device__ __forceinline__ void load_kv_tiles(bf16* dstK, bf16* dstV, const bf16
   }
 }
 
-// S[16 x 64] = Q[16 x D] K^T for one warp; q fragments in registers, K tile in shared memory.
+// S[16 x 64] = Q[16 x D] K^T for one warp; Q rows at sQ (16 rows of this warp) and the K tile in shared memory.
 template <int D>
-__device__ __forceinline__ void qk_tile(float (*s)[4], const uint32_t (*qf)[4], const bf16* sK, int lane) {
+__device__ __forceinline__ void qk_tile(float (*s)[4], const bf16* sQ, const bf16* sK, int lane) {
   constexpr int LD = D + 8;
 #pragma unroll
   for (int nt = 0; nt < 8; ++nt)
@@ -130,34 +128,33 @@ __device__ __forceinline__ void qk_tile(float (*s)[4], const uint32_t (*qf)[4], 
   const int mi = lane >> 3, rr = lane & 7;
 #pragma unroll
   for (int ks = 0; ks < D / 16; ++ks) {
+    uint32_t qf[4];
+    ldsm_x4(qf, smem_u32(sQ + (lane & 15) * LD + ks * 16 + (lane >> 4) * 8));
 #pragma unroll
     for (int nt = 0; nt < 8; nt += 2) {
       uint32_t b[4];
       ldsm_x4(b, smem_u32(sK + (nt * 8 + (mi >> 1) * 8 + rr) * LD + ks * 16 + (mi & 1) * 8));
-      mma_16816(s[nt], qf[ks], b[0], b[1]);
-      mma_16816(s[nt + 1], qf[ks], b[2], b[3]);
+      mma_16816(s[nt], qf, b[0], b[1]);
+      mma_16816(s[nt + 1], qf, b[2], b[3]);
     }
   }
 }
 
-// O[16 x D] += P[16 x 64] V[64 x D]; P given as the float accumulators of qk_tile after exponentiation.
-// The softmax weights stay (nearly) 32-bit: each is split into a bfloat16 head and a bfloat16 remainder,
-// p = hi + lo with |p - hi - lo| <= 2^-17 p, and both parts are multiplied with V. With the head alone the
-// weights would carry a rounding of 2^-9 that the 32-bit softmax of the reference does not have.
+// O[16 x D] = P[16 x 64] V[64 x D] from zero; P given as float weights in the layout of qk_tile's accumulators.
+// Each weight enters as two bfloat16 parts (split_hi_lo), hi . V then lo . V for every step of 16 keys.
 template <int D>
 __device__ __forceinline__ void pv_tile(float (*o)[4], const float (*s)[4], const bf16* sV, int lane) {
   constexpr int LD = D + 8;
   const int mi = lane >> 3, rr = lane & 7;
 #pragma unroll
+  for (int dt = 0; dt < D / 8; ++dt)
+#pragma unroll
+    for (int x = 0; x < 4; ++x) o[dt][x] = 0.0f;
+#pragma unroll
   for (int kk = 0; kk < 4; ++kk) {
     uint32_t hi[4], lo[4];
 #pragma unroll
-    for (int x = 0; x < 4; ++x) {
-      const float p0 = s[2 * kk + (x >> 1)][(x & 1) * 2], p1 = s[2 * kk + (x >> 1)][(x & 1) * 2 + 1];
-      const __nv_bfloat162 h = __floats2bfloat162_rn(p0, p1);
-      hi[x] = *reinterpret_cast<const uint32_t*>(&h);
-      lo[x] = pack_bf16(p0 - __low2float(h), p1 - __high2float(h));
-    }
+    for (int x = 0; x < 4; ++x) split_hi_lo(s[2 * kk + (x >> 1)][(x & 1) * 2], s[2 * kk + (x >> 1)][(x & 1) * 2 + 1], hi[x], lo[x]);
 #pragma unroll
     for (int dt = 0; dt < D / 8; dt += 2) {
       uint32_t b[4];
@@ -170,6 +167,65 @@ __device__ __forceinline__ void pv_tile(float (*o)[4], const float (*s)[4], cons
   }
 }
 
+// One tile for one warp: s holds the raw scores of keys key0 .. key0 + 63 for the thread's two rows (gid, gid + 8)
+// and leaves their weights; m_t, l_t, o_t are the tile's maximum, sum and weighted values per row.
+template <int D>
+__device__ __forceinline__ void tile_partial(float (*s)[4], float (*o_t)[4], float* m_t, float* l_t, int key0, const int* row_pos,
+                                             const int* row_lo, float c, const bf16* sV, int lane) {
+  const int tq = lane & 3;
+  float mx[2] = {-INFINITY, -INFINITY};
+#pragma unroll
+  for (int nt = 0; nt < 8; ++nt)
+#pragma unroll
+    for (int x = 0; x < 4; ++x) {
+      const int h = x >> 1;
+      const int key = key0 + nt * 8 + tq * 2 + (x & 1);
+      if (!(key <= row_pos[h] && key >= row_lo[h])) s[nt][x] = -INFINITY;
+      mx[h] = fmaxf(mx[h], s[nt][x]);
+    }
+  float ref[2], u[2] = {0.0f, 0.0f};
+#pragma unroll
+  for (int h = 0; h < 2; ++h) {
+    mx[h] = fmaxf(mx[h], __shfl_xor_sync(0xffffffffu, mx[h], 1));
+    mx[h] = fmaxf(mx[h], __shfl_xor_sync(0xffffffffu, mx[h], 2));
+    m_t[h] = tile_max(mx[h], c);
+    ref[h] = tile_ref(m_t[h]);
+  }
+  // this thread holds class tq of its rows' keys, in ascending order
+#pragma unroll
+  for (int nt = 0; nt < 8; ++nt)
+#pragma unroll
+    for (int x = 0; x < 4; ++x) {
+      const int h = x >> 1;
+      const float p = s[nt][x] == -INFINITY ? 0.0f : weight(s[nt][x], c, ref[h]);
+      s[nt][x] = p;
+      u[h] = __fadd_rn(u[h], p);
+    }
+#pragma unroll
+  for (int h = 0; h < 2; ++h) {
+    u[h] = __fadd_rn(u[h], __shfl_xor_sync(0xffffffffu, u[h], 1));
+    l_t[h] = __fadd_rn(u[h], __shfl_xor_sync(0xffffffffu, u[h], 2));
+  }
+  pv_tile<D>(o_t, s, sV, lane);
+}
+
+// Folds a part into a state, row by row of the thread's two rows; rows whose part is empty are left alone.
+template <int D>
+__device__ __forceinline__ void fold_rows(float* m, float* l, float (*o)[4], const float* m_t, const float* l_t, const float (*o_t)[4]) {
+#pragma unroll
+  for (int h = 0; h < 2; ++h) {
+    if (m_t[h] == -INFINITY) continue;
+    const FoldFactors f = fold_factors(m[h], m_t[h]);
+    l[h] = fold_value(l[h], l_t[h], f);
+#pragma unroll
+    for (int dt = 0; dt < D / 8; ++dt) {
+      o[dt][2 * h] = fold_value(o[dt][2 * h], o_t[dt][2 * h], f);
+      o[dt][2 * h + 1] = fold_value(o[dt][2 * h + 1], o_t[dt][2 * h + 1], f);
+    }
+    m[h] = f.m;
+  }
+}
+
 // ------------------------------------------------------------------ prompt portions
 template <int D>
 __global__ void __launch_bounds__(128) attn_chunk_kernel(const AttnTcParams p) {
@@ -178,6 +234,7 @@ __global__ void __launch_bounds__(128) attn_chunk_kernel(const AttnTcParams p) {
   bf16* sQ = reinterpret_cast<bf16*>(smem_raw);  // [64][LD]
   bf16* sK = sQ + 64 * LD;                       // [2][64][LD]
   bf16* sV = sK + 2 * 64 * LD;                   // [2][64][LD]
+  float* sT = reinterpret_cast<float*>(sV + 2 * 64 * LD);   // [64][D]: the rows' weighted values over the finished chunks
 
   sb::grid_launch_dependents();
   sb::grid_dependency_wait();
@@ -217,87 +274,85 @@ __global__ void __launch_bounds__(128) attn_chunk_kernel(const AttnTcParams p) {
     row_pos[h] = pi < npos ? pos0 + pi : -1;
     row_lo[h] = p.window > 0 ? row_pos[h] - p.window + 1 : 0;
   }
-  float m[2] = {-INFINITY, -INFINITY}, l[2] = {0.0f, 0.0f};
-  float o[D / 8][4];
+  // the chunk in progress (registers) and the chunks before it (maximum and sum in registers, values in sT,
+  // every element of which belongs to one thread)
+  float m_c[2] = {-INFINITY, -INFINITY}, l_c[2] = {0.0f, 0.0f}, m_r[2] = {-INFINITY, -INFINITY}, l_r[2] = {0.0f, 0.0f};
+  float o_c[D / 8][4];
 #pragma unroll
   for (int dt = 0; dt < D / 8; ++dt)
 #pragma unroll
-    for (int x = 0; x < 4; ++x) o[dt][x] = 0.0f;
-  uint32_t qf[D / 16][4];
+    for (int x = 0; x < 4; ++x) {
+      o_c[dt][x] = 0.0f;
+      sT[(warp * 16 + gid + 8 * (x >> 1)) * D + dt * 8 + tq * 2 + (x & 1)] = 0.0f;
+    }
 
   for (int kt = kt0; kt <= kt1; ++kt) {
     const int buf = (kt - kt0) & 1;
     cp_wait<0>();
     __syncthreads();
-    if (kt == kt0) {
-#pragma unroll
-      for (int ks = 0; ks < D / 16; ++ks)
-        ldsm_x4(qf[ks], smem_u32(sQ + (warp * 16 + (lane & 15)) * LD + ks * 16 + (lane >> 4) * 8));
-    }
     if (kt < kt1) {
       load_kv_tiles<D>(sK + (buf ^ 1) * 64 * LD, sV + (buf ^ 1) * 64 * LD, kplane, p.v_offset, table, p.page_size, p.page_shift,
                        p.page_stride, (kt + 1) * kKeys, key_lo, pos_hi, tid, 128);
       cp_commit();
     }
-    float s[8][4];
-    qk_tile<D>(s, qf, sK + buf * 64 * LD, lane);
-    // scale, mask, running softmax (base 2)
-    float mx[2] = {-INFINITY, -INFINITY};
-#pragma unroll
-    for (int nt = 0; nt < 8; ++nt)
-#pragma unroll
-      for (int x = 0; x < 4; ++x) {
-        const int h = x >> 1;
-        const int key = kt * kKeys + nt * 8 + tq * 2 + (x & 1);
-        const bool ok = key <= row_pos[h] && key >= row_lo[h];
-        s[nt][x] = ok ? s[nt][x] * p.scale_log2 : -INFINITY;
-        mx[h] = fmaxf(mx[h], s[nt][x]);
-      }
-    float alpha[2], m_use[2];
-#pragma unroll
-    for (int h = 0; h < 2; ++h) {
-      mx[h] = fmaxf(mx[h], __shfl_xor_sync(0xffffffffu, mx[h], 1));
-      mx[h] = fmaxf(mx[h], __shfl_xor_sync(0xffffffffu, mx[h], 2));
-      const float m_new = fmaxf(m[h], mx[h]);
-      m_use[h] = m_new == -INFINITY ? 0.0f : m_new;
-      alpha[h] = fast_exp2(m[h] - m_use[h]);
-      m[h] = m_new;
-      l[h] *= alpha[h];
+    {
+      float s[8][4], o_t[D / 8][4], m_t[2], l_t[2];
+      qk_tile<D>(s, sQ + warp * 16 * LD, sK + buf * 64 * LD, lane);
+      tile_partial<D>(s, o_t, m_t, l_t, kt * kKeys, row_pos, row_lo, p.scale_log2, sV + buf * 64 * LD, lane);
+      fold_rows<D>(m_c, l_c, o_c, m_t, l_t, o_t);
     }
+    if ((kt + 1) % (kChunk / kKeys) == 0 || kt == kt1) {
+      // the chunk is complete: fold it into the row's state and start an empty one
 #pragma unroll
-    for (int nt = 0; nt < 8; ++nt)
+      for (int h = 0; h < 2; ++h) {
+        if (m_c[h] != -INFINITY) {
+          const FoldFactors f = fold_factors(m_r[h], m_c[h]);
+          l_r[h] = fold_value(l_r[h], l_c[h], f);
+          float* row = sT + (warp * 16 + gid + 8 * h) * D + tq * 2;
 #pragma unroll
-      for (int x = 0; x < 4; ++x) {
-        const float e2 = fast_exp2(s[nt][x] - m_use[x >> 1]);
-        s[nt][x] = e2;
-        l[x >> 1] += e2;
+          for (int dt = 0; dt < D / 8; ++dt) {
+            row[dt * 8] = fold_value(row[dt * 8], o_c[dt][2 * h], f);
+            row[dt * 8 + 1] = fold_value(row[dt * 8 + 1], o_c[dt][2 * h + 1], f);
+          }
+          m_r[h] = f.m;
+        }
+        m_c[h] = -INFINITY;
+        l_c[h] = 0.0f;
+#pragma unroll
+        for (int dt = 0; dt < D / 8; ++dt) o_c[dt][2 * h] = o_c[dt][2 * h + 1] = 0.0f;
       }
-#pragma unroll
-    for (int dt = 0; dt < D / 8; ++dt) {
-      o[dt][0] *= alpha[0];
-      o[dt][1] *= alpha[0];
-      o[dt][2] *= alpha[1];
-      o[dt][3] *= alpha[1];
     }
-    pv_tile<D>(o, s, sV + buf * 64 * LD, lane);
   }
 #pragma unroll
   for (int h = 0; h < 2; ++h) {
-    l[h] += __shfl_xor_sync(0xffffffffu, l[h], 1);
-    l[h] += __shfl_xor_sync(0xffffffffu, l[h], 2);
     const int r = warp * 16 + gid + 8 * h;
     const int pi = r / G, hh = r % G;
     if (pi < npos) {
-      const float inv = 1.0f / l[h];
+      const float* row = sT + r * D + tq * 2;
       bf16* dst = p.out + (static_cast<int64_t>(row0 + pi) * p.Hq + g * G + hh) * D;
 #pragma unroll
       for (int dt = 0; dt < D / 8; ++dt)
-        *reinterpret_cast<uint32_t*>(dst + dt * 8 + tq * 2) = pack_bf16(o[dt][2 * h] * inv, o[dt][2 * h + 1] * inv);
+        *reinterpret_cast<uint32_t*>(dst + dt * 8 + tq * 2) = pack_bf16(finish(row[dt * 8], l_r[h]), finish(row[dt * 8 + 1], l_r[h]));
     }
   }
 }
 
 // ------------------------------------------------------------------ decoded tokens
+// Folds the records of chunks c0..c1 of one (entry, key/value head) for element (r, d) and returns the finished value.
+template <int D>
+__device__ __forceinline__ float fold_chunks(const float* part_o, const float* part_ml, int64_t rec0, int c0, int c1, int r, int d) {
+  float m = -INFINITY, l = 0.0f, o = 0.0f;
+  for (int c = c0; c <= c1; ++c) {
+    const float m_c = __ldcg(&part_ml[((rec0 + c) * 16 + r) * 2]);
+    if (m_c == -INFINITY) continue;
+    const FoldFactors f = fold_factors(m, m_c);
+    l = fold_value(l, __ldcg(&part_ml[((rec0 + c) * 16 + r) * 2 + 1]), f);
+    o = fold_value(o, __ldcg(&part_o[(rec0 + c) * 16 * D + r * D + d]), f);
+    m = f.m;
+  }
+  return finish(o, l);
+}
+
 template <int D>
 __global__ void __launch_bounds__(128) attn_decode_kernel(const AttnTcParams p) {
   constexpr int LD = D + 8, CH = D / 8;
@@ -349,17 +404,10 @@ __global__ void __launch_bounds__(128) attn_decode_kernel(const AttnTcParams p) 
   cp_wait<0>();
   __syncthreads();
 
-  float m[2] = {-INFINITY, -INFINITY}, l[2] = {0.0f, 0.0f};
-  float o[D / 8][4];
-#pragma unroll
-  for (int dt = 0; dt < D / 8; ++dt)
-#pragma unroll
-    for (int x = 0; x < 4; ++x) o[dt][x] = 0.0f;
+  // every warp computes the tile of its 64 keys
+  float m_t[2] = {-INFINITY, -INFINITY}, l_t[2] = {0.0f, 0.0f};
+  float o_t[D / 8][4];
   if (any) {
-    uint32_t qf[D / 16][4];
-#pragma unroll
-    for (int ks = 0; ks < D / 16; ++ks)
-      ldsm_x4(qf[ks], smem_u32(sQ + (lane & 15) * LD + ks * 16 + (lane >> 4) * 8));
     int row_pos[2], row_lo[2];
 #pragma unroll
     for (int h = 0; h < 2; ++h) {
@@ -368,72 +416,47 @@ __global__ void __launch_bounds__(128) attn_decode_kernel(const AttnTcParams p) 
       row_lo[h] = p.window > 0 ? row_pos[h] - p.window + 1 : 0;
     }
     float s[8][4];
-    qk_tile<D>(s, qf, sK, lane);
+    qk_tile<D>(s, sQ, sK, lane);
+    tile_partial<D>(s, o_t, m_t, l_t, key0, row_pos, row_lo, p.scale_log2, sV, lane);
+  } else {
 #pragma unroll
-    for (int nt = 0; nt < 8; ++nt)
+    for (int dt = 0; dt < D / 8; ++dt)
 #pragma unroll
-      for (int x = 0; x < 4; ++x) {
-        const int h = x >> 1;
-        const int key = key0 + nt * 8 + tq * 2 + (x & 1);
-        const bool ok = key <= row_pos[h] && key >= row_lo[h];
-        s[nt][x] = ok ? s[nt][x] * p.scale_log2 : -INFINITY;
-        m[h] = fmaxf(m[h], s[nt][x]);
-      }
-#pragma unroll
-    for (int h = 0; h < 2; ++h) {
-      m[h] = fmaxf(m[h], __shfl_xor_sync(0xffffffffu, m[h], 1));
-      m[h] = fmaxf(m[h], __shfl_xor_sync(0xffffffffu, m[h], 2));
-    }
-#pragma unroll
-    for (int nt = 0; nt < 8; ++nt)
-#pragma unroll
-      for (int x = 0; x < 4; ++x) {
-        const float mu = m[x >> 1] == -INFINITY ? 0.0f : m[x >> 1];
-        const float e2 = fast_exp2(s[nt][x] - mu);
-        s[nt][x] = e2;
-        l[x >> 1] += e2;
-      }
-#pragma unroll
-    for (int h = 0; h < 2; ++h) {
-      l[h] += __shfl_xor_sync(0xffffffffu, l[h], 1);
-      l[h] += __shfl_xor_sync(0xffffffffu, l[h], 2);
-    }
-    pv_tile<D>(o, s, sV, lane);
+      for (int x = 0; x < 4; ++x) o_t[dt][x] = 0.0f;
   }
-  // every warp leaves (m, l, O) of its 64 keys; they are merged in warp order
   __syncthreads();   // all warps are done with their key/value tiles, whose space the results take
 #pragma unroll
   for (int h = 0; h < 2; ++h) {
     const int r = gid + 8 * h;
     if (tq == 0) {
-      sML[(warp * 16 + r) * 2] = m[h];
-      sML[(warp * 16 + r) * 2 + 1] = l[h];
+      sML[(warp * 16 + r) * 2] = m_t[h];
+      sML[(warp * 16 + r) * 2 + 1] = l_t[h];
     }
 #pragma unroll
     for (int dt = 0; dt < D / 8; ++dt) {
-      sO[(warp * 16 + r) * D + dt * 8 + tq * 2] = o[dt][2 * h];
-      sO[(warp * 16 + r) * D + dt * 8 + tq * 2 + 1] = o[dt][2 * h + 1];
+      sO[(warp * 16 + r) * D + dt * 8 + tq * 2] = o_t[dt][2 * h];
+      sO[(warp * 16 + r) * D + dt * 8 + tq * 2 + 1] = o_t[dt][2 * h + 1];
     }
   }
   __syncthreads();
+  // the chunk's record: its tiles folded in key order into an empty state
   const int64_t rec = (static_cast<int64_t>(item) * p.Hkv + g) * p.chunks + chunk;
   for (int idx = tid; idx < rows * D; idx += 128) {
     const int r = idx / D, d = idx % D;
-    float mm = -INFINITY;
-#pragma unroll
-    for (int w = 0; w < 4; ++w) mm = fmaxf(mm, sML[(w * 16 + r) * 2]);
-    const float mu = mm == -INFINITY ? 0.0f : mm;
-    float acc = 0.0f, ll = 0.0f;
+    float m = -INFINITY, l = 0.0f, o = 0.0f;
 #pragma unroll
     for (int w = 0; w < 4; ++w) {
-      const float f = fast_exp2(sML[(w * 16 + r) * 2] - mu);
-      acc += sO[(w * 16 + r) * D + d] * f;
-      ll += sML[(w * 16 + r) * 2 + 1] * f;
+      const float m_w = sML[(w * 16 + r) * 2];
+      if (m_w == -INFINITY) continue;
+      const FoldFactors f = fold_factors(m, m_w);
+      l = fold_value(l, sML[(w * 16 + r) * 2 + 1], f);
+      o = fold_value(o, sO[(w * 16 + r) * D + d], f);
+      m = f.m;
     }
-    p.part_o[rec * 16 * D + idx] = acc;
+    p.part_o[rec * 16 * D + idx] = o;
     if (d == 0) {
-      p.part_ml[(rec * 16 + r) * 2] = mm;
-      p.part_ml[(rec * 16 + r) * 2 + 1] = ll;
+      p.part_ml[(rec * 16 + r) * 2] = m;
+      p.part_ml[(rec * 16 + r) * 2 + 1] = l;
     }
   }
   if (p.counters == nullptr) return;
@@ -453,15 +476,8 @@ __global__ void __launch_bounds__(128) attn_decode_kernel(const AttnTcParams p) 
   const int64_t rec0 = (static_cast<int64_t>(item) * p.Hkv + g) * p.chunks;
   for (int idx = tid; idx < rows * D; idx += 128) {
     const int r = idx / D, d = idx % D;
-    float mm = -INFINITY;
-    for (int c = c0; c <= c1; ++c) mm = fmaxf(mm, __ldcg(&p.part_ml[((rec0 + c) * 16 + r) * 2]));
-    float acc = 0.0f, ll = 0.0f;
-    for (int c = c0; c <= c1; ++c) {
-      const float f = fast_exp2(__ldcg(&p.part_ml[((rec0 + c) * 16 + r) * 2]) - mm);
-      acc += __ldcg(&p.part_o[(rec0 + c) * 16 * D + r * D + d]) * f;
-      ll += __ldcg(&p.part_ml[((rec0 + c) * 16 + r) * 2 + 1]) * f;
-    }
-    p.out[(static_cast<int64_t>(first_row + r / G) * p.Hq + g * G + r % G) * D + d] = __float2bfloat16_rn(acc / ll);
+    p.out[(static_cast<int64_t>(first_row + r / G) * p.Hq + g * G + r % G) * D + d] =
+        __float2bfloat16_rn(fold_chunks<D>(p.part_o, p.part_ml, rec0, c0, c1, r, d));
   }
 }
 
@@ -477,24 +493,16 @@ __global__ void __launch_bounds__(D) attn_combine_kernel(const AttnTcParams p) {
   const int key_lo = p.window > 0 ? max(0, first_pos - p.window + 1) : 0;
   const int c0 = key_lo / kChunk, c1 = pos_hi / kChunk;
   const int64_t rec0 = (static_cast<int64_t>(item) * p.Hkv + g) * p.chunks;
-  for (int r = 0; r < L * G; ++r) {
-    float mm = -INFINITY;
-    for (int c = c0; c <= c1; ++c) mm = fmaxf(mm, p.part_ml[((rec0 + c) * 16 + r) * 2]);
-    float acc = 0.0f, ll = 0.0f;
-    for (int c = c0; c <= c1; ++c) {
-      const float f = fast_exp2(p.part_ml[((rec0 + c) * 16 + r) * 2] - mm);
-      acc += p.part_o[(rec0 + c) * 16 * D + r * D + d] * f;
-      ll += p.part_ml[((rec0 + c) * 16 + r) * 2 + 1] * f;
-    }
-    p.out[(static_cast<int64_t>(first_row + r / G) * p.Hq + g * G + r % G) * D + d] = __float2bfloat16_rn(acc / ll);
-  }
+  for (int r = 0; r < L * G; ++r)
+    p.out[(static_cast<int64_t>(first_row + r / G) * p.Hq + g * G + r % G) * D + d] =
+        __float2bfloat16_rn(fold_chunks<D>(p.part_o, p.part_ml, rec0, c0, c1, r, d));
 }
 
 template <int D>
 int launch(const AttnTcParams& p, int n_tiles, int n_items, cudaStream_t stream) {
   constexpr int LD = D + 8;
   if (n_tiles > 0) {
-    const size_t smem = static_cast<size_t>(5) * 64 * LD * sizeof(bf16);
+    const size_t smem = static_cast<size_t>(5) * 64 * LD * sizeof(bf16) + static_cast<size_t>(64) * D * sizeof(float);
     static bool set = false;
     if (!set) {
       if (cudaFuncSetAttribute(attn_chunk_kernel<D>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess)

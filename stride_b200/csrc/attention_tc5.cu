@@ -2,21 +2,26 @@
 //
 // One CTA per (tile of 128 query rows of an entry, key/value head). The query heads that share the key/value
 // head are stacked as rows: row r is (position r / G, head r % G), G = Hq / Hkv, so a tile covers 128 / G
-// positions. The CTA walks the key tiles [128 t, 128 t + 128) its rows can see:
+// positions. The CTA walks the spans of 128 keys [128 t, 128 t + 128) its rows can see:
 //
 //   control warp (one thread): TMA loads of the query tile (a 3-D box over [token][head][64]) and of the key
-//     and value tiles, page by page through the block table, into 128-byte-swizzled shared memory (three
+//     and value spans, page by page through the block table, into 128-byte-swizzled shared memory (three
 //     buffers); S = Q K^T by tcgen05.mma (M 128, N 128, K 64) into one of two TMEM accumulators, issued one
-//     tile ahead so that it runs under the softmax of the tile before; O_t = P V by tcgen05.mma (M 128, N 64,
-//     K 128, V as an MN-major operand straight from its [key][64] page layout).
-//   eight softmax warps (two threads per row, TMEM lane = row, each with half of the tile's keys and half of the
-//     output): read S with tcgen05.ld, scale, mask by position, keep the running maximum and sum in float32, write the weights to shared memory as two bfloat16 parts
-//     (p = hi + lo, so the value product sees nearly 32-bit weights, as the reference's 32-bit softmax does),
-//     then fold O_t into the row's float32 output registers: o = o * 2^(m_old - m_new) + O_t.
+//     span ahead so that it runs under the softmax of the span before; O_0 = P_0 V_0 and O_1 = P_1 V_1 for the
+//     span's two tiles of 64 keys by tcgen05.mma (M 128, N 64, K 64, V as an MN-major operand straight from
+//     its [key][64] page layout), each into an accumulator of its own, from zero.
+//   eight softmax warps (two threads per row, TMEM lane = row; thread `half` owns the span's tile `half` and
+//     the output elements [32 half, 32 half + 32)): read S with tcgen05.ld, take the tile's maximum, write the
+//     weights to shared memory as two bfloat16 parts (p = hi + lo, so the value product sees nearly 32-bit
+//     weights, as the reference's 32-bit softmax does), then fold O_0 and O_1 into the row's chunk state and,
+//     every 256 keys, the chunk into the row's state, all in float32 registers.
 //
-// Every mbarrier wait is bounded and reports through a status word. Key tiles past a request's last page are
-// read from its last page instead (finite data, masked by position), so no unallocated page is touched.
+// The arithmetic is that of attention_math.cuh, shared with the mma.sync kernels of attention_tc.cu: a row has
+// the same bits from either. Every mbarrier wait is bounded and reports through a status word. Key spans past
+// a request's last page are read from its last page instead (finite data, masked by position), so no
+// unallocated page is touched.
 // Counterpart in arhaamatiq/stride: AttentionPage / AttentionCombine (src/kernel_common.h:90-309), scalar.
+#include "attention_math.cuh"
 #include "tc5.cuh"
 
 SB_DEFINE_LAST_ERROR()
@@ -32,19 +37,15 @@ constexpr int kKeys = 128;
 constexpr int kTileBytes = 128 * 128;   // 128 rows of 64 bfloat16
 constexpr int kSoftmaxThreads = 256;    // two threads per row: each takes 64 of the tile's 128 keys and 32 of the 64 outputs
 constexpr int kThreads = kSoftmaxThreads + 32;
-constexpr float kLog2e = 1.4426950408889634f;
 constexpr int kStages = 3;              // key/value tiles in flight
 // shared memory: Q | K x kStages | V x kStages | P hi (two 64-key halves) | P lo
 constexpr int kPhiTile = 1 + 2 * kStages, kPloTile = kPhiTile + 2;
 constexpr int kSmemBytes = (kPloTile + 2) * kTileBytes;
 constexpr int kPagesCached = 512;       // block-table entries of the request kept in shared memory
-constexpr uint32_t kTmemCols = 512;     // S0 [0,128) S1 [128,256) O_t [256,320)
+constexpr uint32_t kTmemCols = 512;     // S0 [0,128) S1 [128,256) O of tile 0 [256,320) O of tile 1 [320,384)
+using namespace sb::attn;
+static_assert(kKeys == 2 * kTileKeys && kChunkKeys == 2 * kKeys, "a span is two tiles, a chunk two spans");
 
-__device__ __forceinline__ float fast_exp2(float x) {
-  float y;
-  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
-  return y;
-}
 __device__ __forceinline__ void softmax_barrier() { asm volatile("bar.sync 1, 256;" ::: "memory"); }
 
 struct Fa5Params {
@@ -67,7 +68,7 @@ attn_prefill_tc5_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_
   __shared__ __align__(8) uint64_t q_full, kv_full[kStages], s_full[2], p_full, o_full;
   __shared__ uint32_t tmem_base_s;
   __shared__ int32_t pages_s[kPagesCached];
-  __shared__ float xch[2][kRows];          // the two halves of a row exchange their maximum, and at the end their sum
+  __shared__ float2 xch[2][2][kRows];      // [span parity][tile][row]: the tile's maximum and sum, for the row's other thread
 
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   const uint32_t smem0 = (smem_u32(smem_raw) + 1023u) & ~1023u;
@@ -161,9 +162,10 @@ attn_prefill_tc5_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_
         const uint64_t dv = dV + (i % kStages) * kTileStep;
 #pragma unroll
         for (int ks = 0; ks < kKeys / 16; ++ks) {
-          const uint64_t pa = (ks >> 2) * kTileStep + 2 * (ks & 3);     // the 64-key half of P, the K step inside it
-          umma_bf16(tmem_base + 2 * kKeys, dPhi + pa, dv + ks * kVStep, idesc_pv, ks > 0 ? 1u : 0u);
-          umma_bf16(tmem_base + 2 * kKeys, dPlo + pa, dv + ks * kVStep, idesc_pv, 1u);
+          const uint64_t pa = (ks >> 2) * kTileStep + 2 * (ks & 3);     // the tile's half of P, the K step inside it
+          const uint32_t d = tmem_base + 2 * kKeys + (ks >> 2) * kD;     // the tile's accumulator
+          umma_bf16(d, dPhi + pa, dv + ks * kVStep, idesc_pv, (ks & 3) > 0 ? 1u : 0u);
+          umma_bf16(d, dPlo + pa, dv + ks * kVStep, idesc_pv, 1u);
         }
         umma_commit(smem_u32(&o_full));
         mbar_wait(smem_u32(&o_full), i & 1, p.status, 4);     // then this tile's key/value buffers are free
@@ -173,26 +175,29 @@ attn_prefill_tc5_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_
     __syncwarp();
   } else {
     // ------------------------------------------------ softmax: two threads per row of the tile (= TMEM lane);
-    // thread `half` takes keys [64 half, 64 half + 64) of every key tile and outputs [32 half, 32 half + 32)
+    // thread `half` takes keys [64 half, 64 half + 64) of every span (one tile) and outputs [32 half, 32 half + 32)
     const int r = tid & (kRows - 1), half = tid >> 7;
     const int pi = r / G, hh = r % G;
     const bool valid = pi < npos;
     const int row_pos = valid ? pos0 + pi : -1;
     const int row_lo = p.window > 0 ? row_pos - p.window + 1 : 0;
     const uint32_t lane_addr = static_cast<uint32_t>((warp & 3) * 32) << 16;
-    float m = -INFINITY, l = 0.0f;
-    float o[kD / 2];
+    // the chunk in progress and the chunks before it; both threads of a row keep the same maxima and sums
+    float m_c = -INFINITY, l_c = 0.0f, m_r = -INFINITY, l_r = 0.0f;
+    float o_c[kD / 2], o_r[kD / 2];
 #pragma unroll
-    for (int d = 0; d < kD / 2; ++d) o[d] = 0.0f;
+    for (int d = 0; d < kD / 2; ++d) o_c[d] = o_r[d] = 0.0f;
 
-    // Pass 1 of tile i: this thread's maximum over its 64 scores, left in xch[half][r] for the other half.
+    // Pass 1 of span i: the maximum of this thread's tile (raw scores of the keys the row sees).
+    auto span_masked = [&](int i) {
+      return (kt0 + i) * kKeys + kKeys - 1 > pos0 || (p.window > 0 && (kt0 + i) * kKeys < pos_hi - p.window + 1) || npos * G < kRows;
+    };
     auto pass1 = [&](int i) {
       mbar_wait(smem_u32(&s_full[i & 1]), (i >> 1) & 1, p.status, 5);
       fence_after_sync();
       const uint32_t s_addr = tmem_base + (i & 1) * kKeys + lane_addr + half * 64;
       const int key0 = (kt0 + i) * kKeys + half * 64;
-      const bool masked = (kt0 + i) * kKeys + kKeys - 1 > pos0 || (p.window > 0 && (kt0 + i) * kKeys < pos_hi - p.window + 1) ||
-                          npos * G < kRows;
+      const bool masked = span_masked(i);
       float mx0 = -INFINITY, mx1 = -INFINITY, mx2 = -INFINITY, mx3 = -INFINITY;
 #pragma unroll 1
       for (int c = 0; c < 2; ++c) {
@@ -213,23 +218,18 @@ attn_prefill_tc5_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_
           mx3 = fmaxf(mx3, v[j + 3]);
         }
       }
-      xch[half][r] = fmaxf(fmaxf(mx0, mx1), fmaxf(mx2, mx3));
+      return fmaxf(fmaxf(mx0, mx1), fmaxf(mx2, mx3));
     };
 
-    pass1(0);
+    float raw_max = pass1(0);
     for (int i = 0; i < T; ++i) {
-      // (the scores of tile i have been read once already: pass 1 ran before or during the value product of tile i - 1)
-      softmax_barrier();
-      const float mx = fmaxf(xch[0][r], xch[1][r]) * p.scale_log2;   // the scale is positive
-      softmax_barrier();                                              // xch is free again for pass 1 of the next tile
-      const float m_new = fmaxf(m, mx);
-      const float m_use = m_new == -INFINITY ? 0.0f : m_new;
-      const float alpha = fast_exp2(m - m_use);
+      // (the scores of span i have been read once already: pass 1 ran before or during the value product of span i - 1)
+      const float m_t = tile_max(raw_max, p.scale_log2);
+      const float ref = tile_ref(m_t);
       const uint32_t s_addr = tmem_base + (i & 1) * kKeys + lane_addr + half * 64;
       const int key0 = (kt0 + i) * kKeys + half * 64;
-      const bool masked = (kt0 + i) * kKeys + kKeys - 1 > pos0 || (p.window > 0 && (kt0 + i) * kKeys < pos_hi - p.window + 1) ||
-                          npos * G < kRows;
-      float l0 = 0.0f, l1 = 0.0f, l2 = 0.0f, l3 = 0.0f;
+      const bool masked = span_masked(i);
+      float u0 = 0.0f, u1 = 0.0f, u2 = 0.0f, u3 = 0.0f;     // key j of the tile belongs to class (j % 8) / 2
 #pragma unroll 1
       for (int c = 0; c < 2; ++c) {
         float v[32];
@@ -237,26 +237,17 @@ attn_prefill_tc5_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_
         uint32_t hi[16], lo[16];
 #pragma unroll
         for (int j = 0; j < 32; j += 2) {
-          float p0 = fast_exp2(fmaf(v[j], p.scale_log2, -m_use)), p1 = fast_exp2(fmaf(v[j + 1], p.scale_log2, -m_use));
+          float p0 = weight(v[j], p.scale_log2, ref), p1 = weight(v[j + 1], p.scale_log2, ref);
           if (masked) {
             const int key = key0 + c * 32 + j;
             if (!(key <= row_pos && key >= row_lo)) p0 = 0.0f;
             if (!(key + 1 <= row_pos && key + 1 >= row_lo)) p1 = 0.0f;
           }
-          if (j & 2) {
-            l2 += p0;
-            l3 += p1;
-          } else {
-            l0 += p0;
-            l1 += p1;
-          }
-          // p = hi + lo (+ less than 2^-16 p): hi is p cut to its upper 16 bits, a bfloat16 exactly; lo is the
-          // remainder p - hi, exact in float32, cut the same way. Bit moves only: no conversion instruction.
-          const uint32_t b0 = __float_as_uint(p0), b1 = __float_as_uint(p1);
-          hi[j >> 1] = __byte_perm(b0, b1, 0x7632);
-          const uint32_t r0 = __float_as_uint(p0 - __uint_as_float(b0 & 0xFFFF0000u));
-          const uint32_t r1 = __float_as_uint(p1 - __uint_as_float(b1 & 0xFFFF0000u));
-          lo[j >> 1] = __byte_perm(r0, r1, 0x7632);
+          if ((j & 6) == 0) u0 = __fadd_rn(__fadd_rn(u0, p0), p1);
+          else if ((j & 6) == 2) u1 = __fadd_rn(__fadd_rn(u1, p0), p1);
+          else if ((j & 6) == 4) u2 = __fadd_rn(__fadd_rn(u2, p0), p1);
+          else u3 = __fadd_rn(__fadd_rn(u3, p0), p1);
+          split_hi_lo(p0, p1, hi[j >> 1], lo[j >> 1]);
         }
         // 32 keys = four 16-byte pieces of this row in the 64-key half `half`, at pieces c * 4 .. + 3
         const uint32_t row_off = half * kTileBytes + r * 128;
@@ -267,35 +258,50 @@ attn_prefill_tc5_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_
           *reinterpret_cast<uint4*>(smem + kPloTile * kTileBytes + row_off + piece) = make_uint4(lo[4 * q], lo[4 * q + 1], lo[4 * q + 2], lo[4 * q + 3]);
         }
       }
-      l = l * alpha + ((l0 + l1) + (l2 + l3));
+      xch[i & 1][half][r] = make_float2(m_t, class_sum(u0, u1, u2, u3));
       fence_before_sync();
       fence_async_smem();
       mbar_arrive(smem_u32(&p_full));
-      if (i + 1 < T) pass1(i + 1);           // under the value product of tile i
+      if (i + 1 < T) raw_max = pass1(i + 1);           // under the value product of span i
       mbar_wait(smem_u32(&o_full), i & 1, p.status, 6);
       fence_after_sync();
-      {
-        float v[32];
-        tmem_load32(tmem_base + 2 * kKeys + lane_addr + half * 32, v);
+      softmax_barrier();    // both threads of every row have written xch[i & 1]; it is rewritten two spans later
 #pragma unroll
-        for (int j = 0; j < 32; ++j) o[j] = o[j] * alpha + v[j];
+      for (int t = 0; t < 2; ++t) {
+        float v[32];
+        tmem_load32(tmem_base + 2 * kKeys + t * kD + lane_addr + half * 32, v);
+        const float2 ml = xch[i & 1][t][r];
+        if (ml.x != -INFINITY) {
+          const FoldFactors f = fold_factors(m_c, ml.x);
+          l_c = fold_value(l_c, ml.y, f);
+#pragma unroll
+          for (int j = 0; j < 32; ++j) o_c[j] = fold_value(o_c[j], v[j], f);
+          m_c = f.m;
+        }
       }
-      m = m_new;
+      if (((kt0 + i) & 1) || i == T - 1) {      // the chunk of 256 keys is complete
+        if (m_c != -INFINITY) {
+          const FoldFactors f = fold_factors(m_r, m_c);
+          l_r = fold_value(l_r, l_c, f);
+#pragma unroll
+          for (int j = 0; j < 32; ++j) o_r[j] = fold_value(o_r[j], o_c[j], f);
+          m_r = f.m;
+        }
+        m_c = -INFINITY;
+        l_c = 0.0f;
+#pragma unroll
+        for (int j = 0; j < 32; ++j) o_c[j] = 0.0f;
+      }
       fence_before_sync();
     }
-    softmax_barrier();
-    // the row's sum: this half's part plus the other half's (xch was last read before both halves arrived at p_full)
-    xch[half][r] = l;
-    softmax_barrier();
     if (valid) {
-      const float inv = 1.0f / (xch[0][r] + xch[1][r]);
       bf16* dst = p.out + (static_cast<int64_t>(row0 + pi) * p.Hq + g * G + hh) * kD + half * 32;
 #pragma unroll
       for (int c = 0; c < 4; ++c) {
         uint32_t w[4];
 #pragma unroll
         for (int j = 0; j < 4; ++j) {
-          const __nv_bfloat162 h = __floats2bfloat162_rn(o[c * 8 + 2 * j] * inv, o[c * 8 + 2 * j + 1] * inv);
+          const __nv_bfloat162 h = __floats2bfloat162_rn(finish(o_r[c * 8 + 2 * j], l_r), finish(o_r[c * 8 + 2 * j + 1], l_r));
           w[j] = *reinterpret_cast<const uint32_t*>(&h);
         }
         *reinterpret_cast<uint4*>(dst + c * 8) = make_uint4(w[0], w[1], w[2], w[3]);

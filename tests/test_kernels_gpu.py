@@ -212,6 +212,62 @@ def test_attention_tc_against_plain(D, Hq, Hkv, page, window):
     assert (out2.float().cpu() - ref).abs().max() <= 1e-2 * max(1.0, float(ref.abs().max()))
 
 
+@pytest.mark.parametrize("D,Hq,Hkv,page,window", [(64, 8, 2, 16, 0), (64, 32, 8, 64, 0), (64, 6, 2, 8, 150), (128, 8, 2, 32, 0),
+                                                  (128, 6, 2, 64, 300), (64, 5, 5, 16, 0)])
+def test_attention_kernels_agree_in_bits(D, Hq, Hkv, page, window):
+    """The last 150 positions of a request of 700 tokens, computed as one prompt portion by the mma.sync kernel, as one
+    portion by the tcgen05 kernel (head size 64), as portions of two positions and as single positions by the decode
+    kernel: every row has the same bits each way. This also pins that tcgen05.mma and mma.sync accumulate alike."""
+    from stride_b200.kernels import ops
+    T, R = 700, 150
+    case = _paged_case([R], [T - R], Hq, Hkv, D, page, torch.bfloat16, seed=3 * D + page, peak=(0, 5))
+    G = Hq // Hkv
+    scale = 1.0 / math.sqrt(D)
+    q, cache, table = case["q"], case["cache"], case["table"]
+
+    def run(entries, tc5):
+        """entries: (first row, length) of each entry; its first position is T - R + first row."""
+        E = len(entries)
+        meta = torch.zeros(4, E, dtype=torch.int32)
+        for e, (row, L) in enumerate(entries):
+            meta[:, e] = torch.tensor([0, row, L, T - R + row])
+        meta = meta.to(DEV)
+        out = torch.full_like(q, float("nan"))
+        short = 16 // G
+        if tc5:
+            tiles = [x for e, (row, L) in enumerate(entries) for t in range(-(-L // (128 // G))) for x in (e, t)]
+            ops.attention_tc5(q, out, cache, table, meta, torch.tensor(tiles, dtype=torch.int32, device=DEV), len(tiles) // 2,
+                              Hq, Hkv, D, window, scale)
+            assert ops.attention_tc5_status() == 0
+            return out
+        tiles, items = [], []
+        for e, (row, L) in enumerate(entries):
+            if L <= short:
+                items.append(e)
+            else:
+                tiles += [x for t in range(-(-L // (64 // G))) for x in (e, t)]
+        chunks = (T - 1) // 256 + 1
+        scratch = torch.zeros(max(1, ops.attention_tc_scratch(len(items), Hkv, chunks, D)), device=DEV)
+        counters = torch.zeros(max(1, len(items)) * Hkv, dtype=torch.int32, device=DEV)
+        ops.attention_tc(q, out, cache, table, meta, torch.tensor(tiles + items, dtype=torch.int32, device=DEV), len(tiles) // 2,
+                         len(items), chunks, scratch, Hq, Hkv, D, window, scale, counters=counters)
+        return out
+
+    whole = run([(0, R)], False)
+    ref = _attention_reference(case, Hq, Hkv, D, window)
+    assert (whole.float().cpu() - ref).abs().max() <= 2e-2 * max(1.0, float(ref.abs().max()))
+    singles = run([(r, 1) for r in range(R)], False)
+    assert torch.equal(whole, singles)
+    if 2 * G <= 16:
+        pairs = run([(r, 2) for r in range(0, R, 2)], False)
+        assert torch.equal(whole, pairs)
+    uneven = run([(0, 37), (37, 1), (38, 70), (108, 42)], False)
+    assert torch.equal(whole, uneven)
+    if ops.attention_tc5_supported(Hq, Hkv, D, page):
+        assert torch.equal(whole, run([(0, R)], True))
+        assert torch.equal(whole, run([(0, 37), (37, 1), (38, 70), (108, 42)], True))
+
+
 @pytest.mark.parametrize("D,Hq,Hkv,page,window", [(48, 3, 3, 16, 0), (16, 4, 2, 64, 0), (80, 10, 2, 8, 37), (256, 2, 1, 32, 0)])
 def test_attention_generic_float32(D, Hq, Hkv, page, window):
     from stride_b200.kernels import ops

@@ -38,15 +38,13 @@ def _compare(got, want, dtype, what, noise=None):
 
 class _Bits:
     """Keeps the logits of the first replay of every request and checks that later replays, cut and batched in other
-    ways and lying in other pages, give the same bits: in 32-bit every kernel adds in an order that depends on the
-    token's own position alone."""
+    ways and lying in other pages, give the same bits: in both precisions every kernel adds in an order that depends
+    on the token's own position alone."""
 
-    def __init__(self, exact):
-        self.exact, self.first = exact, {}
+    def __init__(self):
+        self.first = {}
 
     def check(self, i, a, got, what):
-        if not self.exact:
-            return
         for k in range(got.shape[0]):
             ref = self.first.setdefault((i, a + k), got[k].clone())
             assert torch.equal(ref, got[k]), f"{what}: position {a + k} differs in bits from its first replay (max {(ref - got[k]).abs().max():.3e})"
@@ -78,7 +76,7 @@ def test_replay_modes(name, dtype, model_dirs, tmp_path):
     longest = sorted((per(len(r)) for r in reqs), reverse=True)
     pool = max(longest[0] + longest[1] + page, 4 * page)
     tr = TraceRun(model_dirs[name], dtype, tmp_path, pool, page, extra=("--kv-shuffle", "7"))
-    bits = _Bits(dtype == "float32")
+    bits = _Bits()
     try:
         # 1. each request alone and whole, logits at every place
         for i, r in enumerate(reqs):
