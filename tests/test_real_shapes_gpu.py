@@ -90,9 +90,9 @@ def test_real_layer_sizes(name, dtype):
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
 def test_bits_do_not_depend_on_the_batch(dtype):
-    """With the 1B layer sizes (whose attention and down projections are cut into K ranges): a request fed in the same
-    portions has the same logits, bit for bit, alone and among other requests, whatever their number, their order in
-    the batch, the size of the step (2 tokens or 400) and the pages it gets."""
+    """With the 1B layer sizes (whose attention and down projections are cut into K ranges): a request has the same
+    logits, bit for bit, alone and among other requests, whatever their number, their order in the batch, the size of
+    the step (1 token or 400), the pages it gets and the portions it is fed in."""
     from stride_b200 import Engine, EngineOptions, StepEntry
     from stride_b200.weights.random_init import random_tensors
     cfg_dict = SHAPES["1b"]
@@ -102,7 +102,7 @@ def test_bits_do_not_depend_on_the_batch(dtype):
     others = [random_tokens(vocab, 450, 6 + i) for i in range(5)]
     cuts = [(0, 70), (70, 75), (75, 76), (76, 77), (77, 79), (79, 80)] + [(p, p + 1) for p in range(80, 90)]
 
-    def run(seed, company):
+    def run(seed, company, cuts=cuts):
         """company[k]: for step k a list of (other request, tokens it brings), placed before or after mine."""
         eng = Engine(None, EngineOptions(dtype=dtype, max_rows=512, max_full_rows=96, max_slots=8, kv_pages=48, page_size=64,
                                          max_context=512, kv_shuffle_seed=seed), config=cfg_dict, tensors=tensors)
@@ -135,3 +135,7 @@ def test_bits_do_not_depend_on_the_batch(dtype):
     among_prompts = run(11, big)
     assert torch.equal(alone, among_decoders)
     assert torch.equal(alone, among_prompts)
+    # nor on how the request itself is cut into steps: whole, token by token, in portions beside other requests
+    assert torch.equal(alone, run(5, [], [(0, 90)]))
+    assert torch.equal(alone, run(6, [], [(p, p + 1) for p in range(90)]))
+    assert torch.equal(alone, run(7, big, [(0, 3), (3, 40), (40, 42), (42, 43), (43, 90)]))
