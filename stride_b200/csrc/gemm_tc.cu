@@ -62,6 +62,12 @@ __device__ __forceinline__ void tmem_load16(uint32_t taddr, float* v) {
 }
 __device__ __forceinline__ void tc_fence_before() { fence_before_sync(); }
 __device__ __forceinline__ void tc_fence_after() { fence_after_sync(); }
+// Tensor memory is allocated in powers of two of at least 32 columns.
+__host__ __device__ __forceinline__ uint32_t tmem_alloc_cols(int cols) {
+  uint32_t c = 32;
+  while (c < static_cast<uint32_t>(cols)) c <<= 1;
+  return c;
+}
 // Instruction descriptor: D float32, A and B bfloat16, both K-major, M = 128, N = n.
 __device__ __forceinline__ uint32_t instr_desc(int n) { return sb::tc5::instr_desc(kTileM, n, false); }
 
@@ -131,7 +137,7 @@ gemm_tc_single_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_co
   const int kb0 = split * p.kblocks_per_split;
   const int kb1 = min(kblocks, kb0 + p.kblocks_per_split);
   const int iters = kb1 - kb0;
-  const uint32_t tmem_cols = BN < 32 ? 32 : BN;
+  const uint32_t tmem_cols = tmem_alloc_cols(BN);
 
   if (threadIdx.x == 0) {
     prefetch_tensormap(&map_w);
@@ -273,7 +279,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
   const int kblocks = (p.K + kTileK - 1) / kTileK;
   // Tiles are numbered with the weight tile fastest, so CTAs that run together share token tiles in L2.
   const int total_tiles = p.tiles_m * p.tiles_n * p.splits;
-  const uint32_t tmem_cols = (MULTI ? 2 : 1) * BN < 32 ? 32 : (MULTI ? 2 : 1) * BN;   // MULTI: one accumulator fills while the other drains
+  const uint32_t tmem_cols = tmem_alloc_cols((MULTI ? 2 : 1) * BN);   // MULTI: one accumulator fills while the other drains
 
   if (threadIdx.x == 0) {
     prefetch_tensormap(&map_w);
@@ -458,7 +464,7 @@ gemm_tc_fold_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_cons
   const uint32_t smem0 = (smem_u32(smem_raw) + 1023u) & ~1023u;
   const int kblocks = (p.K + kTileK - 1) / kTileK;
   const int total_tiles = p.tiles_m * p.tiles_n;
-  const uint32_t tmem_cols = 2 * BN < 32 ? 32 : 2 * BN;
+  const uint32_t tmem_cols = tmem_alloc_cols(2 * BN);
 
   if (threadIdx.x == 0) {
     prefetch_tensormap(&map_w);
@@ -636,7 +642,23 @@ SB_EXPORT int sb_gemm_tc(const void* x, int64_t ldx, const void* w, int64_t ldw,
   p.M = M;
   p.N = n;
   p.K = K;
-  p.block_n = n <= 16 ? 16 : n <= 32 ? 32 : n <= 64 ? 64 : n <= 128 ? 128 : 256;
+  if (n <= 128) {
+    p.block_n = n <= 16 ? 16 : n <= 32 ? 32 : n <= 64 ? 64 : 128;
+  } else {
+    // Token tiles of 32..256: the width that needs the fewest cycles, counting whole waves of 148 CTAs. A K step of
+    // 64 costs about max(2 BN, 128 + BN) cycles: the tensor cores or, for narrow tiles, the operands' shared-memory reads.
+    // (A token's result does not depend on the width: every element is its own chain over K.)
+    const long long tm = epilogue == kSwiglu ? (half_rows + 63) / 64 : (M + kTileM - 1) / kTileM;
+    long long best = -1;
+    for (int bn = 256; bn >= 32; bn -= 32) {
+      const long long tiles = tm * ((n + bn - 1) / bn);
+      const long long cost = ((tiles + 147) / 148) * (2 * bn > 128 + bn ? 2 * bn : 128 + bn);
+      if (best < 0 || cost < best) {
+        best = cost;
+        p.block_n = bn;
+      }
+    }
+  }
   const int stage_bytes = kStageA + p.block_n * 128;
   p.stages = min(kMaxStages, kSmemBudget / stage_bytes);
   {
@@ -677,7 +699,7 @@ SB_EXPORT int sb_gemm_tc(const void* x, int64_t ldx, const void* w, int64_t ldw,
   }
   // Persistent CTAs: as many as fit the GPU at once (by shared and tensor memory), each walking tiles.
   int per_sm = static_cast<int>((227 * 1024) / (smem + 2048));
-  per_sm = max(1, min(per_sm, 512 / max(32, 2 * p.block_n)));
+  per_sm = max(1, min(per_sm, 512 / static_cast<int>(tmem_alloc_cols(2 * p.block_n))));
   const long long resident = 148ll * per_sm;
   const bool multi = total_tiles > resident;
   if (!multi && (p.tiles_n > 65535 || splits > 65535)) return sb::fail("sb_gemm_tc: grid too large");

@@ -33,6 +33,7 @@ NVCC_FLAGS = ["-O3", "-std=c++17", "-lineinfo", "-shared", "-Xcompiler", "-fPIC"
 # library name -> source file; every name here is built by `build_all()`.
 SOURCES = {
     "elementwise": "elementwise.cu",
+    "norm": "norm.cu",
     "gemm_f32": "gemm_f32.cu",
     "attention_generic": "attention_generic.cu",
     "sampling": "sampling.cu",

@@ -41,7 +41,7 @@ def gemm(a) -> dict:
     copies = a.copies or max(1, min(64, (2 * L2_BYTES) // (M * K * 2) + 1))
     ws = [(torch.randn(M, K, device="cuda") * 0.02).bfloat16() for _ in range(copies)]
     x = torch.randn(n, K, device="cuda").bfloat16()
-    S = ops.gemm_tc_splits(M, K) if epi != ops.SWIGLU and (epi == ops.STORE or n > ops.gemm_tc_partial_tokens()) else 1
+    S = ops.gemm_tc_splits(M, K) if epi == ops.STORE and not a.one_range else 1
     if epi == ops.SWIGLU:
         out = torch.zeros(n, M // 2, device="cuda", dtype=torch.bfloat16)
     else:
@@ -175,6 +175,7 @@ def main(argv=None) -> int:
     g.add_argument("--cols", type=int, default=2048)
     g.add_argument("--epilogue", choices=["store", "add", "swiglu"], default="store")
     g.add_argument("--copies", type=int, default=0)
+    g.add_argument("--one-range", action="store_true", help="keep K in one range whatever the weight's shape")
     g.add_argument("--reps", type=int, default=50)
     t = sub.add_parser("attention")
     t.add_argument("--batch", type=int, default=8)

@@ -81,7 +81,7 @@ def rmsnorm(h: torch.Tensor, weight: torch.Tensor, eps: float, out: torch.Tensor
     `partials` [S, n, H] float32 are summed into h left to right and h is updated in place.
     """
     _cuda(h, weight, out, partials)
-    lib, fn = _fn("elementwise", "sb_rmsnorm", [c_void_p, c_void_p, c_int, c_int64, c_void_p, c_int, c_void_p, c_int,
+    lib, fn = _fn("norm", "sb_rmsnorm", [c_void_p, c_void_p, c_int, c_int64, c_void_p, c_int, c_void_p, c_int,
                                                c_int, c_int, c_float, c_void_p])
     n, H = h.shape
     S = 0 if partials is None else partials.shape[0]

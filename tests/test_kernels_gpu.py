@@ -78,14 +78,14 @@ def test_gemm_tc_swiglu(n, I, K):
 
 @pytest.mark.parametrize("M,K", [(384, 1024), (2048, 2048), (200, 8192), (1000, 136)])
 def test_gemm_tc_does_not_depend_on_the_batch(M, K):
-    """A token's result has the same bits alone, among 7, 100, 200 and 700 other tokens, wherever it stands among
+    """A token's result has the same bits alone and among 7 to 700 other tokens (token tiles of 16 to 256), wherever it stands among
     them: with K in one range, and with the weight's K ranges added by the caller (few tokens) or by the kernel (many)."""
     from stride_b200.kernels import ops
     w = _rand(M, K, seed=7, scale=0.05, dtype=torch.bfloat16)
     x = _rand(700, K, seed=8, dtype=torch.bfloat16)
     S, few = ops.gemm_tc_splits(M, K), ops.gemm_tc_partial_tokens()
     one, ranged = [], []
-    for n, at in ((1, 0), (8, 5), (100, 77), (200, 130), (700, 699)):
+    for n, at in ((1, 0), (8, 5), (100, 77), (200, 130), (256, 255), (333, 1), (700, 699)):
         xs = x[:n].clone()
         xs[at] = x[0]
         out = torch.zeros(n, M, device=DEV)
