@@ -57,6 +57,11 @@ struct AttnTcParams {
   float* part_ml;        // [items][Hkv][chunks][16][2]
   int chunks;
   int* counters;         // [items][Hkv], zero between launches; null: the chunks are folded by attn_combine_kernel
+  // decode with the rotation fused in (qkv != null): q, k, v come from the projection's partial sums
+  const float* qkv;      // [n_partials][n][(Hq + 2 Hkv) D], summed in ascending order
+  int n_partials;
+  int64_t partial_stride;
+  const float* cos_sin;  // [positions][D / 2][2]
 };
 
 __device__ __forceinline__ uint32_t smem_u32(const void* p) { return static_cast<uint32_t>(__cvta_generic_to_shared(p)); }
@@ -353,7 +358,29 @@ __device__ __forceinline__ float fold_chunks(const float* part_o, const float* p
   return finish(o, l);
 }
 
+// Element j and j + D / 2 of one head of one token from the projection's partial sums, rotated by the position's
+// angle j unless it is a value: the arithmetic of rope_append_kernel (elementwise.cu), operation by operation.
 template <int D>
+__device__ __forceinline__ void projected_pair(const AttnTcParams& p, int row, int head, int pos, int j, bool rotate, float& a, float& b) {
+  const float* src = p.qkv + static_cast<int64_t>(row) * (p.Hq + 2 * p.Hkv) * D + static_cast<int64_t>(head) * D;
+  a = src[j];
+  b = src[j + D / 2];
+  for (int s = 1; s < p.n_partials; ++s) {
+    a += src[s * p.partial_stride + j];
+    b += src[s * p.partial_stride + j + D / 2];
+  }
+  if (rotate) {
+    const float2 cs = *reinterpret_cast<const float2*>(p.cos_sin + (static_cast<int64_t>(pos) * (D / 2) + j) * 2);
+    const float ra = __fsub_rn(__fmul_rn(a, cs.x), __fmul_rn(b, cs.y));
+    const float rb = __fadd_rn(__fmul_rn(b, cs.x), __fmul_rn(a, cs.y));
+    a = ra;
+    b = rb;
+  }
+}
+
+// FUSED: the step's queries, keys and values are taken from the projection's partial sums, rotated here, and the
+// keys and values are appended to the cache by the CTA whose chunk holds their position (no rotation kernel runs).
+template <int D, bool FUSED>
 __global__ void __launch_bounds__(128) attn_decode_kernel(const AttnTcParams p) {
   constexpr int LD = D + 8, CH = D / 8;
   extern __shared__ __align__(16) uint8_t smem_raw[];
@@ -389,17 +416,46 @@ __global__ void __launch_bounds__(128) attn_decode_kernel(const AttnTcParams p) 
   if (any) load_kv_tiles<D>(sK, sV, kplane, p.v_offset, table, p.page_size, p.page_shift, p.page_stride, key0, key_lo, first_pos - 1,
                             lane, 32, key_lo, pos_hi);
   sb::grid_dependency_wait();
-  for (int idx = tid; idx < 16 * CH; idx += 128) {
-    const int r = idx / CH, c = idx % CH;
-    bf16* d = sQ + r * LD + c * 8;
-    if (r < rows)
-      cp_async16(smem_u32(d), p.q + (static_cast<int64_t>(first_row + r / G) * p.Hq + g * G + r % G) * D + c * 8);
-    else
-      *reinterpret_cast<uint4*>(d) = make_uint4(0, 0, 0, 0);
+  if (FUSED) {
+    constexpr int half = D / 2;
+    for (int idx = tid; idx < 16 * half; idx += 128) {
+      const int r = idx / half, j = idx % half;
+      float a = 0.0f, b = 0.0f;
+      if (r < rows) projected_pair<D>(p, first_row + r / G, g * G + r % G, first_pos + r / G, j, true, a, b);
+      sQ[r * LD + j] = __float2bfloat16_rn(a);
+      sQ[r * LD + j + half] = __float2bfloat16_rn(b);
+    }
+    // the step's own keys and values that lie in this chunk: into the warps' tiles and into the cache
+    const int lo = max(first_pos, chunk * kChunk), hi = min(pos_hi, chunk * kChunk + kChunk - 1);
+    for (int idx = tid; idx < (hi - lo + 1) * D; idx += 128) {
+      const int pos = lo + idx / D, jj = idx % D;
+      const bool is_v = jj >= half;
+      const int j = jj % half;
+      float a, b;
+      projected_pair<D>(p, first_row + pos - first_pos, p.Hq + (is_v ? p.Hkv : 0) + g, pos, j, !is_v, a, b);
+      const bf16 ha = __float2bfloat16_rn(a), hb = __float2bfloat16_rn(b);
+      bf16* tile = sKV + ((pos - chunk * kChunk) / kKeys) * 2 * 64 * LD + (is_v ? 64 * LD : 0) + (pos % kKeys) * LD;
+      tile[j] = ha;
+      tile[j + half] = hb;
+      const int pi = p.page_shift >= 0 ? pos >> p.page_shift : pos / p.page_size;
+      const int in_page = p.page_shift >= 0 ? pos & (p.page_size - 1) : pos % p.page_size;
+      bf16* dst = const_cast<bf16*>(kplane) + static_cast<int64_t>(table[pi]) * p.page_stride + in_page * D + (is_v ? p.v_offset : 0);
+      dst[j] = ha;
+      dst[j + half] = hb;
+    }
+  } else {
+    for (int idx = tid; idx < 16 * CH; idx += 128) {
+      const int r = idx / CH, c = idx % CH;
+      bf16* d = sQ + r * LD + c * 8;
+      if (r < rows)
+        cp_async16(smem_u32(d), p.q + (static_cast<int64_t>(first_row + r / G) * p.Hq + g * G + r % G) * D + c * 8);
+      else
+        *reinterpret_cast<uint4*>(d) = make_uint4(0, 0, 0, 0);
+    }
+    if (any && key0 + kKeys - 1 >= first_pos)
+      load_kv_tiles<D>(sK, sV, kplane, p.v_offset, table, p.page_size, p.page_shift, p.page_stride, key0, max(first_pos, key_lo), pos_hi,
+                       lane, 32, key_lo, pos_hi);
   }
-  if (any && key0 + kKeys - 1 >= first_pos)
-    load_kv_tiles<D>(sK, sV, kplane, p.v_offset, table, p.page_size, p.page_shift, p.page_stride, key0, max(first_pos, key_lo), pos_hi,
-                     lane, 32, key_lo, pos_hi);
   cp_commit();
   cp_wait<0>();
   __syncthreads();
@@ -515,13 +571,15 @@ int launch(const AttnTcParams& p, int n_tiles, int n_items, cudaStream_t stream)
     const size_t smem = static_cast<size_t>(16 * LD + 8 * 64 * LD) * sizeof(bf16);   // results (4 x 16 x (D + 2) floats) reuse the tiles
     static bool set = false;
     if (!set) {
-      if (cudaFuncSetAttribute(attn_decode_kernel<D>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess)
+      if (cudaFuncSetAttribute(attn_decode_kernel<D, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess ||
+          cudaFuncSetAttribute(attn_decode_kernel<D, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess)
         return sb::fail("sb_attention_tc: cannot raise the shared memory limit");
       set = true;
     }
     AttnTcParams pd = p;
     pd.work = p.work + 2 * n_tiles;
-    sb::launch_pdl(attn_decode_kernel<D>, dim3(n_items, p.Hkv, p.chunks), dim3(128), smem, stream, pd);
+    if (p.qkv != nullptr) sb::launch_pdl(attn_decode_kernel<D, true>, dim3(n_items, p.Hkv, p.chunks), dim3(128), smem, stream, pd);
+    else sb::launch_pdl(attn_decode_kernel<D, false>, dim3(n_items, p.Hkv, p.chunks), dim3(128), smem, stream, pd);
     if (pd.counters == nullptr) sb::launch_pdl(attn_combine_kernel<D>, dim3(n_items, p.Hkv), dim3(D), 0, stream, pd);
   }
   return sb::check_launch("sb_attention_tc");
@@ -537,11 +595,12 @@ SB_EXPORT int64_t sb_attention_tc_scratch(int items, int Hkv, int chunks, int D)
 // work: [n_tiles][2] (entry, tile) for the portion kernel, followed by [n_items] entries for the decode
 // kernel. An entry belongs to the decode kernel iff length * (Hq / Hkv) <= 16. chunks = greatest
 // (last position of a decode entry) / 256 + 1. scratch: sb_attention_tc_scratch(...) floats.
-SB_EXPORT int sb_attention_tc(const void* q, void* out, const void* k_base, const int32_t* block_table, int max_pages,
-                              int page_size, int64_t page_stride, int64_t v_offset, int64_t head_stride,
-                              const int32_t* meta, int meta_stride, const int32_t* work, int n_tiles, int n_items,
-                              int chunks, float* scratch, int* counters, int Hq, int Hkv, int D, int window, float scale,
-                              cudaStream_t stream) {
+namespace {
+int attention_tc_impl(const void* q, void* out, const void* k_base, const int32_t* block_table, int max_pages,
+                      int page_size, int64_t page_stride, int64_t v_offset, int64_t head_stride,
+                      const int32_t* meta, int meta_stride, const int32_t* work, int n_tiles, int n_items,
+                      int chunks, float* scratch, int* counters, int Hq, int Hkv, int D, int window, float scale,
+                      const float* qkv, int n_partials, int64_t partial_stride, const float* cos_sin, cudaStream_t stream) {
   if (n_tiles <= 0 && n_items <= 0) return 0;
   if (Hkv <= 0 || Hq % Hkv != 0 || Hq / Hkv > 16)
     return sb::fail("sb_attention_tc: group ratio %d/%d is not supported (1..16)", Hq, Hkv);
@@ -572,9 +631,41 @@ SB_EXPORT int sb_attention_tc(const void* q, void* out, const void* k_base, cons
   p.part_o = scratch;
   p.part_ml = scratch + static_cast<int64_t>(n_items) * Hkv * chunks * 16 * D;
   p.counters = counters;
+  p.qkv = qkv;
+  p.n_partials = n_partials;
+  p.partial_stride = partial_stride;
+  p.cos_sin = cos_sin;
   if (D == 64) return launch<64>(p, n_tiles, n_items, stream);
   if (D == 128) return launch<128>(p, n_tiles, n_items, stream);
   return sb::fail("sb_attention_tc: head_dim %d has no tensor-core kernel (64 or 128)", D);
+}
+}  // namespace
+
+SB_EXPORT int sb_attention_tc(const void* q, void* out, const void* k_base, const int32_t* block_table, int max_pages,
+                              int page_size, int64_t page_stride, int64_t v_offset, int64_t head_stride,
+                              const int32_t* meta, int meta_stride, const int32_t* work, int n_tiles, int n_items,
+                              int chunks, float* scratch, int* counters, int Hq, int Hkv, int D, int window, float scale,
+                              cudaStream_t stream) {
+  return attention_tc_impl(q, out, k_base, block_table, max_pages, page_size, page_stride, v_offset, head_stride, meta, meta_stride,
+                           work, n_tiles, n_items, chunks, scratch, counters, Hq, Hkv, D, window, scale, nullptr, 0, 0, nullptr, stream);
+}
+
+// The decode kernel with the rotation and the append fused in, for a step whose entries all fit it (length * (Hq / Hkv)
+// <= 16 each): qkv [n_partials][n][(Hq + 2 Hkv) D] float32 are the projection's partial sums (added in ascending
+// order), cos_sin [positions][D / 2][2] the rotation table of a fully rotated head. Queries are rotated in shared
+// memory; the step's keys and values are rotated, rounded and written to the cache (k_base is written) by the CTA
+// whose chunk holds their position. Same bits as sb_rope_append followed by sb_attention_tc.
+SB_EXPORT int sb_attention_decode_rope(const float* qkv, int n_partials, int64_t partial_stride, const float* cos_sin, void* out,
+                                       void* k_base, const int32_t* block_table, int max_pages, int page_size, int64_t page_stride,
+                                       int64_t v_offset, int64_t head_stride, const int32_t* meta, int meta_stride,
+                                       const int32_t* items, int n_items, int chunks, float* scratch, int* counters, int Hq, int Hkv,
+                                       int D, int window, float scale, cudaStream_t stream) {
+  if (n_items <= 0) return 0;
+  if (qkv == nullptr || cos_sin == nullptr || n_partials < 1) return sb::fail("sb_attention_decode_rope: qkv and cos_sin are required");
+  if ((reinterpret_cast<uintptr_t>(cos_sin) & 7) != 0) return sb::fail("sb_attention_decode_rope: cos_sin must be 8-byte aligned");
+  return attention_tc_impl(out, out, k_base, block_table, max_pages, page_size, page_stride, v_offset, head_stride, meta, meta_stride,
+                           items, 0, n_items, chunks, scratch, counters, Hq, Hkv, D, window, scale, qkv, n_partials, partial_stride,
+                           cos_sin, stream);
 }
 
 

@@ -255,6 +255,25 @@ def attention_tc(q, out, cache_layer, block_table, entry_meta, work, n_tiles: in
                    head_dim, window, scale, _stream()))
 
 
+def attention_decode_rope(qkv, cos_sin, out, cache_layer, block_table, entry_meta, items, n_items: int, chunks: int, scratch,
+                          counters, num_heads: int, num_kv_heads: int, head_dim: int, window: int, scale: float) -> None:
+    """The decode kernel of `attention_tc` with `rope_append` fused in, for steps whose entries all fit it: qkv
+    [S, n, (Hq + 2 Hkv) D] float32 partial sums of the projection, cos_sin the table of a fully rotated head. Rotates
+    q in shared memory, appends the step's rotated k and its v to the pages, attends. Same bits as the two kernels."""
+    _cuda(qkv, cos_sin, out, cache_layer, block_table, entry_meta, items, scratch, counters)
+    if not (out.dtype == cache_layer.dtype == torch.bfloat16) or qkv.dtype != torch.float32:
+        raise TypeError("attention_decode_rope takes float32 qkv and bfloat16 out and cache")
+    lib, fn = _fn("attention_tc", "sb_attention_decode_rope",
+                  [c_void_p, c_int, c_int64, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int64, c_int64, c_int64,
+                   c_void_p, c_int, c_void_p, c_int, c_int, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_float, c_void_p])
+    if qkv.dim() == 2:
+        qkv = qkv.unsqueeze(0)
+    _check(lib, fn(_ptr(qkv), qkv.shape[0], qkv.stride(0), _ptr(cos_sin), _ptr(out), _ptr(cache_layer), _ptr(block_table),
+                   block_table.shape[1], cache_layer.shape[3], cache_layer.stride(0), cache_layer.stride(1),
+                   cache_layer.stride(2), _ptr(entry_meta), entry_meta.stride(0), _ptr(items), n_items, chunks, _ptr(scratch),
+                   _ptr(counters), num_heads, num_kv_heads, head_dim, window, scale, _stream()))
+
+
 def attention_tc5_supported(num_heads: int, num_kv_heads: int, head_dim: int, page_size: int) -> bool:
     """True if the tcgen05 prompt-attention kernel takes this shape (head size 64, pages of a power of two >= 8)."""
     if head_dim != 64 or num_kv_heads <= 0 or num_heads % num_kv_heads or num_heads // num_kv_heads > 128:

@@ -106,16 +106,30 @@ class AttentionMixer(Mixer):
     def forward(self, ctx, x, stream, cache):
         n, ws, D = ctx.n, ctx.workspace, self.head_dim
         qkv = self.qkv.forward_partials(x, ws.raw("attn.qkv", (self.qkv.partial_elems(ws.max_tokens),), torch.float32))
+        mixed = ws.get("attn.out", n, (self.num_heads * D,), ctx.act_dtype)
+        G = self.num_heads // self.num_kv_heads
+        tensor_core = ctx.act_dtype == torch.bfloat16 and D in (64, 128) and G <= 16
+        plan = None
+        if tensor_core:
+            tc5 = ops.attention_tc5_supported(self.num_heads, self.num_kv_heads, D, cache.page_size)
+            plan = self._tc_plan(ctx, G, 128 if tc5 else 64)
+        if (plan is not None and plan[1] == 0 and cache.writes and self._rotary == D
+                and plan[2] * self.num_kv_heads * plan[3] <= 296):
+            # only decoded tokens and very short portions, few enough for all CTAs to run at once: rotation and append
+            # happen inside the decode kernel (the same bits; with more CTAs than that the separate kernel is faster)
+            work, _, n_items, chunks = plan
+            scratch = ws.grow("attn.scratch", ops.attention_tc_scratch(n_items, self.num_kv_heads, chunks, D), torch.float32)
+            counters = ws.raw("attn.counters", (ws.max_tokens * self.num_kv_heads,), torch.int32)
+            ops.attention_decode_rope(qkv, self._cos_sin, mixed, cache.pages, cache.block_table, ctx.entry_meta, work, n_items,
+                                      chunks, scratch, counters, self.num_heads, self.num_kv_heads, D, self.window, self.scale)
+            self.o.forward_add(mixed, stream, ws.raw("attn.o_partials", (self.o.partial_elems(ws.max_tokens),), torch.float32))
+            return
         q = ws.get("attn.q", n, (self.num_heads * D,), ctx.act_dtype)
         ops.rope_append(qkv, ctx.positions, ctx.slots, self._cos_sin, self._rotary, q, cache.pages, cache.block_table,
                         self.num_heads, self.num_kv_heads, D, write_kv=cache.writes)
-        mixed = ws.get("attn.out", n, (self.num_heads * D,), ctx.act_dtype)
-        G = self.num_heads // self.num_kv_heads
-        if ctx.act_dtype == torch.bfloat16 and D in (64, 128) and G <= 16:
+        if tensor_core:
             # prompt portions: the tcgen05 kernel where the shape allows it (tiles of 128 rows), else mma.sync (64 rows);
             # decoded tokens and very short portions: the split-key decode kernel
-            tc5 = ops.attention_tc5_supported(self.num_heads, self.num_kv_heads, D, cache.page_size)
-            plan = self._tc_plan(ctx, G, 128 if tc5 else 64)
             work, n_tiles, n_items, chunks = plan
             if tc5 and n_tiles:
                 ops.attention_tc5(q, mixed, cache.pages, cache.block_table, ctx.entry_meta, work, n_tiles, self.num_heads,

@@ -268,6 +268,46 @@ def test_attention_kernels_agree_in_bits(D, Hq, Hkv, page, window):
         assert torch.equal(whole, run([(0, 37), (37, 1), (38, 70), (108, 42)], True))
 
 
+@pytest.mark.parametrize("D,Hq,Hkv,page,window", [(64, 8, 2, 16, 0), (64, 32, 8, 64, 100), (128, 6, 2, 32, 0), (64, 3, 3, 8, 0)])
+def test_decode_attention_with_rotation_fused(D, Hq, Hkv, page, window):
+    """The decode kernel that rotates and appends by itself gives the same output and leaves the same cache, bit for
+    bit, as the rotation kernel followed by the decode kernel. Entries of one to three positions, some crossing a
+    chunk edge (positions 255 | 256) or a page edge."""
+    from stride_b200.kernels import ops
+    G = Hq // Hkv
+    news = [1, min(2, 16 // G), 1, min(3, 16 // G), 1]
+    olds = [300, 255, 0, 509, 63]
+    case = _paged_case(news, olds, Hq, Hkv, D, page, torch.bfloat16, seed=D + Hq)
+    n = sum(news)
+    g = torch.Generator().manual_seed(11)
+    S = 3
+    qkv = torch.randn(S, n, (Hq + 2 * Hkv) * D, generator=g).to(DEV)
+    max_pos = max(a + b for a, b in zip(news, olds))
+    ang = torch.rand(max_pos, D // 2, generator=g) * 6.28
+    cos_sin = torch.stack([ang.cos(), ang.sin()], dim=-1).contiguous().to(DEV)
+    items = torch.arange(len(news), dtype=torch.int32, device=DEV)
+    chunks = (max_pos - 1) // 256 + 1
+    scale = 1.0 / math.sqrt(D)
+
+    def buffers():
+        scratch = torch.zeros(ops.attention_tc_scratch(len(news), Hkv, chunks, D), device=DEV)
+        counters = torch.zeros(len(news) * Hkv, dtype=torch.int32, device=DEV)
+        return case["cache"].clone(), torch.full((n, Hq * D), float("nan"), dtype=torch.bfloat16, device=DEV), scratch, counters
+
+    cache_a, out_a, scratch, counters = buffers()
+    q = torch.zeros(n, Hq * D, dtype=torch.bfloat16, device=DEV)
+    ops.rope_append(qkv, case["positions"], case["slots"], cos_sin, D, q, cache_a, case["table"], Hq, Hkv, D)
+    ops.attention_tc(q, out_a, cache_a, case["table"], case["meta"], items, 0, len(news), chunks, scratch, Hq, Hkv, D, window, scale,
+                     counters=counters)
+    cache_b, out_b, scratch, counters = buffers()
+    ops.attention_decode_rope(qkv, cos_sin, out_b, cache_b, case["table"], case["meta"], items, len(news), chunks, scratch, counters,
+                              Hq, Hkv, D, window, scale)
+    assert torch.isfinite(out_a.float()).all()
+    assert torch.equal(out_a, out_b)
+    assert torch.equal(cache_a, cache_b)
+    assert not torch.equal(cache_a, case["cache"])
+
+
 @pytest.mark.parametrize("D,Hq,Hkv,page,window", [(48, 3, 3, 16, 0), (16, 4, 2, 64, 0), (80, 10, 2, 8, 37), (256, 2, 1, 32, 0)])
 def test_attention_generic_float32(D, Hq, Hkv, page, window):
     from stride_b200.kernels import ops
