@@ -71,6 +71,11 @@ __host__ __device__ __forceinline__ uint32_t tmem_alloc_cols(int cols) {
 // Instruction descriptor: D float32, A and B bfloat16, both K-major, M = 128, N = n.
 __device__ __forceinline__ uint32_t instr_desc(int n) { return sb::tc5::instr_desc(kTileM, n, false); }
 
+// silu(g) = g / (1 + e^-g) with the hardware's approximations of e^x and of the division (two units in the last
+// place each, far below the bfloat16 rounding that follows): the same instruction sequence in every kernel of this
+// file, so that a token's product has the same bits from each.
+__device__ __forceinline__ float silu_fast(float g) { return __fdividef(g, 1.0f + __expf(-g)); }
+
 // Rows of one accumulator tile to global memory: out[n, m] = d (kStore) or out[n, m] += d (kAdd). Each thread
 // owns output feature m and walks the tile's tokens sixteen at a time; for kAdd the residual values of the
 // next sixteen are requested before the current sixteen are summed and stored.
@@ -241,7 +246,7 @@ gemm_tc_single_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_co
             if (n < p.N) {
               const float other = xch[(cb + c) * 64 + (quarter & 1) * 32 + lane];
               const float g = quarter >= 2 ? other : v[c], u = quarter >= 2 ? v[8 + c] : other;
-              out[static_cast<int64_t>(n) * p.ldo + j] = __float2bfloat16_rn((g / (1.0f + __expf(-g))) * u);
+              out[static_cast<int64_t>(n) * p.ldo + j] = __float2bfloat16_rn(silu_fast(g) * u);
             }
           }
         }
@@ -415,7 +420,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
               if (n < p.N) {
                 const float other = xch[(cb + c) * 64 + (quarter & 1) * 32 + lane];
                 const float g = quarter >= 2 ? other : v[c], u = quarter >= 2 ? v[8 + c] : other;
-                out[static_cast<int64_t>(n) * p.ldo + j] = __float2bfloat16_rn((g / (1.0f + __expf(-g))) * u);
+                out[static_cast<int64_t>(n) * p.ldo + j] = __float2bfloat16_rn(silu_fast(g) * u);
               }
             }
           }
@@ -585,6 +590,208 @@ gemm_tc_fold_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_cons
   }
 }
 
+// Many tokens on a pair of CTAs (cta_group::2): a tile of 256 weight rows (kStore) or of 128 gate and 128 up rows
+// (kSwiglu) by BN tokens. Each CTA of the pair loads its half of the weight rows and its half of the tokens, so
+// that a K step of 64 brings 16 KB + BN * 64 bytes a CTA instead of 16 KB + BN * 128: it is the traffic from L2
+// to the SMs that bounds these products. The leader issues the MMAs for both; each CTA's tensor memory holds its
+// 128 rows of the tile and each CTA runs the epilogue for them: the K ranges added in ascending order in registers
+// (kStore, eight epilogue warps as in gemm_tc_fold_kernel) or the SwiGLU product (four warps). A token's result has
+// the bits of the single-CTA kernels: the same accumulation chain per element and the same order of the ranges.
+template <int EPI>
+__global__ void __launch_bounds__(kFoldThreads, 1)
+gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUtensorMap map_x, const GemmParams p) {
+  constexpr int kEpiWarps = 8;
+  extern __shared__ __align__(1024) uint8_t smem_raw[];
+  __shared__ __align__(8) uint64_t full_bar[kMaxStages];    // used in the leader: both CTAs' tiles have landed
+  __shared__ __align__(8) uint64_t empty_bar[kMaxStages];   // in each CTA: the MMAs that read its stage are done
+  __shared__ __align__(8) uint64_t accum_full[2];           // in each CTA: an accumulator is complete
+  __shared__ __align__(8) uint64_t accum_empty[2];          // used in the leader: both CTAs have drained an accumulator
+  __shared__ uint32_t tmem_base_s;
+  __shared__ float xch2[EPI == kSwiglu ? 2 : 1][EPI == kSwiglu ? 16 * 64 : 1];   // gate/up exchange of the SwiGLU epilogue, per warp set
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int rank = static_cast<int>(sb::cluster_rank());
+  const int BN = p.block_n, half_n = BN / 2;
+  const int stage_bytes = kStageA + half_n * 128;
+  const uint32_t smem0 = (smem_u32(smem_raw) + 1023u) & ~1023u;
+  const int kblocks = (p.K + kTileK - 1) / kTileK;
+  const int total_tiles = p.tiles_m * p.tiles_n;            // tiles of the pair
+  const int pair = blockIdx.x >> 1, pairs = gridDim.x >> 1;
+
+  if (threadIdx.x == 0) {
+    prefetch_tensormap(&map_w);
+    prefetch_tensormap(&map_x);
+    for (int s = 0; s < p.stages; ++s) {
+      mbar_init(smem_u32(&full_bar[s]), 1);
+      mbar_init(smem_u32(&empty_bar[s]), 1);
+    }
+    for (int a = 0; a < 2; ++a) {
+      mbar_init(smem_u32(&accum_full[a]), 1);
+      mbar_init(smem_u32(&accum_empty[a]), 2 * kEpiWarps);   // one arrival per epilogue warp of either CTA
+    }
+    mbar_init_fence();
+  }
+  if (warp == 1) tmem_alloc_pair(smem_u32(&tmem_base_s), 512);
+  tc_fence_before();
+  __syncthreads();
+  sb::cluster_sync();      // the peer's barriers exist before anything signals them
+  tc_fence_after();
+  const uint32_t tmem_base = tmem_base_s;
+
+  sb::grid_launch_dependents();
+  if (warp == 0) {
+    if (lane == 0) {
+      // ---------------- producer of this CTA: its half of the weight rows and of the tokens, counted on the leader's barrier
+      sb::grid_dependency_wait();
+      int it = 0;
+      for (int tile = pair; tile < total_tiles; tile += pairs) {
+        const int tile_m = tile % p.tiles_m, tile_n = tile / p.tiles_m;
+        for (int i = 0; i < kblocks; ++i, ++it) {
+          const int slot = it % p.stages;
+          if (it >= p.stages) mbar_wait(smem_u32(&empty_bar[slot]), ((it / p.stages) - 1) & 1, p.status, 1);
+          const uint32_t bar = smem_u32(&full_bar[slot]);
+          const uint32_t a = smem0 + slot * stage_bytes;
+          if (rank == 0) mbar_expect_tx(bar, 2 * stage_bytes);
+          const int k = i * kTileK;
+          if (EPI == kSwiglu) {
+            const int row_w = tile_m * 128 + rank * 64;        // 64 gate rows and their 64 up rows
+            tma_load_2d_pair(a, &map_w, bar, k, row_w);
+            tma_load_2d_pair(a + kStageA / 2, &map_w, bar, k, p.half_rows + row_w);
+          } else {
+            tma_load_2d_pair(a, &map_w, bar, k, tile_m * 256 + rank * kTileM);
+          }
+          tma_load_2d_pair(a + kStageA, &map_x, bar, k, tile_n * BN + rank * half_n);
+        }
+      }
+    }
+  } else if (warp == 1) {
+    if (lane == 0 && rank == 0) {
+      // ---------------- MMA issuer of the pair
+      const uint32_t idesc = sb::tc5::instr_desc(256, BN, false);
+      int it = 0, q = 0;
+      for (int tile = pair; tile < total_tiles; tile += pairs) {
+        for (int r = 0; r < p.splits; ++r, ++q) {
+          const int kb0 = r * p.kblocks_per_split;
+          const int iters = min(kblocks, kb0 + p.kblocks_per_split) - kb0;
+          const int acc = q & 1;
+          if (q >= 2) mbar_wait(smem_u32(&accum_empty[acc]), ((q >> 1) - 1) & 1, p.status, 4);
+          tc_fence_after();
+          const uint32_t tmem_d = tmem_base + acc * BN;
+          for (int i = 0; i < iters; ++i, ++it) {
+            const int slot = it % p.stages;
+            mbar_wait(smem_u32(&full_bar[slot]), (it / p.stages) & 1, p.status, 2);
+            tc_fence_after();
+            const uint32_t a = smem0 + slot * stage_bytes, b = a + kStageA;
+            const uint64_t da = smem_desc_sw128(a), db = smem_desc_sw128(b);
+#pragma unroll
+            for (int k = 0; k < kTileK / 16; ++k) umma_pair_bf16(tmem_d, da + 2 * k, db + 2 * k, idesc, (i > 0 || k > 0) ? 1u : 0u);
+            umma_pair_commit(smem_u32(&empty_bar[slot]));
+          }
+          umma_pair_commit(smem_u32(&accum_full[acc]));
+        }
+      }
+    }
+    __syncwarp();
+  } else {
+    // ---------------- epilogue of this CTA's 128 rows
+    const int quarter = warp & 3;
+    sb::grid_dependency_wait();
+    int q = 0;
+    for (int tile = pair; tile < total_tiles; tile += pairs) {
+      const int tile_m = tile % p.tiles_m, tile_n = tile / p.tiles_m;
+      if (EPI == kSwiglu) {
+        const int acc = q & 1;
+        const bool ok = mbar_wait(smem_u32(&accum_full[acc]), (q >> 1) & 1, p.status, 3);
+        tc_fence_after();
+        const uint32_t tmem_d = tmem_base + acc * BN + (static_cast<uint32_t>(quarter * 32) << 16);
+        const int n0 = tile_n * BN;
+        // lanes 0..63 hold gate rows, lanes 64..127 the matching up rows; the two sets of four warps take
+        // alternate groups of sixteen tokens, each set with its own exchange buffer and barrier
+        const int j = tile_m * 128 + rank * 64 + (quarter & 1) * 32 + lane;  // output feature
+        const int set = (warp - 2) >> 2;
+        float* xch = xch2[set];
+        bf16* out = reinterpret_cast<bf16*>(p.out);
+        for (int c0 = 16 * set; c0 < BN; c0 += 32) {
+          float v[16];
+          tmem_load16(tmem_d + c0, v);
+          // gate warps hand over columns 8..15, up warps columns 0..7: every warp then finishes eight columns
+          if (quarter >= 2) {
+#pragma unroll
+            for (int c = 0; c < 8; ++c) xch[c * 64 + (quarter - 2) * 32 + lane] = v[c];
+          } else {
+#pragma unroll
+            for (int c = 0; c < 8; ++c) xch[(8 + c) * 64 + quarter * 32 + lane] = v[8 + c];
+          }
+          if (set == 0) asm volatile("bar.sync 1, 128;" ::: "memory");
+          else asm volatile("bar.sync 2, 128;" ::: "memory");
+          if (ok && j < p.half_rows) {
+            const int cb = quarter >= 2 ? 8 : 0;
+#pragma unroll
+            for (int c = 0; c < 8; ++c) {
+              const int n = n0 + c0 + cb + c;
+              if (n < p.N) {
+                const float other = xch[(cb + c) * 64 + (quarter & 1) * 32 + lane];
+                const float g = quarter >= 2 ? other : v[c], u = quarter >= 2 ? v[8 + c] : other;
+                out[static_cast<int64_t>(n) * p.ldo + j] = __float2bfloat16_rn(silu_fast(g) * u);
+              }
+            }
+          }
+          if (set == 0) asm volatile("bar.sync 1, 128;" ::: "memory");
+          else asm volatile("bar.sync 2, 128;" ::: "memory");
+        }
+        tc_fence_before();
+        __syncwarp();
+        if (lane == 0) mbar_arrive_leader(smem_u32(&accum_empty[acc]));
+        ++q;
+      } else {
+        const int half = (warp - 2) >> 2, cols = BN / 2;
+        const int m = tile_m * 256 + rank * kTileM + quarter * 32 + lane;
+        const int n0 = tile_n * BN + half * cols;
+        const bool live = m < p.M;
+        float* o = p.out + static_cast<int64_t>(n0) * p.ldo + m;
+        float run[kFoldCols];
+#pragma unroll 1
+        for (int r = 0; r < p.splits; ++r, ++q) {
+          const int acc = q & 1;
+          mbar_wait(smem_u32(&accum_full[acc]), (q >> 1) & 1, p.status, 3);
+          tc_fence_after();
+          const uint32_t tmem_d = tmem_base + acc * BN + half * cols + (static_cast<uint32_t>(quarter * 32) << 16);
+          if (r == 0) {
+#pragma unroll
+            for (int c0 = 0; c0 < kFoldCols; c0 += 16)
+              if (c0 < cols) tmem_load16(tmem_d + c0, run + c0);
+          } else {
+#pragma unroll
+            for (int c0 = 0; c0 < kFoldCols; c0 += 16) {
+              if (c0 < cols) {
+                float v[16];
+                tmem_load16(tmem_d + c0, v);
+#pragma unroll
+                for (int c = 0; c < 16; ++c) run[c0 + c] += v[c];
+              }
+            }
+          }
+          tc_fence_before();
+          __syncwarp();
+          if (lane == 0) mbar_arrive_leader(smem_u32(&accum_empty[acc]));
+        }
+        if (live) {
+#pragma unroll
+          for (int c = 0; c < kFoldCols; ++c)
+            if (c < cols && n0 + c < p.N) o[static_cast<int64_t>(c) * p.ldo] = run[c];
+        }
+      }
+    }
+    tc_fence_before();
+  }
+  __syncthreads();
+  sb::cluster_sync();      // neither CTA frees the pair's tensor memory, or leaves, while the other still works
+  if (warp == 1) {
+    tc_fence_after();
+    tmem_dealloc_pair(tmem_base, 512);
+  }
+}
+
 // ------------------------------------------------------------------ host side
 // Tensor map of a row-major bfloat16 matrix [rows, cols] with leading dimension ld (elements) and a box of
 // box_rows x 64 elements in the 128-byte swizzle.
@@ -674,6 +881,50 @@ SB_EXPORT int sb_gemm_tc(const void* x, int64_t ldx, const void* w, int64_t ldw,
     return sb::fail("sb_gemm_tc: %d splits leave an empty K range (use sb_gemm_tc_splits)", splits);
   p.half_rows = half_rows;
   p.status = status;
+
+  if (n > 256 && epilogue != kAdd) {
+    // Pairs of CTAs: tiles of 256 weight rows (or 128 gate + 128 up rows) by BN tokens, BN chosen by whole waves of 74 pairs.
+    const long long tm = epilogue == kSwiglu ? (half_rows + 127) / 128 : (M + 255) / 256;
+    long long best = -1;
+    int bn_best = 256;
+    for (int bn = 256; bn >= 128; bn -= 32) {
+      const long long cost = ((tm * ((n + bn - 1) / bn) + 73) / 74) * bn;
+      if (best < 0 || cost < best) {
+        best = cost;
+        bn_best = bn;
+      }
+    }
+    p.block_n = bn_best;
+    const int pair_stage = kStageA + (p.block_n / 2) * 128;
+    p.stages = min(kMaxStages, kSmemBudget / pair_stage);
+    p.kblocks_per_split = (kblocks + splits - 1) / splits;
+    if ((kblocks + p.kblocks_per_split - 1) / p.kblocks_per_split != splits)
+      return sb::fail("sb_gemm_tc: %d splits leave an empty K range (use sb_gemm_tc_splits)", splits);
+    p.half_rows = half_rows;
+    p.status = status;
+    p.tiles_m = static_cast<int>(tm);
+    p.tiles_n = (n + p.block_n - 1) / p.block_n;
+    p.splits = splits;
+    CUtensorMap pw, px;
+    if (!tensor_map(w, M, K, ldw, epilogue == kSwiglu ? 64 : kTileM, &pw) || !tensor_map(x, n, K, ldx, p.block_n / 2, &px))
+      return sb::fail("sb_gemm_tc: cuTensorMapEncodeTiled failed (M %d N %d K %d)", M, n, K);
+    const long long tiles = static_cast<long long>(p.tiles_m) * p.tiles_n;
+    if (tiles > (1ll << 30)) return sb::fail("sb_gemm_tc: too many tiles");
+    const dim3 grid(static_cast<unsigned>(2 * min(tiles, 74ll)));
+    const size_t psmem = static_cast<size_t>(p.stages) * pair_stage + 1024;
+    static bool attr_set = false;
+    if (!attr_set) {
+      if (cudaFuncSetAttribute(gemm_tc_pair_kernel<kStore>, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBudget + 2048) != cudaSuccess ||
+          cudaFuncSetAttribute(gemm_tc_pair_kernel<kSwiglu>, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBudget + 2048) != cudaSuccess)
+        return sb::fail("sb_gemm_tc: cannot raise the shared memory limit");
+      attr_set = true;
+    }
+    if (epilogue == kStore)
+      sb::launch_pdl_cluster(gemm_tc_pair_kernel<kStore>, grid, dim3(kFoldThreads), psmem, stream, dim3(2, 1, 1), pw, px, p);
+    else
+      sb::launch_pdl_cluster(gemm_tc_pair_kernel<kSwiglu>, grid, dim3(kFoldThreads), psmem, stream, dim3(2, 1, 1), pw, px, p);
+    return sb::check_launch("sb_gemm_tc");
+  }
 
   CUtensorMap map_w, map_x;
   const int box_w = epilogue == kSwiglu ? 64 : kTileM;

@@ -39,14 +39,20 @@ __device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
       : "memory");
   return ok != 0;
 }
-// Bounded wait: gives up after kWaitCycles, records `code` in *status (if still 0) and returns false.
+// Bounded wait: gives up after kWaitCycles, records `code` in *status (if still 0) and returns false. Once any wait
+// of the launch (or of an earlier one whose status nobody has read) gave up, the others give up at once, so a
+// kernel that lost a signal ends within about a second however many waits it still has in front of it.
 __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, int* status, int code) {
   if (mbar_try_wait(bar, parity)) return true;
   const long long t0 = clock64();
+  int spins = 0;
   while (!mbar_try_wait(bar, parity)) {
-    if (clock64() - t0 > kWaitCycles) {
-      atomicCAS(status, 0, code);
-      return false;
+    if ((++spins & 255) == 0) {
+      if (*reinterpret_cast<volatile int*>(status) != 0) return false;
+      if (clock64() - t0 > kWaitCycles) {
+        atomicCAS(status, 0, code);
+        return false;
+      }
     }
   }
   return true;
@@ -90,6 +96,43 @@ __device__ __forceinline__ void umma_bf16(uint32_t tmem_d, uint64_t desc_a, uint
 }
 __device__ __forceinline__ void umma_commit(uint32_t bar) {
   asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
+}
+
+// ---- the same for a pair of CTAs (a cluster of two on neighbouring SMs, cta_group::2): one tcgen05.mma of the
+// leader (cluster rank 0) multiplies 256 rows, the upper 128 of A and the second half of B's rows lying at the same
+// shared-memory offsets in the peer CTA; each CTA's tensor memory gets its 128 rows of D.
+constexpr uint32_t kPeerBitMask = 0xFEFFFFFFu;   // a shared::cluster address of the pair with the peer bit cleared: the leader's
+__device__ __forceinline__ void tmem_alloc_pair(uint32_t dst_smem, uint32_t cols) {   // one warp of each CTA, same dst offset
+  asm volatile("tcgen05.alloc.cta_group::2.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(dst_smem), "r"(cols) : "memory");
+  asm volatile("tcgen05.relinquish_alloc_permit.cta_group::2.sync.aligned;" ::: "memory");
+}
+__device__ __forceinline__ void tmem_dealloc_pair(uint32_t taddr, uint32_t cols) {
+  asm volatile("tcgen05.dealloc.cta_group::2.sync.aligned.b32 %0, %1;" ::"r"(taddr), "r"(cols) : "memory");
+}
+__device__ __forceinline__ void umma_pair_bf16(uint32_t tmem_d, uint64_t desc_a, uint64_t desc_b, uint32_t idesc, uint32_t accumulate) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "setp.ne.b32 p, %4, 0;\n\t"
+      "tcgen05.mma.cta_group::2.kind::f16 [%0], %1, %2, %3, p;\n\t}" ::"r"(tmem_d),
+      "l"(desc_a), "l"(desc_b), "r"(idesc), "r"(accumulate)
+      : "memory");
+}
+// Arrives on the barrier at this shared-memory offset in both CTAs of the pair once the MMAs issued so far are done.
+__device__ __forceinline__ void umma_pair_commit(uint32_t bar) {
+  asm volatile("tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.multicast::cluster.b64 [%0], %1;" ::"r"(bar),
+               "h"(static_cast<unsigned short>(3))
+               : "memory");
+}
+// A TMA tile load of either CTA of the pair into its own shared memory, counted on the leader's barrier (no multicast).
+__device__ __forceinline__ void tma_load_2d_pair(uint32_t dst, const CUtensorMap* map, uint32_t bar, int x, int y) {
+  asm volatile(
+      "cp.async.bulk.tensor.2d.cta_group::2.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];" ::"r"(dst),
+      "l"(reinterpret_cast<uint64_t>(map)), "r"(bar & kPeerBitMask), "r"(x), "r"(y)
+      : "memory");
+}
+// Arrives on the leader's barrier at this offset, from either CTA of the pair.
+__device__ __forceinline__ void mbar_arrive_leader(uint32_t bar) {
+  asm volatile("mbarrier.arrive.release.cluster.shared::cluster.b64 _, [%0];" ::"r"(bar & kPeerBitMask) : "memory");
 }
 
 __device__ __forceinline__ void tmem_load_wait() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
