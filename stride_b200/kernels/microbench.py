@@ -77,7 +77,7 @@ def attention(a) -> dict:
     if new <= short:
         tiles, items, chunks = [], list(range(B)), (total - 1) // 256 + 1
     else:
-        tiles, items, chunks = [x for e in range(B) for t in range(-(-new // ppt)) for x in (e, t)], [], 0
+        tiles, items, chunks = [x for t in reversed(range(-(-new // ppt))) for e in range(B) for x in (e, t)], [], 0   # longest first
     work = torch.tensor(tiles + items, dtype=torch.int32, device="cuda")
     scratch = torch.zeros(max(1, ops.attention_tc_scratch(len(items), Hkv, chunks, D)), device="cuda")
     counters = torch.zeros(max(1, len(items) * Hkv), dtype=torch.int32, device="cuda")

@@ -90,14 +90,16 @@ class AttentionMixer(Mixer):
             ctx.shared[key] = plan
         if plan is None:
             ppt, short = tile_rows // G, 16 // G
-            tiles, items, last = [], [], 0
+            tiled, items, last = [], [], 0
             for e, (L, p0) in enumerate(zip(ctx.entry_length, ctx.entry_first_pos)):
                 if L <= short:
                     items.append(e)
                     last = max(last, p0 + L - 1)
                 else:
-                    for t in range((L + ppt - 1) // ppt):
-                        tiles += [e, t]
+                    tiled += [(p0 + min(L, (t + 1) * ppt), e, t) for t in range((L + ppt - 1) // ppt)]
+            # the tiles that see the most keys first: CTAs start in this order, and the short ones fill the end
+            tiled.sort(key=lambda k: -k[0])
+            tiles = [x for _, e, t in tiled for x in (e, t)]
             work = ctx.upload_ints(np.asarray(tiles + items, dtype=np.int32))
             plan = (work, len(tiles) // 2, len(items), last // 256 + 1 if items else 0)
             ctx.shared[key] = plan
