@@ -23,6 +23,7 @@ import torch
 
 from ..cache.manager import CacheManager
 from ..config import resolve_architecture
+from ..kernels.build import build_all
 from ..parts import BuildEnv, DecoderModel, StepContext, Workspace
 from ..weights.loader import check_plan, load_weights
 
@@ -89,6 +90,7 @@ class Engine:
                        max_requests=o.max_slots)
         self.env = env
         self.model = DecoderModel(self.spec, env)
+        build_all(sorted(self.model.kernel_libraries()))      # what this model needs, compiled side by side if missing
         plan = self.model.tensor_plan()
         if tensors is None:
             tensors = load_weights(model_dir, plan, self.device)

@@ -105,6 +105,14 @@ class AttentionMixer(Mixer):
             ctx.shared[key] = plan
         return plan
 
+    def kernel_libraries(self):
+        if self.env.compute_dtype != torch.bfloat16:
+            return {"gemm_f32", "elementwise", "attention_generic"}
+        G = self.num_heads // self.num_kv_heads
+        if self.head_dim in (64, 128) and G <= 16:
+            return {"gemm_tc", "elementwise", "attention_tc"} | ({"attention_tc5"} if self.head_dim == 64 else set())
+        return {"gemm_tc", "elementwise", "attention_generic"}
+
     def forward(self, ctx, x, stream, cache):
         n, ws, D = ctx.n, ctx.workspace, self.head_dim
         qkv = self.qkv.forward_partials(x, ws.raw("attn.qkv", (self.qkv.partial_elems(ws.max_tokens),), torch.float32))

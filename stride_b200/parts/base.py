@@ -104,6 +104,12 @@ class Part:
         """Bytes of weights one decode step has to read from this part."""
         return 0
 
+    def kernel_libraries(self) -> set:
+        """Names (keys of `kernels.build.SOURCES`) of the kernel libraries this part will most likely call, so that
+        the engine can compile them side by side before the first step. A hint only: a library that is not
+        listed is compiled when it is first called."""
+        return set()
+
 
 class Norm(Part):
     def forward(self, ctx, stream, out: torch.Tensor) -> None:
@@ -153,6 +159,9 @@ class Block(Part):
 
     def weight_bytes(self) -> int:
         return sum(p.weight_bytes() for p in self.parts())
+
+    def kernel_libraries(self) -> set:
+        return set().union(*(p.kernel_libraries() for p in self.parts()))
 
     @property
     def all_graph_safe(self) -> bool:

@@ -40,6 +40,9 @@ class SwiGLU(FeedForward):
     def weight_bytes(self):
         return self.gate_up.weight_bytes() + self.down.weight_bytes()
 
+    def kernel_libraries(self):
+        return {"gemm_tc"} if self.env.compute_dtype == torch.bfloat16 else {"gemm_f32", "elementwise"}
+
     def forward(self, ctx, x, stream):
         n, ws = ctx.n, ctx.workspace
         z = ws.get("mlp.z", n, (self.intermediate,), ctx.act_dtype)

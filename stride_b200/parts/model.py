@@ -58,6 +58,12 @@ class DecoderModel:
             needs.append(("shared", e.cache_of) if e.cache_of is not None else self.blocks[e.layer].mixer.cache_need())
         return needs
 
+    def kernel_libraries(self) -> set:
+        names = {"elementwise", "gemm_tc" if self.env.compute_dtype == torch.bfloat16 else "gemm_f32"}
+        for p in self._parts():
+            names |= p.kernel_libraries()
+        return names
+
     def weight_bytes(self) -> int:
         """Bytes of weights that one decode step reads: every scheduled layer once, the final
         norm and the head (arhaamatiq/stride counts the same, src/model.cpp:198,235)."""

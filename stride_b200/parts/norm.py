@@ -31,6 +31,9 @@ class RMSNorm(Norm):
     def forward(self, ctx, stream, out):
         ops.rmsnorm(stream.h, self.weight, self.eps, out, partials=stream.take_pending())
 
+    def kernel_libraries(self):
+        return {"norm"}
+
     def forward_rows(self, rows, out):
         """Norm of a plain [n, size] float32 tensor (the rows gathered for the head)."""
         ops.rmsnorm(rows, self.weight, self.eps, out)
