@@ -38,9 +38,10 @@ constexpr int kTileBytes = 128 * 128;   // 128 rows of 64 bfloat16
 constexpr int kSoftmaxThreads = 256;    // two threads per row: each takes 64 of the tile's 128 keys and 32 of the 64 outputs
 constexpr int kThreads = kSoftmaxThreads + 32;
 constexpr int kStages = 3;              // key/value tiles in flight
-// shared memory: Q | K x kStages | V x kStages | P hi (two 64-key halves) | P lo
+// shared memory: Q | K x kStages | V x kStages | P hi (two 64-key halves) | P lo | row state
 constexpr int kPhiTile = 1 + 2 * kStages, kPloTile = kPhiTile + 2;
-constexpr int kSmemBytes = (kPloTile + 2) * kTileBytes;
+constexpr int kRowStateBytes = kRows * kD * 4;   // the rows' weighted values over the finished chunks, [output][row] float32
+constexpr int kSmemBytes = (kPloTile + 2) * kTileBytes + kRowStateBytes;
 constexpr int kPagesCached = 512;       // block-table entries of the request kept in shared memory
 constexpr uint32_t kTmemCols = 512;     // S0 [0,128) S1 [128,256) O of tile 0 [256,320) O of tile 1 [320,384)
 using namespace sb::attn;
@@ -184,65 +185,59 @@ attn_prefill_tc5_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_
     const uint32_t lane_addr = static_cast<uint32_t>((warp & 3) * 32) << 16;
     // the chunk in progress and the chunks before it; both threads of a row keep the same maxima and sums
     float m_c = -INFINITY, l_c = 0.0f, m_r = -INFINITY, l_r = 0.0f;
-    float o_c[kD / 2], o_r[kD / 2];
+    // (the finished chunks' values live in shared memory, element [output][row], touched once a chunk: registers are
+    // needed for the scores of the span in flight)
+    float o_c[kD / 2];
+    float* o_r = reinterpret_cast<float*>(smem + (kPloTile + 2) * kTileBytes) + half * 32 * kRows + r;
 #pragma unroll
-    for (int d = 0; d < kD / 2; ++d) o_c[d] = o_r[d] = 0.0f;
+    for (int d = 0; d < kD / 2; ++d) {
+      o_c[d] = 0.0f;
+      o_r[d * kRows] = 0.0f;
+    }
 
-    // Pass 1 of span i: the maximum of this thread's tile (raw scores of the keys the row sees).
+    // The scores of span i for this thread's tile: read from tensor memory once (both halves in flight together),
+    // the keys the row does not see set to -inf (their weight then comes out as ex2(-inf) = 0), and their maximum.
     auto span_masked = [&](int i) {
       return (kt0 + i) * kKeys + kKeys - 1 > pos0 || (p.window > 0 && (kt0 + i) * kKeys < pos_hi - p.window + 1) || npos * G < kRows;
     };
-    auto pass1 = [&](int i) {
+    uint32_t sv[64];
+    auto read_scores = [&](int i) {
       mbar_wait(smem_u32(&s_full[i & 1]), (i >> 1) & 1, p.status, 5);
       fence_after_sync();
       const uint32_t s_addr = tmem_base + (i & 1) * kKeys + lane_addr + half * 64;
-      const int key0 = (kt0 + i) * kKeys + half * 64;
-      const bool masked = span_masked(i);
+      tmem_load32_nowait(s_addr, sv);
+      tmem_load32_nowait(s_addr + 32, sv + 32);
+      tmem_load_wait();
+      if (span_masked(i)) {
+        const int key0 = (kt0 + i) * kKeys + half * 64;
+#pragma unroll
+        for (int j = 0; j < 64; ++j)
+          if (!(key0 + j <= row_pos && key0 + j >= row_lo)) sv[j] = 0xff800000u;   // -inf
+      }
       float mx0 = -INFINITY, mx1 = -INFINITY, mx2 = -INFINITY, mx3 = -INFINITY;
-#pragma unroll 1
-      for (int c = 0; c < 2; ++c) {
-        float v[32];
-        tmem_load32(s_addr + c * 32, v);
-        if (masked) {
 #pragma unroll
-          for (int j = 0; j < 32; ++j) {
-            const int key = key0 + c * 32 + j;
-            if (!(key <= row_pos && key >= row_lo)) v[j] = -INFINITY;
-          }
-        }
-#pragma unroll
-        for (int j = 0; j < 32; j += 4) {
-          mx0 = fmaxf(mx0, v[j]);
-          mx1 = fmaxf(mx1, v[j + 1]);
-          mx2 = fmaxf(mx2, v[j + 2]);
-          mx3 = fmaxf(mx3, v[j + 3]);
-        }
+      for (int j = 0; j < 64; j += 4) {
+        mx0 = fmaxf(mx0, __uint_as_float(sv[j]));
+        mx1 = fmaxf(mx1, __uint_as_float(sv[j + 1]));
+        mx2 = fmaxf(mx2, __uint_as_float(sv[j + 2]));
+        mx3 = fmaxf(mx3, __uint_as_float(sv[j + 3]));
       }
       return fmaxf(fmaxf(mx0, mx1), fmaxf(mx2, mx3));
     };
 
-    float raw_max = pass1(0);
+    float raw_max = read_scores(0);
     for (int i = 0; i < T; ++i) {
-      // (the scores of span i have been read once already: pass 1 ran before or during the value product of span i - 1)
+      // (the scores of span i are in registers: read before, or during the value product of span i - 1)
       const float m_t = tile_max(raw_max, p.scale_log2);
       const float ref = tile_ref(m_t);
-      const uint32_t s_addr = tmem_base + (i & 1) * kKeys + lane_addr + half * 64;
-      const int key0 = (kt0 + i) * kKeys + half * 64;
-      const bool masked = span_masked(i);
       float u0 = 0.0f, u1 = 0.0f, u2 = 0.0f, u3 = 0.0f;     // key j of the tile belongs to class (j % 8) / 2
-#pragma unroll 1
+#pragma unroll
       for (int c = 0; c < 2; ++c) {
-        float v[32];
-        tmem_load32(s_addr + c * 32, v);
         uint32_t hi[16], lo[16];
 #pragma unroll
         for (int j = 0; j < 32; j += 2) {
-          float p0 = weight(v[j], p.scale_log2, ref), p1 = weight(v[j + 1], p.scale_log2, ref);
-          if (masked) {
-            const int key = key0 + c * 32 + j;
-            if (!(key <= row_pos && key >= row_lo)) p0 = 0.0f;
-            if (!(key + 1 <= row_pos && key + 1 >= row_lo)) p1 = 0.0f;
-          }
+          const float p0 = weight(__uint_as_float(sv[c * 32 + j]), p.scale_log2, ref);
+          const float p1 = weight(__uint_as_float(sv[c * 32 + j + 1]), p.scale_log2, ref);
           if ((j & 6) == 0) u0 = __fadd_rn(__fadd_rn(u0, p0), p1);
           else if ((j & 6) == 2) u1 = __fadd_rn(__fadd_rn(u1, p0), p1);
           else if ((j & 6) == 4) u2 = __fadd_rn(__fadd_rn(u2, p0), p1);
@@ -262,7 +257,7 @@ attn_prefill_tc5_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_
       fence_before_sync();
       fence_async_smem();
       mbar_arrive(smem_u32(&p_full));
-      if (i + 1 < T) raw_max = pass1(i + 1);           // under the value product of span i
+      if (i + 1 < T) raw_max = read_scores(i + 1);     // under the value product of span i
       mbar_wait(smem_u32(&o_full), i & 1, p.status, 6);
       fence_after_sync();
       softmax_barrier();    // both threads of every row have written xch[i & 1]; it is rewritten two spans later
@@ -284,7 +279,7 @@ attn_prefill_tc5_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_
           const FoldFactors f = fold_factors(m_r, m_c);
           l_r = fold_value(l_r, l_c, f);
 #pragma unroll
-          for (int j = 0; j < 32; ++j) o_r[j] = fold_value(o_r[j], o_c[j], f);
+          for (int j = 0; j < 32; ++j) o_r[j * kRows] = fold_value(o_r[j * kRows], o_c[j], f);
           m_r = f.m;
         }
         m_c = -INFINITY;
@@ -301,7 +296,7 @@ attn_prefill_tc5_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_
         uint32_t w[4];
 #pragma unroll
         for (int j = 0; j < 4; ++j) {
-          const __nv_bfloat162 h = __floats2bfloat162_rn(finish(o_r[c * 8 + 2 * j], l_r), finish(o_r[c * 8 + 2 * j + 1], l_r));
+          const __nv_bfloat162 h = __floats2bfloat162_rn(finish(o_r[(c * 8 + 2 * j) * kRows], l_r), finish(o_r[(c * 8 + 2 * j + 1) * kRows], l_r));
           w[j] = *reinterpret_cast<const uint32_t*>(&h);
         }
         *reinterpret_cast<uint4*>(dst + c * 8) = make_uint4(w[0], w[1], w[2], w[3]);
