@@ -11,10 +11,11 @@
 //     span's two tiles of 64 keys by tcgen05.mma (M 128, N 64, K 64, V as an MN-major operand straight from
 //     its [key][64] page layout), each into an accumulator of its own, from zero.
 //   eight softmax warps (two threads per row, TMEM lane = row; thread `half` owns the span's tile `half` and
-//     the output elements [32 half, 32 half + 32)): read S with tcgen05.ld, take the tile's maximum, write the
-//     weights to shared memory as two bfloat16 parts (p = hi + lo, so the value product sees nearly 32-bit
-//     weights, as the reference's 32-bit softmax does), then fold O_0 and O_1 into the row's chunk state and,
-//     every 256 keys, the chunk into the row's state, all in float32 registers.
+//     the output elements [32 half, 32 half + 32)): read S with tcgen05.ld (once a span, kept in registers), take
+//     the tile's maximum, write the weights to tensor memory with tcgen05.st as two bfloat16 parts (p = hi + lo, so
+//     the value product sees nearly 32-bit weights, as the reference's 32-bit softmax does; the value product takes
+//     them from there as its A operand), then fold O_0 and O_1 into the row's chunk state (registers) and, every
+//     256 keys, the chunk into the row's state (shared memory), all in float32.
 //
 // The arithmetic is that of attention_math.cuh, shared with the mma.sync kernels of attention_tc.cu: a row has
 // the same bits from either. Every mbarrier wait is bounded and reports through a status word. Key spans past
@@ -38,12 +39,14 @@ constexpr int kTileBytes = 128 * 128;   // 128 rows of 64 bfloat16
 constexpr int kSoftmaxThreads = 256;    // two threads per row: each takes 64 of the tile's 128 keys and 32 of the 64 outputs
 constexpr int kThreads = kSoftmaxThreads + 32;
 constexpr int kStages = 3;              // key/value tiles in flight
-// shared memory: Q | K x kStages | V x kStages | P hi (two 64-key halves) | P lo | row state
-constexpr int kPhiTile = 1 + 2 * kStages, kPloTile = kPhiTile + 2;
+// shared memory: Q | K x kStages | V x kStages | row state
+constexpr int kTiles = 1 + 2 * kStages;   // tiles of shared memory in front of the row state
 constexpr int kRowStateBytes = kRows * kD * 4;   // the rows' weighted values over the finished chunks, [output][row] float32
-constexpr int kSmemBytes = (kPloTile + 2) * kTileBytes + kRowStateBytes;
+constexpr int kSmemBytes = kTiles * kTileBytes + kRowStateBytes;
 constexpr int kPagesCached = 512;       // block-table entries of the request kept in shared memory
-constexpr uint32_t kTmemCols = 512;     // S0 [0,128) S1 [128,256) O of tile 0 [256,320) O of tile 1 [320,384)
+// tensor memory: S0 [0,128) S1 [128,256) O of tile 0 [256,320) O of tile 1 [320,384) P hi [384,448) P lo [448,512); the
+// weights of 128 keys are 64 columns (two bfloat16 a column), the span's tile t in columns 32 t .. 32 t + 31
+constexpr uint32_t kTmemCols = 512, kTmemPhi = 384, kTmemPlo = 448;
 using namespace sb::attn;
 static_assert(kKeys == 2 * kTileKeys && kChunkKeys == 2 * kKeys, "a span is two tiles, a chunk two spans");
 
@@ -74,8 +77,7 @@ attn_prefill_tc5_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   const uint32_t smem0 = (smem_u32(smem_raw) + 1023u) & ~1023u;
   uint8_t* smem = smem_raw + (smem0 - smem_u32(smem_raw));
-  const uint32_t sQ = smem0, sK = smem0 + kTileBytes, sV = smem0 + (1 + kStages) * kTileBytes,
-                 sPhi = smem0 + kPhiTile * kTileBytes, sPlo = smem0 + kPloTile * kTileBytes;
+  const uint32_t sQ = smem0, sK = smem0 + kTileBytes, sV = smem0 + (1 + kStages) * kTileBytes;
 
   const int g = blockIdx.y;
   const int G = p.Hq / p.Hkv, ppt = kRows / G;
@@ -137,7 +139,6 @@ attn_prefill_tc5_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_
       // descriptors are built once; a tile, a 64-key half or a K step only adds to the start-address field
       const uint32_t idesc_qk = instr_desc(kRows, kKeys, false), idesc_pv = instr_desc(kRows, kD, true);
       const uint64_t dQ = smem_desc_sw128(sQ), dK = smem_desc_sw128(sK), dV = smem_desc_sw128(sV);
-      const uint64_t dPhi = smem_desc_sw128(sPhi), dPlo = smem_desc_sw128(sPlo);
       constexpr uint64_t kTileStep = kTileBytes >> 4, kVStep = 2048 >> 4;
       auto issue_qk = [&](int i) {
         const uint64_t db = dK + (i % kStages) * kTileStep;
@@ -163,10 +164,10 @@ attn_prefill_tc5_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_
         const uint64_t dv = dV + (i % kStages) * kTileStep;
 #pragma unroll
         for (int ks = 0; ks < kKeys / 16; ++ks) {
-          const uint64_t pa = (ks >> 2) * kTileStep + 2 * (ks & 3);     // the tile's half of P, the K step inside it
+          const uint32_t pa = ks * 8;                                    // sixteen keys are eight columns of P
           const uint32_t d = tmem_base + 2 * kKeys + (ks >> 2) * kD;     // the tile's accumulator
-          umma_bf16(d, dPhi + pa, dv + ks * kVStep, idesc_pv, (ks & 3) > 0 ? 1u : 0u);
-          umma_bf16(d, dPlo + pa, dv + ks * kVStep, idesc_pv, 1u);
+          umma_ts_bf16(d, tmem_base + kTmemPhi + pa, dv + ks * kVStep, idesc_pv, (ks & 3) > 0 ? 1u : 0u);
+          umma_ts_bf16(d, tmem_base + kTmemPlo + pa, dv + ks * kVStep, idesc_pv, 1u);
         }
         umma_commit(smem_u32(&o_full));
         mbar_wait(smem_u32(&o_full), i & 1, p.status, 4);     // then this tile's key/value buffers are free
@@ -188,7 +189,7 @@ attn_prefill_tc5_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_
     // (the finished chunks' values live in shared memory, element [output][row], touched once a chunk: registers are
     // needed for the scores of the span in flight)
     float o_c[kD / 2];
-    float* o_r = reinterpret_cast<float*>(smem + (kPloTile + 2) * kTileBytes) + half * 32 * kRows + r;
+    float* o_r = reinterpret_cast<float*>(smem + kTiles * kTileBytes) + half * 32 * kRows + r;
 #pragma unroll
     for (int d = 0; d < kD / 2; ++d) {
       o_c[d] = 0.0f;
@@ -244,18 +245,13 @@ attn_prefill_tc5_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_
           else u3 = __fadd_rn(__fadd_rn(u3, p0), p1);
           split_hi_lo(p0, p1, hi[j >> 1], lo[j >> 1]);
         }
-        // 32 keys = four 16-byte pieces of this row in the 64-key half `half`, at pieces c * 4 .. + 3
-        const uint32_t row_off = half * kTileBytes + r * 128;
-#pragma unroll
-        for (int q = 0; q < 4; ++q) {
-          const uint32_t piece = ((c * 4 + q) ^ (r & 7)) * 16;
-          *reinterpret_cast<uint4*>(smem + kPhiTile * kTileBytes + row_off + piece) = make_uint4(hi[4 * q], hi[4 * q + 1], hi[4 * q + 2], hi[4 * q + 3]);
-          *reinterpret_cast<uint4*>(smem + kPloTile * kTileBytes + row_off + piece) = make_uint4(lo[4 * q], lo[4 * q + 1], lo[4 * q + 2], lo[4 * q + 3]);
-        }
+        // 32 keys = sixteen columns of this row (lane) in tensor memory, the tile's columns 32 half .. 32 half + 31
+        tmem_store16(tmem_base + kTmemPhi + lane_addr + half * 32 + c * 16, hi);
+        tmem_store16(tmem_base + kTmemPlo + lane_addr + half * 32 + c * 16, lo);
       }
+      tmem_store_wait();
       xch[i & 1][half][r] = make_float2(m_t, class_sum(u0, u1, u2, u3));
       fence_before_sync();
-      fence_async_smem();
       mbar_arrive(smem_u32(&p_full));
       if (i + 1 < T) raw_max = read_scores(i + 1);     // under the value product of span i
       mbar_wait(smem_u32(&o_full), i & 1, p.status, 6);

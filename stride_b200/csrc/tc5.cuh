@@ -136,6 +136,26 @@ __device__ __forceinline__ void mbar_arrive_leader(uint32_t bar) {
 }
 
 __device__ __forceinline__ void tmem_load_wait() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
+// Sixteen registers of this thread into sixteen consecutive columns of its TMEM lane; tmem_store_wait() before another
+// thread (or the tensor cores) may read them.
+__device__ __forceinline__ void tmem_store16(uint32_t taddr, const uint32_t* r) {
+  asm volatile(
+      "tcgen05.st.sync.aligned.32x32b.x16.b32 [%0], {%1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, %16};" ::"r"(taddr),
+      "r"(r[0]), "r"(r[1]), "r"(r[2]), "r"(r[3]), "r"(r[4]), "r"(r[5]), "r"(r[6]), "r"(r[7]), "r"(r[8]), "r"(r[9]), "r"(r[10]),
+      "r"(r[11]), "r"(r[12]), "r"(r[13]), "r"(r[14]), "r"(r[15])
+      : "memory");
+}
+__device__ __forceinline__ void tmem_store_wait() { asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory"); }
+// D (+)= A B with A [128 x 16] bfloat16 in tensor memory: row = lane, two elements of consecutive k per 32-bit column
+// (the even k in the low half), eight columns from tmem_a on.
+__device__ __forceinline__ void umma_ts_bf16(uint32_t tmem_d, uint32_t tmem_a, uint64_t desc_b, uint32_t idesc, uint32_t accumulate) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "setp.ne.b32 p, %4, 0;\n\t"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], %2, %3, p;\n\t}" ::"r"(tmem_d),
+      "r"(tmem_a), "l"(desc_b), "r"(idesc), "r"(accumulate)
+      : "memory");
+}
 // 32 consecutive columns of this thread's TMEM lane (the warp reads lanes 32 * (warp % 4) ..), as raw bits and without
 // waiting: several loads can be in flight; tmem_load_wait() before the first use of any of them.
 __device__ __forceinline__ void tmem_load32_nowait(uint32_t taddr, uint32_t* r) {
