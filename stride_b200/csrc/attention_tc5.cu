@@ -44,9 +44,10 @@ constexpr int kTiles = 1 + 2 * kStages;   // tiles of shared memory in front of 
 constexpr int kRowStateBytes = kRows * kD * 4;   // the rows' weighted values over the finished chunks, [output][row] float32
 constexpr int kSmemBytes = kTiles * kTileBytes + kRowStateBytes;
 constexpr int kPagesCached = 512;       // block-table entries of the request kept in shared memory
-// tensor memory: S0 [0,128) S1 [128,256) O of tile 0 [256,320) O of tile 1 [320,384) P hi [384,448) P lo [448,512); the
-// weights of 128 keys are 64 columns (two bfloat16 a column), the span's tile t in columns 32 t .. 32 t + 31
-constexpr uint32_t kTmemCols = 512, kTmemPhi = 384, kTmemPlo = 448;
+// tensor memory: S [0,128), O of tile 0 [128,192), O of tile 1 [192,256), then two buffers of weights (by span parity),
+// each P hi (64 columns) and P lo (64 columns): the weights of 128 keys are 64 columns (two bfloat16 a column), the
+// span's tile t in columns 32 t .. 32 t + 31
+constexpr uint32_t kTmemCols = 512, kTmemO = 128, kTmemP = 256;
 using namespace sb::attn;
 static_assert(kKeys == 2 * kTileKeys && kChunkKeys == 2 * kKeys, "a span is two tiles, a chunk two spans");
 
@@ -69,10 +70,10 @@ struct Fa5Params {
 __global__ void __launch_bounds__(kThreads, 1)
 attn_prefill_tc5_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_kv, const Fa5Params p) {
   extern __shared__ __align__(1024) uint8_t smem_raw[];
-  __shared__ __align__(8) uint64_t q_full, kv_full[kStages], s_full[2], p_full, o_full;
+  __shared__ __align__(8) uint64_t q_full, kv_full[kStages], s_full, s_free, p_full[2], o_full, o_free;
   __shared__ uint32_t tmem_base_s;
   __shared__ int32_t pages_s[kPagesCached];
-  __shared__ float2 xch[2][2][kRows];      // [span parity][tile][row]: the tile's maximum and sum, for the row's other thread
+  __shared__ float2 xch[3][2][kRows];      // [span % 3][tile][row]: the tile's maximum and sum, for the row's other thread
 
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   const uint32_t smem0 = (smem_u32(smem_raw) + 1023u) & ~1023u;
@@ -93,9 +94,11 @@ attn_prefill_tc5_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_
   if (tid == 0) {
     mbar_init(smem_u32(&q_full), 1);
     for (int i = 0; i < kStages; ++i) mbar_init(smem_u32(&kv_full[i]), 1);
-    for (int i = 0; i < 2; ++i) mbar_init(smem_u32(&s_full[i]), 1);
-    mbar_init(smem_u32(&p_full), kSoftmaxThreads);
+    mbar_init(smem_u32(&s_full), 1);
+    mbar_init(smem_u32(&s_free), kSoftmaxThreads);
+    for (int i = 0; i < 2; ++i) mbar_init(smem_u32(&p_full[i]), kSoftmaxThreads);   // one per buffer of weights
     mbar_init(smem_u32(&o_full), 1);
+    mbar_init(smem_u32(&o_free), kSoftmaxThreads);
     mbar_init_fence();
   }
   if (warp == 8) tmem_alloc(smem_u32(&tmem_base_s), kTmemCols);
@@ -143,8 +146,8 @@ attn_prefill_tc5_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_
       auto issue_qk = [&](int i) {
         const uint64_t db = dK + (i % kStages) * kTileStep;
 #pragma unroll
-        for (int k = 0; k < kD / 16; ++k) umma_bf16(tmem_base + (i & 1) * kKeys, dQ + 2 * k, db + 2 * k, idesc_qk, k > 0 ? 1u : 0u);
-        umma_commit(smem_u32(&s_full[i & 1]));
+        for (int k = 0; k < kD / 16; ++k) umma_bf16(tmem_base, dQ + 2 * k, db + 2 * k, idesc_qk, k > 0 ? 1u : 0u);
+        umma_commit(smem_u32(&s_full));
       };
       mbar_expect_tx(smem_u32(&q_full), ppt * G * 128);
       tma_load_3d(sQ, &map_q, smem_u32(&q_full), 0, g * G, row0);
@@ -153,25 +156,35 @@ attn_prefill_tc5_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_
       mbar_wait(smem_u32(&kv_full[0]), 0, p.status, 2);
       fence_after_sync();
       issue_qk(0);
+      // The softmax threads keep a span's scores in registers, so the one S accumulator is free for span i + 1 as soon
+      // as all of them have read span i; with two buffers of weights, the value product of span i runs while they
+      // compute the weights of span i + 1.
       for (int i = 0; i < T; ++i) {
+        mbar_wait(smem_u32(&s_free), i & 1, p.status, 7);
         if (i + 1 < T) {
           mbar_wait(smem_u32(&kv_full[(i + 1) % kStages]), ((i + 1) / kStages) & 1, p.status, 2);
           fence_after_sync();
           issue_qk(i + 1);
         }
-        mbar_wait(smem_u32(&p_full), i & 1, p.status, 3);
+        if (i >= 1) {
+          mbar_wait(smem_u32(&o_full), (i - 1) & 1, p.status, 4);     // then span i - 1's key/value buffers are free
+          if (i - 1 + kStages < T) load_kv(i - 1 + kStages);
+        }
+        // (the softmax threads may be a span ahead: they fill the other buffer of weights while this one is waited for,
+        // hence a barrier per buffer)
+        mbar_wait(smem_u32(&p_full[i & 1]), (i >> 1) & 1, p.status, 3);
+        if (i >= 1) mbar_wait(smem_u32(&o_free), (i - 1) & 1, p.status, 8);   // the O accumulators have been folded
         fence_after_sync();
         const uint64_t dv = dV + (i % kStages) * kTileStep;
+        const uint32_t tp = tmem_base + kTmemP + (i & 1) * 128;
 #pragma unroll
         for (int ks = 0; ks < kKeys / 16; ++ks) {
           const uint32_t pa = ks * 8;                                    // sixteen keys are eight columns of P
-          const uint32_t d = tmem_base + 2 * kKeys + (ks >> 2) * kD;     // the tile's accumulator
-          umma_ts_bf16(d, tmem_base + kTmemPhi + pa, dv + ks * kVStep, idesc_pv, (ks & 3) > 0 ? 1u : 0u);
-          umma_ts_bf16(d, tmem_base + kTmemPlo + pa, dv + ks * kVStep, idesc_pv, 1u);
+          const uint32_t d = tmem_base + kTmemO + (ks >> 2) * kD;        // the tile's accumulator
+          umma_ts_bf16(d, tp + pa, dv + ks * kVStep, idesc_pv, (ks & 3) > 0 ? 1u : 0u);
+          umma_ts_bf16(d, tp + 64 + pa, dv + ks * kVStep, idesc_pv, 1u);
         }
         umma_commit(smem_u32(&o_full));
-        mbar_wait(smem_u32(&o_full), i & 1, p.status, 4);     // then this tile's key/value buffers are free
-        if (i + kStages < T) load_kv(i + kStages);
       }
     }
     __syncwarp();
@@ -203,12 +216,14 @@ attn_prefill_tc5_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_
     };
     uint32_t sv[64];
     auto read_scores = [&](int i) {
-      mbar_wait(smem_u32(&s_full[i & 1]), (i >> 1) & 1, p.status, 5);
+      mbar_wait(smem_u32(&s_full), i & 1, p.status, 5);
       fence_after_sync();
-      const uint32_t s_addr = tmem_base + (i & 1) * kKeys + lane_addr + half * 64;
+      const uint32_t s_addr = tmem_base + lane_addr + half * 64;
       tmem_load32_nowait(s_addr, sv);
       tmem_load32_nowait(s_addr + 32, sv + 32);
       tmem_load_wait();
+      fence_before_sync();
+      mbar_arrive(smem_u32(&s_free));      // this thread has its scores: the accumulator may be overwritten
       if (span_masked(i)) {
         const int key0 = (kt0 + i) * kKeys + half * 64;
 #pragma unroll
@@ -226,11 +241,47 @@ attn_prefill_tc5_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_
       return fmaxf(fmaxf(mx0, mx1), fmaxf(mx2, mx3));
     };
 
+    // Folds the two tiles of span j (their value products are complete) into the chunk, and the chunk into the row.
+    auto fold_span = [&](int j) {
+      mbar_wait(smem_u32(&o_full), j & 1, p.status, 6);
+      fence_after_sync();
+      softmax_barrier();    // both threads of every row have written xch[j % 3]; it is rewritten three spans later
+#pragma unroll
+      for (int t = 0; t < 2; ++t) {
+        float v[32];
+        tmem_load32(tmem_base + kTmemO + t * kD + lane_addr + half * 32, v);
+        const float2 ml = xch[j % 3][t][r];
+        if (ml.x != -INFINITY) {
+          const FoldFactors f = fold_factors(m_c, ml.x);
+          l_c = fold_value(l_c, ml.y, f);
+#pragma unroll
+          for (int k = 0; k < 32; ++k) o_c[k] = fold_value(o_c[k], v[k], f);
+          m_c = f.m;
+        }
+      }
+      fence_before_sync();
+      mbar_arrive(smem_u32(&o_free));       // the accumulators may take the next span's products
+      if (((kt0 + j) & 1) || j == T - 1) {      // the chunk of 256 keys is complete
+        if (m_c != -INFINITY) {
+          const FoldFactors f = fold_factors(m_r, m_c);
+          l_r = fold_value(l_r, l_c, f);
+#pragma unroll
+          for (int k = 0; k < 32; ++k) o_r[k * kRows] = fold_value(o_r[k * kRows], o_c[k], f);
+          m_r = f.m;
+        }
+        m_c = -INFINITY;
+        l_c = 0.0f;
+#pragma unroll
+        for (int k = 0; k < 32; ++k) o_c[k] = 0.0f;
+      }
+    };
+
     float raw_max = read_scores(0);
     for (int i = 0; i < T; ++i) {
-      // (the scores of span i are in registers: read before, or during the value product of span i - 1)
+      // weights of span i from the scores in registers, into the weight buffer of its parity
       const float m_t = tile_max(raw_max, p.scale_log2);
       const float ref = tile_ref(m_t);
+      const uint32_t tp = tmem_base + kTmemP + (i & 1) * 128 + lane_addr + half * 32;
       float u0 = 0.0f, u1 = 0.0f, u2 = 0.0f, u3 = 0.0f;     // key j of the tile belongs to class (j % 8) / 2
 #pragma unroll
       for (int c = 0; c < 2; ++c) {
@@ -245,46 +296,18 @@ attn_prefill_tc5_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_
           else u3 = __fadd_rn(__fadd_rn(u3, p0), p1);
           split_hi_lo(p0, p1, hi[j >> 1], lo[j >> 1]);
         }
-        // 32 keys = sixteen columns of this row (lane) in tensor memory, the tile's columns 32 half .. 32 half + 31
-        tmem_store16(tmem_base + kTmemPhi + lane_addr + half * 32 + c * 16, hi);
-        tmem_store16(tmem_base + kTmemPlo + lane_addr + half * 32 + c * 16, lo);
+        // 32 keys = sixteen columns of this row (lane), the tile's columns 32 half .. 32 half + 31 of P hi and of P lo
+        tmem_store16(tp + c * 16, hi);
+        tmem_store16(tp + 64 + c * 16, lo);
       }
       tmem_store_wait();
-      xch[i & 1][half][r] = make_float2(m_t, class_sum(u0, u1, u2, u3));
+      xch[i % 3][half][r] = make_float2(m_t, class_sum(u0, u1, u2, u3));
       fence_before_sync();
-      mbar_arrive(smem_u32(&p_full));
-      if (i + 1 < T) raw_max = read_scores(i + 1);     // under the value product of span i
-      mbar_wait(smem_u32(&o_full), i & 1, p.status, 6);
-      fence_after_sync();
-      softmax_barrier();    // both threads of every row have written xch[i & 1]; it is rewritten two spans later
-#pragma unroll
-      for (int t = 0; t < 2; ++t) {
-        float v[32];
-        tmem_load32(tmem_base + 2 * kKeys + t * kD + lane_addr + half * 32, v);
-        const float2 ml = xch[i & 1][t][r];
-        if (ml.x != -INFINITY) {
-          const FoldFactors f = fold_factors(m_c, ml.x);
-          l_c = fold_value(l_c, ml.y, f);
-#pragma unroll
-          for (int j = 0; j < 32; ++j) o_c[j] = fold_value(o_c[j], v[j], f);
-          m_c = f.m;
-        }
-      }
-      if (((kt0 + i) & 1) || i == T - 1) {      // the chunk of 256 keys is complete
-        if (m_c != -INFINITY) {
-          const FoldFactors f = fold_factors(m_r, m_c);
-          l_r = fold_value(l_r, l_c, f);
-#pragma unroll
-          for (int j = 0; j < 32; ++j) o_r[j * kRows] = fold_value(o_r[j * kRows], o_c[j], f);
-          m_r = f.m;
-        }
-        m_c = -INFINITY;
-        l_c = 0.0f;
-#pragma unroll
-        for (int j = 0; j < 32; ++j) o_c[j] = 0.0f;
-      }
-      fence_before_sync();
+      mbar_arrive(smem_u32(&p_full[i & 1]));
+      if (i + 1 < T) raw_max = read_scores(i + 1);     // the scores of the next span, computed during the weights of this one
+      if (i >= 1) fold_span(i - 1);                    // its value product ran during the weights of span i
     }
+    fold_span(T - 1);
     if (valid) {
       bf16* dst = p.out + (static_cast<int64_t>(row0 + pi) * p.Hq + g * G + hh) * kD + half * 32;
 #pragma unroll
