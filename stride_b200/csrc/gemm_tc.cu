@@ -792,6 +792,126 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_cons
   }
 }
 
+// The gate|up projection of many tokens with two weight tiles against one token tile: 128 gate rows and their 128 up
+// rows accumulate side by side (two accumulators of BN columns, all of tensor memory), so that a K step of 64 brings
+// 32 KB + BN * 128 bytes for twice the products of a single tile: what bounds these products is the ~26 KB per 512
+// cycles that one SM takes in by TMA. A thread of the epilogue finds a feature's gate and up value in the same lane
+// of the two accumulators: no exchange through shared memory. The accumulators are not double-buffered; the
+// epilogue (eight warps) is short beside the main loop. Same bits as the other SwiGLU epilogues of this file.
+__global__ void __launch_bounds__(kFoldThreads, 1)
+gemm_tc_wide_swiglu_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUtensorMap map_x, const GemmParams p) {
+  extern __shared__ __align__(1024) uint8_t smem_raw[];
+  __shared__ __align__(8) uint64_t full_bar[kMaxStages];
+  __shared__ __align__(8) uint64_t empty_bar[kMaxStages];
+  __shared__ __align__(8) uint64_t accum_full, accum_empty;
+  __shared__ uint32_t tmem_base_s;
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int BN = p.block_n;
+  const int stage_bytes = 2 * kStageA + BN * 128;
+  const uint32_t smem0 = (smem_u32(smem_raw) + 1023u) & ~1023u;
+  const int kblocks = (p.K + kTileK - 1) / kTileK;
+  const int total_tiles = p.tiles_m * p.tiles_n;
+
+  if (threadIdx.x == 0) {
+    prefetch_tensormap(&map_w);
+    prefetch_tensormap(&map_x);
+    for (int s = 0; s < p.stages; ++s) {
+      mbar_init(smem_u32(&full_bar[s]), 1);
+      mbar_init(smem_u32(&empty_bar[s]), 1);
+    }
+    mbar_init(smem_u32(&accum_full), 1);
+    mbar_init(smem_u32(&accum_empty), 8);   // one arrival per epilogue warp
+    mbar_init_fence();
+  }
+  if (warp == 1) tmem_alloc(smem_u32(&tmem_base_s), 512);
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = tmem_base_s;
+
+  sb::grid_launch_dependents();
+  if (warp == 0) {
+    if (lane == 0) {
+      // ---------------- producer
+      sb::grid_dependency_wait();
+      int it = 0;
+      for (int tile = blockIdx.x; tile < total_tiles; tile += gridDim.x) {
+        const int tile_m = tile % p.tiles_m, tile_n = tile / p.tiles_m;
+        for (int i = 0; i < kblocks; ++i, ++it) {
+          const int slot = it % p.stages;
+          if (it >= p.stages) mbar_wait(smem_u32(&empty_bar[slot]), ((it / p.stages) - 1) & 1, p.status, 1);
+          const uint32_t bar = smem_u32(&full_bar[slot]);
+          const uint32_t a = smem0 + slot * stage_bytes;
+          mbar_expect_tx(bar, stage_bytes);
+          tma_load_2d(a, &map_w, bar, i * kTileK, tile_m * kTileM);
+          tma_load_2d(a + kStageA, &map_w, bar, i * kTileK, p.half_rows + tile_m * kTileM);
+          tma_load_2d(a + 2 * kStageA, &map_x, bar, i * kTileK, tile_n * BN);
+        }
+      }
+    }
+  } else if (warp == 1) {
+    if (lane == 0) {
+      // ---------------- MMA issuer: gate rows into columns [0, BN), up rows into [256, 256 + BN)
+      const uint32_t idesc = instr_desc(BN);
+      int it = 0, ti = 0;
+      for (int tile = blockIdx.x; tile < total_tiles; tile += gridDim.x, ++ti) {
+        if (ti >= 1) mbar_wait(smem_u32(&accum_empty), (ti - 1) & 1, p.status, 4);
+        tc_fence_after();
+        for (int i = 0; i < kblocks; ++i, ++it) {
+          const int slot = it % p.stages;
+          mbar_wait(smem_u32(&full_bar[slot]), (it / p.stages) & 1, p.status, 2);
+          tc_fence_after();
+          const uint32_t a = smem0 + slot * stage_bytes;
+          const uint64_t dg = smem_desc_sw128(a), du = smem_desc_sw128(a + kStageA), db = smem_desc_sw128(a + 2 * kStageA);
+#pragma unroll
+          for (int k = 0; k < kTileK / 16; ++k) {
+            umma_bf16(tmem_base, dg + 2 * k, db + 2 * k, idesc, (i > 0 || k > 0) ? 1u : 0u);
+            umma_bf16(tmem_base + 256, du + 2 * k, db + 2 * k, idesc, (i > 0 || k > 0) ? 1u : 0u);
+          }
+          umma_commit(smem_u32(&empty_bar[slot]));
+        }
+        umma_commit(smem_u32(&accum_full));
+      }
+    }
+    __syncwarp();
+  } else {
+    // ---------------- epilogue: warp w reads TMEM lanes 32 * (w % 4) .. and the tile's columns [half * BN / 2, ..)
+    const int quarter = warp & 3, half = (warp - 2) >> 2;
+    sb::grid_dependency_wait();
+    bf16* out = reinterpret_cast<bf16*>(p.out);
+    int ti = 0;
+    for (int tile = blockIdx.x; tile < total_tiles; tile += gridDim.x, ++ti) {
+      const int tile_m = tile % p.tiles_m, tile_n = tile / p.tiles_m;
+      const bool ok = mbar_wait(smem_u32(&accum_full), ti & 1, p.status, 3);
+      tc_fence_after();
+      const int j = tile_m * kTileM + quarter * 32 + lane;     // output feature
+      const uint32_t lane_addr = static_cast<uint32_t>(quarter * 32) << 16;
+      for (int c0 = half * (BN / 2); c0 < (half + 1) * (BN / 2); c0 += 16) {
+        float g[16], u[16];
+        tmem_load16(tmem_base + lane_addr + c0, g);
+        tmem_load16(tmem_base + 256 + lane_addr + c0, u);
+        if (ok && j < p.half_rows) {
+#pragma unroll
+          for (int c = 0; c < 16; ++c) {
+            const int n = tile_n * BN + c0 + c;
+            if (n < p.N) out[static_cast<int64_t>(n) * p.ldo + j] = __float2bfloat16_rn(silu_fast(g[c]) * u[c]);
+          }
+        }
+      }
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(smem_u32(&accum_empty));
+    }
+    tc_fence_before();
+  }
+  __syncthreads();
+  if (warp == 1) {
+    tc_fence_after();
+    tmem_dealloc(tmem_base, 512);
+  }
+}
+
 // ------------------------------------------------------------------ host side
 // Tensor map of a row-major bfloat16 matrix [rows, cols] with leading dimension ld (elements) and a box of
 // box_rows x 64 elements in the 128-byte swizzle.
@@ -882,12 +1002,50 @@ SB_EXPORT int sb_gemm_tc(const void* x, int64_t ldx, const void* w, int64_t ldw,
   p.half_rows = half_rows;
   p.status = status;
 
+  // The SwiGLU product of many tokens runs on pairs of CTAs or with two weight tiles a CTA; both bring the same bytes
+  // from L2 (what bounds these products), the pairs in units half as large. Whichever needs fewer rounds of units of
+  // 128 features x 256 tokens a CTA takes it (two weight tiles on a tie: no traffic between the SMs of a pair).
+  bool wide = false;
+  if (n > 256 && epilogue == kSwiglu) {
+    const long long tn = (n + 255) / 256;
+    const long long pair_rounds = (((half_rows + 127) / 128) * tn + 73) / 74;
+    const long long wide_rounds = 2 * ((((half_rows + kTileM - 1) / kTileM) * tn + 147) / 148);
+    wide = wide_rounds <= pair_rounds;
+  }
+  if (wide) {
+    const long long tm = (half_rows + kTileM - 1) / kTileM;
+    p.block_n = 256;
+    const int wide_stage = 2 * kStageA + p.block_n * 128;
+    p.stages = min(kMaxStages, kSmemBudget / wide_stage);
+    p.kblocks_per_split = kblocks;
+    p.half_rows = half_rows;
+    p.status = status;
+    p.tiles_m = static_cast<int>(tm);
+    p.tiles_n = (n + p.block_n - 1) / p.block_n;
+    p.splits = 1;
+    CUtensorMap ww, wx;
+    if (!tensor_map(w, M, K, ldw, kTileM, &ww) || !tensor_map(x, n, K, ldx, p.block_n, &wx))
+      return sb::fail("sb_gemm_tc: cuTensorMapEncodeTiled failed (M %d N %d K %d)", M, n, K);
+    const long long tiles = static_cast<long long>(p.tiles_m) * p.tiles_n;
+    if (tiles > (1ll << 30)) return sb::fail("sb_gemm_tc: too many tiles");
+    static bool attr_set = false;
+    if (!attr_set) {
+      if (cudaFuncSetAttribute(gemm_tc_wide_swiglu_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBudget + 2048) != cudaSuccess)
+        return sb::fail("sb_gemm_tc: cannot raise the shared memory limit");
+      attr_set = true;
+    }
+    sb::launch_pdl(gemm_tc_wide_swiglu_kernel, dim3(static_cast<unsigned>(min(tiles, 148ll))), dim3(kFoldThreads),
+                   static_cast<size_t>(p.stages) * wide_stage + 1024, stream, ww, wx, p);
+    return sb::check_launch("sb_gemm_tc");
+  }
   if (n > 256 && epilogue != kAdd) {
     // Pairs of CTAs: tiles of 256 weight rows (or 128 gate + 128 up rows) by BN tokens, BN chosen by whole waves of 74 pairs.
     const long long tm = epilogue == kSwiglu ? (half_rows + 127) / 128 : (M + 255) / 256;
     long long best = -1;
     int bn_best = 256;
-    for (int bn = 256; bn >= 128; bn -= 32) {
+    // (narrower tiles bring more bytes from L2 for the same products, which is what bounds a large product: only a
+    // step of fewer than 1,024 tokens is cut into narrower tiles to fill its rounds)
+    for (int bn = 256; bn >= (n >= 1024 ? 256 : 128); bn -= 32) {
       const long long cost = ((tm * ((n + bn - 1) / bn) + 73) / 74) * bn;
       if (best < 0 || cost < best) {
         best = cost;
