@@ -3,7 +3,8 @@
 layers in one model; a schedule that runs one layer twice, the second time reading the first call's
 cache; and a windowed attention layer whose pages are given back as the window passes. The model is built
 by the registry, stepped through the engine in portions and single tokens beside other requests, and
-compared with a plain whole-sequence computation written out below."""
+compared with a plain whole-sequence computation written out below. A second toy architecture further down has a
+feed-forward with routing and another position encoding (a rotation of half of every head by other angles)."""
 from __future__ import annotations
 
 import pytest
@@ -165,3 +166,162 @@ def test_toy_architecture_is_registered_built_and_stepped():
         cm.release_slot(s)
     cm.check()
     assert cm.free_pages() == cm.total_pages()
+
+
+# ----------------------------------------------------------------------------------------------------------------
+# A second toy architecture: a feed-forward with routing (a router in 32-bit picks two of four small experts per
+# token) and another position encoding (angles that grow with the square root of the position, on the first half of
+# every head only), again registered from here and built by the framework's registry.
+from stride_b200.parts import FeedForward, PositionEncoding   # noqa: E402
+
+E, TOPK, IE, ROT = 4, 2, 24, 8
+
+
+@register_part("feed_forward", "toy_routed")
+class RoutedFeedForward(FeedForward):
+    """logits = R x in 32-bit; the TOPK largest (lower index on ties) get weights softmax(their logits); the token's
+    output is the weighted sum of those experts' gated MLPs. Torch operations: a test double, not a kernel."""
+
+    def __init__(self, spec, env):
+        super().__init__(spec, env)
+        self.hidden, self.experts, self.top_k = spec.params["hidden_size"], spec.params["experts"], spec.params["top_k"]
+
+    def tensor_plan(self):
+        t, p = self.spec.tensors, self.spec.params
+        return {t["router"]: TensorPlan((self.experts, self.hidden)),
+                t["gate"]: TensorPlan((self.experts, p["intermediate_size"], self.hidden)),
+                t["up"]: TensorPlan((self.experts, p["intermediate_size"], self.hidden)),
+                t["down"]: TensorPlan((self.experts, self.hidden, p["intermediate_size"]))}
+
+    def bind(self, tensors):
+        t = self.spec.tensors
+        self.router, self.gate, self.up, self.down = (tensors[t[k]].float() for k in ("router", "gate", "up", "down"))
+
+    def forward(self, ctx, x, stream):
+        xf = x.float()
+        logits = xf @ self.router.T                                    # [n, E] float32
+        order = torch.argsort(-logits, dim=1, stable=True)[:, :self.top_k]
+        weights = torch.softmax(torch.gather(logits, 1, order), dim=1)
+        out = torch.zeros_like(xf)
+        for e in range(self.experts):
+            for k in range(self.top_k):
+                rows = (order[:, k] == e).nonzero().flatten()
+                if rows.numel():
+                    a, b = xf[rows] @ self.gate[e].T, xf[rows] @ self.up[e].T
+                    out[rows] += weights[rows, k, None] * (((a / (1 + torch.exp(-a))) * b) @ self.down[e].T)
+        stream.add_(out)
+
+
+@register_part("position", "toy_sqrt")
+class SqrtRotation(PositionEncoding):
+    """Rotation of the first `rotary_dim` elements of a head by angle_i(pos) = sqrt(pos) * base^-i: the table that
+    the framework's rotation kernel reads ([positions, rotary_dim / 2, (cos, sin)] float32) and `rotary_dim`."""
+
+    def __init__(self, spec, env):
+        super().__init__(spec, env)
+        self.rotary_dim = spec.params["rotary_dim"]
+        self.cos_sin = _sqrt_table(env.max_positions, self.rotary_dim, spec.params["base"]).to(env.device)
+
+
+def _sqrt_table(positions, rotary_dim, base):
+    i = torch.arange(rotary_dim // 2, dtype=torch.float64)
+    angle = torch.arange(positions, dtype=torch.float64).sqrt()[:, None] * base ** -i[None, :]
+    return torch.stack([angle.cos(), angle.sin()], dim=-1).float()
+
+
+def _routed_spec(cfg: dict) -> ModelSpec:
+    pos = PartSpec("toy_sqrt", {"rotary_dim": ROT, "base": 3.0})
+    norm = lambda name: PartSpec("rmsnorm", {"size": H, "eps": 1e-6}, {"weight": name})
+    layers = []
+    for i in range(cfg["layers"]):
+        mixer = PartSpec("attention", {"hidden_size": H, "num_heads": HQ, "num_kv_heads": HKV, "head_dim": D, "window": 0, "position": pos},
+                         {"q": f"l{i}.q", "k": f"l{i}.k", "v": f"l{i}.v", "o": f"l{i}.o"})
+        ff = PartSpec("toy_routed", {"hidden_size": H, "intermediate_size": IE, "experts": E, "top_k": TOPK},
+                      {"router": f"l{i}.router", "gate": f"l{i}.egate", "up": f"l{i}.eup", "down": f"l{i}.edown"})
+        layers.append(LayerSpec(mixer, ff, norm(f"l{i}.n1"), norm(f"l{i}.n2")))
+    return ModelSpec(vocab_size=V, hidden_size=H, embedding=PartSpec("lookup", {"vocab_size": V, "hidden_size": H}, {"weight": "emb"}),
+                     layers=tuple(layers), schedule=tuple(ScheduleEntry(i, None) for i in range(cfg["layers"])), final_norm=norm("final"),
+                     head=PartSpec("linear", {"vocab_size": V, "hidden_size": H, "tied": True}, {"weight": "head", "tied_to": "emb"}),
+                     max_positions=128)
+
+
+register_architecture(Architecture("ToyRoutedForCausalLM", lambda d: d, _routed_spec))
+
+
+def _routed_weights(layers):
+    g = torch.Generator().manual_seed(1)
+    r = lambda *s: (torch.randn(*s, generator=g) * 0.25).to(torch.bfloat16)
+    gain = lambda: (1 + 0.2 * torch.randn(H, generator=g)).to(torch.bfloat16)
+    w = {"emb": r(V, H), "final": gain()}
+    for i in range(layers):
+        w.update({f"l{i}.n1": gain(), f"l{i}.n2": gain(), f"l{i}.q": r(HQ * D, H), f"l{i}.k": r(HKV * D, H), f"l{i}.v": r(HKV * D, H),
+                  f"l{i}.o": r(H, HQ * D), f"l{i}.router": r(E, H) * 4, f"l{i}.egate": r(E, IE, H), f"l{i}.eup": r(E, IE, H),
+                  f"l{i}.edown": r(E, H, IE)})
+    return w
+
+
+def _routed_plain(w, tokens, layers):
+    T = len(tokens)
+    pos = torch.arange(T)
+    table = _sqrt_table(T, ROT, 3.0)
+    cos, sin = table[..., 0], table[..., 1]
+
+    def rotate(x):      # [T, heads, D]: the first ROT elements, element j paired with j + ROT / 2
+        a, b, rest = x[..., :ROT // 2], x[..., ROT // 2:ROT], x[..., ROT:]
+        c, s = cos[:, None, :], sin[:, None, :]
+        return torch.cat([a * c - b * s, b * c + a * s, rest], dim=-1)
+
+    h = plain.embedding(torch.tensor(tokens), w["emb"])
+    for l in range(layers):
+        x = plain.rms_norm(h, w[f"l{l}.n1"], 1e-6)
+        q = rotate((x @ w[f"l{l}.q"].float().T).reshape(T, HQ, D))
+        k = rotate((x @ w[f"l{l}.k"].float().T).reshape(T, HKV, D))
+        v = (x @ w[f"l{l}.v"].float().T).reshape(T, HKV, D)
+        h = h + plain.attention(q, k, v, pos, 0) @ w[f"l{l}.o"].float().T
+        x = plain.rms_norm(h, w[f"l{l}.n2"], 1e-6)
+        logits = x @ w[f"l{l}.router"].float().T
+        y = torch.zeros_like(x)
+        for t in range(T):
+            chosen = sorted(range(E), key=lambda e: (-float(logits[t, e]), e))[:TOPK]
+            wts = torch.softmax(logits[t, chosen], dim=0)
+            for wt, e in zip(wts, chosen):
+                a, b = w[f"l{l}.egate"][e].float() @ x[t], w[f"l{l}.eup"][e].float() @ x[t]
+                y[t] += wt * (w[f"l{l}.edown"][e].float() @ ((a / (1 + torch.exp(-a))) * b))
+        h = h + y
+    return plain.rms_norm(h, w["final"], 1e-6) @ w["emb"].float().T
+
+
+def test_toy_routed_feed_forward_and_position_encoding():
+    layers = 2
+    config = {"architectures": ["ToyRoutedForCausalLM"], "layers": layers}
+    w = _routed_weights(layers)
+    eng = Engine(None, EngineOptions(dtype="float32", max_rows=64, max_full_rows=64, max_slots=4, kv_pages=40, page_size=8,
+                                     max_context=128), config=config, tensors=w)
+    assert eng.architecture.name == "ToyRoutedForCausalLM"
+    cm = eng.cache
+    reqs = [random_tokens(V, n, 3 + n) for n in (70, 41)]
+    want = [_routed_plain(w, r, layers) for r in reqs]
+    slots = [cm.acquire_slot() for _ in reqs]
+    fed = [0, 0]
+    sizes = [[9, 1, 1, 20, 2], [5, 1, 1, 13]]
+    step = 0
+    while any(f < len(r) for f, r in zip(fed, reqs)):
+        entries, spans = [], []
+        for i, r in enumerate(reqs):
+            if fed[i] >= len(r):
+                continue
+            n = min(sizes[i][step % len(sizes[i])], len(r) - fed[i])
+            assert cm.ensure(slots[i], fed[i] + n)
+            entries.append(StepEntry(slots[i], fed[i], r[fed[i]:fed[i] + n], list(range(n))))
+            spans.append((i, fed[i], fed[i] + n))
+            fed[i] += n
+        logits = eng.step(entries).cpu()
+        at = 0
+        for i, a, b in spans:
+            ref = want[i][a:b]
+            assert (logits[at:at + b - a] - ref).abs().max() <= 2e-4 * max(1.0, float(ref.pow(2).mean().sqrt())), (step, i, a, b)
+            at += b - a
+        step += 1
+    for s in slots:
+        cm.release_slot(s)
+    cm.check()
