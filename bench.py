@@ -233,10 +233,14 @@ def main() -> int:
         prefill = {"value": round(PREFILL_TOKENS / (pms * 1e-3), 1), "tokens": PREFILL_TOKENS, "ms": round(pms, 3),
                    "frac": round(fl / (pms * 1e-3) / (pk["bf16_tflops"] * 1e12), 4)}
     h2d = engine.last_h2d_bytes if hasattr(engine, "last_h2d_bytes") else engine._ints * 4
+    # stride's own published engine numbers for this workload (256-token prompts, 256 outputs; one RTX 4090, the only
+    # hardware it publishes for; prefill time included there): batch 1, 8, 64 (its README.md:40-42)
+    published = {1: 306.0, 8: 2276.0, 64: 10061.0}
+    vs_baseline = round(value / published[a.batch], 3) if a.batch in published and layers == full_layers else None
     line = {
-        "metric": "decode tok/s at batch 8 (Llama 3.2 1B shape, 256-token prompts)", "value": round(value, 1), "unit": "tokens/s",
+        "metric": f"decode tok/s at batch {a.batch} (Llama 3.2 1B shape, 256-token prompts)", "value": round(value, 1), "unit": "tokens/s",
         "n_gpus": 1, "steps": a.steps, "warmup": a.warmup, "ms_per_step": round(ms, 4), "higher_is_better": True,
-        "scaling": "weak", "vs_baseline": None, "dtype": "bf16", "data": "synthetic uniform token ids, random weights N(0, 0.02)",
+        "scaling": "weak", "vs_baseline": vs_baseline, "dtype": "bf16", "data": "synthetic uniform token ids, random weights N(0, 0.02)",
         "config": {"model": "llama-3.2-1b-shape", "layers": layers, "layers_of_config": full_layers, "hidden": cfg["hidden_size"],
                    "heads": cfg["num_attention_heads"], "kv_heads": cfg["num_key_value_heads"], "head_dim": cfg["head_dim"],
                    "intermediate": cfg["intermediate_size"], "vocab": vocab, "global_batch": a.batch, "seq_len": CONTEXT,
