@@ -139,3 +139,32 @@ def test_bits_do_not_depend_on_the_batch(dtype):
     assert torch.equal(alone, run(5, [], [(0, 90)]))
     assert torch.equal(alone, run(6, [], [(p, p + 1) for p in range(90)]))
     assert torch.equal(alone, run(7, big, [(0, 3), (3, 40), (40, 42), (42, 43), (43, 90)]))
+
+
+def test_serving_under_pressure_keeps_every_request_exact():
+    """The 1B layer sizes (four layers) through the public entry point: 40 requests of 200 to 300 tokens, 24 at a time, in
+    a pool that cannot hold them all, so that some are preempted and replayed; greedy and sampled requests mixed in one
+    run. Every request ends with exactly the tokens (and the bits of the chosen logits) it gets when it runs alone."""
+    from stride_b200 import LLM, Engine, EngineOptions
+    from stride_b200.weights.random_init import random_tensors
+    cfg = dict(SHAPES["1b"], num_hidden_layers=4)
+    tensors = random_tensors(cfg, seed=3, std=0.05, gain_std=0.1)
+    vocab = cfg["vocab_size"]
+    prompts = [random_tokens(vocab, 200 + (37 * i) % 101, 900 + i) for i in range(40)]
+    new = 48
+
+    def engine(pages):
+        return Engine(None, EngineOptions(dtype="bfloat16", max_rows=512, max_full_rows=64, max_slots=32, kv_pages=pages, page_size=64,
+                                          max_context=512), config=cfg, tensors=tensors)
+
+    busy = LLM(engine=engine(24 * 4), concurrency=24, max_rows=512, prefill_chunk=128, row_shuffle_seed=5)
+    got = busy.generate(prompts, new, temperature=0.7, seed=11)
+    stats = busy.last_stats
+    assert stats.preemptions > 0 and stats.replayed_rows > 0
+    busy.engine.cache.check()
+    assert busy.engine.cache.free_pages() == busy.engine.cache.total_pages()
+    alone = LLM(engine=engine(16), concurrency=1, max_rows=512, prefill_chunk=512)
+    for i in (0, 7, 13, 22, 31, 39):
+        (want,) = alone.generate([prompts[i]], new, temperature=0.7, seed=11 + i)
+        assert got[i].tokens == want.tokens, f"request {i}"
+        assert got[i].values == want.values, f"request {i}: the chosen logits differ in bits"
