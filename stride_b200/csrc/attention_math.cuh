@@ -5,8 +5,8 @@
 //          over K steps of 16 in ascending order), m = (max s_j) * c with c = scale * log2(e),
 //          p_j = ex2(fma(s_j, c, -m)), 0 for a key the row does not see. l = sum of p_j: key j belongs to class
 //          (j % 8) / 2, each class is added in ascending order of j, then l = (u0 + u1) + (u2 + u3).
-//          p = hi + lo, two bfloat16 parts cut (not rounded) from p; o = sum over steps of 16 keys, ascending, of
-//          hi . V then lo . V, accumulated on the tensor cores from zero.
+//          p = hi + lo, two bfloat16 parts (p rounded, then the remainder rounded); o = sum over steps of 16 keys,
+//          ascending, of hi . V then lo . V, accumulated on the tensor cores from zero.
 //   chunk  256 keys [256 c, 256 c + 256): the tiles a row sees are folded left to right into an empty state.
 //   row    the chunks a row sees are folded left to right into an empty state; out = o * (1 / l).
 //   fold   (m, l, o) <- (m_t, l_t, o_t): m' = max(m, m_t), a = ex2(m - m'), b = ex2(m_t - m'),
@@ -42,14 +42,14 @@ __device__ __forceinline__ float class_sum(float u0, float u1, float u2, float u
   return __fadd_rn(__fadd_rn(u0, u1), __fadd_rn(u2, u3));
 }
 
-// p0, p1 -> packed bfloat16 pairs (p0 in the low half): hi = p cut to its upper 16 bits, a bfloat16 exactly;
-// lo = the remainder p - hi (exact in float32) cut the same way. Bit moves only.
+// p0, p1 -> packed bfloat16 pairs (p0 in the low half): hi = p rounded to bfloat16, lo = the remainder p - hi (exact in
+// float32) rounded to bfloat16: |p - hi - lo| <= 2^-18 p, without bias.
 __device__ __forceinline__ void split_hi_lo(float p0, float p1, uint32_t& hi, uint32_t& lo) {
-  const uint32_t b0 = __float_as_uint(p0), b1 = __float_as_uint(p1);
-  hi = __byte_perm(b0, b1, 0x7632);
-  const uint32_t r0 = __float_as_uint(__fsub_rn(p0, __uint_as_float(b0 & 0xFFFF0000u)));
-  const uint32_t r1 = __float_as_uint(__fsub_rn(p1, __uint_as_float(b1 & 0xFFFF0000u)));
-  lo = __byte_perm(r0, r1, 0x7632);
+  const __nv_bfloat162 h = __floats2bfloat162_rn(p0, p1);
+  hi = *reinterpret_cast<const uint32_t*>(&h);
+  const float r0 = __fsub_rn(p0, __uint_as_float(hi << 16)), r1 = __fsub_rn(p1, __uint_as_float(hi & 0xFFFF0000u));
+  const __nv_bfloat162 l = __floats2bfloat162_rn(r0, r1);
+  lo = *reinterpret_cast<const uint32_t*>(&l);
 }
 
 struct FoldFactors {
