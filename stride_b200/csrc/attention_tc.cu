@@ -105,6 +105,10 @@ __device__ __forceinline__ void load_kv_tiles(bf16* dstK, bf16* dstV, const bf16
   }
   constexpr int LD = D + 8, CH = D / 8;
   const int c = tid % CH;
+  // A tile starts at a multiple of 64 keys, so with pages of 64, 128, ... keys it lies in one page, which is looked
+  // up once (the copies then do not wait for a table entry each). The entry is only used for keys that are copied.
+  const bool one_page = page_shift >= 6;
+  const bf16* page0 = one_page && key_lo <= key_hi ? kplane + static_cast<int64_t>(table[key0 >> page_shift]) * page_stride : kplane;
   for (int i = tid / CH; i < kKeys; i += threads / CH) {
     const int key = key0 + i;
     bf16* dk = dstK + i * LD + c * 8;
@@ -112,7 +116,7 @@ __device__ __forceinline__ void load_kv_tiles(bf16* dstK, bf16* dstV, const bf16
     if (key >= key_lo && key <= key_hi) {
       const int pi = page_shift >= 0 ? key >> page_shift : key / page_size;
       const int in_page = page_shift >= 0 ? key & (page_size - 1) : key % page_size;
-      const bf16* src = kplane + static_cast<int64_t>(table[pi]) * page_stride + in_page * D + c * 8;
+      const bf16* src = (one_page ? page0 : kplane + static_cast<int64_t>(table[pi]) * page_stride) + in_page * D + c * 8;
       cp_async16(smem_u32(dk), src);
       cp_async16(smem_u32(dv), src + v_offset);
     } else if (key < zero_lo || key > zero_hi) {

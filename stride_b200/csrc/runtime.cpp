@@ -1,0 +1,436 @@
+// The host side of the cache manager and of the scheduler's decisions, in C++ behind a plain C interface.
+//
+// Pool: the books of the paged cache. Pages of every group (layers with the same kind of cache), a last-in-first-out
+// free list per group, a slot per request, and the block tables, which are rows of memory that the caller owns
+// (pinned host memory that is uploaded row by row): the pool writes page ids straight into them. A page is free or
+// held by exactly one live slot. Counterpart in arhaamatiq/stride: KvCache (src/kv_cache.cpp:10-92), which has one
+// group, no windows and the same last-in-first-out order.
+//
+// Planner: which tokens the next step runs. Requests with exactly one unprocessed token first (one row each), then
+// portions of prompts in running order, under the token budget; then the page arithmetic of that plan, and what to
+// do when pages run short (wait for steps in flight, preempt the youngest, or fail when one request alone does not
+// fit). Counterpart: Scheduler::Admit / BuildBatch (src/scheduler.cpp:72-304).
+//
+// Nothing here touches a GPU; it is compiled by the host compiler alone.
+#include <algorithm>
+#include <cstdint>
+#include <cstdio>
+#include <cstring>
+#include <string>
+#include <vector>
+
+#define SB_API extern "C" __attribute__((visibility("default")))
+
+namespace {
+
+constexpr int32_t kNoPage = -1;
+thread_local std::string g_error;
+
+uint64_t splitmix64(uint64_t& s) {
+  uint64_t z = (s += 0x9E3779B97F4A7C15ull);
+  z = (z ^ (z >> 30)) * 0xBF58476D1CE4E5B9ull;
+  z = (z ^ (z >> 27)) * 0x94D049BB133111EBull;
+  return z ^ (z >> 31);
+}
+
+struct Group {
+  int window = 0;
+  int num_pages = 0;
+  int32_t* table = nullptr;            // [max_slots + 1, max_pages_per_seq], kNoPage where nothing is held
+  std::vector<int32_t> free;           // back = next page handed out
+  std::vector<int32_t> first, last;    // per slot: the indices [first, last) are the only ones that can hold a page
+  std::vector<int32_t> count;          // per slot: pages held
+};
+
+struct Pool {
+  int page_size = 0, max_slots = 0, max_pages = 0, max_context = 0;
+  std::vector<Group> groups;
+  std::vector<int32_t> free_slots;     // back = next slot handed out
+  int32_t* length = nullptr;           // [max_slots], caller's memory: tokens the slot's pages have been ensured for
+  uint8_t* live = nullptr;             // [max_slots], caller's memory
+  std::vector<uint8_t> dirty_mark;     // [groups * (max_slots + 1)]
+  std::vector<int32_t> dirty;          // group * (max_slots + 1) + slot of rows that changed
+  bool shuffle = false;
+  uint64_t rng = 0;
+
+  int32_t* row(Group& g, int slot) { return g.table + (size_t)slot * max_pages; }
+  void touch(int gi, int slot) {
+    const int key = gi * (max_slots + 1) + slot;
+    if (!dirty_mark[key]) {
+      dirty_mark[key] = 1;
+      dirty.push_back(key);
+    }
+  }
+  void reshuffle(Group& g) {
+    for (size_t i = g.free.size(); i > 1; --i) std::swap(g.free[i - 1], g.free[splitmix64(rng) % i]);
+  }
+  bool slot_ok(int slot) const { return slot >= 0 && slot < max_slots && live[slot]; }
+
+  // Pages the slot lacks for tokens [start, end): indices are appended to `out` if it is given.
+  int wanted(Group& g, int slot, int start, int end, std::vector<int32_t>* out) {
+    if (end <= start) return 0;
+    const int32_t* r = row(g, slot);
+    int n = 0;
+    for (int i = start / page_size, e = (end - 1) / page_size; i <= e; ++i)
+      if (r[i] == kNoPage) {
+        ++n;
+        if (out) out->push_back(i);
+      }
+    return n;
+  }
+};
+
+enum PlanResult { kPlanRun = 0, kPlanNothing = 1, kPlanDrain = 2, kPlanTooSmall = 3, kPlanPreempt = 4 };
+
+}  // namespace
+
+SB_API const char* sb_last_error() { return g_error.c_str(); }
+
+// `tables[g]` points at group g's block table [max_slots + 1, max_pages_per_seq] (already filled with -1), `length`
+// and `live` at arrays of max_slots entries (zeroed). A shuffle_seed other than 0 permutes the free lists at the
+// start and after every page given back, so that tests see pages in every order.
+SB_API void* sb_pool_create(int n_groups, const int32_t* windows, int32_t* const* tables, int page_size, int num_pages,
+                            int max_slots, int max_pages_per_seq, int max_context, int32_t* length, uint8_t* live,
+                            uint64_t shuffle_seed) {
+  if (page_size <= 0 || max_slots <= 0 || max_pages_per_seq <= 0 || n_groups < 0 || (n_groups && num_pages <= 0)) {
+    g_error = "sb_pool_create: sizes must be positive";
+    return nullptr;
+  }
+  Pool* p = new Pool;
+  p->page_size = page_size;
+  p->max_slots = max_slots;
+  p->max_pages = max_pages_per_seq;
+  p->max_context = max_context;
+  p->length = length;
+  p->live = live;
+  p->shuffle = shuffle_seed != 0;
+  p->rng = shuffle_seed;
+  p->groups.resize(n_groups);
+  p->dirty_mark.assign((size_t)n_groups * (max_slots + 1), 0);
+  for (int s = max_slots - 1; s >= 0; --s) p->free_slots.push_back(s);
+  for (int gi = 0; gi < n_groups; ++gi) {
+    Group& g = p->groups[gi];
+    g.window = windows[gi];
+    g.num_pages = num_pages;
+    g.table = tables[gi];
+    for (int pg = num_pages - 1; pg >= 0; --pg) g.free.push_back(pg);   // page 0 is handed out first
+    if (p->shuffle) p->reshuffle(g);
+    g.first.assign(max_slots, 0);
+    g.last.assign(max_slots, 0);
+    g.count.assign(max_slots, 0);
+  }
+  return p;
+}
+
+SB_API void sb_pool_destroy(void* pool) { delete static_cast<Pool*>(pool); }
+
+// A free slot id, or -1 when every slot is taken.
+SB_API int sb_pool_acquire_slot(void* pool) {
+  Pool* p = static_cast<Pool*>(pool);
+  if (p->free_slots.empty()) return -1;
+  const int slot = p->free_slots.back();
+  p->free_slots.pop_back();
+  p->live[slot] = 1;
+  p->length[slot] = 0;
+  return slot;
+}
+
+// Gives back the slot and every page it holds. 0, or -1 if the slot is not held.
+SB_API int sb_pool_release_slot(void* pool, int slot) {
+  Pool* p = static_cast<Pool*>(pool);
+  if (!p->slot_ok(slot)) return -1;
+  for (size_t gi = 0; gi < p->groups.size(); ++gi) {
+    Group& g = p->groups[gi];
+    if (!g.count[slot]) continue;
+    int32_t* r = p->row(g, slot);
+    for (int i = g.first[slot]; i < g.last[slot]; ++i)
+      if (r[i] != kNoPage) {
+        g.free.push_back(r[i]);
+        r[i] = kNoPage;
+      }
+    g.count[slot] = g.first[slot] = g.last[slot] = 0;
+    p->touch((int)gi, slot);
+    if (p->shuffle) p->reshuffle(g);
+  }
+  p->live[slot] = 0;
+  p->length[slot] = 0;
+  p->free_slots.push_back(slot);
+  return 0;
+}
+
+// Per group, how many new pages the slot needs to hold tokens up to position end - 1.
+SB_API int sb_pool_pages_needed(void* pool, int slot, int end, int32_t* out) {
+  Pool* p = static_cast<Pool*>(pool);
+  if (!p->slot_ok(slot)) return -1;
+  end = std::min(end, p->max_pages * p->page_size);
+  for (size_t gi = 0; gi < p->groups.size(); ++gi) out[gi] = p->wanted(p->groups[gi], slot, p->length[slot], end, nullptr);
+  return 0;
+}
+
+SB_API void sb_pool_free_pages(void* pool, int32_t* out) {
+  Pool* p = static_cast<Pool*>(pool);
+  for (size_t gi = 0; gi < p->groups.size(); ++gi) out[gi] = (int32_t)p->groups[gi].free.size();
+}
+
+SB_API int sb_pool_free_slots(void* pool, int32_t* out, int capacity) {
+  Pool* p = static_cast<Pool*>(pool);
+  const int n = (int)p->free_slots.size();
+  for (int i = 0; i < n && i < capacity; ++i) out[i] = p->free_slots[i];
+  return n;
+}
+
+// The free list of a group, the next page to be handed out last.
+SB_API int sb_pool_free_list(void* pool, int group, int32_t* out, int capacity) {
+  Pool* p = static_cast<Pool*>(pool);
+  const Group& g = p->groups[group];
+  const int n = (int)g.free.size();
+  for (int i = 0; i < n && i < capacity; ++i) out[i] = g.free[i];
+  return n;
+}
+
+// Allocates pages so that the slot can hold tokens up to position end - 1. 1 = done, 0 = a group has too few free
+// pages (nothing changed), -1 = the slot is not held, -2 = beyond the context capacity.
+SB_API int sb_pool_ensure(void* pool, int slot, int end) {
+  Pool* p = static_cast<Pool*>(pool);
+  if (!p->slot_ok(slot)) return -1;
+  if (end > p->max_context) return -2;
+  const int start = p->length[slot];
+  for (Group& g : p->groups)
+    if (p->wanted(g, slot, start, end, nullptr) > (int)g.free.size()) return 0;
+  std::vector<int32_t> idx;
+  for (size_t gi = 0; gi < p->groups.size(); ++gi) {
+    Group& g = p->groups[gi];
+    idx.clear();
+    p->wanted(g, slot, start, end, &idx);
+    if (idx.empty()) continue;
+    int32_t* r = p->row(g, slot);
+    for (int i : idx) {
+      r[i] = g.free.back();
+      g.free.pop_back();
+    }
+    if (!g.count[slot]) {
+      g.first[slot] = idx.front();
+      g.last[slot] = idx.back() + 1;
+    } else {
+      g.first[slot] = std::min(g.first[slot], idx.front());
+      g.last[slot] = std::max(g.last[slot], idx.back() + 1);
+    }
+    g.count[slot] += (int)idx.size();
+    p->touch((int)gi, slot);
+  }
+  p->length[slot] = std::max(p->length[slot], end);
+  return 1;
+}
+
+// Gives back the pages of windowed groups that no token of the slot at position `length` or later can see
+// (length < 0: all tokens the slot has pages for). Returns pages freed, -1 if the slot is not held.
+SB_API int sb_pool_trim(void* pool, int slot, int length) {
+  Pool* p = static_cast<Pool*>(pool);
+  if (!p->slot_ok(slot)) return -1;
+  const int n = length < 0 ? p->length[slot] : std::min(length, p->length[slot]);
+  int freed = 0;
+  for (size_t gi = 0; gi < p->groups.size(); ++gi) {
+    Group& g = p->groups[gi];
+    if (g.window <= 0 || !g.count[slot]) continue;
+    const int first_needed = n - g.window + 1;      // the oldest key the next token (position n) reads
+    if (first_needed < p->page_size) continue;
+    const int keep_from = first_needed / p->page_size;    // index i goes when (i + 1) * page_size <= first_needed
+    int32_t* r = p->row(g, slot);
+    int here = 0;
+    for (int i = g.first[slot], e = std::min(keep_from, g.last[slot]); i < e; ++i)
+      if (r[i] != kNoPage) {
+        g.free.push_back(r[i]);
+        r[i] = kNoPage;
+        ++here;
+      }
+    if (here) {
+      g.count[slot] -= here;
+      g.first[slot] = std::max(g.first[slot], std::min(keep_from, g.last[slot]));
+      p->touch((int)gi, slot);
+      freed += here;
+    }
+    if (freed && p->shuffle) p->reshuffle(g);
+  }
+  return freed;
+}
+
+// The (group, slot) rows that changed since the last call, sorted, as pairs in `out`; the marks are cleared.
+SB_API int sb_pool_take_dirty(void* pool, int32_t* out, int capacity_pairs) {
+  Pool* p = static_cast<Pool*>(pool);
+  std::sort(p->dirty.begin(), p->dirty.end());
+  const int n = (int)p->dirty.size();
+  if (n > capacity_pairs) return -n;
+  for (int i = 0; i < n; ++i) {
+    out[2 * i] = p->dirty[i] / (p->max_slots + 1);
+    out[2 * i + 1] = p->dirty[i] % (p->max_slots + 1);
+    p->dirty_mark[p->dirty[i]] = 0;
+  }
+  p->dirty.clear();
+  return n;
+}
+
+SB_API int sb_pool_held_count(void* pool, int group, int slot) {
+  Pool* p = static_cast<Pool*>(pool);
+  return p->groups[group].count[slot];
+}
+
+// Invariants: every page is free or held by exactly one live slot, never both or twice; no slot is lost.
+// 0, or -1 with the finding in sb_last_error().
+SB_API int sb_pool_check(void* pool) {
+  Pool* p = static_cast<Pool*>(pool);
+  char msg[160];
+  for (size_t gi = 0; gi < p->groups.size(); ++gi) {
+    Group& g = p->groups[gi];
+    std::vector<int32_t> owner(g.num_pages, -2);      // -2 unseen, -1 free, else the slot
+    size_t seen = 0;
+    for (int32_t pg : g.free) {
+      if (pg < 0 || pg >= g.num_pages) {
+        snprintf(msg, sizeof msg, "page id %d on the free list is out of range", pg);
+        g_error = msg;
+        return -1;
+      }
+      if (owner[pg] != -2) {
+        snprintf(msg, sizeof msg, "page %d is on the free list twice", pg);
+        g_error = msg;
+        return -1;
+      }
+      owner[pg] = -1;
+      ++seen;
+    }
+    for (int slot = 0; slot < p->max_slots; ++slot) {
+      const int32_t* r = p->row(g, slot);
+      int count = 0;
+      for (int i = 0; i < p->max_pages; ++i) {
+        const int32_t pg = r[i];
+        if (pg == kNoPage) continue;
+        ++count;
+        if (!p->live[slot]) {
+          snprintf(msg, sizeof msg, "slot %d holds pages but is not live", slot);
+          g_error = msg;
+          return -1;
+        }
+        if (pg < 0 || pg >= g.num_pages || i < g.first[slot] || i >= g.last[slot]) {
+          snprintf(msg, sizeof msg, "block table of slot %d disagrees at index %d", slot, i);
+          g_error = msg;
+          return -1;
+        }
+        if (owner[pg] != -2) {
+          if (owner[pg] == -1) snprintf(msg, sizeof msg, "page %d is held by slot %d and is also free", pg, slot);
+          else snprintf(msg, sizeof msg, "page %d is held by slot %d and is also held by slot %d", pg, slot, owner[pg]);
+          g_error = msg;
+          return -1;
+        }
+        owner[pg] = slot;
+        ++seen;
+      }
+      if (count != g.count[slot]) {
+        snprintf(msg, sizeof msg, "slot %d holds %d pages but %d are counted", slot, count, g.count[slot]);
+        g_error = msg;
+        return -1;
+      }
+    }
+    if (seen != (size_t)g.num_pages) {
+      snprintf(msg, sizeof msg, "%d pages are lost", (int)(g.num_pages - seen));
+      g_error = msg;
+      return -1;
+    }
+    if (p->row(g, p->max_slots)[0] != g.num_pages) {
+      g_error = "the padding slot lost its page";
+      return -1;
+    }
+  }
+  std::vector<uint8_t> is_free(p->max_slots, 0);
+  int live = 0;
+  for (int32_t s : p->free_slots) {
+    if (s < 0 || s >= p->max_slots || is_free[s] || p->live[s]) {
+      g_error = "slot bookkeeping is inconsistent";
+      return -1;
+    }
+    is_free[s] = 1;
+  }
+  for (int s = 0; s < p->max_slots; ++s) live += p->live[s] != 0;
+  if ((int)p->free_slots.size() + live != p->max_slots) {
+    g_error = "a slot is lost";
+    return -1;
+  }
+  return 0;
+}
+
+// Whether a waiting request of `tokens` tokens may start beside n_running others: free pages of every group must
+// cover its tokens plus one page of growth per running request plus one, unless nothing is running.
+SB_API int sb_sched_may_admit(void* pool, int n_running, int tokens) {
+  Pool* p = static_cast<Pool*>(pool);
+  if (p->free_slots.empty()) return 0;
+  if (n_running == 0) return 1;
+  const int need = (tokens + p->page_size - 1) / p->page_size + n_running + 1;
+  for (const Group& g : p->groups)
+    if ((int)g.free.size() < need) return 0;
+  return 1;
+}
+
+// Plans the next step over the running requests (arrays in running order: slot, next unprocessed position, tokens
+// known, closing = no further step is to be launched, inflight = steps launched whose tokens the host has not read,
+// arrival number). Result kPlanRun: `out_index[i]`, `out_count[i]` for i < *out_n are the requests and how many of
+// their tokens run, pages ensured. kPlanNothing: no request has a token to run. kPlanDrain: pages are short while
+// steps are in flight. kPlanTooSmall: pages are short for a single request. kPlanPreempt: pages are short;
+// out_index[0] is the youngest request, which the caller takes out before it plans again. -1: accounting failed.
+SB_API int sb_sched_plan(void* pool, int n, const int32_t* slot, const int32_t* next_pos, const int32_t* total,
+                         const uint8_t* closing, const uint8_t* inflight, const int64_t* arrival, int max_rows,
+                         int prefill_chunk, int32_t* out_index, int32_t* out_count, int32_t* out_n) {
+  Pool* p = static_cast<Pool*>(pool);
+  int budget = max_rows, m = 0;
+  for (int i = 0; i < n && budget > 0; ++i)
+    if (total[i] - next_pos[i] == 1 && !closing[i]) {
+      out_index[m] = i;
+      out_count[m++] = 1;
+      --budget;
+    }
+  for (int i = 0; i < n && budget > 0; ++i) {
+    const int remaining = total[i] - next_pos[i];
+    if (remaining > 1 && !closing[i]) {
+      const int chunk = std::min(remaining, std::min(prefill_chunk, budget));
+      out_index[m] = i;
+      out_count[m++] = chunk;
+      budget -= chunk;
+    }
+  }
+  *out_n = m;
+  if (m == 0) return kPlanNothing;
+  for (int j = 0; j < m; ++j)
+    if (!p->slot_ok(slot[out_index[j]])) {
+      g_error = "sb_sched_plan: a running request has no slot";
+      return -1;
+    }
+  bool is_short = false;
+  for (Group& g : p->groups) {
+    long need = 0;
+    for (int j = 0; j < m; ++j) {
+      const int i = out_index[j], s = slot[i];
+      need += p->wanted(g, s, p->length[s], std::min(next_pos[i] + out_count[j], p->max_pages * p->page_size), nullptr);
+    }
+    if (need > (long)g.free.size()) is_short = true;
+  }
+  if (is_short) {
+    for (int i = 0; i < n; ++i)
+      if (inflight[i]) return kPlanDrain;     // pages of a request with a step in flight cannot be taken away yet
+    if (n <= 1) return kPlanTooSmall;
+    int victim = 0;
+    for (int i = 1; i < n; ++i)
+      if (arrival[i] > arrival[victim]) victim = i;
+    out_index[0] = victim;
+    return kPlanPreempt;
+  }
+  for (int j = 0; j < m; ++j) {
+    const int i = out_index[j];
+    const int r = sb_pool_ensure(pool, slot[i], next_pos[i] + out_count[j]);
+    if (r == -2) {
+      g_error = "sb_sched_plan: a request grows beyond the context capacity";
+      return -1;
+    }
+    if (r != 1) {
+      g_error = "page accounting failed: ensure() refused a planned allocation";
+      return -1;
+    }
+  }
+  return kPlanRun;
+}

@@ -189,7 +189,7 @@ class Engine:
             if e.slot in seen:
                 raise EngineError(f"slot {e.slot} appears twice in one step")
             seen.add(e.slot)
-            if e.slot not in self.cache.live_slots:
+            if not self.cache.is_live(e.slot):
                 raise EngineError(f"slot {e.slot} is not held by a request")
             if e.first_pos < 0 or e.first_pos + L > self.cache.length[e.slot]:
                 raise EngineError(f"slot {e.slot}: tokens {e.first_pos}..{e.first_pos + L - 1} have no pages "
@@ -253,7 +253,7 @@ class Engine:
         meta = buf[4 * R:8 * R].reshape(4, R)
         seen = set()
         for i, e in enumerate(entries):
-            if e.slot in seen or e.slot not in self.cache.live_slots or e.slot == self._pad_slot:
+            if e.slot in seen or not self.cache.is_live(e.slot) or e.slot == self._pad_slot:
                 raise EngineError(f"slot {e.slot} appears twice in one step or is not held by a request")
             seen.add(e.slot)
             if e.first_pos < 0 or e.first_pos + 1 > self.cache.length[e.slot]:

@@ -10,6 +10,11 @@ alike) and plan again; run the batch through `Engine.step`; choose a token for e
 request whose last known token was in the batch; finish on a stop token ("stop") or on
 max_new_tokens ("length") and give slot and pages back.
 
+The decisions (the admission rule, the plan under the budget, the page arithmetic and the
+choice of what to do when pages are short) are taken by the native planner in
+`csrc/runtime.cpp`, on the books of the native page pool; this module keeps the requests,
+their tokens and callbacks, and drives the engine and the sampler.
+
 This restates arhaamatiq/stride's Scheduler (src/scheduler.cpp:72-304) including its
 admission rule (free pages >= pages of the prompt + one page of growth per running request
 + one, unless nothing is running) and its failure when a single running request does not
@@ -18,6 +23,7 @@ empty, finish at intake with "context_length" / "empty_prompt" (src/scheduler.cp
 """
 from __future__ import annotations
 
+import ctypes
 import threading
 from collections import deque
 from dataclasses import dataclass, field
@@ -104,6 +110,22 @@ class _Seq:
 
 
 _DRAIN = object()      # plan(): the steps in flight have to be read back before a decision can be taken
+_PLAN_RUN, _PLAN_NOTHING, _PLAN_DRAIN, _PLAN_TOO_SMALL, _PLAN_PREEMPT = range(5)    # results of sb_sched_plan
+_I32P, _U8P, _I64P = ctypes.POINTER(ctypes.c_int32), ctypes.POINTER(ctypes.c_uint8), ctypes.POINTER(ctypes.c_int64)
+
+
+class _PlanBuffers:
+    """Arrays the native planner reads (one row per running request) and writes (the plan)."""
+    FIELDS = (("slot", np.int32, _I32P), ("next_pos", np.int32, _I32P), ("total", np.int32, _I32P), ("closing", np.uint8, _U8P),
+              ("inflight", np.uint8, _U8P), ("arrival", np.int64, _I64P), ("out_index", np.int32, _I32P), ("out_count", np.int32, _I32P))
+
+    def __init__(self, capacity: int):
+        self.capacity = capacity
+        self.out_n = ctypes.c_int32(0)
+        for name, dtype, ptr in self.FIELDS:
+            arr = np.zeros(capacity, dtype=dtype)
+            setattr(self, name, arr)
+            setattr(self, name + "_p", arr.ctypes.data_as(ptr))
 
 
 class Scheduler:
@@ -120,6 +142,14 @@ class Scheduler:
         self._arrival = 0
         self._rng_state = self.opts.row_shuffle_seed
         self._sampler = sampler or Sampler(engine.device, engine.env.max_logit_rows)
+        lib = self._lib = engine.cache._lib
+        if not getattr(lib, "_sb_sched_typed", False):
+            lib.sb_sched_may_admit.restype, lib.sb_sched_may_admit.argtypes = ctypes.c_int, [ctypes.c_void_p, ctypes.c_int, ctypes.c_int]
+            lib.sb_sched_plan.restype = ctypes.c_int
+            lib.sb_sched_plan.argtypes = [ctypes.c_void_p, ctypes.c_int, _I32P, _I32P, _I32P, _U8P, _U8P, _I64P, ctypes.c_int, ctypes.c_int,
+                                          _I32P, _I32P, ctypes.POINTER(ctypes.c_int32)]
+            lib._sb_sched_typed = True
+        self._buf = _PlanBuffers(max(self.opts.max_seqs, 1))
 
     # ------------------------------------------------------------------ intake
     def submit(self, request: GenRequest) -> None:
@@ -136,10 +166,6 @@ class Scheduler:
         if seq.slot >= 0:
             self.engine.cache.release_slot(seq.slot)
             seq.slot = -1
-
-    def _page_need(self, tokens: int) -> list:
-        ps = self.engine.cache.page_size
-        return [(tokens + ps - 1) // ps for _ in self.engine.cache.groups]
 
     def _admit(self) -> None:
         cache = self.engine.cache
@@ -161,10 +187,8 @@ class Scheduler:
             if nxt.req.cancelled is not None and nxt.req.cancelled.is_set():
                 self._waiting.popleft()
                 continue
-            # Keep room for one page of growth per running request before admitting another.
-            reserve = len(self._running) + 1
-            need = self._page_need(len(nxt.tokens))
-            if self._running and any(f < n + reserve for f, n in zip(cache.free_pages(), need)):
+            # Room for its tokens and one page of growth per running request, and a free slot.
+            if not self._lib.sb_sched_may_admit(cache._pool, len(self._running), len(nxt.tokens)):
                 break
             slot = cache.acquire_slot()
             if slot < 0:
@@ -174,8 +198,7 @@ class Scheduler:
             self._running.append(self._waiting.popleft())
         self.stats.peak_seqs = max(self.stats.peak_seqs, len(self._running))
 
-    def _preempt_youngest(self) -> None:
-        victim = max(self._running, key=lambda s: s.arrival)
+    def _preempt(self, victim: _Seq) -> None:
         self.engine.cache.release_slot(victim.slot)
         victim.slot = -1
         self.stats.preemptions += 1
@@ -186,36 +209,31 @@ class Scheduler:
     # ------------------------------------------------------------------ planning
     def plan(self):
         """[(sequence, tokens to run)] for the next step, pages ensured; None if nothing is to run."""
-        cache = self.engine.cache
+        cache, buf = self.engine.cache, self._buf
         while True:
-            plan = []
-            budget = self.opts.max_rows
-            for s in self._running:
-                if len(s.tokens) - s.next_pos == 1 and budget > 0 and not s.closing:
-                    plan.append((s, 1))
-                    budget -= 1
-            for s in self._running:
-                remaining = len(s.tokens) - s.next_pos
-                if remaining > 1 and budget > 0 and not s.closing:
-                    chunk = min(remaining, self.opts.prefill_chunk, budget)
-                    plan.append((s, chunk))
-                    budget -= chunk
-            if not plan:
+            n = len(self._running)
+            if n == 0:
                 return None
-            need = [0] * len(cache.groups)
-            for s, count in plan:
-                for g, k in enumerate(cache.pages_needed(s.slot, s.next_pos + count)):
-                    need[g] += k
-            if any(n > f for n, f in zip(need, cache.free_pages())):
-                if any(s.inflight for s in self._running):
-                    return _DRAIN       # pages of a request with a step in flight cannot be taken away yet
-                if len(self._running) <= 1:
-                    raise EngineError("the cache pool is too small for one sequence")
-                self._preempt_youngest()
+            run = self._running
+            buf.slot[:n], buf.next_pos[:n], buf.total[:n] = [s.slot for s in run], [s.next_pos for s in run], [len(s.tokens) for s in run]
+            buf.closing[:n], buf.inflight[:n] = [s.closing for s in run], [s.inflight > 0 for s in run]
+            buf.arrival[:n] = [s.arrival for s in run]
+            result = self._lib.sb_sched_plan(cache._pool, n, buf.slot_p, buf.next_pos_p, buf.total_p, buf.closing_p, buf.inflight_p,
+                                             buf.arrival_p, self.opts.max_rows, self.opts.prefill_chunk, buf.out_index_p,
+                                             buf.out_count_p, ctypes.byref(buf.out_n))
+            if result == _PLAN_NOTHING:
+                return None
+            if result == _PLAN_DRAIN:
+                return _DRAIN           # pages of a request with a step in flight cannot be taken away yet
+            if result == _PLAN_TOO_SMALL:
+                raise EngineError("the cache pool is too small for one sequence")
+            if result == _PLAN_PREEMPT:
+                self._preempt(self._running[int(buf.out_index[0])])     # the youngest; then plan again
                 continue
-            for s, count in plan:
-                if not cache.ensure(s.slot, s.next_pos + count):
-                    raise EngineError("page accounting failed: ensure() refused a planned allocation")
+            if result != _PLAN_RUN:
+                raise EngineError(self._lib.sb_last_error().decode())
+            m = buf.out_n.value
+            plan = [(self._running[i], c) for i, c in zip(buf.out_index[:m].tolist(), buf.out_count[:m].tolist())]
             if self.opts.row_shuffle_seed:
                 for i in range(len(plan) - 1, 0, -1):
                     self._rng_state = splitmix64(self._rng_state)

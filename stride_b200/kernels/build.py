@@ -40,7 +40,9 @@ SOURCES = {
     "gemm_tc": "gemm_tc.cu",
     "attention_tc": "attention_tc.cu",
     "attention_tc5": "attention_tc5.cu",
+    "runtime": "runtime.cpp",        # host code only: the cache manager's books and the scheduler's decisions
 }
+HOST_FLAGS = ["-O2", "-std=c++17", "-g1", "-shared", "-fPIC", "-fvisibility=hidden"]
 
 _loaded: dict[str, ctypes.CDLL] = {}
 _lock = threading.Lock()
@@ -55,6 +57,14 @@ def _nvcc() -> str:
         if cand and Path(cand).exists():
             return cand
     raise BuildError("nvcc not found: the CUDA kernels of stride_b200 cannot be built (set NVCC or put nvcc on PATH)")
+
+
+def _host_compiler() -> str:
+    for cand in (os.environ.get("CXX"), "g++", "c++"):
+        found = cand and shutil.which(cand)
+        if found:
+            return found
+    raise BuildError("no C++ compiler found: the host runtime of stride_b200 cannot be built (set CXX)")
 
 
 @functools.lru_cache(maxsize=1)
@@ -77,7 +87,7 @@ def _digest(src: Path) -> str:
     h.update(src.read_bytes())
     for header in sorted(list(CSRC.glob("*.cuh")) + list(CSRC.glob("*.h"))):
         h.update(header.read_bytes())
-    h.update(" ".join(ARCH_FLAGS + NVCC_FLAGS).encode())
+    h.update(" ".join(HOST_FLAGS if src.suffix == ".cpp" else ARCH_FLAGS + NVCC_FLAGS).encode())
     return h.hexdigest()[:12]
 
 
@@ -89,8 +99,12 @@ def library_path(name: str) -> Path:
 def _compile(name: str, out: Path) -> None:
     src = CSRC / SOURCES[name]
     tmp = out.with_suffix(f".tmp{os.getpid()}.so")
-    cmd = [_nvcc(), *ARCH_FLAGS, *NVCC_FLAGS, f"-I{CSRC}", "-o", str(tmp), str(src)]
-    print(f"[stride_b200] compiling {src.name} for sm_100a ...", file=sys.stderr, flush=True)
+    if src.suffix == ".cpp":
+        cmd = [_host_compiler(), *HOST_FLAGS, f"-I{CSRC}", "-o", str(tmp), str(src)]
+        print(f"[stride_b200] compiling {src.name} for the host ...", file=sys.stderr, flush=True)
+    else:
+        cmd = [_nvcc(), *ARCH_FLAGS, *NVCC_FLAGS, f"-I{CSRC}", "-o", str(tmp), str(src)]
+        print(f"[stride_b200] compiling {src.name} for sm_100a ...", file=sys.stderr, flush=True)
     t0 = time.time()
     env = dict(os.environ)
     env.setdefault("TMPDIR", tempfile.gettempdir())
@@ -103,7 +117,7 @@ def _compile(name: str, out: Path) -> None:
             print(f"[stride_b200]   still compiling {src.name} ({time.time() - t0:.0f} s)", file=sys.stderr, flush=True)
     if proc.returncode != 0:
         tmp.unlink(missing_ok=True)
-        raise BuildError(f"nvcc failed on {src}:\n{out_text.decode(errors='replace')}")
+        raise BuildError(f"{Path(cmd[0]).name} failed on {src}:\n{out_text.decode(errors='replace')}")
     os.replace(tmp, out)
     for stale in out.parent.glob(f"{name}-*.so"):
         if stale != out and ".tmp" not in stale.name:

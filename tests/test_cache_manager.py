@@ -105,3 +105,23 @@ def test_random_orders_keep_the_books(seed):
         cm.release_slot(s)
     cm.check()
     assert cm.free_pages() == cm.total_pages() and len(cm.free_slots) == 5
+
+
+def test_check_finds_damaged_books():
+    cm = CacheManager(_needs(), device="cpu", max_slots=3, max_context=64, page_size=4, num_pages=8)
+    a, b = cm.acquire_slot(), cm.acquire_slot()
+    assert cm.ensure(a, 8) and cm.ensure(b, 8)
+    cm.check()
+    table = cm.groups[0].table_host
+    mine = int(table[b, 0])
+    table[b, 0] = table[a, 0]
+    with pytest.raises(CacheError, match="is also held by slot"):
+        cm.check()
+    table[b, 0] = NO_PAGE
+    with pytest.raises(CacheError, match="but 2 are counted"):
+        cm.check()
+    table[b, 0] = mine
+    cm.check()
+    table[2, 0] = 7                                    # a slot nobody holds
+    with pytest.raises(CacheError, match="not live"):
+        cm.check()
