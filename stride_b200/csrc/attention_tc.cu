@@ -29,6 +29,7 @@
 #include "common.cuh"
 #include "noalloc.h"
 
+
 SB_DEFINE_LAST_ERROR()
 
 namespace {
@@ -92,7 +93,8 @@ __device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) {
 // Copies keys and values [key0, key0 + 64) of one kv head into dstK and dstV ([64][D + 8] each); keys outside
 // [key_lo, key_hi] are zero-filled. `threads` threads of the caller take part (tid in 0..threads-1): D / 8
 // threads share a key (one 16-byte piece each), so the page is looked up once for a key's key and value rows.
-template <int D>
+// WHICH: 1 = keys only, 2 = values only, 3 = both.
+template <int D, int WHICH = 3>
 __device__ __forceinline__ void load_kv_tiles(bf16* dstK, bf16* dstV, const bf16* kplane, int64_t v_offset,
                                               const int32_t* table, int page_size, int page_shift, int64_t page_stride,
                                               int key0, int key_lo, int key_hi, int tid, int threads,
@@ -117,11 +119,11 @@ __device__ __forceinline__ void load_kv_tiles(bf16* dstK, bf16* dstV, const bf16
       const int pi = page_shift >= 0 ? key >> page_shift : key / page_size;
       const int in_page = page_shift >= 0 ? key & (page_size - 1) : key % page_size;
       const bf16* src = (one_page ? page0 : kplane + static_cast<int64_t>(table[pi]) * page_stride) + in_page * D + c * 8;
-      cp_async16(smem_u32(dk), src);
-      cp_async16(smem_u32(dv), src + v_offset);
+      if (WHICH & 1) cp_async16(smem_u32(dk), src);
+      if (WHICH & 2) cp_async16(smem_u32(dv), src + v_offset);
     } else if (key < zero_lo || key > zero_hi) {
-      *reinterpret_cast<uint4*>(dk) = make_uint4(0, 0, 0, 0);
-      *reinterpret_cast<uint4*>(dv) = make_uint4(0, 0, 0, 0);
+      if (WHICH & 1) *reinterpret_cast<uint4*>(dk) = make_uint4(0, 0, 0, 0);
+      if (WHICH & 2) *reinterpret_cast<uint4*>(dv) = make_uint4(0, 0, 0, 0);
     }
   }
 }
@@ -151,7 +153,8 @@ __device__ __forceinline__ void qk_tile(float (*s)[4], const bf16* sQ, const bf1
 
 // O[16 x D] = P[16 x 64] V[64 x D] from zero; P given as float weights in the layout of qk_tile's accumulators.
 // Each weight enters as two bfloat16 parts (split_hi_lo), hi . V then lo . V for every step of 16 keys.
-template <int D>
+// kUpper = false: rows 8..15 of the tile are not in use; their weights are taken as zero without being looked at.
+template <int D, bool kUpper = true>
 __device__ __forceinline__ void pv_tile(float (*o)[4], const float (*s)[4], const bf16* sV, int lane) {
   constexpr int LD = D + 8;
   const int mi = lane >> 3, rr = lane & 7;
@@ -163,59 +166,80 @@ __device__ __forceinline__ void pv_tile(float (*o)[4], const float (*s)[4], cons
   for (int kk = 0; kk < 4; ++kk) {
     uint32_t hi[4], lo[4];
 #pragma unroll
-    for (int x = 0; x < 4; ++x) split_hi_lo(s[2 * kk + (x >> 1)][(x & 1) * 2], s[2 * kk + (x >> 1)][(x & 1) * 2 + 1], hi[x], lo[x]);
+    for (int x = 0; x < 4; ++x) {
+      if (!kUpper && (x & 1)) hi[x] = lo[x] = 0u;
+      else split_hi_lo(s[2 * kk + (x >> 1)][(x & 1) * 2], s[2 * kk + (x >> 1)][(x & 1) * 2 + 1], hi[x], lo[x]);
+    }
 #pragma unroll
     for (int dt = 0; dt < D / 8; dt += 2) {
       uint32_t b[4];
       ldsm_x4_trans(b, smem_u32(sV + (kk * 16 + (mi & 1) * 8 + rr) * LD + (dt + (mi >> 1)) * 8));
       mma_16816(o[dt], hi, b[0], b[1]);
-      mma_16816(o[dt], lo, b[0], b[1]);
       mma_16816(o[dt + 1], hi, b[2], b[3]);
+      mma_16816(o[dt], lo, b[0], b[1]);
       mma_16816(o[dt + 1], lo, b[2], b[3]);
     }
   }
 }
 
-// One tile for one warp: s holds the raw scores of keys key0 .. key0 + 63 for the thread's two rows (gid, gid + 8)
-// and leaves their weights; m_t, l_t, o_t are the tile's maximum, sum and weighted values per row.
-template <int D>
-__device__ __forceinline__ void tile_partial(float (*s)[4], float (*o_t)[4], float* m_t, float* l_t, int key0, const int* row_pos,
-                                             const int* row_lo, float c, const bf16* sV, int lane) {
+// The weights of one tile for one warp: s holds the raw scores of keys key0 .. key0 + 63 for the thread's two rows
+// (gid, gid + 8) and leaves their weights; m_t, l_t are the tile's maximum and sum per row. `full` (the same for the
+// whole warp): every row in use sees every key of the tile, so nothing is masked. kUpper = false: rows 8..15 are not
+// in use and are left out (maximum -inf, sum 0; their entries of s are not touched).
+template <bool kUpper>
+__device__ __forceinline__ void tile_weights(float (*s)[4], float* m_t, float* l_t, int key0, const int* row_pos, const int* row_lo,
+                                             float c, int lane, bool full) {
+  constexpr int X = kUpper ? 4 : 2, H = kUpper ? 2 : 1;
   const int tq = lane & 3;
+  if (!full) {
+#pragma unroll
+    for (int nt = 0; nt < 8; ++nt)
+#pragma unroll
+      for (int x = 0; x < X; ++x) {
+        const int h = x >> 1;
+        const int key = key0 + nt * 8 + tq * 2 + (x & 1);
+        if (!(key <= row_pos[h] && key >= row_lo[h])) s[nt][x] = -INFINITY;
+      }
+  }
   float mx[2] = {-INFINITY, -INFINITY};
 #pragma unroll
   for (int nt = 0; nt < 8; ++nt)
 #pragma unroll
-    for (int x = 0; x < 4; ++x) {
-      const int h = x >> 1;
-      const int key = key0 + nt * 8 + tq * 2 + (x & 1);
-      if (!(key <= row_pos[h] && key >= row_lo[h])) s[nt][x] = -INFINITY;
-      mx[h] = fmaxf(mx[h], s[nt][x]);
-    }
+    for (int x = 0; x < X; ++x) mx[x >> 1] = fmaxf(mx[x >> 1], s[nt][x]);
   float ref[2], u[2] = {0.0f, 0.0f};
+  m_t[1] = -INFINITY;
+  l_t[1] = 0.0f;
 #pragma unroll
-  for (int h = 0; h < 2; ++h) {
+  for (int h = 0; h < H; ++h) {
     mx[h] = fmaxf(mx[h], __shfl_xor_sync(0xffffffffu, mx[h], 1));
     mx[h] = fmaxf(mx[h], __shfl_xor_sync(0xffffffffu, mx[h], 2));
     m_t[h] = tile_max(mx[h], c);
     ref[h] = tile_ref(m_t[h]);
   }
-  // this thread holds class tq of its rows' keys, in ascending order
+  // this thread holds class tq of its rows' keys, in ascending order; a score of -inf (a masked key) weighs 0, which
+  // is also what ex2 makes of it
 #pragma unroll
   for (int nt = 0; nt < 8; ++nt)
 #pragma unroll
-    for (int x = 0; x < 4; ++x) {
+    for (int x = 0; x < X; ++x) {
       const int h = x >> 1;
-      const float p = s[nt][x] == -INFINITY ? 0.0f : weight(s[nt][x], c, ref[h]);
+      const float p = weight(s[nt][x], c, ref[h]);
       s[nt][x] = p;
       u[h] = __fadd_rn(u[h], p);
     }
 #pragma unroll
-  for (int h = 0; h < 2; ++h) {
+  for (int h = 0; h < H; ++h) {
     u[h] = __fadd_rn(u[h], __shfl_xor_sync(0xffffffffu, u[h], 1));
     l_t[h] = __fadd_rn(u[h], __shfl_xor_sync(0xffffffffu, u[h], 2));
   }
-  pv_tile<D>(o_t, s, sV, lane);
+}
+
+// One tile for one warp: weights from the raw scores in s, then o_t = the tile's weighted values per row.
+template <int D, bool kUpper = true>
+__device__ __forceinline__ void tile_partial(float (*s)[4], float (*o_t)[4], float* m_t, float* l_t, int key0, const int* row_pos,
+                                             const int* row_lo, float c, const bf16* sV, int lane, bool full = false) {
+  tile_weights<kUpper>(s, m_t, l_t, key0, row_pos, row_lo, c, lane, full);
+  pv_tile<D, kUpper>(o_t, s, sV, lane);
 }
 
 // Folds a part into a state, row by row of the thread's two rows; rows whose part is empty are left alone.
@@ -283,6 +307,10 @@ __global__ void __launch_bounds__(128) attn_chunk_kernel(const AttnTcParams p) {
     row_pos[h] = pi < npos ? pos0 + pi : -1;
     row_lo[h] = p.window > 0 ? row_pos[h] - p.window + 1 : 0;
   }
+  // the positions of this warp's rows that are in use (none: -1)
+  const int warp_pi = warp * 16 / G;
+  const int warp_pos_lo = warp_pi < npos ? pos0 + warp_pi : -1;
+  const int warp_pos_hi = pos0 + min(npos - 1, (warp * 16 + 15) / G);
   // the chunk in progress (registers) and the chunks before it (maximum and sum in registers, values in sT,
   // every element of which belongs to one thread)
   float m_c[2] = {-INFINITY, -INFINITY}, l_c[2] = {0.0f, 0.0f}, m_r[2] = {-INFINITY, -INFINITY}, l_r[2] = {0.0f, 0.0f};
@@ -307,7 +335,10 @@ __global__ void __launch_bounds__(128) attn_chunk_kernel(const AttnTcParams p) {
     {
       float s[8][4], o_t[D / 8][4], m_t[2], l_t[2];
       qk_tile<D>(s, sQ + warp * 16 * LD, sK + buf * 64 * LD, lane);
-      tile_partial<D>(s, o_t, m_t, l_t, kt * kKeys, row_pos, row_lo, p.scale_log2, sV + buf * 64 * LD, lane);
+      // every row of this warp that is in use sees every key of the tile: nothing to mask
+      const bool full = warp_pos_lo >= 0 && kt * kKeys + kKeys - 1 <= warp_pos_lo &&
+                        kt * kKeys >= (p.window > 0 ? warp_pos_hi - p.window + 1 : 0);
+      tile_partial<D>(s, o_t, m_t, l_t, kt * kKeys, row_pos, row_lo, p.scale_log2, sV + buf * 64 * LD, lane, full);
       fold_rows<D>(m_c, l_c, o_c, m_t, l_t, o_t);
     }
     if ((kt + 1) % (kChunk / kKeys) == 0 || kt == kt1) {
@@ -389,7 +420,10 @@ __global__ void __launch_bounds__(128) attn_decode_kernel(const AttnTcParams p) 
   constexpr int LD = D + 8, CH = D / 8;
   extern __shared__ __align__(16) uint8_t smem_raw[];
   bf16* sQ = reinterpret_cast<bf16*>(smem_raw);           // [16][LD]
-  bf16* sKV = sQ + 16 * LD;                               // [4 warps][K, V][64][LD]
+  // FUSED: [4 warps][K, V][64][LD]. Otherwise [4 warps][64][LD]: a warp's values take the place of its keys once the
+  // scores are out, which lets twice as many warps live on an SM; the values travel while the weights are computed.
+  bf16* sKV = sQ + 16 * LD;
+  constexpr int kBufs = FUSED ? 2 : 1;
   float* sO = reinterpret_cast<float*>(sKV);               // [4][16][D], over the key/value tiles once they are used up
   float* sML = sO + 4 * 16 * D;                           // [4][16][2]
   __shared__ int is_last_s;
@@ -411,14 +445,14 @@ __global__ void __launch_bounds__(128) attn_decode_kernel(const AttnTcParams p) 
   const bf16* kplane = p.k_base + static_cast<int64_t>(g) * p.head_stride;
   const int rows = L * G;
 
-  bf16* sK = sKV + warp * 2 * 64 * LD;
-  bf16* sV = sK + 64 * LD;
+  bf16* sK = sKV + warp * kBufs * 64 * LD;
+  bf16* sV = sK + (kBufs - 1) * 64 * LD;
   const int key0 = chunk * kChunk + warp * kKeys;
   const bool any = key0 <= pos_hi && key0 + kKeys - 1 >= key_lo;
   // Keys before this step's first position were written by earlier steps: their tiles are requested before
   // waiting for the kernels in front (which write this step's keys and the queries).
-  if (any) load_kv_tiles<D>(sK, sV, kplane, p.v_offset, table, p.page_size, p.page_shift, p.page_stride, key0, key_lo, first_pos - 1,
-                            lane, 32, key_lo, pos_hi);
+  if (any) load_kv_tiles<D, FUSED ? 3 : 1>(sK, sV, kplane, p.v_offset, table, p.page_size, p.page_shift, p.page_stride, key0, key_lo,
+                                           first_pos - 1, lane, 32, key_lo, pos_hi);
   sb::grid_dependency_wait();
   if (FUSED) {
     constexpr int half = D / 2;
@@ -457,8 +491,8 @@ __global__ void __launch_bounds__(128) attn_decode_kernel(const AttnTcParams p) 
         *reinterpret_cast<uint4*>(d) = make_uint4(0, 0, 0, 0);
     }
     if (any && key0 + kKeys - 1 >= first_pos)
-      load_kv_tiles<D>(sK, sV, kplane, p.v_offset, table, p.page_size, p.page_shift, p.page_stride, key0, max(first_pos, key_lo), pos_hi,
-                       lane, 32, key_lo, pos_hi);
+      load_kv_tiles<D, 1>(sK, sV, kplane, p.v_offset, table, p.page_size, p.page_shift, p.page_stride, key0, max(first_pos, key_lo), pos_hi,
+                          lane, 32, key_lo, pos_hi);
   }
   cp_commit();
   cp_wait<0>();
@@ -477,7 +511,20 @@ __global__ void __launch_bounds__(128) attn_decode_kernel(const AttnTcParams p) 
     }
     float s[8][4];
     qk_tile<D>(s, sQ, sK, lane);
-    tile_partial<D>(s, o_t, m_t, l_t, key0, row_pos, row_lo, p.scale_log2, sV, lane);
+    if (!FUSED) {
+      __syncwarp();     // every lane has read the keys; the values take their place
+      load_kv_tiles<D, 2>(sK, sV, kplane, p.v_offset, table, p.page_size, p.page_shift, p.page_stride, key0, key_lo, pos_hi, lane, 32);
+      cp_commit();
+    }
+    const bool full = key0 + kKeys - 1 <= first_pos && key0 >= (p.window > 0 ? pos_hi - p.window + 1 : 0);
+    if (rows > 8) tile_weights<true>(s, m_t, l_t, key0, row_pos, row_lo, p.scale_log2, lane, full);
+    else tile_weights<false>(s, m_t, l_t, key0, row_pos, row_lo, p.scale_log2, lane, full);
+    if (!FUSED) {
+      cp_wait<0>();
+      __syncwarp();
+    }
+    if (rows > 8) pv_tile<D, true>(o_t, s, sV, lane);
+    else pv_tile<D, false>(o_t, s, sV, lane);
   } else {
 #pragma unroll
     for (int dt = 0; dt < D / 8; ++dt)
@@ -488,15 +535,14 @@ __global__ void __launch_bounds__(128) attn_decode_kernel(const AttnTcParams p) 
 #pragma unroll
   for (int h = 0; h < 2; ++h) {
     const int r = gid + 8 * h;
+    if (r >= rows) continue;     // only rows in use are folded below
     if (tq == 0) {
       sML[(warp * 16 + r) * 2] = m_t[h];
       sML[(warp * 16 + r) * 2 + 1] = l_t[h];
     }
 #pragma unroll
-    for (int dt = 0; dt < D / 8; ++dt) {
-      sO[(warp * 16 + r) * D + dt * 8 + tq * 2] = o_t[dt][2 * h];
-      sO[(warp * 16 + r) * D + dt * 8 + tq * 2 + 1] = o_t[dt][2 * h + 1];
-    }
+    for (int dt = 0; dt < D / 8; ++dt)
+      *reinterpret_cast<float2*>(&sO[(warp * 16 + r) * D + dt * 8 + tq * 2]) = make_float2(o_t[dt][2 * h], o_t[dt][2 * h + 1]);
   }
   __syncthreads();
   // the chunk's record: its tiles folded in key order into an empty state
@@ -572,17 +618,20 @@ int launch(const AttnTcParams& p, int n_tiles, int n_items, cudaStream_t stream)
     sb::launch_pdl(attn_chunk_kernel<D>, dim3(n_tiles, p.Hkv), dim3(128), smem, stream, p);
   }
   if (n_items > 0) {
-    const size_t smem = static_cast<size_t>(16 * LD + 8 * 64 * LD) * sizeof(bf16);   // results (4 x 16 x (D + 2) floats) reuse the tiles
+    // queries and the warps' tiles (keys and values, or one for both in turn); the results (4 x 16 x (D + 2) floats) reuse the tiles
+    const size_t smem_fused = static_cast<size_t>(16 * LD + 8 * 64 * LD) * sizeof(bf16);
+    const size_t smem = static_cast<size_t>(16 * LD + 4 * 64 * LD) * sizeof(bf16);
+    static_assert(4 * 64 * LD * sizeof(bf16) >= 4 * 16 * (D + 2) * sizeof(float), "the results must fit over the tiles");
     static bool set = false;
     if (!set) {
       if (cudaFuncSetAttribute(attn_decode_kernel<D, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess ||
-          cudaFuncSetAttribute(attn_decode_kernel<D, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess)
+          cudaFuncSetAttribute(attn_decode_kernel<D, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem_fused) != cudaSuccess)
         return sb::fail("sb_attention_tc: cannot raise the shared memory limit");
       set = true;
     }
     AttnTcParams pd = p;
     pd.work = p.work + 2 * n_tiles;
-    if (p.qkv != nullptr) sb::launch_pdl(attn_decode_kernel<D, true>, dim3(n_items, p.Hkv, p.chunks), dim3(128), smem, stream, pd);
+    if (p.qkv != nullptr) sb::launch_pdl(attn_decode_kernel<D, true>, dim3(n_items, p.Hkv, p.chunks), dim3(128), smem_fused, stream, pd);
     else sb::launch_pdl(attn_decode_kernel<D, false>, dim3(n_items, p.Hkv, p.chunks), dim3(128), smem, stream, pd);
     if (pd.counters == nullptr) sb::launch_pdl(attn_combine_kernel<D>, dim3(n_items, p.Hkv), dim3(D), 0, stream, pd);
   }

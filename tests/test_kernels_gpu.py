@@ -268,6 +268,37 @@ def test_attention_kernels_agree_in_bits(D, Hq, Hkv, page, window):
         assert torch.equal(whole, run([(0, 37), (37, 1), (38, 70), (108, 42)], True))
 
 
+@pytest.mark.parametrize("D,Hq,Hkv,page,window", [(64, 8, 2, 64, 0), (64, 32, 8, 128, 0), (64, 6, 2, 8, 700), (128, 8, 2, 64, 0),
+                                                  (128, 6, 2, 48, 1100), (64, 5, 5, 16, 0), (64, 24, 2, 64, 0)])
+def test_decode_attention_over_long_contexts(D, Hq, Hkv, page, window):
+    """Decoded tokens (and one entry of two positions) over contexts of 1 to 2,300 keys, pages of 8 to 128 keys (one
+    lookup per tile, or one per key), 1 to 12 query heads per key/value head (rows 8 to 15 of a tile in use or not),
+    one far key that stands out: the decode kernel agrees with the float64 reference and leaves its counters ready."""
+    from stride_b200.kernels import ops
+    G = Hq // Hkv
+    news = [1, 1, min(2, 16 // G), 1, 1, 1]
+    olds = [2299, 0, 1279, 255, 256, 1800]
+    case = _paged_case(news, olds, Hq, Hkv, D, page, torch.bfloat16, seed=5 * D + page, peak=(0, 3))
+    q, cache, table, meta = case["q"], case["cache"], case["table"], case["meta"]
+    scale = 1.0 / math.sqrt(D)
+    E = len(news)
+    items = torch.arange(E, dtype=torch.int32, device=DEV)
+    chunks = max(a + b - 1 for a, b in zip(news, olds)) // 256 + 1
+    out = torch.full_like(q, float("nan"))
+    scratch = torch.zeros(ops.attention_tc_scratch(E, Hkv, chunks, D), device=DEV)
+    counters = torch.zeros(E * Hkv, dtype=torch.int32, device=DEV)
+    ops.attention_tc(q, out, cache, table, meta, items, 0, E, chunks, scratch, Hq, Hkv, D, window, scale, counters=counters)
+    torch.cuda.synchronize()
+    assert int(counters.abs().sum()) == 0
+    ref = _attention_reference(case, Hq, Hkv, D, window)
+    assert (out.float().cpu() - ref).abs().max() <= 2e-2 * max(1.0, float(ref.abs().max()))
+    # the same entries again, in another order in the batch: the same bits
+    order = torch.tensor([3, 0, 5, 1, 4, 2], dtype=torch.int32, device=DEV)
+    again = torch.full_like(q, float("nan"))
+    ops.attention_tc(q, again, cache, table, meta, order, 0, E, chunks, scratch, Hq, Hkv, D, window, scale, counters=counters)
+    assert torch.equal(out, again)
+
+
 @pytest.mark.parametrize("D,Hq,Hkv,page,window", [(64, 8, 2, 16, 0), (64, 32, 8, 64, 100), (128, 6, 2, 32, 0), (64, 3, 3, 8, 0)])
 def test_decode_attention_with_rotation_fused(D, Hq, Hkv, page, window):
     """The decode kernel that rotates and appends by itself gives the same output and leaves the same cache, bit for
