@@ -51,6 +51,7 @@ struct AttnTcParams {
   int meta_stride;
   const int32_t* work;   // chunk kernel: [tiles][2] = (entry, tile in entry); decode kernel: [items] = entry
   int Hq, Hkv;
+  int g_mul;             // ceil(65536 / (Hq / Hkv)): r / G = (r * g_mul) >> 16 for the row numbers that occur (checked on the host)
   int window;
   float scale_log2;      // softmax scale * log2(e)
   // decode only
@@ -64,6 +65,9 @@ struct AttnTcParams {
   int64_t partial_stride;
   const float* cos_sin;  // [positions][D / 2][2]
 };
+
+// Row r of a tile is (position r / G, head r % G); G is not known at compile time, so the division is a multiplication.
+__device__ __forceinline__ int div_g(const AttnTcParams& p, int r) { return (r * p.g_mul) >> 16; }
 
 __device__ __forceinline__ uint32_t smem_u32(const void* p) { return static_cast<uint32_t>(__cvta_generic_to_shared(p)); }
 __device__ __forceinline__ void cp_async16(uint32_t dst, const void* src) {
@@ -111,6 +115,28 @@ __device__ __forceinline__ void load_kv_tiles(bf16* dstK, bf16* dstV, const bf16
   // up once (the copies then do not wait for a table entry each). The entry is only used for keys that are copied.
   const bool one_page = page_shift >= 6;
   const bf16* page0 = one_page && key_lo <= key_hi ? kplane + static_cast<int64_t>(table[key0 >> page_shift]) * page_stride : kplane;
+  if (one_page && key0 >= key_lo && key0 + kKeys - 1 <= key_hi) {
+    // the whole tile is wanted and lies in one page: 64 rows of D elements in a row, copied without a test per key
+    // (one address of each kind is computed; the copies differ by constants)
+    const int i0 = tid / CH;
+    const bf16* srck = page0 + ((key0 & (page_size - 1)) + i0) * D + c * 8;
+    const bf16* srcv = srck + v_offset;
+    const uint32_t dk = smem_u32(dstK + i0 * LD + c * 8), dv = smem_u32(dstV + i0 * LD + c * 8);
+    if (threads == 32) {
+#pragma unroll
+      for (int it = 0; it < kKeys / (32 / CH); ++it) {
+        if (WHICH & 1) cp_async16(dk + it * (32 / CH) * LD * 2, srck + it * (32 / CH) * D);
+        if (WHICH & 2) cp_async16(dv + it * (32 / CH) * LD * 2, srcv + it * (32 / CH) * D);
+      }
+    } else {
+#pragma unroll
+      for (int it = 0; it < kKeys / (128 / CH); ++it) {
+        if (WHICH & 1) cp_async16(dk + it * (128 / CH) * LD * 2, srck + it * (128 / CH) * D);
+        if (WHICH & 2) cp_async16(dv + it * (128 / CH) * LD * 2, srcv + it * (128 / CH) * D);
+      }
+    }
+    return;
+  }
   for (int i = tid / CH; i < kKeys; i += threads / CH) {
     const int key = key0 + i;
     bf16* dk = dstK + i * LD + c * 8;
@@ -287,7 +313,7 @@ __global__ void __launch_bounds__(128) attn_chunk_kernel(const AttnTcParams p) {
   // Q tile: row r = (position r / G, head g * G + r % G)
   for (int idx = tid; idx < 64 * CH; idx += 128) {
     const int r = idx / CH, c = idx % CH;
-    const int pi = r / G, hh = r % G;
+    const int pi = div_g(p, r), hh = r - pi * G;
     bf16* d = sQ + r * LD + c * 8;
     if (pi < npos)
       cp_async16(smem_u32(d), p.q + (static_cast<int64_t>(row0 + pi) * p.Hq + g * G + hh) * D + c * 8);
@@ -303,7 +329,7 @@ __global__ void __launch_bounds__(128) attn_chunk_kernel(const AttnTcParams p) {
 #pragma unroll
   for (int h = 0; h < 2; ++h) {
     const int r = warp * 16 + gid + 8 * h;
-    const int pi = r / G;
+    const int pi = div_g(p, r);
     row_pos[h] = pi < npos ? pos0 + pi : -1;
     row_lo[h] = p.window > 0 ? row_pos[h] - p.window + 1 : 0;
   }
@@ -366,7 +392,7 @@ __global__ void __launch_bounds__(128) attn_chunk_kernel(const AttnTcParams p) {
 #pragma unroll
   for (int h = 0; h < 2; ++h) {
     const int r = warp * 16 + gid + 8 * h;
-    const int pi = r / G, hh = r % G;
+    const int pi = div_g(p, r), hh = r - pi * G;
     if (pi < npos) {
       const float* row = sT + r * D + tq * 2;
       bf16* dst = p.out + (static_cast<int64_t>(row0 + pi) * p.Hq + g * G + hh) * D;
@@ -391,6 +417,25 @@ __device__ __forceinline__ float fold_chunks(const float* part_o, const float* p
     m = f.m;
   }
   return finish(o, l);
+}
+
+// The same for elements (r, d) and (r, d + 1), d even: the row's factors are computed once.
+template <int D>
+__device__ __forceinline__ void fold_chunks2(const float* part_o, const float* part_ml, int64_t rec0, int c0, int c1, int r, int d,
+                                             float& a, float& b) {
+  float m = -INFINITY, l = 0.0f, o0 = 0.0f, o1 = 0.0f;
+  for (int c = c0; c <= c1; ++c) {
+    const float2 ml = __ldcg(reinterpret_cast<const float2*>(&part_ml[((rec0 + c) * 16 + r) * 2]));
+    if (ml.x == -INFINITY) continue;
+    const FoldFactors f = fold_factors(m, ml.x);
+    const float2 v = __ldcg(reinterpret_cast<const float2*>(&part_o[(rec0 + c) * 16 * D + r * D + d]));
+    l = fold_value(l, ml.y, f);
+    o0 = fold_value(o0, v.x, f);
+    o1 = fold_value(o1, v.y, f);
+    m = f.m;
+  }
+  a = finish(o0, l);
+  b = finish(o1, l);
 }
 
 // Element j and j + D / 2 of one head of one token from the projection's partial sums, rotated by the position's
@@ -486,7 +531,7 @@ __global__ void __launch_bounds__(128) attn_decode_kernel(const AttnTcParams p) 
       const int r = idx / CH, c = idx % CH;
       bf16* d = sQ + r * LD + c * 8;
       if (r < rows)
-        cp_async16(smem_u32(d), p.q + (static_cast<int64_t>(first_row + r / G) * p.Hq + g * G + r % G) * D + c * 8);
+        cp_async16(smem_u32(d), p.q + (static_cast<int64_t>(first_row + div_g(p, r)) * p.Hq + g * G + r - div_g(p, r) * G) * D + c * 8);
       else
         *reinterpret_cast<uint4*>(d) = make_uint4(0, 0, 0, 0);
     }
@@ -506,7 +551,7 @@ __global__ void __launch_bounds__(128) attn_decode_kernel(const AttnTcParams p) 
 #pragma unroll
     for (int h = 0; h < 2; ++h) {
       const int r = gid + 8 * h;
-      row_pos[h] = r < rows ? first_pos + r / G : -1;
+      row_pos[h] = r < rows ? first_pos + div_g(p, r) : -1;
       row_lo[h] = p.window > 0 ? row_pos[h] - p.window + 1 : 0;
     }
     float s[8][4];
@@ -545,25 +590,26 @@ __global__ void __launch_bounds__(128) attn_decode_kernel(const AttnTcParams p) 
       *reinterpret_cast<float2*>(&sO[(warp * 16 + r) * D + dt * 8 + tq * 2]) = make_float2(o_t[dt][2 * h], o_t[dt][2 * h + 1]);
   }
   __syncthreads();
-  // the chunk's record: its tiles folded in key order into an empty state
+  // the chunk's record: its tiles folded in key order into an empty state; a thread takes two neighbouring
+  // elements of a row, which share the row's factors
   const int64_t rec = (static_cast<int64_t>(item) * p.Hkv + g) * p.chunks + chunk;
-  for (int idx = tid; idx < rows * D; idx += 128) {
-    const int r = idx / D, d = idx % D;
-    float m = -INFINITY, l = 0.0f, o = 0.0f;
+  constexpr int PR = D / 2;
+  const int d = (tid % PR) * 2;
+  for (int r = tid / PR; r < rows; r += 128 / PR) {
+    float m = -INFINITY, l = 0.0f, o0 = 0.0f, o1 = 0.0f;
 #pragma unroll
     for (int w = 0; w < 4; ++w) {
-      const float m_w = sML[(w * 16 + r) * 2];
-      if (m_w == -INFINITY) continue;
-      const FoldFactors f = fold_factors(m, m_w);
-      l = fold_value(l, sML[(w * 16 + r) * 2 + 1], f);
-      o = fold_value(o, sO[(w * 16 + r) * D + d], f);
+      const float2 ml = *reinterpret_cast<const float2*>(&sML[(w * 16 + r) * 2]);
+      if (ml.x == -INFINITY) continue;
+      const FoldFactors f = fold_factors(m, ml.x);
+      const float2 v = *reinterpret_cast<const float2*>(&sO[(w * 16 + r) * D + d]);
+      l = fold_value(l, ml.y, f);
+      o0 = fold_value(o0, v.x, f);
+      o1 = fold_value(o1, v.y, f);
       m = f.m;
     }
-    p.part_o[rec * 16 * D + idx] = o;
-    if (d == 0) {
-      p.part_ml[(rec * 16 + r) * 2] = m;
-      p.part_ml[(rec * 16 + r) * 2 + 1] = l;
-    }
+    *reinterpret_cast<float2*>(&p.part_o[rec * 16 * D + r * D + d]) = make_float2(o0, o1);
+    if (d == 0) *reinterpret_cast<float2*>(&p.part_ml[(rec * 16 + r) * 2]) = make_float2(m, l);
   }
   if (p.counters == nullptr) return;
   // The CTA that finishes an entry's last chunk folds all of them, in ascending order, and writes the rows.
@@ -580,10 +626,11 @@ __global__ void __launch_bounds__(128) attn_decode_kernel(const AttnTcParams p) 
   if (!is_last_s) return;
   __threadfence();
   const int64_t rec0 = (static_cast<int64_t>(item) * p.Hkv + g) * p.chunks;
-  for (int idx = tid; idx < rows * D; idx += 128) {
-    const int r = idx / D, d = idx % D;
-    p.out[(static_cast<int64_t>(first_row + r / G) * p.Hq + g * G + r % G) * D + d] =
-        __float2bfloat16_rn(fold_chunks<D>(p.part_o, p.part_ml, rec0, c0, c1, r, d));
+  for (int r = tid / PR; r < rows; r += 128 / PR) {
+    float a, b;
+    fold_chunks2<D>(p.part_o, p.part_ml, rec0, c0, c1, r, d, a, b);
+    const int pi = div_g(p, r);
+    *reinterpret_cast<uint32_t*>(p.out + (static_cast<int64_t>(first_row + pi) * p.Hq + g * G + r - pi * G) * D + d) = pack_bf16(a, b);
   }
 }
 
@@ -678,6 +725,9 @@ int attention_tc_impl(const void* q, void* out, const void* k_base, const int32_
   p.work = work;
   p.Hq = Hq;
   p.Hkv = Hkv;
+  p.g_mul = (65536 + Hq / Hkv - 1) / (Hq / Hkv);
+  for (int r = 0; r < 64; ++r)
+    if (((r * p.g_mul) >> 16) != r / (Hq / Hkv)) return sb::fail("sb_attention_tc: the row arithmetic does not hold for %d/%d heads", Hq, Hkv);
   p.window = window;
   p.scale_log2 = scale * kLog2e;
   p.chunks = chunks;
