@@ -39,6 +39,10 @@ using bf16 = __nv_bfloat16;
 using namespace sb::attn;
 constexpr int kKeys = kTileKeys;    // keys per tile
 constexpr int kChunk = kChunkKeys;  // keys per chunk (4 tiles; the decode kernel gives each warp one)
+#ifndef SB_DECODE_CTAS64
+#define SB_DECODE_CTAS64 6
+#endif
+constexpr int kDecodeCtas64 = SB_DECODE_CTAS64;   // CTAs of the decode kernel per SM at head size 64 (bounds its registers)
 
 struct AttnTcParams {
   const bf16* q;     // [n][Hq * D]
@@ -97,8 +101,16 @@ __device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) {
 // Copies keys and values [key0, key0 + 64) of one kv head into dstK and dstV ([64][D + 8] each); keys outside
 // [key_lo, key_hi] are zero-filled. `threads` threads of the caller take part (tid in 0..threads-1): D / 8
 // threads share a key (one 16-byte piece each), so the page is looked up once for a key's key and value rows.
+// Element offset of the 16-byte piece `piece` of row `row` of a [64][D] tile. SW = false: rows of D + 8 elements
+// (the padding keeps ldmatrix off bank conflicts). SW = true: rows of D elements, the piece's low three bits XORed
+// with the row's, which does the same without the padding.
+template <int D, bool SW>
+__device__ __forceinline__ int tile_offset(int row, int piece) {
+  return SW ? row * D + ((piece ^ (row & 7)) << 3) : row * (D + 8) + (piece << 3);
+}
+
 // WHICH: 1 = keys only, 2 = values only, 3 = both.
-template <int D, int WHICH = 3>
+template <int D, int WHICH = 3, bool SW = false>
 __device__ __forceinline__ void load_kv_tiles(bf16* dstK, bf16* dstV, const bf16* kplane, int64_t v_offset,
                                               const int32_t* table, int page_size, int page_shift, int64_t page_stride,
                                               int key0, int key_lo, int key_hi, int tid, int threads,
@@ -121,26 +133,36 @@ __device__ __forceinline__ void load_kv_tiles(bf16* dstK, bf16* dstV, const bf16
     const int i0 = tid / CH;
     const bf16* srck = page0 + ((key0 & (page_size - 1)) + i0) * D + c * 8;
     const bf16* srcv = srck + v_offset;
-    const uint32_t dk = smem_u32(dstK + i0 * LD + c * 8), dv = smem_u32(dstV + i0 * LD + c * 8);
+    constexpr int RS = SW ? D : LD;       // elements per row of the tile
     if (threads == 32) {
+      // rows i0 + ph * S + 8 j: those of one ph share the row's low three bits, hence the swizzled piece
+      constexpr int S = 32 / CH, P = 8 / S;
 #pragma unroll
-      for (int it = 0; it < kKeys / (32 / CH); ++it) {
-        if (WHICH & 1) cp_async16(dk + it * (32 / CH) * LD * 2, srck + it * (32 / CH) * D);
-        if (WHICH & 2) cp_async16(dv + it * (32 / CH) * LD * 2, srcv + it * (32 / CH) * D);
+      for (int ph = 0; ph < P; ++ph) {
+        const int off = tile_offset<D, SW>(i0 + ph * S, c);
+        const uint32_t dk = smem_u32(dstK + off), dv = smem_u32(dstV + off);
+#pragma unroll
+        for (int j = 0; j < kKeys / 8; ++j) {
+          if (WHICH & 1) cp_async16(dk + j * 8 * RS * 2, srck + (ph * S + 8 * j) * D);
+          if (WHICH & 2) cp_async16(dv + j * 8 * RS * 2, srcv + (ph * S + 8 * j) * D);
+        }
       }
     } else {
+      // 128 threads: a thread's rows are 8 or 16 apart
+      const int off = tile_offset<D, SW>(i0, c);
+      const uint32_t dk = smem_u32(dstK + off), dv = smem_u32(dstV + off);
 #pragma unroll
       for (int it = 0; it < kKeys / (128 / CH); ++it) {
-        if (WHICH & 1) cp_async16(dk + it * (128 / CH) * LD * 2, srck + it * (128 / CH) * D);
-        if (WHICH & 2) cp_async16(dv + it * (128 / CH) * LD * 2, srcv + it * (128 / CH) * D);
+        if (WHICH & 1) cp_async16(dk + it * (128 / CH) * RS * 2, srck + it * (128 / CH) * D);
+        if (WHICH & 2) cp_async16(dv + it * (128 / CH) * RS * 2, srcv + it * (128 / CH) * D);
       }
     }
     return;
   }
   for (int i = tid / CH; i < kKeys; i += threads / CH) {
     const int key = key0 + i;
-    bf16* dk = dstK + i * LD + c * 8;
-    bf16* dv = dstV + i * LD + c * 8;
+    bf16* dk = dstK + tile_offset<D, SW>(i, c);
+    bf16* dv = dstV + tile_offset<D, SW>(i, c);
     if (key >= key_lo && key <= key_hi) {
       const int pi = page_shift >= 0 ? key >> page_shift : key / page_size;
       const int in_page = page_shift >= 0 ? key & (page_size - 1) : key % page_size;
@@ -155,7 +177,7 @@ __device__ __forceinline__ void load_kv_tiles(bf16* dstK, bf16* dstV, const bf16
 }
 
 // S[16 x 64] = Q[16 x D] K^T for one warp; Q rows at sQ (16 rows of this warp) and the K tile in shared memory.
-template <int D>
+template <int D, bool SW = false>
 __device__ __forceinline__ void qk_tile(float (*s)[4], const bf16* sQ, const bf16* sK, int lane) {
   constexpr int LD = D + 8;
 #pragma unroll
@@ -170,7 +192,7 @@ __device__ __forceinline__ void qk_tile(float (*s)[4], const bf16* sQ, const bf1
 #pragma unroll
     for (int nt = 0; nt < 8; nt += 2) {
       uint32_t b[4];
-      ldsm_x4(b, smem_u32(sK + (nt * 8 + (mi >> 1) * 8 + rr) * LD + ks * 16 + (mi & 1) * 8));
+      ldsm_x4(b, smem_u32(sK + tile_offset<D, SW>(nt * 8 + (mi >> 1) * 8 + rr, ks * 2 + (mi & 1))));
       mma_16816(s[nt], qf, b[0], b[1]);
       mma_16816(s[nt + 1], qf, b[2], b[3]);
     }
@@ -180,9 +202,8 @@ __device__ __forceinline__ void qk_tile(float (*s)[4], const bf16* sQ, const bf1
 // O[16 x D] = P[16 x 64] V[64 x D] from zero; P given as float weights in the layout of qk_tile's accumulators.
 // Each weight enters as two bfloat16 parts (split_hi_lo), hi . V then lo . V for every step of 16 keys.
 // kUpper = false: rows 8..15 of the tile are not in use; their weights are taken as zero without being looked at.
-template <int D, bool kUpper = true>
+template <int D, bool kUpper = true, bool SW = false>
 __device__ __forceinline__ void pv_tile(float (*o)[4], const float (*s)[4], const bf16* sV, int lane) {
-  constexpr int LD = D + 8;
   const int mi = lane >> 3, rr = lane & 7;
 #pragma unroll
   for (int dt = 0; dt < D / 8; ++dt)
@@ -199,7 +220,7 @@ __device__ __forceinline__ void pv_tile(float (*o)[4], const float (*s)[4], cons
 #pragma unroll
     for (int dt = 0; dt < D / 8; dt += 2) {
       uint32_t b[4];
-      ldsm_x4_trans(b, smem_u32(sV + (kk * 16 + (mi & 1) * 8 + rr) * LD + (dt + (mi >> 1)) * 8));
+      ldsm_x4_trans(b, smem_u32(sV + tile_offset<D, SW>(kk * 16 + (mi & 1) * 8 + rr, dt + (mi >> 1))));
       mma_16816(o[dt], hi, b[0], b[1]);
       mma_16816(o[dt + 1], hi, b[2], b[3]);
       mma_16816(o[dt], lo, b[0], b[1]);
@@ -461,14 +482,16 @@ __device__ __forceinline__ void projected_pair(const AttnTcParams& p, int row, i
 // FUSED: the step's queries, keys and values are taken from the projection's partial sums, rotated here, and the
 // keys and values are appended to the cache by the CTA whose chunk holds their position (no rotation kernel runs).
 template <int D, bool FUSED>
-__global__ void __launch_bounds__(128) attn_decode_kernel(const AttnTcParams p) {
+__global__ void __launch_bounds__(128, FUSED ? 3 : (D == 64 ? kDecodeCtas64 : 3)) attn_decode_kernel(const AttnTcParams p) {
   constexpr int LD = D + 8, CH = D / 8;
-  extern __shared__ __align__(16) uint8_t smem_raw[];
-  bf16* sQ = reinterpret_cast<bf16*>(smem_raw);           // [16][LD]
-  // FUSED: [4 warps][K, V][64][LD]. Otherwise [4 warps][64][LD]: a warp's values take the place of its keys once the
-  // scores are out, which lets twice as many warps live on an SM; the values travel while the weights are computed.
-  bf16* sKV = sQ + 16 * LD;
-  constexpr int kBufs = FUSED ? 2 : 1;
+  // FUSED: tiles [4 warps][K, V][64][D + 8]. Otherwise [4 warps][64][D], swizzled: a warp's values take the place of
+  // its keys once the scores are out, which lets twice as many warps live on an SM; the values travel while the
+  // weights are computed.
+  constexpr bool SW = !FUSED;
+  constexpr int kBufs = FUSED ? 2 : 1, kTile = SW ? 64 * D : 64 * LD;
+  extern __shared__ __align__(128) uint8_t smem_tiles[];
+  bf16* sKV = reinterpret_cast<bf16*>(smem_tiles);
+  bf16* sQ = sKV + 4 * kBufs * kTile;                      // [16][LD]
   float* sO = reinterpret_cast<float*>(sKV);               // [4][16][D], over the key/value tiles once they are used up
   float* sML = sO + 4 * 16 * D;                           // [4][16][2]
   __shared__ int is_last_s;
@@ -490,13 +513,13 @@ __global__ void __launch_bounds__(128) attn_decode_kernel(const AttnTcParams p) 
   const bf16* kplane = p.k_base + static_cast<int64_t>(g) * p.head_stride;
   const int rows = L * G;
 
-  bf16* sK = sKV + warp * kBufs * 64 * LD;
-  bf16* sV = sK + (kBufs - 1) * 64 * LD;
+  bf16* sK = sKV + warp * kBufs * kTile;
+  bf16* sV = sK + (kBufs - 1) * kTile;
   const int key0 = chunk * kChunk + warp * kKeys;
   const bool any = key0 <= pos_hi && key0 + kKeys - 1 >= key_lo;
   // Keys before this step's first position were written by earlier steps: their tiles are requested before
   // waiting for the kernels in front (which write this step's keys and the queries).
-  if (any) load_kv_tiles<D, FUSED ? 3 : 1>(sK, sV, kplane, p.v_offset, table, p.page_size, p.page_shift, p.page_stride, key0, key_lo,
+  if (any) load_kv_tiles<D, FUSED ? 3 : 1, SW>(sK, sV, kplane, p.v_offset, table, p.page_size, p.page_shift, p.page_stride, key0, key_lo,
                                            first_pos - 1, lane, 32, key_lo, pos_hi);
   sb::grid_dependency_wait();
   if (FUSED) {
@@ -536,8 +559,8 @@ __global__ void __launch_bounds__(128) attn_decode_kernel(const AttnTcParams p) 
         *reinterpret_cast<uint4*>(d) = make_uint4(0, 0, 0, 0);
     }
     if (any && key0 + kKeys - 1 >= first_pos)
-      load_kv_tiles<D, 1>(sK, sV, kplane, p.v_offset, table, p.page_size, p.page_shift, p.page_stride, key0, max(first_pos, key_lo), pos_hi,
-                          lane, 32, key_lo, pos_hi);
+      load_kv_tiles<D, 1, SW>(sK, sV, kplane, p.v_offset, table, p.page_size, p.page_shift, p.page_stride, key0, max(first_pos, key_lo),
+                              pos_hi, lane, 32, key_lo, pos_hi);
   }
   cp_commit();
   cp_wait<0>();
@@ -555,10 +578,10 @@ __global__ void __launch_bounds__(128) attn_decode_kernel(const AttnTcParams p) 
       row_lo[h] = p.window > 0 ? row_pos[h] - p.window + 1 : 0;
     }
     float s[8][4];
-    qk_tile<D>(s, sQ, sK, lane);
+    qk_tile<D, SW>(s, sQ, sK, lane);
     if (!FUSED) {
       __syncwarp();     // every lane has read the keys; the values take their place
-      load_kv_tiles<D, 2>(sK, sV, kplane, p.v_offset, table, p.page_size, p.page_shift, p.page_stride, key0, key_lo, pos_hi, lane, 32);
+      load_kv_tiles<D, 2, SW>(sK, sV, kplane, p.v_offset, table, p.page_size, p.page_shift, p.page_stride, key0, key_lo, pos_hi, lane, 32);
       cp_commit();
     }
     const bool full = key0 + kKeys - 1 <= first_pos && key0 >= (p.window > 0 ? pos_hi - p.window + 1 : 0);
@@ -568,8 +591,8 @@ __global__ void __launch_bounds__(128) attn_decode_kernel(const AttnTcParams p) 
       cp_wait<0>();
       __syncwarp();
     }
-    if (rows > 8) pv_tile<D, true>(o_t, s, sV, lane);
-    else pv_tile<D, false>(o_t, s, sV, lane);
+    if (rows > 8) pv_tile<D, true, SW>(o_t, s, sV, lane);
+    else pv_tile<D, false, SW>(o_t, s, sV, lane);
   } else {
 #pragma unroll
     for (int dt = 0; dt < D / 8; ++dt)
@@ -667,8 +690,8 @@ int launch(const AttnTcParams& p, int n_tiles, int n_items, cudaStream_t stream)
   if (n_items > 0) {
     // queries and the warps' tiles (keys and values, or one for both in turn); the results (4 x 16 x (D + 2) floats) reuse the tiles
     const size_t smem_fused = static_cast<size_t>(16 * LD + 8 * 64 * LD) * sizeof(bf16);
-    const size_t smem = static_cast<size_t>(16 * LD + 4 * 64 * LD) * sizeof(bf16);
-    static_assert(4 * 64 * LD * sizeof(bf16) >= 4 * 16 * (D + 2) * sizeof(float), "the results must fit over the tiles");
+    const size_t smem = static_cast<size_t>(16 * LD + 4 * 64 * D) * sizeof(bf16);
+    static_assert(4 * 64 * D * sizeof(bf16) >= 4 * 16 * (D + 2) * sizeof(float), "the results must fit over the tiles");
     static bool set = false;
     if (!set) {
       if (cudaFuncSetAttribute(attn_decode_kernel<D, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess ||
