@@ -119,13 +119,15 @@ def step(a) -> dict:
     cfg = dict(LLAMA_1B_SHAPE, num_hidden_layers=a.layers)
     B, T = a.batch, a.prefill
     opts = EngineOptions(dtype="bfloat16", max_rows=max(512, B, T), max_full_rows=max(B, 1), max_slots=B + 2,
-                         kv_pages=B * 8 + T // 64 + 48, page_size=64, max_context=4096)
+                         kv_pages=B * (a.context // 64 + 4) + T // 64 + 48, page_size=64, max_context=4096)
     eng = Engine.from_random(cfg, 0, opts)
     gen = torch.Generator().manual_seed(1)
     slots = [eng.cache.acquire_slot() for _ in range(B)]
     for s in slots:
         eng.cache.ensure(s, a.context)
-        eng.step([StepEntry(s, 0, torch.randint(0, 1000, (a.context,), generator=gen).tolist(), [])])
+        for at in range(0, a.context, opts.max_rows):
+            n = min(opts.max_rows, a.context - at)
+            eng.step([StepEntry(s, at, torch.randint(0, 1000, (n,), generator=gen).tolist(), [])])
 
     def decode(k):
         entries = []
