@@ -393,6 +393,9 @@ SB_EXPORT int sb_attention_tc5(const void* q, void* out, const void* k_base, int
   return sb::check_launch("sb_attention_tc5");
 }
 
+// From now on the kernel reports into `device_word` (see sb_gemm_tc_use_status_word); null: into its own again.
+SB_EXPORT void sb_attention_tc5_use_status_word(int* device_word) { status_word_given() = device_word; }
+
 // Reads and clears the status word: 0 = every wait completed. Synchronises the device.
 SB_EXPORT int sb_attention_tc5_status() {
   int* status = status_word();

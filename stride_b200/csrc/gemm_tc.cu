@@ -1149,6 +1149,31 @@ SB_EXPORT int sb_gemm_tc(const void* x, int64_t ldx, const void* w, int64_t ldw,
   return sb::check_launch("sb_gemm_tc");
 }
 
+// From now on the kernels of this library report into `device_word` (an int of device memory that the caller
+// keeps alive and has zeroed); null: into the library's own word again. Kernels already recorded in a CUDA graph keep
+// the word they were recorded with.
+SB_EXPORT void sb_gemm_tc_use_status_word(int* device_word) { status_word_given() = device_word; }
+
+namespace {
+// A wait that nothing ends: one thread waits on a barrier on which nobody arrives, gives up after the usual limit
+// and reports `code`.
+__global__ void lost_signal_kernel(int* status, int code) {
+  __shared__ __align__(8) uint64_t bar;
+  mbar_init(smem_u32(&bar), 1);
+  mbar_init_fence();
+  mbar_wait(smem_u32(&bar), 0, status, code);
+}
+}  // namespace
+
+// Self-test of the reporting path: launches the kernel above (about a second) and returns; the status word then
+// reads `code` until somebody clears it.
+SB_EXPORT int sb_gemm_tc_lost_signal_selftest(int code, cudaStream_t stream) {
+  int* status = status_word();
+  if (!status) return sb::fail("sb_gemm_tc: cannot allocate the status word");
+  lost_signal_kernel<<<1, 1, 0, stream>>>(status, code);
+  return sb::check_launch("sb_gemm_tc_lost_signal_selftest");
+}
+
 // Reads and clears the status word: 0 = every wait completed; 1, 2, 3 = the producer, the MMA issuer or
 // the epilogue gave up waiting. Synchronises the device.
 SB_EXPORT int sb_gemm_tc_status() {

@@ -37,12 +37,21 @@ __device__ __forceinline__ unsigned long long pack_best(float v, int idx) {
   return (static_cast<unsigned long long>(order_key(v)) << 32) | (0xFFFFFFFFu - static_cast<uint32_t>(idx));
 }
 
+// `watch` (optional): the status word of the kernels that made the logits. If a wait inside one of them gave up
+// (the word is not 0), the token reported to the host is -1 - code instead of a token id, so that the failure
+// travels with the step's result and costs no copy of its own; what is scattered for the next step stays a token id.
+__device__ __forceinline__ int poisoned(int token, const int* watch) {
+  if (watch == nullptr) return token;
+  const int code = *reinterpret_cast<const volatile int*>(watch);
+  return code != 0 ? -1 - code : token;
+}
+
 // `scatter` (optional): the chosen token is also stored at scatter[scatter_index[row]] (the request's slot), where
 // the next step's embedding looks for it.
 __global__ void __launch_bounds__(kThreads) argmax_kernel(const float* __restrict__ logits, int64_t ld, int vocab,
                                                            int32_t* __restrict__ tokens, float* __restrict__ values,
                                                            const int32_t* __restrict__ scatter_index,
-                                                           int32_t* __restrict__ scatter) {
+                                                           int32_t* __restrict__ scatter, const int* __restrict__ watch) {
   __shared__ unsigned long long best_s[32];
   sb::grid_launch_dependents();
   sb::grid_dependency_wait();
@@ -64,7 +73,7 @@ __global__ void __launch_bounds__(kThreads) argmax_kernel(const float* __restric
   if (threadIdx.x == 0) {
     for (int i = 1; i < kThreads / 32; ++i) best = best_s[i] > best ? best_s[i] : best;
     const int idx = best == 0 ? 0 : static_cast<int>(0xFFFFFFFFu - static_cast<uint32_t>(best & 0xFFFFFFFFu));
-    tokens[blockIdx.x] = idx;
+    tokens[blockIdx.x] = poisoned(idx, watch);
     values[blockIdx.x] = l[idx];
     if (scatter != nullptr) scatter[scatter_index[blockIdx.x]] = idx;
   }
@@ -73,7 +82,8 @@ __global__ void __launch_bounds__(kThreads) argmax_kernel(const float* __restric
 __global__ void __launch_bounds__(kThreads) sample_temperature_kernel(
     const float* __restrict__ logits, int64_t ld, int vocab, const float* __restrict__ temperatures,
     const unsigned long long* __restrict__ seeds, const int32_t* __restrict__ lengths, int32_t* __restrict__ tokens,
-    float* __restrict__ values, const int32_t* __restrict__ scatter_index, int32_t* __restrict__ scatter) {
+    float* __restrict__ values, const int32_t* __restrict__ scatter_index, int32_t* __restrict__ scatter,
+    const int* __restrict__ watch) {
   __shared__ double hist[256];
   __shared__ int count[256];
   __shared__ float red[32];
@@ -163,7 +173,7 @@ __global__ void __launch_bounds__(kThreads) sample_temperature_kernel(
     for (int i = t; i < vocab; i += kThreads) {
       const float v = l[i];
       if (v == v && order_key(v) == key) {
-        tokens[row] = i;
+        tokens[row] = poisoned(i, watch);
         values[row] = v;
         if (scatter != nullptr) scatter[scatter_index[row]] = i;
       }
@@ -181,7 +191,7 @@ __global__ void __launch_bounds__(kThreads) sample_temperature_kernel(
         if (skip-- == 0) break;
       }
     }
-    tokens[row] = pick;
+    tokens[row] = poisoned(pick, watch);
     values[row] = l[pick];
     if (scatter != nullptr) scatter[scatter_index[row]] = pick;
   }
@@ -189,11 +199,18 @@ __global__ void __launch_bounds__(kThreads) sample_temperature_kernel(
 
 }  // namespace
 
+namespace {
+const int* g_watch = nullptr;
+}
+// From now on the kernels of this library look at `device_word` (the status word of the kernels that make the
+// logits; null: at nothing) and report -1 - its value instead of a token while it is not 0.
+SB_EXPORT void sb_sampling_use_status_word(const int* device_word) { g_watch = device_word; }
+
 SB_EXPORT int sb_argmax(const float* logits, int64_t ld, int rows, int vocab, int32_t* tokens, float* values,
                         const int32_t* scatter_index, int32_t* scatter, cudaStream_t stream) {
   if (rows <= 0) return 0;
   if (vocab <= 0) return sb::fail("sb_argmax: empty vocabulary");
-  sb::launch_pdl(argmax_kernel, dim3(rows), dim3(kThreads), 0, stream, logits, ld, vocab, tokens, values, scatter_index, scatter);
+  sb::launch_pdl(argmax_kernel, dim3(rows), dim3(kThreads), 0, stream, logits, ld, vocab, tokens, values, scatter_index, scatter, g_watch);
   return sb::check_launch("sb_argmax");
 }
 
@@ -203,6 +220,6 @@ SB_EXPORT int sb_sample_temperature(const float* logits, int64_t ld, int rows, i
   if (rows <= 0) return 0;
   if (vocab <= 0) return sb::fail("sb_sample_temperature: empty vocabulary");
   sb::launch_pdl(sample_temperature_kernel, dim3(rows), dim3(kThreads), 0, stream, logits, ld, vocab, temperatures, seeds, lengths, tokens, values, scatter_index,
-                 scatter);
+                 scatter, g_watch);
   return sb::check_launch("sb_sample_temperature");
 }

@@ -259,8 +259,14 @@ inline bool tensor_map_bf16(const void* base, int rank, const int64_t* dims, con
   return true;
 }
 
-// One int of device memory per library for the bounded waits' error codes.
+// One int of device memory for the bounded waits' error codes: the library's own, or the one its user handed it
+// (so that all libraries of a process report into one word, which an engine can read back with every step).
+inline int*& status_word_given() {
+  static int* word = nullptr;
+  return word;
+}
 inline int* status_word() {
+  if (status_word_given()) return status_word_given();
   static int* word = nullptr;
   static std::once_flag once;
   std::call_once(once, [] {

@@ -90,7 +90,13 @@ class Engine:
                        max_requests=o.max_slots)
         self.env = env
         self.model = DecoderModel(self.spec, env)
-        build_all(sorted(self.model.kernel_libraries()))      # what this model needs, compiled side by side if missing
+        libraries = self.model.kernel_libraries()
+        build_all(sorted(libraries))      # what this model needs, compiled side by side if missing
+        # the word into which the tensor-core kernels' bounded waits report; the sampling kernels pass it on to the host
+        self._status_device = None
+        if self.device.type == "cuda" and libraries & {"gemm_tc", "attention_tc5"}:
+            from ..kernels import ops
+            self._status_device = ops.shared_status_word(libraries | {"sampling"})
         plan = self.model.tensor_plan()
         if tensors is None:
             tensors = load_weights(model_dir, plan, self.device)
@@ -224,6 +230,19 @@ class Engine:
         self.logit_slots = d[8 * R:8 * R + count]
         self.steps += 1
         return logits
+
+    def check_kernels(self, code: int = 0) -> None:
+        """Raises if a bounded wait inside a tensor-core kernel gave up, in which case the steps since are not valid:
+        `code` is what the sampling kernels reported instead of a token, or 0 to read the status word now (which
+        waits for the device)."""
+        if self._status_device is None:
+            return
+        if code == 0:
+            code = int(self._status_device.item())
+        if code != 0:
+            self._status_device.zero_()
+            raise EngineError(f"a wait inside a tensor-core kernel gave up (code {code}): a signal was lost and the "
+                              f"results of the step are not valid")
 
     # ------------------------------------------------------------------ decode steps as CUDA graphs
     def _graph_step(self, entries: list) -> Optional[torch.Tensor]:

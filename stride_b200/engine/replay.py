@@ -76,7 +76,9 @@ def main(argv=None) -> int:
             live[rid][1] = fed + len(tokens)
         logits = engine.step(entries) if entries else None
         if logits is not None:
-            logits.detach().to("cpu", torch.float32).numpy().astype("<f4", copy=False).tofile(out / f"{step}.f32")
+            host = logits.detach().to("cpu", torch.float32)
+            engine.check_kernels()        # the copy waited for the step: a wait that gave up inside a kernel is an error
+            host.numpy().astype("<f4", copy=False).tofile(out / f"{step}.f32")
         else:
             torch.cuda.synchronize()
         for slot, _ in (live[r] for r in live):

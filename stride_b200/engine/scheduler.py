@@ -206,6 +206,14 @@ class Scheduler:
         self._running.remove(victim)
         self._waiting.appendleft(victim)
 
+    def _check_kernels(self, tokens) -> None:
+        """The step's tokens are on the host. The sampling kernels report -1 - code instead of a token when a wait
+        inside one of the step's tensor-core kernels gave up: that is an error, not a token."""
+        worst = min((int(t) for t in tokens), default=0)
+        if worst < 0:
+            self.engine.check_kernels(-1 - worst)
+            raise EngineError(f"the sampler returned {worst} instead of a token")
+
     # ------------------------------------------------------------------ planning
     def plan(self):
         """[(sequence, tokens to run)] for the next step, pages ensured; None if nothing is to run."""
@@ -268,6 +276,7 @@ class Scheduler:
         self.stats.peak_blocks = max(self.stats.peak_blocks, used)
         if wanted:
             tokens, values = self._sampler.choose(logits, [s.req.sampling for s in wanted], [len(s.tokens) for s in wanted])
+            self._check_kernels(tokens)
             full = None
             if any(s.req.full_logits and s.req.on_token for s in wanted):
                 full = logits.to("cpu").numpy()
@@ -346,6 +355,7 @@ class Scheduler:
         cache = self.engine.cache
         if ticket is not None:
             tokens, values = self._sampler.collect(ticket)
+            self._check_kernels(tokens)
             for i, s in enumerate(wanted):
                 s.inflight -= 1
                 if s.done:                                   # finished by a stop token a step ago: this row was surplus

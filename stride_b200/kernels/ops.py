@@ -233,6 +233,35 @@ def gemm_tc_status() -> int:
     return lib.sb_gemm_tc_status()
 
 
+_status_word = None
+_status_users = {"gemm_tc": "sb_gemm_tc_use_status_word", "attention_tc5": "sb_attention_tc5_use_status_word",
+                 "sampling": "sb_sampling_use_status_word"}   # the sampling kernels only read it
+_status_registered: set = set()
+
+
+def shared_status_word(libraries=("gemm_tc",)) -> torch.Tensor:
+    """One int32 on the device into which the bounded waits of the tensor-core kernels report when they give up:
+    0 = every wait completed. Made at the first call; those of `libraries` that have such waits (gemm_tc,
+    attention_tc5) use it from then on, and the sampling kernels report -1 - its value instead of a token while it is
+    not 0, so that a lost signal is an error and not a wrong token."""
+    global _status_word
+    if _status_word is None:
+        _status_word = torch.zeros(1, dtype=torch.int32, device="cuda")
+    for lib_name in sorted(set(libraries) & set(_status_users) - _status_registered):
+        fn = getattr(library(lib_name), _status_users[lib_name])
+        fn.argtypes, fn.restype = [c_void_p], None
+        fn(_status_word.data_ptr())
+        _status_registered.add(lib_name)
+    return _status_word
+
+
+def lost_signal_selftest(code: int = 9) -> None:
+    """Launches a kernel whose only wait is never answered: after about a second it gives up and the status word
+    reads `code`. Exercises the path by which a lost signal inside a tensor-core kernel becomes an error."""
+    lib, fn = _fn("gemm_tc", "sb_gemm_tc_lost_signal_selftest", [c_int, c_void_p])
+    _check(lib, fn(code, _stream()))
+
+
 def attention_tc_scratch(items: int, num_kv_heads: int, chunks: int, head_dim: int) -> int:
     """Floats of scratch `attention_tc` needs."""
     return items * num_kv_heads * chunks * 16 * (head_dim + 2)

@@ -144,6 +144,9 @@ class Sampler:
         self._events[turn].synchronize()
         tokens = self._host_tokens[turn][0, :rows].tolist()
         values = self._host_values[turn][0, :rows].tolist()
+        if rows and min(tokens) < 0:
+            # the kernels report -1 - code instead of tokens: a wait inside a kernel that made these logits gave up
+            return [min(tokens)] * rows, values
         for i in device_rows:
             tokens[i] = int(self._host_tokens[turn][1, i])
             values[i] = float(self._host_values[turn][1, i])

@@ -158,3 +158,22 @@ def test_command_line(model_dirs, tmp_path):
         ref = plain.forward(cfg, w, p + row["tokens"][:1])
         assert np.abs(logits[i, 0] - ref[len(p) - 1].numpy()).max() <= 2e-4
         assert np.abs(logits[i, 1] - ref[len(p)].numpy()).max() <= 2e-4
+
+
+def test_a_lost_signal_inside_a_kernel_is_an_error(model_dirs):
+    """A bounded wait that gives up (here: a kernel whose only wait nothing answers, which ends by itself after about
+    a second) leaves its code in the status word that the engine reads back with every step: generation raises instead
+    of returning tokens, and works again afterwards."""
+    from stride_b200 import LLM
+    from stride_b200.engine.engine import EngineError
+    from stride_b200.kernels import ops
+    llm = LLM(model_dirs["A"], dtype="bfloat16", concurrency=2, max_rows=64, page_size=TINY["A"][2], kv_pages=64, max_slots=4)
+    prompts = _prompts("A", [5, 9])
+    good = llm.generate(prompts, max_new_tokens=4)
+    ops.lost_signal_selftest(code=9)
+    with pytest.raises(EngineError, match="code 9"):
+        llm.generate(prompts, max_new_tokens=4)
+    assert ops.gemm_tc_status() == 0          # the engine cleared the word when it raised
+    llm2 = LLM(model_dirs["A"], dtype="bfloat16", concurrency=2, max_rows=64, page_size=TINY["A"][2], kv_pages=64, max_slots=4)
+    again = llm2.generate(prompts, max_new_tokens=4)
+    assert [o.tokens for o in again] == [o.tokens for o in good]
