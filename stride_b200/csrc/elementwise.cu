@@ -167,7 +167,22 @@ __global__ void rope_append_vec_kernel(RopeAppendParams p) {
   sb::grid_dependency_wait();   // everything above is an input of the step; qkv comes from the kernel before
   const float* src = p.qkv + static_cast<int64_t>(row) * heads * D + static_cast<int64_t>(head) * D;
   float4 a = *reinterpret_cast<const float4*>(src + j), b = *reinterpret_cast<const float4*>(src + half + j);
-  for (int s = 1; s < p.n_partials; ++s) {
+  // the K ranges' sums are added in ascending order; they are fetched four at a time so that the loads overlap
+  int s = 1;
+  for (; s + 3 < p.n_partials; s += 4) {
+    float4 pa[4], pb[4];
+#pragma unroll
+    for (int u = 0; u < 4; ++u) {
+      pa[u] = *reinterpret_cast<const float4*>(src + (s + u) * p.partial_stride + j);
+      pb[u] = *reinterpret_cast<const float4*>(src + (s + u) * p.partial_stride + half + j);
+    }
+#pragma unroll
+    for (int u = 0; u < 4; ++u) {
+      a = add4(a, pa[u]);
+      b = add4(b, pb[u]);
+    }
+  }
+  for (; s < p.n_partials; ++s) {
     a = add4(a, *reinterpret_cast<const float4*>(src + s * p.partial_stride + j));
     b = add4(b, *reinterpret_cast<const float4*>(src + s * p.partial_stride + half + j));
   }

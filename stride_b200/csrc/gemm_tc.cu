@@ -937,7 +937,10 @@ SB_EXPORT int sb_gemm_tc_splits(int M, int K) {
 }
 
 // The most tokens for which sb_gemm_tc leaves one partial buffer per K range; with more it adds the ranges itself.
-SB_EXPORT int sb_gemm_tc_partial_tokens() { return 128; }
+// (Measured at the 1B layer sizes: up to 512 tokens a CTA per K range and the consumer's additions beat one CTA that
+// walks all ranges of its tile, since the tiles of so few tokens leave most SMs idle: a step of 256 tokens 2.28 ms
+// against 3.0 ms, of 512 tokens 2.94 against 3.15; at 1,024 tokens the partial sums' traffic costs more than it saves.)
+SB_EXPORT int sb_gemm_tc_partial_tokens() { return 512; }
 
 // out = x . W^T on the tensor cores.
 //   epilogue 0: out float32 [n, ldo]; `splits` K ranges (sb_gemm_tc_splits, or 1). Up to sb_gemm_tc_partial_tokens()
@@ -953,7 +956,7 @@ SB_EXPORT int sb_gemm_tc(const void* x, int64_t ldx, const void* w, int64_t ldw,
   if ((reinterpret_cast<uintptr_t>(x) | reinterpret_cast<uintptr_t>(w)) & 15)
     return sb::fail("sb_gemm_tc: operands must be 16-byte aligned");
   if (epilogue < 0 || epilogue > 2) return sb::fail("sb_gemm_tc: unknown epilogue %d", epilogue);
-  const bool fold = splits > 1 && n > 128;   // the kernel adds the ranges
+  const bool fold = splits > 1 && n > sb_gemm_tc_partial_tokens();   // the kernel adds the ranges
   if (epilogue == kSwiglu && splits != 1) return sb::fail("sb_gemm_tc: the SwiGLU epilogue takes no K ranges");
   if (epilogue == kAdd && splits != 1) return sb::fail("sb_gemm_tc: the sum of K ranges is added to the residual by its consumer (plain store)");
   if (epilogue == kSwiglu && (half_rows <= 0 || M != 2 * half_rows)) return sb::fail("sb_gemm_tc: swiglu needs M = 2 * half_rows");
@@ -978,7 +981,7 @@ SB_EXPORT int sb_gemm_tc(const void* x, int64_t ldx, const void* w, int64_t ldw,
     const long long tm = epilogue == kSwiglu ? (half_rows + 63) / 64 : (M + kTileM - 1) / kTileM;
     long long best = -1;
     for (int bn = 256; bn >= 32; bn -= 32) {
-      const long long tiles = tm * ((n + bn - 1) / bn);
+      const long long tiles = tm * ((n + bn - 1) / bn) * (fold ? 1 : splits);
       const long long cost = ((tiles + 147) / 148) * (2 * bn > 128 + bn ? 2 * bn : 128 + bn);
       if (best < 0 || cost < best) {
         best = cost;
@@ -1038,7 +1041,7 @@ SB_EXPORT int sb_gemm_tc(const void* x, int64_t ldx, const void* w, int64_t ldw,
                    static_cast<size_t>(p.stages) * wide_stage + 1024, stream, ww, wx, p);
     return sb::check_launch("sb_gemm_tc");
   }
-  if (n > 256 && epilogue != kAdd) {
+  if (n > 256 && epilogue != kAdd && (splits == 1 || fold)) {
     // Pairs of CTAs: tiles of 256 weight rows (or 128 gate + 128 up rows) by BN tokens, BN chosen by whole waves of 74 pairs.
     const long long tm = epilogue == kSwiglu ? (half_rows + 127) / 128 : (M + 255) / 256;
     long long best = -1;

@@ -9,6 +9,7 @@ SB_DEFINE_LAST_ERROR()
 namespace {
 
 using bf16 = __nv_bfloat16;
+constexpr int kRowsKernelMin = 1536;   // more rows than this, and no partial sums: the warp-per-row kernel
 
 // ------------------------------------------------------------------ rmsnorm
 // One block per row. The row is h + (partial_0 + partial_1 + ...), the partials summed left to
@@ -189,7 +190,9 @@ SB_EXPORT int sb_rmsnorm(float* h, const float* partials, int n_partials, int64_
   const bool vec = H % 4 == 0 && partial_stride % 4 == 0 && ((reinterpret_cast<uintptr_t>(h) | reinterpret_cast<uintptr_t>(partials)) & 15) == 0;
   const int units = vec ? H / 4 : H;
   const int threads = units >= 1024 ? 1024 : units >= 512 ? 512 : units >= 256 ? 256 : 128;
-  if (vec && n > 64 && ((reinterpret_cast<uintptr_t>(out) | reinterpret_cast<uintptr_t>(weight)) & 15) == 0) {
+  // (a block per row is the faster of the two up to about 1,500 rows, and whenever partial sums are to be added:
+  // measured at H = 2048, 256 rows: 2.9 us against 9.7 us; 2,048 rows: 19.4 against 18.7)
+  if (vec && n > kRowsKernelMin && n_partials <= 1 && ((reinterpret_cast<uintptr_t>(out) | reinterpret_cast<uintptr_t>(weight)) & 15) == 0) {
     // the warp-per-row kernel adds the squares in the order of the block-per-row kernel with `threads` threads
     const dim3 grid((n + 1) / 2);
 #define SB_ROWS_J(TO, W, JT) \

@@ -411,20 +411,23 @@ def test_rmsnorm_with_partials(n, H):
 
 @pytest.mark.parametrize("H", [64, 264, 1024, 2048, 3072, 4096, 8192])
 def test_rmsnorm_does_not_depend_on_the_batch(H):
-    """A row's normed values have the same bits in a step of 3 rows (one block per row) and of 300 (one warp per row)."""
+    """A row's normed values have the same bits in a step of 3 rows and of 300 (one block per row) and of 1,700 (one warp
+    per row, which takes over for many rows with at most one partial sum to add), and with two partial sums at 3 or 300."""
     from stride_b200.kernels import ops
-    h = _rand(300, H, seed=4, scale=3.0)
-    parts = _rand(2, 300, H, seed=5)
+    N = 1700
+    h = _rand(N, H, seed=4, scale=3.0)
+    parts = _rand(2, N, H, seed=5)
     w = _rand(H, seed=6, dtype=torch.bfloat16)
     for out_dtype in (torch.float32, torch.bfloat16):
-        outs = []
-        for n in (3, 64, 65, 300):
-            hh = h[:n].clone()
-            out = torch.zeros(n, H, dtype=out_dtype, device=DEV)
-            ops.rmsnorm(hh, w, 1e-5, out, partials=parts[:, :n].contiguous())
-            outs.append(out[:3].clone())
-        for other in outs[1:]:
-            assert torch.equal(outs[0], other)
+        for P, sizes in ((1, (3, 64, 300, N)), (2, (3, 65, 300)), (0, (3, 300, N))):
+            outs = []
+            for n in sizes:
+                hh = h[:n].clone()
+                out = torch.zeros(n, H, dtype=out_dtype, device=DEV)
+                ops.rmsnorm(hh, w, 1e-5, out, partials=parts[:P, :n].contiguous() if P else None)
+                outs.append(out[:3].clone())
+            for other in outs[1:]:
+                assert torch.equal(outs[0], other)
 
 
 def test_embed_swiglu_gather():
