@@ -989,6 +989,10 @@ SB_EXPORT int sb_gemm_tc(const void* x, int64_t ldx, const void* w, int64_t ldw,
       }
     }
   }
+  // K ranges on CTAs of their own and more than 256 tokens: each tile's K loop is short (4 to 15 steps at the 1B
+  // sizes), so a tile is mostly pipeline fill and epilogue; tiles of 64 tokens run three CTAs an SM, which hides that
+  // (measured, 384 tokens: [2048, 2048] 12.2 us against 21.5, [3072, 2048] 13.7 against 22.9, [2048, 8192] 22.2 against 27.9).
+  if (!fold && splits > 1 && n > 256) p.block_n = 64;
   const int stage_bytes = kStageA + p.block_n * 128;
   p.stages = min(kMaxStages, kSmemBudget / stage_bytes);
   {
@@ -1048,8 +1052,11 @@ SB_EXPORT int sb_gemm_tc(const void* x, int64_t ldx, const void* w, int64_t ldw,
     int bn_best = 256;
     // (narrower tiles bring more bytes from L2 for the same products, which is what bounds a large product: only a
     // step of fewer than 1,024 tokens is cut into narrower tiles to fill its rounds)
-    for (int bn = 256; bn >= (n >= 1024 ? 256 : 128); bn -= 32) {
-      const long long cost = ((tm * ((n + bn - 1) / bn) + 73) / 74) * bn;
+    for (int bn = 256; bn >= 128; bn -= 32) {
+      // cycles of a K step of 64: the tensor cores (2 BN), or the bytes a CTA takes in (16 KB of weights and its half
+      // of the token tile) at about 51 bytes a cycle; times whole rounds of 74 pairs
+      const long long step = max(2ll * bn, (16384ll + 64 * bn) / 51);
+      const long long cost = ((tm * ((n + bn - 1) / bn) + 73) / 74) * step;
       if (best < 0 || cost < best) {
         best = cost;
         bn_best = bn;

@@ -23,13 +23,20 @@ L2_BYTES = 126 << 20
 
 
 def _time(fn, reps: int, warmup: int = 3) -> float:
+    """Microseconds per call of `fn`, its `reps` calls recorded in a CUDA graph and replayed, so that short kernels
+    are not timed by the host's launches."""
     for _ in range(warmup):
         fn()
     torch.cuda.synchronize()
+    graph = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(graph):
+        for _ in range(reps):
+            fn()
+    graph.replay()
+    torch.cuda.synchronize()
     start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     start.record()
-    for _ in range(reps):
-        fn()
+    graph.replay()
     stop.record()
     torch.cuda.synchronize()
     return start.elapsed_time(stop) * 1e3 / reps      # microseconds
