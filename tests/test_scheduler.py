@@ -166,3 +166,71 @@ def test_batch_order_shuffle_changes_nothing():
     solo = _solo()
     outs, _ = _run(FakeEngine(), PROMPTS, opts=SchedulerOptions(max_seqs=4, max_rows=9, prefill_chunk=3, row_shuffle_seed=5))
     assert [o["tokens"] for o in outs] == [o["tokens"] for o in solo]
+
+
+@pytest.mark.parametrize("seed", range(8))
+def test_native_planner_decisions_under_random_states(seed):
+    """The planner in csrc/runtime.cpp against its rules restated here, over random sets of running requests: decoded
+    tokens first, then portions in running order, under the budget; pages ensured when it says run; the youngest named
+    when pages are short; drain while a step is in flight; too small when one request alone does not fit."""
+    import ctypes
+    import random
+
+    import numpy as np
+    rng = random.Random(seed)
+    page = rng.choice([2, 4, 8])
+    eng = FakeEngine(pages=rng.choice([6, 12, 40]), page_size=page, max_slots=8, max_rows=64, max_context=64)
+    sched = Scheduler(eng, SchedulerOptions(max_seqs=8, max_rows=rng.choice([4, 9, 32]), prefill_chunk=rng.choice([2, 5, 16])),
+                      sampler=HashSampler())
+    cache, lib, buf = eng.cache, sched._lib, sched._buf
+    for _ in range(60):
+        while cache.live_slots:
+            cache.release_slot(next(iter(cache.live_slots)))
+        n = rng.randint(1, 6)
+        slots = [cache.acquire_slot() for _ in range(n)]
+        total = [rng.randint(1, 40) for _ in range(n)]
+        nxt = []
+        for s, t in zip(slots, total):
+            done = rng.choice([0, 0, t - 1, rng.randint(0, t - 1)])
+            if not cache.ensure(s, done):
+                done = 0
+            nxt.append(done)
+        closing = [rng.random() < 0.15 for _ in range(n)]
+        inflight = [rng.random() < 0.1 for _ in range(n)]
+        arrival = rng.sample(range(100), n)
+        buf.slot[:n], buf.next_pos[:n], buf.total[:n] = slots, nxt, total
+        buf.closing[:n], buf.inflight[:n], buf.arrival[:n] = closing, inflight, arrival
+        free_before = cache.free_pages()[0]
+        held = {i: -(-int(cache.length[slots[i]]) // page) for i in range(n)}      # pages each request has
+        result = lib.sb_sched_plan(cache._pool, n, buf.slot_p, buf.next_pos_p, buf.total_p, buf.closing_p, buf.inflight_p,
+                                   buf.arrival_p, sched.opts.max_rows, sched.opts.prefill_chunk, buf.out_index_p,
+                                   buf.out_count_p, ctypes.byref(buf.out_n))
+        # the rules, restated
+        budget, want = sched.opts.max_rows, []
+        for i in range(n):
+            if total[i] - nxt[i] == 1 and not closing[i] and budget > 0:
+                want.append((i, 1))
+                budget -= 1
+        for i in range(n):
+            rem = total[i] - nxt[i]
+            if rem > 1 and not closing[i] and budget > 0:
+                c = min(rem, sched.opts.prefill_chunk, budget)
+                want.append((i, c))
+                budget -= c
+        need = sum(max(0, -(-(nxt[i] + c) // page) - held[i]) for i, c in want)
+        if not want:
+            assert result == 1
+        elif need > free_before:
+            if any(inflight):
+                assert result == 2
+            elif n <= 1:
+                assert result == 3
+            else:
+                assert result == 4 and int(buf.out_index[0]) == max(range(n), key=lambda i: arrival[i])
+            assert cache.free_pages()[0] == free_before          # nothing was taken
+        else:
+            m = buf.out_n.value
+            assert result == 0 and list(zip(buf.out_index[:m].tolist(), buf.out_count[:m].tolist())) == want
+            assert cache.free_pages()[0] == free_before - need
+            assert all(cache.length[slots[i]] >= nxt[i] + c for i, c in want)
+        cache.check()
