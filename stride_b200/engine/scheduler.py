@@ -303,7 +303,9 @@ class Scheduler:
 
     # ------------------------------------------------------------------ pipelined running
     def _can_pipeline(self) -> bool:
-        return isinstance(self._sampler, Sampler) and getattr(self.engine, "sampled", None) is not None
+        """Pipelining needs a sampler with `launch` / `collect` that leaves every row's token where the next step's
+        embedding finds it (it says so with `pipelined = True`), and an engine that keeps such a table."""
+        return bool(getattr(self._sampler, "pipelined", False)) and getattr(self.engine, "sampled", None) is not None
 
     def _launch(self):
         """Queue one step on the GPU without waiting for its tokens: rows whose input token is not known yet (it is
@@ -379,7 +381,7 @@ class Scheduler:
                     if s.inflight == 0:
                         self._finish(s)                      # else its slot is given back when the surplus step is read
         windowed = any(g.window > 0 for g in cache.groups)
-        if ticket is None and windowed:
+        if ticket is None and windowed and getattr(self.engine, "device", None) is not None and str(self.engine.device) != "cpu":
             import torch
             torch.cuda.current_stream().synchronize()      # pages are only given back once the step has run
         if windowed:

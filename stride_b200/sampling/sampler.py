@@ -87,6 +87,8 @@ class Sampler:
     scatter[scatter_index[row]] (the engine's per-request table that the next step's embedding reads).
     """
 
+    pipelined = True     # `launch` leaves tokens where the next step finds them: the scheduler may run a step ahead
+
     def __init__(self, device, max_rows: int):
         self.device = torch.device(device)
         self.max_rows = max_rows

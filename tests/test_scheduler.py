@@ -234,3 +234,111 @@ def test_native_planner_decisions_under_random_states(seed):
             assert cache.free_pages()[0] == free_before - need
             assert all(cache.length[slots[i]] >= nxt[i] + c for i, c in want)
         cache.check()
+
+
+# ---------------------------------------------------------------------------- one step ahead
+class PipeEngine(FakeEngine):
+    """The fake engine with what running a step ahead needs: a table of every slot's last chosen token, which a row
+    whose token is still being chosen (-1) reads, as the embedding kernel does on the device."""
+
+    def __init__(self, **kw):
+        super().__init__(**kw)
+        self.sampled = {}
+        self.logit_slots = []
+        self.placeholders = 0
+
+    def step(self, entries):
+        fixed = []
+        for e in entries:
+            tokens = list(e.tokens)
+            if tokens == [-1]:
+                tokens = [self.sampled[e.slot]]
+                self.placeholders += 1
+            assert all(t >= 0 for t in tokens), "only a single decoded token may be a placeholder"
+            fixed.append(SimpleNamespace(slot=e.slot, first_pos=e.first_pos, tokens=tokens, want=e.want))
+        self.logit_slots = [e.slot for e in fixed for _ in e.want]
+        return super().step(fixed)
+
+
+class PipeSampler(HashSampler):
+    pipelined = True
+
+    def launch(self, logits, params, lengths, scatter_index=None, scatter=None):
+        tokens, values = self.choose(logits, params, lengths)
+        if scatter is not None:
+            for slot, t in zip(scatter_index, tokens):
+                scatter[slot] = t
+        return tokens, values
+
+    def collect(self, ticket):
+        return ticket
+
+
+def _run_ahead(engine, prompts, max_new=12, opts=None, stops=()):
+    sched = Scheduler(engine, opts or SchedulerOptions(max_seqs=8, max_rows=16, prefill_chunk=5), sampler=PipeSampler())
+    assert sched._can_pipeline()
+    outs = [dict(tokens=[], finish=None) for _ in prompts]
+
+    def cb(i):
+        def on_token(ev, logits):
+            if ev.token >= 0:
+                assert ev.index == len(outs[i]["tokens"])
+                outs[i]["tokens"].append(ev.token)
+            if ev.finished:
+                assert outs[i]["finish"] is None
+                outs[i]["finish"] = ev.finish_reason
+        return on_token
+    for i, p in enumerate(prompts):
+        sched.submit(GenRequest(prompt=p, max_new_tokens=max_new, stop_tokens=stops, on_token=cb(i)))
+    sched.run()
+    assert sched.idle()
+    engine.cache.check()
+    assert engine.cache.free_pages() == engine.cache.total_pages()
+    return outs, sched
+
+
+def test_a_step_ahead_gives_the_same_tokens():
+    """The scheduler queues step N + 1 before it has read step N's tokens (rows carry -1 and read the token from the
+    engine's table): same tokens, same finishes, every slot and page given back."""
+    solo = _solo()
+    eng = PipeEngine()
+    outs, sched = _run_ahead(eng, PROMPTS)
+    assert [o["tokens"] for o in outs] == [o["tokens"] for o in solo]
+    assert all(o["finish"] == "length" for o in outs) and eng.placeholders > 0
+    assert sched.stats.generated == 72
+    outs, _ = _run_ahead(PipeEngine(), PROMPTS, opts=SchedulerOptions(max_seqs=4, max_rows=9, prefill_chunk=3, row_shuffle_seed=5))
+    assert [o["tokens"] for o in outs] == [o["tokens"] for o in solo]
+
+
+def test_a_step_ahead_with_stop_tokens_and_short_pools():
+    solo = _solo()
+    # a stop token ends a request whose next row is already queued: that surplus row changes nothing
+    for which in (0, 3, 5):
+        stop = solo[which]["tokens"][4]
+        outs, _ = _run_ahead(PipeEngine(), PROMPTS, stops=(stop,))
+        for o, s in zip(outs, solo):
+            want = s["tokens"][:s["tokens"].index(stop) + 1] if stop in s["tokens"] else s["tokens"]
+            assert o["tokens"] == want and o["finish"] == ("stop" if stop in s["tokens"] else "length")
+    # pages run out: steps in flight are read back first, then the youngest is preempted and replayed
+    eng = PipeEngine(pages=9, page_size=4)
+    outs, sched = _run_ahead(eng, PROMPTS, opts=SchedulerOptions(max_seqs=6, max_rows=16, prefill_chunk=5))
+    assert sched.stats.preemptions > 0
+    assert [o["tokens"] for o in outs] == [o["tokens"] for o in solo]
+    with pytest.raises(EngineError, match="too small for one sequence"):
+        _run_ahead(PipeEngine(pages=3, page_size=4), [list(range(10))], max_new=20, opts=SchedulerOptions(max_seqs=2, max_rows=16, prefill_chunk=16))
+
+
+def test_a_step_ahead_with_cancellation():
+    eng = PipeEngine()
+    sched = Scheduler(eng, SchedulerOptions(max_seqs=4, max_rows=16, prefill_chunk=8), sampler=PipeSampler())
+    flag = threading.Event()
+    got, other = [], []
+    sched.submit(GenRequest(prompt=[1, 2, 3], max_new_tokens=100, cancelled=flag, on_token=lambda ev, l: got.append(ev.token)))
+    sched.submit(GenRequest(prompt=[4, 5], max_new_tokens=30, on_token=lambda ev, l: other.append(ev.token)))
+    sched.run(steps=6)
+    flag.set()
+    sched.run()
+    assert 0 < len(got) < 100 and len(other) == 30 and sched.idle()
+    assert other == _run(FakeEngine(), [[4, 5]], max_new=30)[0][0]["tokens"]
+    eng.cache.check()
+    assert eng.cache.free_pages() == eng.cache.total_pages()
