@@ -6,7 +6,7 @@
 // held by exactly one live slot. Counterpart in arhaamatiq/stride: KvCache (src/kv_cache.cpp:10-92), which has one
 // group, no windows and the same last-in-first-out order.
 //
-// Planner: which tokens the next step runs. Requests with exactly one unprocessed token first (one row each), then
+// Planner and Sched: which tokens the next step runs. Requests with exactly one unprocessed token first (one row each), then
 // portions of prompts in running order, under the token budget; then the page arithmetic of that plan, and what to
 // do when pages run short (wait for steps in flight, preempt the youngest, or fail when one request alone does not
 // fit). Counterpart: Scheduler::Admit / BuildBatch (src/scheduler.cpp:72-304).
@@ -433,4 +433,330 @@ SB_API int sb_sched_plan(void* pool, int n, const int32_t* slot, const int32_t* 
     }
   }
   return kPlanRun;
+}
+
+// ------------------------------------------------------------------ Sched: the requests and their tokens
+//
+// The scheduler's state and rules: every request's tokens, how far they have been run, what has been generated, which
+// requests wait and which run, admission, the plan of a step (with preemption of the youngest when pages are short),
+// and what a chosen token means for its request (stop token, length, fingerprint). The caller drives the engine and
+// the sampler and keeps what cannot live here (callbacks, sampling parameters). Counterpart in arhaamatiq/stride:
+// Scheduler (src/scheduler.cpp:72-304), whose policy this is; running one step ahead is this engine's own.
+namespace {
+
+constexpr uint64_t kFnvOffset = 14695981039346656037ull, kFnvPrime = 1099511628211ull;
+
+uint64_t fnv_mix(uint64_t h, uint32_t v) {
+  for (int i = 0; i < 4; ++i) {
+    h ^= (v >> (i * 8)) & 0xFFu;
+    h *= kFnvPrime;
+  }
+  return h;
+}
+
+// One turn of the batch-order shuffle's generator: the state becomes the mixed value.
+uint64_t mix64(uint64_t x) {
+  x += 0x9E3779B97F4A7C15ull;
+  x = (x ^ (x >> 30)) * 0xBF58476D1CE4E5B9ull;
+  x = (x ^ (x >> 27)) * 0x94D049BB133111EBull;
+  return x ^ (x >> 31);
+}
+
+struct Seq {
+  std::vector<int32_t> tokens;     // prompt, then generated tokens; -1 stands for a token that is being chosen
+  std::vector<int32_t> stops;
+  int prompt_len = 0, next_pos = 0, generated = 0, launched = 0, inflight = 0, slot = -1, max_new = 0;
+  int64_t arrival = 0;
+  uint64_t fingerprint = kFnvOffset;
+  bool closing = false, done = false, cancelled = false, live = false;
+};
+
+struct SchedStats {
+  int64_t steps = 0, rows = 0, generated = 0, preemptions = 0, replayed_rows = 0, peak_seqs = 0, peak_blocks = 0;
+};
+
+struct Sched {
+  Pool* pool = nullptr;
+  int max_seqs = 0, max_rows = 0, prefill_chunk = 0, max_context = 0;
+  uint64_t shuffle_state = 0;
+  bool shuffle = false;
+  std::vector<Seq> seqs;             // by id; ids of finished requests are used again
+  std::vector<int32_t> free_ids;
+  std::vector<int32_t> waiting;      // front = next to be admitted
+  std::vector<int32_t> running;      // in the order of admission
+  int64_t next_arrival = 0;
+  SchedStats stats;
+  // scratch of the planner
+  std::vector<int32_t> a_slot, a_next, a_total, o_index, o_count;
+  std::vector<uint8_t> a_closing, a_inflight;
+  std::vector<int64_t> a_arrival;
+
+  void release(Seq& s) {
+    if (s.slot >= 0) {
+      sb_pool_release_slot(pool, s.slot);
+      s.slot = -1;
+    }
+  }
+  void retire(int id) {       // the request is over and holds nothing: its id may be used again
+    Seq& s = seqs[id];
+    s.live = false;
+    s.tokens.clear();
+    s.tokens.shrink_to_fit();
+    free_ids.push_back(id);
+  }
+  void drop_finished() {
+    size_t k = 0;
+    for (int id : running) {
+      Seq& s = seqs[id];
+      if ((s.done && s.slot < 0) || !s.live) {
+        if (s.live) retire(id);
+      } else {
+        running[k++] = id;
+      }
+    }
+    running.resize(k);
+  }
+};
+
+}  // namespace
+
+SB_API void* sb_sched_create(void* pool, int max_seqs, int max_rows, int prefill_chunk, int max_context, uint64_t row_shuffle_seed) {
+  if (!pool || max_seqs <= 0 || max_rows <= 0 || prefill_chunk <= 0) {
+    g_error = "sb_sched_create: sizes must be positive";
+    return nullptr;
+  }
+  Sched* s = new Sched;
+  s->pool = static_cast<Pool*>(pool);
+  s->max_seqs = max_seqs;
+  s->max_rows = max_rows;
+  s->prefill_chunk = prefill_chunk;
+  s->max_context = max_context;
+  s->shuffle = row_shuffle_seed != 0;
+  s->shuffle_state = row_shuffle_seed;
+  return s;
+}
+
+SB_API void sb_sched_destroy(void* sched) { delete static_cast<Sched*>(sched); }
+
+// Takes a request in. Returns its id (>= 0), -1 for an empty prompt, -2 for a prompt that leaves no room in the
+// context; both refusals use up an arrival number, as an accepted request does.
+SB_API int sb_sched_add(void* sched, const int32_t* prompt, int n, int max_new, const int32_t* stops, int n_stops) {
+  Sched* sc = static_cast<Sched*>(sched);
+  const int64_t arrival = sc->next_arrival++;
+  if (n <= 0) return -1;
+  const int room = sc->max_context - n;
+  if (room <= 0) return -2;
+  int id;
+  if (!sc->free_ids.empty()) {
+    id = sc->free_ids.back();
+    sc->free_ids.pop_back();
+  } else {
+    id = (int)sc->seqs.size();
+    sc->seqs.emplace_back();
+  }
+  Seq& s = sc->seqs[id];
+  s = Seq();
+  s.tokens.assign(prompt, prompt + n);
+  s.stops.assign(stops, stops + n_stops);
+  s.prompt_len = n;
+  s.max_new = std::min(max_new, room);
+  s.arrival = arrival;
+  s.live = true;
+  sc->waiting.push_back(id);
+  return id;
+}
+
+// The request is dropped at the next step (or, while one of its steps is in flight, once that has been read back).
+SB_API void sb_sched_cancel(void* sched, int id) {
+  Sched* sc = static_cast<Sched*>(sched);
+  if (id >= 0 && id < (int)sc->seqs.size() && sc->seqs[id].live) sc->seqs[id].cancelled = true;
+}
+
+// counts[0] = requests waiting, counts[1] = requests running.
+SB_API void sb_sched_counts(void* sched, int32_t* counts) {
+  Sched* sc = static_cast<Sched*>(sched);
+  counts[0] = (int32_t)sc->waiting.size();
+  counts[1] = (int32_t)sc->running.size();
+}
+
+SB_API int sb_sched_queue(void* sched, int which, int32_t* out, int capacity) {
+  Sched* sc = static_cast<Sched*>(sched);
+  const std::vector<int32_t>& q = which == 0 ? sc->waiting : sc->running;
+  for (int i = 0; i < (int)q.size() && i < capacity; ++i) out[i] = q[i];
+  return (int)q.size();
+}
+
+// steps, rows, generated, preemptions, replayed_rows, peak_seqs, peak_blocks
+SB_API void sb_sched_stats(void* sched, int64_t* out) {
+  const SchedStats& t = static_cast<Sched*>(sched)->stats;
+  const int64_t v[7] = {t.steps, t.rows, t.generated, t.preemptions, t.replayed_rows, t.peak_seqs, t.peak_blocks};
+  std::memcpy(out, v, sizeof v);
+}
+
+// Begins a step: drops cancelled requests, admits waiting ones while slots and pages allow, plans the batch under the
+// token budget (preempting the youngest running request while pages are short) and ensures its pages. On kPlanRun the
+// entries are ent_id / ent_slot / ent_first / ent_count / ent_last (last: the entry reaches the request's last known
+// token, so a token is to be chosen for it), their tokens one after another in `tokens` (-1: a token still being
+// chosen), *out_n entries; every request's position has been moved on. Other results leave nothing to run:
+// kPlanNothing, kPlanDrain (the steps in flight have to be read back before a decision can be taken), kPlanTooSmall.
+SB_API int sb_sched_begin_step(void* sched, int32_t* ent_id, int32_t* ent_slot, int32_t* ent_first, int32_t* ent_count,
+                               uint8_t* ent_last, int32_t* tokens, int32_t* out_n) {
+  Sched* sc = static_cast<Sched*>(sched);
+  Pool* pool = sc->pool;
+  *out_n = 0;
+  // cancelled requests: while a step of one is in flight nothing can be given back yet
+  for (int id : sc->running)
+    if (sc->seqs[id].cancelled && sc->seqs[id].inflight > 0) return kPlanDrain;
+  {
+    size_t k = 0;
+    for (int id : sc->running) {
+      Seq& s = sc->seqs[id];
+      if (s.cancelled) {
+        sc->release(s);
+        sc->retire(id);
+      } else {
+        sc->running[k++] = id;
+      }
+    }
+    sc->running.resize(k);
+  }
+  // admission: room for the request's tokens and one page of growth per running request, and a free slot
+  while (!sc->waiting.empty() && (int)sc->running.size() < sc->max_seqs) {
+    const int id = sc->waiting.front();
+    Seq& s = sc->seqs[id];
+    if (s.cancelled) {
+      sc->waiting.erase(sc->waiting.begin());
+      sc->retire(id);
+      continue;
+    }
+    if (!sb_sched_may_admit(pool, (int)sc->running.size(), (int)s.tokens.size())) break;
+    const int slot = sb_pool_acquire_slot(pool);
+    if (slot < 0) break;
+    s.slot = slot;
+    s.next_pos = 0;        // (re)computed from the first token: its pages were given back on preemption
+    sc->waiting.erase(sc->waiting.begin());
+    sc->running.push_back(id);
+  }
+  sc->stats.peak_seqs = std::max<int64_t>(sc->stats.peak_seqs, (int64_t)sc->running.size());
+
+  int m = 0;
+  while (true) {
+    const int n = (int)sc->running.size();
+    if (n == 0) return kPlanNothing;
+    sc->a_slot.resize(n), sc->a_next.resize(n), sc->a_total.resize(n), sc->a_closing.resize(n), sc->a_inflight.resize(n);
+    sc->a_arrival.resize(n), sc->o_index.resize(std::max(n, 1)), sc->o_count.resize(std::max(n, 1));
+    for (int i = 0; i < n; ++i) {
+      const Seq& s = sc->seqs[sc->running[i]];
+      sc->a_slot[i] = s.slot, sc->a_next[i] = s.next_pos, sc->a_total[i] = (int)s.tokens.size();
+      sc->a_closing[i] = s.closing, sc->a_inflight[i] = s.inflight > 0, sc->a_arrival[i] = s.arrival;
+    }
+    int32_t planned = 0;
+    const int r = sb_sched_plan(pool, n, sc->a_slot.data(), sc->a_next.data(), sc->a_total.data(), sc->a_closing.data(),
+                                sc->a_inflight.data(), sc->a_arrival.data(), sc->max_rows, sc->prefill_chunk, sc->o_index.data(),
+                                sc->o_count.data(), &planned);
+    if (r == kPlanPreempt) {
+      // the youngest goes back to the front of the queue and is later recomputed from its first token
+      const int at = sc->o_index[0], id = sc->running[at];
+      Seq& victim = sc->seqs[id];
+      sc->release(victim);
+      sc->stats.preemptions += 1;
+      sc->stats.replayed_rows += victim.next_pos;
+      sc->running.erase(sc->running.begin() + at);
+      sc->waiting.insert(sc->waiting.begin(), id);
+      continue;
+    }
+    if (r != kPlanRun) return r;
+    m = planned;
+    break;
+  }
+  if (sc->shuffle)
+    for (int i = m - 1; i > 0; --i) {
+      sc->shuffle_state = mix64(sc->shuffle_state);
+      const int j = (int)(sc->shuffle_state % (uint64_t)(i + 1));
+      std::swap(sc->o_index[i], sc->o_index[j]);
+      std::swap(sc->o_count[i], sc->o_count[j]);
+    }
+  int at = 0;
+  for (int j = 0; j < m; ++j) {
+    const int id = sc->running[sc->o_index[j]], count = sc->o_count[j];
+    Seq& s = sc->seqs[id];
+    ent_id[j] = id, ent_slot[j] = s.slot, ent_first[j] = s.next_pos, ent_count[j] = count;
+    ent_last[j] = s.next_pos + count == (int)s.tokens.size();
+    std::memcpy(tokens + at, s.tokens.data() + s.next_pos, sizeof(int32_t) * count);
+    at += count;
+    s.next_pos += count;
+  }
+  *out_n = m;
+  sc->stats.steps += 1;
+  sc->stats.rows += at;
+  int64_t used = 0;
+  for (const Group& g : pool->groups) used = std::max<int64_t>(used, (int64_t)g.num_pages - (int64_t)g.free.size());
+  sc->stats.peak_blocks = std::max(sc->stats.peak_blocks, used);
+  return kPlanRun;
+}
+
+// The tokens of these requests are being chosen by a step that was queued without waiting for them: each gets a
+// placeholder; a request whose last token (by its limit) this is takes part in no further step.
+SB_API void sb_sched_launched(void* sched, const int32_t* ids, int n) {
+  Sched* sc = static_cast<Sched*>(sched);
+  for (int i = 0; i < n; ++i) {
+    Seq& s = sc->seqs[ids[i]];
+    s.tokens.push_back(-1);
+    s.inflight += 1;
+    s.launched += 1;
+    if (s.launched >= s.max_new) s.closing = true;
+  }
+}
+
+// The chosen tokens (and their logits) of requests ids[0..n): ahead = 0, the step was waited for: the token is
+// appended; ahead = 1, the step had been queued ahead (sb_sched_launched): the token takes the place of the
+// request's oldest placeholder, and a request that a stop token finished a step ago ignores its surplus row.
+// Per row: kind 0 = ignored, 1 = a token, 2 = a token that stops the request, 3 = a token that reaches its limit;
+// the token's index among the generated ones and the fingerprint (FNV-1a over token and logit bits) so far.
+// A finished request gives its slot and pages back as soon as none of its steps is in flight.
+SB_API void sb_sched_commit(void* sched, int ahead, const int32_t* ids, const int32_t* tokens, const float* values, int n,
+                            uint8_t* kind, int32_t* index, uint64_t* fingerprint) {
+  Sched* sc = static_cast<Sched*>(sched);
+  for (int i = 0; i < n; ++i) {
+    Seq& s = sc->seqs[ids[i]];
+    kind[i] = 0, index[i] = 0, fingerprint[i] = s.fingerprint;
+    if (ahead) {
+      s.inflight -= 1;
+      if (s.done) {                                   // finished by a stop token a step ago: this row was surplus
+        if (s.inflight == 0) sc->release(s);
+        continue;
+      }
+    }
+    const int32_t tok = tokens[i];
+    uint32_t bits;
+    std::memcpy(&bits, &values[i], sizeof bits);
+    s.fingerprint = fnv_mix(fnv_mix(s.fingerprint, (uint32_t)tok), bits);
+    if (ahead) s.tokens[s.prompt_len + s.generated] = tok;   // the oldest placeholder
+    else s.tokens.push_back(tok);
+    s.generated += 1;
+    sc->stats.generated += 1;
+    index[i] = s.generated - 1;
+    fingerprint[i] = s.fingerprint;
+    kind[i] = 1;
+    if (std::find(s.stops.begin(), s.stops.end(), tok) != s.stops.end()) kind[i] = 2;
+    else if (s.generated >= s.max_new) kind[i] = 3;
+    if (kind[i] >= 2) {
+      s.done = s.closing = true;
+      if (!ahead || s.inflight == 0) sc->release(s);   // else its slot goes back when the surplus step is read
+    }
+  }
+}
+
+// Ends a step that has finished on the GPU: windowed groups give back the pages behind the window of the requests
+// that ran (ids with the position each had reached, or end < 0 for all its tokens), finished requests leave.
+SB_API void sb_sched_end_step(void* sched, const int32_t* ids, const int32_t* ends, int n) {
+  Sched* sc = static_cast<Sched*>(sched);
+  bool windowed = false;
+  for (const Group& g : sc->pool->groups) windowed |= g.window > 0;
+  if (windowed)
+    for (int i = 0; i < n; ++i) {
+      const Seq& s = sc->seqs[ids[i]];
+      if (s.live && s.slot >= 0 && !s.done) sb_pool_trim(sc->pool, s.slot, ends[i]);
+    }
+  sc->drop_finished();
 }

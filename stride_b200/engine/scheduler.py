@@ -10,10 +10,11 @@ alike) and plan again; run the batch through `Engine.step`; choose a token for e
 request whose last known token was in the batch; finish on a stop token ("stop") or on
 max_new_tokens ("length") and give slot and pages back.
 
-The decisions (the admission rule, the plan under the budget, the page arithmetic and the
-choice of what to do when pages are short) are taken by the native planner in
-`csrc/runtime.cpp`, on the books of the native page pool; this module keeps the requests,
-their tokens and callbacks, and drives the engine and the sampler.
+The requests' tokens and state, admission, the plan under the budget with its page
+arithmetic and preemption, and what a chosen token means for its request (stop token, length,
+fingerprint) live in the native `Sched` of `csrc/runtime.cpp`, on the books of the native page
+pool; this module keeps what cannot live there (callbacks, sampling parameters, cancellation
+flags) and drives the engine and the sampler, one step ahead of the tokens where it can.
 
 This restates arhaamatiq/stride's Scheduler (src/scheduler.cpp:72-304) including its
 admission rule (free pages >= pages of the prompt + one page of growth per running request
@@ -31,24 +32,8 @@ from typing import Callable, Optional
 
 import numpy as np
 
-from ..sampling.sampler import Sampler, SamplingParams, splitmix64
+from ..sampling.sampler import Sampler, SamplingParams
 from .engine import Engine, EngineError, StepEntry
-
-_FNV_OFFSET = 14695981039346656037
-_FNV_PRIME = 1099511628211
-_MASK = (1 << 64) - 1
-
-
-def _fnv_mix(h: int, v: int) -> int:
-    for i in range(4):
-        h ^= (v >> (i * 8)) & 0xFF
-        h = (h * _FNV_PRIME) & _MASK
-    return h
-
-
-def _float_bits(v: float) -> int:
-    return int(np.float32(v).view(np.uint32))
-
 
 @dataclass
 class TokenEvent:
@@ -90,42 +75,56 @@ class SchedulerStats:
     peak_blocks: int = 0
 
 
-class _Seq:
-    __slots__ = ("req", "tokens", "prompt_len", "next_pos", "generated", "slot", "arrival", "fingerprint", "done",
-                 "inflight", "launched", "closing")
-
-    def __init__(self, req: GenRequest, arrival: int):
-        self.req = req
-        self.tokens = list(req.prompt)
-        self.prompt_len = len(self.tokens)
-        self.next_pos = 0
-        self.generated = 0
-        self.slot = -1
-        self.arrival = arrival
-        self.fingerprint = _FNV_OFFSET
-        self.done = False
-        self.inflight = 0       # pipelined mode: steps launched for this request whose tokens the host has not read yet
-        self.launched = 0       # tokens whose sampling has been launched (>= generated)
-        self.closing = False    # no further step is to be launched for it (it finishes with a token already launched)
-
-
-_DRAIN = object()      # plan(): the steps in flight have to be read back before a decision can be taken
-_PLAN_RUN, _PLAN_NOTHING, _PLAN_DRAIN, _PLAN_TOO_SMALL, _PLAN_PREEMPT = range(5)    # results of sb_sched_plan
+_DRAIN = object()      # the steps in flight have to be read back before a decision can be taken
+_PLAN_RUN, _PLAN_NOTHING, _PLAN_DRAIN, _PLAN_TOO_SMALL, _PLAN_PREEMPT = range(5)    # results of the native planner
 _I32P, _U8P, _I64P = ctypes.POINTER(ctypes.c_int32), ctypes.POINTER(ctypes.c_uint8), ctypes.POINTER(ctypes.c_int64)
+_U64P, _F32P = ctypes.POINTER(ctypes.c_uint64), ctypes.POINTER(ctypes.c_float)
+_FINISH = {2: "stop", 3: "length"}
 
 
-class _PlanBuffers:
-    """Arrays the native planner reads (one row per running request) and writes (the plan)."""
-    FIELDS = (("slot", np.int32, _I32P), ("next_pos", np.int32, _I32P), ("total", np.int32, _I32P), ("closing", np.uint8, _U8P),
-              ("inflight", np.uint8, _U8P), ("arrival", np.int64, _I64P), ("out_index", np.int32, _I32P), ("out_count", np.int32, _I32P))
+class _Buffers:
+    """Named numpy arrays with their ctypes pointers (`name_p`)."""
+    POINTERS = {np.int32: _I32P, np.uint8: _U8P, np.int64: _I64P, np.uint64: _U64P, np.float32: _F32P}
 
-    def __init__(self, capacity: int):
+    def __init__(self, capacity: int, fields):
         self.capacity = capacity
-        self.out_n = ctypes.c_int32(0)
-        for name, dtype, ptr in self.FIELDS:
+        for name, dtype in fields:
             arr = np.zeros(capacity, dtype=dtype)
             setattr(self, name, arr)
-            setattr(self, name + "_p", arr.ctypes.data_as(ptr))
+            setattr(self, name + "_p", arr.ctypes.data_as(self.POINTERS[dtype]))
+
+
+class _PlanBuffers(_Buffers):
+    """Arrays the native planner `sb_sched_plan` reads (one row per running request) and writes (the plan)."""
+
+    def __init__(self, capacity: int):
+        super().__init__(capacity, (("slot", np.int32), ("next_pos", np.int32), ("total", np.int32), ("closing", np.uint8),
+                                    ("inflight", np.uint8), ("arrival", np.int64), ("out_index", np.int32), ("out_count", np.int32)))
+        self.out_n = ctypes.c_int32(0)
+
+
+def native_scheduler(lib):
+    """The runtime library with the scheduler's functions typed."""
+    if not getattr(lib, "_sb_sched_typed", False):
+        vp, ci = ctypes.c_void_p, ctypes.c_int
+        lib.sb_sched_may_admit.restype, lib.sb_sched_may_admit.argtypes = ci, [vp, ci, ci]
+        lib.sb_sched_plan.restype = ci
+        lib.sb_sched_plan.argtypes = [vp, ci, _I32P, _I32P, _I32P, _U8P, _U8P, _I64P, ci, ci, _I32P, _I32P, ctypes.POINTER(ctypes.c_int32)]
+        lib.sb_sched_create.restype, lib.sb_sched_create.argtypes = vp, [vp, ci, ci, ci, ci, ctypes.c_uint64]
+        lib.sb_sched_destroy.restype, lib.sb_sched_destroy.argtypes = None, [vp]
+        lib.sb_sched_add.restype, lib.sb_sched_add.argtypes = ci, [vp, _I32P, ci, ci, _I32P, ci]
+        lib.sb_sched_cancel.restype, lib.sb_sched_cancel.argtypes = None, [vp, ci]
+        lib.sb_sched_counts.restype, lib.sb_sched_counts.argtypes = None, [vp, _I32P]
+        lib.sb_sched_queue.restype, lib.sb_sched_queue.argtypes = ci, [vp, ci, _I32P, ci]
+        lib.sb_sched_stats.restype, lib.sb_sched_stats.argtypes = None, [vp, _I64P]
+        lib.sb_sched_begin_step.restype = ci
+        lib.sb_sched_begin_step.argtypes = [vp, _I32P, _I32P, _I32P, _I32P, _U8P, _I32P, ctypes.POINTER(ctypes.c_int32)]
+        lib.sb_sched_launched.restype, lib.sb_sched_launched.argtypes = None, [vp, _I32P, ci]
+        lib.sb_sched_commit.restype = None
+        lib.sb_sched_commit.argtypes = [vp, ci, _I32P, _I32P, _F32P, ci, _U8P, _I32P, _U64P]
+        lib.sb_sched_end_step.restype, lib.sb_sched_end_step.argtypes = None, [vp, _I32P, _I32P, ci]
+        lib._sb_sched_typed = True
+    return lib
 
 
 class Scheduler:
@@ -134,24 +133,30 @@ class Scheduler:
         self.opts = options or SchedulerOptions()
         if self.opts.max_rows > engine.options.max_rows:
             raise EngineError(f"scheduler max_rows {self.opts.max_rows} exceeds the engine's {engine.options.max_rows}")
-        self.stats = SchedulerStats()
         self._mu = threading.Lock()
         self._incoming: deque = deque()
-        self._waiting: deque = deque()
-        self._running: list = []
-        self._arrival = 0
-        self._rng_state = self.opts.row_shuffle_seed
+        self._requests: dict = {}          # native id -> GenRequest of every request that waits or runs
         self._sampler = sampler or Sampler(engine.device, engine.env.max_logit_rows)
-        lib = self._lib = engine.cache._lib
-        if not getattr(lib, "_sb_sched_typed", False):
-            lib.sb_sched_may_admit.restype, lib.sb_sched_may_admit.argtypes = ctypes.c_int, [ctypes.c_void_p, ctypes.c_int, ctypes.c_int]
-            lib.sb_sched_plan.restype = ctypes.c_int
-            lib.sb_sched_plan.argtypes = [ctypes.c_void_p, ctypes.c_int, _I32P, _I32P, _I32P, _U8P, _U8P, _I64P, ctypes.c_int, ctypes.c_int,
-                                          _I32P, _I32P, ctypes.POINTER(ctypes.c_int32)]
-            lib._sb_sched_typed = True
-        self._buf = _PlanBuffers(max(self.opts.max_seqs, 1))
+        self._lib = native_scheduler(engine.cache._lib)
+        self._sched = self._lib.sb_sched_create(engine.cache._pool, self.opts.max_seqs, self.opts.max_rows, self.opts.prefill_chunk,
+                                                engine.max_context, self.opts.row_shuffle_seed)
+        if not self._sched:
+            raise EngineError(self._lib.sb_last_error().decode())
+        rows = max(self.opts.max_rows, 1)
+        self._plan = _Buffers(rows, (("id", np.int32), ("slot", np.int32), ("first", np.int32), ("count", np.int32), ("last", np.uint8),
+                                     ("tokens", np.int32)))
+        self._plan_n = ctypes.c_int32(0)
+        self._rows = _Buffers(rows, (("id", np.int32), ("token", np.int32), ("value", np.float32), ("kind", np.uint8), ("index", np.int32),
+                                     ("fingerprint", np.uint64), ("end", np.int32)))
+        self._counts = np.zeros(2, dtype=np.int32)
+        self._stats = np.zeros(7, dtype=np.int64)
 
-    # ------------------------------------------------------------------ intake
+    def __del__(self):
+        sched, self._sched = getattr(self, "_sched", None), None
+        if sched:
+            self._lib.sb_sched_destroy(sched)
+
+    # ------------------------------------------------------------------ intake and views
     def submit(self, request: GenRequest) -> None:
         """Thread-safe."""
         with self._mu:
@@ -159,146 +164,132 @@ class Scheduler:
 
     def idle(self) -> bool:
         with self._mu:
-            return not (self._incoming or self._waiting or self._running)
+            if self._incoming:
+                return False
+        self._lib.sb_sched_counts(self._sched, self._counts.ctypes.data_as(_I32P))
+        return not self._counts.any()
 
-    def _finish(self, seq: _Seq) -> None:
-        seq.done = True
-        if seq.slot >= 0:
-            self.engine.cache.release_slot(seq.slot)
-            seq.slot = -1
+    @property
+    def stats(self) -> SchedulerStats:
+        self._lib.sb_sched_stats(self._sched, self._stats.ctypes.data_as(_I64P))
+        return SchedulerStats(*(int(v) for v in self._stats))
 
-    def _admit(self) -> None:
-        cache = self.engine.cache
-        capacity = self.engine.max_context
+    def _queue(self, which: int) -> list:
+        buf = np.zeros(self.opts.max_seqs + len(self._requests) + 1, dtype=np.int32)
+        n = self._lib.sb_sched_queue(self._sched, which, buf.ctypes.data_as(_I32P), buf.size)
+        return buf[:n].tolist()
+
+    @property
+    def _waiting(self) -> list:
+        """Ids of the requests that wait, the next to be admitted first."""
+        return self._queue(0)
+
+    @property
+    def _running(self) -> list:
+        """Ids of the requests that run, in the order of admission."""
+        return self._queue(1)
+
+    def _intake(self) -> None:
+        """Hands new requests to the native scheduler and tells it which requests were cancelled."""
         with self._mu:
-            while self._incoming:
-                seq = _Seq(self._incoming.popleft(), self._arrival)
-                self._arrival += 1
-                room = capacity - seq.prompt_len
-                if room <= 0 or seq.prompt_len == 0:
-                    if seq.req.on_token:
-                        seq.req.on_token(TokenEvent(finished=True, finish_reason="empty_prompt" if seq.prompt_len == 0
-                                                    else "context_length"), None)
-                    continue
-                seq.req.max_new_tokens = min(seq.req.max_new_tokens, room)
-                self._waiting.append(seq)
-        while self._waiting and len(self._running) < self.opts.max_seqs:
-            nxt = self._waiting[0]
-            if nxt.req.cancelled is not None and nxt.req.cancelled.is_set():
-                self._waiting.popleft()
+            incoming, self._incoming = list(self._incoming), deque()
+        for req in incoming:
+            prompt = np.asarray(req.prompt, dtype=np.int32).reshape(-1)
+            stops = np.asarray(tuple(req.stop_tokens), dtype=np.int32).reshape(-1)
+            rid = self._lib.sb_sched_add(self._sched, prompt.ctypes.data_as(_I32P), prompt.size, int(req.max_new_tokens),
+                                         stops.ctypes.data_as(_I32P), stops.size)
+            if rid < 0:
+                if req.on_token:
+                    req.on_token(TokenEvent(finished=True, finish_reason="empty_prompt" if rid == -1 else "context_length"), None)
                 continue
-            # Room for its tokens and one page of growth per running request, and a free slot.
-            if not self._lib.sb_sched_may_admit(cache._pool, len(self._running), len(nxt.tokens)):
-                break
-            slot = cache.acquire_slot()
-            if slot < 0:
-                break
-            nxt.slot = slot
-            nxt.next_pos = 0        # (re)computed from the first token: its pages were given back on preemption
-            self._running.append(self._waiting.popleft())
-        self.stats.peak_seqs = max(self.stats.peak_seqs, len(self._running))
+            self._requests[rid] = req
+        for rid, req in list(self._requests.items()):
+            if req.cancelled is not None and req.cancelled.is_set():
+                self._lib.sb_sched_cancel(self._sched, rid)
+                del self._requests[rid]
 
-    def _preempt(self, victim: _Seq) -> None:
-        self.engine.cache.release_slot(victim.slot)
-        victim.slot = -1
-        self.stats.preemptions += 1
-        self.stats.replayed_rows += victim.next_pos
-        self._running.remove(victim)
-        self._waiting.appendleft(victim)
+    # ------------------------------------------------------------------ the parts of a step
+    def _begin(self):
+        """The next step's entries, or None (nothing to run) or _DRAIN. Returns (entries, ids of the requests a token is
+        to be chosen for, number of entries); the plan's arrays keep the ids and positions."""
+        self._intake()
+        p = self._plan
+        result = self._lib.sb_sched_begin_step(self._sched, p.id_p, p.slot_p, p.first_p, p.count_p, p.last_p, p.tokens_p,
+                                               ctypes.byref(self._plan_n))
+        if result == _PLAN_NOTHING:
+            return None
+        if result == _PLAN_DRAIN:
+            return _DRAIN
+        if result == _PLAN_TOO_SMALL:
+            raise EngineError("the cache pool is too small for one sequence")
+        if result != _PLAN_RUN:
+            raise EngineError(self._lib.sb_last_error().decode())
+        m = self._plan_n.value
+        ids, slots, firsts, counts, lasts = (a[:m].tolist() for a in (p.id, p.slot, p.first, p.count, p.last))
+        tokens = p.tokens[:sum(counts)].tolist()
+        entries, wanted, at = [], [], 0
+        for rid, slot, first, count, last in zip(ids, slots, firsts, counts, lasts):
+            entries.append(StepEntry(slot=slot, first_pos=first, tokens=tokens[at:at + count], want=[count - 1] if last else []))
+            if last:
+                wanted.append(rid)
+            at += count
+        ends = (ids, [f + c for f, c in zip(firsts, counts)])
+        return entries, wanted, ends
 
-    def _check_kernels(self, tokens) -> None:
-        """The step's tokens are on the host. The sampling kernels report -1 - code instead of a token when a wait
-        inside one of the step's tensor-core kernels gave up: that is an error, not a token."""
+    def _commit(self, ahead: bool, wanted: list, tokens, values, full) -> None:
+        """Hands the chosen tokens to the native scheduler and tells the requests what it made of them."""
+        n = len(wanted)
         worst = min((int(t) for t in tokens), default=0)
         if worst < 0:
+            # the sampling kernels report -1 - code instead of a token when a wait inside one of the step's tensor-core
+            # kernels gave up: that is an error, not a token
             self.engine.check_kernels(-1 - worst)
             raise EngineError(f"the sampler returned {worst} instead of a token")
-
-    # ------------------------------------------------------------------ planning
-    def plan(self):
-        """[(sequence, tokens to run)] for the next step, pages ensured; None if nothing is to run."""
-        cache, buf = self.engine.cache, self._buf
-        while True:
-            n = len(self._running)
-            if n == 0:
-                return None
-            run = self._running
-            buf.slot[:n], buf.next_pos[:n], buf.total[:n] = [s.slot for s in run], [s.next_pos for s in run], [len(s.tokens) for s in run]
-            buf.closing[:n], buf.inflight[:n] = [s.closing for s in run], [s.inflight > 0 for s in run]
-            buf.arrival[:n] = [s.arrival for s in run]
-            result = self._lib.sb_sched_plan(cache._pool, n, buf.slot_p, buf.next_pos_p, buf.total_p, buf.closing_p, buf.inflight_p,
-                                             buf.arrival_p, self.opts.max_rows, self.opts.prefill_chunk, buf.out_index_p,
-                                             buf.out_count_p, ctypes.byref(buf.out_n))
-            if result == _PLAN_NOTHING:
-                return None
-            if result == _PLAN_DRAIN:
-                return _DRAIN           # pages of a request with a step in flight cannot be taken away yet
-            if result == _PLAN_TOO_SMALL:
-                raise EngineError("the cache pool is too small for one sequence")
-            if result == _PLAN_PREEMPT:
-                self._preempt(self._running[int(buf.out_index[0])])     # the youngest; then plan again
+        r = self._rows
+        r.id[:n], r.token[:n], r.value[:n] = wanted, tokens, values
+        self._lib.sb_sched_commit(self._sched, 1 if ahead else 0, r.id_p, r.token_p, r.value_p, n, r.kind_p, r.index_p, r.fingerprint_p)
+        kinds, indices, prints = r.kind[:n].tolist(), r.index[:n].tolist(), r.fingerprint[:n].tolist()
+        for i, rid in enumerate(wanted):
+            kind = kinds[i]
+            req = self._requests.get(rid)
+            if kind == 0 or req is None:          # a surplus row, or a request that was cancelled meanwhile
                 continue
-            if result != _PLAN_RUN:
-                raise EngineError(self._lib.sb_last_error().decode())
-            m = buf.out_n.value
-            plan = [(self._running[i], c) for i, c in zip(buf.out_index[:m].tolist(), buf.out_count[:m].tolist())]
-            if self.opts.row_shuffle_seed:
-                for i in range(len(plan) - 1, 0, -1):
-                    self._rng_state = splitmix64(self._rng_state)
-                    j = self._rng_state % (i + 1)
-                    plan[i], plan[j] = plan[j], plan[i]
-            return plan
+            if kind >= 2:
+                del self._requests[rid]
+            if req.on_token:
+                ev = TokenEvent(token=int(tokens[i]), value=float(values[i]), index=indices[i], fingerprint=prints[i],
+                                finished=kind >= 2, finish_reason=_FINISH.get(kind))
+                req.on_token(ev, full[i] if (full is not None and req.full_logits) else None)
+
+    def _end(self, ends, whole: bool) -> None:
+        ids, positions = ends
+        n = len(ids)
+        r = self._rows
+        r.id[:n] = ids
+        r.end[:n] = -1 if whole else positions
+        self._lib.sb_sched_end_step(self._sched, r.id_p, r.end_p, n)
+
+    def _full_logits(self, wanted: list, logits):
+        if any(self._requests[rid].full_logits and self._requests[rid].on_token for rid in wanted if rid in self._requests):
+            return logits.to("cpu").numpy()
+        return None
 
     # ------------------------------------------------------------------ one step
     def step(self) -> bool:
-        """Run one engine step. False when nothing is queued or running."""
-        cache = self.engine.cache
-        for s in list(self._running):
-            if s.req.cancelled is not None and s.req.cancelled.is_set():
-                cache.release_slot(s.slot)
-                self._running.remove(s)
-        self._admit()
-        plan = self.plan()
-        if plan is None:
+        """Run one engine step and wait for its tokens. False when nothing is queued or running."""
+        begun = self._begin()
+        if begun is None:
             return False
-        entries, wanted = [], []
-        for s, count in plan:
-            a = s.next_pos
-            last = a + count == len(s.tokens)
-            entries.append(StepEntry(slot=s.slot, first_pos=a, tokens=s.tokens[a:a + count], want=[count - 1] if last else []))
-            if last:
-                wanted.append(s)
-            s.next_pos += count
+        if begun is _DRAIN:
+            raise EngineError("the scheduler asked to drain an empty pipeline")
+        entries, wanted, ends = begun
         logits = self.engine.step(entries)
-        self.stats.steps += 1
-        self.stats.rows += sum(c for _, c in plan)
-        used = max((t - f for t, f in zip(cache.total_pages(), cache.free_pages())), default=0)
-        self.stats.peak_blocks = max(self.stats.peak_blocks, used)
         if wanted:
-            tokens, values = self._sampler.choose(logits, [s.req.sampling for s in wanted], [len(s.tokens) for s in wanted])
-            self._check_kernels(tokens)
-            full = None
-            if any(s.req.full_logits and s.req.on_token for s in wanted):
-                full = logits.to("cpu").numpy()
-            for i, s in enumerate(wanted):
-                tok, val = int(tokens[i]), float(values[i])
-                s.fingerprint = _fnv_mix(_fnv_mix(s.fingerprint, tok & 0xFFFFFFFF), _float_bits(val))
-                s.tokens.append(tok)
-                s.generated += 1
-                self.stats.generated += 1
-                ev = TokenEvent(token=tok, value=val, index=s.generated - 1, fingerprint=s.fingerprint)
-                if tok in s.req.stop_tokens:
-                    ev.finished, ev.finish_reason = True, "stop"
-                elif s.generated >= s.req.max_new_tokens:
-                    ev.finished, ev.finish_reason = True, "length"
-                if s.req.on_token:
-                    s.req.on_token(ev, full[i] if (full is not None and s.req.full_logits) else None)
-                if ev.finished:
-                    self._finish(s)
-        for s in self._running:
-            if not s.done:
-                cache.trim(s.slot)
-        self._running = [s for s in self._running if not s.done]
+            reqs = [self._requests[rid] for rid in wanted]
+            lengths = [e.first_pos + len(e.tokens) for e in entries if e.want]
+            tokens, values = self._sampler.choose(logits, [q.sampling for q in reqs], lengths)
+            self._commit(False, wanted, tokens, values, self._full_logits(wanted, logits))
+        self._end(ends, whole=True)
         return True
 
     # ------------------------------------------------------------------ pipelined running
@@ -311,84 +302,32 @@ class Scheduler:
         """Queue one step on the GPU without waiting for its tokens: rows whose input token is not known yet (it is
         being sampled by the step before) carry -1 and read it on the device. Returns a record for `_collect`, None
         when there is nothing to run, or _DRAIN when the steps in flight have to be read back first."""
-        cache = self.engine.cache
-        for s in list(self._running):
-            if s.req.cancelled is not None and s.req.cancelled.is_set():
-                if s.inflight:
-                    return _DRAIN
-                cache.release_slot(s.slot)
-                self._running.remove(s)
-        self._admit()
-        plan = self.plan()
-        if plan is None or plan is _DRAIN:
-            return plan
-        entries, wanted, ends = [], [], []
-        for s, count in plan:
-            a = s.next_pos
-            last = a + count == len(s.tokens)
-            entries.append(StepEntry(slot=s.slot, first_pos=a, tokens=s.tokens[a:a + count], want=[count - 1] if last else []))
-            if last:
-                wanted.append(s)
-            s.next_pos += count
-            ends.append((s, s.next_pos))
-        pipelined = all(Sampler.on_device(s.req.sampling) and not s.req.full_logits for s in wanted)
+        begun = self._begin()
+        if begun is None or begun is _DRAIN:
+            return begun
+        entries, wanted, ends = begun
         logits = self.engine.step(entries)
-        self.stats.steps += 1
-        self.stats.rows += sum(c for _, c in plan)
-        used = max((t - f for t, f in zip(cache.total_pages(), cache.free_pages())), default=0)
-        self.stats.peak_blocks = max(self.stats.peak_blocks, used)
-        ticket, full = None, None
+        ticket, full, pipelined = None, None, True
         if wanted:
-            ticket = self._sampler.launch(logits, [s.req.sampling for s in wanted], [len(s.tokens) for s in wanted],
-                                          self.engine.logit_slots, self.engine.sampled)
-            if any(s.req.full_logits and s.req.on_token for s in wanted):
-                full = logits.to("cpu").numpy()             # synchronises: such a step is not pipelined
-            for s in wanted:
-                s.tokens.append(-1)                          # stands for the token being sampled
-                s.inflight += 1
-                s.launched += 1
-                if s.launched >= s.req.max_new_tokens:
-                    s.closing = True                         # that token is its last ("length")
+            reqs = [self._requests[rid] for rid in wanted]
+            pipelined = all(Sampler.on_device(q.sampling) and not q.full_logits for q in reqs)
+            lengths = [e.first_pos + len(e.tokens) for e in entries if e.want]
+            ticket = self._sampler.launch(logits, [q.sampling for q in reqs], lengths, self.engine.logit_slots, self.engine.sampled)
+            full = self._full_logits(wanted, logits)             # synchronises: such a step is not pipelined
+            ids = np.asarray(wanted, dtype=np.int32)
+            self._lib.sb_sched_launched(self._sched, ids.ctypes.data_as(_I32P), ids.size)
         return (wanted, ticket, full, ends, pipelined)
 
     def _collect(self, record) -> None:
         """Read back the tokens of a launched step and do the bookkeeping `step()` does after sampling."""
         wanted, ticket, full, ends, _ = record
-        cache = self.engine.cache
         if ticket is not None:
             tokens, values = self._sampler.collect(ticket)
-            self._check_kernels(tokens)
-            for i, s in enumerate(wanted):
-                s.inflight -= 1
-                if s.done:                                   # finished by a stop token a step ago: this row was surplus
-                    if s.inflight == 0 and s.slot >= 0:
-                        self._finish(s)
-                    continue
-                tok, val = int(tokens[i]), float(values[i])
-                s.fingerprint = _fnv_mix(_fnv_mix(s.fingerprint, tok & 0xFFFFFFFF), _float_bits(val))
-                s.tokens[s.prompt_len + s.generated] = tok   # the oldest placeholder
-                s.generated += 1
-                self.stats.generated += 1
-                ev = TokenEvent(token=tok, value=val, index=s.generated - 1, fingerprint=s.fingerprint)
-                if tok in s.req.stop_tokens:
-                    ev.finished, ev.finish_reason = True, "stop"
-                elif s.generated >= s.req.max_new_tokens:
-                    ev.finished, ev.finish_reason = True, "length"
-                if s.req.on_token:
-                    s.req.on_token(ev, full[i] if (full is not None and s.req.full_logits) else None)
-                if ev.finished:
-                    s.done = s.closing = True
-                    if s.inflight == 0:
-                        self._finish(s)                      # else its slot is given back when the surplus step is read
-        windowed = any(g.window > 0 for g in cache.groups)
-        if ticket is None and windowed and getattr(self.engine, "device", None) is not None and str(self.engine.device) != "cpu":
+            self._commit(True, wanted, tokens, values, full)
+        elif any(g.window > 0 for g in self.engine.cache.groups) and str(getattr(self.engine, "device", "cpu")) != "cpu":
             import torch
             torch.cuda.current_stream().synchronize()      # pages are only given back once the step has run
-        if windowed:
-            for s, end in ends:
-                if s.slot >= 0 and not s.done:
-                    cache.trim(s.slot, end)
-        self._running = [s for s in self._running if not (s.done and s.slot < 0)]
+        self._end(ends, whole=False)
 
     def run(self, steps: Optional[int] = None) -> int:
         """Run until nothing is queued or running, or for `steps` engine steps. With a GPU engine the next step is

@@ -182,7 +182,8 @@ def test_native_planner_decisions_under_random_states(seed):
     eng = FakeEngine(pages=rng.choice([6, 12, 40]), page_size=page, max_slots=8, max_rows=64, max_context=64)
     sched = Scheduler(eng, SchedulerOptions(max_seqs=8, max_rows=rng.choice([4, 9, 32]), prefill_chunk=rng.choice([2, 5, 16])),
                       sampler=HashSampler())
-    cache, lib, buf = eng.cache, sched._lib, sched._buf
+    from stride_b200.engine.scheduler import _PlanBuffers
+    cache, lib, buf = eng.cache, sched._lib, _PlanBuffers(8)
     for _ in range(60):
         while cache.live_slots:
             cache.release_slot(next(iter(cache.live_slots)))
@@ -342,3 +343,20 @@ def test_a_step_ahead_with_cancellation():
     assert other == _run(FakeEngine(), [[4, 5]], max_new=30)[0][0]["tokens"]
     eng.cache.check()
     assert eng.cache.free_pages() == eng.cache.total_pages()
+
+
+def test_fingerprints_are_fnv1a_over_tokens_and_logit_bits():
+    """arhaamatiq/stride's request fingerprint (src/scheduler.cpp:26-31): FNV-1a over the four bytes of every chosen
+    token and the four bytes of its float32 logit, in order."""
+    import struct
+    seen = []
+    sched = Scheduler(FakeEngine(), SchedulerOptions(max_seqs=2, max_rows=16, prefill_chunk=8), sampler=HashSampler())
+    sched.submit(GenRequest(prompt=[3, 1, 4, 1, 5], max_new_tokens=6, on_token=lambda ev, l: seen.append(ev)))
+    sched.run()
+    h = 14695981039346656037
+    for ev in seen:
+        for word in (ev.token & 0xFFFFFFFF, struct.unpack("<I", struct.pack("<f", ev.value))[0]):
+            for i in range(4):
+                h = ((h ^ ((word >> (8 * i)) & 0xFF)) * 1099511628211) & ((1 << 64) - 1)
+        assert ev.fingerprint == h
+    assert [ev.index for ev in seen] == list(range(6)) and seen[-1].finished and seen[-1].finish_reason == "length"
