@@ -2,6 +2,7 @@
 slot has been fed: any token fed twice, skipped, or at a wrong position changes what is generated."""
 from __future__ import annotations
 
+import ctypes
 import hashlib
 import threading
 from types import SimpleNamespace
@@ -360,3 +361,28 @@ def test_fingerprints_are_fnv1a_over_tokens_and_logit_bits():
                 h = ((h ^ ((word >> (8 * i)) & 0xFF)) * 1099511628211) & ((1 << 64) - 1)
         assert ev.fingerprint == h
     assert [ev.index for ev in seen] == list(range(6)) and seen[-1].finished and seen[-1].finish_reason == "length"
+
+
+def test_request_ids_are_used_again_and_waiting_requests_can_be_cancelled():
+    """Many more requests than ever run at once go through two slots; a request cancelled while it waits never runs;
+    the native table of requests is as large as the most requests known at once, however many are served."""
+    eng = FakeEngine(max_slots=2)
+    sched = Scheduler(eng, SchedulerOptions(max_seqs=2, max_rows=8, prefill_chunk=4), sampler=HashSampler())
+    done, flags = {}, {}
+    for i in range(40):
+        flags[i] = threading.Event()
+        sched.submit(GenRequest(prompt=[i + 1, 2, 3], max_new_tokens=3, cancelled=flags[i],
+                                on_token=lambda ev, l, i=i: done.setdefault(i, []).append(ev.token)))
+    for i in (5, 6, 39):
+        flags[i].set()                       # they still wait: cancelled before they ever run
+    sched.run()
+    assert sched.idle() and not sched._requests
+    assert sorted(done) == [i for i in range(40) if i not in (5, 6, 39)] and all(len(v) == 3 for v in done.values())
+    assert max(sched._lib.sb_sched_add(sched._sched, None, 0, 1, None, 0) for _ in range(1)) == -1     # an empty prompt is refused
+    for i, toks in done.items():
+        assert toks == _run(FakeEngine(), [[i + 1, 2, 3]], max_new=3)[0][0]["tokens"]
+    eng.cache.check()
+    assert eng.cache.free_pages() == eng.cache.total_pages() and len(eng.cache.free_slots) == 2
+    # forty requests were known at once, so forty ids exist; whoever comes later gets one of them again
+    later = [sched._lib.sb_sched_add(sched._sched, (ctypes.c_int32 * 2)(7, 8), 2, 1, None, 0) for _ in range(40)]
+    assert sorted(later) == list(range(40))
