@@ -386,3 +386,27 @@ def test_request_ids_are_used_again_and_waiting_requests_can_be_cancelled():
     # forty requests were known at once, so forty ids exist; whoever comes later gets one of them again
     later = [sched._lib.sb_sched_add(sched._sched, (ctypes.c_int32 * 2)(7, 8), 2, 1, None, 0) for _ in range(40)]
     assert sorted(later) == list(range(40))
+
+
+@pytest.mark.parametrize("ahead", [False, True])
+def test_windowed_groups_give_pages_back_while_requests_run(ahead):
+    """With a window of 8 keys a request of 5 + 40 tokens never holds more than a few pages of 4, waited for or a step
+    ahead; the tokens are those of a pool without a window (the fake model does not look at the cache)."""
+    class Windowed(PipeEngine if ahead else FakeEngine):
+        def __init__(self):
+            super().__init__(pages=12, page_size=4)
+            need = CacheNeed("pages", kv_heads=1, head_dim=2, window=8, dtype=torch.float32)
+            self.cache = CacheManager([need], device="cpu", max_slots=8, max_context=64, page_size=4, num_pages=12)
+            self.most = 0
+
+        def step(self, entries):
+            out = super().step(entries)
+            self.most = max(self.most, 12 - self.cache.free_pages()[0])
+            return out
+    eng = Windowed()
+    prompts = [[1, 2, 3, 4, 5], [9, 8, 7]]
+    outs, sched = (_run_ahead if ahead else _run)(eng, prompts, max_new=40, opts=SchedulerOptions(max_seqs=2, max_rows=8, prefill_chunk=4))
+    want = [_run(FakeEngine(), [p], max_new=40)[0][0]["tokens"] for p in prompts]
+    assert [o["tokens"] for o in outs] == want
+    # two requests of up to 45 tokens would hold 23 pages without the window; 12 exist and no request was preempted
+    assert sched.stats.preemptions == 0 and eng.most <= 10
