@@ -760,3 +760,98 @@ SB_API void sb_sched_end_step(void* sched, const int32_t* ids, const int32_t* en
     }
   sc->drop_finished();
 }
+
+// ------------------------------------------------------------------ staging a step's integer inputs
+//
+// One array of 9 R int32 (R = the most rows of a step) carries every integer input of a step to the device in one
+// copy: tokens [0, R), positions [R, 2R), slots [2R, 3R), rows whose logits are wanted [3R, 4R), the entries'
+// records [4R, 8R) as four rows of R (slot, first row, length, first position), and the slot of every wanted row
+// [8R, 9R). These functions check a step against the pool's books and fill that array.
+namespace {
+
+int stage_fail(const char* fmt, long a = 0, long b = 0, long c = 0) {
+  char msg[200];
+  snprintf(msg, sizeof msg, fmt, a, b, c);
+  g_error = msg;
+  return -1;
+}
+
+}  // namespace
+
+// Entries i < E: slot[i], first[i] (position of its first token), count[i] tokens taken one after another from
+// `tokens`, n_want[i] places (indices into the entry's tokens) taken one after another from `want`. A token id is
+// 0 .. vocab - 1, or -1 for the single token of an entry of one (the token is still being chosen and is read on the
+// device). out[0] = rows, out[1] = wanted rows. 0, or -1 with the reason in sb_last_error(); nothing but `staging`
+// is written.
+SB_API int sb_stage_step(void* pool, int E, const int32_t* slot, const int32_t* first, const int32_t* count, const int32_t* tokens,
+                         const int32_t* n_want, const int32_t* want, int vocab, int R, int max_logit_rows, int32_t* staging,
+                         int32_t* out) {
+  Pool* p = static_cast<Pool*>(pool);
+  long n = 0, w_total = 0;
+  for (int i = 0; i < E; ++i) {
+    if (count[i] <= 0) return stage_fail("a step entry without tokens");
+    n += count[i];
+    w_total += n_want[i];
+  }
+  if (n > R) return stage_fail("step of %ld tokens exceeds max_rows %ld", n, R);
+  if (w_total > max_logit_rows) return stage_fail("logits wanted at %ld places exceed max_full_rows %ld", w_total, max_logit_rows);
+  std::vector<uint8_t> seen(p->max_slots, 0);
+  int32_t *tok = staging, *pos = staging + R, *slt = staging + 2 * R, *rows = staging + 3 * R, *meta = staging + 4 * R,
+          *row_slot = staging + 8 * R;
+  int at = 0, w = 0, wi = 0;
+  for (int i = 0; i < E; ++i) {
+    const int s = slot[i], L = count[i];
+    if (!p->slot_ok(s)) return stage_fail("slot %ld is not held by a request", s);
+    if (seen[s]) return stage_fail("slot %ld appears twice in one step", s);
+    seen[s] = 1;
+    if (first[i] < 0 || first[i] + L > p->length[s])
+      return stage_fail("slot %ld: tokens up to position %ld have no pages (ensured up to %ld)", s, (long)first[i] + L - 1, p->length[s]);
+    for (int j = 0; j < L; ++j) {
+      const int32_t t = tokens[at + j];
+      if (!((t >= 0 && t < vocab) || (t == -1 && L == 1)))
+        return stage_fail("token id %ld out of range 0..%ld in the entry of slot %ld", t, (long)vocab - 1, s);
+      tok[at + j] = t;
+      pos[at + j] = first[i] + j;
+      slt[at + j] = s;
+    }
+    for (int k = 0; k < n_want[i]; ++k, ++wi) {
+      const int j = want[wi];
+      if (j < 0 || j >= L) return stage_fail("wanted place %ld is outside the entry's %ld tokens", j, L);
+      rows[w] = at + j;
+      row_slot[w] = s;
+      ++w;
+    }
+    meta[i] = s, meta[R + i] = at, meta[2 * R + i] = L, meta[3 * R + i] = first[i];
+    at += L;
+  }
+  out[0] = at;
+  out[1] = w;
+  return 0;
+}
+
+// A step of E decoded tokens, each wanted, padded to B rows for a recorded graph: the padding rows belong to
+// `pad_slot` at position 0 with token 0. token[i] may be -1 (still being chosen).
+SB_API int sb_stage_decode(void* pool, int E, int B, int pad_slot, const int32_t* slot, const int32_t* first, const int32_t* token,
+                           int vocab, int R, int32_t* staging) {
+  Pool* p = static_cast<Pool*>(pool);
+  if (E <= 0 || B < E || B > R) return stage_fail("a decode step of %ld rows padded to %ld does not fit max_rows %ld", E, B, R);
+  std::vector<uint8_t> seen(p->max_slots, 0);
+  int32_t *tok = staging, *pos = staging + R, *slt = staging + 2 * R, *rows = staging + 3 * R, *meta = staging + 4 * R,
+          *row_slot = staging + 8 * R;
+  for (int i = 0; i < E; ++i) {
+    const int s = slot[i];
+    if (!p->slot_ok(s) || s == pad_slot || seen[s]) return stage_fail("slot %ld appears twice in one step or is not held by a request", s);
+    seen[s] = 1;
+    if (first[i] < 0 || first[i] + 1 > p->length[s])
+      return stage_fail("slot %ld: token %ld has no page (ensured up to %ld)", s, first[i], p->length[s]);
+    if (token[i] < -1 || token[i] >= vocab) return stage_fail("token id %ld out of range 0..%ld", token[i], (long)vocab - 1);
+    tok[i] = token[i], pos[i] = first[i], slt[i] = s, row_slot[i] = s;
+    meta[i] = s, meta[R + i] = i, meta[2 * R + i] = 1, meta[3 * R + i] = first[i];
+  }
+  for (int i = E; i < B; ++i) {
+    tok[i] = 0, pos[i] = 0, slt[i] = pad_slot, row_slot[i] = pad_slot;
+    meta[i] = pad_slot, meta[R + i] = i, meta[2 * R + i] = 1, meta[3 * R + i] = 0;
+  }
+  for (int i = 0; i < B; ++i) rows[i] = i;
+  return 0;
+}

@@ -13,6 +13,8 @@ ascending here, which is what the scheduler there produces too.
 """
 from __future__ import annotations
 
+import ctypes
+
 import json
 from dataclasses import dataclass, field
 from pathlib import Path
@@ -57,6 +59,23 @@ class StepEntry:
 
 
 _DTYPES = {"float32": torch.float32, "fp32": torch.float32, "bfloat16": torch.bfloat16, "bf16": torch.bfloat16}
+_I32P = ctypes.POINTER(ctypes.c_int32)
+
+
+def _i32(array: np.ndarray):
+    if array.dtype != np.int32 or not array.flags["C_CONTIGUOUS"]:
+        raise EngineError("a step's arrays must be contiguous int32")
+    return array.ctypes.data_as(_I32P)
+
+
+def _native_stager(lib):
+    """The runtime library with the functions that check a step and fill its staging area typed."""
+    if not getattr(lib, "_sb_stage_typed", False):
+        vp, ci = ctypes.c_void_p, ctypes.c_int
+        lib.sb_stage_step.restype, lib.sb_stage_step.argtypes = ci, [vp, ci, _I32P, _I32P, _I32P, _I32P, _I32P, _I32P, ci, ci, ci, _I32P, _I32P]
+        lib.sb_stage_decode.restype, lib.sb_stage_decode.argtypes = ci, [vp, ci, ci, ci, _I32P, _I32P, _I32P, ci, ci, _I32P]
+        lib._sb_stage_typed = True
+    return lib
 
 
 class Engine:
@@ -116,6 +135,10 @@ class Engine:
         self._staging = torch.empty(self._ints, dtype=torch.int32, pin_memory=True)
         self._staging_np = self._staging.numpy()
         self._device_ints = torch.zeros(self._ints, dtype=torch.int32, device=self.device)
+        self._staging_p = self._staging_np.ctypes.data_as(_I32P)
+        self._staged = np.zeros(2, dtype=np.int32)          # rows and wanted rows of the step just staged
+        self._staged_p = self._staged.ctypes.data_as(_I32P)
+        self._stager = _native_stager(self.cache._lib)
         self._copied = torch.cuda.Event()
         self._copy_pending = False
         # A second staging area for small integer tables that parts make during a step (work lists).
@@ -162,72 +185,58 @@ class Engine:
         """Run one batch. Returns the logits [wanted, vocab] float32 on the device, in the order of
         the entries and of their `want` lists, or None if nothing is wanted. The tensor is a view of
         an engine buffer: it is overwritten by the next step."""
-        o = self.options
-        n = sum(len(e.tokens) for e in entries)
+        E = len(entries)
+        if sum(len(e.tokens) for e in entries) == 0:
+            return None
+        for e in entries:
+            if len(e.tokens) == 0:
+                raise EngineError("a step entry without tokens")
+        tokens = np.fromiter((t for e in entries for t in e.tokens), dtype=np.int64)
+        if tokens.min() < -1 or tokens.max() >= self.spec.vocab_size:
+            raise EngineError(f"token id out of range 0..{self.spec.vocab_size - 1}")
+        want = np.fromiter((j for e in entries for j in e.want), dtype=np.int64)
+        if want.size and (want.min() < 0 or want.max() >= (1 << 31)):
+            raise EngineError("a wanted place is outside its entry's tokens")
+        return self.step_arrays(E, np.fromiter((e.slot for e in entries), dtype=np.int32, count=E),
+                                np.fromiter((e.first_pos for e in entries), dtype=np.int32, count=E),
+                                np.fromiter((len(e.tokens) for e in entries), dtype=np.int32, count=E), tokens.astype(np.int32),
+                                np.fromiter((len(e.want) for e in entries), dtype=np.int32, count=E), want.astype(np.int32))
+
+    def step_arrays(self, E: int, slot, first, count, tokens, n_want, want) -> Optional[torch.Tensor]:
+        """`step` for a batch given as int32 arrays (contiguous, at least as long as used): entry i < E is
+        slot[i], first[i], its count[i] tokens taken one after another from `tokens`, and n_want[i] wanted places
+        taken one after another from `want`. The native stager checks the batch against the cache's books and fills
+        the staging area; the scheduler hands its plan over in this form."""
+        o, R, lib = self.options, self.options.max_rows, self._stager
+        n = int(count[:E].sum()) if E else 0
         if n == 0:
             return None
-        if self._pad_slot >= 0 and n == len(entries):
-            logits = self._graph_step(entries)
-            if logits is not None:
-                return logits
-        if n > o.max_rows:
-            raise EngineError(f"step of {n} tokens exceeds max_rows {o.max_rows}")
-        count = sum(len(e.want) for e in entries)
-        if count > self.env.max_logit_rows:
-            raise EngineError(f"logits wanted at {count} places exceed max_full_rows {self.env.max_logit_rows}")
-        R = o.max_rows
+        if self._pad_slot >= 0 and n == E and E <= self.env.max_logit_rows and bool((n_want[:E] == 1).all()) and not want[:E].any():
+            return self._graph_step(E, slot, first, tokens)
         if self._copy_pending:
             self._copied.synchronize()
         if self._aux_pending:
             self._aux_copied.synchronize()
             self._aux_pending = False
         self._aux_used = 0
-        buf = self._staging_np
-        tok, pos, slt, rows = buf[0:n], buf[R:R + n], buf[2 * R:2 * R + n], buf[3 * R:3 * R + count]
-        meta = buf[4 * R:8 * R].reshape(4, R)
-        at = w = 0
-        seen = set()
-        vocab = self.spec.vocab_size
-        for i, e in enumerate(entries):
-            L = len(e.tokens)
-            if L == 0:
-                raise EngineError("a step entry without tokens")
-            if e.slot in seen:
-                raise EngineError(f"slot {e.slot} appears twice in one step")
-            seen.add(e.slot)
-            if not self.cache.is_live(e.slot):
-                raise EngineError(f"slot {e.slot} is not held by a request")
-            if e.first_pos < 0 or e.first_pos + L > self.cache.length[e.slot]:
-                raise EngineError(f"slot {e.slot}: tokens {e.first_pos}..{e.first_pos + L - 1} have no pages "
-                                  f"(ensured up to {self.cache.length[e.slot]})")
-            t = np.asarray(e.tokens, dtype=np.int64)
-            if (t.min() < 0 and not (L == 1 and t[0] == -1)) or t.max() >= vocab:
-                raise EngineError(f"token id out of range 0..{vocab - 1} in the entry of slot {e.slot}")
-            tok[at:at + L] = t
-            pos[at:at + L] = np.arange(e.first_pos, e.first_pos + L)
-            slt[at:at + L] = e.slot
-            for j in e.want:
-                if not 0 <= j < L:
-                    raise EngineError(f"wanted place {j} is outside the entry's {L} tokens")
-                rows[w] = at + j
-                buf[8 * R + w] = e.slot
-                w += 1
-            meta[0, i], meta[1, i], meta[2, i], meta[3, i] = e.slot, at, L, e.first_pos
-            at += L
+        if lib.sb_stage_step(self.cache._pool, E, _i32(slot), _i32(first), _i32(count), _i32(tokens), _i32(n_want), _i32(want),
+                             self.spec.vocab_size, R, self.env.max_logit_rows, self._staging_p, self._staged_p) < 0:
+            raise EngineError(lib.sb_last_error().decode())
+        wanted = int(self._staged[1])
+        meta = self._staging_np[4 * R:8 * R].reshape(4, R)
         self._device_ints.copy_(self._staging, non_blocking=True)
         self._copied.record()
         self._copy_pending = True
         self.cache.sync()
         d = self._device_ints
-        E = len(entries)
         ctx = StepContext(
             n=n, token_ids=d[0:n], positions=d[R:R + n], slots=d[2 * R:2 * R + n], workspace=self.workspace,
             compute_dtype=self.compute_dtype,
-            entry_slots=[e.slot for e in entries], entry_first_row=[int(x) for x in meta[1, :E]],
-            entry_length=[len(e.tokens) for e in entries], entry_first_pos=[e.first_pos for e in entries],
+            entry_slots=slot[:E].tolist(), entry_first_row=meta[1, :E].tolist(),
+            entry_length=count[:E].tolist(), entry_first_pos=first[:E].tolist(),
             entry_meta=d[4 * R:8 * R].view(4, R)[:, :E], upload_ints=self._upload_ints, sampled=self.sampled)
-        logits = self.model.forward(ctx, self.caches, d[3 * R:3 * R + count], count)
-        self.logit_slots = d[8 * R:8 * R + count]
+        logits = self.model.forward(ctx, self.caches, d[3 * R:3 * R + wanted], wanted)
+        self.logit_slots = d[8 * R:8 * R + wanted]
         self.steps += 1
         return logits
 
@@ -245,47 +254,25 @@ class Engine:
                               f"results of the step are not valid")
 
     # ------------------------------------------------------------------ decode steps as CUDA graphs
-    def _graph_step(self, entries: list) -> Optional[torch.Tensor]:
+    def _graph_step(self, E: int, slot, first, tokens) -> torch.Tensor:
         """A step in which every entry is one decoded token whose logits are wanted: padded to a batch
-        bucket, run from a CUDA graph recorded for (batch bucket, context bucket). Returns None if the step
-        does not qualify."""
-        o = self.options
-        E = len(entries)
-        if self._pad_slot < 0 or E == 0 or E > self.env.max_logit_rows:
-            return None
-        for e in entries:
-            if len(e.tokens) != 1 or e.want != [0]:
-                return None
+        bucket, run from a CUDA graph recorded for (batch bucket, context bucket)."""
+        o, lib = self.options, self._stager
         B = 1
         while B < E:
             B *= 2
         if B > min(o.max_rows, self.env.max_logit_rows):
             B = E
-        last = max(e.first_pos for e in entries)
+        last = int(first[:E].max())
         keys = 256
         while keys <= last:
             keys *= 2
-        R, vocab = o.max_rows, self.spec.vocab_size
+        R = o.max_rows
         if self._copy_pending:
             self._copied.synchronize()
-        buf = self._staging_np
-        meta = buf[4 * R:8 * R].reshape(4, R)
-        seen = set()
-        for i, e in enumerate(entries):
-            if e.slot in seen or not self.cache.is_live(e.slot) or e.slot == self._pad_slot:
-                raise EngineError(f"slot {e.slot} appears twice in one step or is not held by a request")
-            seen.add(e.slot)
-            if e.first_pos < 0 or e.first_pos + 1 > self.cache.length[e.slot]:
-                raise EngineError(f"slot {e.slot}: token {e.first_pos} has no page (ensured up to {self.cache.length[e.slot]})")
-            t = int(e.tokens[0])
-            if not -1 <= t < vocab:
-                raise EngineError(f"token id {t} out of range 0..{vocab - 1}")
-            buf[i], buf[R + i], buf[2 * R + i], buf[8 * R + i] = t, e.first_pos, e.slot, e.slot
-            meta[0, i], meta[1, i], meta[2, i], meta[3, i] = e.slot, i, 1, e.first_pos
-        for i in range(E, B):
-            buf[i], buf[R + i], buf[2 * R + i], buf[8 * R + i] = 0, 0, self._pad_slot, self._pad_slot
-            meta[0, i], meta[1, i], meta[2, i], meta[3, i] = self._pad_slot, i, 1, 0
-        buf[3 * R:3 * R + B] = np.arange(B)
+        if lib.sb_stage_decode(self.cache._pool, E, B, self._pad_slot, _i32(slot), _i32(first), _i32(tokens), self.spec.vocab_size, R,
+                               self._staging_p) < 0:
+            raise EngineError(lib.sb_last_error().decode())
         self._device_ints.copy_(self._staging, non_blocking=True)
         self._copied.record()
         self._copy_pending = True

@@ -144,7 +144,7 @@ class Scheduler:
             raise EngineError(self._lib.sb_last_error().decode())
         rows = max(self.opts.max_rows, 1)
         self._plan = _Buffers(rows, (("id", np.int32), ("slot", np.int32), ("first", np.int32), ("count", np.int32), ("last", np.uint8),
-                                     ("tokens", np.int32)))
+                                     ("tokens", np.int32), ("n_want", np.int32), ("want", np.int32)))
         self._plan_n = ctypes.c_int32(0)
         self._rows = _Buffers(rows, (("id", np.int32), ("token", np.int32), ("value", np.float32), ("kind", np.uint8), ("index", np.int32),
                                      ("fingerprint", np.uint64), ("end", np.int32)))
@@ -210,8 +210,9 @@ class Scheduler:
 
     # ------------------------------------------------------------------ the parts of a step
     def _begin(self):
-        """The next step's entries, or None (nothing to run) or _DRAIN. Returns (entries, ids of the requests a token is
-        to be chosen for, number of entries); the plan's arrays keep the ids and positions."""
+        """The next step, or None (nothing to run) or _DRAIN: (a call that runs it on the engine and returns its logits,
+        ids of the requests a token is to be chosen for, the tokens each of those has before the new one, (ids, positions
+        reached) of all requests in the step)."""
         self._intake()
         p = self._plan
         result = self._lib.sb_sched_begin_step(self._sched, p.id_p, p.slot_p, p.first_p, p.count_p, p.last_p, p.tokens_p,
@@ -225,16 +226,22 @@ class Scheduler:
         if result != _PLAN_RUN:
             raise EngineError(self._lib.sb_last_error().decode())
         m = self._plan_n.value
-        ids, slots, firsts, counts, lasts = (a[:m].tolist() for a in (p.id, p.slot, p.first, p.count, p.last))
-        tokens = p.tokens[:sum(counts)].tolist()
-        entries, wanted, at = [], [], 0
-        for rid, slot, first, count, last in zip(ids, slots, firsts, counts, lasts):
-            entries.append(StepEntry(slot=slot, first_pos=first, tokens=tokens[at:at + count], want=[count - 1] if last else []))
-            if last:
-                wanted.append(rid)
-            at += count
+        ids, firsts, counts, lasts = (a[:m].tolist() for a in (p.id, p.first, p.count, p.last))
+        wanted = [rid for rid, last in zip(ids, lasts) if last]
+        lengths = [f + c for f, c, last in zip(firsts, counts, lasts) if last]     # tokens each has before the new one
         ends = (ids, [f + c for f, c in zip(firsts, counts)])
-        return entries, wanted, ends
+        if hasattr(self.engine, "step_arrays"):
+            # the plan goes to the engine as the arrays it is: the native stager reads them
+            p.n_want[:m] = p.last[:m]
+            k = len(wanted)
+            p.want[:k] = (p.count[:m] - 1)[p.last[:m] != 0]
+            return (lambda: self.engine.step_arrays(m, p.slot, p.first, p.count, p.tokens, p.n_want, p.want)), wanted, lengths, ends
+        slots, tokens = p.slot[:m].tolist(), p.tokens[:sum(counts)].tolist()
+        entries, at = [], 0
+        for slot, first, count, last in zip(slots, firsts, counts, lasts):
+            entries.append(StepEntry(slot=slot, first_pos=first, tokens=tokens[at:at + count], want=[count - 1] if last else []))
+            at += count
+        return (lambda: self.engine.step(entries)), wanted, lengths, ends
 
     def _commit(self, ahead: bool, wanted: list, tokens, values, full) -> None:
         """Hands the chosen tokens to the native scheduler and tells the requests what it made of them."""
@@ -282,11 +289,10 @@ class Scheduler:
             return False
         if begun is _DRAIN:
             raise EngineError("the scheduler asked to drain an empty pipeline")
-        entries, wanted, ends = begun
-        logits = self.engine.step(entries)
+        run_step, wanted, lengths, ends = begun
+        logits = run_step()
         if wanted:
             reqs = [self._requests[rid] for rid in wanted]
-            lengths = [e.first_pos + len(e.tokens) for e in entries if e.want]
             tokens, values = self._sampler.choose(logits, [q.sampling for q in reqs], lengths)
             self._commit(False, wanted, tokens, values, self._full_logits(wanted, logits))
         self._end(ends, whole=True)
@@ -305,13 +311,12 @@ class Scheduler:
         begun = self._begin()
         if begun is None or begun is _DRAIN:
             return begun
-        entries, wanted, ends = begun
-        logits = self.engine.step(entries)
+        run_step, wanted, lengths, ends = begun
+        logits = run_step()
         ticket, full, pipelined = None, None, True
         if wanted:
             reqs = [self._requests[rid] for rid in wanted]
             pipelined = all(Sampler.on_device(q.sampling) and not q.full_logits for q in reqs)
-            lengths = [e.first_pos + len(e.tokens) for e in entries if e.want]
             ticket = self._sampler.launch(logits, [q.sampling for q in reqs], lengths, self.engine.logit_slots, self.engine.sampled)
             full = self._full_logits(wanted, logits)             # synchronises: such a step is not pipelined
             ids = np.asarray(wanted, dtype=np.int32)

@@ -177,3 +177,36 @@ def test_a_lost_signal_inside_a_kernel_is_an_error(model_dirs):
     llm2 = LLM(model_dirs["A"], dtype="bfloat16", concurrency=2, max_rows=64, page_size=TINY["A"][2], kv_pages=64, max_slots=4)
     again = llm2.generate(prompts, max_new_tokens=4)
     assert [o.tokens for o in again] == [o.tokens for o in good]
+
+
+def test_the_engine_refuses_steps_that_disagree_with_the_cache(model_dirs):
+    """Bad entries are an error before anything runs (unknown or repeated slot, tokens without pages, a token id out
+    of range, a wanted place outside the entry), for prompt portions and for decoded tokens (the graph path); the
+    engine works on afterwards. A batch given as arrays gives the same bits as the same batch given as entries."""
+    from stride_b200 import Engine, EngineOptions, StepEntry
+    from stride_b200.engine.engine import EngineError
+    cfg, page = TINY["A"][0], TINY["A"][2]
+    eng = Engine(model_dirs["A"], EngineOptions(dtype="bfloat16", max_rows=32, max_full_rows=8, max_slots=4, kv_pages=32, page_size=page))
+    a, b = eng.cache.acquire_slot(), eng.cache.acquire_slot()
+    assert eng.cache.ensure(a, 12) and eng.cache.ensure(b, 6)
+    vocab = cfg["vocab_size"]
+    for entries, reason in (
+            ([StepEntry(a, 0, [1, 2], []), StepEntry(a, 2, [3], [0])], "appears twice"),
+            ([StepEntry(3, 0, [1, 2], [])], "not held by a request"),
+            ([StepEntry(b, 4, [1, 2, 3], [])], "have no pages"),
+            ([StepEntry(a, 0, [1, vocab], [])], "out of range"),
+            ([StepEntry(a, 0, [1, 2], [2])], "outside the entry"),
+            ([StepEntry(a, 0, [1, 2], []), StepEntry(b, 0, [], [])], "without tokens"),
+            ([StepEntry(a, 0, list(range(33)), [])], "exceeds max_rows"),
+            ([StepEntry(a, 0, [1], [0]), StepEntry(a, 1, [2], [0])], "appears twice"),          # decoded tokens: the graph path
+            ([StepEntry(b, 6, [1], [0])], "has no page")):
+        with pytest.raises(EngineError, match=reason):
+            eng.step(entries)
+    batch = [StepEntry(a, 0, [5, 6, 7, 8, 9], [4]), StepEntry(b, 0, [11, 12, 13], [0, 2])]
+    first = eng.step(batch).clone()
+    i32 = lambda v: np.asarray(v, dtype=np.int32)
+    again = eng.step_arrays(2, i32([a, b]), i32([0, 0]), i32([5, 3]), i32([5, 6, 7, 8, 9, 11, 12, 13]), i32([1, 2]), i32([4, 0, 2]))
+    assert first.shape == (3, vocab) and torch.equal(first, again)
+    one = eng.step([StepEntry(a, 5, [3], [0]), StepEntry(b, 3, [4], [0])]).clone()              # from a graph, padded to two rows
+    same = eng.step_arrays(2, i32([a, b]), i32([5, 3]), i32([1, 1]), i32([3, 4]), i32([1, 1]), i32([0, 0]))
+    assert torch.equal(one, same)
