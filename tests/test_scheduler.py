@@ -410,3 +410,92 @@ def test_windowed_groups_give_pages_back_while_requests_run(ahead):
     assert [o["tokens"] for o in outs] == want
     # two requests of up to 45 tokens would hold 23 pages without the window; 12 exist and no request was preempted
     assert sched.stats.preemptions == 0 and eng.most <= 10
+
+
+@pytest.mark.parametrize("seed", range(10))
+def test_every_step_is_the_plain_schedulers_step(seed):
+    """Random workloads (prompts of 1 to 30 tokens, limits, stop tokens, pools from roomy to tight, requests that arrive
+    while others run): the engine's scheduler runs, step for step, the batch that the plain restatement of the policy
+    (tests/plain_scheduler.py) runs: the same requests in the same order, the same positions and tokens, a new token
+    wanted for the same ones; it ends the same requests for the same reasons and preempts as often."""
+    import random
+
+    from plain_scheduler import PlainScheduler
+    rng = random.Random(seed)
+    page, pages = rng.choice([2, 4, 8]), rng.choice([10, 16, 64])
+    sizes = dict(max_seqs=rng.choice([2, 4, 8]), max_rows=rng.choice([4, 9, 16]), prefill_chunk=rng.choice([2, 5, 16]))
+    eng = FakeEngine(pages=pages, page_size=page, max_slots=8, max_rows=16, max_context=48)
+    sched = Scheduler(eng, SchedulerOptions(**sizes), sampler=HashSampler())
+    plain = PlainScheduler(pages=pages, page_size=page, max_slots=8, max_context=48, **sizes)
+    finishes, slot_name = {}, {}
+
+    def submit(name):
+        prompt = [rng.randrange(VOCAB) for _ in range(rng.choice([0, 1, 2, 5, 9, 17, 30, 48]))]
+        limit, stops = rng.choice([1, 3, 8, 40]), tuple(rng.sample(range(VOCAB), rng.choice([0, 0, 6])))
+        # (a pool of 10 pages of 2 cannot hold the longest: keep those workloads to what one request can hold)
+        if len(prompt) + limit > pages * page - page:
+            prompt = prompt[:max(0, pages * page - page - limit)]
+
+        def on_token(ev, logits, name=name):
+            if ev.finished:
+                finishes[name] = ev.finish_reason
+        sched.submit(GenRequest(prompt=prompt, max_new_tokens=limit, stop_tokens=stops, on_token=on_token))
+        early = plain.submit(name, prompt, limit, stops)
+        return early
+
+    expect = {}
+    names = iter(range(1000))
+    for _ in range(rng.randint(1, 6)):
+        n = next(names)
+        expect[n] = submit(n)
+    for _ in range(400):
+        want = plain.plan()
+        before = len(eng.batches)
+        ran = sched.step()
+        assert ran == (want is not None)
+        if want is None:
+            if rng.random() < 0.5:      # idle: stop here, or wait for somebody to arrive
+                break
+        else:
+            got = eng.batches[before]
+            assert [(f, c, w) for _, f, c, w in got] == [(f, len(t), w) for _, f, t, w in want]
+            for (slot, first, count, wants), (name, _, tokens, _) in zip(got, want):
+                if first == 0:
+                    slot_name[slot] = name
+                assert slot_name[slot] == name and eng.fed[slot][first:first + count] == tokens
+                if wants:
+                    token = HashSampler().choose([list(eng.fed[slot])], None, [first + count])[0][0]
+                    reason = plain.chosen(name, token)
+                    if reason:
+                        expect[name] = reason
+        if rng.random() < 0.15:
+            n = next(names)
+            expect[n] = submit(n)
+    while sched.step():
+        want = plain.plan()
+        assert want is not None
+        for (slot, first, count, wants), (name, _, tokens, _) in zip(eng.batches[-1], want):
+            if first == 0:
+                slot_name[slot] = name
+            if wants:
+                reason = plain.chosen(name, HashSampler().choose([list(eng.fed[slot])], None, [first + count])[0][0])
+                if reason:
+                    expect[name] = reason
+    assert plain.plan() is None
+    assert finishes == {k: v for k, v in expect.items() if v is not None}
+    assert sched.stats.preemptions == plain.preemptions
+    eng.cache.check()
+    assert eng.cache.free_pages() == eng.cache.total_pages()
+    _PLAIN_RUNS.append((sched.stats.preemptions, sorted(set(finishes.values()))))
+
+
+_PLAIN_RUNS = []
+
+
+def test_the_random_workloads_met_every_case():
+    """(runs after the comparison above) Between them the workloads preempted, stopped on stop tokens, reached limits and
+    refused prompts, so the comparison has seen every rule."""
+    if len(_PLAIN_RUNS) < 10:
+        pytest.skip("the comparison did not run in this session")
+    assert any(p > 0 for p, _ in _PLAIN_RUNS)
+    assert {"stop", "length", "empty_prompt", "context_length"} <= {r for _, reasons in _PLAIN_RUNS for r in reasons}
