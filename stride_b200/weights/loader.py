@@ -48,18 +48,47 @@ def storage_dtype(dtype: torch.dtype, integer: bool) -> torch.dtype:
     return torch.float32 if dtype in (torch.float32, torch.float64) else torch.bfloat16
 
 
-def load_weights(model_dir, plan: dict, device) -> dict:
-    """Read `model.safetensors` of `model_dir`, check it against `plan`, return name -> device tensor."""
-    path = Path(model_dir) / "model.safetensors"
-    f = SafetensorsFile(path)
+def _open_files(model_dir) -> dict:
+    """name of every tensor of the model folder -> the open file that holds it: `model.safetensors`, or the shards
+    that `model.safetensors.index.json` names (its `weight_map`: tensor name -> file name), as large checkpoints are
+    distributed. arhaamatiq/stride reads the single file only (src/model.cpp:150)."""
+    folder = Path(model_dir)
+    single, index = folder / "model.safetensors", folder / "model.safetensors.index.json"
+    if single.exists() or not index.exists():
+        f = SafetensorsFile(single)
+        return {n: f for n in f.names()}
+    import json
     try:
-        check_plan(plan, {n: f.shape(n) for n in f.names()}, str(path))
+        weight_map = json.loads(index.read_text())["weight_map"]
+    except (ValueError, KeyError, TypeError) as e:
+        raise WeightsError(f"{index} is not a shard index (a JSON object with a weight_map): {e}") from e
+    files, where = {}, {}
+    try:
+        for name, shard in sorted(weight_map.items()):
+            if shard not in files:
+                files[shard] = SafetensorsFile(folder / shard)
+            if not files[shard].has(name):
+                raise WeightsError(f"{index} says that {shard} holds {name}, which it does not")
+            where[name] = files[shard]
+    except Exception:
+        for f in files.values():
+            f.close()
+        raise
+    return where
+
+
+def load_weights(model_dir, plan: dict, device) -> dict:
+    """Read the model folder's safetensors (one file or shards), check them against `plan`, return name -> device tensor."""
+    where = _open_files(model_dir)
+    try:
+        check_plan(plan, {n: f.shape(n) for n, f in where.items()}, str(Path(model_dir)))
         out = {}
         for name, want in plan.items():
-            if not f.has(name):
+            if name not in where:
                 continue
-            t = f.get(name)
+            t = where[name].get(name)
             out[name] = t.to(device=device, dtype=storage_dtype(t.dtype, want.integer), copy=True)
         return out
     finally:
-        f.close()
+        for f in {id(f): f for f in where.values()}.values():
+            f.close()

@@ -139,3 +139,42 @@ def test_random_weights_are_seeded_per_tensor(tmp_path):
     assert torch.equal(f.get("model.embed_tokens.weight"), a["model.embed_tokens.weight"])
     f32 = random_tensors(TINY_A, 0, dtype=torch.float32)
     assert f32["model.norm.weight"].dtype == torch.float32
+
+
+def test_sharded_checkpoints_load_like_the_single_file(tmp_path):
+    """A model folder with `model.safetensors.index.json` and two shards gives the same tensors as the single file;
+    an index that names a missing shard, or a tensor its shard does not hold, is an error that says so."""
+    import json
+
+    from stride_b200.weights.safetensors_io import SafetensorsError
+    model = write_random_model(tmp_path / "m", TINY_B, 2)
+    plan = model_plan(TINY_B)
+    whole = load_weights(model, plan, "cpu")
+    names = sorted(whole)
+    halves = {"model-00001-of-00002.safetensors": names[::2], "model-00002-of-00002.safetensors": names[1::2]}
+    sharded = tmp_path / "s"
+    sharded.mkdir()
+    (sharded / "config.json").write_text((model / "config.json").read_text())
+    for shard, keys in halves.items():
+        write_safetensors(sharded / shard, {n: whole[n] for n in keys})
+    index = {"metadata": {}, "weight_map": {n: shard for shard, keys in halves.items() for n in keys}}
+    (sharded / "model.safetensors.index.json").write_text(json.dumps(index))
+    again = load_weights(sharded, plan, "cpu")
+    assert set(again) == set(whole) and all(torch.equal(again[n], whole[n]) and again[n].dtype == whole[n].dtype for n in whole)
+    # one error for all that is wrong, as with a single file
+    del index["weight_map"]["model.norm.weight"]
+    (sharded / "model.safetensors.index.json").write_text(json.dumps(index))
+    with pytest.raises(WeightsError) as e:
+        load_weights(sharded, plan, "cpu")
+    assert e.value.missing == ["model.norm.weight"]
+    index["weight_map"]["model.norm.weight"] = "model-00001-of-00002.safetensors"       # it lives in the other shard
+    (sharded / "model.safetensors.index.json").write_text(json.dumps(index))
+    with pytest.raises(WeightsError, match="which it does not"):
+        load_weights(sharded, plan, "cpu")
+    index["weight_map"]["model.norm.weight"] = "model-00003-of-00002.safetensors"
+    (sharded / "model.safetensors.index.json").write_text(json.dumps(index))
+    with pytest.raises(SafetensorsError, match="cannot open"):
+        load_weights(sharded, plan, "cpu")
+    (sharded / "model.safetensors.index.json").write_text("[1, 2]")
+    with pytest.raises(WeightsError, match="not a shard index"):
+        load_weights(sharded, plan, "cpu")
