@@ -855,3 +855,14 @@ SB_API int sb_stage_decode(void* pool, int E, int B, int pad_slot, const int32_t
   for (int i = 0; i < B; ++i) rows[i] = i;
   return 0;
 }
+
+// Gives up every request: slots and pages go back, the queues are empty. For a caller that met an error in the middle
+// of a run and wants the pool as it found it (it has made sure that no step is still running on the GPU).
+SB_API void sb_sched_abort(void* sched) {
+  Sched* sc = static_cast<Sched*>(sched);
+  for (int id : sc->running) sc->release(sc->seqs[id]);
+  for (size_t id = 0; id < sc->seqs.size(); ++id)
+    if (sc->seqs[id].live) sc->retire((int)id);
+  sc->running.clear();
+  sc->waiting.clear();
+}

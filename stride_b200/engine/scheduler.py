@@ -123,6 +123,7 @@ def native_scheduler(lib):
         lib.sb_sched_commit.restype = None
         lib.sb_sched_commit.argtypes = [vp, ci, _I32P, _I32P, _F32P, ci, _U8P, _I32P, _U64P]
         lib.sb_sched_end_step.restype, lib.sb_sched_end_step.argtypes = None, [vp, _I32P, _I32P, ci]
+        lib.sb_sched_abort.restype, lib.sb_sched_abort.argtypes = None, [vp]
         lib._sb_sched_typed = True
     return lib
 
@@ -334,10 +335,32 @@ class Scheduler:
             torch.cuda.current_stream().synchronize()      # pages are only given back once the step has run
         self._end(ends, whole=False)
 
+    def abort(self) -> None:
+        """Give up every request (no callbacks): slots and pages go back to the cache, the queues are empty. Waits for
+        the GPU first, since steps may still be running on pages that are about to be handed out again."""
+        if str(getattr(self.engine, "device", "cpu")) != "cpu":
+            import torch
+            try:
+                torch.cuda.synchronize()
+            except RuntimeError:
+                pass
+        with self._mu:
+            self._incoming.clear()
+        self._requests.clear()
+        self._lib.sb_sched_abort(self._sched)
+
     def run(self, steps: Optional[int] = None) -> int:
         """Run until nothing is queued or running, or for `steps` engine steps. With a GPU engine the next step is
         queued before the tokens of the current one are read (see `_launch`), so the host's work per step overlaps
-        the GPU's. Returns the number of steps run."""
+        the GPU's. Returns the number of steps run. An error on the way (from the engine, the sampler or a callback)
+        aborts all requests before it is passed on, so that the engine's cache is left as it was found."""
+        try:
+            return self._run(steps)
+        except BaseException:
+            self.abort()
+            raise
+
+    def _run(self, steps: Optional[int]) -> int:
         if not self._can_pipeline():
             n = 0
             while (steps is None or n < steps) and self.step():

@@ -499,3 +499,25 @@ def test_the_random_workloads_met_every_case():
         pytest.skip("the comparison did not run in this session")
     assert any(p > 0 for p, _ in _PLAIN_RUNS)
     assert {"stop", "length", "empty_prompt", "context_length"} <= {r for _, reasons in _PLAIN_RUNS for r in reasons}
+
+
+@pytest.mark.parametrize("ahead", [False, True])
+def test_an_error_in_the_middle_of_a_run_leaves_the_cache_as_it_was(ahead):
+    """The engine fails at its seventh step: the error reaches the caller, every slot and page is back, and the same
+    engine serves the next run as if nothing had happened."""
+    class Failing(PipeEngine if ahead else FakeEngine):
+        fail_at = 7
+
+        def step(self, entries):
+            if len(self.batches) + 1 == self.fail_at:
+                self.fail_at = -1
+                raise EngineError("the seventh step fails")
+            return super().step(entries)
+    eng = Failing()
+    run = _run_ahead if ahead else _run
+    with pytest.raises(EngineError, match="seventh"):
+        run(eng, PROMPTS)
+    eng.cache.check()
+    assert eng.cache.free_pages() == eng.cache.total_pages() and len(eng.cache.free_slots) == 8
+    outs, _ = run(eng, PROMPTS)
+    assert [o["tokens"] for o in outs] == [o["tokens"] for o in _solo()]
