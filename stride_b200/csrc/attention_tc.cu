@@ -679,11 +679,11 @@ int launch(const AttnTcParams& p, int n_tiles, int n_items, cudaStream_t stream)
   constexpr int LD = D + 8;
   if (n_tiles > 0) {
     const size_t smem = static_cast<size_t>(5) * 64 * LD * sizeof(bf16) + static_cast<size_t>(64) * D * sizeof(float);
-    static bool set = false;
-    if (!set) {
+    static sb::DeviceOnce once;
+    if (once.needed()) {
       if (cudaFuncSetAttribute(attn_chunk_kernel<D>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess)
         return sb::fail("sb_attention_tc: cannot raise the shared memory limit");
-      set = true;
+      once.done();
     }
     sb::launch_pdl(attn_chunk_kernel<D>, dim3(n_tiles, p.Hkv), dim3(128), smem, stream, p);
   }
@@ -692,12 +692,12 @@ int launch(const AttnTcParams& p, int n_tiles, int n_items, cudaStream_t stream)
     const size_t smem_fused = static_cast<size_t>(16 * LD + 8 * 64 * LD) * sizeof(bf16);
     const size_t smem = static_cast<size_t>(16 * LD + 4 * 64 * D) * sizeof(bf16);
     static_assert(4 * 64 * D * sizeof(bf16) >= 4 * 16 * (D + 2) * sizeof(float), "the results must fit over the tiles");
-    static bool set = false;
-    if (!set) {
+    static sb::DeviceOnce once;
+    if (once.needed()) {
       if (cudaFuncSetAttribute(attn_decode_kernel<D, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess ||
           cudaFuncSetAttribute(attn_decode_kernel<D, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem_fused) != cudaSuccess)
         return sb::fail("sb_attention_tc: cannot raise the shared memory limit");
-      set = true;
+      once.done();
     }
     AttnTcParams pd = p;
     pd.work = p.work + 2 * n_tiles;
@@ -711,6 +711,11 @@ int launch(const AttnTcParams& p, int n_tiles, int n_items, cudaStream_t stream)
 }  // namespace
 
 // Floats of scratch that `sb_attention_tc` needs for `items` short entries and `chunks` key chunks.
+// How many CTAs of the fused rotate + append + attend decode kernel run at once on the current device: up to this many
+// (entries x key/value heads x chunks) the fused kernel is the faster choice, beyond it the separate rotation kernel is
+// (both give the same bits). Two CTAs of its shared-memory size fit an SM.
+SB_EXPORT int sb_attention_decode_rope_resident_ctas() { return 2 * sb::sm_count(); }
+
 SB_EXPORT int64_t sb_attention_tc_scratch(int items, int Hkv, int chunks, int D) {
   return static_cast<int64_t>(items) * Hkv * chunks * 16 * (D + 2);
 }

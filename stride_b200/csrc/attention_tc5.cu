@@ -383,11 +383,11 @@ SB_EXPORT int sb_attention_tc5(const void* q, void* out, const void* k_base, int
   const int kbox[2] = {kD, p.box_rows};
   if (!tensor_map_bf16(q, 3, qdims, qstrides, qbox, &map_q) || !tensor_map_bf16(k_base, 2, kdims, kstrides, kbox, &map_kv))
     return sb::fail("sb_attention_tc5: cuTensorMapEncodeTiled failed");
-  static bool attr_set = false;
-  if (!attr_set) {
+  static sb::DeviceOnce once;
+  if (once.needed()) {
     if (cudaFuncSetAttribute(attn_prefill_tc5_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBytes + 1024) != cudaSuccess)
       return sb::fail("sb_attention_tc5: cannot raise the shared memory limit");
-    attr_set = true;
+    once.done();
   }
   sb::launch_pdl(attn_prefill_tc5_kernel, dim3(n_tiles, Hkv), dim3(kThreads), static_cast<size_t>(kSmemBytes + 1024), stream, map_q, map_kv, p);
   return sb::check_launch("sb_attention_tc5");

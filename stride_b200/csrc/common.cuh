@@ -10,10 +10,12 @@
 #include <cuda_runtime.h>
 #include <stdint.h>
 
+#include <atomic>
 #include <cstdarg>
 #include <cstdio>
 #include <mutex>
 #include <set>
+#include <utility>
 
 #define SB_EXPORT extern "C" __attribute__((visibility("default")))
 
@@ -50,11 +52,43 @@ __device__ __forceinline__ void grid_launch_dependents() { asm volatile("griddep
 // make the SMs switch their L1 / shared split (which would keep a successor from becoming resident early).
 inline void prefer_max_shared(const void* kernel) {
   static std::mutex mu;
-  static std::set<const void*> done;
+  static std::set<std::pair<const void*, int>> done;     // a kernel's attributes are kept per device
+  int device = 0;
+  cudaGetDevice(&device);
   std::lock_guard<std::mutex> lock(mu);
-  if (done.insert(kernel).second)
+  if (done.insert({kernel, device}).second)
     cudaFuncSetAttribute(kernel, cudaFuncAttributePreferredSharedMemoryCarveout, cudaSharedmemCarveoutMaxShared);
 }
+
+// The number of SMs of the current device (148 on a B200), asked once per device: what grids of persistent CTAs and
+// "does everything run at once" decisions are sized by.
+inline int sm_count() {
+  static std::atomic<int> cached[64];
+  int d = 0;
+  cudaGetDevice(&d);
+  int n = cached[d & 63].load(std::memory_order_relaxed);
+  if (n <= 0) {
+    if (cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, d) != cudaSuccess || n <= 0) n = 148;
+    cached[d & 63].store(n, std::memory_order_relaxed);
+  }
+  return n;
+}
+
+// A kernel's attributes (its shared-memory limit among them) are kept per device: `DeviceOnce` remembers on which
+// devices a call site has set them. Usage: static DeviceOnce once; if (once.needed()) { set ...; once.done(); }
+struct DeviceOnce {
+  std::atomic<unsigned long long> mask{0};
+  bool needed() {
+    int d = 0;
+    cudaGetDevice(&d);
+    return !((mask.load(std::memory_order_acquire) >> (d & 63)) & 1ull);
+  }
+  void done() {
+    int d = 0;
+    cudaGetDevice(&d);
+    mask.fetch_or(1ull << (d & 63), std::memory_order_release);
+  }
+};
 
 template <class... KArgs, class... Args>
 inline void launch_pdl(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t stream, Args&&... args) {

@@ -294,7 +294,7 @@ SB_EXPORT int sb_rope_append(const float* qkv, int n_partials, int64_t partial_s
 SB_EXPORT int sb_swiglu(const float* gate_up, void* out, int out_dtype, int n, int I, cudaStream_t stream) {
   if (n <= 0) return 0;
   const int64_t total = static_cast<int64_t>(n) * I;
-  const int blocks = static_cast<int>((total + 255) / 256 < 148 * 16 ? (total + 255) / 256 : 148 * 16);
+  const int blocks = static_cast<int>((total + 255) / 256 < sb::sm_count() * 16 ? (total + 255) / 256 : sb::sm_count() * 16);
   if (out_dtype == 0) sb::launch_pdl(swiglu_kernel<float>, blocks, 256, 0, stream, gate_up, static_cast<float*>(out), n, I);
   else if (out_dtype == 1) sb::launch_pdl(swiglu_kernel<bf16>, blocks, 256, 0, stream, gate_up, static_cast<bf16*>(out), n, I);
   else return sb::fail("sb_swiglu: unsupported out dtype %d", out_dtype);

@@ -929,6 +929,8 @@ bool tensor_map(const void* base, int64_t rows, int64_t cols, int64_t ld, int bo
 SB_EXPORT int sb_gemm_tc_splits(int M, int K) {
   const int tiles_m = (M + kTileM - 1) / kTileM;
   const int kblocks = (K + kTileK - 1) / kTileK;
+  // (the literal is the SM count of the GPU this engine is written for: the ranges must follow from the weight's shape
+  // alone, never from the device that happens to run it, or two devices would add a token's sums in different orders)
   int splits = 148 / tiles_m;   // at most one wave of CTAs
   splits = min(splits, kblocks / 2);
   splits = max(splits, 1);
@@ -965,6 +967,7 @@ SB_EXPORT int sb_gemm_tc(const void* x, int64_t ldx, const void* w, int64_t ldw,
   int* status = status_word();
   if (!status) return sb::fail("sb_gemm_tc: cannot allocate the status word");
 
+  const long long sms = sb::sm_count(), pairs = sms / 2;
   GemmParams p{};
   p.out = static_cast<float*>(out);
   p.ldo = ldo;
@@ -982,7 +985,7 @@ SB_EXPORT int sb_gemm_tc(const void* x, int64_t ldx, const void* w, int64_t ldw,
     long long best = -1;
     for (int bn = 256; bn >= 32; bn -= 32) {
       const long long tiles = tm * ((n + bn - 1) / bn) * (fold ? 1 : splits);
-      const long long cost = ((tiles + 147) / 148) * (2 * bn > 128 + bn ? 2 * bn : 128 + bn);
+      const long long cost = ((tiles + sms - 1) / sms) * (2 * bn > 128 + bn ? 2 * bn : 128 + bn);
       if (best < 0 || cost < best) {
         best = cost;
         p.block_n = bn;
@@ -1001,7 +1004,7 @@ SB_EXPORT int sb_gemm_tc(const void* x, int64_t ldx, const void* w, int64_t ldw,
     // tokens: one CTA an SM with the deepest ring; its two accumulators overlap epilogue and main loop.
     const long long tiles = static_cast<long long>(epilogue == kSwiglu ? (half_rows + 63) / 64 : (M + kTileM - 1) / kTileM) *
                             ((n + p.block_n - 1) / p.block_n) * splits;
-    if (tiles > 2 * 148 && p.block_n <= 64) p.stages = max(2, min(p.stages, (kSmemBudget + 16 * 1024) / 3 / stage_bytes));
+    if (tiles > 2 * sms && p.block_n <= 64) p.stages = max(2, min(p.stages, (kSmemBudget + 16 * 1024) / 3 / stage_bytes));
   }
   p.kblocks_per_split = (kblocks + splits - 1) / splits;
   if ((kblocks + p.kblocks_per_split - 1) / p.kblocks_per_split != splits)
@@ -1015,8 +1018,8 @@ SB_EXPORT int sb_gemm_tc(const void* x, int64_t ldx, const void* w, int64_t ldw,
   bool wide = false;
   if (n > 256 && epilogue == kSwiglu) {
     const long long tn = (n + 255) / 256;
-    const long long pair_rounds = (((half_rows + 127) / 128) * tn + 73) / 74;
-    const long long wide_rounds = 2 * ((((half_rows + kTileM - 1) / kTileM) * tn + 147) / 148);
+    const long long pair_rounds = (((half_rows + 127) / 128) * tn + pairs - 1) / pairs;
+    const long long wide_rounds = 2 * ((((half_rows + kTileM - 1) / kTileM) * tn + sms - 1) / sms);
     wide = wide_rounds <= pair_rounds;
   }
   if (wide) {
@@ -1035,13 +1038,13 @@ SB_EXPORT int sb_gemm_tc(const void* x, int64_t ldx, const void* w, int64_t ldw,
       return sb::fail("sb_gemm_tc: cuTensorMapEncodeTiled failed (M %d N %d K %d)", M, n, K);
     const long long tiles = static_cast<long long>(p.tiles_m) * p.tiles_n;
     if (tiles > (1ll << 30)) return sb::fail("sb_gemm_tc: too many tiles");
-    static bool attr_set = false;
-    if (!attr_set) {
+    static sb::DeviceOnce once;
+    if (once.needed()) {
       if (cudaFuncSetAttribute(gemm_tc_wide_swiglu_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBudget + 2048) != cudaSuccess)
         return sb::fail("sb_gemm_tc: cannot raise the shared memory limit");
-      attr_set = true;
+      once.done();
     }
-    sb::launch_pdl(gemm_tc_wide_swiglu_kernel, dim3(static_cast<unsigned>(min(tiles, 148ll))), dim3(kFoldThreads),
+    sb::launch_pdl(gemm_tc_wide_swiglu_kernel, dim3(static_cast<unsigned>(min(tiles, sms))), dim3(kFoldThreads),
                    static_cast<size_t>(p.stages) * wide_stage + 1024, stream, ww, wx, p);
     return sb::check_launch("sb_gemm_tc");
   }
@@ -1056,7 +1059,7 @@ SB_EXPORT int sb_gemm_tc(const void* x, int64_t ldx, const void* w, int64_t ldw,
       // cycles of a K step of 64: the tensor cores (2 BN), or the bytes a CTA takes in (16 KB of weights and its half
       // of the token tile) at about 51 bytes a cycle; times whole rounds of 74 pairs
       const long long step = max(2ll * bn, (16384ll + 64 * bn) / 51);
-      const long long cost = ((tm * ((n + bn - 1) / bn) + 73) / 74) * step;
+      const long long cost = ((tm * ((n + bn - 1) / bn) + pairs - 1) / pairs) * step;
       if (best < 0 || cost < best) {
         best = cost;
         bn_best = bn;
@@ -1078,14 +1081,14 @@ SB_EXPORT int sb_gemm_tc(const void* x, int64_t ldx, const void* w, int64_t ldw,
       return sb::fail("sb_gemm_tc: cuTensorMapEncodeTiled failed (M %d N %d K %d)", M, n, K);
     const long long tiles = static_cast<long long>(p.tiles_m) * p.tiles_n;
     if (tiles > (1ll << 30)) return sb::fail("sb_gemm_tc: too many tiles");
-    const dim3 grid(static_cast<unsigned>(2 * min(tiles, 74ll)));
+    const dim3 grid(static_cast<unsigned>(2 * min(tiles, pairs)));
     const size_t psmem = static_cast<size_t>(p.stages) * pair_stage + 1024;
-    static bool attr_set = false;
-    if (!attr_set) {
+    static sb::DeviceOnce once;
+    if (once.needed()) {
       if (cudaFuncSetAttribute(gemm_tc_pair_kernel<kStore>, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBudget + 2048) != cudaSuccess ||
           cudaFuncSetAttribute(gemm_tc_pair_kernel<kSwiglu>, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBudget + 2048) != cudaSuccess)
         return sb::fail("sb_gemm_tc: cannot raise the shared memory limit");
-      attr_set = true;
+      once.done();
     }
     if (epilogue == kStore)
       sb::launch_pdl_cluster(gemm_tc_pair_kernel<kStore>, grid, dim3(kFoldThreads), psmem, stream, dim3(2, 1, 1), pw, px, p);
@@ -1106,12 +1109,12 @@ SB_EXPORT int sb_gemm_tc(const void* x, int64_t ldx, const void* w, int64_t ldw,
   if (total_tiles > (1ll << 30)) return sb::fail("sb_gemm_tc: too many tiles");
   const size_t smem = static_cast<size_t>(p.stages) * stage_bytes + 1024;
   if (fold) {
-    const dim3 grid(static_cast<unsigned>(min(total_tiles, 148ll)));
-    static bool attr_set = false;
-    if (!attr_set) {
+    const dim3 grid(static_cast<unsigned>(min(total_tiles, sms)));
+    static sb::DeviceOnce once;
+    if (once.needed()) {
       if (cudaFuncSetAttribute(gemm_tc_fold_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBudget + 2048) != cudaSuccess)
         return sb::fail("sb_gemm_tc: cannot raise the shared memory limit");
-      attr_set = true;
+      once.done();
     }
     sb::launch_pdl(gemm_tc_fold_kernel, grid, dim3(kFoldThreads), smem, stream, map_w, map_x, p);
     return sb::check_launch("sb_gemm_tc");
@@ -1119,29 +1122,29 @@ SB_EXPORT int sb_gemm_tc(const void* x, int64_t ldx, const void* w, int64_t ldw,
   // Persistent CTAs: as many as fit the GPU at once (by shared and tensor memory), each walking tiles.
   int per_sm = static_cast<int>((227 * 1024) / (smem + 2048));
   per_sm = max(1, min(per_sm, 512 / static_cast<int>(tmem_alloc_cols(2 * p.block_n))));
-  const long long resident = 148ll * per_sm;
+  const long long resident = sms * per_sm;
   const bool multi = total_tiles > resident;
   if (!multi && (p.tiles_n > 65535 || splits > 65535)) return sb::fail("sb_gemm_tc: grid too large");
   const dim3 grid(static_cast<unsigned>(multi ? resident : total_tiles));
 #define SB_LAUNCH_M(EPI, MULTI)                                                                         \
   do {                                                                                                  \
-    static bool attr_set = false;                                                                       \
-    if (!attr_set) {                                                                                    \
+    static sb::DeviceOnce once;                                                                       \
+    if (once.needed()) {                                                                                    \
       if (cudaFuncSetAttribute(gemm_tc_kernel<EPI, MULTI>, cudaFuncAttributeMaxDynamicSharedMemorySize, \
                                kSmemBudget + 2048) != cudaSuccess)                                      \
         return sb::fail("sb_gemm_tc: cannot raise the shared memory limit");                            \
-      attr_set = true;                                                                                  \
+      once.done();                                                                                  \
     }                                                                                                   \
     sb::launch_pdl(gemm_tc_kernel<EPI, MULTI>, grid, dim3(kThreads), smem, stream, map_w, map_x, p);    \
   } while (0)
 #define SB_LAUNCH_S(EPI)                                                                                \
   do {                                                                                                  \
-    static bool attr_set = false;                                                                       \
-    if (!attr_set) {                                                                                    \
+    static sb::DeviceOnce once;                                                                       \
+    if (once.needed()) {                                                                                    \
       if (cudaFuncSetAttribute(gemm_tc_single_kernel<EPI>, cudaFuncAttributeMaxDynamicSharedMemorySize, \
                                kSmemBudget + 2048) != cudaSuccess)                                      \
         return sb::fail("sb_gemm_tc: cannot raise the shared memory limit");                            \
-      attr_set = true;                                                                                  \
+      once.done();                                                                                  \
     }                                                                                                   \
     sb::launch_pdl(gemm_tc_single_kernel<EPI>, dim3(p.tiles_m, p.tiles_n, splits), dim3(kThreads), smem, stream, map_w, map_x, p); \
   } while (0)

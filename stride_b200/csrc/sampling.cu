@@ -5,7 +5,8 @@
 //
 // Temperature sampling restates arhaamatiq/stride's host sampler
 // (src/scheduler.cpp:193-243) without sorting: tokens are ranked by (logit
-// descending, index ascending), weight_i = exp((l_i - l_max) / T) in 64-bit,
+// descending, index ascending), weight_i = exp((l_i - l_max) / T) in 64-bit (kept
+// as an integer multiple of 2^-40, so that sums do not depend on their order),
 // u = uniform * sum of weights, and the token is the first in rank order whose
 // cumulative weight exceeds u. The rank order is walked by a radix search over
 // the logit's bit pattern (four passes of eight bits, weighted histograms).
@@ -79,17 +80,25 @@ __global__ void __launch_bounds__(kThreads) argmax_kernel(const float* __restric
   }
 }
 
+// Weights are kept as integers, w_i = floor(exp((l_i - l_max) / T) * 2^40) with the exponential in 64-bit floating
+// point: integer sums do not depend on the order in which threads add, so the histograms below, and with them the
+// token, are the same in every run and every batch. (The largest logit has weight 2^40 exactly; a token whose weight
+// is below 2^-40 of it is never drawn; a vocabulary of four million tokens still sums below 2^63.)
+__device__ __forceinline__ unsigned long long fixed_weight(float v, double top, double T) {
+  return __double2ull_rd(exp((static_cast<double>(v) - top) / T) * 1099511627776.0);
+}
+
 __global__ void __launch_bounds__(kThreads) sample_temperature_kernel(
     const float* __restrict__ logits, int64_t ld, int vocab, const float* __restrict__ temperatures,
     const unsigned long long* __restrict__ seeds, const int32_t* __restrict__ lengths, int32_t* __restrict__ tokens,
     float* __restrict__ values, const int32_t* __restrict__ scatter_index, int32_t* __restrict__ scatter,
     const int* __restrict__ watch) {
-  __shared__ double hist[256];
+  __shared__ unsigned long long hist[256];
   __shared__ int count[256];
   __shared__ float red[32];
-  __shared__ double dred[32];
+  __shared__ unsigned long long total_s;
   __shared__ uint32_t prefix_s;
-  __shared__ double u_s;
+  __shared__ unsigned long long u_s;
   __shared__ int found_s;
   sb::grid_launch_dependents();
   sb::grid_dependency_wait();
@@ -106,28 +115,29 @@ __global__ void __launch_bounds__(kThreads) sample_temperature_kernel(
   mx = sb::block_max(mx, red);
   const double top = static_cast<double>(mx);
 
-  // Sum of the weights, in a fixed order: per thread ascending, lanes by shuffle, warps left to right.
-  double sum = 0.0;
+  if (t == 0) total_s = 0;
+  __syncthreads();
+  unsigned long long sum = 0;
   for (int i = t; i < vocab; i += kThreads) {
     const float v = l[i];
-    if (v == v) sum += exp((static_cast<double>(v) - top) / T);
+    if (v == v) sum += fixed_weight(v, top, T);
   }
   for (int o = 16; o > 0; o >>= 1) sum += __shfl_xor_sync(0xffffffffu, sum, o);
-  if ((t & 31) == 0) dred[t >> 5] = sum;
+  if ((t & 31) == 0) atomicAdd(&total_s, sum);
   __syncthreads();
   if (t == 0) {
-    double total = 0.0;
-    for (int i = 0; i < kThreads / 32; ++i) total += dred[i];
+    // u = floor(uniform * total), uniform = (r >> 11) * 2^-53: a 53 x 62 bit product, shifted down by 53
     const unsigned long long r =
         splitmix64(seeds[row] ^ (static_cast<unsigned long long>(static_cast<uint32_t>(lengths[row])) * 0x9E3779B97F4A7C15ULL));
-    u_s = static_cast<double>(r >> 11) * (1.0 / 9007199254740992.0) * total;
+    const unsigned long long m = r >> 11, total = total_s;
+    u_s = (__umul64hi(m, total) << 11) | ((m * total) >> 53);
     prefix_s = 0;
   }
   __syncthreads();
 
   for (int shift = 24; shift >= 0; shift -= 8) {
     for (int b = t; b < 256; b += kThreads) {
-      hist[b] = 0.0;
+      hist[b] = 0;
       count[b] = 0;
     }
     __syncthreads();
@@ -139,12 +149,12 @@ __global__ void __launch_bounds__(kThreads) sample_temperature_kernel(
       const uint32_t key = order_key(v);
       if ((key & mask) != prefix) continue;
       const int b = (key >> shift) & 0xFF;
-      atomicAdd(&hist[b], exp((static_cast<double>(v) - top) / T));
+      atomicAdd(&hist[b], fixed_weight(v, top, T));
       atomicAdd(&count[b], 1);
     }
     __syncthreads();
     if (t == 0) {
-      double u = u_s, cum = 0.0;
+      unsigned long long u = u_s, cum = 0;
       int chosen = -1, lowest = 0;
       for (int b = 255; b >= 0; --b) {
         if (count[b] == 0) continue;
@@ -155,10 +165,10 @@ __global__ void __launch_bounds__(kThreads) sample_temperature_kernel(
         }
         cum += hist[b];
       }
-      if (chosen < 0) {  // u is not below the total (rounding): the last token in rank order
+      if (chosen < 0) {  // only tokens of weight 0 are left: the last token in rank order
         chosen = lowest;
-        cum = 0.0;
-        u = hist[lowest];  // past every token of the bucket, so the last one is taken below
+        cum = 0;
+        u = hist[lowest];
       }
       u_s = u - cum;
       prefix_s = prefix | (static_cast<uint32_t>(chosen) << shift);
@@ -182,13 +192,17 @@ __global__ void __launch_bounds__(kThreads) sample_temperature_kernel(
     int first = -1;
     for (int i = 0; i < vocab && first < 0; ++i)
       if (l[i] == l[i] && order_key(l[i]) == key) first = i;
-    const double w = exp((static_cast<double>(l[first]) - top) / T);
-    int skip = w > 0.0 ? static_cast<int>(fmin(u_s / w, static_cast<double>(found_s - 1))) : found_s - 1;
-    int pick = first;
-    for (int i = first; i < vocab; ++i) {
-      if (l[i] == l[i] && order_key(l[i]) == key) {
-        pick = i;
-        if (skip-- == 0) break;
+    int pick = 0;
+    if (first >= 0) {     // (a row without a single number has no such token: token 0 then)
+      const unsigned long long w = fixed_weight(l[first], top, T);
+      unsigned long long skip = w > 0 ? u_s / w : static_cast<unsigned long long>(found_s - 1);
+      if (skip > static_cast<unsigned long long>(found_s - 1)) skip = found_s - 1;
+      pick = first;
+      for (int i = first; i < vocab; ++i) {
+        if (l[i] == l[i] && order_key(l[i]) == key) {
+          pick = i;
+          if (skip-- == 0) break;
+        }
       }
     }
     tokens[row] = poisoned(pick, watch);

@@ -267,6 +267,20 @@ def attention_tc_scratch(items: int, num_kv_heads: int, chunks: int, head_dim: i
     return items * num_kv_heads * chunks * 16 * (head_dim + 2)
 
 
+_decode_rope_limit = None
+
+
+def attention_decode_rope_limit() -> int:
+    """Up to this many CTAs (entries x key/value heads x chunks) `attention_decode_rope` runs all at once on this
+    device and is the faster choice; asked of the library once."""
+    global _decode_rope_limit
+    if _decode_rope_limit is None:
+        lib = library("attention_tc")
+        lib.sb_attention_decode_rope_resident_ctas.restype = c_int
+        _decode_rope_limit = int(lib.sb_attention_decode_rope_resident_ctas())
+    return _decode_rope_limit
+
+
 def attention_tc(q, out, cache_layer, block_table, entry_meta, work, n_tiles: int, n_items: int, chunks: int,
                  scratch, num_heads: int, num_kv_heads: int, head_dim: int, window: int, scale: float,
                  counters=None) -> None:

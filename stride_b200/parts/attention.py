@@ -124,7 +124,7 @@ class AttentionMixer(Mixer):
             tc5 = ops.attention_tc5_supported(self.num_heads, self.num_kv_heads, D, cache.page_size)
             plan = self._tc_plan(ctx, G, 128 if tc5 else 64)
         if (plan is not None and plan[1] == 0 and cache.writes and self._rotary == D
-                and plan[2] * self.num_kv_heads * plan[3] <= 296):
+                and plan[2] * self.num_kv_heads * plan[3] <= ops.attention_decode_rope_limit()):
             # only decoded tokens and very short portions, few enough for all CTAs to run at once: rotation and append
             # happen inside the decode kernel (the same bits; with more CTAs than that the separate kernel is faster)
             work, _, n_items, chunks = plan

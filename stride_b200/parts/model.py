@@ -81,8 +81,7 @@ class DecoderModel:
         for i, e in enumerate(self.spec.schedule):
             self.blocks[e.layer].forward(ctx, stream, caches[i])
         if count == 0:
-            stream.fold()
-            return None
+            return None        # pending partial sums die with the stream: nobody reads h after the last layer
         rows = ws.raw("model.head_rows", (ws.max_tokens, H), torch.float32)[:count]
         ops.gather_rows(stream.h, logit_rows, rows, partials=stream.take_pending())
         x = ws.raw("model.head_x", (ws.max_tokens, H), ctx.act_dtype)[:count]

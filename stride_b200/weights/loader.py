@@ -43,9 +43,12 @@ def check_plan(plan: dict, available: dict, source: str) -> None:
 
 
 def storage_dtype(dtype: torch.dtype, integer: bool) -> torch.dtype:
+    """How a checkpoint tensor is kept: bfloat16 as it is, 32- and 64-bit floating point as float32, and float16 as
+    float32 too (every float16 value is a float32 value, while bfloat16 would drop three bits of its mantissa without a
+    word); integers as int32."""
     if integer or not dtype.is_floating_point:
         return torch.int32
-    return torch.float32 if dtype in (torch.float32, torch.float64) else torch.bfloat16
+    return torch.bfloat16 if dtype == torch.bfloat16 else torch.float32
 
 
 def _open_files(model_dir) -> dict:

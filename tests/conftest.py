@@ -157,9 +157,26 @@ def logit_tolerance(dtype: str, reference: torch.Tensor, noise: float | None = N
     return 3e-2 * rms
 
 
-def bf16_noise(cfg, weights, tokens) -> float:
-    """max |plain with bfloat16 rounding - plain in float32| over all logits of the sequence."""
+class Noise(float):
+    """max |plain with bfloat16 rounding - plain in float32| over a set of logits; `.mean` is the mean of the same."""
+    mean = 0.0
+
+
+def bf16_noise(cfg, weights, tokens, rows=None) -> Noise:
+    """The bfloat16 rounding noise of the plain implementation over all logits of the sequence (or at `rows`)."""
     import plain_llama as plain
-    a = plain.forward(cfg, weights, tokens, torch.float32, torch.bfloat16)
-    b = plain.forward(cfg, weights, tokens, torch.float32, None)
-    return float((a - b).abs().max())
+    a = plain.forward(cfg, weights, tokens, torch.float32, torch.bfloat16, rows=rows)
+    b = plain.forward(cfg, weights, tokens, torch.float32, None, rows=rows)
+    noise = Noise(float((a - b).abs().max()))
+    noise.mean = float((a - b).abs().mean())
+    return noise
+
+
+def check_mean_deviation(got: torch.Tensor, want: torch.Tensor, noise, what: str) -> None:
+    """The second yardstick of the bfloat16 comparison, for whole sequences: the MEAN deviation of the engine from the
+    plain implementation (rounding at the same places) stays within half of the MEAN of bfloat16's own rounding noise, the
+    factor the maximum is held to as well. The maximum alone is set by the single worst logit and would let a defect pass
+    that moves every logit a little. (Measured ratios of the means: 0.15 on tiny configuration D at 300 tokens, 0.29 at
+    the 1B layer sizes over 2,048 tokens, where the same bits come out of 256-token portions through other kernels.)"""
+    mean = float((got - want).abs().mean())
+    assert mean <= 0.5 * noise.mean, f"{what}: mean |diff| {mean:.3e} > 0.5 x the mean rounding noise {noise.mean:.3e}"

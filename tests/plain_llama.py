@@ -225,8 +225,9 @@ def swiglu(x: torch.Tensor, w_gate: torch.Tensor, w_up: torch.Tensor) -> torch.T
 # --------------------------------------------------------------------------- model
 
 def forward(cfg: PlainConfig, w: dict, tokens, dtype=torch.float32, act_dtype=None,
-            window: int = 0) -> torch.Tensor:
-    """Logits [T, vocab] at every position of one whole sequence.
+            window: int = 0, rows=None) -> torch.Tensor:
+    """Logits [T, vocab] at every position of one whole sequence, or [len(rows), vocab] at the
+    positions `rows` alone (the layers run on the whole sequence either way).
 
     Order of a block: norm, q/k/v, rope on q and k, attention, o_proj added to the
     residual, norm, SwiGLU, down_proj added to the residual (src/engine.cpp:166-237);
@@ -253,6 +254,8 @@ def forward(cfg: PlainConfig, w: dict, tokens, dtype=torch.float32, act_dtype=No
         x = _round(rms_norm(h, w[p + "post_attention_layernorm.weight"], cfg.rms_norm_eps), act_dtype)
         z = _round(swiglu(x, w[p + "mlp.gate_proj.weight"], w[p + "mlp.up_proj.weight"]), act_dtype)
         h = h + z @ w[p + "mlp.down_proj.weight"].to(dtype).T
+    if rows is not None:
+        h = h[torch.as_tensor(list(rows), dtype=torch.long)]
     x = _round(rms_norm(h, w["model.norm.weight"], cfg.rms_norm_eps), act_dtype)
     head = w["lm_head.weight"] if "lm_head.weight" in w else w["model.embed_tokens.weight"]
     return x @ head.to(dtype).T

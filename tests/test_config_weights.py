@@ -71,7 +71,7 @@ def test_safetensors_round_trip_and_dtypes(tmp_path):
     assert sorted(f.names()) == list("abcde") and f.shape("a") == (3, 5) and f.dtype("c") == torch.int64
     for k in t:
         assert torch.equal(f.get(k), t[k])
-    assert storage_dtype(torch.bfloat16, False) == torch.bfloat16 and storage_dtype(torch.float16, False) == torch.bfloat16
+    assert storage_dtype(torch.bfloat16, False) == torch.bfloat16 and storage_dtype(torch.float16, False) == torch.float32
     assert storage_dtype(torch.float32, False) == torch.float32 and storage_dtype(torch.int64, False) == torch.int32
     with pytest.raises(SafetensorsError, match="missing tensor 'zz'"):
         f.get("zz")
@@ -178,3 +178,15 @@ def test_sharded_checkpoints_load_like_the_single_file(tmp_path):
     (sharded / "model.safetensors.index.json").write_text("[1, 2]")
     with pytest.raises(WeightsError, match="not a shard index"):
         load_weights(sharded, plan, "cpu")
+
+
+def test_float16_checkpoints_are_widened_exactly(tmp_path):
+    """A float16 tensor is kept as float32 (exact), never as bfloat16, which would drop mantissa bits silently."""
+    plan = model_plan(TINY_A)
+    tensors = random_tensors(TINY_A, 3, dtype=torch.float32)
+    half = {n: t.to(torch.float16) for n, t in tensors.items()}
+    (tmp_path / "config.json").write_text("{}")
+    write_safetensors(tmp_path / "model.safetensors", half)
+    got = load_weights(tmp_path, plan, "cpu")
+    for n, t in half.items():
+        assert got[n].dtype == torch.float32 and torch.equal(got[n], t.to(torch.float32))

@@ -22,7 +22,8 @@ def _prompts(name, lengths, seed=50):
 
 @pytest.mark.parametrize("name,lengths", [("A", [5, 9, 13, 17]), ("B", [1, 40, 23, 8, 31, 17])])
 def test_greedy_generation_matches_plain_float32(name, lengths, model_dirs):
-    """BASELINE-style prompts; float32 greedy tokens equal the plain implementation's, token by token."""
+    """Prompts of the two tiny workloads (4 requests of 5 to 17 tokens; 6 of 1 to 40, fed in portions of 7); float32 greedy
+    tokens equal the plain implementation's, token by token."""
     from stride_b200 import LLM
     cfg, w = plain.load_plain(model_dirs[name])
     prompts = _prompts(name, lengths)

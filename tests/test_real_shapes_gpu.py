@@ -7,7 +7,7 @@ import pytest
 import torch
 
 import plain_llama as plain
-from conftest import bf16_noise, logit_tolerance, random_tokens
+from conftest import bf16_noise, check_mean_deviation, logit_tolerance, random_tokens
 
 pytestmark = pytest.mark.gpu
 
@@ -168,3 +168,76 @@ def test_serving_under_pressure_keeps_every_request_exact():
         (want,) = alone.generate([prompts[i]], new, temperature=0.7, seed=11 + i)
         assert got[i].tokens == want.tokens, f"request {i}"
         assert got[i].values == want.values, f"request {i}: the chosen logits differ in bits"
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_a_prompt_of_2048_tokens_whole_in_portions_and_in_company(dtype):
+    """The step the prefill figure is measured on, at the 1B layer sizes (two layers): one prompt of 2,048 tokens fed
+    whole, in portions of 256, and as 1,100 + 948 beside two requests that decode. Above 512 tokens the projections with
+    K ranges add their ranges in registers, above 1,536 rows the norm runs a warp per row, and the tcgen05 attention walks
+    sixteen tiles of one request: the logits at the first place, at tile and portion edges and at the last place are the
+    same bits in all three, and the plain implementation's within tolerance."""
+    from stride_b200 import Engine, EngineOptions, StepEntry
+    from stride_b200.weights.random_init import random_tensors
+    cfg_dict = SHAPES["1b"]
+    tensors = random_tensors(cfg_dict, seed=4, std=0.05, gain_std=0.1)
+    cfg = plain.PlainConfig.from_dict(cfg_dict)
+    T = 2048
+    mine = random_tokens(cfg.vocab_size, T, 77)
+    others = [random_tokens(cfg.vocab_size, 90, 78), random_tokens(cfg.vocab_size, 140, 79)]
+    places = sorted({0, 1, 63, 64, 127, 128, 129, 255, 256, 257, 511, 512, 513, 767, 768, 1023, 1024, 1099, 1100, 1101, 1279,
+                     1280, 1535, 1536, 1537, 1791, 1792, 1919, 1920, 2046, 2047})
+    act = torch.bfloat16 if dtype == "bfloat16" else None
+    want = plain.forward(cfg, tensors, mine, torch.float32, act, rows=places)
+    noise = bf16_noise(cfg, tensors, mine, rows=places) if act is not None else None
+
+    def engine(seed):
+        return Engine(None, EngineOptions(dtype=dtype, max_rows=2048, max_full_rows=64, max_slots=4, kv_pages=40, page_size=64,
+                                          max_context=2048, kv_shuffle_seed=seed), config=cfg_dict, tensors=tensors)
+
+    def feed(eng, slot, cuts, company=None):
+        """Feeds `mine` in the portions `cuts`; returns the logits at `places`, in order."""
+        cm, out = eng.cache, []
+        for a, b in cuts:
+            assert cm.ensure(slot, b)
+            me = StepEntry(slot, a, mine[a:b], [p - a for p in places if a <= p < b])
+            entries = [me] if company is None else company(me)
+            lg = eng.step(entries)
+            at = sum(len(e.want) for e in entries[:entries.index(me)])
+            out.append(lg[at:at + len(me.want)].clone())
+        return torch.cat(out).cpu()
+
+    eng = engine(0)
+    whole = feed(eng, eng.cache.acquire_slot(), [(0, T)])
+    tol = logit_tolerance(dtype, want, noise)
+    assert (whole - want).abs().max() <= tol, f"{dtype} whole: {(whole - want).abs().max():.3e} > {tol:.3e}"
+    if noise is not None:
+        check_mean_deviation(whole, want, noise, "2,048 tokens whole")
+    del eng
+
+    eng = engine(3)
+    portions = feed(eng, eng.cache.acquire_slot(), [(a, a + 256) for a in range(0, T, 256)])
+    assert torch.equal(whole, portions), f"portions of 256 differ from the whole prompt by {(whole - portions).abs().max():.3e}"
+    del eng
+
+    eng = engine(5)
+    cm = eng.cache
+    slots = [cm.acquire_slot() for _ in range(3)]
+    fed = [60, 100]
+    for j in (0, 1):                   # the two others: most of their prompt first ..
+        assert cm.ensure(slots[1 + j], fed[j])
+        eng.step([StepEntry(slots[1 + j], 0, others[j][:fed[j]], [])])
+
+    def company(me):                   # .. then each decodes one token beside every portion of mine
+        entries = []
+        for j in (0, 1):
+            assert cm.ensure(slots[1 + j], fed[j] + 1)
+            entries.append(StepEntry(slots[1 + j], fed[j], others[j][fed[j]:fed[j] + 1], [0]))
+            fed[j] += 1
+        return [entries[0], me, entries[1]]
+
+    mixed = feed(eng, slots[0], [(0, 1100), (1100, T)], company)
+    assert torch.equal(whole, mixed), f"1,100 + 948 beside two decoding requests differ from the whole prompt by {(whole - mixed).abs().max():.3e}"
+    if dtype == "bfloat16":
+        from stride_b200.kernels import ops
+        assert ops.gemm_tc_status() == 0 and ops.attention_tc5_status() == 0

@@ -8,7 +8,7 @@ import pytest
 import torch
 
 import plain_llama as plain
-from conftest import TINY, TraceRun, bf16_noise, logit_tolerance, random_tokens
+from conftest import TINY, TraceRun, bf16_noise, check_mean_deviation, logit_tolerance, random_tokens
 
 pytestmark = pytest.mark.gpu
 
@@ -30,10 +30,16 @@ def _plain_logits(model_dir, requests, dtype):
 
 
 def _compare(got, want, dtype, what, noise=None):
+    if want is None:        # this configuration and precision is held to bit-equality between the replays alone
+        return
     tol = logit_tolerance(dtype, want, noise)
     diff = (got - want).abs()
     worst = int(diff.max(dim=1).values.argmax())
     assert diff.max() <= tol, f"{what}: max |diff| {diff.max():.3e} > {tol:.3e}, first bad place {int((diff.max(dim=1).values > tol).nonzero()[0])}, worst {worst}"
+
+
+def _cut(logits, a, b):
+    return None if logits is None else logits[a:b]
 
 
 class _Bits:
@@ -65,12 +71,15 @@ def _portions(n, sizes):
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
 @pytest.mark.parametrize("name", ["A", "B", "C", "D", "U"])
 def test_replay_modes(name, dtype, model_dirs, tmp_path):
-    if name == "U" and dtype == "bfloat16":
-        pytest.skip("U makes every key carry weight 1/T; losing one moves logits by ~1e-3, which float32 shows and bfloat16 cannot resolve")
     cfg, _, page = TINY[name]
     vocab = cfg["vocab_size"]
     reqs = _requests(name)
-    want = _plain_logits(model_dirs[name], reqs, dtype)
+    if name == "U" and dtype == "bfloat16":
+        # U makes every key carry weight 1/T; losing one moves logits by ~1e-3, which float32 shows and bfloat16 cannot
+        # resolve: no comparison with the plain implementation here, but the four replays still have to agree in bits
+        want = [(None, None)] * len(reqs)
+    else:
+        want = _plain_logits(model_dirs[name], reqs, dtype)
     # The pool holds the two longest requests plus one page: mixed replay must reuse pages.
     per = lambda n: -(-n // page) * page
     longest = sorted((per(len(r)) for r in reqs), reverse=True)
@@ -82,23 +91,25 @@ def test_replay_modes(name, dtype, model_dirs, tmp_path):
         for i, r in enumerate(reqs):
             s = tr.run([(f"w{i}", r, range(len(r)))], end=[f"w{i}"])
             _compare(tr.logits(s, vocab), want[i][0], dtype, f"{name} whole request {i}", want[i][1])
+            if want[i][1] is not None:
+                check_mean_deviation(tr.logits(s, vocab), want[i][0], want[i][1], f"{name} whole request {i}")
             bits.check(i, 0, tr.logits(s, vocab), f"{name} whole request {i}")
         # 2. all but the last 32 tokens in one step, then one by one
         for i, r in enumerate(reqs):
             cut = max(1, len(r) - 32)
             s = tr.run([(f"d{i}", r[:cut], [cut - 1])])
-            _compare(tr.logits(s, vocab), want[i][0][cut - 1:cut], dtype, f"{name} request {i} prefill end", want[i][1])
+            _compare(tr.logits(s, vocab), _cut(want[i][0], cut - 1, cut), dtype, f"{name} request {i} prefill end", want[i][1])
             bits.check(i, cut - 1, tr.logits(s, vocab), f"{name} request {i} prefill end")
             for p in range(cut, len(r)):
                 s = tr.run([(f"d{i}", r[p:p + 1], [0])], end=[f"d{i}"] if p == len(r) - 1 else [])
-                _compare(tr.logits(s, vocab), want[i][0][p:p + 1], dtype, f"{name} request {i} decode at {p}", want[i][1])
+                _compare(tr.logits(s, vocab), _cut(want[i][0], p, p + 1), dtype, f"{name} request {i} decode at {p}", want[i][1])
                 bits.check(i, p, tr.logits(s, vocab), f"{name} request {i} decode at {p}")
         # 3. portions of changing size, down to two tokens
         for i, r in enumerate(reqs):
             cuts = _portions(len(r), [7, 2, 19, 3, 2, 31, 5])
             for j, (a, b) in enumerate(cuts):
                 s = tr.run([(f"p{i}", r[a:b], range(b - a))], end=[f"p{i}"] if j == len(cuts) - 1 else [])
-                _compare(tr.logits(s, vocab), want[i][0][a:b], dtype, f"{name} request {i} portion {a}:{b}", want[i][1])
+                _compare(tr.logits(s, vocab), _cut(want[i][0], a, b), dtype, f"{name} request {i} portion {a}:{b}", want[i][1])
                 bits.check(i, a, tr.logits(s, vocab), f"{name} request {i} portion {a}:{b}")
         # 4. mixed: requests start at different steps, portions beside single tokens, pages reused
         fed = [0] * len(reqs)
@@ -126,7 +137,7 @@ def test_replay_modes(name, dtype, model_dirs, tmp_path):
             got = tr.logits(s, vocab)
             at = 0
             for i, a, b in spans:
-                _compare(got[at:at + b - a], want[i][0][a:b], dtype, f"{name} mixed step {steps} request {i} {a}:{b}", want[i][1])
+                _compare(got[at:at + b - a], _cut(want[i][0], a, b), dtype, f"{name} mixed step {steps} request {i} {a}:{b}", want[i][1])
                 bits.check(i, a, got[at:at + b - a], f"{name} mixed step {steps} request {i} {a}:{b}")
                 at += b - a
             steps += 1
