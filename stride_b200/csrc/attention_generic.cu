@@ -13,6 +13,7 @@
 // Counterparts in arhaamatiq/stride: AttentionPage and AttentionCombine
 // (src/kernel_common.h:90-253, 256-309), which cut by 64-token page.
 #include "common.cuh"
+#include "step_ops.h"
 
 SB_DEFINE_LAST_ERROR()
 
@@ -127,4 +128,15 @@ SB_EXPORT int sb_attention_generic(const void* q, void* out, int dtype, const vo
   else if (dtype == 1) sb::launch_pdl(attention_generic_kernel<bf16, bf16, bf16>, grid, dim3(kTile), smem, stream, p);
   else return sb::fail("sb_attention_generic: unsupported dtype %d", dtype);
   return sb::check_launch("sb_attention_generic");
+}
+
+// ------------------------------------------------------------------ operation of the native step program (step_ops.h)
+// i: 0 q, 1 out, 2 dtype, 3 cache layer, 4 block table, 5 pages per sequence, 6 page size, 7 page stride, 8 v offset,
+//    9 head stride, 10 Hq, 11 Hkv, 12 D, 13 window; f: 0 scale
+SB_EXPORT int sb_op_attention_generic(const SbOp* op, const SbStep* s, void* stream) {
+  using namespace sbstep;
+  return sb_attention_generic(ptr<const void>(op->i[0]), ptr<void>(op->i[1]), (int)op->i[2], ptr<const void>(op->i[3]),
+                              ptr<const int32_t>(op->i[4]), (int)op->i[5], (int)op->i[6], op->i[7], op->i[8], op->i[9], positions(s),
+                              slots(s), s->n, (int)op->i[10], (int)op->i[11], (int)op->i[12], (int)op->i[13], static_cast<float>(op->f[0]),
+                              static_cast<cudaStream_t>(stream));
 }

@@ -27,6 +27,7 @@
 // (src/kernel_common.h:90-309), which are scalar.
 #include "attention_math.cuh"
 #include "common.cuh"
+#include "step_ops.h"
 #include "noalloc.h"
 
 
@@ -846,4 +847,34 @@ SB_EXPORT int sb_attention_decode_noalloc(const void* q, void* out, const void* 
   if (int rc = noalloc_scratch(&scratch)) return rc;
   return sb_attention_tc(q, out, k_base, block_table, max_pages, page_size, page_stride, v_offset, head_stride, meta,
                          meta_stride, items, 0, n_items, chunks, scratch, nullptr, Hq, Hkv, D, window, scale, stream);
+}
+
+// ------------------------------------------------------------------ operation of the native step program (step_ops.h)
+// The decode items of the step's tile plan (and its tiles, unless the tcgen05 kernel took them) on the mma.sync
+// kernels; with a fused plan, rotation and append run inside the decode kernel, from the projection's partial sums.
+// i: 0 q, 1 out, 2 cache layer, 3 block table, 4 pages per sequence, 5 page size, 6 page stride, 7 v offset, 8 head stride,
+//    9 scratch, 10 floats of scratch, 11 counters, 12 Hq, 13 Hkv, 14 D, 15 window, 16 tile plan,
+//    17 the tiles went to the tcgen05 kernel, 18 qkv partial sums (flat), 19 their width, 20 K ranges S,
+//    21 most tokens with a buffer per range, 22 cos_sin; f: 0 scale
+SB_EXPORT int sb_op_attention_tc(const SbOp* op, const SbStep* s, void* stream) {
+  using namespace sbstep;
+  const SbTilePlan& plan = s->plan[op->i[16]];
+  const int Hq = (int)op->i[12], Hkv = (int)op->i[13], D = (int)op->i[14];
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  if (plan.items > 0 && sb_attention_tc_scratch(plan.items, Hkv, plan.chunks, D) > op->i[10])
+    return sb::fail("sb_op_attention_tc: %d decode entries over %d chunks need more scratch than the engine set aside (%lld floats)",
+                    plan.items, plan.chunks, (long long)op->i[10]);
+  if (plan.fused) {
+    const int P = partial_count(op->i[20], op->i[21], s->n);
+    return sb_attention_decode_rope(ptr<const float>(op->i[18]), P, static_cast<int64_t>(s->n) * op->i[19], ptr<const float>(op->i[22]),
+                                    ptr<void>(op->i[1]), ptr<void>(op->i[2]), ptr<const int32_t>(op->i[3]), (int)op->i[4], (int)op->i[5],
+                                    op->i[6], op->i[7], op->i[8], entry_meta(s), s->max_rows, work(s, plan), plan.items, plan.chunks,
+                                    ptr<float>(op->i[9]), ptr<int>(op->i[11]), Hq, Hkv, D, (int)op->i[15], static_cast<float>(op->f[0]), st);
+  }
+  const int tiles = op->i[17] ? 0 : plan.tiles;
+  if (tiles <= 0 && plan.items <= 0) return SB_OP_SKIPPED;
+  const int32_t* list = work(s, plan) + (op->i[17] ? 2 * plan.tiles : 0);
+  return sb_attention_tc(ptr<const void>(op->i[0]), ptr<void>(op->i[1]), ptr<const void>(op->i[2]), ptr<const int32_t>(op->i[3]),
+                         (int)op->i[4], (int)op->i[5], op->i[6], op->i[7], op->i[8], entry_meta(s), s->max_rows, list, tiles, plan.items,
+                         plan.chunks, ptr<float>(op->i[9]), ptr<int>(op->i[11]), Hq, Hkv, D, (int)op->i[15], static_cast<float>(op->f[0]), st);
 }

@@ -24,6 +24,7 @@
 // Counterpart in arhaamatiq/stride: AttentionPage / AttentionCombine (src/kernel_common.h:90-309), scalar.
 #include "attention_math.cuh"
 #include "tc5.cuh"
+#include "step_ops.h"
 
 SB_DEFINE_LAST_ERROR()
 
@@ -404,4 +405,18 @@ SB_EXPORT int sb_attention_tc5_status() {
   if (cudaMemcpy(&host, status, sizeof(int), cudaMemcpyDeviceToHost) != cudaSuccess) return -2;
   if (host != 0) cudaMemset(status, 0, sizeof(int));
   return host;
+}
+
+// ------------------------------------------------------------------ operation of the native step program (step_ops.h)
+// The tiles of the step's tile plan (prompt portions) on the tcgen05 kernel.
+// i: 0 q, 1 out, 2 cache layer, 3 pages of the arena, 4 block table, 5 pages per sequence, 6 page size, 7 page stride,
+//    8 v offset, 9 head stride, 10 Hq, 11 Hkv, 12 D, 13 window, 14 tile plan; f: 0 scale
+SB_EXPORT int sb_op_attention_tc5(const SbOp* op, const SbStep* s, void* stream) {
+  using namespace sbstep;
+  const SbTilePlan& plan = s->plan[op->i[14]];
+  if (plan.fused || plan.tiles <= 0) return SB_OP_SKIPPED;
+  return sb_attention_tc5(ptr<const void>(op->i[0]), ptr<void>(op->i[1]), ptr<const void>(op->i[2]), (int)op->i[3],
+                          ptr<const int32_t>(op->i[4]), (int)op->i[5], (int)op->i[6], op->i[7], op->i[8], op->i[9], entry_meta(s),
+                          s->max_rows, work(s, plan), plan.tiles, s->n, (int)op->i[10], (int)op->i[11], (int)op->i[12], (int)op->i[13],
+                          static_cast<float>(op->f[0]), static_cast<cudaStream_t>(stream));
 }

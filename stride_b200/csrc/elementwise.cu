@@ -8,6 +8,7 @@
 // (src/kernels.cu:247-281), the activation of Mlp13 (src/kernels.cu:359-360),
 // Compact (src/kernels.cu:365-380).
 #include "common.cuh"
+#include "step_ops.h"
 
 SB_DEFINE_LAST_ERROR()
 
@@ -306,4 +307,43 @@ SB_EXPORT int sb_gather_rows(const float* in, const float* partials, int n_parti
   if (count <= 0) return 0;
   sb::launch_pdl(gather_rows_kernel, count, 256, 0, stream, in, partials, n_partials, partial_stride, rows, out, H);
   return sb::check_launch("sb_gather_rows");
+}
+
+// ------------------------------------------------------------------ operations of the native step program (step_ops.h)
+// i: 0 table, 1 table dtype, 2 out (float32 [n, H]), 3 H, 4 vocab, 5 the table of last sampled tokens (or 0)
+SB_EXPORT int sb_op_embed(const SbOp* op, const SbStep* s, void* stream) {
+  using namespace sbstep;
+  const int32_t* sampled = ptr<const int32_t>(op->i[5]);
+  return sb_embed(tokens(s), ptr<const void>(op->i[0]), (int)op->i[1], ptr<float>(op->i[2]), s->n, (int)op->i[3], (int)op->i[4],
+                  sampled ? slots(s) : nullptr, sampled, static_cast<cudaStream_t>(stream));
+}
+
+// i: 0 qkv partial sums (flat), 1 their width, 2 K ranges S, 3 most tokens with a buffer per range, 4 cos_sin, 5 rotary_dim,
+//    6 q_out, 7 q dtype, 8 cache layer, 9 cache dtype, 10 block table, 11 pages per sequence, 12 page size,
+//    13 page stride, 14 v offset, 15 head stride, 16 Hq, 17 Hkv, 18 D, 19 write_kv, 20 tile plan (-1: none)
+SB_EXPORT int sb_op_rope_append(const SbOp* op, const SbStep* s, void* stream) {
+  using namespace sbstep;
+  if (op->i[20] >= 0 && s->plan[op->i[20]].fused) return SB_OP_SKIPPED;     // the decode kernel rotates and appends itself
+  const int P = partial_count(op->i[2], op->i[3], s->n);
+  return sb_rope_append(ptr<const float>(op->i[0]), P, static_cast<int64_t>(s->n) * op->i[1], positions(s), slots(s),
+                        ptr<const float>(op->i[4]), (int)op->i[5], ptr<void>(op->i[6]), (int)op->i[7], ptr<void>(op->i[8]), (int)op->i[9],
+                        ptr<const int32_t>(op->i[10]), (int)op->i[11], (int)op->i[12], op->i[13], op->i[14], op->i[15], s->n,
+                        (int)op->i[16], (int)op->i[17], (int)op->i[18], (int)op->i[19], static_cast<cudaStream_t>(stream));
+}
+
+// i: 0 gate_up (float32 [n, 2 I]), 1 out, 2 out dtype, 3 I
+SB_EXPORT int sb_op_swiglu(const SbOp* op, const SbStep* s, void* stream) {
+  using namespace sbstep;
+  return sb_swiglu(ptr<const float>(op->i[0]), ptr<void>(op->i[1]), (int)op->i[2], s->n, (int)op->i[3], static_cast<cudaStream_t>(stream));
+}
+
+// The rows whose logits are wanted, with the pending partial sums of the last projection added.
+// i: 0 h, 1 pending partial sums (flat; 0: none), 2 K ranges S, 3 most tokens with a buffer per range, 4 out, 5 H
+SB_EXPORT int sb_op_gather_rows(const SbOp* op, const SbStep* s, void* stream) {
+  using namespace sbstep;
+  if (s->wanted <= 0) return SB_OP_SKIPPED;
+  const float* partials = ptr<const float>(op->i[1]);
+  const int P = partials ? partial_count(op->i[2], op->i[3], s->n) : 0;
+  return sb_gather_rows(ptr<const float>(op->i[0]), partials, P, static_cast<int64_t>(s->n) * op->i[5], wanted_rows(s), ptr<float>(op->i[4]),
+                        s->wanted, (int)op->i[5], static_cast<cudaStream_t>(stream));
 }

@@ -7,6 +7,7 @@
 // Counterparts in arhaamatiq/stride: gemm_partial and its users GemmResidual,
 // Mlp13, LmFull of the exact path (src/kernels.cu:63-94, 294-325, 329-363, 427-452).
 #include "common.cuh"
+#include "step_ops.h"
 
 SB_DEFINE_LAST_ERROR()
 
@@ -102,4 +103,15 @@ SB_EXPORT int sb_gemm_f32(const void* x, int x_dtype, int64_t ldx, const void* w
 #undef SB_GEMM_W
 #undef SB_GEMM
   return sb::check_launch("sb_gemm_f32");
+}
+
+// ------------------------------------------------------------------ operation of the native step program (step_ops.h)
+// i: 0 x, 1 x dtype, 2 ldx, 3 weight, 4 weight dtype, 5 ldw, 6 out, 7 ldo, 8 M, 9 K, 10 accumulate,
+//    11 rows: 0 = the step's tokens, 1 = the rows whose logits are wanted
+SB_EXPORT int sb_op_linear_f32(const SbOp* op, const SbStep* s, void* stream) {
+  using namespace sbstep;
+  const int n = op->i[11] ? s->wanted : s->n;
+  if (n <= 0) return SB_OP_SKIPPED;
+  return sb_gemm_f32(ptr<const void>(op->i[0]), (int)op->i[1], op->i[2], ptr<const void>(op->i[3]), (int)op->i[4], op->i[5],
+                     ptr<float>(op->i[6]), op->i[7], n, (int)op->i[8], (int)op->i[9], (int)op->i[10], static_cast<cudaStream_t>(stream));
 }

@@ -30,6 +30,7 @@
 // Counterparts in arhaamatiq/stride: TcQkv, TcGemmResidual, TcMlp13, TcLmFull on wmma
 // (src/kernels_tc.cu:347-655).
 #include "tc5.cuh"
+#include "step_ops.h"
 
 SB_DEFINE_LAST_ERROR()
 
@@ -1196,4 +1197,31 @@ SB_EXPORT int sb_gemm_tc_status() {
   if (cudaMemcpy(&host, status, sizeof(int), cudaMemcpyDeviceToHost) != cudaSuccess) return -2;
   if (host != 0) cudaMemset(status, 0, sizeof(int));
   return host;
+}
+
+// ------------------------------------------------------------------ operation of the native step program (step_ops.h)
+// i: 0 x (bfloat16 [n, ldx]), 1 ldx, 2 weight, 3 ldw, 4 out, 5 M, 6 K,
+//    7 mode: 0 = out float32 [n, M], K in one range; 1 = partial sums [P, n, M] of the weight's K ranges (P = S up to
+//            sb_gemm_tc_partial_tokens() tokens, else 1: the kernel adds the ranges); 2 = out float32 [n, M] += result;
+//            3 = SwiGLU, out bfloat16 [n, M / 2]
+//    8 K ranges S (mode 1), 9 rows: 0 = the step's tokens, 1 = the rows whose logits are wanted
+SB_EXPORT int sb_op_linear_tc(const SbOp* op, const SbStep* s, void* stream) {
+  using namespace sbstep;
+  const int n = op->i[9] ? s->wanted : s->n;
+  if (n <= 0) return SB_OP_SKIPPED;
+  const int M = (int)op->i[5], K = (int)op->i[6], mode = (int)op->i[7], S = (int)op->i[8];
+  const void* x = ptr<const void>(op->i[0]);
+  const void* w = ptr<const void>(op->i[2]);
+  void* out = ptr<void>(op->i[4]);
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  switch (mode) {
+    case 0: return sb_gemm_tc(x, op->i[1], w, op->i[3], out, M, n, M, K, kStore, 1, 0, 0, st);
+    case 1: {
+      const bool buffers = S > 1 && n <= sb_gemm_tc_partial_tokens();
+      return sb_gemm_tc(x, op->i[1], w, op->i[3], out, M, n, M, K, kStore, S, buffers ? static_cast<int64_t>(n) * M : 0, 0, st);
+    }
+    case 2: return sb_gemm_tc(x, op->i[1], w, op->i[3], out, M, n, M, K, kAdd, 1, 0, 0, st);
+    case 3: return sb_gemm_tc(x, op->i[1], w, op->i[3], out, M / 2, n, M, K, kSwiglu, 1, 0, M / 2, st);
+    default: return sb::fail("sb_op_linear_tc: unknown mode %d", mode);
+  }
 }

@@ -3,6 +3,7 @@
 //
 // Counterpart in arhaamatiq/stride: RmsNorm (src/kernels.cu:119-200).
 #include "common.cuh"
+#include "step_ops.h"
 
 SB_DEFINE_LAST_ERROR()
 
@@ -241,3 +242,16 @@ SB_EXPORT int sb_rmsnorm(float* h, const float* partials, int n_partials, int64_
   return sb::check_launch("sb_rmsnorm");
 }
 
+// ------------------------------------------------------------------ operation of the native step program (step_ops.h)
+// i: 0 h, 1 pending partial sums (flat; 0: none), 2 K ranges S, 3 most tokens with a buffer per range, 4 weight,
+//    5 weight dtype, 6 out, 7 out dtype, 8 H, 9 rows: 0 = the step's tokens, 1 = the rows whose logits are wanted
+// f: 0 eps
+SB_EXPORT int sb_op_rmsnorm(const SbOp* op, const SbStep* s, void* stream) {
+  using namespace sbstep;
+  const int n = op->i[9] ? s->wanted : s->n;
+  if (n <= 0) return SB_OP_SKIPPED;
+  const float* partials = ptr<const float>(op->i[1]);
+  const int P = partials ? partial_count(op->i[2], op->i[3], n) : 0;
+  return sb_rmsnorm(ptr<float>(op->i[0]), partials, P, static_cast<int64_t>(n) * op->i[8], ptr<const void>(op->i[4]), (int)op->i[5],
+                    ptr<void>(op->i[6]), (int)op->i[7], n, (int)op->i[8], static_cast<float>(op->f[0]), static_cast<cudaStream_t>(stream));
+}

@@ -13,6 +13,7 @@
 //
 // Nothing here touches a GPU; it is compiled by the host compiler alone.
 #include <algorithm>
+#include <chrono>
 #include <cstdint>
 #include <cstdio>
 #include <cstring>
@@ -865,4 +866,156 @@ SB_API void sb_sched_abort(void* sched) {
     if (sc->seqs[id].live) sc->retire((int)id);
   sc->running.clear();
   sc->waiting.clear();
+}
+
+// ------------------------------------------------------------------ the step program
+//
+// The operations of a step, recorded once when the engine is built (see step_ops.h), and the runner that calls them
+// in order for every step. `sb_program_prepare` fills the step's record: its sizes, and for every tile plan that a
+// mixer asked for the cut of the step's entries into attention tiles and decode items, written behind the step's
+// other integer inputs in the staging area so that everything travels in one copy. Counterpart in arhaamatiq/stride:
+// the launch sequences of Engine::step_exact / step_tensor_core and the attention items built on the host
+// (src/engine.cpp:93-103, 144-462).
+#include "step_ops.h"
+
+namespace {
+
+struct Program {
+  std::vector<SbOp> ops;
+  std::vector<SbTilePlan> plans;     // keys only
+  int R = 0;
+  int work_ints = 0;                  // room for work lists behind the 9 R fixed regions
+  int launched = 0;                   // operations that launched something in the last run
+};
+
+}  // namespace
+
+// R: the most rows of a step; work_ints: int32 of room for the plans' work lists behind the staging area's 9 R.
+SB_API void* sb_program_create(int R, int work_ints) {
+  Program* p = new Program();
+  p->R = R;
+  p->work_ints = work_ints;
+  return p;
+}
+
+SB_API void sb_program_destroy(void* program) { delete static_cast<Program*>(program); }
+
+// A tile plan for mixers of head ratio `group` whose prompt kernel takes tiles of `tile_rows` rows, with `kv_heads`
+// key/value heads; fused_limit >= 0: steps of items only run rotation and append inside the decode kernel while
+// items x kv_heads x chunks stays within it. Returns the plan's index in SbStep::plan (equal requests share one), or -1.
+SB_API int sb_program_plan(void* program, int group, int tile_rows, int kv_heads, int fused_limit) {
+  Program* p = static_cast<Program*>(program);
+  if (group <= 0 || group > 16 || tile_rows < group) {
+    g_error = "a tile plan needs a head ratio of 1..16 and tiles of at least one position";
+    return -1;
+  }
+  for (size_t k = 0; k < p->plans.size(); ++k) {
+    const SbTilePlan& q = p->plans[k];
+    if (q.group == group && q.tile_rows == tile_rows && q.kv_heads == kv_heads && q.fused_limit == fused_limit) return (int)k;
+  }
+  if (p->plans.size() >= SB_MAX_PLANS) {
+    g_error = "a model may ask for at most " + std::to_string(SB_MAX_PLANS) + " different tile plans";
+    return -1;
+  }
+  SbTilePlan q{};
+  q.group = group, q.tile_rows = tile_rows, q.kv_heads = kv_heads, q.fused_limit = fused_limit;
+  p->plans.push_back(q);
+  return (int)p->plans.size() - 1;
+}
+
+SB_API int sb_program_add(void* program, const SbOp* op) {
+  Program* p = static_cast<Program*>(program);
+  if (op == nullptr || op->fn == nullptr) {
+    g_error = "an operation without a function";
+    return -1;
+  }
+  p->ops.push_back(*op);
+  return (int)p->ops.size() - 1;
+}
+
+SB_API int sb_program_size(void* program) { return (int)static_cast<Program*>(program)->ops.size(); }
+
+// Fills `step` for a batch whose integer inputs were staged at `staging` (sb_stage_step or sb_stage_decode: E entries
+// of count[i] tokens from position first[i]; n rows, `wanted` of them wanted) and will lie at `device_ints` once
+// copied. static_keys > 0: a recorded decode step of E single-token entries (the padding included), planned for keys
+// below static_keys whatever the positions are. 0, or -1 when the work lists do not fit.
+SB_API int sb_program_prepare(void* program, int E, const int32_t* count, const int32_t* first, int n, int wanted, int static_keys,
+                              int32_t* staging, const int32_t* device_ints, SbStep* step) {
+  Program* p = static_cast<Program*>(program);
+  memset(step, 0, sizeof(SbStep));
+  step->n = n, step->entries = E, step->wanted = wanted, step->static_keys = static_keys, step->max_rows = p->R;
+  step->n_plans = (int)p->plans.size();
+  step->ints = device_ints;
+  int32_t* work = staging + 9 * (int64_t)p->R;
+  int at = 0;
+  for (size_t k = 0; k < p->plans.size(); ++k) {
+    SbTilePlan q = p->plans[k];
+    q.work_offset = at;
+    if (static_keys > 0) {
+      if (at + E > p->work_ints) return stage_fail("the step's work lists exceed the staging area");
+      for (int e = 0; e < E; ++e) work[at + e] = e;
+      q.tiles = 0, q.items = E, q.chunks = (static_keys + 255) / 256;
+      at += E;
+    } else {
+      const int ppt = q.tile_rows / q.group, few = 16 / q.group;
+      struct Tile { int key, entry, tile; };
+      std::vector<Tile> tiles;
+      std::vector<int> items;
+      int last = 0;
+      for (int e = 0; e < E; ++e) {
+        const int L = count[e], p0 = first[e];
+        if (L <= few) {
+          items.push_back(e);
+          last = std::max(last, p0 + L - 1);
+        } else {
+          for (int t = 0; t < (L + ppt - 1) / ppt; ++t) tiles.push_back({p0 + std::min(L, (t + 1) * ppt), e, t});
+        }
+      }
+      // the tiles that see the most keys first: CTAs start in this order, and the short ones fill the end
+      std::stable_sort(tiles.begin(), tiles.end(), [](const Tile& a, const Tile& b) { return a.key > b.key; });
+      const int need = 2 * (int)tiles.size() + (int)items.size();
+      if (at + need > p->work_ints) return stage_fail("the step's work lists exceed the staging area");
+      for (const Tile& t : tiles) work[at++] = t.entry, work[at++] = t.tile;
+      for (int e : items) work[at++] = e;
+      q.tiles = (int)tiles.size(), q.items = (int)items.size(), q.chunks = items.empty() ? 0 : last / 256 + 1;
+    }
+    q.fused = q.tiles == 0 && q.items > 0 && q.fused_limit >= 0 && (int64_t)q.items * q.kv_heads * q.chunks <= q.fused_limit;
+    at = (at + 3) & ~3;
+    step->plan[k] = q;
+  }
+  return 0;
+}
+
+// Runs the program's operations in order on `stream`. 0, or -1 with *failed = the index of the operation that failed
+// (its library's sb_last_error() has the reason). *launched = operations that launched something.
+SB_API int sb_program_run(void* program, const SbStep* step, void* stream, int32_t* failed, int32_t* launched) {
+  Program* p = static_cast<Program*>(program);
+  int count = 0;
+  for (size_t k = 0; k < p->ops.size(); ++k) {
+    const SbOp& op = p->ops[k];
+    const int rc = reinterpret_cast<SbOpFn>(op.fn)(&op, step, stream);
+    if (rc == SB_OP_LAUNCHED) {
+      ++count;
+    } else if (rc != SB_OP_SKIPPED) {
+      if (failed) *failed = (int32_t)k;
+      if (launched) *launched = count;
+      return -1;
+    }
+  }
+  if (launched) *launched = count;
+  return 0;
+}
+
+// The same run with the host's time for every operation (microseconds into per_op_us[sb_program_size()]): what the
+// launches themselves cost the CPU, for finding an operation whose set-up is slow. Returns like sb_program_run.
+SB_API int sb_program_run_timed(void* program, const SbStep* step, void* stream, double* per_op_us) {
+  Program* p = static_cast<Program*>(program);
+  for (size_t k = 0; k < p->ops.size(); ++k) {
+    const SbOp& op = p->ops[k];
+    const auto t0 = std::chrono::steady_clock::now();
+    const int rc = reinterpret_cast<SbOpFn>(op.fn)(&op, step, stream);
+    per_op_us[k] = std::chrono::duration<double, std::micro>(std::chrono::steady_clock::now() - t0).count();
+    if (rc != SB_OP_LAUNCHED && rc != SB_OP_SKIPPED) return -1;
+  }
+  return 0;
 }

@@ -26,6 +26,7 @@ import torch
 from ..cache.manager import CacheManager
 from ..config import resolve_architecture
 from ..kernels.build import build_all
+from ..kernels.native import NotNative, StepProgram
 from ..parts import BuildEnv, DecoderModel, StepContext, Workspace
 from ..weights.loader import check_plan, load_weights
 
@@ -47,6 +48,7 @@ class EngineOptions:
     max_context: int = 0               # longest sequence (0: config.json's max_position_embeddings)
     kv_shuffle_seed: int = 0           # tests: hand out pages in random order
     cuda_graphs: bool = True           # replay decode-only steps from CUDA graphs (one per batch and context bucket)
+    native_step: bool = True           # launch a step's kernels from the native step program (else part by part from Python)
     device: str = "cuda:0"
 
 
@@ -130,8 +132,10 @@ class Engine:
         self.caches = [self.cache.layer_cache(i) for i in range(len(self.spec.schedule))]
         self.workspace = Workspace(self.device, o.max_rows)
         # One pinned staging buffer and one device buffer for all integer inputs of a step:
-        # tokens, positions, slots, logit rows (max_rows each), entry records (4 x max_rows), and the slot of every logit row.
-        self._ints = 9 * o.max_rows
+        # tokens, positions, slots, logit rows (max_rows each), entry records (4 x max_rows), the slot of every logit row,
+        # and the work lists of the attention kernels that the native step program plans.
+        self._work_ints = 4 * o.max_rows + 64
+        self._ints = 9 * o.max_rows + self._work_ints
         self._staging = torch.empty(self._ints, dtype=torch.int32, pin_memory=True)
         self._staging_np = self._staging.numpy()
         self._device_ints = torch.zeros(self._ints, dtype=torch.int32, device=self.device)
@@ -159,6 +163,18 @@ class Engine:
         self._graph_generation = 0
         # Padding rows of a graph step write their key and value to the cache manager's spare slot.
         self._pad_slot = self.cache.pad_slot if (o.cuda_graphs and self.model.graph_safe) else -1
+        # The step as a native program: every part describes its operations once; a part that cannot leaves the
+        # model to the Python driver (`DecoderModel.forward`), which launches the same kernels part by part.
+        self._program, self._program_logits = None, None
+        if o.native_step:
+            from ..kernels import ops
+            program = StepProgram(self.workspace, o.max_rows, self._work_ints, ops.gemm_tc_partial_tokens() if self.compute_dtype == torch.bfloat16 else 0)
+            try:
+                self._program_logits = self.model.emit(program, self.caches, self.sampled)
+                self._program = program
+            except NotNative:
+                self._program = None
+        self.h2d_bytes_per_step = self._ints * 4
 
     @classmethod
     def from_random(cls, config: dict, seed: int, options: Optional[EngineOptions] = None) -> "Engine":
@@ -223,6 +239,16 @@ class Engine:
                              self.spec.vocab_size, R, self.env.max_logit_rows, self._staging_p, self._staged_p) < 0:
             raise EngineError(lib.sb_last_error().decode())
         wanted = int(self._staged[1])
+        if self._program is not None:
+            self._program.prepare(E, _i32(count), _i32(first), n, wanted, 0, self._staging_p, self._device_ints)
+            self._device_ints.copy_(self._staging, non_blocking=True)
+            self._copied.record()
+            self._copy_pending = True
+            self.cache.sync()
+            self._program.run()
+            self.logit_slots = self._device_ints[8 * R:8 * R + wanted]
+            self.steps += 1
+            return self._program_logits[:wanted] if wanted else None
         meta = self._staging_np[4 * R:8 * R].reshape(4, R)
         self._device_ints.copy_(self._staging, non_blocking=True)
         self._copied.record()
@@ -273,6 +299,8 @@ class Engine:
         if lib.sb_stage_decode(self.cache._pool, E, B, self._pad_slot, _i32(slot), _i32(first), _i32(tokens), self.spec.vocab_size, R,
                                self._staging_p) < 0:
             raise EngineError(lib.sb_last_error().decode())
+        if self._program is not None:
+            self._program.prepare(B, None, None, B, B, keys, self._staging_p, self._device_ints)
         self._device_ints.copy_(self._staging, non_blocking=True)
         self._copied.record()
         self._copy_pending = True
@@ -285,6 +313,9 @@ class Engine:
         d = self._device_ints
 
         def run():
+            if self._program is not None:
+                self._program.run()
+                return self._program_logits[:B]
             ctx = StepContext(
                 n=B, token_ids=d[0:B], positions=d[R:R + B], slots=d[2 * R:2 * R + B], workspace=self.workspace,
                 compute_dtype=self.compute_dtype, entry_slots=[0] * B, entry_first_row=list(range(B)),

@@ -82,6 +82,54 @@ class Linear:
             stream.fold()
             ops.gemm_f32(x, self.weight, stream.h, accumulate=True)
 
+    # ------------------------------------------------------------------ the same, as operations of the native step program
+    # (`x`, `out`, `flat`, `z` are the full buffers, of which a step uses its first n rows)
+    def _f32_op(self, program, x, out, ldo: int, accumulate: bool, wanted_rows: bool) -> None:
+        program.add("gemm_f32", "sb_op_linear_f32", [x, x.dtype, x.stride(0), self.weight, self.weight.dtype, self.weight.stride(0), out, ldo,
+                                                      self.out_features, self.in_features, int(accumulate), int(wanted_rows)])
+
+    def _tc_op(self, program, x, out, mode: int, splits: int = 1, wanted_rows: bool = False) -> None:
+        program.add("gemm_tc", "sb_op_linear_tc", [x, x.stride(0), self.weight, self.weight.stride(0), out, self.out_features,
+                                                    self.in_features, mode, splits, int(wanted_rows)])
+
+    def emit(self, program, x: torch.Tensor, out: torch.Tensor, wanted_rows: bool = False) -> None:
+        """`forward`; with `wanted_rows` the rows are the step's wanted rows (the head), not its tokens."""
+        if self._tc(x):
+            self._tc_op(program, x, out, 0, wanted_rows=wanted_rows)
+        else:
+            self._f32_op(program, x, out, out.stride(0), False, wanted_rows)
+
+    def emit_partials(self, program, x: torch.Tensor, flat: torch.Tensor) -> int:
+        """`forward_partials`; returns the number of K ranges S that the reader of `flat` has to expect
+        ([S, n, out_features] up to `program.few_tokens` tokens, [1, n, out_features] beyond)."""
+        if not self._tc(x):
+            self._f32_op(program, x, flat, self.out_features, False, False)
+            return 1
+        self._tc_op(program, x, flat, 1, self.splits)
+        return self.splits
+
+    def emit_add(self, program, x: torch.Tensor, flat: torch.Tensor = None) -> None:
+        """`forward_add` onto the program's residual stream."""
+        if self._tc(x) and flat is not None and self.splits > 1:
+            program.need_folded("a projection that leaves partial sums")
+            self._tc_op(program, x, flat, 1, self.splits)
+            program.pending = (flat, self.splits, self.out_features)
+            return
+        program.need_folded("a projection")
+        if self._tc(x):
+            self._tc_op(program, x, program.h, 2)
+        else:
+            self._f32_op(program, x, program.h, program.h.stride(0), True, False)
+
+    def emit_swiglu(self, program, x: torch.Tensor, z: torch.Tensor, scratch_fn) -> None:
+        """`forward_swiglu`."""
+        if self._tc(x) and z.dtype == torch.bfloat16:
+            self._tc_op(program, x, z, 3)
+        else:
+            gate_up = scratch_fn()
+            self._f32_op(program, x, gate_up, gate_up.stride(0), False, False)
+            program.add("elementwise", "sb_op_swiglu", [gate_up, z, z.dtype, self.out_features // 2])
+
     def forward_swiglu(self, x: torch.Tensor, z: torch.Tensor, scratch_fn) -> None:
         """W = [gate rows; up rows]: z[n, I] = silu(x . gate^T) * (x . up^T). `scratch_fn()` gives a
         float32 [n, 2 I] buffer for the unfused path."""

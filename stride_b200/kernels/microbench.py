@@ -7,6 +7,7 @@ workloads that the ncu summaries under profiles/ were captured on.
     python -m stride_b200.kernels.microbench attention --batch 1 --new 2048 --context 0  # one prompt
     python -m stride_b200.kernels.microbench step --batch 8                              # timeline of a decode step
     python -m stride_b200.kernels.microbench step --prefill 2048                         # timeline of a 2,048-token prompt
+    python -m stride_b200.kernels.microbench host --tokens 256                           # the host's cost of queueing a mixed step
 
 Weights are cycled through `--copies` buffers larger than L2 in total, so every launch streams from HBM.
 """
@@ -175,6 +176,60 @@ def step(a) -> dict:
             "by_kernel": {k: {"launches": c, "critical_us": round(v, 1)} for k, (c, v) in sorted(agg.items(), key=lambda x: -x[1][1])}}
 
 
+def host(a) -> dict:
+    """What the host spends to queue one step (Llama 3.2 1B shape): `decoders` requests that decode one token each beside
+    a prompt portion of `tokens - decoders` tokens, with the native step program and with the Python driver: the host's
+    time to queue the step onto an idle GPU, and the time per step when the steps run back to back (the larger of the
+    host's and the GPU's share)."""
+    import time
+
+    from .. import Engine, EngineOptions, StepEntry
+    cfg = dict(LLAMA_1B_SHAPE, num_hidden_layers=a.layers)
+    out = {"tokens": a.tokens, "decoders": a.decoders, "layers": a.layers}
+    for native in (True, False):
+        eng = Engine.from_random(cfg, 0, EngineOptions(dtype="bfloat16", max_rows=max(512, a.tokens), max_full_rows=a.decoders + 1,
+                                                       max_slots=a.decoders + 2, kv_pages=(a.decoders + 1) * 64, page_size=64,
+                                                       max_context=4096, native_step=native))
+        cm = eng.cache
+        slots = [cm.acquire_slot() for _ in range(a.decoders + 1)]
+        for s in slots[:-1]:
+            cm.ensure(s, 100)
+            eng.step([StepEntry(s, 0, list(range(100)), [])])
+        portion = a.tokens - a.decoders
+
+        def one(k):
+            entries = []
+            for s in slots[:-1]:
+                cm.ensure(s, 101 + k)
+                entries.append(StepEntry(s, 100 + k, [7], [0]))
+            cm.ensure(slots[-1], portion)
+            entries.append(StepEntry(slots[-1], 0, list(range(portion)), [portion - 1]))     # the same portion again and again
+            eng.step(entries)
+
+        for k in range(3):
+            one(k)
+        # the host's share: each step queued onto an idle GPU (a full launch queue would make the host wait for the GPU)
+        spent = 0.0
+        for k in range(3, 3 + a.reps):
+            torch.cuda.synchronize()
+            t0 = time.perf_counter()
+            one(k)
+            spent += time.perf_counter() - t0
+        # the GPU's share: the same steps back to back
+        torch.cuda.synchronize()
+        start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        start.record()
+        for k in range(3 + a.reps, 3 + 2 * a.reps):
+            one(k)
+        stop.record()
+        torch.cuda.synchronize()
+        key = "native" if native else "python"
+        out[key + "_host_us_per_step"] = round(spent * 1e6 / a.reps, 1)
+        out[key + "_back_to_back_us_per_step"] = round(start.elapsed_time(stop) * 1e3 / a.reps, 1)
+        del eng
+    return out
+
+
 def main(argv=None) -> int:
     ap = argparse.ArgumentParser(description=__doc__, formatter_class=argparse.RawDescriptionHelpFormatter)
     sub = ap.add_subparsers(dest="what", required=True)
@@ -201,8 +256,13 @@ def main(argv=None) -> int:
     st.add_argument("--context", type=int, default=256)
     st.add_argument("--prefill", type=int, default=0, help="time one prompt of this many tokens instead of a decode step")
     st.add_argument("--layers", type=int, default=16)
+    h = sub.add_parser("host")
+    h.add_argument("--tokens", type=int, default=256)
+    h.add_argument("--decoders", type=int, default=8)
+    h.add_argument("--layers", type=int, default=16)
+    h.add_argument("--reps", type=int, default=30)
     a = ap.parse_args(argv)
-    print(json.dumps({"gemm": gemm, "attention": attention, "step": step}[a.what](a), indent=1 if a.what == "step" else None))
+    print(json.dumps({"gemm": gemm, "attention": attention, "step": step, "host": host}[a.what](a), indent=1 if a.what == "step" else None))
     return 0
 
 

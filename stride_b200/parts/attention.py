@@ -154,3 +154,47 @@ class AttentionMixer(Mixer):
             ops.attention_generic(q, mixed, cache.pages, cache.block_table, ctx.positions, ctx.slots,
                                   self.num_heads, self.num_kv_heads, D, self.window, self.scale)
         self.o.forward_add(mixed, stream, ws.raw("attn.o_partials", (self.o.partial_elems(ws.max_tokens),), torch.float32))
+
+    def emit(self, program, x, cache):
+        """`forward` as operations of the native step program: the projection, then rotation and append, the
+        attention kernels that this shape takes (each finds its share of the step in the step's tile plan, or skips),
+        the output projection."""
+        ws, env, D = program.workspace, self.env, self.head_dim
+        act, T = env.act_dtype, ws.max_tokens
+        qkv = ws.raw("attn.qkv", (self.qkv.partial_elems(T),), torch.float32)
+        S = self.qkv.emit_partials(program, x, qkv)
+        mixed = ws.get("attn.out", T, (self.num_heads * D,), act)
+        q = ws.get("attn.q", T, (self.num_heads * D,), act)
+        G = self.num_heads // self.num_kv_heads
+        tensor_core = act == torch.bfloat16 and D in (64, 128) and G <= 16
+        pages, table = cache.pages, cache.block_table
+        where = [pages, table, table.shape[1], pages.shape[3], pages.stride(0), pages.stride(1), pages.stride(2)]
+        plan = -1
+        if tensor_core:
+            tc5 = ops.attention_tc5_supported(self.num_heads, self.num_kv_heads, D, cache.page_size)
+            fused = cache.writes and self._rotary == D
+            plan = program.plan(G, 128 if tc5 else 64, self.num_kv_heads, ops.attention_decode_rope_limit() if fused else -1)
+        program.add("elementwise", "sb_op_rope_append",
+                    [qkv, self.qkv_width, S, program.few_tokens, self._cos_sin, self._rotary, q, q.dtype, pages, pages.dtype, table,
+                     table.shape[1], pages.shape[3], pages.stride(0), pages.stride(1), pages.stride(2), self.num_heads,
+                     self.num_kv_heads, D, int(cache.writes), plan])
+        if tensor_core:
+            if tc5:
+                program.add("attention_tc5", "sb_op_attention_tc5",
+                            [q, mixed, pages, pages.shape[0], *where[1:], self.num_heads, self.num_kv_heads, D, self.window, plan], [self.scale])
+            # scratch for the most decode entries a step can bring, over the longest context
+            # (a recorded decode step pads its batch and its key range to powers of two)
+            items = min(T, 2 * env.max_requests + 2) if env.max_requests else T
+            keys = 256
+            while keys < env.max_positions:
+                keys *= 2
+            chunks = keys // 256
+            scratch = ws.grow("attn.scratch", ops.attention_tc_scratch(items, self.num_kv_heads, chunks, D), torch.float32)
+            counters = ws.raw("attn.counters", (T * self.num_kv_heads,), torch.int32)
+            program.add("attention_tc", "sb_op_attention_tc",
+                        [q, mixed, *where, scratch, scratch.numel(), counters, self.num_heads, self.num_kv_heads, D, self.window, plan,
+                         int(tc5), qkv, self.qkv_width, S, program.few_tokens, self._cos_sin], [self.scale])
+        else:
+            program.add("attention_generic", "sb_op_attention_generic",
+                        [q, mixed, q.dtype, *where, self.num_heads, self.num_kv_heads, D, self.window], [self.scale])
+        self.o.emit_add(program, mixed, ws.raw("attn.o_partials", (self.o.partial_elems(T),), torch.float32))

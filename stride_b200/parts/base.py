@@ -11,6 +11,11 @@ A new kind is one class registered under a category:
 Life of a part: `__init__(spec, env)`; `tensor_plan()` tells the loader which
 checkpoint tensors it needs; `bind(tensors)` receives them (already on the
 device); then `forward(...)` is called once per step and schedule entry.
+
+A part may also describe its share of a step once, as operations of the native step
+program (`emit(program, ...)`, the counterpart of `forward` over the full-size buffers;
+see `kernels/native.py`): when every part of a model does, a step is one native call.
+A part without `emit` makes the engine drive the model through `forward`, part by part.
 """
 from __future__ import annotations
 
@@ -19,6 +24,7 @@ from typing import Optional
 
 import torch
 
+from ..kernels.native import NotNative
 from .spec import PartSpec, TensorPlan
 
 _REGISTRY: dict = {}
@@ -110,6 +116,11 @@ class Part:
         listed is compiled when it is first called."""
         return set()
 
+    def emit(self, program, *args) -> None:
+        """The part's `forward` as operations appended to the native step program; the arguments are those of
+        `forward` without the step's context, tensors being the full-size buffers. Optional."""
+        raise NotNative(f"{type(self).__name__} has no native form")
+
 
 class Norm(Part):
     def forward(self, ctx, stream, out: torch.Tensor) -> None:
@@ -169,3 +180,6 @@ class Block(Part):
 
     def forward(self, ctx, stream, cache) -> None:
         raise NotImplementedError
+
+    def emit(self, program, cache) -> None:
+        raise NotNative(f"{type(self).__name__} has no native form")

@@ -16,3 +16,11 @@ class PreNormBlock(Block):
         self.mixer.forward(ctx, x, stream, cache)
         self.feed_forward_norm.forward(ctx, stream, x)
         self.feed_forward.forward(ctx, x, stream)
+
+    def emit(self, program, cache):
+        ws = program.workspace
+        x = ws.get("block.x", ws.max_tokens, (program.h.shape[1],), self.env.act_dtype)
+        self.mixer_norm.emit(program, x)
+        self.mixer.emit(program, x, cache)
+        self.feed_forward_norm.emit(program, x)
+        self.feed_forward.emit(program, x)

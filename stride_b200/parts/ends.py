@@ -38,6 +38,9 @@ class Embedding(Part):
     def forward(self, ctx, out):
         ops.embed(ctx.token_ids, self.weight, out, ctx.slots if ctx.sampled is not None else None, ctx.sampled)
 
+    def emit(self, program, out, sampled):
+        program.add("elementwise", "sb_op_embed", [self.weight, self.weight.dtype, out, self.hidden, self.weight.shape[0], sampled])
+
 
 @register_part("head", "linear")
 class LinearHead(Part):
@@ -72,3 +75,6 @@ class LinearHead(Part):
     def forward(self, x, logits):
         """logits[count, vocab] float32 = x . W^T for the normed rows x."""
         self.linear.forward(x, logits)
+
+    def emit(self, program, x, logits):
+        self.linear.emit(program, x, logits, wanted_rows=True)

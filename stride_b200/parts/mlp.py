@@ -48,3 +48,9 @@ class SwiGLU(FeedForward):
         z = ws.get("mlp.z", n, (self.intermediate,), ctx.act_dtype)
         self.gate_up.forward_swiglu(x, z, lambda: ws.get("mlp.gate_up", n, (2 * self.intermediate,), torch.float32))
         self.down.forward_add(z, stream, ws.raw("mlp.down_partials", (self.down.partial_elems(ws.max_tokens),), torch.float32))
+
+    def emit(self, program, x):
+        ws = program.workspace
+        z = ws.get("mlp.z", ws.max_tokens, (self.intermediate,), self.env.act_dtype)
+        self.gate_up.emit_swiglu(program, x, z, lambda: ws.get("mlp.gate_up", ws.max_tokens, (2 * self.intermediate,), torch.float32))
+        self.down.emit_add(program, z, ws.raw("mlp.down_partials", (self.down.partial_elems(ws.max_tokens),), torch.float32))

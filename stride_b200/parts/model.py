@@ -91,3 +91,21 @@ class DecoderModel:
         logits = ws.raw("model.logits", (self.env.max_logit_rows, self.spec.vocab_size), torch.float32)[:count]
         self.head.forward(x, logits)
         return logits
+
+    def emit(self, program, caches: list, sampled) -> torch.Tensor:
+        """The whole step as operations of the native step program (what `forward` launches, in the same order);
+        returns the buffer [max_logit_rows, vocab] the logits of the wanted rows land in. Raises `NotNative` when a part
+        has no native form."""
+        ws, H = program.workspace, self.spec.hidden_size
+        program.h = ws.get("model.h", ws.max_tokens, (H,), torch.float32)
+        self.embedding.emit(program, program.h, sampled)
+        for i, e in enumerate(self.spec.schedule):
+            self.blocks[e.layer].emit(program, caches[i])
+        rows = ws.raw("model.head_rows", (ws.max_tokens, H), torch.float32)
+        flat, S, _ = program.take_pending() or (None, 1, 0)
+        program.add("elementwise", "sb_op_gather_rows", [program.h, flat, S, program.few_tokens, rows, H])
+        x = ws.raw("model.head_x", (ws.max_tokens, H), self.env.act_dtype)
+        self.final_norm.emit_rows(program, rows, x)
+        logits = ws.raw("model.logits", (self.env.max_logit_rows, self.spec.vocab_size), torch.float32)
+        self.head.emit(program, x, logits)
+        return logits

@@ -37,3 +37,14 @@ class RMSNorm(Norm):
     def forward_rows(self, rows, out):
         """Norm of a plain [n, size] float32 tensor (the rows gathered for the head)."""
         ops.rmsnorm(rows, self.weight, self.eps, out)
+
+    def _op(self, program, h, pending, out, wanted_rows: bool):
+        flat, S, _ = pending if pending is not None else (None, 1, 0)
+        program.add("norm", "sb_op_rmsnorm", [h, flat, S, program.few_tokens, self.weight, self.weight.dtype, out, out.dtype, self.size,
+                                              int(wanted_rows)], [self.eps])
+
+    def emit(self, program, out):
+        self._op(program, program.h, program.take_pending(), out, False)
+
+    def emit_rows(self, program, rows, out):
+        self._op(program, rows, None, out, True)
