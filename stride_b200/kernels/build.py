@@ -30,7 +30,8 @@ CSRC = Path(__file__).resolve().parent.parent / "csrc"
 ARCH_FLAGS = ["-gencode", "arch=compute_100a,code=sm_100a"]
 NVCC_FLAGS = ["-O3", "-std=c++17", "-lineinfo", "-shared", "-Xcompiler", "-fPIC", "-Xcompiler", "-fvisibility=hidden"]
 
-# library name -> source file; every name here is built by `build_all()`.
+# library name -> source file (relative to csrc/, or absolute for libraries registered from outside the package);
+# every name here is built by `build_all()`.
 SOURCES = {
     "elementwise": "elementwise.cu",
     "norm": "norm.cu",
@@ -43,6 +44,30 @@ SOURCES = {
     "runtime": "runtime.cpp",        # host code only: the cache manager's books and the scheduler's decisions
 }
 HOST_FLAGS = ["-O2", "-std=c++17", "-g1", "-shared", "-fPIC", "-fvisibility=hidden"]
+
+
+def register_kernel_library(name: str, source) -> None:
+    """Make `source` (a `.cu` file, or a `.cpp` file of host code, anywhere on disk) known as the kernel library `name`:
+    from then on `library(name)` compiles it like the package's own sources (nvcc for sm_100a, the package's `csrc` on
+    the include path, so it may use `common.cuh` and `step_ops.h`) and loads it; a part outside the package names it in
+    `kernel_libraries()` and in `program.add(name, function, ...)`. Its functions follow the package's convention:
+    `extern "C"`, 0 on success, and an `sb_last_error()` (SB_DEFINE_LAST_ERROR) for the reason otherwise."""
+    path = Path(source).resolve()
+    if not path.is_file():
+        raise BuildError(f"kernel library '{name}': no source file at {path}")
+    known = SOURCES.get(name)
+    if known is not None and _source(name) != path:
+        raise BuildError(f"a kernel library named '{name}' is already registered with another source ({_source(name)})")
+    SOURCES[name] = str(path)
+
+
+def _source(name: str) -> Path:
+    try:
+        p = Path(SOURCES[name])
+    except KeyError:
+        raise BuildError(f"no kernel library named '{name}' (known: {', '.join(sorted(SOURCES))}); "
+                         f"register_kernel_library(name, source) adds one") from None
+    return p if p.is_absolute() else CSRC / p
 
 _loaded: dict[str, ctypes.CDLL] = {}
 _lock = threading.Lock()
@@ -92,12 +117,12 @@ def _digest(src: Path) -> str:
 
 
 def library_path(name: str) -> Path:
-    src = CSRC / SOURCES[name]
+    src = _source(name)
     return _build_dir() / f"{name}-{_digest(src)}.so"
 
 
 def _compile(name: str, out: Path) -> None:
-    src = CSRC / SOURCES[name]
+    src = _source(name)
     tmp = out.with_suffix(f".tmp{os.getpid()}.so")
     if src.suffix == ".cpp":
         cmd = [_host_compiler(), *HOST_FLAGS, f"-I{CSRC}", "-o", str(tmp), str(src)]

@@ -52,10 +52,13 @@ class AttentionMixer(Mixer):
 
     def tensor_plan(self):
         t, D = self.spec.tensors, self.head_dim
-        return {t["q"]: TensorPlan((self.num_heads * D, self.hidden)),
+        plan = {t["q"]: TensorPlan((self.num_heads * D, self.hidden)),
                 t["k"]: TensorPlan((self.num_kv_heads * D, self.hidden)),
                 t["v"]: TensorPlan((self.num_kv_heads * D, self.hidden)),
                 t["o"]: TensorPlan((self.hidden, self.num_heads * D))}
+        if self.position is not None:
+            plan.update(self.position.tensor_plan())      # a position part may have tensors of its own (a learned table)
+        return plan
 
     def bind(self, tensors):
         t = self.spec.tensors
@@ -68,7 +71,14 @@ class AttentionMixer(Mixer):
             # No rotation: a table of cos = 1, sin = 0 is never read because rotary_dim is 0.
             self._cos_sin, self._rotary = torch.zeros(1, device=self.env.device), 0
         else:
-            self._cos_sin, self._rotary = self.position.cos_sin, self.position.rotary_dim
+            self.position.bind(tensors)
+            table, rotary = getattr(self.position, "cos_sin", None), getattr(self.position, "rotary_dim", None)
+            if not isinstance(table, torch.Tensor) or rotary is None or table.dim() != 3 or table.shape[-1] != 2 \
+                    or rotary % 2 or not 0 <= rotary <= self.head_dim or (rotary and table.shape[1] != rotary // 2):
+                raise TypeError(f"the position part '{self.spec.params['position'].kind}' does not offer what the attention mixer's kernels "
+                                f"read: cos_sin [positions, rotary_dim / 2, 2] float32 and an even rotary_dim <= head_dim {self.head_dim} "
+                                f"(see parts.base.PositionEncoding); an encoding of another nature needs a mixer of its own")
+            self._cos_sin, self._rotary = table, int(rotary)
 
     def weight_bytes(self):
         return self.qkv.weight_bytes() + self.o.weight_bytes()

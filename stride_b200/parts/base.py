@@ -129,7 +129,17 @@ class Norm(Part):
 
 
 class PositionEncoding(Part):
-    """Holds whatever table its mixer's kernels read; built once for `env.max_positions`."""
+    """Holds whatever table its mixer's kernels read; built once for `env.max_positions`.
+
+    The attention mixer of this package rotates queries and keys in pairs (d, d + rotary_dim / 2) of a head (the
+    "rotate-half" pairing) and reads two attributes of its position part after `bind`:
+        cos_sin     float32 [positions, rotary_dim / 2, 2] on the device: cos and sin of every position and pair
+        rotary_dim  how many leading elements of a head are rotated (even, <= head_dim; 0: none)
+    A position part that offers these (whatever its angles are: another base, another scaling, learned) works with it
+    unchanged. An encoding of another nature (a bias on the scores, interleaved pairs, a norm of q and k) needs a mixer of
+    its own; the attention mixer refuses a position part without the two attributes with a message that says so."""
+    cos_sin = None
+    rotary_dim = None
 
 
 class Mixer(Part):
@@ -148,35 +158,53 @@ class FeedForward(Part):
 
 
 class Block(Part):
-    """An arrangement of a mixer, a feed-forward and their norms around the residual stream."""
+    """An arrangement of parts around the residual stream. `ROLES` names the parts a block of this kind is made of
+    and the registry category of each; the model builds them from the layer's `LayerSpec.parts` and hands them over
+    as `self.parts[role]` (also reachable as attributes: `self.mixer`). A new arrangement (other norms, one norm for two
+    branches, no feed-forward) is a subclass with its own ROLES, `forward` and, if it has one, `emit`."""
 
-    def __init__(self, spec, env, mixer: Mixer, feed_forward: FeedForward, mixer_norm: Norm, feed_forward_norm: Norm):
+    ROLES = {"mixer_norm": "norm", "mixer": "mixer", "feed_forward_norm": "norm", "feed_forward": "feed_forward"}
+
+    def __init__(self, spec, env, parts: dict):
         super().__init__(spec, env)
-        self.mixer, self.feed_forward = mixer, feed_forward
-        self.mixer_norm, self.feed_forward_norm = mixer_norm, feed_forward_norm
+        missing = [r for r in self.ROLES if r not in parts]
+        if missing:
+            raise ValueError(f"a '{getattr(spec, 'block', type(self).__name__)}' block needs the parts {', '.join(self.ROLES)}; missing: {', '.join(missing)}")
+        self.parts = dict(parts)
 
-    def parts(self):
-        return (self.mixer_norm, self.mixer, self.feed_forward_norm, self.feed_forward)
+    def __getattr__(self, name):
+        parts = self.__dict__.get("parts")
+        if parts is not None and name in parts:
+            return parts[name]
+        raise AttributeError(name)
+
+    def all_parts(self):
+        return tuple(self.parts[r] for r in self.ROLES)
+
+    def cache_need(self):
+        """What this block's layer asks of the cache manager: by default what its part in the role "mixer" asks."""
+        mixer = self.parts.get("mixer")
+        return mixer.cache_need() if mixer is not None else None
 
     def tensor_plan(self) -> dict:
         plan = {}
-        for p in self.parts():
+        for p in self.all_parts():
             plan.update(p.tensor_plan())
         return plan
 
     def bind(self, tensors: dict) -> None:
-        for p in self.parts():
+        for p in self.all_parts():
             p.bind(tensors)
 
     def weight_bytes(self) -> int:
-        return sum(p.weight_bytes() for p in self.parts())
+        return sum(p.weight_bytes() for p in self.all_parts())
 
     def kernel_libraries(self) -> set:
-        return set().union(*(p.kernel_libraries() for p in self.parts()))
+        return set().union(*(p.kernel_libraries() for p in self.all_parts()))
 
     @property
     def all_graph_safe(self) -> bool:
-        return self.graph_safe and all(p.graph_safe for p in self.parts())
+        return self.graph_safe and all(p.graph_safe for p in self.all_parts())
 
     def forward(self, ctx, stream, cache) -> None:
         raise NotImplementedError

@@ -15,12 +15,13 @@ class DecoderModel:
         self.spec, self.env = spec, env
         self.embedding = part_class("embedding", spec.embedding.kind)(spec.embedding, env)
         self.blocks = []
-        for layer in spec.layers:
-            mixer = part_class("mixer", layer.mixer.kind)(layer.mixer, env)
-            ff = part_class("feed_forward", layer.feed_forward.kind)(layer.feed_forward, env)
-            n1 = part_class("norm", layer.mixer_norm.kind)(layer.mixer_norm, env)
-            n2 = part_class("norm", layer.feed_forward_norm.kind)(layer.feed_forward_norm, env)
-            self.blocks.append(part_class("block", layer.block)(layer, env, mixer, ff, n1, n2))
+        for i, layer in enumerate(spec.layers):
+            block_class = part_class("block", layer.block)
+            unknown = [r for r in layer.parts if r not in block_class.ROLES]
+            if unknown:
+                raise ValueError(f"layer {i}: a '{layer.block}' block has no role {', '.join(unknown)} (its roles: {', '.join(block_class.ROLES)})")
+            parts = {role: part_class(block_class.ROLES[role], ps.kind)(ps, env) for role, ps in layer.parts.items()}
+            self.blocks.append(block_class(layer, env, parts))
         self.final_norm = part_class("norm", spec.final_norm.kind)(spec.final_norm, env)
         self.head = part_class("head", spec.head.kind)(spec.head, env)
         for i, e in enumerate(spec.schedule):
@@ -55,7 +56,7 @@ class DecoderModel:
         """Per schedule entry: a CacheNeed, None, or ("shared", j)."""
         needs = []
         for e in self.spec.schedule:
-            needs.append(("shared", e.cache_of) if e.cache_of is not None else self.blocks[e.layer].mixer.cache_need())
+            needs.append(("shared", e.cache_of) if e.cache_of is not None else self.blocks[e.layer].cache_need())
         return needs
 
     def kernel_libraries(self) -> set:

@@ -325,3 +325,190 @@ def test_toy_routed_feed_forward_and_position_encoding():
     for s in slots:
         cm.release_slot(s)
     cm.check()
+
+
+# ----------------------------------------------------------------------------------------------------------------
+# A third toy architecture: a block of its own kind (ONE norm whose output feeds the mixer and the feed-forward side by
+# side: h += mixer(norm(h)) + ff(norm(h))) and a feed-forward that brings its own CUDA source, registered as a kernel
+# library from here, with a native operation, so that the whole toy model runs as one native step program. Nothing in
+# the framework's files knows of either.
+import ctypes   # noqa: E402
+
+from stride_b200.kernels import ops as _ops   # noqa: E402
+from stride_b200.kernels.build import library, register_kernel_library   # noqa: E402
+from stride_b200.parts import Block   # noqa: E402
+
+TOY_KERNEL = r'''
+#include "common.cuh"
+#include "step_ops.h"
+SB_DEFINE_LAST_ERROR()
+namespace {
+// h[t, j] += a[j] * tanhf(b[j] * x[t, j]): a per-token transform with two learned vectors
+__global__ void vecgate_kernel(const float* __restrict__ x, const float* __restrict__ a, const float* __restrict__ b,
+                               float* __restrict__ h, int n, int H) {
+  sb::grid_launch_dependents();
+  sb::grid_dependency_wait();
+  const int i = blockIdx.x * blockDim.x + threadIdx.x;
+  if (i < n * H) h[i] += a[i % H] * tanhf(b[i % H] * x[i]);
+}
+}  // namespace
+SB_EXPORT int toy_vecgate(const float* x, const float* a, const float* b, float* h, int n, int H, cudaStream_t stream) {
+  if (n <= 0) return 0;
+  sb::launch_pdl(vecgate_kernel, dim3((n * H + 255) / 256), dim3(256), 0, stream, x, a, b, h, n, H);
+  return sb::check_launch("toy_vecgate");
+}
+// the same as an operation of the native step program. i: 0 x, 1 a, 2 b, 3 h, 4 H
+SB_EXPORT int toy_op_vecgate(const SbOp* op, const SbStep* s, void* stream) {
+  using namespace sbstep;
+  return toy_vecgate(ptr<const float>(op->i[0]), ptr<const float>(op->i[1]), ptr<const float>(op->i[2]), ptr<float>(op->i[3]), s->n,
+                     (int)op->i[4], static_cast<cudaStream_t>(stream));
+}
+'''
+
+
+@pytest.fixture(scope="module")
+def toy_library(tmp_path_factory):
+    src = tmp_path_factory.mktemp("toy_kernels") / "toy_vecgate.cu"
+    src.write_text(TOY_KERNEL)
+    register_kernel_library("toy_vecgate", src)
+    return "toy_vecgate"
+
+
+@register_part("feed_forward", "toy_vecgate")
+class VecGate(FeedForward):
+    """h += a * tanh(b * x), by a kernel of the test's own library. float32 activations only."""
+    graph_safe = True
+
+    def tensor_plan(self):
+        size = self.spec.params["hidden_size"]
+        return {self.spec.tensors["a"]: TensorPlan((size,)), self.spec.tensors["b"]: TensorPlan((size,))}
+
+    def bind(self, tensors):
+        self.a, self.b = (tensors[self.spec.tensors[k]].float().contiguous() for k in ("a", "b"))
+
+    def kernel_libraries(self):
+        return {"toy_vecgate"}
+
+    def forward(self, ctx, x, stream):
+        stream.fold()
+        fn = library("toy_vecgate").toy_vecgate
+        fn.argtypes = [ctypes.c_void_p] * 4 + [ctypes.c_int, ctypes.c_int, ctypes.c_void_p]
+        assert fn(x.data_ptr(), self.a.data_ptr(), self.b.data_ptr(), stream.h.data_ptr(), ctx.n, x.shape[1], _ops._stream()) == 0
+
+    def emit(self, program, x):
+        program.need_folded("the vector gate")
+        program.add("toy_vecgate", "toy_op_vecgate", [x, self.a, self.b, program.h, x.shape[1]])
+
+
+@register_part("block", "toy_parallel")
+class ParallelBlock(Block):
+    """One norm; the mixer and the feed-forward both read its output and both add to the residual."""
+    ROLES = {"norm": "norm", "mixer": "mixer", "feed_forward": "feed_forward"}
+    graph_safe = True
+
+    def forward(self, ctx, stream, cache):
+        x = ctx.workspace.get("toy_parallel.x", ctx.n, (stream.h.shape[1],), ctx.act_dtype)
+        self.norm.forward(ctx, stream, x)
+        self.mixer.forward(ctx, x, stream, cache)
+        self.feed_forward.forward(ctx, x, stream)
+
+    def emit(self, program, cache):
+        ws = program.workspace
+        x = ws.get("toy_parallel.x", ws.max_tokens, (program.h.shape[1],), self.env.act_dtype)
+        self.norm.emit(program, x)
+        self.mixer.emit(program, x, cache)
+        self.feed_forward.emit(program, x)
+
+
+def _parallel_spec(cfg: dict) -> ModelSpec:
+    rope = PartSpec("rope", {"head_dim": D, "theta": 10000.0, "scaling": {}})
+    norm = lambda name: PartSpec("rmsnorm", {"size": H, "eps": 1e-5}, {"weight": name})
+    layers = []
+    for i in range(cfg["layers"]):
+        mixer = PartSpec("attention", {"hidden_size": H, "num_heads": HQ, "num_kv_heads": HKV, "head_dim": D, "window": 0, "position": rope},
+                         {"q": f"l{i}.q", "k": f"l{i}.k", "v": f"l{i}.v", "o": f"l{i}.o"})
+        ff = PartSpec("toy_vecgate", {"hidden_size": H}, {"a": f"l{i}.a", "b": f"l{i}.b"})
+        layers.append(LayerSpec("toy_parallel", {"norm": norm(f"l{i}.n"), "mixer": mixer, "feed_forward": ff}))
+    return ModelSpec(vocab_size=V, hidden_size=H, embedding=PartSpec("lookup", {"vocab_size": V, "hidden_size": H}, {"weight": "emb"}),
+                     layers=tuple(layers), schedule=tuple(ScheduleEntry(i, None) for i in range(cfg["layers"])), final_norm=norm("final"),
+                     head=PartSpec("linear", {"vocab_size": V, "hidden_size": H, "tied": True}, {"weight": "head", "tied_to": "emb"}),
+                     max_positions=128)
+
+
+register_architecture(Architecture("ToyParallelForCausalLM", lambda d: d, _parallel_spec))
+
+
+def _parallel_plain(w, tokens, layers):
+    T = len(tokens)
+    pos = torch.arange(T)
+    cfg = plain.PlainConfig(hidden_size=H, intermediate_size=I, num_hidden_layers=1, num_attention_heads=HQ, vocab_size=V,
+                            num_key_value_heads=HKV, head_dim=D)
+    cos, sin = plain.rope_table(cfg, pos)
+    h = plain.embedding(torch.tensor(tokens), w["emb"])
+    for l in range(layers):
+        x = plain.rms_norm(h, w[f"l{l}.n"], 1e-5)
+        q = plain.rope_apply((x @ w[f"l{l}.q"].float().T).reshape(T, HQ, D), cos, sin)
+        k = plain.rope_apply((x @ w[f"l{l}.k"].float().T).reshape(T, HKV, D), cos, sin)
+        v = (x @ w[f"l{l}.v"].float().T).reshape(T, HKV, D)
+        h = h + plain.attention(q, k, v, pos, 0) @ w[f"l{l}.o"].float().T + w[f"l{l}.a"].float() * torch.tanh(w[f"l{l}.b"].float() * x)
+    return plain.rms_norm(h, w["final"], 1e-5) @ w["emb"].float().T
+
+
+def test_a_block_of_its_own_kind_with_a_part_that_brings_its_kernel(toy_library):
+    layers = 3
+    config = {"architectures": ["ToyParallelForCausalLM"], "layers": layers}
+    g = torch.Generator().manual_seed(2)
+    r = lambda *s: (torch.randn(*s, generator=g) * 0.25).to(torch.bfloat16)
+    gain = lambda: (1 + 0.2 * torch.randn(H, generator=g)).to(torch.bfloat16)
+    w = {"emb": r(V, H), "final": gain()}
+    for i in range(layers):
+        w.update({f"l{i}.n": gain(), f"l{i}.q": r(HQ * D, H), f"l{i}.k": r(HKV * D, H), f"l{i}.v": r(HKV * D, H), f"l{i}.o": r(H, HQ * D),
+                  f"l{i}.a": r(H) * 4, f"l{i}.b": r(H) * 4})
+    reqs = [random_tokens(V, n, 11 + n) for n in (50, 23)]
+    want = [_parallel_plain(w, q, layers) for q in reqs]
+    results = {}
+    for native in (True, False):
+        eng = Engine(None, EngineOptions(dtype="float32", max_rows=64, max_full_rows=64, max_slots=4, kv_pages=40, page_size=8,
+                                         max_context=128, native_step=native), config=config, tensors=w)
+        # every part of this model has a native form, the test's own among them: the step is one native program
+        assert (eng._program is not None) == native
+        cm = eng.cache
+        slots = [cm.acquire_slot() for _ in reqs]
+        fed, step, got = [0, 0], 0, []
+        sizes = [[7, 1, 1, 16, 2], [3, 1, 1, 9]]
+        while any(f < len(q) for f, q in zip(fed, reqs)):
+            entries, spans = [], []
+            for i, q in enumerate(reqs):
+                if fed[i] >= len(q):
+                    continue
+                n = min(sizes[i][step % len(sizes[i])], len(q) - fed[i])
+                assert cm.ensure(slots[i], fed[i] + n)
+                entries.append(StepEntry(slots[i], fed[i], q[fed[i]:fed[i] + n], list(range(n))))
+                spans.append((i, fed[i], fed[i] + n))
+                fed[i] += n
+            logits = eng.step(entries).cpu()
+            got.append(logits.clone())
+            at = 0
+            for i, a, b in spans:
+                ref = want[i][a:b]
+                assert (logits[at:at + b - a] - ref).abs().max() <= 2e-4 * max(1.0, float(ref.pow(2).mean().sqrt())), (native, step, i, a, b)
+                at += b - a
+            step += 1
+        results[native] = got
+    assert all(torch.equal(a, b) for a, b in zip(results[True], results[False]))
+
+
+def test_a_position_part_of_another_nature_is_refused_with_a_reason():
+    @register_part("position", "toy_bias_only")
+    class BiasOnly(PositionEncoding):
+        """No rotation tables: an encoding that the attention mixer's kernels cannot apply."""
+
+    mixer = PartSpec("attention", {"hidden_size": H, "num_heads": HQ, "num_kv_heads": HKV, "head_dim": D, "window": 0,
+                                   "position": PartSpec("toy_bias_only", {})}, {"q": "q", "k": "k", "v": "v", "o": "o"})
+    from stride_b200.parts import BuildEnv
+    from stride_b200.parts.base import part_class
+    env = BuildEnv(device=torch.device("cuda"), compute_dtype=torch.float32, max_tokens=8, max_positions=16)
+    part = part_class("mixer", "attention")(mixer, env)
+    z = lambda *s: torch.zeros(*s, device="cuda", dtype=torch.bfloat16)
+    with pytest.raises(TypeError, match="cos_sin"):
+        part.bind({"q": z(HQ * D, H), "k": z(HKV * D, H), "v": z(HKV * D, H), "o": z(H, HQ * D)})
