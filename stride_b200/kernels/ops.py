@@ -318,8 +318,8 @@ def attention_decode_rope(qkv, cos_sin, out, cache_layer, block_table, entry_met
 
 
 def attention_tc5_supported(num_heads: int, num_kv_heads: int, head_dim: int, page_size: int) -> bool:
-    """True if the tcgen05 prompt-attention kernel takes this shape (head size 64, pages of a power of two >= 8)."""
-    if head_dim != 64 or num_kv_heads <= 0 or num_heads % num_kv_heads or num_heads // num_kv_heads > 128:
+    """True if the tcgen05 prompt-attention kernel takes this shape (head size 64 or 128, pages of a power of two >= 8)."""
+    if head_dim not in (64, 128) or num_kv_heads <= 0 or num_heads % num_kv_heads or num_heads // num_kv_heads > 128:
         return False
     return page_size >= 8 and page_size & (page_size - 1) == 0
 

@@ -120,7 +120,7 @@ class AttentionMixer(Mixer):
             return {"gemm_f32", "elementwise", "attention_generic"}
         G = self.num_heads // self.num_kv_heads
         if self.head_dim in (64, 128) and G <= 16:
-            return {"gemm_tc", "elementwise", "attention_tc"} | ({"attention_tc5"} if self.head_dim == 64 else set())
+            return {"gemm_tc", "elementwise", "attention_tc", "attention_tc5"}
         return {"gemm_tc", "elementwise", "attention_generic"}
 
     def forward(self, ctx, x, stream, cache):
@@ -148,7 +148,7 @@ class AttentionMixer(Mixer):
         ops.rope_append(qkv, ctx.positions, ctx.slots, self._cos_sin, self._rotary, q, cache.pages, cache.block_table,
                         self.num_heads, self.num_kv_heads, D, write_kv=cache.writes)
         if tensor_core:
-            # prompt portions: the tcgen05 kernel where the shape allows it (tiles of 128 rows), else mma.sync (64 rows);
+            # prompt portions: the tcgen05 kernel where the page size allows it (tiles of 128 rows), else mma.sync (64 rows);
             # decoded tokens and very short portions: the split-key decode kernel
             work, n_tiles, n_items, chunks = plan
             if tc5 and n_tiles:

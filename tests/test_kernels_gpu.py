@@ -216,7 +216,7 @@ def test_attention_tc_against_plain(D, Hq, Hkv, page, window):
                                                   (128, 6, 2, 64, 300), (64, 5, 5, 16, 0)])
 def test_attention_kernels_agree_in_bits(D, Hq, Hkv, page, window):
     """The last 150 positions of a request of 700 tokens, computed as one prompt portion by the mma.sync kernel, as one
-    portion by the tcgen05 kernel (head size 64), as portions of two positions and as single positions by the decode
+    portion by the tcgen05 kernel, as portions of two positions and as single positions by the decode
     kernel: every row has the same bits each way. This also pins that tcgen05.mma and mma.sync accumulate alike."""
     from stride_b200.kernels import ops
     T, R = 700, 150
@@ -520,12 +520,12 @@ def test_argmax_and_temperature_sampling():
             assert int(tok[r]) == want and float(val[r]) == wv
 
 
+@pytest.mark.parametrize("D", [64, 128])
 @pytest.mark.parametrize("Hq,Hkv,page,window", [(8, 2, 16, 0), (4, 4, 8, 0), (12, 4, 64, 100), (16, 1, 128, 0), (6, 2, 256, 0), (32, 8, 64, 0)])
-def test_attention_tc5_against_plain(Hq, Hkv, page, window):
-    """The tcgen05 prompt-attention kernel: portions with and without cached history, several key tiles, shuffled pages,
-    ratios that do and do not divide 128, one far key that dominates a query."""
+def test_attention_tc5_against_plain(Hq, Hkv, page, window, D):
+    """The tcgen05 prompt-attention kernel at both head sizes: portions with and without cached history, several key
+    tiles, shuffled pages, ratios that do and do not divide 128, one far key that dominates a query."""
     from stride_b200.kernels import ops
-    D = 64
     assert ops.attention_tc5_supported(Hq, Hkv, D, page)
     new = [77, 200, 40, 130, 64, 300]
     old = [0, 100, 510, 5, 63, 0]
