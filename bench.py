@@ -240,12 +240,12 @@ def reference_arm(a) -> int:
         wrote_s = time.time() - t0
         prompts = offline_prompts(64, PROMPT)
 
-        def run(batch: int, max_new: int) -> dict:
+        def run(batch: int, max_new: int, path: str = "tc") -> dict:
             """One run of the stock command line, as scripts/bench/offline.py:70-78 calls it."""
-            path = tmp / f"p{batch}.jsonl"
-            if not path.exists():
-                path.write_text("".join(json.dumps({"id": i, "tokens": p}) + "\n" for i, p in enumerate(prompts[:batch])))
-            cmd = [str(cli), "--path", "tc", "--model", str(tmp / "model"), "--input", str(path), "--output", str(tmp / "o.jsonl"),
+            source = tmp / f"p{batch}.jsonl"
+            if not source.exists():
+                source.write_text("".join(json.dumps({"id": i, "tokens": p}) + "\n" for i, p in enumerate(prompts[:batch])))
+            cmd = [str(cli), "--path", path, "--model", str(tmp / "model"), "--input", str(source), "--output", str(tmp / "o.jsonl"),
                    "--max-new", str(max_new), "--kv-gb", "16", "--concurrency", str(batch), "--max-rows", "2048",
                    "--prefill-chunk", "256", "--max-slots", "256"]
             proc = subprocess.run(cmd, capture_output=True, text=True, timeout=900)
@@ -253,16 +253,16 @@ def reference_arm(a) -> int:
                 raise RuntimeError(f"stride_cli exited with {proc.returncode}: " + " | ".join(proc.stderr.strip().splitlines()[-3:]))
             return json.loads(proc.stderr.strip().splitlines()[-1])
 
-        def measure(batch: int, repeats: int) -> dict:
+        def measure(batch: int, repeats: int, path: str = "tc") -> dict:
             """Generated tokens / run_seconds of the whole run (prefill included), first run discarded; and the
             decode steps alone: the time of the run with 256 outputs less the time of the run with one."""
             whole, first = [], []
             for r in range(repeats + 1):
-                d = run(batch, OUTPUTS)
+                d = run(batch, OUTPUTS, path)
                 if r > 0:
                     whole.append(d)
             for r in range(repeats):
-                first.append(run(batch, 1))
+                first.append(run(batch, 1, path))
             t_whole = statistics.median(d["run_seconds"] for d in whole)
             t_first = statistics.median(d["run_seconds"] for d in first)
             generated = whole[0]["generated"]
@@ -289,6 +289,11 @@ def reference_arm(a) -> int:
                 except (RuntimeError, subprocess.TimeoutExpired, ValueError, IndexError) as e:
                     points[f"decode_b{b}"] = None
                     points[f"error_b{b}"] = str(e)[:200]
+            try:        # its exact (float32) path, the counterpart of this engine's float32 point
+                points["decode_b1_float32"] = round(measure(1, 1, "exact")["decode"], 1)
+            except (RuntimeError, subprocess.TimeoutExpired, ValueError, IndexError) as e:
+                points["decode_b1_float32"] = None
+                points["error_float32"] = str(e)[:200]
         weight_bytes = 2 * (cfg["num_hidden_layers"] * (cfg["hidden_size"] * (cfg["num_attention_heads"] + 2 * cfg["num_key_value_heads"]) * cfg["head_dim"]
                                                       + cfg["num_attention_heads"] * cfg["head_dim"] * cfg["hidden_size"]
                                                       + 3 * cfg["hidden_size"] * cfg["intermediate_size"]) + cfg["vocab_size"] * cfg["hidden_size"])

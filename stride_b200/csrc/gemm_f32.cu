@@ -75,6 +75,110 @@ __global__ void __launch_bounds__(256) gemm_f32_kernel(const TX* __restrict__ x,
   }
 }
 
+// ------------------------------------------------------------------ few tokens (decode steps)
+// Up to 16 tokens: the product is a stream over the weights, and the tile kernel above would leave most of the GPU idle
+// (its 64 x 64 tiles give a [2048, 2048] weight 32 blocks). Here a block of 128 threads takes 32 output features:
+// thread (f, g) owns feature f and tokens 4 g .. 4 g + 3, one chain of fused multiply-adds each over k = 0 .. K - 1 in
+// ascending order from zero, exactly the chain of the tile kernel, so a token has the same bits from either. The
+// weights' and tokens' next 64 values of k travel into registers while the current 64 are multiplied from shared memory.
+constexpr int SF = 32;   // features per block
+constexpr int SK = 64;   // k per round
+constexpr int ST = 16;   // most tokens
+
+template <class T>
+__device__ __forceinline__ void load8(const T* p, bool ok, float* v);
+template <>
+__device__ __forceinline__ void load8<bf16>(const bf16* p, bool ok, float* v) {
+  uint4 raw = make_uint4(0, 0, 0, 0);
+  if (ok) raw = *reinterpret_cast<const uint4*>(p);
+  const uint32_t w[4] = {raw.x, raw.y, raw.z, raw.w};
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    v[2 * i] = __uint_as_float(w[i] << 16);
+    v[2 * i + 1] = __uint_as_float(w[i] & 0xFFFF0000u);
+  }
+}
+template <>
+__device__ __forceinline__ void load8<float>(const float* p, bool ok, float* v) {
+  float4 a = make_float4(0, 0, 0, 0), b = a;
+  if (ok) {
+    a = *reinterpret_cast<const float4*>(p);
+    b = *reinterpret_cast<const float4*>(p + 4);
+  }
+  v[0] = a.x, v[1] = a.y, v[2] = a.z, v[3] = a.w, v[4] = b.x, v[5] = b.y, v[6] = b.z, v[7] = b.w;
+}
+
+// VEC: rows of x and w start 16-byte aligned and K is a multiple of 8, so that eight values load at once.
+template <class TX, class TW, bool ACC, bool VEC>
+__global__ void __launch_bounds__(128) gemm_f32_small_kernel(const TX* __restrict__ x, int64_t ldx, const TW* __restrict__ w,
+                                                              int64_t ldw, float* __restrict__ out, int64_t ldo, int n, int M, int K) {
+  __shared__ float ws[SK][SF + 1];
+  __shared__ __align__(16) float xs[ST][SK];
+  sb::grid_launch_dependents();
+  const int t = threadIdx.x;
+  const int f0 = blockIdx.x * SF;
+  // what this thread fetches each round: eight consecutive k of weight row t / 8 + 16 j (j = 0, 1) and of token t / 8
+  const int lk = (t % 8) * 8, lr = t / 8;
+  float wv[2][8], xv[8];
+  auto fetch = [&](int k0, bool weights, bool tokens) {
+    const int k = k0 + lk;
+    if (weights) {
+#pragma unroll
+      for (int j = 0; j < 2; ++j) {
+        const int row = f0 + lr + 16 * j;
+        if (VEC) {
+          load8<TW>(w + static_cast<int64_t>(row) * ldw + k, row < M && k < K, wv[j]);
+        } else {
+#pragma unroll
+          for (int e = 0; e < 8; ++e) wv[j][e] = (row < M && k + e < K) ? sb::widen(w[static_cast<int64_t>(row) * ldw + k + e]) : 0.0f;
+        }
+      }
+    }
+    if (tokens) {
+      if (VEC) {
+        load8<TX>(x + static_cast<int64_t>(lr) * ldx + k, lr < n && k < K, xv);
+      } else {
+#pragma unroll
+        for (int e = 0; e < 8; ++e) xv[e] = (lr < n && k + e < K) ? sb::widen(x[static_cast<int64_t>(lr) * ldx + k + e]) : 0.0f;
+      }
+    }
+  };
+  // the weights do not depend on the kernels before this one: their first round is requested before waiting
+  fetch(0, true, false);
+  sb::grid_dependency_wait();
+  fetch(0, false, true);
+  const int f = t % SF, g = t / SF;
+  float acc[4] = {0.0f, 0.0f, 0.0f, 0.0f};
+  for (int k0 = 0; k0 < K; k0 += SK) {
+#pragma unroll
+    for (int j = 0; j < 2; ++j)
+#pragma unroll
+      for (int e = 0; e < 8; ++e) ws[lk + e][lr + 16 * j] = wv[j][e];
+#pragma unroll
+    for (int e = 0; e < 8; ++e) xs[lr][lk + e] = xv[e];
+    __syncthreads();
+    if (k0 + SK < K) fetch(k0 + SK, true, true);
+#pragma unroll 16
+    for (int k = 0; k < SK; ++k) {
+      const float b = ws[k][f];
+#pragma unroll
+      for (int i = 0; i < 4; ++i) acc[i] = fmaf(xs[4 * g + i][k], b, acc[i]);
+    }
+    __syncthreads();
+  }
+  const int c = f0 + f;
+  if (c < M) {
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      const int r = 4 * g + i;
+      if (r < n) {
+        float* o = out + static_cast<int64_t>(r) * ldo + c;
+        *o = ACC ? (*o + acc[i]) : acc[i];
+      }
+    }
+  }
+}
+
 }  // namespace
 
 // out[n, M] = x . W^T, or out += x . W^T when `accumulate` is set (the residual add).
@@ -84,6 +188,35 @@ SB_EXPORT int sb_gemm_f32(const void* x, int x_dtype, int64_t ldx, const void* w
                           int64_t ldo, int n, int M, int K, int accumulate, cudaStream_t stream) {
   if (n <= 0 || M <= 0) return 0;
   if (K <= 0) return sb::fail("sb_gemm_f32: K must be positive");
+  if (weight_dtype != 0 && weight_dtype != 1) return sb::fail("sb_gemm_f32: unsupported weight dtype %d", weight_dtype);
+  if (x_dtype != 0 && x_dtype != 1) return sb::fail("sb_gemm_f32: unsupported activation dtype %d", x_dtype);
+  if (n <= ST) {
+    const int xb = x_dtype == 0 ? 4 : 2, wb = weight_dtype == 0 ? 4 : 2;
+    const bool vec = K % 8 == 0 && (ldx * xb) % 16 == 0 && (ldw * wb) % 16 == 0 &&
+                     ((reinterpret_cast<uintptr_t>(x) | reinterpret_cast<uintptr_t>(w)) & 15) == 0;
+    const dim3 sgrid((M + SF - 1) / SF);
+#define SB_SMALL(TX, TW, ACC, VEC)                                                                                        \
+  sb::launch_pdl(gemm_f32_small_kernel<TX, TW, ACC, VEC>, sgrid, dim3(128), 0, stream, static_cast<const TX*>(x), ldx, \
+                 static_cast<const TW*>(w), ldw, out, ldo, n, M, K)
+#define SB_SMALL_V(TX, TW, ACC) \
+  do {                          \
+    if (vec) SB_SMALL(TX, TW, ACC, true); \
+    else SB_SMALL(TX, TW, ACC, false);    \
+  } while (0)
+#define SB_SMALL_A(TX, TW)                      \
+  do {                                          \
+    if (accumulate) SB_SMALL_V(TX, TW, true);   \
+    else SB_SMALL_V(TX, TW, false);             \
+  } while (0)
+    if (x_dtype == 0 && weight_dtype == 0) SB_SMALL_A(float, float);
+    else if (x_dtype == 0) SB_SMALL_A(float, bf16);
+    else if (weight_dtype == 0) SB_SMALL_A(bf16, float);
+    else SB_SMALL_A(bf16, bf16);
+#undef SB_SMALL_A
+#undef SB_SMALL_V
+#undef SB_SMALL
+    return sb::check_launch("sb_gemm_f32");
+  }
   dim3 grid((M + TN - 1) / TN, (n + TM - 1) / TM);
   if (grid.y > 65535) return sb::fail("sb_gemm_f32: %d rows exceed the grid (max %d)", n, 65535 * TM);
 #define SB_GEMM(TX, TW, ACC)                                                                          \

@@ -449,6 +449,28 @@ def test_embed_swiglu_gather():
     assert torch.equal(got, (gu + (parts[0] + parts[1]))[rows.long()])
 
 
+@pytest.mark.parametrize("M,K,wdtype,xdtype", [(333, 2048, torch.bfloat16, torch.float32), (70, 1000, torch.float32, torch.float32),
+                                               (129, 203, torch.bfloat16, torch.float32), (64, 512, torch.bfloat16, torch.bfloat16)])
+def test_gemm_f32_does_not_depend_on_the_batch(M, K, wdtype, xdtype):
+    """Up to 16 tokens the float32 product runs as a stream over the weights, beyond that in tiles: a token has the same
+    bits from either kernel, alone or among others, stored or added to what was there."""
+    from stride_b200.kernels import ops
+    x = _rand(40, K, seed=5, dtype=xdtype)
+    w = _rand(M, K, seed=6, dtype=wdtype)
+    base = _rand(40, M, seed=7)
+    tiles, tiles_acc = torch.zeros(40, M, device=DEV), base.clone()
+    ops.gemm_f32(x, w, tiles)
+    ops.gemm_f32(x, w, tiles_acc, accumulate=True)
+    ref = x.double() @ w.double().T
+    assert (tiles.double() - ref).abs().max() <= 2e-6 * float(ref.abs().max()) * math.sqrt(K)
+    for rows in ([3], [0, 1], list(range(5, 21)), list(range(24, 37))):
+        xs = x[rows].contiguous()
+        out, acc = torch.zeros(len(rows), M, device=DEV), base[rows].clone()
+        ops.gemm_f32(xs, w, out)
+        ops.gemm_f32(xs, w, acc, accumulate=True)
+        assert torch.equal(out, tiles[rows]) and torch.equal(acc, tiles_acc[rows]), f"{len(rows)} tokens"
+
+
 @pytest.mark.parametrize("n,M,K,wdtype", [(5, 77, 33, torch.float32), (70, 130, 200, torch.bfloat16), (1, 1000, 64, torch.bfloat16)])
 def test_gemm_f32(n, M, K, wdtype):
     from stride_b200.kernels import ops
