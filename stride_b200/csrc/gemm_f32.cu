@@ -85,86 +85,123 @@ constexpr int SF = 32;   // features per block
 constexpr int SK = 64;   // k per round
 constexpr int ST = 16;   // most tokens
 
+constexpr int SR = 4;    // rounds of loads in flight per thread
+
+// Eight consecutive values as they are stored, fetched in one or two 16-byte loads and widened when they are used.
 template <class T>
-__device__ __forceinline__ void load8(const T* p, bool ok, float* v);
+struct Raw8;
 template <>
-__device__ __forceinline__ void load8<bf16>(const bf16* p, bool ok, float* v) {
-  uint4 raw = make_uint4(0, 0, 0, 0);
-  if (ok) raw = *reinterpret_cast<const uint4*>(p);
-  const uint32_t w[4] = {raw.x, raw.y, raw.z, raw.w};
+struct Raw8<bf16> {
+  uint4 raw;
+  __device__ __forceinline__ void load(const bf16* p, bool ok) {
+    raw = make_uint4(0, 0, 0, 0);
+    if (ok) raw = *reinterpret_cast<const uint4*>(p);
+  }
+  __device__ __forceinline__ void set(int e, float v) {
+    uint32_t* w = &raw.x;
+    const uint32_t bits = static_cast<uint32_t>(__bfloat16_as_ushort(__float2bfloat16_rn(v)));   // exact: v was widened from bfloat16
+    w[e >> 1] = (e & 1) ? ((w[e >> 1] & 0x0000FFFFu) | (bits << 16)) : ((w[e >> 1] & 0xFFFF0000u) | bits);
+  }
+  __device__ __forceinline__ void widen(float* v) const {
+    const uint32_t w[4] = {raw.x, raw.y, raw.z, raw.w};
 #pragma unroll
-  for (int i = 0; i < 4; ++i) {
-    v[2 * i] = __uint_as_float(w[i] << 16);
-    v[2 * i + 1] = __uint_as_float(w[i] & 0xFFFF0000u);
+    for (int i = 0; i < 4; ++i) {
+      v[2 * i] = __uint_as_float(w[i] << 16);
+      v[2 * i + 1] = __uint_as_float(w[i] & 0xFFFF0000u);
+    }
   }
-}
+};
 template <>
-__device__ __forceinline__ void load8<float>(const float* p, bool ok, float* v) {
-  float4 a = make_float4(0, 0, 0, 0), b = a;
-  if (ok) {
-    a = *reinterpret_cast<const float4*>(p);
-    b = *reinterpret_cast<const float4*>(p + 4);
+struct Raw8<float> {
+  float4 a, b;
+  __device__ __forceinline__ void load(const float* p, bool ok) {
+    a = make_float4(0, 0, 0, 0), b = a;
+    if (ok) {
+      a = *reinterpret_cast<const float4*>(p);
+      b = *reinterpret_cast<const float4*>(p + 4);
+    }
   }
-  v[0] = a.x, v[1] = a.y, v[2] = a.z, v[3] = a.w, v[4] = b.x, v[5] = b.y, v[6] = b.z, v[7] = b.w;
-}
+  __device__ __forceinline__ void set(int e, float v) { (&a.x)[e] = v; }     // a and b are adjacent: e = 0 .. 7
+  __device__ __forceinline__ void widen(float* v) const {
+    v[0] = a.x, v[1] = a.y, v[2] = a.z, v[3] = a.w, v[4] = b.x, v[5] = b.y, v[6] = b.z, v[7] = b.w;
+  }
+};
 
 // VEC: rows of x and w start 16-byte aligned and K is a multiple of 8, so that eight values load at once.
 template <class TX, class TW, bool ACC, bool VEC>
 __global__ void __launch_bounds__(128) gemm_f32_small_kernel(const TX* __restrict__ x, int64_t ldx, const TW* __restrict__ w,
                                                               int64_t ldw, float* __restrict__ out, int64_t ldo, int n, int M, int K) {
   __shared__ float ws[SK][SF + 1];
-  __shared__ __align__(16) float xs[ST][SK];
+  __shared__ __align__(16) float xs[SK][ST];     // [k][token]: a thread's four tokens are one 16-byte read
   sb::grid_launch_dependents();
   const int t = threadIdx.x;
   const int f0 = blockIdx.x * SF;
-  // what this thread fetches each round: eight consecutive k of weight row t / 8 + 16 j (j = 0, 1) and of token t / 8
+  // what this thread fetches each round: eight consecutive k of weight rows t / 8 and t / 8 + 16 and of token t / 8.
+  // SR rounds are in flight at a time: a stream over the weights needs that many bytes on their way to keep HBM busy.
   const int lk = (t % 8) * 8, lr = t / 8;
-  float wv[2][8], xv[8];
-  auto fetch = [&](int k0, bool weights, bool tokens) {
+  Raw8<TW> wv[SR][2];
+  Raw8<TX> xv[SR];
+  auto fetch_w = [&](Raw8<TW>* dst, int k0) {
     const int k = k0 + lk;
-    if (weights) {
 #pragma unroll
-      for (int j = 0; j < 2; ++j) {
-        const int row = f0 + lr + 16 * j;
-        if (VEC) {
-          load8<TW>(w + static_cast<int64_t>(row) * ldw + k, row < M && k < K, wv[j]);
-        } else {
-#pragma unroll
-          for (int e = 0; e < 8; ++e) wv[j][e] = (row < M && k + e < K) ? sb::widen(w[static_cast<int64_t>(row) * ldw + k + e]) : 0.0f;
-        }
-      }
-    }
-    if (tokens) {
+    for (int j = 0; j < 2; ++j) {
+      const int row = f0 + lr + 16 * j;
       if (VEC) {
-        load8<TX>(x + static_cast<int64_t>(lr) * ldx + k, lr < n && k < K, xv);
+        dst[j].load(w + static_cast<int64_t>(row) * ldw + k, row < M && k < K);
       } else {
 #pragma unroll
-        for (int e = 0; e < 8; ++e) xv[e] = (lr < n && k + e < K) ? sb::widen(x[static_cast<int64_t>(lr) * ldx + k + e]) : 0.0f;
+        for (int e = 0; e < 8; ++e) dst[j].set(e, (row < M && k + e < K) ? sb::widen(w[static_cast<int64_t>(row) * ldw + k + e]) : 0.0f);
       }
     }
   };
-  // the weights do not depend on the kernels before this one: their first round is requested before waiting
-  fetch(0, true, false);
+  auto fetch_x = [&](Raw8<TX>& dst, int k0) {
+    const int k = k0 + lk;
+    if (VEC) {
+      dst.load(x + static_cast<int64_t>(lr) * ldx + k, lr < n && k < K);
+    } else {
+#pragma unroll
+      for (int e = 0; e < 8; ++e) dst.set(e, (lr < n && k + e < K) ? sb::widen(x[static_cast<int64_t>(lr) * ldx + k + e]) : 0.0f);
+    }
+  };
+  // the weights do not depend on the kernels before this one: their first rounds are requested before waiting
+#pragma unroll
+  for (int r = 0; r < SR; ++r) fetch_w(wv[r], r * SK);
   sb::grid_dependency_wait();
-  fetch(0, false, true);
+#pragma unroll
+  for (int r = 0; r < SR; ++r) fetch_x(xv[r], r * SK);
   const int f = t % SF, g = t / SF;
   float acc[4] = {0.0f, 0.0f, 0.0f, 0.0f};
-  for (int k0 = 0; k0 < K; k0 += SK) {
+  for (int k0 = 0; k0 < K; k0 += SR * SK) {
 #pragma unroll
-    for (int j = 0; j < 2; ++j)
+    for (int r = 0; r < SR; ++r) {
+      const int kk = k0 + r * SK;
+      if (kk >= K) break;
+      float v[8];
 #pragma unroll
-      for (int e = 0; e < 8; ++e) ws[lk + e][lr + 16 * j] = wv[j][e];
+      for (int j = 0; j < 2; ++j) {
+        wv[r][j].widen(v);
 #pragma unroll
-    for (int e = 0; e < 8; ++e) xs[lr][lk + e] = xv[e];
-    __syncthreads();
-    if (k0 + SK < K) fetch(k0 + SK, true, true);
+        for (int e = 0; e < 8; ++e) ws[lk + e][lr + 16 * j] = v[e];
+      }
+      xv[r].widen(v);
+#pragma unroll
+      for (int e = 0; e < 8; ++e) xs[lk + e][lr] = v[e];
+      __syncthreads();
+      fetch_w(wv[r], kk + SR * SK);     // (past the end: nothing is read)
+      fetch_x(xv[r], kk + SR * SK);
+      if (4 * g < n) {      // (a warp has one g: warps whose tokens the step does not have only help with the loads)
 #pragma unroll 16
-    for (int k = 0; k < SK; ++k) {
-      const float b = ws[k][f];
-#pragma unroll
-      for (int i = 0; i < 4; ++i) acc[i] = fmaf(xs[4 * g + i][k], b, acc[i]);
+        for (int k = 0; k < SK; ++k) {
+          const float b = ws[k][f];
+          const float4 a = *reinterpret_cast<const float4*>(&xs[k][4 * g]);
+          acc[0] = fmaf(a.x, b, acc[0]);
+          acc[1] = fmaf(a.y, b, acc[1]);
+          acc[2] = fmaf(a.z, b, acc[2]);
+          acc[3] = fmaf(a.w, b, acc[3]);
+        }
+      }
+      __syncthreads();
     }
-    __syncthreads();
   }
   const int c = f0 + f;
   if (c < M) {
