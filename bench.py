@@ -157,9 +157,10 @@ def build_reference() -> tuple:
     how = "nvcc -O3 -fmad=false -Xcompiler=-fno-strict-aliasing -DSTRIDE_BACKEND_CUDA, arch sm_100 (CMakeLists.txt:36-44 has 89)"
     if cli.exists():
         return cli, how + "; prebuilt"
-    src = REF_DIR if (REF_DIR / "src").exists() else Path("/root/reference")
+    # the unmodified copy under baseline/_ref, else a checkout named by STRIDE_REFERENCE or lying beside this repository
+    src = REF_DIR if (REF_DIR / "src").exists() else Path(os.environ.get("STRIDE_REFERENCE", ROOT.parent / "reference"))
     if not (src / "src" / "engine.cpp").exists():
-        return None, "the reference's sources are neither under baseline/_ref nor at /root/reference"
+        return None, "the reference's sources are neither under baseline/_ref nor in a checkout beside this repository (STRIDE_REFERENCE)"
     inc = _json_include()
     nvcc = shutil.which("nvcc") or "/usr/local/cuda/bin/nvcc"
     if inc is None or not Path(nvcc).exists():
