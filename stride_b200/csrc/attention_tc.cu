@@ -853,7 +853,8 @@ SB_EXPORT int sb_attention_decode_noalloc(const void* q, void* out, const void* 
 // The decode items of the step's tile plan (and its tiles, unless the tcgen05 kernel took them) on the mma.sync
 // kernels; with a fused plan, rotation and append run inside the decode kernel, from the projection's partial sums.
 // i: 0 q, 1 out, 2 cache layer, 3 block table, 4 pages per sequence, 5 page size, 6 page stride, 7 v offset, 8 head stride,
-//    9 scratch, 10 floats of scratch, 11 counters, 12 Hq, 13 Hkv, 14 D, 15 window, 16 tile plan,
+//    9 where the scratch buffer is noted (two int64 on the host: its device address and its size in floats; the engine
+//    enlarges the buffer before a step that needs more), 10 unused, 11 counters, 12 Hq, 13 Hkv, 14 D, 15 window, 16 tile plan,
 //    17 the tiles went to the tcgen05 kernel, 18 qkv partial sums (flat), 19 their width, 20 K ranges S,
 //    21 most tokens with a buffer per range, 22 cos_sin; f: 0 scale
 SB_EXPORT int sb_op_attention_tc(const SbOp* op, const SbStep* s, void* stream) {
@@ -861,20 +862,22 @@ SB_EXPORT int sb_op_attention_tc(const SbOp* op, const SbStep* s, void* stream) 
   const SbTilePlan& plan = s->plan[op->i[16]];
   const int Hq = (int)op->i[12], Hkv = (int)op->i[13], D = (int)op->i[14];
   cudaStream_t st = static_cast<cudaStream_t>(stream);
-  if (plan.items > 0 && sb_attention_tc_scratch(plan.items, Hkv, plan.chunks, D) > op->i[10])
+  const int64_t* noted = ptr<const int64_t>(op->i[9]);
+  float* scratch = ptr<float>(noted[0]);
+  if (plan.items > 0 && sb_attention_tc_scratch(plan.items, Hkv, plan.chunks, D) > noted[1])
     return sb::fail("sb_op_attention_tc: %d decode entries over %d chunks need more scratch than the engine set aside (%lld floats)",
-                    plan.items, plan.chunks, (long long)op->i[10]);
+                    plan.items, plan.chunks, (long long)noted[1]);
   if (plan.fused) {
     const int P = partial_count(op->i[20], op->i[21], s->n);
     return sb_attention_decode_rope(ptr<const float>(op->i[18]), P, static_cast<int64_t>(s->n) * op->i[19], ptr<const float>(op->i[22]),
                                     ptr<void>(op->i[1]), ptr<void>(op->i[2]), ptr<const int32_t>(op->i[3]), (int)op->i[4], (int)op->i[5],
                                     op->i[6], op->i[7], op->i[8], entry_meta(s), s->max_rows, work(s, plan), plan.items, plan.chunks,
-                                    ptr<float>(op->i[9]), ptr<int>(op->i[11]), Hq, Hkv, D, (int)op->i[15], static_cast<float>(op->f[0]), st);
+                                    scratch, ptr<int>(op->i[11]), Hq, Hkv, D, (int)op->i[15], static_cast<float>(op->f[0]), st);
   }
   const int tiles = op->i[17] ? 0 : plan.tiles;
   if (tiles <= 0 && plan.items <= 0) return SB_OP_SKIPPED;
   const int32_t* list = work(s, plan) + (op->i[17] ? 2 * plan.tiles : 0);
   return sb_attention_tc(ptr<const void>(op->i[0]), ptr<void>(op->i[1]), ptr<const void>(op->i[2]), ptr<const int32_t>(op->i[3]),
                          (int)op->i[4], (int)op->i[5], op->i[6], op->i[7], op->i[8], entry_meta(s), s->max_rows, list, tiles, plan.items,
-                         plan.chunks, ptr<float>(op->i[9]), ptr<int>(op->i[11]), Hq, Hkv, D, (int)op->i[15], static_cast<float>(op->f[0]), st);
+                         plan.chunks, scratch, ptr<int>(op->i[11]), Hq, Hkv, D, (int)op->i[15], static_cast<float>(op->f[0]), st);
 }

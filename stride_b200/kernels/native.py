@@ -87,6 +87,7 @@ class StepProgram:
         self._keep: list = []                 # tensors the operations point into
         self.step = SbStep()
         self._failed, self._launched = c_int32(0), c_int32(0)
+        self._growing: dict = {}              # name -> [note (address, elements), dtype, {key: need(step) -> elements}]
 
     def __del__(self):
         handle, self._handle = getattr(self, "_handle", None), None
@@ -119,6 +120,22 @@ class StepProgram:
             raise RuntimeError(self._lib.sb_last_error().decode())
         self._libraries.append(library_name)
 
+    def growing_buffer(self, name: str, dtype: torch.dtype, key, need) -> int:
+        """A flat buffer of the workspace whose size depends on the step (`Workspace.grow`): `need(step) -> elements` is
+        asked before every step and the buffer enlarged when it is too small. Returns the host address of its note, two
+        int64 (the buffer's device address, its size in elements), which an operation reads when it runs; operations
+        that ask under one `name` share one buffer. `key` tells equal askers apart from different ones."""
+        entry = self._growing.setdefault(name, [(c_int64 * 2)(0, 0), dtype, {}])
+        entry[2].setdefault(key, need)
+        return ctypes.addressof(entry[0])
+
+    def _grow(self) -> None:
+        for name, (note, dtype, askers) in self._growing.items():
+            need = max(fn(self.step) for fn in askers.values())
+            if need > note[1]:
+                buf = self.workspace.grow(name, need, dtype)       # (moves the buffer: recorded graphs are dropped by the engine)
+                note[0], note[1] = buf.data_ptr(), buf.numel()
+
     def take_pending(self):
         p, self.pending = self.pending, None
         return p
@@ -132,6 +149,8 @@ class StepProgram:
         if self._lib.sb_program_prepare(self._handle, E, count, first, n, wanted, static_keys, staging_p, device_ints.data_ptr(),
                                         ctypes.byref(self.step)) < 0:
             raise RuntimeError(self._lib.sb_last_error().decode())
+        if self._growing:
+            self._grow()
 
     def run(self) -> None:
         """Launch the step that `prepare` described on the current torch stream."""

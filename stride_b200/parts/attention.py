@@ -192,17 +192,13 @@ class AttentionMixer(Mixer):
             if tc5:
                 program.add("attention_tc5", "sb_op_attention_tc5",
                             [q, mixed, pages, pages.shape[0], *where[1:], self.num_heads, self.num_kv_heads, D, self.window, plan], [self.scale])
-            # scratch for the most decode entries a step can bring, over the longest context
-            # (a recorded decode step pads its batch and its key range to powers of two)
-            items = min(T, 2 * env.max_requests + 2) if env.max_requests else T
-            keys = 256
-            while keys < env.max_positions:
-                keys *= 2
-            chunks = keys // 256
-            scratch = ws.grow("attn.scratch", ops.attention_tc_scratch(items, self.num_kv_heads, chunks, D), torch.float32)
+            # the decode kernel's chunk records: as many as the step's decode entries and their longest context need
+            kv, need = self.num_kv_heads, ops.attention_tc_scratch
+            scratch = program.growing_buffer("attn.scratch", torch.float32, (plan, kv, D),
+                                             lambda step, k=plan: need(step.plan[k].items, kv, step.plan[k].chunks, D))
             counters = ws.raw("attn.counters", (T * self.num_kv_heads,), torch.int32)
             program.add("attention_tc", "sb_op_attention_tc",
-                        [q, mixed, *where, scratch, scratch.numel(), counters, self.num_heads, self.num_kv_heads, D, self.window, plan,
+                        [q, mixed, *where, scratch, 0, counters, self.num_heads, self.num_kv_heads, D, self.window, plan,
                          int(tc5), qkv, self.qkv_width, S, program.few_tokens, self._cos_sin], [self.scale])
         else:
             program.add("attention_generic", "sb_op_attention_generic",
