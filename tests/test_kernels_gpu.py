@@ -542,6 +542,31 @@ def test_argmax_and_temperature_sampling():
             assert int(tok[r]) == want and float(val[r]) == wv
 
 
+def test_argmax_of_a_large_vocabulary_in_slices():
+    """A large vocabulary is cut into slices, one CTA each: the largest logit and the smallest index among equals still
+    win, whichever slices they lie in; not-a-numbers are passed over; a second call finds the library's words clean."""
+    from stride_b200.kernels import ops
+    rows, V = 5, 70003
+    for call in range(3):
+        logits = _rand(rows, V, seed=20 + call, scale=2.0)
+        top = float(logits.max()) + 1.0
+        logits[0, 69000] = logits[0, 41] = logits[0, 30000] = top       # equal maxima in three slices: index 41 wins
+        logits[1, V - 1] = top                                          # the very last logit
+        logits[2, 17] = float("nan")
+        logits[2, 5000] = top
+        logits[3] = float("nan")                                        # nothing to choose from: token 0
+        slots = torch.tensor([3, 0, 4, 1, 2], dtype=torch.int32, device=DEV)
+        table = torch.full((5,), -1, dtype=torch.int32, device=DEV)
+        tok = torch.full((rows,), -5, dtype=torch.int32, device=DEV)
+        val = torch.zeros(rows, device=DEV)
+        ops.argmax(logits, tok, val, slots, table)
+        clean = torch.nan_to_num(logits, nan=-float("inf"))
+        want = clean.argmax(dim=1)
+        assert tok.tolist()[:3] == [41, V - 1, 5000] and int(tok[3]) == 0 and int(tok[4]) == int(want[4])
+        assert float(val[0]) == top and float(val[4]) == float(clean[4, want[4]])
+        assert table[slots.long()].tolist() == tok.tolist()
+
+
 @pytest.mark.parametrize("D", [64, 128])
 @pytest.mark.parametrize("Hq,Hkv,page,window", [(8, 2, 16, 0), (4, 4, 8, 0), (12, 4, 64, 100), (16, 1, 128, 0), (6, 2, 256, 0), (32, 8, 64, 0)])
 def test_attention_tc5_against_plain(Hq, Hkv, page, window, D):
