@@ -8,8 +8,9 @@
 // descending, index ascending), weight_i = exp((l_i - l_max) / T) in 64-bit (kept
 // as an integer multiple of 2^-40, so that sums do not depend on their order),
 // u = uniform * sum of weights, and the token is the first in rank order whose
-// cumulative weight exceeds u. The rank order is walked by a radix search over
-// the logit's bit pattern (four passes of eight bits, weighted histograms).
+// cumulative weight exceeds u. The rank order is walked by weighted histograms:
+// 256 bins of the distance from the largest logit, then a radix search over the
+// logit's bit pattern inside the chosen bin (four passes of eight bits).
 // The uniform is keyed on (seed, length of the sequence) alone:
 // r = splitmix64(seed ^ (length * 0x9E3779B97F4A7C15)), uniform = (r >> 11) * 2^-53,
 // so a draw does not depend on the batch or the schedule.
@@ -20,6 +21,7 @@ SB_DEFINE_LAST_ERROR()
 namespace {
 
 constexpr int kThreads = 1024;
+constexpr int kSampleThreads = 512;   // threads of a CTA of the temperature sampler
 
 __device__ __forceinline__ uint32_t order_key(float v) {
   const uint32_t b = __float_as_uint(v);
@@ -138,115 +140,247 @@ __global__ void __launch_bounds__(kSplitThreads) argmax_split_kernel(const float
   }
 }
 
-__global__ void __launch_bounds__(kThreads) sample_temperature_kernel(
+// f(logit, index) for the logits [begin, end) of a row, in no particular order (what the callers add up does not depend
+// on it). With `vec` (the row starts 16-byte aligned and `begin` is a multiple of four) a thread has four 16-byte loads in
+// flight at a time: with one, a walk over a row took as long as its trips to memory one after another.
+template <class F>
+__device__ __forceinline__ void for_each_logit(const float* __restrict__ l, int begin, int end, bool vec, F f) {
+  const int t = threadIdx.x;
+  int done = begin;
+  if (vec) {
+    const float4* l4 = reinterpret_cast<const float4*>(l);
+    const int b4 = begin / 4, e4 = end / 4;
+    for (int i0 = b4 + t; i0 < e4; i0 += 4 * kSampleThreads) {
+      float4 v[4];
+#pragma unroll
+      for (int u = 0; u < 4; ++u)
+        if (i0 + u * kSampleThreads < e4) v[u] = l4[i0 + u * kSampleThreads];
+#pragma unroll
+      for (int u = 0; u < 4; ++u) {
+        const int i = i0 + u * kSampleThreads;
+        if (i < e4) {
+          f(v[u].x, 4 * i);
+          f(v[u].y, 4 * i + 1);
+          f(v[u].z, 4 * i + 2);
+          f(v[u].w, 4 * i + 3);
+        }
+      }
+    }
+    done = max(begin, e4 * 4);
+  }
+  for (int i = done + t; i < end; i += kSampleThreads) f(l[i], i);
+}
+
+// Shared memory of another CTA of the cluster: the address of `p` (a shared-memory address of this CTA) in CTA `rank`.
+__device__ __forceinline__ uint32_t peer_shared(const void* p, uint32_t rank) {
+  uint32_t out;
+  asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(out) : "r"(static_cast<uint32_t>(__cvta_generic_to_shared(p))), "r"(rank));
+  return out;
+}
+__device__ __forceinline__ unsigned long long peer_load_u64(uint32_t addr) {
+  unsigned long long v;
+  asm volatile("ld.shared::cluster.u64 %0, [%1];" : "=l"(v) : "r"(addr) : "memory");
+  return v;
+}
+__device__ __forceinline__ uint32_t peer_load_u32(uint32_t addr) {
+  uint32_t v;
+  asm volatile("ld.shared::cluster.u32 %0, [%1];" : "=r"(v) : "r"(addr) : "memory");
+  return v;
+}
+__device__ __forceinline__ uint32_t cluster_size() {
+  uint32_t n;
+  asm volatile("mov.u32 %0, %%cluster_nctarank;" : "=r"(n));
+  return n;
+}
+
+// The rank order (logit descending, index ascending) is walked in two levels. First 256 bins of the distance from the
+// largest logit, d = max - l, linear over [0, min(max - min, 30 T)]: a monotone function of the logit, so the bins follow
+// the rank order, and one that spreads a vocabulary's bulk over many bins whatever the temperature is (the leading byte of
+// the logit's bit pattern would put it into a handful, and a hundred thousand additions to a handful of shared-memory
+// words take a millisecond). A token further than 30 T from the top has weight floor(e^-30 * 2^40) = 0 and is passed
+// over. Then, inside the chosen bin, the radix search over the logit's bit pattern, eight bits a pass.
+//
+// A row belongs to a cluster of CTAs (blockIdx.x = the CTA's rank, blockIdx.y = the row): each takes a slice of the
+// vocabulary and keeps histograms of its own, since the 64-bit exponentials of a large vocabulary are more than one
+// SM's few 64-bit units do in a decode step's time; after every walk the first CTA adds the cluster's histograms up
+// through distributed shared memory (integers: no order to keep), decides, and the others read its decision.
+struct Decision {
+  unsigned long long u;      // what is left of the draw inside the chosen part
+  uint32_t prefix;           // the logit's bits chosen so far
+  int bin, found;
+};
+
+__global__ void __launch_bounds__(kSampleThreads) sample_temperature_kernel(
     const float* __restrict__ logits, int64_t ld, int vocab, const float* __restrict__ temperatures,
     const unsigned long long* __restrict__ seeds, const int32_t* __restrict__ lengths, int32_t* __restrict__ tokens,
     float* __restrict__ values, const int32_t* __restrict__ scatter_index, int32_t* __restrict__ scatter,
     const int* __restrict__ watch) {
   __shared__ unsigned long long hist[256];
-  __shared__ int count[256];
+  __shared__ unsigned int count[256];
   __shared__ float red[32];
-  __shared__ unsigned long long total_s;
-  __shared__ uint32_t prefix_s;
-  __shared__ unsigned long long u_s;
-  __shared__ int found_s;
+  __shared__ float extremes[2];
+  __shared__ Decision decision;
   sb::grid_launch_dependents();
   sb::grid_dependency_wait();
-  const int row = blockIdx.x, t = threadIdx.x;
+  const int row = blockIdx.y, t = threadIdx.x;
+  const uint32_t rank = sb::cluster_rank(), ranks = cluster_size();
   const float* l = logits + static_cast<int64_t>(row) * ld;
-  if (!(temperatures[row] > 0.0f)) return;     // a greedy row: the argmax kernel has chosen its token
-  const double T = static_cast<double>(temperatures[row]);
+  const bool sampled = temperatures[row] > 0.0f;     // (a greedy row: the argmax kernel has chosen its token; the cluster
+  const double T = static_cast<double>(temperatures[row]);   // still walks through its barriers together)
+  // this CTA's slice, a multiple of four logits so that every slice starts 16-byte aligned within an aligned row
+  const int slice = ((vocab + static_cast<int>(ranks) - 1) / static_cast<int>(ranks) + 3) & ~3;
+  const int begin = sampled ? min(vocab, static_cast<int>(rank) * slice) : 0, end = sampled ? min(vocab, begin + slice) : 0;
+  const bool vec = (reinterpret_cast<uintptr_t>(l) & 15) == 0;
 
-  float mx = -INFINITY;
-  for (int i = t; i < vocab; i += kThreads) {
-    const float v = l[i];
-    if (v == v) mx = fmaxf(mx, v);
-  }
+  float mx = -INFINITY, mn = INFINITY;
+  for_each_logit(l, begin, end, vec, [&](float v, int) {
+    if (v == v) {
+      mx = fmaxf(mx, v);
+      mn = fminf(mn, v);
+    }
+  });
   mx = sb::block_max(mx, red);
+  mn = -sb::block_max(-mn, red);
+  if (t == 0) extremes[0] = mx, extremes[1] = mn;
+  sb::cluster_sync();
+  for (uint32_t r = 0; r < ranks; ++r) {
+    mx = fmaxf(mx, __uint_as_float(peer_load_u32(peer_shared(&extremes[0], r))));
+    mn = fminf(mn, __uint_as_float(peer_load_u32(peer_shared(&extremes[1], r))));
+  }
   const double top = static_cast<double>(mx);
-
-  if (t == 0) total_s = 0;
-  __syncthreads();
-  unsigned long long sum = 0;
-  for (int i = t; i < vocab; i += kThreads) {
-    const float v = l[i];
-    if (v == v) sum += fixed_weight(v, top, T);
-  }
-  for (int o = 16; o > 0; o >>= 1) sum += __shfl_xor_sync(0xffffffffu, sum, o);
-  if ((t & 31) == 0) atomicAdd(&total_s, sum);
-  __syncthreads();
-  if (t == 0) {
-    // u = floor(uniform * total), uniform = (r >> 11) * 2^-53: a 53 x 62 bit product, shifted down by 53
-    const unsigned long long r =
-        splitmix64(seeds[row] ^ (static_cast<unsigned long long>(static_cast<uint32_t>(lengths[row])) * 0x9E3779B97F4A7C15ULL));
-    const unsigned long long m = r >> 11, total = total_s;
-    u_s = (__umul64hi(m, total) << 11) | ((m * total) >> 53);
-    prefix_s = 0;
-  }
-  __syncthreads();
-
-  for (int shift = 24; shift >= 0; shift -= 8) {
-    for (int b = t; b < 256; b += kThreads) {
-      hist[b] = 0;
-      count[b] = 0;
+  const float cut = 30.0f * temperatures[row];
+  float range = fminf(mx - mn, cut);
+  if (!(range > 0.0f)) range = 1.0f;             // one distinct logit (or none): everything lands in bin 0
+  const float per_bin = 255.0f / range;
+  // the bin of a logit: 0 for the largest, ascending with the distance from it; -1: weight 0, never drawn
+  auto bin_of = [&](float v) {
+    const float d = mx - v;
+    if (!(d <= cut)) return -1;
+    const float b = d * per_bin;
+    return b >= 255.0f ? 255 : static_cast<int>(b);
+  };
+  // the cluster's histograms added up by its first CTA (thread b takes bin b)
+  auto cluster_sum = [&](int b, unsigned long long& weight, unsigned int& number) {
+    weight = 0, number = 0;
+    for (uint32_t r = 0; r < ranks; ++r) {
+      weight += peer_load_u64(peer_shared(&hist[b], r));
+      number += peer_load_u32(peer_shared(&count[b], r));
     }
-    __syncthreads();
-    const uint32_t prefix = prefix_s;
-    const uint32_t mask = shift == 24 ? 0u : (0xFFFFFFFFu << (shift + 8));
-    for (int i = t; i < vocab; i += kThreads) {
-      const float v = l[i];
-      if (v != v) continue;
-      const uint32_t key = order_key(v);
-      if ((key & mask) != prefix) continue;
-      const int b = (key >> shift) & 0xFF;
-      atomicAdd(&hist[b], fixed_weight(v, top, T));
-      atomicAdd(&count[b], 1);
-    }
+  };
+
+  for (int b = t; b < 256; b += kSampleThreads) hist[b] = 0, count[b] = 0;
+  __syncthreads();
+  for_each_logit(l, begin, end, vec, [&](float v, int) {
+    if (v != v) return;
+    const int b = bin_of(v);
+    if (b < 0) return;
+    const unsigned long long w = fixed_weight(v, top, T);
+    if (w != 0) atomicAdd(&hist[b], w);
+  });
+  sb::cluster_sync();
+  if (rank == 0) {
+    unsigned long long w = 0;
+    unsigned int c = 0;
+    if (t < 256) cluster_sum(t, w, c);
+    __syncthreads();         // (this CTA's own histogram has been read: it is overwritten with the sums)
+    if (t < 256) hist[t] = w;
     __syncthreads();
     if (t == 0) {
-      unsigned long long u = u_s, cum = 0;
-      int chosen = -1, lowest = 0;
-      for (int b = 255; b >= 0; --b) {
-        if (count[b] == 0) continue;
-        lowest = b;
+      unsigned long long total = 0;
+      for (int b = 0; b < 256; ++b) total += hist[b];
+      // u = floor(uniform * total), uniform = (r >> 11) * 2^-53: a 53 x 62 bit product, shifted down by 53; u < total
+      const unsigned long long r =
+          splitmix64(seeds[row] ^ (static_cast<unsigned long long>(static_cast<uint32_t>(lengths[row])) * 0x9E3779B97F4A7C15ULL));
+      const unsigned long long m = r >> 11;
+      unsigned long long u = (__umul64hi(m, total) << 11) | ((m * total) >> 53), cum = 0;
+      int chosen = 0;
+      for (int b = 0; b < 256; ++b) {
         if (u < cum + hist[b]) {
           chosen = b;
           break;
         }
         cum += hist[b];
       }
-      if (chosen < 0) {  // only tokens of weight 0 are left: the last token in rank order
-        chosen = lowest;
-        cum = 0;
-        u = hist[lowest];
-      }
-      u_s = u - cum;
-      prefix_s = prefix | (static_cast<uint32_t>(chosen) << shift);
-      found_s = count[chosen];
+      decision.bin = chosen;
+      decision.u = u - cum;
+      decision.prefix = 0;
+      decision.found = 0;
     }
+  }
+  sb::cluster_sync();
+  const int bin = static_cast<int>(peer_load_u32(peer_shared(&decision.bin, 0)));
+
+  for (int shift = 24; shift >= 0; shift -= 8) {
+    // (the first CTA has read every histogram of the walk before, and does not touch its decision again before the
+    // barrier after this walk: no barrier is needed here)
+    const uint32_t prefix = peer_load_u32(peer_shared(&decision.prefix, 0));
+    for (int b = t; b < 256; b += kSampleThreads) hist[b] = 0, count[b] = 0;
     __syncthreads();
+    const uint32_t mask = shift == 24 ? 0u : (0xFFFFFFFFu << (shift + 8));
+    for_each_logit(l, begin, end, vec, [&](float v, int) {
+      if (v != v || bin_of(v) != bin) return;
+      const uint32_t key = order_key(v);
+      if ((key & mask) != prefix) return;
+      const int b = (key >> shift) & 0xFF;
+      atomicAdd(&hist[b], fixed_weight(v, top, T));
+      atomicAdd(&count[b], 1u);
+    });
+    sb::cluster_sync();
+    if (rank == 0) {
+      unsigned long long w = 0;
+      unsigned int c = 0;
+      if (t < 256) cluster_sum(t, w, c);
+      __syncthreads();
+      if (t < 256) hist[t] = w, count[t] = c;
+      __syncthreads();
+      if (t == 0) {
+        unsigned long long u = decision.u, cum = 0;
+        int chosen = -1, lowest = 0;
+        for (int b = 255; b >= 0; --b) {
+          if (count[b] == 0) continue;
+          lowest = b;
+          if (u < cum + hist[b]) {
+            chosen = b;
+            break;
+          }
+          cum += hist[b];
+        }
+        if (chosen < 0) {  // (a row without a single number: nothing was counted)
+          chosen = lowest;
+          cum = 0;
+          u = hist[lowest];
+        }
+        decision.u = u - cum;
+        decision.prefix = prefix | (static_cast<uint32_t>(chosen) << shift);
+        decision.found = static_cast<int>(count[chosen]);
+      }
+    }
+    sb::cluster_sync();
   }
 
-  // Every token whose key is prefix_s has the same logit and weight; they rank by index.
-  const uint32_t key = prefix_s;
-  if (found_s == 1) {
-    for (int i = t; i < vocab; i += kThreads) {
-      const float v = l[i];
+  // Every token whose key is the chosen one has the same logit and weight; they rank by index.
+  const uint32_t key = peer_load_u32(peer_shared(&decision.prefix, 0));
+  const int found = static_cast<int>(peer_load_u32(peer_shared(&decision.found, 0)));
+  const unsigned long long u_left = peer_load_u64(peer_shared(&decision.u, 0));
+  sb::cluster_sync();        // nobody leaves while another CTA may still read its shared memory
+  if (!sampled) return;
+  if (found == 1) {
+    for_each_logit(l, begin, end, vec, [&](float v, int i) {
       if (v == v && order_key(v) == key) {
         tokens[row] = poisoned(i, watch);
         values[row] = v;
         if (scatter != nullptr) scatter[scatter_index[row]] = i;
       }
-    }
-  } else if (t == 0) {
+    });
+  } else if (rank == 0 && t == 0) {
     int first = -1;
     for (int i = 0; i < vocab && first < 0; ++i)
       if (l[i] == l[i] && order_key(l[i]) == key) first = i;
     int pick = 0;
     if (first >= 0) {     // (a row without a single number has no such token: token 0 then)
       const unsigned long long w = fixed_weight(l[first], top, T);
-      unsigned long long skip = w > 0 ? u_s / w : static_cast<unsigned long long>(found_s - 1);
-      if (skip > static_cast<unsigned long long>(found_s - 1)) skip = found_s - 1;
+      unsigned long long skip = w > 0 ? u_left / w : static_cast<unsigned long long>(found - 1);
+      if (skip > static_cast<unsigned long long>(found - 1)) skip = found - 1;
       pick = first;
       for (int i = first; i < vocab; ++i) {
         if (l[i] == l[i] && order_key(l[i]) == key) {
@@ -291,7 +425,11 @@ SB_EXPORT int sb_sample_temperature(const float* logits, int64_t ld, int rows, i
                                     float* values, const int32_t* scatter_index, int32_t* scatter, cudaStream_t stream) {
   if (rows <= 0) return 0;
   if (vocab <= 0) return sb::fail("sb_sample_temperature: empty vocabulary");
-  sb::launch_pdl(sample_temperature_kernel, dim3(rows), dim3(kThreads), 0, stream, logits, ld, vocab, temperatures, seeds, lengths, tokens, values, scatter_index,
-                 scatter, g_watch);
+  if (rows > 65535) return sb::fail("sb_sample_temperature: %d rows exceed the grid", rows);
+  // a cluster of up to eight CTAs a row: slices of at least 4,096 logits
+  unsigned ranks = 1;
+  while (ranks < 8 && vocab / static_cast<int>(2 * ranks) >= 4096) ranks *= 2;
+  sb::launch_pdl_cluster(sample_temperature_kernel, dim3(ranks, rows), dim3(kSampleThreads), 0, stream, dim3(ranks, 1, 1), logits, ld, vocab, temperatures,
+                         seeds, lengths, tokens, values, scatter_index, scatter, g_watch);
   return sb::check_launch("sb_sample_temperature");
 }

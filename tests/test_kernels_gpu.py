@@ -542,6 +542,50 @@ def test_argmax_and_temperature_sampling():
             assert int(tok[r]) == want and float(val[r]) == wv
 
 
+@pytest.mark.parametrize("temperature", [0.02, 0.7, 1.5, 50.0])
+def test_temperature_sampling_follows_the_plain_sampler_at_every_temperature(temperature):
+    """The two-level search (bins of the distance from the largest logit, then the logit's bits) picks the plain
+    sampler's token whether the temperature leaves one candidate or spreads the draw over the whole vocabulary; equal
+    logits rank by index; masked (-inf) and not-a-number logits are never drawn."""
+    import plain_llama as plain
+    from stride_b200.kernels import ops
+    rows, V = 4, 12007
+    logits = _rand(rows, V, seed=31, scale=2.5)
+    logits[1, 100:140] = logits[1].max()            # forty equal maxima
+    logits[2, ::3] = -float("inf")
+    logits[3, 7] = float("nan")
+    temps = torch.full((rows,), temperature, device=DEV)
+    tok = torch.zeros(rows, dtype=torch.int32, device=DEV)
+    val = torch.zeros(rows, device=DEV)
+    clean = torch.nan_to_num(logits, nan=-float("inf")).cpu()
+    for length in (3, 90, 2500):
+        seeds = torch.tensor([11, 2**63 - 9, 5, 77], dtype=torch.int64, device=DEV)
+        lengths = torch.full((rows,), length, dtype=torch.int32, device=DEV)
+        ops.sample_temperature(logits, temps, seeds, lengths, tok, val)
+        for r in range(rows):
+            want, wv = plain.choose_token(clean[r], temperature, 1.0, 0, int(seeds[r]), length)
+            assert int(tok[r]) == want and float(val[r]) == wv, (temperature, length, r)
+
+
+def test_temperature_sampling_of_a_large_vocabulary_on_a_cluster():
+    """70,001 logits a row: eight CTAs share a row, their histograms joined through distributed shared memory."""
+    import plain_llama as plain
+    from stride_b200.kernels import ops
+    rows, V = 3, 70001
+    logits = _rand(rows, V, seed=41, scale=3.0)
+    logits[1, 60000:60020] = logits[1].max()         # equal maxima in the last CTA's slice
+    temps = torch.tensor([0.9, 0.3, 4.0], device=DEV)
+    seeds = torch.tensor([3, 4, 5], dtype=torch.int64, device=DEV)
+    tok = torch.zeros(rows, dtype=torch.int32, device=DEV)
+    val = torch.zeros(rows, device=DEV)
+    for length in (10, 777):
+        lengths = torch.full((rows,), length, dtype=torch.int32, device=DEV)
+        ops.sample_temperature(logits, temps, seeds, lengths, tok, val)
+        for r in range(rows):
+            want, wv = plain.choose_token(logits[r].cpu(), float(temps[r]), 1.0, 0, int(seeds[r]), length)
+            assert int(tok[r]) == want and float(val[r]) == wv, (length, r)
+
+
 def test_argmax_of_a_large_vocabulary_in_slices():
     """A large vocabulary is cut into slices, one CTA each: the largest logit and the smallest index among equals still
     win, whichever slices they lie in; not-a-numbers are passed over; a second call finds the library's words clean."""
