@@ -204,6 +204,8 @@ __device__ __forceinline__ uint32_t cluster_size() {
 // vocabulary and keeps histograms of its own, since the 64-bit exponentials of a large vocabulary are more than one
 // SM's few 64-bit units do in a decode step's time; after every walk the first CTA adds the cluster's histograms up
 // through distributed shared memory (integers: no order to keep), decides, and the others read its decision.
+constexpr int kMaxMatches = 1024;   // equal logits of one slice that are listed; more are walked one by one
+
 struct Decision {
   unsigned long long u;      // what is left of the draw inside the chosen part
   uint32_t prefix;           // the logit's bits chosen so far
@@ -220,6 +222,8 @@ __global__ void __launch_bounds__(kSampleThreads) sample_temperature_kernel(
   __shared__ float red[32];
   __shared__ float extremes[2];
   __shared__ Decision decision;
+  __shared__ int match_n;
+  __shared__ int match_idx[kMaxMatches];
   sb::grid_launch_dependents();
   sb::grid_dependency_wait();
   const int row = blockIdx.y, t = threadIdx.x;
@@ -358,40 +362,63 @@ __global__ void __launch_bounds__(kSampleThreads) sample_temperature_kernel(
     sb::cluster_sync();
   }
 
-  // Every token whose key is the chosen one has the same logit and weight; they rank by index.
+  // Every token whose key is the chosen one has the same logit and weight; they rank by index, and the draw's remainder
+  // says how many of them to pass over. (Equal logits are no rarity: a vocabulary of 128 k has hundreds of pairs.) Each
+  // CTA lists the matches of its slice; the slices lie in index order, so the counts of the CTAs in front tell a CTA
+  // whether the wanted match is one of its own, and which.
   const uint32_t key = peer_load_u32(peer_shared(&decision.prefix, 0));
-  const int found = static_cast<int>(peer_load_u32(peer_shared(&decision.found, 0)));
   const unsigned long long u_left = peer_load_u64(peer_shared(&decision.u, 0));
+  if (t == 0) match_n = 0;
+  __syncthreads();
+  for_each_logit(l, begin, end, vec, [&](float v, int i) {
+    if (v == v && order_key(v) == key) {
+      const int k = atomicAdd(&match_n, 1);
+      if (k < kMaxMatches) match_idx[k] = i;
+    }
+  });
+  sb::cluster_sync();
+  int before = 0, found = 0;
+  for (uint32_t r = 0; r < ranks; ++r) {
+    const int c = static_cast<int>(peer_load_u32(peer_shared(&match_n, r)));
+    if (r < rank) before += c;
+    found += c;
+  }
   sb::cluster_sync();        // nobody leaves while another CTA may still read its shared memory
   if (!sampled) return;
-  if (found == 1) {
-    for_each_logit(l, begin, end, vec, [&](float v, int i) {
-      if (v == v && order_key(v) == key) {
-        tokens[row] = poisoned(i, watch);
-        values[row] = v;
-        if (scatter != nullptr) scatter[scatter_index[row]] = i;
-      }
-    });
-  } else if (rank == 0 && t == 0) {
-    int first = -1;
-    for (int i = 0; i < vocab && first < 0; ++i)
-      if (l[i] == l[i] && order_key(l[i]) == key) first = i;
-    int pick = 0;
-    if (first >= 0) {     // (a row without a single number has no such token: token 0 then)
-      const unsigned long long w = fixed_weight(l[first], top, T);
-      unsigned long long skip = w > 0 ? u_left / w : static_cast<unsigned long long>(found - 1);
-      if (skip > static_cast<unsigned long long>(found - 1)) skip = found - 1;
-      pick = first;
-      for (int i = first; i < vocab; ++i) {
-        if (l[i] == l[i] && order_key(l[i]) == key) {
-          pick = i;
-          if (skip-- == 0) break;
-        }
+  if (found == 0) {          // a row without a single number: token 0
+    if (rank == 0 && t == 0) {
+      tokens[row] = poisoned(0, watch);
+      values[row] = l[0];
+      if (scatter != nullptr) scatter[scatter_index[row]] = 0;
+    }
+    return;
+  }
+  const float v_key = __uint_as_float((key & 0x80000000u) ? (key & 0x7FFFFFFFu) : ~key);
+  const unsigned long long w = fixed_weight(v_key, top, T);
+  unsigned long long skip = w > 0 ? u_left / w : static_cast<unsigned long long>(found - 1);
+  if (skip > static_cast<unsigned long long>(found - 1)) skip = found - 1;
+  const int local = static_cast<int>(skip) - before, mine = match_n;
+  if (local < 0 || local >= mine) return;
+  auto publish = [&](int i) {
+    tokens[row] = poisoned(i, watch);
+    values[row] = v_key;
+    if (scatter != nullptr) scatter[scatter_index[row]] = i;
+  };
+  if (mine <= kMaxMatches) {
+    // the match with exactly `local` smaller indices among this CTA's matches
+    for (int a = t; a < mine; a += kSampleThreads) {
+      int smaller = 0;
+      for (int b = 0; b < mine; ++b) smaller += match_idx[b] < match_idx[a];
+      if (smaller == local) publish(match_idx[a]);
+    }
+  } else if (t == 0) {       // more equal logits in one slice than the list holds: walk the slice in index order
+    int seen = 0;
+    for (int i = begin; i < end; ++i) {
+      if (l[i] == l[i] && order_key(l[i]) == key && seen++ == local) {
+        publish(i);
+        break;
       }
     }
-    tokens[row] = poisoned(pick, watch);
-    values[row] = l[pick];
-    if (scatter != nullptr) scatter[scatter_index[row]] = pick;
   }
 }
 

@@ -91,17 +91,16 @@ class Sampler:
 
     def __init__(self, device, max_rows: int):
         self.device = torch.device(device)
-        self.max_rows = max_rows
-        self._tokens = torch.zeros(2, max_rows, dtype=torch.int32, device=self.device)
-        self._values = torch.zeros(2, max_rows, dtype=torch.float32, device=self.device)
-        self._temps = torch.zeros(max_rows, dtype=torch.float32, device=self.device)
-        self._seeds = torch.zeros(max_rows, dtype=torch.int64, device=self.device)
-        self._lengths = torch.zeros(max_rows, dtype=torch.int32, device=self.device)
-        self._host_tokens = [torch.zeros(2, max_rows, dtype=torch.int32, pin_memory=True) for _ in range(2)]
-        self._host_values = [torch.zeros(2, max_rows, dtype=torch.float32, pin_memory=True) for _ in range(2)]
-        self._host_temps = [torch.zeros(max_rows, dtype=torch.float32, pin_memory=True) for _ in range(2)]
-        self._host_seeds = [torch.zeros(max_rows, dtype=torch.int64, pin_memory=True) for _ in range(2)]
-        self._host_lengths = [torch.zeros(max_rows, dtype=torch.int32, pin_memory=True) for _ in range(2)]
+        self.max_rows = R = max_rows + (max_rows & 1)          # even, so that the 64-bit seeds stay 8-byte aligned
+        # One device buffer and one copy each way per step: what the kernels read (temperatures, seeds, lengths: 4 R
+        # 32-bit words) and what they write (greedy tokens and values, sampled tokens and values: 4 x rows words).
+        self._inputs = torch.zeros(4 * R, dtype=torch.int32, device=self.device)
+        self._outputs = torch.zeros(4 * R, dtype=torch.int32, device=self.device)
+        self._temps = self._inputs[0:R].view(torch.float32)
+        self._seeds = self._inputs[R:3 * R].view(torch.int64)
+        self._lengths = self._inputs[3 * R:4 * R]
+        self._host_inputs = [torch.zeros(4 * R, dtype=torch.int32, pin_memory=True) for _ in range(2)]
+        self._host_outputs = [torch.zeros(4 * R, dtype=torch.int32, pin_memory=True) for _ in range(2)]
         self._events = [torch.cuda.Event(), torch.cuda.Event()]
         self._turn = 0
 
@@ -111,31 +110,30 @@ class Sampler:
         return p.temperature <= 0.0 or (p.top_k <= 0 and p.top_p >= 1.0)
 
     def launch(self, logits: torch.Tensor, params: list, lengths: list, scatter_index=None, scatter=None):
-        rows = logits.shape[0]
-        if rows > self.max_rows:
-            raise ValueError(f"{rows} rows exceed the sampler's {self.max_rows}")
-        ops.argmax(logits, self._tokens[0, :rows], self._values[0, :rows], scatter_index, scatter)
+        rows, R = logits.shape[0], self.max_rows
+        if rows > R:
+            raise ValueError(f"{rows} rows exceed the sampler's {R}")
+        out = self._outputs
+        tokens = [out[k * rows:(k + 1) * rows] for k in (0, 2)]
+        values = [out[k * rows:(k + 1) * rows].view(torch.float32) for k in (1, 3)]
+        ops.argmax(logits, tokens[0], values[0], scatter_index, scatter)
         device_rows = [i for i, p in enumerate(params) if p.temperature > 0.0 and p.top_k <= 0 and p.top_p >= 1.0]
         host_rows = [i for i, p in enumerate(params) if p.temperature > 0.0 and not (p.top_k <= 0 and p.top_p >= 1.0)]
         turn = self._turn
         self._turn ^= 1
         self._events[turn].synchronize()       # the launch that used this set of host buffers two turns ago is done
         if device_rows:
-            ht, hs, hl = self._host_temps[turn].numpy(), self._host_seeds[turn].numpy(), self._host_lengths[turn].numpy()
+            host = self._host_inputs[turn].numpy()
             on = set(device_rows)
-            for i, p in enumerate(params):
-                ht[i] = p.temperature if i in on else 0.0        # rows not sampled on the device are skipped by the kernel
-                hs[i] = np.uint64(p.seed & _MASK).astype(np.int64)
-                hl[i] = lengths[i]
-            self._temps[:rows].copy_(self._host_temps[turn][:rows], non_blocking=True)
-            self._seeds[:rows].copy_(self._host_seeds[turn][:rows], non_blocking=True)
-            self._lengths[:rows].copy_(self._host_lengths[turn][:rows], non_blocking=True)
-            ops.sample_temperature(logits, self._temps[:rows], self._seeds[:rows], self._lengths[:rows],
-                                   self._tokens[1, :rows], self._values[1, :rows], scatter_index, scatter)
-        # contiguous pieces only: a strided device-to-host copy would go through a staging buffer and block
-        for k in ((0, 1) if device_rows else (0,)):
-            self._host_tokens[turn][k, :rows].copy_(self._tokens[k, :rows], non_blocking=True)
-            self._host_values[turn][k, :rows].copy_(self._values[k, :rows], non_blocking=True)
+            # (rows not sampled on the device get temperature 0 and are skipped by the kernel)
+            host[0:rows].view(np.float32)[:] = [p.temperature if i in on else 0.0 for i, p in enumerate(params)]
+            host[R:R + 2 * rows].view(np.uint64)[:] = [p.seed & _MASK for p in params]
+            host[3 * R:3 * R + rows] = lengths
+            self._inputs.copy_(self._host_inputs[turn], non_blocking=True)
+            ops.sample_temperature(logits, self._temps[:rows], self._seeds[:rows], self._lengths[:rows], tokens[1], values[1],
+                                   scatter_index, scatter)
+        words = (4 if device_rows else 2) * rows
+        self._host_outputs[turn][:words].copy_(out[:words], non_blocking=True)
         host_logits = logits[host_rows].to("cpu") if host_rows else None      # synchronises
         self._events[turn].record()
         return (turn, rows, device_rows, host_rows, host_logits, params, lengths)
@@ -144,14 +142,17 @@ class Sampler:
         """(tokens list, values list) of a launch."""
         turn, rows, device_rows, host_rows, host_logits, params, lengths = ticket
         self._events[turn].synchronize()
-        tokens = self._host_tokens[turn][0, :rows].tolist()
-        values = self._host_values[turn][0, :rows].tolist()
+        host = self._host_outputs[turn]
+        tokens = host[0:rows].tolist()
+        values = host[rows:2 * rows].view(torch.float32).tolist()
         if rows and min(tokens) < 0:
             # the kernels report -1 - code instead of tokens: a wait inside a kernel that made these logits gave up
             return [min(tokens)] * rows, values
-        for i in device_rows:
-            tokens[i] = int(self._host_tokens[turn][1, i])
-            values[i] = float(self._host_values[turn][1, i])
+        if device_rows:
+            sampled_tokens = host[2 * rows:3 * rows].tolist()
+            sampled_values = host[3 * rows:4 * rows].view(torch.float32).tolist()
+            for i in device_rows:
+                tokens[i], values[i] = sampled_tokens[i], sampled_values[i]
         for k, i in enumerate(host_rows):
             tokens[i], values[i] = choose_token_host(host_logits[k].numpy(), params[i], lengths[i])
         return tokens, values

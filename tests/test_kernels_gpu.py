@@ -574,11 +574,12 @@ def test_temperature_sampling_of_a_large_vocabulary_on_a_cluster():
     rows, V = 3, 70001
     logits = _rand(rows, V, seed=41, scale=3.0)
     logits[1, 60000:60020] = logits[1].max()         # equal maxima in the last CTA's slice
-    temps = torch.tensor([0.9, 0.3, 4.0], device=DEV)
+    logits[2, 8740:8770] = logits[2].max() + 3.0     # thirty equal maxima across the border of the first two slices (8,752)
+    temps = torch.tensor([0.9, 0.3, 0.05], device=DEV)
     seeds = torch.tensor([3, 4, 5], dtype=torch.int64, device=DEV)
     tok = torch.zeros(rows, dtype=torch.int32, device=DEV)
     val = torch.zeros(rows, device=DEV)
-    for length in (10, 777):
+    for length in (10, 777, 778, 779, 780, 2000):
         lengths = torch.full((rows,), length, dtype=torch.int32, device=DEV)
         ops.sample_temperature(logits, temps, seeds, lengths, tok, val)
         for r in range(rows):
