@@ -204,7 +204,58 @@ __device__ __forceinline__ uint32_t cluster_size() {
 // vocabulary and keeps histograms of its own, since the 64-bit exponentials of a large vocabulary are more than one
 // SM's few 64-bit units do in a decode step's time; after every walk the first CTA adds the cluster's histograms up
 // through distributed shared memory (integers: no order to keep), decides, and the others read its decision.
-constexpr int kMaxMatches = 1024;   // equal logits of one slice that are listed; more are walked one by one
+constexpr int kMaxMatches = 512;    // equal logits of one slice that are listed; more are walked one by one
+constexpr int kCandidates = 512;    // logits of the chosen bin that a CTA lists from its slice
+constexpr int kAllCandidates = 8 * kCandidates;   // .. and that the first CTA gathers from the whole cluster
+
+// The logit whose order_key is `key`.
+__device__ __forceinline__ float key_value(uint32_t key) { return __uint_as_float((key & 0x80000000u) ? (key & 0x7FFFFFFFu) : ~key); }
+
+// The bin in which a draw falls, found by one warp instead of one thread: position p of the rank order is bin p
+// (ascending) or 255 - p (descending); lane L takes positions 8 L .. 8 L + 7, the lanes' sums are scanned with
+// shuffles, the lane whose range holds the draw walks its eight bins. Returns the bin (-1: the draw lies beyond every
+// bin) and leaves the weight in front of it in `before`; `total` is the sum of all bins. All 32 lanes call it.
+__device__ __forceinline__ unsigned long long bins_total(const unsigned long long* hist, bool descending, unsigned long long& mine,
+                                                         unsigned long long& inclusive) {
+  const int lane = threadIdx.x & 31;
+  mine = 0;
+#pragma unroll
+  for (int k = 0; k < 8; ++k) {
+    const int p = 8 * lane + k;
+    mine += hist[descending ? 255 - p : p];
+  }
+  inclusive = mine;
+#pragma unroll
+  for (int o = 1; o < 32; o <<= 1) {
+    const unsigned long long up = __shfl_up_sync(0xffffffffu, inclusive, o);
+    if (lane >= o) inclusive += up;
+  }
+  return __shfl_sync(0xffffffffu, inclusive, 31);
+}
+__device__ __forceinline__ int pick_bin(const unsigned long long* hist, bool descending, unsigned long long u, unsigned long long mine,
+                                        unsigned long long inclusive, unsigned long long& before) {
+  const int lane = threadIdx.x & 31;
+  const unsigned holds = __ballot_sync(0xffffffffu, u < inclusive);
+  if (holds == 0) {
+    before = 0;
+    return -1;
+  }
+  const int owner = __ffs(holds) - 1;
+  int chosen = -1;
+  unsigned long long cum = inclusive - mine;
+  if (lane == owner) {
+#pragma unroll
+    for (int k = 0; k < 8; ++k) {
+      const int p = 8 * lane + k, b = descending ? 255 - p : p;
+      if (chosen < 0) {
+        if (u < cum + hist[b]) chosen = b;
+        else cum += hist[b];
+      }
+    }
+  }
+  before = __shfl_sync(0xffffffffu, cum, owner);
+  return __shfl_sync(0xffffffffu, chosen, owner);
+}
 
 struct Decision {
   unsigned long long u;      // what is left of the draw inside the chosen part
@@ -222,8 +273,12 @@ __global__ void __launch_bounds__(kSampleThreads) sample_temperature_kernel(
   __shared__ float red[32];
   __shared__ float extremes[2];
   __shared__ Decision decision;
-  __shared__ int match_n;
+  __shared__ int match_n, cand_n;
   __shared__ int match_idx[kMaxMatches];
+  __shared__ uint32_t cand_key[kCandidates];
+  __shared__ int cand_idx[kCandidates];
+  __shared__ uint32_t all_key[kAllCandidates];     // (used by the cluster's first CTA)
+  __shared__ int all_idx[kAllCandidates];
   sb::grid_launch_dependents();
   sb::grid_dependency_wait();
   const int row = blockIdx.y, t = threadIdx.x;
@@ -289,30 +344,142 @@ __global__ void __launch_bounds__(kSampleThreads) sample_temperature_kernel(
     __syncthreads();         // (this CTA's own histogram has been read: it is overwritten with the sums)
     if (t < 256) hist[t] = w;
     __syncthreads();
-    if (t == 0) {
-      unsigned long long total = 0;
-      for (int b = 0; b < 256; ++b) total += hist[b];
+    if (t < 32) {
+      unsigned long long mine, inclusive, before;
+      const unsigned long long total = bins_total(hist, false, mine, inclusive);
       // u = floor(uniform * total), uniform = (r >> 11) * 2^-53: a 53 x 62 bit product, shifted down by 53; u < total
       const unsigned long long r =
           splitmix64(seeds[row] ^ (static_cast<unsigned long long>(static_cast<uint32_t>(lengths[row])) * 0x9E3779B97F4A7C15ULL));
       const unsigned long long m = r >> 11;
-      unsigned long long u = (__umul64hi(m, total) << 11) | ((m * total) >> 53), cum = 0;
-      int chosen = 0;
-      for (int b = 0; b < 256; ++b) {
-        if (u < cum + hist[b]) {
-          chosen = b;
-          break;
-        }
-        cum += hist[b];
+      const unsigned long long u = (__umul64hi(m, total) << 11) | ((m * total) >> 53);
+      const int chosen = pick_bin(hist, false, u, mine, inclusive, before);
+      if (t == 0) {
+        decision.bin = chosen < 0 ? 0 : chosen;     // (no number in the row: nothing will be found in bin 0 either)
+        decision.u = u - before;
+        decision.prefix = 0;
+        decision.found = 0;
       }
-      decision.bin = chosen;
-      decision.u = u - cum;
-      decision.prefix = 0;
-      decision.found = 0;
     }
   }
   sb::cluster_sync();
   const int bin = static_cast<int>(peer_load_u32(peer_shared(&decision.bin, 0)));
+
+  // The chosen bin usually holds a few hundred logits. Every CTA lists those of its slice (bits and index); if all lists
+  // fit, the first CTA finishes alone, reading the others' lists through distributed shared memory: no further walk over
+  // the row and no further barrier but the last. Otherwise (a vocabulary of nearly equal logits) the walks below go on.
+  if (t == 0) cand_n = 0;
+  __syncthreads();
+  for_each_logit(l, begin, end, vec, [&](float v, int i) {
+    if (v != v || bin_of(v) != bin) return;
+    const int k = atomicAdd(&cand_n, 1);
+    if (k < kCandidates) cand_key[k] = order_key(v), cand_idx[k] = i;
+  });
+  sb::cluster_sync();
+  bool listed = true;
+  for (uint32_t r = 0; r < ranks; ++r) listed = listed && peer_load_u32(peer_shared(&cand_n, r)) <= static_cast<uint32_t>(kCandidates);
+  if (listed) {
+    if (rank == 0 && sampled) {
+      // candidate c of the cluster: entry c - first[r] of CTA r's list
+      __shared__ int first_of[9];
+      if (t == 0) {
+        first_of[0] = 0;
+        for (uint32_t r = 0; r < ranks; ++r) first_of[r + 1] = first_of[r] + static_cast<int>(peer_load_u32(peer_shared(&cand_n, r)));
+      }
+      __syncthreads();
+      const int total = first_of[ranks];
+      // fetched once through distributed shared memory, then worked on here
+      for (uint32_t r = 0; r < ranks; ++r)
+        for (int c = first_of[r] + t; c < first_of[r + 1]; c += kSampleThreads) {
+          all_key[c] = peer_load_u32(peer_shared(&cand_key[c - first_of[r]], r));
+          all_idx[c] = static_cast<int>(peer_load_u32(peer_shared(&cand_idx[c - first_of[r]], r)));
+        }
+      __syncthreads();
+      auto candidate = [&](int c, uint32_t& ckey, int& cidx) { ckey = all_key[c], cidx = all_idx[c]; };
+      uint32_t prefix = 0;
+      for (int shift = 24; shift >= 0; shift -= 8) {
+        for (int b = t; b < 256; b += kSampleThreads) hist[b] = 0, count[b] = 0;
+        __syncthreads();
+        const uint32_t mask = shift == 24 ? 0u : (0xFFFFFFFFu << (shift + 8));
+        for (int c = t; c < total; c += kSampleThreads) {
+          uint32_t ckey;
+          int cidx;
+          candidate(c, ckey, cidx);
+          if ((ckey & mask) != prefix) continue;
+          const int b = (ckey >> shift) & 0xFF;
+          atomicAdd(&hist[b], fixed_weight(key_value(ckey), top, T));
+          atomicAdd(&count[b], 1u);
+        }
+        __syncthreads();
+        if (t < 32) {
+          unsigned long long mine, inclusive, before;
+          bins_total(hist, true, mine, inclusive);
+          const unsigned long long u = decision.u;
+          const int chosen = pick_bin(hist, true, u, mine, inclusive, before);
+          __syncwarp();
+          if (t == 0) {      // (nothing chosen: a row without a single number; the token is then 0)
+            decision.u = chosen < 0 ? 0 : u - before;
+            decision.prefix = prefix | (static_cast<uint32_t>(chosen < 0 ? 0 : chosen) << shift);
+            decision.found = chosen < 0 ? 0 : static_cast<int>(count[chosen]);
+          }
+        }
+        __syncthreads();
+        prefix = decision.prefix;
+      }
+      // the tokens with the chosen bits rank by index: the one that has as many smaller indices as the draw passes over
+      const int found = decision.found;
+      if (found == 0) {
+        if (t == 0) {
+          tokens[row] = poisoned(0, watch);
+          values[row] = l[0];
+          if (scatter != nullptr) scatter[scatter_index[row]] = 0;
+        }
+      } else {
+        const float v_key = key_value(prefix);
+        const unsigned long long w = fixed_weight(v_key, top, T);
+        unsigned long long skip = w > 0 ? decision.u / w : static_cast<unsigned long long>(found - 1);
+        if (skip > static_cast<unsigned long long>(found - 1)) skip = found - 1;
+        auto publish = [&](int i) {
+          tokens[row] = poisoned(i, watch);
+          values[row] = v_key;
+          if (scatter != nullptr) scatter[scatter_index[row]] = i;
+        };
+        if (t == 0) match_n = 0;
+        __syncthreads();
+        if (found <= kMaxMatches) {
+          // list the tokens with the chosen bits; the wanted one has exactly `skip` smaller indices among them
+          for (int c = t; c < total; c += kSampleThreads) {
+            uint32_t ckey;
+            int cidx;
+            candidate(c, ckey, cidx);
+            if (ckey == prefix) match_idx[atomicAdd(&match_n, 1)] = cidx;
+          }
+          __syncthreads();
+          for (int a = t; a < found; a += kSampleThreads) {
+            unsigned long long smaller = 0;
+            for (int b = 0; b < found; ++b) smaller += match_idx[b] < match_idx[a];
+            if (smaller == skip) publish(match_idx[a]);
+          }
+        } else {
+          for (int c = t; c < total; c += kSampleThreads) {
+            uint32_t ckey;
+            int cidx;
+            candidate(c, ckey, cidx);
+            if (ckey != prefix) continue;
+            unsigned long long smaller = 0;
+            for (int o = 0; o < total; ++o) {
+              uint32_t okey;
+              int oidx;
+              candidate(o, okey, oidx);
+              smaller += okey == prefix && oidx < cidx;
+            }
+            if (smaller == skip) publish(cidx);
+          }
+        }
+      }
+    }
+    sb::cluster_sync();      // the other CTAs' lists stay until the first CTA is done with them
+    return;
+  }
 
   for (int shift = 24; shift >= 0; shift -= 8) {
     // (the first CTA has read every histogram of the walk before, and does not touch its decision again before the
@@ -337,26 +504,17 @@ __global__ void __launch_bounds__(kSampleThreads) sample_temperature_kernel(
       __syncthreads();
       if (t < 256) hist[t] = w, count[t] = c;
       __syncthreads();
-      if (t == 0) {
-        unsigned long long u = decision.u, cum = 0;
-        int chosen = -1, lowest = 0;
-        for (int b = 255; b >= 0; --b) {
-          if (count[b] == 0) continue;
-          lowest = b;
-          if (u < cum + hist[b]) {
-            chosen = b;
-            break;
-          }
-          cum += hist[b];
+      if (t < 32) {
+        unsigned long long mine, inclusive, before;
+        bins_total(hist, true, mine, inclusive);
+        const unsigned long long u = decision.u;
+        const int chosen = pick_bin(hist, true, u, mine, inclusive, before);
+        __syncwarp();
+        if (t == 0) {      // (nothing chosen: a row without a single number; the token is then 0)
+          decision.u = chosen < 0 ? 0 : u - before;
+          decision.prefix = prefix | (static_cast<uint32_t>(chosen < 0 ? 0 : chosen) << shift);
+          decision.found = chosen < 0 ? 0 : static_cast<int>(count[chosen]);
         }
-        if (chosen < 0) {  // (a row without a single number: nothing was counted)
-          chosen = lowest;
-          cum = 0;
-          u = hist[lowest];
-        }
-        decision.u = u - cum;
-        decision.prefix = prefix | (static_cast<uint32_t>(chosen) << shift);
-        decision.found = static_cast<int>(count[chosen]);
       }
     }
     sb::cluster_sync();
@@ -393,7 +551,7 @@ __global__ void __launch_bounds__(kSampleThreads) sample_temperature_kernel(
     }
     return;
   }
-  const float v_key = __uint_as_float((key & 0x80000000u) ? (key & 0x7FFFFFFFu) : ~key);
+  const float v_key = key_value(key);
   const unsigned long long w = fixed_weight(v_key, top, T);
   unsigned long long skip = w > 0 ? u_left / w : static_cast<unsigned long long>(found - 1);
   if (skip > static_cast<unsigned long long>(found - 1)) skip = found - 1;

@@ -567,6 +567,27 @@ def test_temperature_sampling_follows_the_plain_sampler_at_every_temperature(tem
             assert int(tok[r]) == want and float(val[r]) == wv, (temperature, length, r)
 
 
+def test_temperature_sampling_among_equal_logits():
+    """Vocabularies of equal logits (all of them, or all but a few): every token weighs the same and the draw picks by
+    index; far more candidates than a CTA lists, so the walks over the whole row take over."""
+    import plain_llama as plain
+    from stride_b200.kernels import ops
+    rows, V = 3, 20011
+    logits = torch.full((rows, V), 1.25, device=DEV)
+    logits[1, 5:9] = -3.0
+    logits[2, ::2] = 1.25000012                       # two values one step of float32 apart
+    temps = torch.tensor([1.0, 0.6, 2.0], device=DEV)
+    tok = torch.zeros(rows, dtype=torch.int32, device=DEV)
+    val = torch.zeros(rows, device=DEV)
+    for length in (1, 50, 51, 3000):
+        seeds = torch.tensor([9, 10, 11], dtype=torch.int64, device=DEV)
+        lengths = torch.full((rows,), length, dtype=torch.int32, device=DEV)
+        ops.sample_temperature(logits, temps, seeds, lengths, tok, val)
+        for r in range(rows):
+            want, wv = plain.choose_token(logits[r].cpu(), float(temps[r]), 1.0, 0, int(seeds[r]), length)
+            assert int(tok[r]) == want and float(val[r]) == wv, (length, r, int(tok[r]), want)
+
+
 def test_temperature_sampling_of_a_large_vocabulary_on_a_cluster():
     """70,001 logits a row: eight CTAs share a row, their histograms joined through distributed shared memory."""
     import plain_llama as plain
