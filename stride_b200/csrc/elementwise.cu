@@ -92,17 +92,26 @@ __global__ void rope_append_kernel(RopeAppendParams p) {
   // positions, slots, the block table and the cos/sin table are inputs of the step; only qkv comes from the kernel before
   sb::grid_dependency_wait();
   const float* src = p.qkv + static_cast<int64_t>(row) * width + static_cast<int64_t>(head) * D;
-  float a = src[d0], b = src[d1];
-  int s = 1;
-  for (; s + 4 <= p.n_partials; s += 4) {
-    const float* q0 = src + s * p.partial_stride;
-    const float a0 = q0[d0], b0 = q0[d1], a1 = q0[p.partial_stride + d0], b1 = q0[p.partial_stride + d1];
-    const float a2 = q0[2 * p.partial_stride + d0], b2 = q0[2 * p.partial_stride + d1];
-    const float a3 = q0[3 * p.partial_stride + d0], b3 = q0[3 * p.partial_stride + d1];
-    a = (((a + a0) + a1) + a2) + a3;
-    b = (((b + b0) + b1) + b2) + b3;
+  // the K ranges' sums are added in ascending order; up to kInFlight of them are requested at once (each is a round
+  // trip to L2, and with few tokens those are what this kernel's time consists of)
+  constexpr int kInFlight = 8;
+  float pa[kInFlight], pb[kInFlight];
+#pragma unroll
+  for (int s = 0; s < kInFlight; ++s) {
+    if (s < p.n_partials) {
+      pa[s] = src[s * p.partial_stride + d0];
+      pb[s] = src[s * p.partial_stride + d1];
+    }
   }
-  for (; s < p.n_partials; ++s) {
+  float a = pa[0], b = pb[0];
+#pragma unroll
+  for (int s = 1; s < kInFlight; ++s) {
+    if (s < p.n_partials) {
+      a += pa[s];
+      b += pb[s];
+    }
+  }
+  for (int s = kInFlight; s < p.n_partials; ++s) {
     a += src[s * p.partial_stride + d0];
     b += src[s * p.partial_stride + d1];
   }
@@ -167,23 +176,25 @@ __global__ void rope_append_vec_kernel(RopeAppendParams p) {
   }
   sb::grid_dependency_wait();   // everything above is an input of the step; qkv comes from the kernel before
   const float* src = p.qkv + static_cast<int64_t>(row) * heads * D + static_cast<int64_t>(head) * D;
-  float4 a = *reinterpret_cast<const float4*>(src + j), b = *reinterpret_cast<const float4*>(src + half + j);
-  // the K ranges' sums are added in ascending order; they are fetched four at a time so that the loads overlap
-  int s = 1;
-  for (; s + 3 < p.n_partials; s += 4) {
-    float4 pa[4], pb[4];
+  // the K ranges' sums are added in ascending order; up to kInFlight of them are requested at once
+  constexpr int kInFlight = 8;
+  float4 pa[kInFlight], pb[kInFlight];
 #pragma unroll
-    for (int u = 0; u < 4; ++u) {
-      pa[u] = *reinterpret_cast<const float4*>(src + (s + u) * p.partial_stride + j);
-      pb[u] = *reinterpret_cast<const float4*>(src + (s + u) * p.partial_stride + half + j);
-    }
-#pragma unroll
-    for (int u = 0; u < 4; ++u) {
-      a = add4(a, pa[u]);
-      b = add4(b, pb[u]);
+  for (int s = 0; s < kInFlight; ++s) {
+    if (s < p.n_partials) {
+      pa[s] = *reinterpret_cast<const float4*>(src + s * p.partial_stride + j);
+      pb[s] = *reinterpret_cast<const float4*>(src + s * p.partial_stride + half + j);
     }
   }
-  for (; s < p.n_partials; ++s) {
+  float4 a = pa[0], b = pb[0];
+#pragma unroll
+  for (int s = 1; s < kInFlight; ++s) {
+    if (s < p.n_partials) {
+      a = add4(a, pa[s]);
+      b = add4(b, pb[s]);
+    }
+  }
+  for (int s = kInFlight; s < p.n_partials; ++s) {
     a = add4(a, *reinterpret_cast<const float4*>(src + s * p.partial_stride + j));
     b = add4(b, *reinterpret_cast<const float4*>(src + s * p.partial_stride + half + j));
   }
@@ -235,8 +246,17 @@ __global__ void gather_rows_kernel(const float* __restrict__ in, const float* __
   for (int i = threadIdx.x; i < H; i += blockDim.x) {
     float v = in[static_cast<int64_t>(src) * H + i];
     if (n_partials > 0) {
-      float sum = partials[static_cast<int64_t>(src) * H + i];
-      for (int s = 1; s < n_partials; ++s) sum += partials[s * partial_stride + static_cast<int64_t>(src) * H + i];
+      constexpr int kInFlight = 12;     // partial sums requested at once, then added in ascending order
+      const float* p = partials + static_cast<int64_t>(src) * H + i;
+      float part[kInFlight];
+#pragma unroll
+      for (int s = 0; s < kInFlight; ++s)
+        if (s < n_partials) part[s] = p[s * partial_stride];
+      float sum = part[0];
+#pragma unroll
+      for (int s = 1; s < kInFlight; ++s)
+        if (s < n_partials) sum += part[s];
+      for (int s = kInFlight; s < n_partials; ++s) sum += p[s * partial_stride];
       v += sum;
     }
     out[static_cast<int64_t>(blockIdx.x) * H + i] = v;

@@ -29,7 +29,7 @@
 //
 // Counterparts in arhaamatiq/stride: TcQkv, TcGemmResidual, TcMlp13, TcLmFull on wmma
 // (src/kernels_tc.cu:347-655).
-#include "tc5.cuh"
+#include "gemm_tc_tile.cuh"
 #include "step_ops.h"
 
 SB_DEFINE_LAST_ERROR()
@@ -37,75 +37,26 @@ SB_DEFINE_LAST_ERROR()
 namespace {
 
 using namespace sb::tc5;
-using bf16 = __nv_bfloat16;
+using namespace sb::gemm_tile;
 
-constexpr int kTileM = 128;
-constexpr int kTileK = 64;            // elements: 128 bytes of bfloat16, one swizzle row
-constexpr int kStageA = kTileM * 128;  // bytes
 constexpr int kMaxStages = 8;
 constexpr int kThreads = 192;
 constexpr int kSmemBudget = 200 * 1024;
 
-enum Epilogue { kStore = 0, kAdd = 1, kSwiglu = 2 };
-
-// ------------------------------------------------------------------ helpers on top of tc5.cuh
-__device__ __forceinline__ void tmem_load16(uint32_t taddr, float* v) {
-  uint32_t r[16];
-  asm volatile(
-      "tcgen05.ld.sync.aligned.32x32b.x16.b32 {%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15}, [%16];"
-      : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]),
-        "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15])
-      : "r"(taddr)
-      : "memory");
-  tmem_load_wait();
-#pragma unroll
-  for (int i = 0; i < 16; ++i) v[i] = __uint_as_float(r[i]);
-}
-__device__ __forceinline__ void tc_fence_before() { fence_before_sync(); }
-__device__ __forceinline__ void tc_fence_after() { fence_after_sync(); }
-// Tensor memory is allocated in powers of two of at least 32 columns.
-__host__ __device__ __forceinline__ uint32_t tmem_alloc_cols(int cols) {
-  uint32_t c = 32;
-  while (c < static_cast<uint32_t>(cols)) c <<= 1;
-  return c;
-}
-// Instruction descriptor: D float32, A and B bfloat16, both K-major, M = 128, N = n.
-__device__ __forceinline__ uint32_t instr_desc(int n) { return sb::tc5::instr_desc(kTileM, n, false); }
-
-// silu(g) = g / (1 + e^-g) with the hardware's approximations of e^x and of the division (two units in the last
-// place each, far below the bfloat16 rounding that follows): the same instruction sequence in every kernel of this
-// file, so that a token's product has the same bits from each.
-__device__ __forceinline__ float silu_fast(float g) { return __fdividef(g, 1.0f + __expf(-g)); }
-
-// Rows of one accumulator tile to global memory: out[n, m] = d (kStore) or out[n, m] += d (kAdd). Each thread
-// owns output feature m and walks the tile's tokens sixteen at a time; for kAdd the residual values of the
-// next sixteen are requested before the current sixteen are summed and stored.
-template <int EPI>
-__device__ __forceinline__ void store_tile(uint32_t tmem_row, float* out, int m, int M, int n0, int N, int64_t ldo, int BN, bool ok) {
-  const bool live = m < M && ok;
-  float nxt[16];
-  if (EPI == kAdd && live) {
-#pragma unroll
-    for (int c = 0; c < 16; ++c) nxt[c] = (n0 + c < N) ? out[static_cast<int64_t>(n0 + c) * ldo + m] : 0.0f;
+// Where a thread stands in the ring of stages: the stage and the parity of its current use, kept by counting (a
+// division per K step costs the issuing thread more than the products it issues). A producer starts with parity 1: a
+// wait on that parity of a barrier nobody has arrived on yet returns at once, so its first round through the ring is free.
+struct RingPos {
+  uint32_t slot, par;
+  const uint32_t stages;
+  __device__ __forceinline__ RingPos(int stages_, uint32_t par0) : slot(0), par(par0), stages(static_cast<uint32_t>(stages_)) {}
+  __device__ __forceinline__ void advance() {
+    if (++slot == stages) slot = 0, par ^= 1;
   }
-  for (int c0 = 0; c0 < BN; c0 += 16) {
-    float v[16], old[16];
-    float* o = out + static_cast<int64_t>(n0 + c0) * ldo + m;
-    if (EPI == kAdd && live) {
-#pragma unroll
-      for (int c = 0; c < 16; ++c) old[c] = nxt[c];
-      if (c0 + 16 < BN) {
-#pragma unroll
-        for (int c = 0; c < 16; ++c) nxt[c] = (n0 + c0 + 16 + c < N) ? o[static_cast<int64_t>(16 + c) * ldo] : 0.0f;
-      }
-    }
-    tmem_load16(tmem_row + c0, v);
-    if (live) {
-#pragma unroll
-      for (int c = 0; c < 16; ++c)
-        if (n0 + c0 + c < N) o[static_cast<int64_t>(c) * ldo] = EPI == kAdd ? old[c] + v[c] : v[c];
-    }
-  }
+};
+// The shared-memory descriptor of a tile `offset` bytes (a multiple of 16) into the stage at `slot`.
+__device__ __forceinline__ uint64_t stage_desc(uint64_t desc_fixed, uint32_t smem0, uint32_t slot, uint32_t stage_bytes, uint32_t offset) {
+  return desc_fixed | (((smem0 + offset) & 0x3FFFF) >> 4) + slot * (stage_bytes >> 4);
 }
 
 struct GemmParams {
@@ -189,28 +140,42 @@ gemm_tc_single_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_co
       for (int i = 0; i < ahead; ++i) load_w(i);
       sb::grid_dependency_wait();
       for (int i = 0; i < ahead; ++i) load_x(i);
+      // (the stage and its parity are counted, not divided out: with so few tokens a K step is bounded by the
+      // instructions of the threads that issue it)
+      int st = ahead == p.stages ? 0 : ahead;
+      uint32_t par = 0;
       for (int i = ahead; i < iters; ++i) {
-        mbar_wait(smem_u32(&empty_bar[i % p.stages]), ((i / p.stages) - 1) & 1, p.status, 1);
-        load_w(i);
-        load_x(i);
+        mbar_wait(smem_u32(&empty_bar[st]), par, p.status, 1);
+        const uint32_t bar = smem_u32(&full_bar[st]);
+        const uint32_t a = smem0 + st * stage_bytes;
+        const int k = (kb0 + i) * kTileK;
+        mbar_expect_tx(bar, stage_bytes);
+        tma_load_2d(a, &map_w, bar, k, row_w);
+        if (EPI == kSwiglu) tma_load_2d(a + kStageA / 2, &map_w, bar, k, p.half_rows + row_w);
+        tma_load_2d(a + kStageA, &map_x, bar, k, tile_n * BN);
+        if (++st == p.stages) st = 0, par ^= 1;
       }
     }
   } else if (warp == 1) {
     if (lane == 0) {
       // ---------------- MMA issuer
       const uint32_t idesc = instr_desc(BN);
+      const uint64_t desc_fixed = smem_desc_sw128(0);
+      const uint32_t a_lo = (smem0 & 0x3FFFF) >> 4, stage_lo = static_cast<uint32_t>(stage_bytes) >> 4;
+      const uint32_t full0 = smem_u32(&full_bar[0]), empty0 = smem_u32(&empty_bar[0]);
+      uint32_t st = 0, par = 0, accumulate = 0;
       for (int i = 0; i < iters; ++i) {
-        const int s = i % p.stages;
-        mbar_wait(smem_u32(&full_bar[s]), (i / p.stages) & 1, p.status, 2);
+        mbar_wait(full0 + 8 * st, par, p.status, 2);
         tc_fence_after();
-        const uint32_t a = smem0 + s * stage_bytes, b = a + kStageA;
-        const uint64_t da = smem_desc_sw128(a), db = smem_desc_sw128(b);
-#pragma unroll
-        for (int k = 0; k < kTileK / 16; ++k) {
-          // 16 elements = 32 bytes along K: +2 in the descriptor's 16-byte address units
-          umma_bf16(tmem_base, da + 2 * k, db + 2 * k, idesc, (i > 0 || k > 0) ? 1u : 0u);
-        }
-        umma_commit(smem_u32(&empty_bar[s]));
+        const uint64_t da = desc_fixed | (a_lo + st * stage_lo), db = da + (kStageA >> 4);
+        // 16 elements = 32 bytes along K: +2 in the descriptor's 16-byte address units
+        umma_bf16(tmem_base, da, db, idesc, accumulate);
+        umma_bf16(tmem_base, da + 2, db + 2, idesc, 1u);
+        umma_bf16(tmem_base, da + 4, db + 4, idesc, 1u);
+        umma_bf16(tmem_base, da + 6, db + 6, idesc, 1u);
+        accumulate = 1u;
+        umma_commit(empty0 + 8 * st);
+        if (++st == static_cast<uint32_t>(p.stages)) st = 0, par ^= 1;
       }
       umma_commit(smem_u32(&accum_bar));
     }
@@ -223,36 +188,8 @@ gemm_tc_single_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_co
     tc_fence_after();
     const int n0 = tile_n * BN;
     if (EPI == kSwiglu) {
-      // lanes 0..63 hold gate rows, lanes 64..127 the matching up rows
       float* xch = reinterpret_cast<float*>(smem_raw + ((smem0 - smem_u32(smem_raw))));  // stage 0 is free by now
-      const int j = tile_m * 64 + (quarter & 1) * 32 + lane;  // output feature
-      bf16* out = reinterpret_cast<bf16*>(p.out);
-      for (int c0 = 0; c0 < BN; c0 += 16) {
-        float v[16];
-        tmem_load16(tmem_base + (static_cast<uint32_t>(quarter * 32) << 16) + c0, v);
-        // gate warps hand over columns 8..15, up warps columns 0..7: every warp then finishes eight columns
-        if (quarter >= 2) {
-#pragma unroll
-          for (int c = 0; c < 8; ++c) xch[c * 64 + (quarter - 2) * 32 + lane] = v[c];
-        } else {
-#pragma unroll
-          for (int c = 0; c < 8; ++c) xch[(8 + c) * 64 + quarter * 32 + lane] = v[8 + c];
-        }
-        asm volatile("bar.sync 1, 128;" ::: "memory");
-        if (ok && j < p.half_rows) {
-          const int cb = quarter >= 2 ? 8 : 0;
-#pragma unroll
-          for (int c = 0; c < 8; ++c) {
-            const int n = n0 + c0 + cb + c;
-            if (n < p.N) {
-              const float other = xch[(cb + c) * 64 + (quarter & 1) * 32 + lane];
-              const float g = quarter >= 2 ? other : v[c], u = quarter >= 2 ? v[8 + c] : other;
-              out[static_cast<int64_t>(n) * p.ldo + j] = __float2bfloat16_rn(silu_fast(g) * u);
-            }
-          }
-        }
-        asm volatile("bar.sync 1, 128;" ::: "memory");
-      }
+      swiglu_tile(tmem_base, xch, reinterpret_cast<bf16*>(p.out), p.ldo, tile_m, p.half_rows, n0, p.N, BN, quarter, lane, ok);
     } else {
       store_tile<EPI>(tmem_base + (static_cast<uint32_t>(quarter * 32) << 16), p.out + static_cast<int64_t>(split) * p.split_stride,
                       tile_m * kTileM + quarter * 32 + lane, p.M, n0, p.N, p.ldo, BN, ok);
@@ -312,7 +249,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
       // ---------------- producer: TMA loads. The weights do not depend on the kernels before this one,
       // so the first ring of weight tiles is requested before waiting for them to finish; the tokens'
       // tiles follow once their producer is done.
-      int it = 0;          // k-blocks issued so far, over all tiles of this CTA
+      RingPos pos(p.stages, 1);     // over the K blocks of all tiles of this CTA
       bool waited = false;
       for (int tile = blockIdx.x; tile < total_tiles; tile += MULTI ? gridDim.x : total_tiles) {
         const int tile_m = tile % p.tiles_m, rest = tile / p.tiles_m;
@@ -341,15 +278,14 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
           for (int j = 0; j < ahead; ++j) load_w(j, j);
           sb::grid_dependency_wait();
           waited = true;
-          for (int j = 0; j < ahead; ++j) load_x(j, j);
+          for (int j = 0; j < ahead; ++j) load_x(j, j), pos.advance();
           i = ahead;
-          it = ahead;
         }
-        for (; i < iters; ++i, ++it) {
-          const int slot = it % p.stages;
-          if (it >= p.stages) mbar_wait(smem_u32(&empty_bar[slot]), ((it / p.stages) - 1) & 1, p.status, 1);
-          load_w(i, slot);
-          load_x(i, slot);
+        for (; i < iters; ++i) {
+          mbar_wait(smem_u32(&empty_bar[pos.slot]), pos.par, p.status, 1);
+          load_w(i, pos.slot);
+          load_x(i, pos.slot);
+          pos.advance();
         }
       }
     }
@@ -357,7 +293,9 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
     if (lane == 0) {
       // ---------------- MMA issuer
       const uint32_t idesc = instr_desc(BN);
-      int it = 0, ti = 0;
+      const uint64_t desc_fixed = smem_desc_sw128(0);
+      RingPos pos(p.stages, 0);
+      int ti = 0;
       for (int tile = blockIdx.x; tile < total_tiles; tile += MULTI ? gridDim.x : total_tiles, ++ti) {
         const int split = tile / (p.tiles_m * p.tiles_n);
         const int kb0 = split * p.kblocks_per_split;
@@ -367,18 +305,17 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
         if (MULTI && ti >= 2) mbar_wait(smem_u32(&accum_empty[acc]), ((ti >> 1) - 1) & 1, p.status, 4);
         tc_fence_after();
         const uint32_t tmem_d = tmem_base + acc * BN;
-        for (int i = 0; i < iters; ++i, ++it) {
-          const int slot = it % p.stages;
-          mbar_wait(smem_u32(&full_bar[slot]), (it / p.stages) & 1, p.status, 2);
+        for (int i = 0; i < iters; ++i) {
+          mbar_wait(smem_u32(&full_bar[pos.slot]), pos.par, p.status, 2);
           tc_fence_after();
-          const uint32_t a = smem0 + slot * stage_bytes, b = a + kStageA;
-          const uint64_t da = smem_desc_sw128(a), db = smem_desc_sw128(b);
+          const uint64_t da = stage_desc(desc_fixed, smem0, pos.slot, stage_bytes, 0), db = stage_desc(desc_fixed, smem0, pos.slot, stage_bytes, kStageA);
 #pragma unroll
           for (int k = 0; k < kTileK / 16; ++k) {
             // 16 elements = 32 bytes along K: +2 in the descriptor's 16-byte address units
             umma_bf16(tmem_d, da + 2 * k, db + 2 * k, idesc, (i > 0 || k > 0) ? 1u : 0u);
           }
-          umma_commit(smem_u32(&empty_bar[slot]));
+          umma_commit(smem_u32(&empty_bar[pos.slot]));
+          pos.advance();
         }
         umma_commit(smem_u32(&accum_full[acc]));
       }
@@ -496,17 +433,17 @@ gemm_tc_fold_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_cons
     if (lane == 0) {
       // ---------------- producer: the K blocks of a tile in ascending order (its ranges are consecutive)
       sb::grid_dependency_wait();
-      int it = 0;
+      RingPos pos(p.stages, 1);
       for (int tile = blockIdx.x; tile < total_tiles; tile += gridDim.x) {
         const int tile_m = tile % p.tiles_m, tile_n = tile / p.tiles_m;
-        for (int i = 0; i < kblocks; ++i, ++it) {
-          const int slot = it % p.stages;
-          if (it >= p.stages) mbar_wait(smem_u32(&empty_bar[slot]), ((it / p.stages) - 1) & 1, p.status, 1);
-          const uint32_t bar = smem_u32(&full_bar[slot]);
-          const uint32_t a = smem0 + slot * stage_bytes;
+        for (int i = 0; i < kblocks; ++i) {
+          mbar_wait(smem_u32(&empty_bar[pos.slot]), pos.par, p.status, 1);
+          const uint32_t bar = smem_u32(&full_bar[pos.slot]);
+          const uint32_t a = smem0 + pos.slot * stage_bytes;
           mbar_expect_tx(bar, stage_bytes);
           tma_load_2d(a, &map_w, bar, i * kTileK, tile_m * kTileM);
           tma_load_2d(a + kStageA, &map_x, bar, i * kTileK, tile_n * BN);
+          pos.advance();
         }
       }
     }
@@ -514,7 +451,9 @@ gemm_tc_fold_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_cons
     if (lane == 0) {
       // ---------------- MMA issuer: range q of this CTA (counted over all its tiles) fills accumulator q & 1
       const uint32_t idesc = instr_desc(BN);
-      int it = 0, q = 0;
+      const uint64_t desc_fixed = smem_desc_sw128(0);
+      RingPos pos(p.stages, 0);
+      int q = 0;
       for (int tile = blockIdx.x; tile < total_tiles; tile += gridDim.x) {
         for (int r = 0; r < p.splits; ++r, ++q) {
           const int kb0 = r * p.kblocks_per_split;
@@ -523,15 +462,14 @@ gemm_tc_fold_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_cons
           if (q >= 2) mbar_wait(smem_u32(&accum_empty[acc]), ((q >> 1) - 1) & 1, p.status, 4);
           tc_fence_after();
           const uint32_t tmem_d = tmem_base + acc * BN;
-          for (int i = 0; i < iters; ++i, ++it) {
-            const int slot = it % p.stages;
-            mbar_wait(smem_u32(&full_bar[slot]), (it / p.stages) & 1, p.status, 2);
+          for (int i = 0; i < iters; ++i) {
+            mbar_wait(smem_u32(&full_bar[pos.slot]), pos.par, p.status, 2);
             tc_fence_after();
-            const uint32_t a = smem0 + slot * stage_bytes, b = a + kStageA;
-            const uint64_t da = smem_desc_sw128(a), db = smem_desc_sw128(b);
+            const uint64_t da = stage_desc(desc_fixed, smem0, pos.slot, stage_bytes, 0), db = stage_desc(desc_fixed, smem0, pos.slot, stage_bytes, kStageA);
 #pragma unroll
             for (int k = 0; k < kTileK / 16; ++k) umma_bf16(tmem_d, da + 2 * k, db + 2 * k, idesc, (i > 0 || k > 0) ? 1u : 0u);
-            umma_commit(smem_u32(&empty_bar[slot]));
+            umma_commit(smem_u32(&empty_bar[pos.slot]));
+            pos.advance();
           }
           umma_commit(smem_u32(&accum_full[acc]));
         }
@@ -644,12 +582,12 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_cons
     if (lane == 0) {
       // ---------------- producer of this CTA: its half of the weight rows and of the tokens, counted on the leader's barrier
       sb::grid_dependency_wait();
-      int it = 0;
+      RingPos pos(p.stages, 1);
       for (int tile = pair; tile < total_tiles; tile += pairs) {
         const int tile_m = tile % p.tiles_m, tile_n = tile / p.tiles_m;
-        for (int i = 0; i < kblocks; ++i, ++it) {
-          const int slot = it % p.stages;
-          if (it >= p.stages) mbar_wait(smem_u32(&empty_bar[slot]), ((it / p.stages) - 1) & 1, p.status, 1);
+        for (int i = 0; i < kblocks; ++i, pos.advance()) {
+          const uint32_t slot = pos.slot;
+          mbar_wait(smem_u32(&empty_bar[slot]), pos.par, p.status, 1);
           const uint32_t bar = smem_u32(&full_bar[slot]);
           const uint32_t a = smem0 + slot * stage_bytes;
           if (rank == 0) mbar_expect_tx(bar, 2 * stage_bytes);
@@ -669,7 +607,9 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_cons
     if (lane == 0 && rank == 0) {
       // ---------------- MMA issuer of the pair
       const uint32_t idesc = sb::tc5::instr_desc(256, BN, false);
-      int it = 0, q = 0;
+      const uint64_t desc_fixed = smem_desc_sw128(0);
+      RingPos pos(p.stages, 0);
+      int q = 0;
       for (int tile = pair; tile < total_tiles; tile += pairs) {
         for (int r = 0; r < p.splits; ++r, ++q) {
           const int kb0 = r * p.kblocks_per_split;
@@ -678,15 +618,14 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_cons
           if (q >= 2) mbar_wait(smem_u32(&accum_empty[acc]), ((q >> 1) - 1) & 1, p.status, 4);
           tc_fence_after();
           const uint32_t tmem_d = tmem_base + acc * BN;
-          for (int i = 0; i < iters; ++i, ++it) {
-            const int slot = it % p.stages;
-            mbar_wait(smem_u32(&full_bar[slot]), (it / p.stages) & 1, p.status, 2);
+          for (int i = 0; i < iters; ++i) {
+            mbar_wait(smem_u32(&full_bar[pos.slot]), pos.par, p.status, 2);
             tc_fence_after();
-            const uint32_t a = smem0 + slot * stage_bytes, b = a + kStageA;
-            const uint64_t da = smem_desc_sw128(a), db = smem_desc_sw128(b);
+            const uint64_t da = stage_desc(desc_fixed, smem0, pos.slot, stage_bytes, 0), db = stage_desc(desc_fixed, smem0, pos.slot, stage_bytes, kStageA);
 #pragma unroll
             for (int k = 0; k < kTileK / 16; ++k) umma_pair_bf16(tmem_d, da + 2 * k, db + 2 * k, idesc, (i > 0 || k > 0) ? 1u : 0u);
-            umma_pair_commit(smem_u32(&empty_bar[slot]));
+            umma_pair_commit(smem_u32(&empty_bar[pos.slot]));
+            pos.advance();
           }
           umma_pair_commit(smem_u32(&accum_full[acc]));
         }
@@ -836,18 +775,18 @@ gemm_tc_wide_swiglu_kernel(const __grid_constant__ CUtensorMap map_w, const __gr
     if (lane == 0) {
       // ---------------- producer
       sb::grid_dependency_wait();
-      int it = 0;
+      RingPos pos(p.stages, 1);
       for (int tile = blockIdx.x; tile < total_tiles; tile += gridDim.x) {
         const int tile_m = tile % p.tiles_m, tile_n = tile / p.tiles_m;
-        for (int i = 0; i < kblocks; ++i, ++it) {
-          const int slot = it % p.stages;
-          if (it >= p.stages) mbar_wait(smem_u32(&empty_bar[slot]), ((it / p.stages) - 1) & 1, p.status, 1);
-          const uint32_t bar = smem_u32(&full_bar[slot]);
-          const uint32_t a = smem0 + slot * stage_bytes;
+        for (int i = 0; i < kblocks; ++i) {
+          mbar_wait(smem_u32(&empty_bar[pos.slot]), pos.par, p.status, 1);
+          const uint32_t bar = smem_u32(&full_bar[pos.slot]);
+          const uint32_t a = smem0 + pos.slot * stage_bytes;
           mbar_expect_tx(bar, stage_bytes);
           tma_load_2d(a, &map_w, bar, i * kTileK, tile_m * kTileM);
           tma_load_2d(a + kStageA, &map_w, bar, i * kTileK, p.half_rows + tile_m * kTileM);
           tma_load_2d(a + 2 * kStageA, &map_x, bar, i * kTileK, tile_n * BN);
+          pos.advance();
         }
       }
     }
@@ -855,16 +794,18 @@ gemm_tc_wide_swiglu_kernel(const __grid_constant__ CUtensorMap map_w, const __gr
     if (lane == 0) {
       // ---------------- MMA issuer: gate rows into columns [0, BN), up rows into [256, 256 + BN)
       const uint32_t idesc = instr_desc(BN);
-      int it = 0, ti = 0;
+      const uint64_t desc_fixed = smem_desc_sw128(0);
+      RingPos pos(p.stages, 0);
+      int ti = 0;
       for (int tile = blockIdx.x; tile < total_tiles; tile += gridDim.x, ++ti) {
         if (ti >= 1) mbar_wait(smem_u32(&accum_empty), (ti - 1) & 1, p.status, 4);
         tc_fence_after();
-        for (int i = 0; i < kblocks; ++i, ++it) {
-          const int slot = it % p.stages;
-          mbar_wait(smem_u32(&full_bar[slot]), (it / p.stages) & 1, p.status, 2);
+        for (int i = 0; i < kblocks; ++i, pos.advance()) {
+          const uint32_t slot = pos.slot;
+          mbar_wait(smem_u32(&full_bar[slot]), pos.par, p.status, 2);
           tc_fence_after();
-          const uint32_t a = smem0 + slot * stage_bytes;
-          const uint64_t dg = smem_desc_sw128(a), du = smem_desc_sw128(a + kStageA), db = smem_desc_sw128(a + 2 * kStageA);
+          const uint64_t dg = stage_desc(desc_fixed, smem0, slot, stage_bytes, 0), du = stage_desc(desc_fixed, smem0, slot, stage_bytes, kStageA),
+                         db = stage_desc(desc_fixed, smem0, slot, stage_bytes, 2 * kStageA);
 #pragma unroll
           for (int k = 0; k < kTileK / 16; ++k) {
             umma_bf16(tmem_base, dg + 2 * k, db + 2 * k, idesc, (i > 0 || k > 0) ? 1u : 0u);

@@ -29,7 +29,7 @@ __device__ __forceinline__ float4 add4(float4 a, float4 b) { return make_float4(
 __device__ __forceinline__ float add4(float a, float b) { return a + b; }
 
 template <class TW, class TO, int VEC>
-__global__ void rmsnorm_kernel(float* __restrict__ h, const float* __restrict__ partials, int n_partials,
+__global__ void __launch_bounds__(1024) rmsnorm_kernel(float* __restrict__ h, const float* __restrict__ partials, int n_partials,
                                int64_t partial_stride, const TW* __restrict__ weight, TO* __restrict__ out,
                                int H, float eps) {
   using V = typename VecF<VEC>::type;
@@ -50,15 +50,20 @@ __global__ void rmsnorm_kernel(float* __restrict__ h, const float* __restrict__ 
   for (int i = threadIdx.x; i < units; i += blockDim.x) {
     V v = hr[i];
     if (n_partials > 0) {
+      // up to kInFlight partial sums are requested at once (every load of a few tokens' row is a round trip to L2,
+      // and they are what this kernel's time consists of), then added left to right
+      constexpr int kInFlight = 8;
       const V* p = reinterpret_cast<const V*>(partials + static_cast<int64_t>(r) * H) + i;
       const int64_t ps = partial_stride / VEC;
-      V sum = p[0];
-      int s = 1;
-      for (; s + 4 <= n_partials; s += 4) {
-        const V a = p[s * ps], b = p[(s + 1) * ps], c = p[(s + 2) * ps], d = p[(s + 3) * ps];
-        sum = add4(add4(add4(add4(sum, a), b), c), d);
-      }
-      for (; s < n_partials; ++s) sum = add4(sum, p[s * ps]);
+      V part[kInFlight];
+#pragma unroll
+      for (int s = 0; s < kInFlight; ++s)
+        if (s < n_partials) part[s] = p[s * ps];
+      V sum = part[0];
+#pragma unroll
+      for (int s = 1; s < kInFlight; ++s)
+        if (s < n_partials) sum = add4(sum, part[s]);
+      for (int s = kInFlight; s < n_partials; ++s) sum = add4(sum, p[s * ps]);
       v = add4(v, sum);
       hr[i] = v;
     }

@@ -935,6 +935,17 @@ SB_API int sb_program_add(void* program, const SbOp* op) {
 
 SB_API int sb_program_size(void* program) { return (int)static_cast<Program*>(program)->ops.size(); }
 
+// Operation `index` stands for the `count` operations behind it whenever it launches (SbOp::covers).
+SB_API int sb_program_set_covers(void* program, int index, int count) {
+  Program* p = static_cast<Program*>(program);
+  if (index < 0 || count < 0 || (size_t)index + (size_t)count >= p->ops.size()) {
+    g_error = "an operation can only stand for operations that follow it";
+    return -1;
+  }
+  p->ops[index].covers = count;
+  return 0;
+}
+
 // Fills `step` for a batch whose integer inputs were staged at `staging` (sb_stage_step or sb_stage_decode: E entries
 // of count[i] tokens from position first[i]; n rows, `wanted` of them wanted) and will lie at `device_ints` once
 // copied. static_keys > 0: a recorded decode step of E single-token entries (the padding included), planned for keys
@@ -996,6 +1007,7 @@ SB_API int sb_program_run(void* program, const SbStep* step, void* stream, int32
     const int rc = reinterpret_cast<SbOpFn>(op.fn)(&op, step, stream);
     if (rc == SB_OP_LAUNCHED) {
       ++count;
+      k += (size_t)op.covers;
     } else if (rc != SB_OP_SKIPPED) {
       if (failed) *failed = (int32_t)k;
       if (launched) *launched = count;
@@ -1016,6 +1028,8 @@ SB_API int sb_program_run_timed(void* program, const SbStep* step, void* stream,
     const int rc = reinterpret_cast<SbOpFn>(op.fn)(&op, step, stream);
     per_op_us[k] = std::chrono::duration<double, std::micro>(std::chrono::steady_clock::now() - t0).count();
     if (rc != SB_OP_LAUNCHED && rc != SB_OP_SKIPPED) return -1;
+    if (rc == SB_OP_LAUNCHED)
+      for (int64_t c = 0; c < op.covers && k + 1 < p->ops.size(); ++c) per_op_us[++k] = 0.0;
   }
   return 0;
 }

@@ -11,6 +11,9 @@
 // An operation function has the signature `int fn(const SbOp*, const SbStep*, void* stream)` and returns
 // SB_OP_LAUNCHED, SB_OP_FAILED (the reason is in its library's sb_last_error()) or SB_OP_SKIPPED (this step needs
 // nothing of it). Any library may provide operations; the runner knows none of them by name.
+//
+// An operation may stand for the `covers` operations that follow it (one kernel that does the work of many, for the
+// steps it is made for): when it launches, the runner passes over those; when it skips, they run as usual.
 #pragma once
 
 #include <stdint.h>
@@ -52,6 +55,7 @@ typedef struct SbOp {
   void* fn;                    // SbOpFn
   int64_t i[SB_OP_INTS];       // the operation's own integer and pointer arguments (see each sb_op_* function)
   double f[SB_OP_FLOATS];
+  int64_t covers;              // > 0: when this operation launches, the next `covers` operations do not run
 } SbOp;
 
 typedef int (*SbOpFn)(const SbOp*, const SbStep*, void*);

@@ -49,6 +49,7 @@ class EngineOptions:
     kv_shuffle_seed: int = 0           # tests: hand out pages in random order
     cuda_graphs: bool = True           # replay decode-only steps from CUDA graphs (one per batch and context bucket)
     native_step: bool = True           # launch a step's kernels from the native step program (else part by part from Python)
+    decode_chain: bool = False         # native steps of decoded tokens only: all layers as one persistent kernel (the same bits; measured slower)
     device: str = "cuda:0"
 
 
@@ -108,14 +109,14 @@ class Engine:
         self.compute_dtype = _DTYPES[o.dtype]
         env = BuildEnv(device=self.device, compute_dtype=self.compute_dtype, max_tokens=o.max_rows,
                        max_positions=self.max_context, max_logit_rows=min(o.max_full_rows, o.max_rows),
-                       max_requests=o.max_slots)
+                       max_requests=o.max_slots, decode_chain=o.decode_chain and o.native_step)
         self.env = env
         self.model = DecoderModel(self.spec, env)
         libraries = self.model.kernel_libraries()
         build_all(sorted(libraries))      # what this model needs, compiled side by side if missing
         # the word into which the tensor-core kernels' bounded waits report; the sampling kernels pass it on to the host
         self._status_device = None
-        if self.device.type == "cuda" and libraries & {"gemm_tc", "attention_tc5"}:
+        if self.device.type == "cuda" and libraries & {"gemm_tc", "attention_tc5", "decode_chain"}:
             from ..kernels import ops
             self._status_device = ops.shared_status_word(libraries | {"sampling"})
         plan = self.model.tensor_plan()
@@ -276,6 +277,8 @@ class Engine:
             code = int(self._status_device.item())
         if code != 0:
             self._status_device.zero_()
+            for chain in (self._program.chains if self._program is not None else ()):
+                chain.reset()          # (a chain that gave up leaves its phase counter where it was)
             raise EngineError(f"a wait inside a tensor-core kernel gave up (code {code}): a signal was lost and the "
                               f"results of the step are not valid")
 

@@ -41,6 +41,7 @@ SOURCES = {
     "gemm_tc": "gemm_tc.cu",
     "attention_tc": "attention_tc.cu",
     "attention_tc5": "attention_tc5.cu",
+    "decode_chain": "decode_chain.cu",
     "runtime": "runtime.cpp",        # host code only: the cache manager's books and the scheduler's decisions
 }
 HOST_FLAGS = ["-O2", "-std=c++17", "-g1", "-shared", "-fPIC", "-fvisibility=hidden"]

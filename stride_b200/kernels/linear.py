@@ -89,8 +89,12 @@ class Linear:
                                                       self.out_features, self.in_features, int(accumulate), int(wanted_rows)])
 
     def _tc_op(self, program, x, out, mode: int, splits: int = 1, wanted_rows: bool = False) -> None:
+        # the decode chain has phases for partial sums per K range and for SwiGLU, on the step's tokens
+        phase = None
+        if not wanted_rows and mode in (1, 3):
+            phase = lambda chain: chain.linear(x, self.weight, out, mode == 3, splits if mode == 1 else 1)
         program.add("gemm_tc", "sb_op_linear_tc", [x, x.stride(0), self.weight, self.weight.stride(0), out, self.out_features,
-                                                    self.in_features, mode, splits, int(wanted_rows)])
+                                                    self.in_features, mode, splits, int(wanted_rows)], chain=phase)
 
     def emit(self, program, x: torch.Tensor, out: torch.Tensor, wanted_rows: bool = False) -> None:
         """`forward`; with `wanted_rows` the rows are the step's wanted rows (the head), not its tokens."""

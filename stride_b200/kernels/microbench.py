@@ -127,7 +127,8 @@ def step(a) -> dict:
     cfg = dict(LLAMA_1B_SHAPE, num_hidden_layers=a.layers)
     B, T = a.batch, a.prefill
     opts = EngineOptions(dtype="bfloat16", max_rows=max(512, B, T), max_full_rows=max(B, 1), max_slots=B + 2,
-                         kv_pages=B * (a.context // 64 + 4) + T // 64 + 48, page_size=64, max_context=4096)
+                         kv_pages=B * (a.context // 64 + 4) + T // 64 + 48, page_size=64, max_context=4096,
+                         decode_chain=a.chain)
     eng = Engine.from_random(cfg, 0, opts)
     gen = torch.Generator().manual_seed(1)
     slots = [eng.cache.acquire_slot() for _ in range(B)]
@@ -174,6 +175,73 @@ def step(a) -> dict:
     return {"step": "prefill" if T else "decode", "batch": B, "context": a.context, "prefill": T, "layers": a.layers,
             "wall_us": round(ks[-1][2] - ks[0][1], 1), "kernels": len(ks),
             "by_kernel": {k: {"launches": c, "critical_us": round(v, 1)} for k, (c, v) in sorted(agg.items(), key=lambda x: -x[1][1])}}
+
+
+def chain(a) -> dict:
+    """Where the time of the decode chain goes (Llama 3.2 1B shape): the kernel's own nanosecond stamps per phase and
+    CTA, summarised per phase of a layer as medians over the layers: the phase's share of the critical path (from the
+    last arrival of the phase in front to its own last arrival), and for the CTAs that had a share in it the median
+    time until their input was there, of their work, and of the arrival itself."""
+    import ctypes
+    import statistics
+
+    from .. import Engine, EngineOptions, StepEntry
+    from .build import library
+    cfg = dict(LLAMA_1B_SHAPE, num_hidden_layers=a.layers)
+    B = a.batch
+    opts = EngineOptions(dtype="bfloat16", max_rows=max(512, B), max_full_rows=max(B, 1), max_slots=B + 2,
+                         kv_pages=B * (a.context // 64 + 4) + 48, page_size=64, max_context=4096, cuda_graphs=False, decode_chain=True)
+    eng = Engine.from_random(cfg, 0, opts)
+    gen = torch.Generator().manual_seed(1)
+    slots = [eng.cache.acquire_slot() for _ in range(B)]
+    for s in slots:
+        eng.cache.ensure(s, a.context)
+        for at in range(0, a.context, opts.max_rows):
+            n = min(opts.max_rows, a.context - at)
+            eng.step([StepEntry(s, at, torch.randint(0, 1000, (n,), generator=gen).tolist(), [])])
+    the_chain = eng._program.chains[0]
+    phases, sms = len(the_chain), torch.cuda.get_device_properties(0).multi_processor_count
+    stamps = torch.zeros(2, phases, sms, 4, dtype=torch.int64, device="cuda")
+    lib = library("decode_chain")
+    lib.sb_chain_trace.argtypes, lib.sb_chain_trace.restype = [ctypes.c_void_p, ctypes.c_void_p], None
+    for k in range(5):
+        if k == 4:
+            lib.sb_chain_trace(the_chain.handle, stamps.data_ptr())
+        entries = []
+        for s in slots:
+            eng.cache.ensure(s, a.context + k + 1)
+            entries.append(StepEntry(s, a.context + k, [5], [0]))
+        eng.step(entries)
+    torch.cuda.synchronize()
+    lib.sb_chain_trace(the_chain.handle, None)
+    both = stamps.cpu().numpy().astype("float64")
+    t, mma = both[0], both[1]
+    t0 = t[0, :, 0].min()
+    end = t[:, :, 3].max(axis=1)                      # a phase's last arrival
+    per_layer = phases // a.layers
+    rows = []
+    for k in range(per_layer):
+        crit, wait, work, arrive, busy, first, w_wait, x_wait, issued = [], [], [], [], [], [], [], [], []
+        for L in range(1 if a.layers > 1 else 0, a.layers):
+            ph = L * per_layer + k
+            crit.append(end[ph] - end[ph - 1] if ph else end[0] - t0)
+            had = t[ph, :, 1] > 0
+            busy.append(int(had.sum()))
+            if had.any():
+                wait.append(float(statistics.median((t[ph, had, 1] - end[ph - 1]) if ph else (t[ph, had, 1] - t0))))
+                work.append(float(statistics.median(t[ph, had, 2] - t[ph, had, 1])))
+                arrive.append(float(statistics.median(t[ph, had, 3] - t[ph, had, 2])))
+            did = mma[ph, :, 0] > 0
+            if did.any() and ph:
+                first.append(float(statistics.median(mma[ph, did, 0] - end[ph - 1])))
+                w_wait.append(float(statistics.median(mma[ph, did, 1])))
+                x_wait.append(float(statistics.median(mma[ph, did, 2])))
+                issued.append(float(statistics.median(mma[ph, did, 3] - end[ph - 1])))
+        med = lambda v: round(statistics.median(v) / 1000, 2) if v else None
+        rows.append({"phase": k, "critical_us": med(crit), "ctas": statistics.median(busy), "input_after_us": med(wait), "work_us": med(work),
+                     "arrive_us": med(arrive), "mma_first_operands_after_us": med(first), "mma_waited_for_weights_us": med(w_wait),
+                     "mma_waited_for_tokens_us": med(x_wait), "mma_issued_after_us": med(issued)})
+    return {"batch": B, "context": a.context, "layers": a.layers, "kernel_us": round((end[-1] - t0) / 1000, 1), "phases_of_a_layer": rows}
 
 
 def host(a) -> dict:
@@ -256,13 +324,18 @@ def main(argv=None) -> int:
     st.add_argument("--context", type=int, default=256)
     st.add_argument("--prefill", type=int, default=0, help="time one prompt of this many tokens instead of a decode step")
     st.add_argument("--layers", type=int, default=16)
+    st.add_argument("--chain", action="store_true", help="decode steps with all layers as one persistent kernel (the decode chain)")
     h = sub.add_parser("host")
+    ch = sub.add_parser("chain", help="the decode chain's own per-phase time stamps")
+    ch.add_argument("--batch", type=int, default=8)
+    ch.add_argument("--context", type=int, default=256)
+    ch.add_argument("--layers", type=int, default=16)
     h.add_argument("--tokens", type=int, default=256)
     h.add_argument("--decoders", type=int, default=8)
     h.add_argument("--layers", type=int, default=16)
     h.add_argument("--reps", type=int, default=30)
     a = ap.parse_args(argv)
-    print(json.dumps({"gemm": gemm, "attention": attention, "step": step, "host": host}[a.what](a), indent=1 if a.what == "step" else None))
+    print(json.dumps({"gemm": gemm, "attention": attention, "step": step, "host": host, "chain": chain}[a.what](a), indent=1 if a.what in ("step", "chain") else None))
     return 0
 
 

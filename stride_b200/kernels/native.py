@@ -38,7 +38,7 @@ class SbStep(ctypes.Structure):
 
 
 class SbOp(ctypes.Structure):
-    _fields_ = [("fn", c_void_p), ("i", c_int64 * OP_INTS), ("f", c_double * OP_FLOATS)]
+    _fields_ = [("fn", c_void_p), ("i", c_int64 * OP_INTS), ("f", c_double * OP_FLOATS), ("covers", c_int64)]
 
 
 _I32P = ctypes.POINTER(c_int32)
@@ -52,6 +52,7 @@ def _runtime():
         lib.sb_program_plan.restype, lib.sb_program_plan.argtypes = c_int, [c_void_p, c_int, c_int, c_int, c_int]
         lib.sb_program_add.restype, lib.sb_program_add.argtypes = c_int, [c_void_p, ctypes.POINTER(SbOp)]
         lib.sb_program_size.restype, lib.sb_program_size.argtypes = c_int, [c_void_p]
+        lib.sb_program_set_covers.restype, lib.sb_program_set_covers.argtypes = c_int, [c_void_p, c_int, c_int]
         lib.sb_program_prepare.restype = c_int
         lib.sb_program_prepare.argtypes = [c_void_p, c_int, _I32P, _I32P, c_int, c_int, c_int, _I32P, c_void_p, ctypes.POINTER(SbStep)]
         lib.sb_program_run.restype = c_int
@@ -71,6 +72,71 @@ def _value(v) -> int:
     return int(v)
 
 
+NO_PHASE = "no phase"     # `chain=` of an operation that has nothing to do in a step of decoded tokens only
+
+
+class DecodeChain:
+    """The layers of a step of decoded tokens as phases of one persistent kernel (`csrc/decode_chain.cu`): the same
+    arithmetic as the layers' separate operations, which it stands for in such steps. Parts add their phase beside
+    their operation (`StepProgram.add(..., chain=...)`); the methods mirror the operations they stand for."""
+
+    def __init__(self, max_rows: int):
+        from ctypes import c_float
+        self._lib = lib = library("decode_chain")
+        if not getattr(lib, "_sb_chain_typed", False):
+            lib.sb_chain_create.restype, lib.sb_chain_create.argtypes = c_void_p, [c_int]
+            lib.sb_chain_destroy.restype, lib.sb_chain_destroy.argtypes = None, [c_void_p]
+            lib.sb_chain_size.restype, lib.sb_chain_size.argtypes = c_int, [c_void_p]
+            lib.sb_chain_finish.restype, lib.sb_chain_finish.argtypes = c_int, [c_void_p]
+            lib.sb_chain_reset.restype, lib.sb_chain_reset.argtypes = c_int, [c_void_p]
+            lib.sb_chain_max_tokens.restype, lib.sb_chain_max_tokens.argtypes = c_int, []
+            lib.sb_chain_norm.restype = c_int
+            lib.sb_chain_norm.argtypes = [c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_int, c_void_p, c_int, c_int, c_float]
+            lib.sb_chain_linear.restype = c_int
+            lib.sb_chain_linear.argtypes = [c_void_p, c_void_p, c_int64, c_void_p, c_int64, c_void_p, c_int, c_int, c_int, c_int]
+            lib.sb_chain_attention.restype = c_int
+            lib.sb_chain_attention.argtypes = [c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int64, c_int64,
+                                               c_int64, c_int64, c_void_p, c_int, c_int, c_int, c_int, c_float, c_int]
+            lib._sb_chain_typed = True
+        self.handle = lib.sb_chain_create(max_rows)
+        self.keep: list = []
+
+    def __del__(self):
+        handle, self.handle = getattr(self, "handle", None), None
+        if handle:
+            self._lib.sb_chain_destroy(handle)
+
+    def __len__(self):
+        return self._lib.sb_chain_size(self.handle)
+
+    def _check(self, rc: int) -> None:
+        if rc != 0:
+            raise NotNative(self._lib.sb_last_error().decode())
+
+    def norm(self, h, pending, gain, x, size: int, eps: float) -> None:
+        flat, S, _ = pending if pending is not None else (None, 1, 0)
+        self.keep += [h, flat, gain, x]
+        self._check(self._lib.sb_chain_norm(self.handle, _value(h), _value(flat), S, _value(gain), _value(gain.dtype), _value(x), _value(x.dtype), size, eps))
+
+    def linear(self, x, weight, out, swiglu: bool, splits: int) -> None:
+        self.keep += [x, weight, out]
+        M, K = weight.shape
+        self._check(self._lib.sb_chain_linear(self.handle, _value(x), x.stride(0), _value(weight), weight.stride(0), _value(out), M, K, int(swiglu), splits))
+
+    def attention(self, qkv, S: int, cos_sin, out, pages, table, scratch_note: int, counters, num_heads: int, num_kv_heads: int, head_dim: int,
+                  window: int, scale: float, plan: int) -> None:
+        self.keep += [qkv, cos_sin, out, pages, table, counters]
+        self._check(self._lib.sb_chain_attention(self.handle, _value(qkv), S, _value(cos_sin), _value(out), _value(pages), _value(table), table.shape[1],
+                                                 pages.shape[3], pages.stride(0), pages.stride(1), pages.stride(2), scratch_note, _value(counters),
+                                                 num_heads, num_kv_heads, head_dim, window, scale, plan))
+
+    def finish(self) -> None:
+        self._check(self._lib.sb_chain_finish(self.handle))
+
+    def reset(self) -> None:
+        self._lib.sb_chain_reset(self.handle)
+
+
 class StepProgram:
     """The operations of one engine's step, the tile plans its mixers asked for, and what the build of the
     operations shares: the workspace, and which partial sums are pending on the residual stream."""
@@ -88,6 +154,9 @@ class StepProgram:
         self.step = SbStep()
         self._failed, self._launched = c_int32(0), c_int32(0)
         self._growing: dict = {}              # name -> [note (address, elements), dtype, {key: need(step) -> elements}]
+        self.chain = None                     # the DecodeChain being built between begin_chain() and end_chain(), if still whole
+        self._chain_at = -1                   # the index of the chain's operation
+        self.chains: list = []                # finished chains (kept alive; reset after a failed launch)
 
     def __del__(self):
         handle, self._handle = getattr(self, "_handle", None), None
@@ -103,10 +172,40 @@ class StepProgram:
             raise NotNative(self._lib.sb_last_error().decode())
         return k
 
-    def add(self, library_name: str, function: str, ints, floats=()) -> None:
-        """Append the operation `function` of kernel library `library_name` with its fixed arguments."""
+    def begin_chain(self) -> None:
+        """From here to `end_chain()` every operation is asked for its phase of the decode chain; if all of them
+        have one, one operation in front of them stands for them all in steps of decoded tokens only."""
+        chain = DecodeChain(self.max_rows)
+        self._chain_at = len(self)
+        self.add("decode_chain", "sb_op_decode_chain", [chain.handle])
+        self.chain = chain
+
+    def end_chain(self) -> bool:
+        chain, self.chain = self.chain, None
+        if chain is None or len(chain) == 0:
+            return False
+        chain.finish()
+        if self._lib.sb_program_set_covers(self._handle, self._chain_at, len(self) - self._chain_at - 1) < 0:
+            raise RuntimeError(self._lib.sb_last_error().decode())
+        self.chains.append(chain)
+        return True
+
+    def add(self, library_name: str, function: str, ints, floats=(), chain=None) -> None:
+        """Append the operation `function` of kernel library `library_name` with its fixed arguments. `chain`: while a
+        decode chain is being built, a function that adds the operation's phase to it (called with the chain; it may
+        raise `NotNative`), or NO_PHASE; an operation without one ends the building of the chain."""
         if len(ints) > OP_INTS or len(floats) > OP_FLOATS:
             raise ValueError(f"{function}: too many arguments for one operation")
+        if self.chain is not None:
+            building, self.chain = self.chain, None
+            if chain is NO_PHASE:
+                self.chain = building
+            elif chain is not None:
+                try:
+                    chain(building)
+                    self.chain = building
+                except NotNative:
+                    pass
         lib = library(library_name)
         op = SbOp()
         op.fn = ctypes.cast(getattr(lib, function), c_void_p).value

@@ -235,6 +235,7 @@ def gemm_tc_status() -> int:
 
 _status_word = None
 _status_users = {"gemm_tc": "sb_gemm_tc_use_status_word", "attention_tc5": "sb_attention_tc5_use_status_word",
+                 "decode_chain": "sb_decode_chain_use_status_word",
                  "sampling": "sb_sampling_use_status_word"}   # the sampling kernels only read it
 _status_registered: set = set()
 

@@ -18,6 +18,7 @@ import torch
 
 from ..kernels import ops
 from ..kernels.linear import Linear
+from ..kernels.native import NO_PHASE
 from .base import CacheNeed, Mixer, part_class, register_part
 from .spec import TensorPlan
 
@@ -184,14 +185,17 @@ class AttentionMixer(Mixer):
             tc5 = ops.attention_tc5_supported(self.num_heads, self.num_kv_heads, D, cache.page_size)
             fused = cache.writes and self._rotary == D
             plan = program.plan(G, 128 if tc5 else 64, self.num_kv_heads, ops.attention_decode_rope_limit() if fused else -1)
+        # (in a step of decoded tokens only, rotation and append can happen inside the attention kernel: the decode chain
+        # counts on it, so it takes this mixer only with a fully rotated head and a cache of its own)
         program.add("elementwise", "sb_op_rope_append",
                     [qkv, self.qkv_width, S, program.few_tokens, self._cos_sin, self._rotary, q, q.dtype, pages, pages.dtype, table,
                      table.shape[1], pages.shape[3], pages.stride(0), pages.stride(1), pages.stride(2), self.num_heads,
-                     self.num_kv_heads, D, int(cache.writes), plan])
+                     self.num_kv_heads, D, int(cache.writes), plan], chain=NO_PHASE if tensor_core and fused else None)
         if tensor_core:
             if tc5:
                 program.add("attention_tc5", "sb_op_attention_tc5",
-                            [q, mixed, pages, pages.shape[0], *where[1:], self.num_heads, self.num_kv_heads, D, self.window, plan], [self.scale])
+                            [q, mixed, pages, pages.shape[0], *where[1:], self.num_heads, self.num_kv_heads, D, self.window, plan], [self.scale],
+                            chain=NO_PHASE)
             # the decode kernel's chunk records: as many as the step's decode entries and their longest context need
             kv, need = self.num_kv_heads, ops.attention_tc_scratch
             scratch = program.growing_buffer("attn.scratch", torch.float32, (plan, kv, D),
@@ -199,7 +203,9 @@ class AttentionMixer(Mixer):
             counters = ws.raw("attn.counters", (T * self.num_kv_heads,), torch.int32)
             program.add("attention_tc", "sb_op_attention_tc",
                         [q, mixed, *where, scratch, 0, counters, self.num_heads, self.num_kv_heads, D, self.window, plan,
-                         int(tc5), qkv, self.qkv_width, S, program.few_tokens, self._cos_sin], [self.scale])
+                         int(tc5), qkv, self.qkv_width, S, program.few_tokens, self._cos_sin], [self.scale],
+                        chain=lambda chain: chain.attention(qkv, S, self._cos_sin, mixed, pages, table, scratch, counters, self.num_heads,
+                                                            self.num_kv_heads, D, self.window, self.scale, plan))
         else:
             program.add("attention_generic", "sb_op_attention_generic",
                         [q, mixed, q.dtype, *where, self.num_heads, self.num_kv_heads, D, self.window], [self.scale])

@@ -59,6 +59,7 @@ class BuildEnv:
     max_positions: int              # longest sequence
     max_logit_rows: int = 0         # most places of one step whose logits are wanted (0: max_tokens)
     max_requests: int = 0           # most requests alive at once (0: unknown)
+    decode_chain: bool = False      # steps of decoded tokens only run their layers as one persistent kernel
 
     def __post_init__(self):
         if self.max_logit_rows <= 0:

@@ -63,6 +63,8 @@ class DecoderModel:
         names = {"elementwise", "gemm_tc" if self.env.compute_dtype == torch.bfloat16 else "gemm_f32"}
         for p in self._parts():
             names |= p.kernel_libraries()
+        if self.env.decode_chain and {"gemm_tc", "attention_tc"} <= names:
+            names.add("decode_chain")
         return names
 
     def weight_bytes(self) -> int:
@@ -100,8 +102,15 @@ class DecoderModel:
         ws, H = program.workspace, self.spec.hidden_size
         program.h = ws.get("model.h", ws.max_tokens, (H,), torch.float32)
         self.embedding.emit(program, program.h, sampled)
+        chained = self.env.decode_chain and "decode_chain" in self.kernel_libraries()
+        if chained:
+            # every operation of the layers also names its phase of the decode chain; if all of them have one, one
+            # kernel stands for the layers in steps of decoded tokens only
+            program.begin_chain()
         for i, e in enumerate(self.spec.schedule):
             self.blocks[e.layer].emit(program, caches[i])
+        if chained:
+            program.end_chain()
         rows = ws.raw("model.head_rows", (ws.max_tokens, H), torch.float32)
         flat, S, _ = program.take_pending() or (None, 1, 0)
         program.add("elementwise", "sb_op_gather_rows", [program.h, flat, S, program.few_tokens, rows, H])

@@ -40,8 +40,9 @@ class RMSNorm(Norm):
 
     def _op(self, program, h, pending, out, wanted_rows: bool):
         flat, S, _ = pending if pending is not None else (None, 1, 0)
+        phase = None if wanted_rows else (lambda chain: chain.norm(h, pending, self.weight, out, self.size, self.eps))
         program.add("norm", "sb_op_rmsnorm", [h, flat, S, program.few_tokens, self.weight, self.weight.dtype, out, out.dtype, self.size,
-                                              int(wanted_rows)], [self.eps])
+                                              int(wanted_rows)], [self.eps], chain=phase)
 
     def emit(self, program, out):
         self._op(program, program.h, program.take_pending(), out, False)

@@ -116,6 +116,27 @@ def test_operations_run_in_order_and_may_skip_or_fail():
     lib.sb_program_destroy(program)
 
 
+def test_an_operation_may_stand_for_those_behind_it():
+    """`covers`: when the operation launches, the runner passes over the covered ones; when it skips, they run."""
+    lib = _runtime()
+    for first_rc, expect in ((0, [20, 23]), (2, [20, 21, 22, 23])):
+        program = lib.sb_program_create(R, WORK)
+        for tag, rc in ((20, first_rc), (21, 0), (22, 0), (23, 0)):
+            op = SbOp()
+            op.fn = ctypes.cast(_record, ctypes.c_void_p).value
+            op.i[0], op.i[1] = tag, rc
+            lib.sb_program_add(program, ctypes.byref(op))
+        assert lib.sb_program_set_covers(program, 0, 2) == 0
+        assert lib.sb_program_set_covers(program, 2, 2) < 0 and "follow" in lib.sb_last_error().decode()     # beyond the end
+        step = SbStep()
+        failed, launched = ctypes.c_int32(-1), ctypes.c_int32(-1)
+        del _CALLS[:]
+        assert lib.sb_program_run(program, ctypes.byref(step), None, ctypes.byref(failed), ctypes.byref(launched)) == 0
+        assert [c[0] for c in _CALLS] == expect
+        assert launched.value == (2 if first_rc == 0 else 3)
+        lib.sb_program_destroy(program)
+
+
 def test_a_blocks_roles_are_checked():
     import torch
 
