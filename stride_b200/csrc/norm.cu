@@ -28,8 +28,8 @@ struct VecF<1> { using type = float; };
 __device__ __forceinline__ float4 add4(float4 a, float4 b) { return make_float4(a.x + b.x, a.y + b.y, a.z + b.z, a.w + b.w); }
 __device__ __forceinline__ float add4(float a, float b) { return a + b; }
 
-template <class TW, class TO, int VEC>
-__global__ void __launch_bounds__(1024) rmsnorm_kernel(float* __restrict__ h, const float* __restrict__ partials, int n_partials,
+template <class TW, class TO, int VEC, int MAXT>     // MAXT: the most threads of a block (1024, or 512 with more registers each)
+__global__ void __launch_bounds__(MAXT) rmsnorm_kernel(float* __restrict__ h, const float* __restrict__ partials, int n_partials,
                                int64_t partial_stride, const TW* __restrict__ weight, TO* __restrict__ out,
                                int H, float eps) {
   using V = typename VecF<VEC>::type;
@@ -52,7 +52,7 @@ __global__ void __launch_bounds__(1024) rmsnorm_kernel(float* __restrict__ h, co
     if (n_partials > 0) {
       // up to kInFlight partial sums are requested at once (every load of a few tokens' row is a round trip to L2,
       // and they are what this kernel's time consists of), then added left to right
-      constexpr int kInFlight = 8;
+      constexpr int kInFlight = MAXT > 512 ? 8 : 12;
       const V* p = reinterpret_cast<const V*>(partials + static_cast<int64_t>(r) * H) + i;
       const int64_t ps = partial_stride / VEC;
       V part[kInFlight];
@@ -227,10 +227,17 @@ SB_EXPORT int sb_rmsnorm(float* h, const float* partials, int n_partials, int64_
   }
 #define SB_NORM_V(TW, TO, VEC)                                                                                   \
   do {                                                                                                           \
-    if (smem > 48 * 1024)                                                                                        \
-      cudaFuncSetAttribute(rmsnorm_kernel<TW, TO, VEC>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem); \
-    sb::launch_pdl(rmsnorm_kernel<TW, TO, VEC>, n, threads, smem, stream, h, partials, n_partials, partial_stride, \
-                   static_cast<const TW*>(weight), static_cast<TO*>(out), H, eps);                              \
+    if (threads > 512) {                                                                                         \
+      if (smem > 48 * 1024)                                                                                      \
+        cudaFuncSetAttribute(rmsnorm_kernel<TW, TO, VEC, 1024>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem); \
+      sb::launch_pdl(rmsnorm_kernel<TW, TO, VEC, 1024>, n, threads, smem, stream, h, partials, n_partials, partial_stride, \
+                     static_cast<const TW*>(weight), static_cast<TO*>(out), H, eps);                            \
+    } else {                                                                                                     \
+      if (smem > 48 * 1024)                                                                                      \
+        cudaFuncSetAttribute(rmsnorm_kernel<TW, TO, VEC, 512>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem); \
+      sb::launch_pdl(rmsnorm_kernel<TW, TO, VEC, 512>, n, threads, smem, stream, h, partials, n_partials, partial_stride, \
+                     static_cast<const TW*>(weight), static_cast<TO*>(out), H, eps);                            \
+    }                                                                                                            \
   } while (0)
 #define SB_NORM(TW, TO)          \
   do {                           \
