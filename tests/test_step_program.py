@@ -137,6 +137,33 @@ def test_an_operation_may_stand_for_those_behind_it():
         lib.sb_program_destroy(program)
 
 
+def test_an_operation_without_a_phase_ends_the_building_of_the_chain(tmp_path):
+    """Parts name their phase of the decode chain beside their operation; one operation that names none (a part from
+    outside the package) and the layers have no chain: the placeholder operation stays and always skips."""
+    from stride_b200.kernels.native import NO_PHASE, NotNative, StepProgram
+    src = tmp_path / "phase_less.cu"
+    src.write_text('#include "common.cuh"\n#include "step_ops.h"\nSB_DEFINE_LAST_ERROR()\n'
+                   'SB_EXPORT int phase_less_op(const SbOp*, const SbStep*, void*) { return SB_OP_SKIPPED; }\n')
+    register_kernel_library("phase_less_library", src)
+    program = StepProgram(None, 64, 64, 512)
+    program.begin_chain()
+    assert program.chain is not None and len(program) == 1
+    program.add("phase_less_library", "phase_less_op", [1], chain=NO_PHASE)
+    assert program.chain is not None
+    seen = []
+    program.add("phase_less_library", "phase_less_op", [2], chain=lambda chain: seen.append(chain))
+    assert program.chain is not None and seen == [program.chain]
+
+    def refuses(chain):
+        raise NotNative("this shape has no phase")
+    program.add("phase_less_library", "phase_less_op", [3], chain=refuses)
+    assert program.chain is None
+    program.begin_chain()
+    program.add("phase_less_library", "phase_less_op", [4])          # no phase named at all
+    assert program.chain is None
+    assert program.end_chain() is False and program.chains == []
+
+
 def test_a_blocks_roles_are_checked():
     import torch
 
