@@ -167,13 +167,17 @@ struct BlockEnv {
   __device__ __forceinline__ void sync() { __syncthreads(); }
   __device__ __forceinline__ void wait_inputs() { sb::grid_dependency_wait(); }
 };
-template <int D, bool FUSED>
+template <int D, bool FUSED, bool CLUSTER>
 __global__ void __launch_bounds__(128, FUSED ? 3 : (D == 64 ? kDecodeCtas64 : 3)) attn_decode_kernel(const AttnTcParams p) {
   extern __shared__ __align__(128) uint8_t smem_tiles[];
   __shared__ int is_last_s;
   sb::grid_launch_dependents();
   BlockEnv env;
-  decode_unit<D, FUSED>(p, blockIdx.x, blockIdx.y, blockIdx.z, smem_tiles, &is_last_s, threadIdx.x, env);
+  // (CLUSTER: the chunk's record lies over the used-up key/value tiles, behind the warps' results [4][16][D + 2]; the
+  // cluster is the grid's z extent, so the rank is the chunk)
+  static_assert((4 * 16 * (D + 2) + decode_record_floats<D>()) * sizeof(float) <= 4 * 64 * D * sizeof(bf16), "the record must fit over the tiles");
+  float* record = CLUSTER ? reinterpret_cast<float*>(smem_tiles) + 4 * 16 * (D + 2) : nullptr;
+  decode_unit<D, FUSED, CLUSTER>(p, blockIdx.x, blockIdx.y, blockIdx.z, smem_tiles, &is_last_s, threadIdx.x, env, record);
 }
 
 template <int D>
@@ -213,15 +217,28 @@ int launch(const AttnTcParams& p, int n_tiles, int n_items, cudaStream_t stream)
     static_assert(4 * 64 * D * sizeof(bf16) >= 4 * 16 * (D + 2) * sizeof(float), "the results must fit over the tiles");
     static sb::DeviceOnce once;
     if (once.needed()) {
-      if (cudaFuncSetAttribute(attn_decode_kernel<D, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess ||
-          cudaFuncSetAttribute(attn_decode_kernel<D, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem_fused) != cudaSuccess)
+      if (cudaFuncSetAttribute(attn_decode_kernel<D, false, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess ||
+          cudaFuncSetAttribute(attn_decode_kernel<D, true, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem_fused) != cudaSuccess ||
+          cudaFuncSetAttribute(attn_decode_kernel<D, false, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess ||
+          cudaFuncSetAttribute(attn_decode_kernel<D, true, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem_fused) != cudaSuccess)
         return sb::fail("sb_attention_tc: cannot raise the shared memory limit");
       once.done();
     }
     AttnTcParams pd = p;
     pd.work = p.work + 2 * n_tiles;
-    if (p.qkv != nullptr) sb::launch_pdl(attn_decode_kernel<D, true>, dim3(n_items, p.Hkv, p.chunks), dim3(128), smem_fused, stream, pd);
-    else sb::launch_pdl(attn_decode_kernel<D, false>, dim3(n_items, p.Hkv, p.chunks), dim3(128), smem, stream, pd);
+    const dim3 grid(n_items, p.Hkv, p.chunks);
+    // 2 to 8 chunks whose records the kernel folds itself: the chunks of an entry as one cluster (records through
+    // distributed shared memory); one chunk needs no fold, more than 8 go through records in global memory and a ticket
+    const bool cluster = pd.counters != nullptr && p.chunks >= 2 && p.chunks <= 8;
+    if (cluster) {
+      const dim3 shape(1, 1, p.chunks);
+      if (p.qkv != nullptr) sb::launch_pdl_cluster(attn_decode_kernel<D, true, true>, grid, dim3(128), smem_fused, stream, shape, pd);
+      else sb::launch_pdl_cluster(attn_decode_kernel<D, false, true>, grid, dim3(128), smem, stream, shape, pd);
+    } else if (p.qkv != nullptr) {
+      sb::launch_pdl(attn_decode_kernel<D, true, false>, grid, dim3(128), smem_fused, stream, pd);
+    } else {
+      sb::launch_pdl(attn_decode_kernel<D, false, false>, grid, dim3(128), smem, stream, pd);
+    }
     if (pd.counters == nullptr) sb::launch_pdl(attn_combine_kernel<D>, dim3(n_items, p.Hkv), dim3(D), 0, stream, pd);
   }
   return sb::check_launch("sb_attention_tc");

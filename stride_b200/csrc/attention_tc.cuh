@@ -356,11 +356,18 @@ __device__ __forceinline__ void projected_pair(const AttnTcParams& p, int row, i
 // partial sums) may be read. smem_tiles: decode_unit_smem<D, FUSED>() bytes, 128-byte aligned; is_last_s: one int of
 // shared memory. A caller that runs several units in a row synchronises between them.
 template <int D, bool FUSED>
-constexpr size_t decode_unit_smem() {
+__host__ __device__ constexpr size_t decode_unit_smem() {
   return FUSED ? static_cast<size_t>(16 * (D + 8) + 8 * 64 * (D + 8)) * sizeof(bf16) : static_cast<size_t>(16 * (D + 8) + 4 * 64 * D) * sizeof(bf16);
 }
-template <int D, bool FUSED, class Env>
-__device__ __forceinline__ void decode_unit(const AttnTcParams& p, int item, int g, int chunk, uint8_t* smem_tiles, int* is_last_p, int tid, Env& env) {
+// CLUSTER: the CTAs of an entry's chunks are one thread-block cluster (rank = chunk, at most 8): every CTA leaves its
+// chunk's record in its own shared memory (cluster_record: decode_record_floats<D>() floats that nothing else uses), and
+// the CTA of rank 0 folds them in ascending order through distributed shared memory: two cluster barriers instead of a
+// record in global memory, a ticket and a second look at memory (3.2 us a layer for a decode step at the 1B sizes).
+template <int D>
+__host__ __device__ constexpr int decode_record_floats() { return 16 * (D + 2); }
+template <int D, bool FUSED, bool CLUSTER, class Env>
+__device__ __forceinline__ void decode_unit(const AttnTcParams& p, int item, int g, int chunk, uint8_t* smem_tiles, int* is_last_p, int tid, Env& env,
+                                            float* cluster_record = nullptr) {
   constexpr int LD = D + 8, CH = D / 8;
   // FUSED: tiles [4 warps][K, V][64][D + 8]. Otherwise [4 warps][64][D], swizzled: a warp's values take the place of
   // its keys once the scores are out, which lets twice as many warps live on an SM; the values travel while the
@@ -379,13 +386,41 @@ __device__ __forceinline__ void decode_unit(const AttnTcParams& p, int item, int
             first_pos = p.meta[3 * p.meta_stride + e];
   const int pos_hi = first_pos + L - 1;
   const int key_lo = p.window > 0 ? max(0, first_pos - p.window + 1) : 0;
+  const int rows = L * G;
+  constexpr int PR = D / 2;
+  const int d = (tid % PR) * 2;
+  const int c0 = key_lo / kChunk, c1 = pos_hi / kChunk;
+  // CLUSTER: once every CTA's record is in its shared memory, rank 0 folds the entry's chunks in ascending order (the
+  // arithmetic of fold_chunks2) and writes the rows; the others stay until it has read them.
+  auto cluster_fold = [&]() {
+    sb::cluster_sync();
+    if (chunk == 0) {
+      for (int r = tid / PR; r < rows; r += 128 / PR) {
+        float m = -INFINITY, l = 0.0f, o0 = 0.0f, o1 = 0.0f;
+        for (int c = c0; c <= c1; ++c) {
+          const float2 ml = sb::cluster_load_float2(sb::cluster_peer_address(cluster_record + 16 * D + r * 2, c));
+          if (ml.x == -INFINITY) continue;
+          const FoldFactors f = fold_factors(m, ml.x);
+          const float2 v = sb::cluster_load_float2(sb::cluster_peer_address(cluster_record + r * D + d, c));
+          l = fold_value(l, ml.y, f);
+          o0 = fold_value(o0, v.x, f);
+          o1 = fold_value(o1, v.y, f);
+          m = f.m;
+        }
+        const int pi = div_g(p, r);
+        *reinterpret_cast<uint32_t*>(p.out + (static_cast<int64_t>(first_row + pi) * p.Hq + g * G + r - pi * G) * D + d) =
+            pack_bf16(finish(o0, l), finish(o1, l));
+      }
+    }
+    sb::cluster_sync();
+  };
   if (chunk * kChunk > pos_hi || chunk * kChunk + kChunk - 1 < key_lo) {   // no key of this chunk is visible
     env.wait_inputs();
+    if (CLUSTER) cluster_fold();
     return;
   }
   const int32_t* table = p.block_table + static_cast<int64_t>(slot) * p.max_pages;
   const bf16* kplane = p.k_base + static_cast<int64_t>(g) * p.head_stride;
-  const int rows = L * G;
 
   bf16* sK = sKV + warp * kBufs * kTile;
   bf16* sV = sK + (kBufs - 1) * kTile;
@@ -490,8 +525,9 @@ __device__ __forceinline__ void decode_unit(const AttnTcParams& p, int item, int
   // the chunk's record: its tiles folded in key order into an empty state; a thread takes two neighbouring
   // elements of a row, which share the row's factors
   const int64_t rec = (static_cast<int64_t>(item) * p.Hkv + g) * p.chunks + chunk;
-  constexpr int PR = D / 2;
-  const int d = (tid % PR) * 2;
+  // The entry's only chunk (at most 256 keys in view): its record is the row, so it is folded into the empty row state here,
+  // with the operations the last CTA of several would use, and written; no record, no ticket, no second look at memory.
+  const bool alone = !CLUSTER && p.counters != nullptr && c0 == c1;
   for (int r = tid / PR; r < rows; r += 128 / PR) {
     float m = -INFINITY, l = 0.0f, o0 = 0.0f, o1 = 0.0f;
 #pragma unroll
@@ -505,12 +541,33 @@ __device__ __forceinline__ void decode_unit(const AttnTcParams& p, int item, int
       o1 = fold_value(o1, v.y, f);
       m = f.m;
     }
+    if (alone) {
+      float lr = 0.0f, a = 0.0f, b = 0.0f;
+      if (m != -INFINITY) {
+        const FoldFactors f = fold_factors(-INFINITY, m);
+        lr = fold_value(lr, l, f);
+        a = fold_value(a, o0, f);
+        b = fold_value(b, o1, f);
+      }
+      const int pi = div_g(p, r);
+      *reinterpret_cast<uint32_t*>(p.out + (static_cast<int64_t>(first_row + pi) * p.Hq + g * G + r - pi * G) * D + d) =
+          pack_bf16(finish(a, lr), finish(b, lr));
+      continue;
+    }
+    if (CLUSTER) {
+      *reinterpret_cast<float2*>(cluster_record + r * D + d) = make_float2(o0, o1);
+      if (d == 0) *reinterpret_cast<float2*>(cluster_record + 16 * D + r * 2) = make_float2(m, l);
+      continue;
+    }
     *reinterpret_cast<float2*>(&p.part_o[rec * 16 * D + r * D + d]) = make_float2(o0, o1);
     if (d == 0) *reinterpret_cast<float2*>(&p.part_ml[(rec * 16 + r) * 2]) = make_float2(m, l);
   }
-  if (p.counters == nullptr) return;
+  if (CLUSTER) {
+    cluster_fold();      // (also when this chunk is the entry's only one: the other CTAs of the cluster wait at its barriers)
+    return;
+  }
+  if (p.counters == nullptr || alone) return;
   // The CTA that finishes an entry's last chunk folds all of them, in ascending order, and writes the rows.
-  const int c0 = key_lo / kChunk, c1 = pos_hi / kChunk;
   env.sync();
   if (tid == 0) {
     __threadfence();   // the CTA's records (made visible to this thread by the barrier) before the ticket

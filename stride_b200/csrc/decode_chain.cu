@@ -465,7 +465,7 @@ __global__ void __launch_bounds__(kChainThreads, 1) decode_chain_kernel(const Ch
         for (int u = cta; u < units; u += G) {
           worker_sync();       // the unit in front is done with the tiles
           const int item = u % p.items, g = (u / p.items) % a.Hkv, chunk = u / (p.items * a.Hkv);
-          at::decode_unit<D, true>(a, item, g, chunk, work_smem, &is_last_s, wtid, env);
+          at::decode_unit<D, true, false>(a, item, g, chunk, work_smem, &is_last_s, wtid, env);
         }
         env.wait_inputs();     // (a CTA without units still sees the phase in front complete before it arrives)
       }
