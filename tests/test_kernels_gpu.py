@@ -299,6 +299,33 @@ def test_decode_attention_over_long_contexts(D, Hq, Hkv, page, window):
     assert torch.equal(out, again)
 
 
+@pytest.mark.parametrize("D,Hq,Hkv,page,window", [(64, 8, 2, 64, 0), (128, 6, 2, 32, 0), (64, 4, 4, 16, 300)])
+@pytest.mark.parametrize("olds", [[255, 3], [256, 100, 0], [1279, 300, 0, 1023], [2047, 5, 1800]])
+def test_decode_attention_folds_its_chunks_three_ways_with_the_same_bits(D, Hq, Hkv, page, window, olds):
+    """One chunk (the rows are written at once), 2 to 8 chunks (a cluster per entry, records through distributed shared
+    memory) and the records in global memory folded by a kernel of its own give the same bits; the batch's longest
+    context decides which of the first two runs, entries shorter than it sit in the same clusters."""
+    from stride_b200.kernels import ops
+    news = [1] * len(olds)
+    case = _paged_case(news, olds, Hq, Hkv, D, page, torch.bfloat16, seed=D + len(olds), peak=(0, 1))
+    q, cache, table, meta = case["q"], case["cache"], case["table"], case["meta"]
+    E = len(news)
+    items = torch.arange(E, dtype=torch.int32, device=DEV)
+    chunks = max(olds) // 256 + 1
+    assert 1 <= chunks <= 8
+    scale = 1.0 / math.sqrt(D)
+    outs = []
+    for own_fold in (True, False):
+        out = torch.full_like(q, float("nan"))
+        scratch = torch.zeros(ops.attention_tc_scratch(E, Hkv, chunks, D), device=DEV)
+        counters = torch.zeros(E * Hkv, dtype=torch.int32, device=DEV) if own_fold else None
+        ops.attention_tc(q, out, cache, table, meta, items, 0, E, chunks, scratch, Hq, Hkv, D, window, scale, counters=counters)
+        outs.append(out)
+    assert torch.equal(outs[0], outs[1])
+    ref = _attention_reference(case, Hq, Hkv, D, window)
+    assert (outs[0].float().cpu() - ref).abs().max() <= 2e-2 * max(1.0, float(ref.abs().max()))
+
+
 @pytest.mark.parametrize("D,Hq,Hkv,page,window", [(64, 8, 2, 16, 0), (64, 32, 8, 64, 100), (128, 6, 2, 32, 0), (64, 3, 3, 8, 0)])
 def test_decode_attention_with_rotation_fused(D, Hq, Hkv, page, window):
     """The decode kernel that rotates and appends by itself gives the same output and leaves the same cache, bit for
