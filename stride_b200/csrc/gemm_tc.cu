@@ -996,7 +996,9 @@ SB_EXPORT int sb_gemm_tc(const void* x, int64_t ldx, const void* w, int64_t ldw,
                    static_cast<size_t>(p.stages) * wide_stage + 1024, stream, ww, wx, p);
     return sb::check_launch("sb_gemm_tc");
   }
-  if (n > 256 && epilogue != kAdd && (splits == 1 || fold)) {
+  // (pairs from 129 tokens on when K is one range: a CTA of a pair takes in half of the token tile, and with more than
+  // 128 tokens a single CTA's intake of both operands, not HBM, bounds a K step: a step of 256 tokens 1.52 -> 1.44 ms)
+  if (n > 128 && epilogue != kAdd && (splits == 1 || fold)) {
     // Pairs of CTAs: tiles of 256 weight rows (or 128 gate + 128 up rows) by BN tokens, BN chosen by whole waves of 74 pairs.
     const long long tm = epilogue == kSwiglu ? (half_rows + 127) / 128 : (M + 255) / 256;
     long long best = -1;
