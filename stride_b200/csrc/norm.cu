@@ -204,14 +204,14 @@ SB_EXPORT int sb_rmsnorm(float* h, const float* partials, int n_partials, int64_
 #define SB_ROWS_J(TO, W, JT) \
   sb::launch_pdl(rmsnorm_rows_kernel<TO, W, JT>, grid, dim3(64), 0, stream, h, partials, n_partials, partial_stride, \
                  weight, weight_dtype == 1, static_cast<TO*>(out), n, H, eps)
-  // the row stays in registers between the passes when it has at most 32 pieces a lane (with `threads` < 1024 it has
-  // fewer than 2 * threads / 4 pieces, two rounds at most)
+  // the row stays in registers between the passes while it has at most 16 pieces a lane; wider rows are read again from
+  // L2 in the second pass (measured: 32 pieces in registers leave too few warps an SM: width 4096 58 -> 38 us for 2,048
+  // rows, width 3072 48 -> 30; at width 2048, 16 pieces, registers are the faster way, 17 us against 21)
 #define SB_ROWS(TO)                                                      \
   do {                                                                   \
-    if (threads == 1024 && units <= 1024) SB_ROWS_J(TO, 32, 1);      \
-    else if (threads == 1024) SB_ROWS_J(TO, 32, 0);                  \
+    if (threads == 1024) SB_ROWS_J(TO, 32, 0);                           \
     else if (threads == 512 && units <= 512) SB_ROWS_J(TO, 16, 1);   \
-    else if (threads == 512) SB_ROWS_J(TO, 16, 2);                   \
+    else if (threads == 512) SB_ROWS_J(TO, 16, 0);                   \
     else if (threads == 256 && units <= 256) SB_ROWS_J(TO, 8, 1);    \
     else if (threads == 256) SB_ROWS_J(TO, 8, 2);                    \
     else if (units <= 128) SB_ROWS_J(TO, 4, 1);                      \

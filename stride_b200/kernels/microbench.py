@@ -112,10 +112,19 @@ LLAMA_1B_SHAPE = {
                      "original_max_position_embeddings": 8192},
     "tie_word_embeddings": True, "rms_norm_eps": 1e-5, "max_position_embeddings": 4096,
 }
+# the layer sizes of Llama 3.2 3B and Llama 3.1 8B (head size 128)
+LLAMA_SHAPES = {
+    "1b": LLAMA_1B_SHAPE,
+    "3b": dict(LLAMA_1B_SHAPE, hidden_size=3072, num_hidden_layers=28, num_attention_heads=24, head_dim=128),
+    "8b": dict(LLAMA_1B_SHAPE, hidden_size=4096, intermediate_size=14336, num_hidden_layers=32, head_dim=128, tie_word_embeddings=False,
+               max_position_embeddings=8192,
+               rope_scaling={"rope_type": "llama3", "factor": 8.0, "low_freq_factor": 1.0, "high_freq_factor": 4.0,
+                             "original_max_position_embeddings": 8192}),
+}
 
 
 def step(a) -> dict:
-    """Kernel timeline of one engine step (Llama 3.2 1B shape, random weights) from torch.profiler: a decode step of
+    """Kernel timeline of one engine step (Llama 3.2 1B shape unless `shape` says otherwise, random weights) from torch.profiler: a decode step of
     `batch` requests replayed from its CUDA graph, or a prompt of `prefill` tokens. Kernels overlap under programmatic
     dependent launch, so each kernel is charged the time from its predecessor's end to its own end."""
     import collections
@@ -124,7 +133,7 @@ def step(a) -> dict:
     from torch.profiler import ProfilerActivity, profile
 
     from .. import Engine, EngineOptions, StepEntry
-    cfg = dict(LLAMA_1B_SHAPE, num_hidden_layers=a.layers)
+    cfg = dict(LLAMA_SHAPES[a.shape], num_hidden_layers=a.layers)
     B, T = a.batch, a.prefill
     opts = EngineOptions(dtype="bfloat16", max_rows=max(512, B, T), max_full_rows=max(B, 1), max_slots=B + 2,
                          kv_pages=B * (a.context // 64 + 4) + T // 64 + 48, page_size=64, max_context=4096,
@@ -324,6 +333,7 @@ def main(argv=None) -> int:
     st.add_argument("--context", type=int, default=256)
     st.add_argument("--prefill", type=int, default=0, help="time one prompt of this many tokens instead of a decode step")
     st.add_argument("--layers", type=int, default=16)
+    st.add_argument("--shape", choices=sorted(LLAMA_SHAPES), default="1b", help="layer sizes: Llama 3.2 1B, 3.2 3B or 3.1 8B")
     st.add_argument("--chain", action="store_true", help="decode steps with all layers as one persistent kernel (the decode chain)")
     h = sub.add_parser("host")
     ch = sub.add_parser("chain", help="the decode chain's own per-phase time stamps")
