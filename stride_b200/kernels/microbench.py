@@ -43,7 +43,26 @@ def _time(fn, reps: int, warmup: int = 3) -> float:
     return start.elapsed_time(stop) * 1e3 / reps      # microseconds
 
 
+def gemm_f32(a) -> dict:
+    """The linear layer of the 32-bit path: float32 activations, bfloat16 weights, FMA on the CUDA cores."""
+    n, M, K = a.tokens, a.rows, a.cols
+    copies = a.copies or max(1, min(64, (2 * L2_BYTES) // (M * K * 2) + 1))
+    ws = [(torch.randn(M, K, device="cuda") * 0.02).bfloat16() for _ in range(copies)]
+    x = torch.randn(n, K, device="cuda")
+    out = torch.zeros(n, M, device="cuda")
+    state = {"i": 0}
+
+    def run():
+        ops.gemm_f32(x, ws[state["i"] % copies], out, a.epilogue == "add")
+        state["i"] += 1
+    us = _time(run, a.reps)
+    return {"kernel": "gemm_f32", "tokens": n, "rows": M, "cols": K, "epilogue": a.epilogue, "us": round(us, 2),
+            "weight_GBps": round(M * K * 2 / us / 1e3, 1), "TFLOPs": round(2.0 * n * M * K / us / 1e6, 2)}
+
+
 def gemm(a) -> dict:
+    if a.float32:
+        return gemm_f32(a)
     n, M, K = a.tokens, a.rows, a.cols
     epi = {"store": ops.STORE, "add": ops.ADD, "swiglu": ops.SWIGLU}[a.epilogue]
     copies = a.copies or max(1, min(64, (2 * L2_BYTES) // (M * K * 2) + 1))
@@ -318,6 +337,7 @@ def main(argv=None) -> int:
     g.add_argument("--copies", type=int, default=0)
     g.add_argument("--one-range", action="store_true", help="keep K in one range whatever the weight's shape")
     g.add_argument("--reps", type=int, default=50)
+    g.add_argument("--float32", action="store_true", help="the 32-bit path's linear layer (FMA, no tensor cores)")
     t = sub.add_parser("attention")
     t.add_argument("--batch", type=int, default=8)
     t.add_argument("--context", type=int, default=512)

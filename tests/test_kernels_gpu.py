@@ -406,7 +406,8 @@ def test_attention_outputs_are_nearly_all_correctly_rounded(T, R):
         assert (out.cpu().float() - want.float()).abs().max() <= 2.0 ** -7 * float(want.float().abs().max())
 
 
-@pytest.mark.parametrize("D,Hq,Hkv,page,window", [(48, 3, 3, 16, 0), (16, 4, 2, 64, 0), (80, 10, 2, 8, 37), (256, 2, 1, 32, 0)])
+@pytest.mark.parametrize("D,Hq,Hkv,page,window", [(48, 3, 3, 16, 0), (16, 4, 2, 64, 0), (80, 10, 2, 8, 37), (256, 2, 1, 32, 0),
+                                                   (50, 2, 1, 16, 21), (7, 3, 3, 8, 0), (512, 1, 1, 16, 0), (64, 8, 2, 64, 100), (132, 2, 2, 16, 0)])
 def test_attention_generic_float32(D, Hq, Hkv, page, window):
     from stride_b200.kernels import ops
     new = [1, 50, 1, 130, 2]
@@ -416,6 +417,31 @@ def test_attention_generic_float32(D, Hq, Hkv, page, window):
     ops.attention_generic(case["q"], out, case["cache"], case["table"], case["positions"], case["slots"], Hq, Hkv, D, window, D ** -0.5)
     ref = _attention_reference(case, Hq, Hkv, D, window)
     assert (out.cpu() - ref).abs().max() <= 2e-5 * max(1.0, float(ref.abs().max()))
+
+
+@pytest.mark.parametrize("D,Hq,Hkv,page,window,dtype", [(64, 8, 2, 64, 0, torch.float32), (80, 3, 1, 16, 300, torch.float32),
+                                                         (128, 4, 4, 32, 0, torch.bfloat16), (256, 2, 1, 16, 0, torch.float32),
+                                                         (512, 1, 1, 8, 0, torch.float32), (16, 2, 2, 64, 0, torch.float32)])
+def test_attention_generic_tiles_side_by_side_give_the_bits_of_tiles_in_a_row(D, Hq, Hkv, page, window, dtype):
+    """A few rows: a cluster of blocks per (row, head), each with tiles of its own, folded out of the others' shared memory.
+    Many rows: one block per (row, head), tile after tile. The same rows give the same bits both ways. The longest
+    request has more tiles than the cluster has blocks, so that a block holds two."""
+    from stride_b200.kernels import ops
+    new, old = [1, 1, 2], [1100, 130, 5]
+    case = _paged_case(new, old, Hq, Hkv, D, page, dtype, seed=D + 1, peak=(0, 3))
+    n = sum(new)
+    few = torch.full_like(case["q"], float("nan"))
+    ops.attention_generic(case["q"], few, case["cache"], case["table"], case["positions"], case["slots"], Hq, Hkv, D, window, D ** -0.5)
+    copies = 4 * 148 // (n * Hq) + 2   # more blocks than a cluster per (row, head) is launched for
+    q = case["q"].repeat(copies, 1)
+    many = torch.full_like(q, float("nan"))
+    ops.attention_generic(q, many, case["cache"], case["table"], case["positions"].repeat(copies), case["slots"].repeat(copies),
+                          Hq, Hkv, D, window, D ** -0.5)
+    for c in range(copies):
+        assert torch.equal(many[c * n:(c + 1) * n], few)
+    ref = _attention_reference(case, Hq, Hkv, D, window)
+    tol = 2e-5 if dtype == torch.float32 else 2.0 ** -7
+    assert (few.float().cpu() - ref).abs().max() <= tol * max(1.0, float(ref.abs().max()))
 
 
 # ---------------------------------------------------------------------------- the small kernels
