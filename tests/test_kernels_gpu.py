@@ -503,10 +503,13 @@ def test_embed_swiglu_gather():
 
 
 @pytest.mark.parametrize("M,K,wdtype,xdtype", [(333, 2048, torch.bfloat16, torch.float32), (70, 1000, torch.float32, torch.float32),
-                                               (129, 203, torch.bfloat16, torch.float32), (64, 512, torch.bfloat16, torch.bfloat16)])
+                                               (129, 203, torch.bfloat16, torch.float32), (64, 512, torch.bfloat16, torch.bfloat16),
+                                               (3, 52008, torch.bfloat16, torch.float32), (1, 264, torch.float32, torch.float32)])
 def test_gemm_f32_does_not_depend_on_the_batch(M, K, wdtype, xdtype):
-    """Up to 16 tokens the float32 product runs as a stream over the weights, beyond that in tiles: a token has the same
-    bits from either kernel, alone or among others, stored or added to what was there."""
+    """One token is a stream over the weights by persistent warps (the token in shared memory, or, too wide for that, the
+    tile kernel with a tile of one); 2 to 4, 5 to 16 and more tokens take tiles of three shapes; a K that is no multiple
+    of eight takes the element-wise loads. A token has the same bits from all of them, alone or among others, stored or
+    added to what was there."""
     from stride_b200.kernels import ops
     x = _rand(40, K, seed=5, dtype=xdtype)
     w = _rand(M, K, seed=6, dtype=wdtype)
