@@ -25,6 +25,8 @@
 // ([pages][2][Hkv][page_size][D] per layer); a key tile may span several pages.
 // Counterparts in arhaamatiq/stride: AttentionPage / AttentionCombine with KvT = bfloat16
 // (src/kernel_common.h:90-309), which are scalar.
+#include <algorithm>
+
 #include "attention_tc.cuh"
 #include "step_ops.h"
 #include "noalloc.h"
@@ -164,6 +166,7 @@ __global__ void __launch_bounds__(128) attn_chunk_kernel(const AttnTcParams p) {
 // projection's partial sums, rotated there, and the keys and values are appended to the cache by the CTA whose chunk
 // holds their position (no rotation kernel runs).
 struct BlockEnv {
+  static constexpr bool kFoldAhead = true;    // the next group of chunk records is requested while one is folded
   __device__ __forceinline__ void sync() { __syncthreads(); }
   __device__ __forceinline__ void wait_inputs() { sb::grid_dependency_wait(); }
 };
@@ -197,6 +200,150 @@ __global__ void __launch_bounds__(D) attn_combine_kernel(const AttnTcParams p) {
         __float2bfloat16_rn(fold_chunks<D>(p.part_o, p.part_ml, rec0, c0, c1, r, d));
 }
 
+// The same fold for long contexts (tens to hundreds of chunks an entry), where the requests for the records and the
+// latency of a chunk's own operations, not their number, set the time. The records of as many chunks as a stage of
+// shared memory holds are brought in with asynchronous copies, all in flight at once, while the stage before them is
+// folded; and the fold of a stage is taken apart by what hangs on what: (A) a row's running maximum before every chunk,
+// a warp's scan (a maximum is exact in any order); (B) the chunks' factors a = ex2(m - m'), b = ex2(m_t - m'), which hang
+// on those maxima alone, and the products v_t * b, all threads at once; (C) the sums l and o, one fused multiply-add a
+// chunk and element, which is all that has to wait for the chunk before. The operations and their operands are those
+// of fold_records. One request of 131,072 cached tokens (512 chunks): the fold by the CTA
+// that finishes last took 70 of the layer's 113 us, the keys and values themselves 43.
+// A CTA takes kStreamSlice of a head's D outputs (an SM brings in some 40 KB a microsecond, and a long context's records
+// are megabytes): the maxima and factors are computed by every slice's CTA anew, the values are shared out.
+constexpr int kStreamThreads = 256, kStreamChunks = 128, kStreamSlice = 16;   // threads; most chunks a stage; outputs a CTA
+template <int D>
+__global__ void __launch_bounds__(kStreamThreads) attn_combine_stream_kernel(const AttnTcParams p, int stage_floats) {
+  extern __shared__ __align__(16) float stages[];   // [2][stage_floats]
+  __shared__ float before[kStreamChunks][16];        // [chunk of the stage][row]: the row's maximum before the chunk
+  __shared__ float factor_a[kStreamChunks][16];      // a of (chunk, row); negative: the row sees no key of the chunk
+  __shared__ float l_rows[16];
+  sb::grid_launch_dependents();
+  sb::grid_dependency_wait();
+  const int item = blockIdx.x, g = blockIdx.y, d0 = blockIdx.z * kStreamSlice;
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  const int G = p.Hq / p.Hkv;
+  const int e = p.work[item];
+  const int first_row = p.meta[p.meta_stride + e], L = p.meta[2 * p.meta_stride + e], first_pos = p.meta[3 * p.meta_stride + e];
+  const int pos_hi = first_pos + L - 1;
+  const int key_lo = p.window > 0 ? max(0, first_pos - p.window + 1) : 0;
+  const int c0 = key_lo / kChunk, c1 = pos_hi / kChunk;
+  const int64_t rec0 = (static_cast<int64_t>(item) * p.Hkv + g) * p.chunks;
+  const int rows = L * G;                                       // at most 16
+  // a chunk in a stage: its rows' values of this slice [rows][kStreamSlice], then the rows' (maximum, sum) pairs, padded to 16 bytes
+  const int o_floats = rows * kStreamSlice, chunk_floats = o_floats + (rows * 2 + 3) / 4 * 4;
+  const int S = min(kStreamChunks, stage_floats / chunk_floats) & ~7;   // chunks a stage, a multiple of 8 (the host sizes it for at least 8 chunks of 16 rows)
+  auto request = [&](int first, int buf) {     // a warp brings whole chunks, 16 bytes a lane and copy
+    const int n = min(S, c1 - first + 1);
+    const uint32_t dst = smem_u32(stages + buf * stage_floats);
+    for (int c = warp; c < n; c += kStreamThreads / 32) {
+      const float* src_o = p.part_o + (rec0 + first + c) * 16 * D + d0;
+      const float* src_ml = p.part_ml + (rec0 + first + c) * 32;
+      for (int q = 4 * lane; q < chunk_floats; q += 128)
+        cp_async16(dst + (c * chunk_floats + q) * 4,
+                   q < o_floats ? src_o + (q / kStreamSlice) * D + q % kStreamSlice : src_ml + (q - o_floats));
+    }
+    cp_commit();
+  };
+  float m_row = -INFINITY;                       // (A) the running maximum of row `warp`, in every lane of warps < rows
+  // (C) thread (row r_c, j_c): j_c < kStreamSlice / 2: the outputs d0 + 2 j_c and the next; j_c == kStreamSlice / 2: the sum l (in o0)
+  constexpr int kCols = kStreamSlice / 2 + 1;
+  float o0 = 0.0f, o1 = 0.0f;
+  const int r_c = tid / kCols, j_c = tid % kCols;
+  request(c0, 0);
+  int buf = 0;
+  for (int first = c0; first <= c1; first += S, buf ^= 1) {
+    const bool more = first + S <= c1;
+    if (more) request(first + S, buf ^ 1);
+    if (more) cp_wait<1>();
+    else cp_wait<0>();
+    __syncthreads();
+    float* src = stages + buf * stage_floats;
+    const int n = min(S, c1 - first + 1);
+    // (A) warp r scans row r's maxima, 32 chunks at a time (a maximum is exact in any order)
+    for (int r = warp; r < rows; r += kStreamThreads / 32) {
+      float m_run = __shfl_sync(0xffffffffu, m_row, r / (kStreamThreads / 32));   // lane j keeps the warp's j-th row
+      for (int cb = 0; cb < n; cb += 32) {
+        const int c = cb + lane;
+        // (a chunk without a key for the row has -inf, which leaves a maximum as it is)
+        float incl = c < n ? src[c * chunk_floats + o_floats + r * 2] : -INFINITY;
+#pragma unroll
+        for (int o = 1; o < 32; o <<= 1) {
+          const float y = __shfl_up_sync(0xffffffffu, incl, o);
+          if (lane >= o) incl = fmaxf(incl, y);
+        }
+        float excl = __shfl_up_sync(0xffffffffu, incl, 1);
+        excl = lane == 0 ? m_run : fmaxf(m_run, excl);
+        if (c < n) before[c][r] = excl;
+        m_run = fmaxf(m_run, __shfl_sync(0xffffffffu, incl, 31));
+      }
+      if (lane == r / (kStreamThreads / 32)) m_row = m_run;
+    }
+    __syncthreads();
+    // (B) the factors of every (chunk, row), and the chunk's values and sum times b, in place
+    for (int i = tid; i < n * rows; i += kStreamThreads) {
+      const int c = i / rows, r = i - c * rows;
+      float* rec = src + c * chunk_floats;
+      const float m_t = rec[o_floats + r * 2];
+      float a = -1.0f;
+      if (m_t != -INFINITY) {
+        const FoldFactors f = fold_factors(before[c][r], m_t);
+        a = f.a;
+        rec[o_floats + r * 2 + 1] = __fmul_rn(rec[o_floats + r * 2 + 1], f.b);
+#pragma unroll
+        for (int q = 0; q < kStreamSlice / 4; ++q) {
+          float4 v = *reinterpret_cast<float4*>(rec + r * kStreamSlice + 4 * q);
+          v.x = __fmul_rn(v.x, f.b), v.y = __fmul_rn(v.y, f.b), v.z = __fmul_rn(v.z, f.b), v.w = __fmul_rn(v.w, f.b);
+          *reinterpret_cast<float4*>(rec + r * kStreamSlice + 4 * q) = v;
+        }
+      }
+      factor_a[c][r] = a;
+    }
+    for (int i = n * 16 + tid; i < ((n + 7) & ~7) * 16; i += kStreamThreads) factor_a[i >> 4][i & 15] = -1.0f;   // (C) reads whole groups of eight
+    __syncthreads();
+    // (C) the sums; eight chunks' operands are read before they are chained (past the stage's last chunk: a < 0)
+    if (r_c < rows) {
+      const float* wp = j_c < kStreamSlice / 2 ? src + r_c * kStreamSlice + 2 * j_c : src + o_floats + r_c * 2;   // (the sum: the pair (m_t, l_t b))
+      const float* ap = &factor_a[0][r_c];
+      int off[8];
+#pragma unroll
+      for (int u = 0; u < 8; ++u) off[u] = u * chunk_floats;
+      for (int c = 0; c < n; c += 8, wp += 8 * chunk_floats, ap += 8 * 16) {
+        float a[8];
+        float2 w[8];
+#pragma unroll
+        for (int u = 0; u < 8; ++u) {
+          a[u] = ap[u * 16];
+          w[u] = *reinterpret_cast<const float2*>(wp + off[u]);
+        }
+        if (j_c < kStreamSlice / 2) {
+#pragma unroll
+          for (int u = 0; u < 8; ++u)
+            if (a[u] >= 0.0f) o0 = __fmaf_rn(o0, a[u], w[u].x), o1 = __fmaf_rn(o1, a[u], w[u].y);
+        } else {
+#pragma unroll
+          for (int u = 0; u < 8; ++u)
+            if (a[u] >= 0.0f) o0 = __fmaf_rn(o0, a[u], w[u].y);
+        }
+      }
+    }
+    __syncthreads();   // this stage is requested again in the next round; `before` and `factor_a` are rewritten
+  }
+  if (r_c < rows && j_c == kStreamSlice / 2) l_rows[r_c] = o0;
+  __syncthreads();
+  if (r_c < rows && j_c < kStreamSlice / 2) {
+    const int pi = div_g(p, r_c);
+    const float l = l_rows[r_c];
+    *reinterpret_cast<uint32_t*>(p.out + (static_cast<int64_t>(first_row + pi) * p.Hq + g * G + r_c - pi * G) * D + d0 + 2 * j_c) =
+        pack_bf16(finish(o0, l), finish(o1, l));
+  }
+}
+
+// From this many chunks on the records are folded by attn_combine_stream_kernel, while the entries are few (with many,
+// the fold by each entry's last CTA hides under the other entries' CTAs).
+constexpr int kStreamFoldChunks = 32;
+constexpr size_t kStreamStageBytes = 40 * 1024;
+
 template <int D>
 int launch(const AttnTcParams& p, int n_tiles, int n_items, cudaStream_t stream) {
   constexpr int LD = D + 8;
@@ -226,6 +373,8 @@ int launch(const AttnTcParams& p, int n_tiles, int n_items, cudaStream_t stream)
     }
     AttnTcParams pd = p;
     pd.work = p.work + 2 * n_tiles;
+    const bool stream_fold = p.chunks >= kStreamFoldChunks && static_cast<long long>(n_items) * p.Hkv * (D / kStreamSlice) <= 2ll * sb::sm_count();
+    if (stream_fold) pd.counters = nullptr;    // every chunk leaves its record; no CTA folds
     const dim3 grid(n_items, p.Hkv, p.chunks);
     // 2 to 8 chunks whose records the kernel folds itself: the chunks of an entry as one cluster (records through
     // distributed shared memory); one chunk needs no fold, more than 8 go through records in global memory and a ticket
@@ -242,7 +391,21 @@ int launch(const AttnTcParams& p, int n_tiles, int n_items, cudaStream_t stream)
     } else {
       sb::launch_pdl(attn_decode_kernel<D, false, false>, grid, dim3(128), smem, stream, pd);
     }
-    if (pd.counters == nullptr) sb::launch_pdl(attn_combine_kernel<D>, dim3(n_items, p.Hkv), dim3(D), 0, stream, pd);
+    if (stream_fold) {
+      // two stages, each with room for all chunks (of 16 rows, in whole groups of eight) if that fits
+      const size_t chunk_bytes = static_cast<size_t>(16 * kStreamSlice + 32) * sizeof(float);
+      const size_t stage = std::min(kStreamStageBytes, static_cast<size_t>((p.chunks + 7) / 8 * 8) * chunk_bytes);
+      static sb::DeviceOnce once_stream;
+      if (once_stream.needed()) {
+        if (cudaFuncSetAttribute(attn_combine_stream_kernel<D>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)(2 * kStreamStageBytes)) != cudaSuccess)
+          return sb::fail("sb_attention_tc: cannot raise the shared memory limit");
+        once_stream.done();
+      }
+      sb::launch_pdl(attn_combine_stream_kernel<D>, dim3(n_items, p.Hkv, D / kStreamSlice), dim3(kStreamThreads), 2 * stage, stream, pd,
+                     static_cast<int>(stage / sizeof(float)));
+    } else if (pd.counters == nullptr) {
+      sb::launch_pdl(attn_combine_kernel<D>, dim3(n_items, p.Hkv), dim3(D), 0, stream, pd);
+    }
   }
   return sb::check_launch("sb_attention_tc");
 }

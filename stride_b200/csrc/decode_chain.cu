@@ -128,6 +128,7 @@ __device__ __forceinline__ Phase load_phase(const Phase* p) {
 // The workers' view of the chain for attention_tc.cuh's decode_unit: the 128 workers meet on their named barrier, and
 // the unit's inputs are there once the phase in front is complete.
 struct ChainEnv {
+  static constexpr bool kFoldAhead = false;
   const unsigned* counter;
   unsigned target;
   int* status;

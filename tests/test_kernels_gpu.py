@@ -326,6 +326,37 @@ def test_decode_attention_folds_its_chunks_three_ways_with_the_same_bits(D, Hq, 
     assert (outs[0].float().cpu() - ref).abs().max() <= 2e-2 * max(1.0, float(ref.abs().max()))
 
 
+@pytest.mark.parametrize("D,Hq,Hkv,page,window", [(64, 8, 2, 64, 0), (128, 6, 2, 32, 0), (64, 4, 4, 16, 8500)])
+def test_decode_attention_folds_the_records_of_a_long_context_three_ways_with_the_same_bits(D, Hq, Hkv, page, window):
+    """Tens of chunks an entry. Few entries: the records are folded by a kernel of its own that streams them through
+    shared memory. Many entries: by the CTA that finishes an entry last, or (no counters) by the plain fold kernel. The
+    same rows have the same bits from all three; entries of two tokens and a short entry sit in the same launch."""
+    from stride_b200.kernels import ops
+    G = Hq // Hkv
+    olds, news = [9000, 300, 8191], [1, min(2, 16 // G), 2]
+    case = _paged_case(news, olds, Hq, Hkv, D, page, torch.bfloat16, seed=D + 3, peak=(0, 700))
+    q, cache, table, meta = case["q"], case["cache"], case["table"], case["meta"]
+    E = len(news)
+    chunks = max(a + b - 1 for a, b in zip(olds, news)) // 256 + 1
+    assert chunks >= 32
+    scale = 1.0 / math.sqrt(D)
+
+    def run(copies, with_counters):
+        items = torch.arange(E, dtype=torch.int32, device=DEV).repeat(copies)   # (copies of an entry write the same rows)
+        out = torch.full_like(q, float("nan"))
+        scratch = torch.zeros(ops.attention_tc_scratch(E * copies, Hkv, chunks, D), device=DEV)
+        counters = torch.zeros(E * copies * Hkv, dtype=torch.int32, device=DEV) if with_counters else None
+        ops.attention_tc(q, out, cache, table, meta, items, 0, E * copies, chunks, scratch, Hq, Hkv, D, window, scale, counters=counters)
+        return out
+    streamed = run(1, True)
+    many = 148 // (E * Hkv) + 1          # more (entry, head) pairs than SMs: the streaming kernel is not chosen
+    assert torch.equal(run(many, True), streamed)
+    assert torch.equal(run(many, False), streamed)
+    assert torch.equal(run(1, False), streamed)
+    ref = _attention_reference(case, Hq, Hkv, D, window)
+    assert (streamed.float().cpu() - ref).abs().max() <= 2e-2 * max(1.0, float(ref.abs().max()))
+
+
 @pytest.mark.parametrize("D,Hq,Hkv,page,window", [(64, 8, 2, 16, 0), (64, 32, 8, 64, 100), (128, 6, 2, 32, 0), (64, 3, 3, 8, 0)])
 def test_decode_attention_with_rotation_fused(D, Hq, Hkv, page, window):
     """The decode kernel that rotates and appends by itself gives the same output and leaves the same cache, bit for
