@@ -241,3 +241,66 @@ def test_a_prompt_of_2048_tokens_whole_in_portions_and_in_company(dtype):
     if dtype == "bfloat16":
         from stride_b200.kernels import ops
         assert ops.gemm_tc_status() == 0 and ops.attention_tc5_status() == 0
+
+
+LONG = {"architectures": ["LlamaForCausalLM"], "hidden_size": 128, "intermediate_size": 192, "num_hidden_layers": 1,
+        "num_attention_heads": 4, "num_key_value_heads": 1, "head_dim": 64, "vocab_size": 300, "rope_theta": 10000.0,
+        "tie_word_embeddings": True, "rms_norm_eps": 1e-5, "max_position_embeddings": 9000}
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_decoding_over_a_long_context_alone_and_in_company(dtype):
+    """A context of 8,448 tokens (34 chunks of 256 keys, 67 tiles of 128) and eight decoded tokens, at a small width.
+    The decoded tokens' attention folds tens of partial results: in bfloat16 by a kernel of its own that streams the
+    chunks' records when the step's entries are few, by the entry's last CTA when they are many; in float32 by a cluster
+    of blocks per head or by one block. The long request decodes alone, beside one other request and beside eighty:
+    the same bits each time, and the plain implementation's logits within tolerance."""
+    from stride_b200 import Engine, EngineOptions, StepEntry
+    from stride_b200.weights.random_init import random_tensors
+    tensors = random_tensors(LONG, seed=8, std=0.2, gain_std=0.2)
+    cfg = plain.PlainConfig.from_dict(LONG)
+    P, N = 8448, 8
+    seq = random_tokens(cfg.vocab_size, P + N, 91)
+    places = [100, P - 1] + list(range(P, P + N))
+    act = torch.bfloat16 if dtype == "bfloat16" else None
+    want = plain.forward(cfg, tensors, seq, torch.float32, act, rows=places)
+    noise = bf16_noise(cfg, tensors, seq, rows=places) if act is not None else None
+
+    def run(portion, others):
+        eng = Engine(None, EngineOptions(dtype=dtype, max_rows=2112, max_full_rows=96, max_slots=84, kv_pages=240, page_size=64,
+                                         max_context=9000, kv_shuffle_seed=others), config=LONG, tensors=tensors)
+        cm = eng.cache
+        mine = cm.acquire_slot()
+        out = []
+        for a in range(0, P, portion):
+            b = min(P, a + portion)
+            assert cm.ensure(mine, b)
+            lg = eng.step([StepEntry(mine, a, seq[a:b], [p - a for p in places if a <= p < b])])
+            if lg is not None:
+                out.append(lg.clone())
+        company = []
+        for j in range(others):
+            slot = cm.acquire_slot()
+            toks = random_tokens(cfg.vocab_size, 3 + N, 200 + j)
+            assert cm.ensure(slot, 3)
+            eng.step([StepEntry(slot, 0, toks[:3], [])])
+            company.append((slot, toks))
+        for k in range(N):
+            entries = []
+            for slot, toks in company:
+                assert cm.ensure(slot, 4 + k)
+                entries.append(StepEntry(slot, 3 + k, toks[3 + k:4 + k], [0]))
+            assert cm.ensure(mine, P + k + 1)
+            me = StepEntry(mine, P + k, seq[P + k:P + k + 1], [0])
+            entries.insert(len(entries) // 2, me)
+            out.append(eng.step(entries)[entries.index(me)].clone()[None])
+        return torch.cat(out).cpu()
+
+    alone = run(2112, 0)
+    tol = logit_tolerance(dtype, want, noise)
+    assert (alone - want).abs().max() <= tol, f"{dtype}: {(alone - want).abs().max():.3e} > {tol:.3e}"
+    assert torch.equal(run(1000, 1), alone), "beside one other request"
+    assert torch.equal(run(2112, 80), alone), "beside eighty other requests"
+    if dtype == "bfloat16":
+        from stride_b200.kernels import ops
+        assert ops.gemm_tc_status() == 0 and ops.attention_tc5_status() == 0
