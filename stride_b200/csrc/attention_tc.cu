@@ -207,10 +207,10 @@ __global__ void __launch_bounds__(D) attn_combine_kernel(const AttnTcParams p) {
 // a warp's scan (a maximum is exact in any order); (B) the chunks' factors a = ex2(m - m'), b = ex2(m_t - m'), which hang
 // on those maxima alone, and the products v_t * b, all threads at once; (C) the sums l and o, one fused multiply-add a
 // chunk and element, which is all that has to wait for the chunk before. The operations and their operands are those
-// of fold_records. One request of 131,072 cached tokens (512 chunks): the fold by the CTA
-// that finishes last took 70 of the layer's 113 us, the keys and values themselves 43.
-// A CTA takes kStreamSlice of a head's D outputs (an SM brings in some 40 KB a microsecond, and a long context's records
-// are megabytes): the maxima and factors are computed by every slice's CTA anew, the values are shared out.
+// of fold_records. One request of 131,072 cached tokens (512 chunks): the keys and values themselves take 43 us a
+// layer; the fold by the CTA that finishes last another 63, this kernel 29.
+// A CTA takes kStreamSlice of a head's D outputs: the maxima and factors are computed by every slice's CTA anew, the
+// values are shared out.
 constexpr int kStreamThreads = 256, kStreamChunks = 128, kStreamSlice = 16;   // threads; most chunks a stage; outputs a CTA
 template <int D>
 __global__ void __launch_bounds__(kStreamThreads) attn_combine_stream_kernel(const AttnTcParams p, int stage_floats) {
