@@ -232,7 +232,7 @@ __global__ void __launch_bounds__(kStreamThreads) attn_combine_stream_kernel(con
   const int rows = L * G;                                       // at most 16
   // a chunk in a stage: its rows' values of this slice [rows][kStreamSlice], then the rows' (maximum, sum) pairs, padded to 16 bytes
   const int o_floats = rows * kStreamSlice, chunk_floats = o_floats + (rows * 2 + 3) / 4 * 4;
-  const int S = min(kStreamChunks, stage_floats / chunk_floats) & ~7;   // chunks a stage, a multiple of 8 (the host sizes it for at least 8 chunks of 16 rows)
+  const int S = max(8, min(kStreamChunks, stage_floats / chunk_floats) & ~7);   // chunks a stage, a multiple of 8 (the host sizes a stage for at least 32 chunks of 16 rows)
   auto request = [&](int first, int buf) {     // a warp brings whole chunks, 16 bytes a lane and copy
     const int n = min(S, c1 - first + 1);
     const uint32_t dst = smem_u32(stages + buf * stage_floats);
