@@ -52,6 +52,7 @@ SHAPES = {
 PROMPT = 256
 OUTPUTS = 256
 PREFILL_TOKENS = 2048
+LONG_CONTEXT = 32768     # cached tokens of the one request of the long-context decode point
 REGIONS = 5            # timed regions of K steps each; the median is reported
 FALLBACK_PEAKS = {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "source": "fallback"}
 
@@ -452,6 +453,32 @@ def main() -> int:
             cache.release_slot(slot)
         return statistics.median(times)
 
+    def long_context_run(ctx: int, steps: int = 16, portion: int = 2048):
+        """Milliseconds a decode step of one request that holds `ctx` cached tokens (its prompt fed in portions first)."""
+        o = EngineOptions(dtype="bfloat16", max_rows=portion, max_full_rows=1, max_slots=2, kv_pages=ctx // page + 8, page_size=page,
+                          max_context=ctx + 256)
+        eng = Engine.from_random(cfg, seed=0, options=o)
+        cache = eng.cache
+        slot = cache.acquire_slot()
+        toks = torch.randint(0, vocab, (ctx + steps + 8,), generator=gen).tolist()
+        for a0 in range(0, ctx, portion):
+            cache.ensure(slot, a0 + portion)
+            eng.step([StepEntry(slot, a0, toks[a0:a0 + portion], [])])
+
+        def one(k):
+            cache.ensure(slot, ctx + k + 1)
+            eng.step([StepEntry(slot, ctx + k, [toks[ctx + k]], [0])])
+        for k in range(4):
+            one(k)
+        torch.cuda.synchronize()
+        start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        start.record()
+        for k in range(4, 4 + steps):
+            one(k)
+        stop.record()
+        torch.cuda.synchronize()
+        return start.elapsed_time(stop) / steps
+
     clocks = ClockSampler()
     clocks.start()
     rs, launches = decode_run(engine, a.batch, a.steps, a.warmup, regions)
@@ -479,6 +506,14 @@ def main() -> int:
         r32, _ = decode_run(e32, 1, 16, 3, 1)
         points["decode_b1_float32"] = round(1000.0 / r32[0][0], 1)
         del e32
+        torch.cuda.empty_cache()
+        # one request with a long context (bfloat16): where a decode step is mostly the attention over its own cache
+        try:
+            lms = long_context_run(LONG_CONTEXT)
+            points[f"decode_b1_ctx{LONG_CONTEXT}"] = round(1000.0 / lms, 1)
+            points[f"hbm_frac_b1_ctx{LONG_CONTEXT}"] = round((weight_bytes + LONG_CONTEXT * kv_token_bytes) / (lms * 1e-3) / 1e9 / pk["hbm_gbs"], 4)
+        except Exception as e:          # the headline line does not hang on this point
+            points[f"error_ctx{LONG_CONTEXT}"] = str(e)[:200]
     line = {
         "metric": f"decode tok/s at batch {a.batch} (Llama 3.2 1B shape, 256-token prompts)", "value": round(value, 1), "unit": "tokens/s",
         "n_gpus": 1, "steps": a.steps, "warmup": a.warmup, "ms_per_step": round(ms, 4), "higher_is_better": True,
