@@ -155,7 +155,7 @@ def step(a) -> dict:
     cfg = dict(LLAMA_SHAPES[a.shape], num_hidden_layers=a.layers)
     B, T = a.batch, a.prefill
     opts = EngineOptions(dtype="bfloat16", max_rows=max(512, B, T), max_full_rows=max(B, 1), max_slots=B + 2,
-                         kv_pages=B * (a.context // 64 + 4) + T // 64 + 48, page_size=64, max_context=4096,
+                         kv_pages=B * (a.context // 64 + 4) + T // 64 + 48, page_size=64, max_context=max(4096, a.context + 64, T),
                          decode_chain=a.chain)
     eng = Engine.from_random(cfg, 0, opts)
     gen = torch.Generator().manual_seed(1)
