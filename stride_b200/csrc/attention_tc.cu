@@ -216,15 +216,16 @@ template <int D>
 __global__ void __launch_bounds__(kStreamThreads) attn_combine_stream_kernel(const AttnTcParams p, int stage_floats) {
   extern __shared__ __align__(16) float stages[];   // [2][stage_floats]
   __shared__ float before[kStreamChunks][16];        // [chunk of the stage][row]: the row's maximum before the chunk
-  __shared__ float factor_a[kStreamChunks][16];      // a of (chunk, row); negative: the row sees no key of the chunk
+  __shared__ float factor_a[kStreamChunks][16];      // a of (chunk, row); 1 where the row sees no key of the chunk
   __shared__ float l_rows[16];
   sb::grid_launch_dependents();
-  sb::grid_dependency_wait();
   const int item = blockIdx.x, g = blockIdx.y, d0 = blockIdx.z * kStreamSlice;
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   const int G = p.Hq / p.Hkv;
+  // (the step's work list and entries were copied in before its first kernel: read before waiting for the records)
   const int e = p.work[item];
   const int first_row = p.meta[p.meta_stride + e], L = p.meta[2 * p.meta_stride + e], first_pos = p.meta[3 * p.meta_stride + e];
+  sb::grid_dependency_wait();
   const int pos_hi = first_pos + L - 1;
   const int key_lo = p.window > 0 ? max(0, first_pos - p.window + 1) : 0;
   const int c0 = key_lo / kChunk, c1 = pos_hi / kChunk;
@@ -280,28 +281,31 @@ __global__ void __launch_bounds__(kStreamThreads) attn_combine_stream_kernel(con
       if (lane == r / (kStreamThreads / 32)) m_row = m_run;
     }
     __syncthreads();
-    // (B) the factors of every (chunk, row), and the chunk's values and sum times b, in place
-    for (int i = tid; i < n * rows; i += kStreamThreads) {
+    // (B) the factors of every (chunk, row), and the chunk's values and sum times b, in place. A chunk in which the row
+    // sees no key, and the places that fill the stage's last group of eight, get a = 1 and values -0: (C) then leaves
+    // the sums as they are, bit for bit (x * 1 + -0 = x for every x, either zero included), without asking.
+    for (int i = tid; i < ((n + 7) & ~7) * rows; i += kStreamThreads) {
       const int c = i / rows, r = i - c * rows;
       float* rec = src + c * chunk_floats;
-      const float m_t = rec[o_floats + r * 2];
-      float a = -1.0f;
+      const float m_t = c < n ? rec[o_floats + r * 2] : -INFINITY;
+      float a = 1.0f, b = 0.0f;
       if (m_t != -INFINITY) {
         const FoldFactors f = fold_factors(before[c][r], m_t);
-        a = f.a;
-        rec[o_floats + r * 2 + 1] = __fmul_rn(rec[o_floats + r * 2 + 1], f.b);
+        a = f.a, b = f.b;
+      }
+      const bool use = m_t != -INFINITY;
+      rec[o_floats + r * 2 + 1] = use ? __fmul_rn(rec[o_floats + r * 2 + 1], b) : -0.0f;
 #pragma unroll
-        for (int q = 0; q < kStreamSlice / 4; ++q) {
-          float4 v = *reinterpret_cast<float4*>(rec + r * kStreamSlice + 4 * q);
-          v.x = __fmul_rn(v.x, f.b), v.y = __fmul_rn(v.y, f.b), v.z = __fmul_rn(v.z, f.b), v.w = __fmul_rn(v.w, f.b);
-          *reinterpret_cast<float4*>(rec + r * kStreamSlice + 4 * q) = v;
-        }
+      for (int q = 0; q < kStreamSlice / 4; ++q) {
+        float4 v = *reinterpret_cast<float4*>(rec + r * kStreamSlice + 4 * q);
+        v.x = use ? __fmul_rn(v.x, b) : -0.0f, v.y = use ? __fmul_rn(v.y, b) : -0.0f;
+        v.z = use ? __fmul_rn(v.z, b) : -0.0f, v.w = use ? __fmul_rn(v.w, b) : -0.0f;
+        *reinterpret_cast<float4*>(rec + r * kStreamSlice + 4 * q) = v;
       }
       factor_a[c][r] = a;
     }
-    for (int i = n * 16 + tid; i < ((n + 7) & ~7) * 16; i += kStreamThreads) factor_a[i >> 4][i & 15] = -1.0f;   // (C) reads whole groups of eight
     __syncthreads();
-    // (C) the sums; eight chunks' operands are read before they are chained (past the stage's last chunk: a < 0)
+    // (C) the sums; eight chunks' operands are read before they are chained
     if (r_c < rows) {
       const float* wp = j_c < kStreamSlice / 2 ? src + r_c * kStreamSlice + 2 * j_c : src + o_floats + r_c * 2;   // (the sum: the pair (m_t, l_t b))
       const float* ap = &factor_a[0][r_c];
@@ -318,12 +322,10 @@ __global__ void __launch_bounds__(kStreamThreads) attn_combine_stream_kernel(con
         }
         if (j_c < kStreamSlice / 2) {
 #pragma unroll
-          for (int u = 0; u < 8; ++u)
-            if (a[u] >= 0.0f) o0 = __fmaf_rn(o0, a[u], w[u].x), o1 = __fmaf_rn(o1, a[u], w[u].y);
+          for (int u = 0; u < 8; ++u) o0 = __fmaf_rn(o0, a[u], w[u].x), o1 = __fmaf_rn(o1, a[u], w[u].y);
         } else {
 #pragma unroll
-          for (int u = 0; u < 8; ++u)
-            if (a[u] >= 0.0f) o0 = __fmaf_rn(o0, a[u], w[u].y);
+          for (int u = 0; u < 8; ++u) o0 = __fmaf_rn(o0, a[u], w[u].y);
         }
       }
     }
